@@ -1,0 +1,188 @@
+/*
+ * turbovec_b200 — C ABI of the B200 (sm_100a) encode-and-scan library.
+ *
+ * The reference (a Rust crate) has no FFI seam for this path: its Python
+ * binding calls the index types in process.  This header therefore mirrors
+ * the reference's index-level API one to one, so that a Rust `extern "C"`
+ * shim (or the pyo3 classes) can forward to it without reshaping arguments.
+ * Every entry point names the reference function it replaces; paths are
+ * relative to the reference project root.
+ *
+ * Conventions
+ *  - All pointers are HOST pointers unless the name says `_device`.
+ *  - Arrays are row-major and contiguous; the caller owns every buffer.
+ *  - Every call returns a tv_status; 0 is success.  A failing call leaves the
+ *    index exactly as it was (the reference's all-or-nothing contract,
+ *    turbovec/src/lib.rs:889-930).  tv_last_error() gives the message.
+ *  - Calls are synchronous: results are complete when the call returns.
+ *  - A handle may be used from several threads; mutating calls are exclusive,
+ *    searches are serialised per handle on the handle's stream.
+ *  - There is no CPU fallback: every compute entry point needs a CUDA device.
+ */
+#ifndef TURBOVEC_B200_H
+#define TURBOVEC_B200_H
+
+#include <stddef.h>
+#include <stdint.h>
+
+#ifdef __cplusplus
+extern "C" {
+#endif
+
+typedef struct tv_index tv_index;
+
+/* Status codes.  One per error variant of turbovec/src/error.rs. */
+typedef enum tv_status {
+    TV_OK = 0,
+    /* ConstructError, error.rs:166-183 (raised lib.rs:629-638) */
+    TV_ERR_BIT_WIDTH_OUT_OF_RANGE = 1,
+    TV_ERR_DIM_NOT_POSITIVE_MULTIPLE_OF_8 = 2,
+    TV_ERR_DIM_TOO_LARGE = 3,
+    /* AddError, error.rs:45-116 (raised lib.rs:1114-1148, id_map.rs:379-434) */
+    TV_ERR_DIM_MISMATCH = 10,
+    TV_ERR_ZERO_DIM = 11,
+    TV_ERR_DIM_NOT_MULTIPLE_OF_8 = 12,
+    TV_ERR_BUFFER_NOT_MULTIPLE_OF_DIM = 13,
+    TV_ERR_IDS_COUNT_MISMATCH = 14,
+    TV_ERR_ID_ALREADY_PRESENT = 15,
+    TV_ERR_DUPLICATE_ID_IN_BATCH = 16,
+    TV_ERR_INVALID_INPUT_VALUE = 17,
+    /* SearchError, error.rs:234-275 (raised lib.rs:1363-1433, id_map.rs:672-677) */
+    TV_ERR_ALLOWLIST_EMPTY = 20,
+    TV_ERR_UNKNOWN_ID = 21,
+    TV_ERR_QUERY_BUFFER_NOT_MULTIPLE_OF_DIM = 22,
+    TV_ERR_INVALID_QUERY_VALUE = 23,
+    TV_ERR_MASK_LENGTH_MISMATCH = 24,
+    /* contract violations the reference panics on (lib.rs:718-721, 2869-2873) */
+    TV_ERR_DIM_NOT_SET = 30,
+    TV_ERR_SLOT_OUT_OF_RANGE = 31,
+    TV_ERR_WRONG_INDEX_KIND = 32,
+    /* FromPartsError, error.rs:324-433 (checks lib.rs:2383-2492) */
+    TV_ERR_PARTS_INVALID = 40,
+    /* CalibrateError, error.rs:516-588 */
+    TV_ERR_CALIBRATE_SAMPLE_TOO_SMALL = 50,
+    TV_ERR_CALIBRATE_DEGENERATE_SAMPLE = 51,
+    TV_ERR_CALIBRATE_NOT_EMPTY = 52,
+    /* this library */
+    TV_ERR_INVALID_ARGUMENT = 90,
+    TV_ERR_CUDA = 91,
+    TV_ERR_OUT_OF_MEMORY = 92,
+    TV_ERR_UNSUPPORTED = 93,
+    TV_ERR_DEVICE_TIMEOUT = 94
+} tv_status;
+
+/* Index kinds: turbovec/src/lib.rs:295 (TurboQuantIndex), id_map.rs:221 (IdMapIndex). */
+enum { TV_KIND_POSITIONAL = 0, TV_KIND_IDMAP = 1 };
+
+/*
+ * Score arithmetic.  The reference picks one of its kernel families from the
+ * host CPU's features (turbovec/src/pack.rs:1189-1263, search.rs:2975-2980);
+ * each rounds scores differently.  AUTO is what an x86 host with AVX-512
+ * VBMI+VNNI runs: permute-dot int8 for 4-bit when ngroups % 4 == 0, the u8
+ * LUT scan with (f32)isum*scale+bias for 2/3-bit when ngroups % 4 == 0, and
+ * the u8 LUT scan with one fma per 256 byte-groups otherwise.
+ */
+enum {
+    TV_SCORE_AUTO = 0,
+    TV_SCORE_PERMUTE_DOT = 1,
+    TV_SCORE_LUT_MULADD = 2,
+    TV_SCORE_LUT_FLUSH = 3
+};
+
+/* Options for tv_set_option. */
+enum {
+    TV_OPT_SCORE_MODE = 1,      /* one of TV_SCORE_* */
+    TV_OPT_MMA_MIN_BATCH = 2,   /* query batches of at least this size use the expanded-int8 tensor path (0 = never) */
+    TV_OPT_FORCE_CAREFUL = 3    /* 1: run the candidate-overflow recovery schedule always (testing) */
+};
+
+/* ---- construction: TurboQuantIndex::new / new_lazy (lib.rs:629, 670), IdMapIndex::new (id_map.rs:278) ---- */
+/* dim == 0 creates a lazy index whose dimension is fixed by the first add.  device = CUDA ordinal. */
+int tv_index_create(size_t dim, int bit_width, int kind, int device, tv_index **out);
+void tv_index_destroy(tv_index *h);
+
+/* Message of the most recent failing call on this handle (or of the last failed create when h == NULL). */
+const char *tv_last_error(const tv_index *h);
+/* Offender of the last TV_ERR_INVALID_INPUT_VALUE / TV_ERR_INVALID_QUERY_VALUE (error.rs:104-116, 262-270),
+ * or id of the last TV_ERR_ID_ALREADY_PRESENT / DUPLICATE_ID_IN_BATCH / UNKNOWN_ID in *id. */
+void tv_error_detail(const tv_index *h, size_t *vector_index, size_t *coord_index, float *value, uint64_t *id);
+
+/* ---- introspection: len / dim_opt / bit_width (lib.rs:3031-3064) ---- */
+size_t tv_len(const tv_index *h);
+size_t tv_dim(const tv_index *h);      /* 0 while lazy */
+int tv_bit_width(const tv_index *h);
+int tv_kind(const tv_index *h);
+int tv_set_option(tv_index *h, int option, int64_t value);
+int64_t tv_get_option(const tv_index *h, int option);
+
+/* ---- ingest: add_2d (lib.rs:1114-1210) -> encode_and_append (lib.rs:823) -> encode::encode (encode.rs:510) ---- */
+int tv_add(tv_index *h, const float *vectors, size_t n, size_t dim);
+/* add_with_ids_2d (id_map.rs:373-469); TV_KIND_IDMAP only. */
+int tv_add_with_ids(tv_index *h, const float *vectors, size_t n, size_t dim, const uint64_t *ids);
+/* Same as tv_add but `vectors` is device memory on the handle's device.  The finite/|x|<1e16 check of
+ * encode.rs:58-74 runs on the device.  Used when the producer already lives on the GPU. */
+int tv_add_device(tv_index *h, const float *vectors_device, size_t n, size_t dim);
+
+/* ---- removal: swap_remove (lib.rs:2864-3028), IdMapIndex::remove (id_map.rs:520-567) ---- */
+int tv_swap_remove(tv_index *h, size_t slot, size_t *moved_from);
+int tv_remove(tv_index *h, uint64_t id, int *removed);
+int tv_contains(const tv_index *h, uint64_t id, int *present);         /* id_map.rs:593 */
+/* Copies slot_to_id[0..len) (id_map.rs:631 iter_ids order). */
+int tv_ids(const tv_index *h, uint64_t *ids_out, size_t capacity);
+
+/* ---- search: try_search_with_mask (lib.rs:1345-1485) -> search::search (search.rs:3206) ----
+ * mask_bool: NULL or `mask_len` bytes, non-zero = slot allowed (must equal len, lib.rs:1427-1433).
+ * scores_out / slots_out: nq * min(k, len) entries; row stride is *k_eff = min(k, len, n_allowed).
+ * A lazy or empty index yields k_eff = 0 and TV_OK (lib.rs:1355-1402). */
+int tv_search(tv_index *h, const float *queries, size_t nq, size_t dim, size_t k, const uint8_t *mask_bool,
+              size_t mask_len, float *scores_out, int64_t *slots_out, size_t *k_eff);
+/* Same with the mask already packed: bit i of little-endian u64 word i/64 = slot i (search.rs:2996-3004). */
+int tv_search_mask_words(tv_index *h, const float *queries, size_t nq, size_t dim, size_t k,
+                         const uint64_t *mask_words, size_t n_words, float *scores_out, int64_t *slots_out,
+                         size_t *k_eff);
+/* try_search_with_allowlist (id_map.rs:664-712); allow_ids == NULL means unfiltered.  ids_out receives ids. */
+int tv_search_allowlist(tv_index *h, const float *queries, size_t nq, size_t dim, size_t k,
+                        const uint64_t *allow_ids, size_t n_allow, float *scores_out, uint64_t *ids_out,
+                        size_t *k_eff);
+/* Device-resident variant: queries, optional mask words, scores and slots all in device memory.
+ * Nothing crosses PCIe except the launch parameters and one status word. */
+int tv_search_device(tv_index *h, const float *queries_device, size_t nq, size_t k,
+                     const uint64_t *mask_words_device, float *scores_out_device, int64_t *slots_out_device,
+                     size_t *k_eff);
+
+/* ---- warm-up: prepare (lib.rs:1496) — builds tables and caches the first search would build ---- */
+int tv_prepare(tv_index *h);
+
+/* ---- raw parts: codes_blocked_seq / scales / packed_codes / from_parts (lib.rs:2088, 2533, 2528, 2371) ----
+ * blocked: ceil(len/32) * ngroups * 32 bytes in the reference's sequential-blocked layout
+ * (pack.rs:340-361); scales: len floats. */
+size_t tv_blocked_bytes(const tv_index *h);
+int tv_export_blocked(const tv_index *h, uint8_t *blocked_out, size_t blocked_capacity, float *scales_out,
+                      size_t scales_capacity);
+/* Bit-plane rows as packed_codes() returns them: len * bit_width*dim/8 bytes (encode.rs:1464-1470). */
+int tv_export_packed(const tv_index *h, uint8_t *packed_out, size_t capacity);
+/* from_parts: replaces the contents of an EMPTY index with n rows given as bit-plane rows + scales
+ * (+ ids for TV_KIND_IDMAP, else NULL).  Validation follows lib.rs:2383-2492. */
+int tv_import_packed(tv_index *h, size_t dim, const uint8_t *packed, size_t n, const float *scales,
+                     const uint64_t *ids);
+/* Codebook the index encodes against: codebook_for_write (lib.rs:2108).  boundaries: 2^bits-1, centroids: 2^bits. */
+int tv_codebook(tv_index *h, float *boundaries_out, float *centroids_out);
+/* Rotate rows exactly as queries are rotated (Rotation::apply, rotation.rs:202) — diagnostic entry point. */
+int tv_rotate(tv_index *h, const float *rows, size_t n, size_t dim, float *rotated_out);
+
+/* ---- TQ+ calibration: calibrate_2d (lib.rs:2599-2723) on an EMPTY index; tqplus_shift/scale (lib.rs:2535-2545) ---- */
+int tv_calibrate(tv_index *h, const float *sample, size_t n, size_t dim);
+int tv_calibration(const tv_index *h, float *shift_out, float *scale_out, size_t capacity, int *is_calibrated);
+int tv_set_calibration(tv_index *h, size_t dim, const float *shift, const float *scale);
+
+/* ---- instrumentation ---- */
+/* Kernels of this library launched on this handle since creation (for benchmark bookkeeping). */
+uint64_t tv_launch_count(const tv_index *h);
+/* Device time of the kernels of the last search / add call, from CUDA events on the handle's stream (ms). */
+float tv_last_kernel_ms(const tv_index *h);
+const char *tv_version(void);
+
+#ifdef __cplusplus
+}
+#endif
+#endif /* TURBOVEC_B200_H */

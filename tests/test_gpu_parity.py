@@ -1,0 +1,336 @@
+"""CUDA path vs the CPU oracle through the C ABI (via the ctypes classes): bit-exact codes, scales and
+rotation; scores and id lists identical under the oracle's own arithmetic."""
+import numpy as np
+import pytest
+
+from oracle import oracle as O
+from tests.golden import reference_goldens as G
+from tests.util import anisotropic, assert_topk_equal, clustered
+
+pytestmark = pytest.mark.gpu
+
+
+@pytest.fixture(scope="module")
+def T():
+    import turbovec_b200
+    return turbovec_b200
+
+
+# ---------------------------------------------------------------- rotation
+@pytest.mark.parametrize("dim", [8, 16, 24, 64, 128, 200, 256, 768, 1000, 1536, 2048, 3072, 4096, 6144])
+def test_rotation_bit_exact(T, dim):
+    rng = np.random.default_rng(dim)
+    x = (rng.standard_normal((5, dim)) * 10 ** rng.uniform(-2, 2, (5, 1))).astype(np.float32)
+    idx = T.TurboQuantIndex(dim, 4)
+    idx.prepare()
+    got = idx.rotate(x)
+    want = O.rotate_rows(x)
+    assert np.array_equal(got.view(np.uint32), want.view(np.uint32))
+
+
+def test_rotation_goldens_on_device(T):
+    for dim, inp, gold in [(8, [i - 3.5 for i in range(8)], G.ROTATION_DIM8),
+                           (24, [((i * 7) % 11) - 5.0 for i in range(24)], G.ROTATION_DIM24),
+                           (64, [((i * 13) % 29) - 14.0 for i in range(64)], G.ROTATION_DIM64)]:
+        idx = T.TurboQuantIndex(dim, 2)
+        idx.prepare()
+        out = idx.rotate(np.array([inp], dtype=np.float32))
+        assert [int(v) for v in out.view(np.uint32)[0]] == gold
+
+
+# ---------------------------------------------------------------- ingest
+@pytest.mark.parametrize("row", G.ENCODE_FINGERPRINT, ids=lambda r: f"d{r[0]}b{r[1]}")
+def test_encode_fingerprint_on_device(T, row):
+    """The reference's frozen encode fingerprint reproduced by the ingest kernel (calibrated encode)."""
+    dim, bits, g_bnd, g_cent, _g_cal, g_codes, g_scales, _ = row
+    x = O.lcg_vectors(2000, dim, G.cell_seed(dim, bits))
+    shift, scale = O.fit_calibration(x, bits)      # the fit itself is host-side and checked in the oracle tests
+    idx = T.TurboQuantIndex(dim, bits)
+    idx.set_calibration(shift, scale)
+    idx.add(x)
+    bnd, cent = idx.codebook()
+    assert O.fnv1a(bnd) == g_bnd and O.fnv1a(cent) == g_cent
+    assert O.fnv1a(idx.packed_codes()) == g_codes
+    assert O.fnv1a(idx.scales()) == g_scales
+
+
+@pytest.mark.parametrize("dim,bits", [(1536, 4), (1536, 2), (3072, 2), (200, 4), (200, 2), (600, 3), (64, 4), (4096, 4)])
+def test_ingest_matches_oracle(T, dim, bits):
+    n = 1000 + 37
+    x = anisotropic(n, dim, seed=dim + bits) if dim != 200 else clustered(n, dim, seed=3)
+    enc = O.encode(x, bits)
+    want_blocked = O.packed_to_blocked(enc["packed"], bits, dim)
+    idx = T.TurboQuantIndex(dim, bits)
+    # ragged batches: partial head blocks, single rows, block-aligned runs
+    cuts = [0, 1, 5, 32, 33, 100, 517, 1000, n]
+    for a, b in zip(cuts[:-1], cuts[1:]):
+        idx.add(x[a:b])
+    assert len(idx) == n
+    got = idx.codes_blocked_seq()
+    mism = int((got != want_blocked).sum())
+    assert mism == 0, f"{mism} code bytes differ"
+    assert np.array_equal(idx.scales().view(np.uint32), enc["scales"].view(np.uint32))
+    assert np.array_equal(idx.packed_codes(), enc["packed"])
+
+
+def test_ingest_zero_and_tiny_rows(T):
+    x = anisotropic(40, 256, seed=1)
+    x[3] = 0.0
+    x[17] = 1e-23
+    enc = O.encode(x, 4)
+    idx = T.TurboQuantIndex(256, 4)
+    idx.add(x)
+    s = idx.scales()
+    assert s[3] == 0.0 and s[17] == 0.0
+    assert np.array_equal(s.view(np.uint32), enc["scales"].view(np.uint32))
+    assert np.array_equal(idx.packed_codes(), enc["packed"])
+
+
+def test_add_rejects_invalid_and_leaves_index_unchanged(T):
+    x = anisotropic(70, 128, seed=2)
+    idx = T.TurboQuantIndex(128, 4)
+    idx.add(x[:40])
+    before_codes, before_scales = idx.codes_blocked_seq(), idx.scales()
+    bad = x[40:].copy()
+    bad[7, 5] = np.nan
+    bad[9, 0] = np.inf
+    with pytest.raises(ValueError, match="vector 7 coordinate 5"):
+        idx.add(bad)
+    assert len(idx) == 40
+    assert np.array_equal(idx.codes_blocked_seq(), before_codes)
+    assert np.array_equal(idx.scales(), before_scales)
+    idx.add(x[40:])
+    enc = O.encode(x, 4)
+    assert np.array_equal(idx.codes_blocked_seq(), O.packed_to_blocked(enc["packed"], 4, 128))
+
+
+# ---------------------------------------------------------------- search
+def _build(T, x, bits, kind="pos", ids=None):
+    dim = x.shape[1]
+    if kind == "pos":
+        idx = T.TurboQuantIndex(dim, bits)
+        idx.add(x)
+    else:
+        idx = T.IdMapIndex(dim, bits)
+        idx.add_with_ids(x, ids)
+    return idx
+
+
+def _oracle_search(x, q, bits, k, mask=None, mode=O.MODE_AUTO):
+    n, dim = x.shape
+    enc = O.encode(x, bits)
+    blocked = O.packed_to_blocked(enc["packed"], bits, dim)
+    words = None if mask is None else O.pack_mask(mask)
+    return O.search(q, blocked, enc["scales"], n, dim, bits, k, mask_words=words, mode=mode)
+
+
+@pytest.mark.parametrize("dim,bits,n,nq", [
+    (1536, 4, 3000, 1), (1536, 4, 3000, 7), (1536, 4, 5003, 70), (256, 4, 4100, 33), (200, 4, 2000, 5),
+    (1536, 2, 3000, 1), (1536, 2, 3000, 9), (3072, 2, 1500, 6), (200, 2, 2500, 6), (600, 3, 2000, 5), (1024, 3, 1500, 3),
+])
+def test_search_matches_oracle(T, dim, bits, n, nq):
+    x = anisotropic(n, dim, seed=11)
+    q = anisotropic(nq, dim, seed=11, offset=1000)
+    idx = _build(T, x, bits)
+    for k in (1, 10, 100):
+        s, i = idx.search(q, k)
+        rs, ri = _oracle_search(x, q, bits, k)
+        assert s.shape == (nq, min(k, n))
+        assert np.array_equal(i, ri), f"k={k}: id lists differ"
+        assert np.array_equal(s, rs), f"k={k}: scores differ"
+
+
+def test_search_large_n_chunk_schedule(T):
+    """Enough vectors for several growing chunks, and the bounded recovery schedule gives the same answer."""
+    n, dim, nq = 200_000, 64, 12
+    x = anisotropic(n, dim, seed=5)
+    q = anisotropic(nq, dim, seed=5, offset=9)
+    idx = _build(T, x, 4)
+    s, i = idx.search(q, 10)
+    rs, ri = _oracle_search(x, q, 4, 10)
+    assert np.array_equal(i, ri) and np.array_equal(s, rs)
+    idx.set_option(T.OPT_FORCE_CAREFUL, 1)
+    s2, i2 = idx.search(q, 10)
+    assert np.array_equal(i2, ri) and np.array_equal(s2, rs)
+
+
+def test_search_adversarial_order_overflows_and_recovers(T):
+    """Rows sorted by increasing similarity to the query overflow the candidate buffer of the growing
+    schedule; the bounded schedule must then return the exact answer."""
+    n, dim = 150_000, 64
+    x = anisotropic(n, dim, seed=8)
+    q = anisotropic(1, dim, seed=8, offset=3)
+    order = np.argsort(x @ q[0])
+    x = np.ascontiguousarray(x[order])
+    idx = _build(T, x, 4)
+    s, i = idx.search(q, 10)
+    rs, ri = _oracle_search(x, q, 4, 10)
+    assert np.array_equal(i, ri) and np.array_equal(s, rs)
+
+
+@pytest.mark.parametrize("bits", [4, 2])
+def test_filtered_search(T, bits):
+    n, dim, nq = 6000, 256, 9
+    x = anisotropic(n, dim, seed=21)
+    q = anisotropic(nq, dim, seed=21, offset=5)
+    idx = _build(T, x, bits)
+    rng = np.random.default_rng(0)
+    for sel in (0.001, 0.01, 0.1, 0.5, 1.0):
+        mask = rng.random(n) < sel
+        if not mask.any():
+            mask[123] = True
+        for k in (10, 100):
+            s, i = idx.search(q, k, mask=mask)
+            rs, ri = _oracle_search(x, q, bits, k, mask=mask)
+            assert s.shape == (nq, min(k, int(mask.sum())))
+            assert np.array_equal(i, ri) and np.array_equal(s, rs)
+            assert mask[i].all()
+            # the packed-word entry point agrees
+            s2, i2 = idx.search_mask_words(q, k, O.pack_mask(mask))
+            assert np.array_equal(i2, ri) and np.array_equal(s2, rs)
+    # contiguous range and all-false
+    mask = np.zeros(n, bool)
+    mask[1000:1007] = True
+    s, i = idx.search(q, 10, mask=mask)
+    assert s.shape == (nq, 7) and set(i[0]) == set(range(1000, 1007))
+    s, i = idx.search(q, 10, mask=np.zeros(n, bool))
+    assert s.shape == (nq, 0) and i.shape == (nq, 0)
+
+
+def test_search_edge_cases(T):
+    dim = 128
+    x = anisotropic(100, dim, seed=4)
+    idx = T.TurboQuantIndex(dim, 4)
+    q = anisotropic(3, dim, seed=4, offset=2)
+    s, i = idx.search(q, 5)                       # empty index
+    assert s.shape == (3, 0)
+    idx.add(x)
+    s, i = idx.search(q, 1000)                    # k clamps to n
+    assert s.shape == (3, 100)
+    assert np.all(np.diff(s, axis=1) <= 0)
+    s, i = idx.search(np.zeros((0, dim), np.float32), 5)
+    assert s.shape == (0, 5)
+    # zero query: all scores tie, slots 0..k-1 by the tie rule
+    s, i = idx.search(np.zeros((1, dim), np.float32), 7)
+    assert list(i[0]) == list(range(7)) and np.all(np.isfinite(s))
+    with pytest.raises(ValueError):
+        idx.search(np.full((1, dim), np.nan, np.float32), 3)
+    with pytest.raises(ValueError):
+        idx.search(q[:, :64].copy(), 3)
+    with pytest.raises(ValueError):
+        idx.search(q, 3, mask=np.ones(99, bool))
+    lazy = T.TurboQuantIndex(None, 4)
+    s, i = lazy.search(q, 3)
+    assert s.shape == (3, 0)
+
+
+def test_duplicate_vectors_tie_by_slot(T):
+    dim = 128
+    base = anisotropic(10, dim, seed=6)
+    x = np.ascontiguousarray(np.tile(base, (20, 1)))   # every vector 20 times
+    idx = _build(T, x, 4)
+    q = base[:2].copy()
+    s, i = idx.search(q, 25)
+    rs, ri = _oracle_search(x, q, 4, 25)
+    assert np.array_equal(i, ri) and np.array_equal(s, rs)
+
+
+def test_batch_equals_single(T):
+    dim, n = 512, 3000
+    x = anisotropic(n, dim, seed=9)
+    q = anisotropic(19, dim, seed=9, offset=1)
+    idx = _build(T, x, 4)
+    s, i = idx.search(q, 10)
+    for j in range(19):
+        s1, i1 = idx.search(q[j:j + 1], 10)
+        assert np.array_equal(i1[0], i[j]) and np.array_equal(s1[0], s[j])
+
+
+# ---------------------------------------------------------------- mutation and ids
+def test_swap_remove(T):
+    dim, n = 128, 70
+    x = anisotropic(n, dim, seed=12)
+    idx = _build(T, x, 4)
+    keep = list(range(n))
+    for victim in (5, 68, 0, 31, 32):
+        moved = idx.swap_remove(victim)
+        assert moved == len(keep) - 1
+        keep[victim] = keep[-1]
+        keep.pop()
+        enc = O.encode(x[keep], 4)
+        assert np.array_equal(idx.codes_blocked_seq(), O.packed_to_blocked(enc["packed"], 4, dim))
+        assert np.array_equal(idx.scales(), enc["scales"])
+    with pytest.raises(IndexError):
+        idx.swap_remove(len(keep))
+
+
+def test_idmap_semantics(T):
+    dim, n = 128, 500
+    x = anisotropic(n, dim, seed=14)
+    ids = (np.random.default_rng(1).permutation(n) + 10**9).astype(np.uint64)
+    idx = _build(T, x, 4, "idmap", ids)
+    q = anisotropic(4, dim, seed=14, offset=8)
+    s, got = idx.search(q, 10)
+    rs, ri = _oracle_search(x, q, 4, 10)
+    assert np.array_equal(got, ids[ri]) and np.array_equal(s, rs)
+    allow = ids[::7].copy()
+    mask = np.zeros(n, bool)
+    mask[::7] = True
+    s, got = idx.search(q, 10, allowlist=allow)
+    rs, ri = _oracle_search(x, q, 4, 10, mask=mask)
+    assert np.array_equal(got, ids[ri]) and np.array_equal(s, rs)
+    # n_allowed < k
+    s, got = idx.search(q, 10, allowlist=ids[:3].copy())
+    assert s.shape == (4, 3) and set(got[0]) == set(ids[:3])
+    with pytest.raises(KeyError):
+        idx.search(q, 10, allowlist=np.array([5], np.uint64))
+    with pytest.raises(ValueError):
+        idx.search(q, 10, allowlist=np.array([], np.uint64))
+    with pytest.raises(ValueError, match="already present"):
+        idx.add_with_ids(x[:1], ids[:1].copy())
+    with pytest.raises(ValueError, match="twice"):
+        idx.add_with_ids(x[:2], np.array([1, 1], np.uint64))
+    assert len(idx) == n
+    # removal moves the last row into the hole
+    assert idx.remove(int(ids[10])) is True
+    assert idx.remove(int(ids[10])) is False
+    assert int(ids[10]) not in idx and int(ids[-1]) in idx
+    cur = list(ids)
+    cur[10] = cur[-1]
+    cur.pop()
+    assert list(idx.ids()) == cur
+    xs = x.copy()
+    xs[10] = xs[-1]
+    xs = xs[:-1]
+    s, got = idx.search(q, 10)
+    rs, ri = _oracle_search(xs, q, 4, 10)
+    assert np.array_equal(got, np.array(cur, np.uint64)[ri]) and np.array_equal(s, rs)
+
+
+def test_from_parts_roundtrip(T):
+    dim, n = 256, 333
+    x = anisotropic(n, dim, seed=15)
+    a = _build(T, x, 2)
+    b = T.TurboQuantIndex.from_parts(dim, 2, a.packed_codes(), a.scales())
+    assert np.array_equal(a.codes_blocked_seq(), b.codes_blocked_seq())
+    q = anisotropic(3, dim, seed=15, offset=1)
+    sa, ia = a.search(q, 10)
+    sb, ib = b.search(q, 10)
+    assert np.array_equal(ia, ib) and np.array_equal(sa, sb)
+
+
+def test_recall_at_10_matches_reference_floor(T):
+    """recall@10 against exact fp32 inner products equals the oracle's (same codes, same arithmetic) and
+    clears the floors of turbovec/tests/recall_sanity.rs:97-118 on clustered data."""
+    n, dim, nq = 2000, 1536, 50
+    x = clustered(n, dim, seed=77, n_clusters=50)
+    q = clustered(nq, dim, seed=77, n_clusters=50, offset=4)
+    truth = np.argsort(-(q @ x.T), axis=1)[:, :10]
+    for bits, floor in ((4, 0.70), (3, 0.58), (2, 0.40)):
+        idx = _build(T, x, bits)
+        _, i = idx.search(q, 10)
+        _, ri = _oracle_search(x, q, bits, 10)
+        rec = np.mean([len(set(i[j]) & set(truth[j])) / 10 for j in range(nq)])
+        rec_ref = np.mean([len(set(ri[j]) & set(truth[j])) / 10 for j in range(nq)])
+        assert abs(rec - rec_ref) <= 0.002
+        assert rec >= floor

@@ -1,0 +1,87 @@
+"""CPU-only checks: the shared library loads and exports the whole C ABI, host-side argument validation
+works without a device, and the product never reaches for the oracle."""
+import ctypes
+import os
+import re
+
+import numpy as np
+import pytest
+
+ROOT = os.path.dirname(os.path.dirname(os.path.abspath(__file__)))
+
+
+@pytest.fixture(scope="module")
+def lib():
+    from turbovec_b200 import build, _native
+    build.build()
+    return _native.load()
+
+
+def test_every_declared_symbol_is_exported(lib):
+    header = open(os.path.join(ROOT, "include", "turbovec_b200.h")).read()
+    declared = set(re.findall(r"\b(tv_[a-z_0-9]+)\s*\(", header))
+    declared -= {"tv_status", "tv_index"}
+    assert len(declared) >= 30
+    from turbovec_b200 import _native
+    assert declared == set(_native.SIGNATURES), declared ^ set(_native.SIGNATURES)
+    for name in declared:
+        assert hasattr(lib, name), name
+
+
+def test_constructor_validation_needs_no_device(lib):
+    h = ctypes.c_void_p()
+    assert lib.tv_index_create(1536, 5, 0, 0, ctypes.byref(h)) == 1       # BitWidthOutOfRange
+    assert lib.tv_index_create(1537, 4, 0, 0, ctypes.byref(h)) == 2       # DimNotPositiveMultipleOf8
+    assert lib.tv_index_create(16392, 4, 0, 0, ctypes.byref(h)) == 3      # DimTooLarge
+    assert b"16384" in lib.tv_last_error(None)
+
+
+def test_no_cpu_fallback_without_device():
+    import torch
+    if torch.cuda.is_available():
+        pytest.skip("a device is present")
+    import turbovec_b200 as T
+    with pytest.raises(RuntimeError, match="no CPU path"):
+        T.TurboQuantIndex(64, 4)
+
+
+def test_python_argument_errors():
+    import turbovec_b200 as T
+    with pytest.raises(TypeError):
+        T._f32_2d("vectors", np.zeros((2, 8), np.float64))
+    with pytest.raises(ValueError):
+        T._f32_2d("vectors", np.zeros((8, 2), np.float32).T)
+    with pytest.raises(TypeError):
+        T._size("k", 1.5)
+    with pytest.raises(ValueError):
+        T._size("k", -1)
+
+
+def test_product_does_not_touch_the_oracle():
+    pkg = os.path.join(ROOT, "turbovec_b200")
+    for dirpath, _, files in os.walk(pkg):
+        if os.path.basename(dirpath) == "build":
+            continue
+        for f in files:
+            if f.endswith((".py", ".cu", ".cuh", ".cpp", ".hpp", ".h")):
+                text = open(os.path.join(dirpath, f)).read()
+                assert "oracle" not in text.lower(), f"{f} mentions the oracle"
+
+
+def test_key_order_matches_reference_order():
+    """(score desc, slot asc) <=> ascending u64 key; checked on the host twin of the device transform."""
+    import struct
+
+    def desc_bits(s):
+        if s == 0.0:
+            s = 0.0
+        u = struct.unpack("<I", struct.pack("<f", s))[0]
+        asc = (~u & 0xFFFFFFFF) if u & 0x80000000 else (u | 0x80000000)
+        return ~asc & 0xFFFFFFFF
+
+    vals = [-np.inf, -3.5, -1e-30, -0.0, 0.0, 1e-38, 2.0, 2.0000002, np.inf]
+    keys = [(desc_bits(np.float32(v)) << 32) | 5 for v in vals]
+    assert keys[3] == keys[4]                                   # the two zeros tie
+    dedup = [k for j, k in enumerate(keys) if j != 3]
+    assert dedup == sorted(dedup, reverse=True)                 # larger score -> smaller key
+    assert ((desc_bits(np.float32(1.0)) << 32) | 3) < ((desc_bits(np.float32(1.0)) << 32) | 4)

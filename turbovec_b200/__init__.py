@@ -1,0 +1,276 @@
+"""turbovec_b200 — B200-native encode-and-scan path of turbovec behind the reference's index API.
+
+The two classes mirror the reference's Python classes (turbovec-python/src/lib.rs:416-947 and
+:952-1540): same method names, argument meaning, result shapes and exception types.  Everything
+below them runs in libturbovec_b200.so on the GPU; nothing is computed in Python.
+"""
+from __future__ import annotations
+
+import ctypes as C
+
+import numpy as np
+
+from . import _native
+from ._native import (OPT_FORCE_CAREFUL, OPT_MMA_MIN_BATCH, OPT_SCORE_MODE, SCORE_AUTO, SCORE_LUT_FLUSH,
+                      SCORE_LUT_MULADD, SCORE_PERMUTE_DOT)
+
+__all__ = ["TurboQuantIndex", "IdMapIndex", "BATCH_CHUNK_SIZE"]
+
+# turbovec-python/python/turbovec/__init__.py:17 — batches above this are fed in slices
+BATCH_CHUNK_SIZE = 4096
+
+
+def _f32_2d(name: str, a) -> np.ndarray:
+    # turbovec-python/src/lib.rs:56-63: float32, 2-D, C-contiguous, no silent conversion
+    if not isinstance(a, np.ndarray) or a.dtype != np.float32 or a.ndim != 2:
+        kind = f"{type(a).__name__}" if not isinstance(a, np.ndarray) else f"ndarray of dtype {a.dtype}, {a.ndim}-D"
+        raise TypeError(f"{name} must be a 2-D float32 numpy array, got {kind}")
+    if not a.flags.c_contiguous:
+        raise ValueError(f"{name} must be C-contiguous")
+    return a
+
+
+def _typed_1d(name: str, a, dtype, label: str) -> np.ndarray:
+    if not isinstance(a, np.ndarray) or a.dtype != dtype or a.ndim != 1:
+        kind = f"{type(a).__name__}" if not isinstance(a, np.ndarray) else f"ndarray of dtype {a.dtype}, {a.ndim}-D"
+        raise TypeError(f"{name} must be a 1-D {label} numpy array, got {kind}")
+    if not a.flags.c_contiguous:
+        raise ValueError(f"{name} must be C-contiguous")
+    return a
+
+
+def _size(name: str, v) -> int:
+    # turbovec-python/src/lib.rs:153-179
+    if isinstance(v, bool) or not isinstance(v, (int, np.integer)):
+        raise TypeError(f"{name} must be an int, got {type(v).__name__}")
+    if v < 0:
+        raise ValueError(f"{name} must be non-negative, got {v}")
+    return int(v)
+
+
+def _ptr(a):
+    return None if a is None else a.ctypes.data_as(C.c_void_p)
+
+
+class _Base:
+    _KIND = 0
+
+    def __init__(self, dim=None, bit_width=None, *, device: int = 0):
+        self._lib = _native.load()
+        self._h = C.c_void_p()
+        d = 0 if dim is None else _size("dim", dim)
+        if dim is not None and d == 0:
+            raise ValueError("dim must be a positive multiple of 8, got 0")
+        bits = 4 if bit_width is None else _size("bit_width", bit_width)
+        rc = self._lib.tv_index_create(d, bits, self._KIND, int(device), C.byref(self._h))
+        if rc != 0:
+            msg = self._lib.tv_last_error(None).decode()
+            raise (RuntimeError if rc >= 90 else ValueError)(msg)
+
+    def __del__(self):
+        h, self._h = getattr(self, "_h", None), None
+        if h:
+            self._lib.tv_index_destroy(h)
+
+    # ---- helpers ----
+    def _check(self, rc: int):
+        if rc == 0:
+            return
+        msg = self._lib.tv_last_error(self._h).decode()
+        if rc in _native.ERR_ID_KEYERROR:
+            raise KeyError(msg)
+        if rc in _native.ERR_INDEXERROR:
+            raise IndexError(msg)
+        if rc >= 90:
+            raise RuntimeError(msg)
+        raise ValueError(msg)
+
+    def __len__(self) -> int:
+        return int(self._lib.tv_len(self._h))
+
+    @property
+    def dim(self):
+        d = int(self._lib.tv_dim(self._h))
+        return d if d else None
+
+    @property
+    def bit_width(self) -> int:
+        return int(self._lib.tv_bit_width(self._h))
+
+    @property
+    def calibration_state(self) -> str:
+        flag = C.c_int(0)
+        self._lib.tv_calibration(self._h, None, None, 0, C.byref(flag))
+        return "calibrated" if flag.value else "uncalibrated"
+
+    def prepare(self) -> None:
+        self._check(self._lib.tv_prepare(self._h))
+
+    def set_option(self, option: int, value: int) -> None:
+        self._check(self._lib.tv_set_option(self._h, option, value))
+
+    def get_option(self, option: int) -> int:
+        return int(self._lib.tv_get_option(self._h, option))
+
+    @property
+    def launch_count(self) -> int:
+        return int(self._lib.tv_launch_count(self._h))
+
+    @property
+    def last_kernel_ms(self) -> float:
+        return float(self._lib.tv_last_kernel_ms(self._h))
+
+    def set_calibration(self, shift: np.ndarray, scale: np.ndarray) -> None:
+        shift = _typed_1d("shift", shift, np.float32, "float32")
+        scale = _typed_1d("scale", scale, np.float32, "float32")
+        if shift.shape != scale.shape:
+            raise ValueError("shift and scale must have the same length")
+        self._check(self._lib.tv_set_calibration(self._h, shift.size, _ptr(shift), _ptr(scale)))
+
+    def calibrate(self, sample: np.ndarray) -> None:
+        sample = _f32_2d("sample", sample)
+        self._check(self._lib.tv_calibrate(self._h, _ptr(sample), sample.shape[0], sample.shape[1]))
+
+    def codebook(self):
+        bits = self.bit_width
+        b = np.empty((1 << bits) - 1, np.float32)
+        c = np.empty(1 << bits, np.float32)
+        self._check(self._lib.tv_codebook(self._h, _ptr(b), _ptr(c)))
+        return b, c
+
+    def rotate(self, rows: np.ndarray) -> np.ndarray:
+        rows = _f32_2d("rows", rows)
+        out = np.empty_like(rows)
+        self._check(self._lib.tv_rotate(self._h, _ptr(rows), rows.shape[0], rows.shape[1], _ptr(out)))
+        return out
+
+    def codes_blocked_seq(self) -> np.ndarray:
+        out = np.empty(int(self._lib.tv_blocked_bytes(self._h)), np.uint8)
+        self._check(self._lib.tv_export_blocked(self._h, _ptr(out), out.size, None, 0))
+        return out
+
+    def scales(self) -> np.ndarray:
+        out = np.empty(len(self), np.float32)
+        self._check(self._lib.tv_export_blocked(self._h, None, 0, _ptr(out), out.size))
+        return out
+
+    def packed_codes(self) -> np.ndarray:
+        d = self.dim or 0
+        out = np.empty((len(self), self.bit_width * d // 8), np.uint8)
+        self._check(self._lib.tv_export_packed(self._h, _ptr(out), out.size))
+        return out
+
+    def _search_raw(self, queries, k, fn, extra, out_dtype):
+        queries = _f32_2d("queries", queries)
+        k = _size("k", k)
+        nq, ncols = queries.shape
+        idx_dim = self.dim
+        if idx_dim is not None and ncols != idx_dim:
+            raise ValueError(f"query dim {ncols} does not match index dim {idx_dim}")
+        kk = min(k, len(self))
+        scores = np.empty((nq, max(kk, 1)), np.float32)
+        ids = np.empty((nq, max(kk, 1)), out_dtype)
+        k_eff = C.c_size_t(0)
+        self._check(fn(self._h, _ptr(queries), nq, ncols, k, *extra, _ptr(scores), _ptr(ids), C.byref(k_eff)))
+        ke = int(k_eff.value)
+        return (scores.ravel()[: nq * ke].reshape(nq, ke).copy(), ids.ravel()[: nq * ke].reshape(nq, ke).copy())
+
+
+class TurboQuantIndex(_Base):
+    """Positional index: results are slot numbers.  Mirrors turbovec-python/src/lib.rs:416-947."""
+    _KIND = 0
+
+    def add(self, vectors: np.ndarray) -> None:
+        vectors = _f32_2d("vectors", vectors)
+        self._check(self._lib.tv_add(self._h, _ptr(vectors), vectors.shape[0], vectors.shape[1]))
+
+    def add_device(self, device_ptr: int, n: int, dim: int) -> None:
+        """Adds n rows that already sit in device memory (row-major float32 at `device_ptr`)."""
+        self._check(self._lib.tv_add_device(self._h, C.c_void_p(device_ptr), n, dim))
+
+    def search(self, queries: np.ndarray, k: int, *, mask=None):
+        extra = (None, 0)
+        if mask is not None:
+            mask = _typed_1d("mask", mask, np.bool_, "bool")
+            if mask.size != len(self):
+                raise ValueError(f"mask length {mask.size} does not match index size {len(self)}")
+            extra = (_ptr(mask), mask.size)
+        return self._search_raw(queries, k, self._lib.tv_search, extra, np.int64)
+
+    def search_mask_words(self, queries: np.ndarray, k: int, words: np.ndarray):
+        words = _typed_1d("words", words, np.uint64, "uint64")
+        return self._search_raw(queries, k, self._lib.tv_search_mask_words, (_ptr(words), words.size), np.int64)
+
+    def search_device(self, q_ptr: int, nq: int, k: int, scores_ptr: int, slots_ptr: int, mask_words_ptr: int = 0) -> int:
+        """Device-resident search; returns k_eff.  Output rows have stride k_eff."""
+        k_eff = C.c_size_t(0)
+        self._check(self._lib.tv_search_device(self._h, C.c_void_p(q_ptr), nq, k,
+                                                C.c_void_p(mask_words_ptr) if mask_words_ptr else None,
+                                                C.c_void_p(scores_ptr), C.c_void_p(slots_ptr), C.byref(k_eff)))
+        return int(k_eff.value)
+
+    def swap_remove(self, idx: int) -> int:
+        idx = _size("idx", idx)
+        moved = C.c_size_t(0)
+        self._check(self._lib.tv_swap_remove(self._h, idx, C.byref(moved)))
+        return int(moved.value)
+
+    @classmethod
+    def from_parts(cls, dim: int, bit_width: int, packed: np.ndarray, scales: np.ndarray, *, device: int = 0):
+        self = cls(dim, bit_width, device=device)
+        packed = np.ascontiguousarray(packed, np.uint8)
+        scales = np.ascontiguousarray(scales, np.float32)
+        self._check(self._lib.tv_import_packed(self._h, dim, _ptr(packed), scales.size, _ptr(scales), None))
+        return self
+
+    def __repr__(self):
+        return f"TurboQuantIndex(dim={self.dim}, bit_width={self.bit_width}, len={len(self)})"
+
+
+class IdMapIndex(_Base):
+    """Index addressed by caller-chosen uint64 ids.  Mirrors turbovec-python/src/lib.rs:952-1540."""
+    _KIND = 1
+
+    def add_with_ids(self, vectors: np.ndarray, ids: np.ndarray) -> None:
+        vectors = _f32_2d("vectors", vectors)
+        ids = _typed_1d("ids", ids, np.uint64, "uint64")
+        if ids.size != vectors.shape[0]:
+            raise ValueError(f"ids length {ids.size} does not match number of vectors {vectors.shape[0]}")
+        self._check(self._lib.tv_add_with_ids(self._h, _ptr(vectors), vectors.shape[0], vectors.shape[1], _ptr(ids)))
+
+    def remove(self, id) -> bool:
+        if isinstance(id, bool) or not isinstance(id, (int, np.integer)):
+            raise TypeError(f"id must be an int, got {type(id).__name__}")
+        if id < 0 or id >= 1 << 64:
+            return False
+        removed = C.c_int(0)
+        self._check(self._lib.tv_remove(self._h, int(id), C.byref(removed)))
+        return bool(removed.value)
+
+    def contains(self, id) -> bool:
+        if isinstance(id, bool) or not isinstance(id, (int, np.integer)):
+            raise TypeError(f"id must be an int, got {type(id).__name__}")
+        if id < 0 or id >= 1 << 64:
+            return False
+        present = C.c_int(0)
+        self._check(self._lib.tv_contains(self._h, int(id), C.byref(present)))
+        return bool(present.value)
+
+    __contains__ = contains
+
+    def ids(self) -> np.ndarray:
+        out = np.empty(len(self), np.uint64)
+        self._check(self._lib.tv_ids(self._h, _ptr(out), out.size))
+        return out
+
+    def search(self, queries: np.ndarray, k: int, *, allowlist=None):
+        extra = (None, 0)
+        if allowlist is not None:
+            allowlist = _typed_1d("allowlist", allowlist, np.uint64, "uint64")
+            if allowlist.size == 0:
+                raise ValueError("allowlist is empty")
+            extra = (_ptr(allowlist), allowlist.size)
+        return self._search_raw(queries, k, self._lib.tv_search_allowlist, extra, np.uint64)
+
+    def __repr__(self):
+        return f"IdMapIndex(dim={self.dim}, bit_width={self.bit_width}, len={len(self)})"

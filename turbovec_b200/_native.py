@@ -1,0 +1,86 @@
+"""ctypes binding of libturbovec_b200.so.  There is no fallback: if the library is missing or a CUDA
+device cannot be opened, the caller gets an exception."""
+from __future__ import annotations
+
+import ctypes as C
+import os
+
+_HERE = os.path.dirname(os.path.abspath(__file__))
+LIB_PATH = os.path.join(_HERE, "libturbovec_b200.so")
+
+_f32p = C.POINTER(C.c_float)
+_u8p = C.POINTER(C.c_uint8)
+_u64p = C.POINTER(C.c_uint64)
+_i64p = C.POINTER(C.c_int64)
+_szp = C.POINTER(C.c_size_t)
+_intp = C.POINTER(C.c_int)
+_H = C.c_void_p
+
+# name -> (restype, argtypes); every symbol declared in include/turbovec_b200.h
+SIGNATURES = {
+    "tv_version": (C.c_char_p, []),
+    "tv_index_create": (C.c_int, [C.c_size_t, C.c_int, C.c_int, C.c_int, C.POINTER(_H)]),
+    "tv_index_destroy": (None, [_H]),
+    "tv_last_error": (C.c_char_p, [_H]),
+    "tv_error_detail": (None, [_H, _szp, _szp, _f32p, _u64p]),
+    "tv_len": (C.c_size_t, [_H]),
+    "tv_dim": (C.c_size_t, [_H]),
+    "tv_bit_width": (C.c_int, [_H]),
+    "tv_kind": (C.c_int, [_H]),
+    "tv_set_option": (C.c_int, [_H, C.c_int, C.c_int64]),
+    "tv_get_option": (C.c_int64, [_H, C.c_int]),
+    "tv_add": (C.c_int, [_H, C.c_void_p, C.c_size_t, C.c_size_t]),
+    "tv_add_with_ids": (C.c_int, [_H, C.c_void_p, C.c_size_t, C.c_size_t, C.c_void_p]),
+    "tv_add_device": (C.c_int, [_H, C.c_void_p, C.c_size_t, C.c_size_t]),
+    "tv_swap_remove": (C.c_int, [_H, C.c_size_t, _szp]),
+    "tv_remove": (C.c_int, [_H, C.c_uint64, _intp]),
+    "tv_contains": (C.c_int, [_H, C.c_uint64, _intp]),
+    "tv_ids": (C.c_int, [_H, C.c_void_p, C.c_size_t]),
+    "tv_search": (C.c_int, [_H, C.c_void_p, C.c_size_t, C.c_size_t, C.c_size_t, C.c_void_p, C.c_size_t,
+                            C.c_void_p, C.c_void_p, _szp]),
+    "tv_search_mask_words": (C.c_int, [_H, C.c_void_p, C.c_size_t, C.c_size_t, C.c_size_t, C.c_void_p, C.c_size_t,
+                                       C.c_void_p, C.c_void_p, _szp]),
+    "tv_search_allowlist": (C.c_int, [_H, C.c_void_p, C.c_size_t, C.c_size_t, C.c_size_t, C.c_void_p, C.c_size_t,
+                                      C.c_void_p, C.c_void_p, _szp]),
+    "tv_search_device": (C.c_int, [_H, C.c_void_p, C.c_size_t, C.c_size_t, C.c_void_p, C.c_void_p, C.c_void_p, _szp]),
+    "tv_prepare": (C.c_int, [_H]),
+    "tv_blocked_bytes": (C.c_size_t, [_H]),
+    "tv_export_blocked": (C.c_int, [_H, C.c_void_p, C.c_size_t, C.c_void_p, C.c_size_t]),
+    "tv_export_packed": (C.c_int, [_H, C.c_void_p, C.c_size_t]),
+    "tv_import_packed": (C.c_int, [_H, C.c_size_t, C.c_void_p, C.c_size_t, C.c_void_p, C.c_void_p]),
+    "tv_codebook": (C.c_int, [_H, C.c_void_p, C.c_void_p]),
+    "tv_rotate": (C.c_int, [_H, C.c_void_p, C.c_size_t, C.c_size_t, C.c_void_p]),
+    "tv_calibrate": (C.c_int, [_H, C.c_void_p, C.c_size_t, C.c_size_t]),
+    "tv_calibration": (C.c_int, [_H, C.c_void_p, C.c_void_p, C.c_size_t, _intp]),
+    "tv_set_calibration": (C.c_int, [_H, C.c_size_t, C.c_void_p, C.c_void_p]),
+    "tv_launch_count": (C.c_uint64, [_H]),
+    "tv_last_kernel_ms": (C.c_float, [_H]),
+}
+
+_lib = None
+
+
+def load() -> C.CDLL:
+    """Loads the shared library (once).  Raises if it has not been built."""
+    global _lib
+    if _lib is not None:
+        return _lib
+    if not os.path.exists(LIB_PATH):
+        raise ImportError(
+            f"{LIB_PATH} is missing: build it with `python -m turbovec_b200.build` (needs nvcc). "
+            "turbovec_b200 has no CPU implementation to fall back to.")
+    lib = C.CDLL(LIB_PATH)
+    for name, (res, args) in SIGNATURES.items():
+        fn = getattr(lib, name)
+        fn.restype = res
+        fn.argtypes = args
+    _lib = lib
+    return lib
+
+
+# status codes of include/turbovec_b200.h
+OK = 0
+ERR_ID_KEYERROR = {21}
+ERR_INDEXERROR = {31}
+SCORE_AUTO, SCORE_PERMUTE_DOT, SCORE_LUT_MULADD, SCORE_LUT_FLUSH = 0, 1, 2, 3
+OPT_SCORE_MODE, OPT_MMA_MIN_BATCH, OPT_FORCE_CAREFUL = 1, 2, 3

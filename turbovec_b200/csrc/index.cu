@@ -1,0 +1,1012 @@
+// Host side of the library: the index state machine (what TurboQuantIndex / IdMapIndex own in the
+// reference, turbovec/src/lib.rs:295-401 and id_map.rs:221-272) with the code array, the scales and all
+// scratch resident in device memory, and the C ABI declared in include/turbovec_b200.h.
+#include <cuda_runtime.h>
+
+#include <algorithm>
+#include <cmath>
+#include <cstring>
+#include <mutex>
+#include <string>
+#include <unordered_map>
+#include <unordered_set>
+#include <vector>
+
+#include "../../include/turbovec_b200.h"
+#include "host_tables.hpp"
+#include "ingest.cuh"
+#include "search.cuh"
+#include "tv_common.cuh"
+
+namespace {
+
+using namespace tv;
+
+thread_local std::string g_create_error;
+
+template <typename T>
+struct DeviceArray {
+    T *ptr = nullptr;
+    size_t cap = 0;   // elements
+    ~DeviceArray() { release(); }
+    void release() {
+        if (ptr) cudaFree(ptr);
+        ptr = nullptr;
+        cap = 0;
+    }
+    // Grows without preserving contents.
+    cudaError_t reserve(size_t n) {
+        if (n <= cap) return cudaSuccess;
+        release();
+        cudaError_t e = cudaMalloc(&ptr, std::max<size_t>(n, 1) * sizeof(T));
+        if (e == cudaSuccess) cap = n;
+        return e;
+    }
+};
+
+template <typename T>
+struct PinnedArray {
+    T *ptr = nullptr;
+    size_t cap = 0;
+    ~PinnedArray() { if (ptr) cudaFreeHost(ptr); }
+    cudaError_t reserve(size_t n) {
+        if (n <= cap) return cudaSuccess;
+        if (ptr) cudaFreeHost(ptr);
+        ptr = nullptr; cap = 0;
+        cudaError_t e = cudaMallocHost(&ptr, std::max<size_t>(n, 1) * sizeof(T));
+        if (e == cudaSuccess) cap = n;
+        return e;
+    }
+};
+
+struct DeviceFlags {        // one pinned + one device copy of the status words of a call
+    unsigned long long first_invalid;
+    unsigned long long n_allowed;
+    uint32_t n_live;
+    uint32_t overflow;
+    uint32_t error;
+    uint32_t k_eff;
+};
+
+}  // namespace
+
+struct tv_index {
+    int kind = TV_KIND_POSITIONAL;
+    int bits = 4;
+    int device = 0;
+    size_t dim = 0;          // 0 = lazy
+    size_t n = 0;
+    int ngroups = 0;
+    int sm_count = 148;
+    size_t smem_limit = 0;
+
+    std::mutex mu;
+    std::string last_error;
+    size_t err_vec = 0, err_coord = 0;
+    float err_value = 0.f;
+    uint64_t err_id = 0;
+
+    // options
+    int score_mode = TV_SCORE_AUTO;
+    int64_t mma_min_batch = 0;
+    int force_careful = 0;
+
+    cudaStream_t stream = nullptr;
+    cudaEvent_t ev0 = nullptr, ev1 = nullptr;
+    uint64_t launches = 0;
+    float last_ms = 0.f;
+
+    // tables (host + device)
+    bool tables_ready = false;
+    RotationTables rot;
+    Codebook cb;
+    std::vector<float> shift, scale_tq;      // empty = uncalibrated
+    DeviceArray<uint16_t> d_perm;            // [2][dim]
+    DeviceArray<float> d_codebook;           // boundaries (16 slots) then centroids (16 slots)
+    DeviceArray<float> d_calib;              // shift, scale, inv_scale  [3][dim]
+    float level_scale = 1.f;                 // cs of the permute-dot level table
+    int8_t levels[16] = {0};
+
+    // storage
+    uint8_t *d_codes = nullptr;
+    size_t code_blocks_cap = 0;
+    float *d_scales = nullptr;
+    size_t scales_cap = 0;
+
+    // scratch
+    DeviceArray<float> d_stage;              // ingest staging / query upload
+    DeviceArray<float> d_qrot, d_qscale, d_qbias;
+    DeviceArray<uint8_t> d_luts;
+    DeviceArray<int8_t> d_weights;
+    DeviceArray<uint32_t> d_wfrag;
+    DeviceArray<uint64_t> d_mask;
+    DeviceArray<uint8_t> d_mask_bool;
+    DeviceArray<uint32_t> d_slots_in, d_live;
+    DeviceArray<uint64_t> d_cand, d_thr, d_topk;
+    DeviceArray<uint32_t> d_cnt;
+    DeviceArray<float> d_scores;
+    DeviceArray<int64_t> d_slots;
+    DeviceFlags *d_flags = nullptr;
+    DeviceFlags *h_flags = nullptr;
+    PinnedArray<float> h_scores;
+    PinnedArray<int64_t> h_slots;
+
+    // id map (ids never reach the device; id_map.rs:221-272)
+    std::vector<uint64_t> slot_to_id;
+    std::unordered_map<uint64_t, uint32_t> id_to_slot;
+
+    ~tv_index() {
+        cudaSetDevice(device);
+        if (stream) cudaStreamSynchronize(stream);
+        if (d_codes) cudaFree(d_codes);
+        if (d_scales) cudaFree(d_scales);
+        if (d_flags) cudaFree(d_flags);
+        if (h_flags) cudaFreeHost(h_flags);
+        if (ev0) cudaEventDestroy(ev0);
+        if (ev1) cudaEventDestroy(ev1);
+        if (stream) cudaStreamDestroy(stream);
+    }
+};
+
+namespace {
+
+int fail(tv_index *h, int code, const std::string &msg) {
+    if (h) h->last_error = msg;
+    else g_create_error = msg;
+    return code;
+}
+
+#define TV_CUDA(expr)                                                                              \
+    do {                                                                                           \
+        cudaError_t e__ = (expr);                                                                  \
+        if (e__ != cudaSuccess) {                                                                  \
+            cudaGetLastError();                                                                    \
+            return fail(h, e__ == cudaErrorMemoryAllocation ? TV_ERR_OUT_OF_MEMORY : TV_ERR_CUDA,  \
+                        std::string(#expr) + ": " + cudaGetErrorString(e__));                      \
+        }                                                                                          \
+    } while (0)
+
+int resolve_mode(const tv_index *h) {
+    const int vm = (h->ngroups % 4) == 0;
+    int m = h->score_mode;
+    if (m == TV_SCORE_AUTO) m = (vm && h->bits == 4) ? TV_SCORE_PERMUTE_DOT : (vm ? TV_SCORE_LUT_MULADD : TV_SCORE_LUT_FLUSH);
+    if (m == TV_SCORE_PERMUTE_DOT && h->bits != 4) m = TV_SCORE_LUT_MULADD;
+    return m;
+}
+
+// Builds rotation tables, codebook and the permute-dot level table for the (now fixed) dimension.
+int ensure_tables(tv_index *h) {
+    if (h->tables_ready) return TV_OK;
+    const int dim = int(h->dim);
+    h->ngroups = dim / (8 / h->bits);
+    h->rot = build_rotation_tables(dim);
+    h->cb = codebook(h->bits, dim);
+    TV_CUDA(h->d_perm.reserve(size_t(2) * dim));
+    TV_CUDA(cudaMemcpyAsync(h->d_perm.ptr, h->rot.packed[0].data(), size_t(dim) * 2, cudaMemcpyHostToDevice, h->stream));
+    TV_CUDA(cudaMemcpyAsync(h->d_perm.ptr + dim, h->rot.packed[1].data(), size_t(dim) * 2, cudaMemcpyHostToDevice, h->stream));
+    float cbuf[32] = {0};
+    for (size_t i = 0; i < h->cb.boundaries.size(); ++i) cbuf[i] = h->cb.boundaries[i];
+    for (size_t i = 0; i < h->cb.centroids.size(); ++i) cbuf[16 + i] = h->cb.centroids[i];
+    TV_CUDA(h->d_codebook.reserve(32));
+    TV_CUDA(cudaMemcpyAsync(h->d_codebook.ptr, cbuf, sizeof cbuf, cudaMemcpyHostToDevice, h->stream));
+    TV_CUDA(cudaStreamSynchronize(h->stream));
+    if (h->bits == 4) {
+        // search.rs:2812-2819: cs = cmax/127, level = clamp(round(c/cs), +-127)
+        float cmax = 0.f;
+        for (float c : h->cb.centroids) cmax = std::fmax(cmax, std::fabs(c));
+        const float cs = cmax > 0.f ? cmax / 127.0f : 1.0f;
+        for (int i = 0; i < 16; ++i) {
+            float r = std::round(h->cb.centroids[i] / cs);
+            r = std::fmin(std::fmax(r, -127.0f), 127.0f);
+            h->levels[i] = int8_t(int(r));
+        }
+        h->level_scale = cs;
+    }
+    h->tables_ready = true;
+    return TV_OK;
+}
+
+int upload_calibration(tv_index *h) {
+    if (h->shift.empty()) return TV_OK;
+    const size_t dim = h->dim;
+    std::vector<float> buf(3 * dim);
+    for (size_t d = 0; d < dim; ++d) {
+        buf[d] = h->shift[d];
+        buf[dim + d] = h->scale_tq[d];
+        buf[2 * dim + d] = 1.0f / h->scale_tq[d];     // encode.rs:593
+    }
+    TV_CUDA(h->d_calib.reserve(3 * dim));
+    TV_CUDA(cudaMemcpyAsync(h->d_calib.ptr, buf.data(), buf.size() * 4, cudaMemcpyHostToDevice, h->stream));
+    TV_CUDA(cudaStreamSynchronize(h->stream));
+    return TV_OK;
+}
+
+// Grows the code / scale arrays to hold `n_total` vectors.  New space is zero so that padding lanes read
+// as zero bytes (pack.rs:347-358).  Growth is geometric (x1.5) and copies once.
+int ensure_capacity(tv_index *h, size_t n_total) {
+    const size_t blocks = (n_total + kBlock - 1) / kBlock;
+    const size_t block_bytes = size_t(h->ngroups) * kBlock;
+    if (blocks > h->code_blocks_cap) {
+        size_t new_cap = std::max(blocks, h->code_blocks_cap + h->code_blocks_cap / 2);
+        new_cap = std::max<size_t>(new_cap, 64);
+        uint8_t *fresh = nullptr;
+        cudaError_t e = cudaMalloc(&fresh, new_cap * block_bytes);
+        if (e != cudaSuccess && new_cap > blocks) {      // retry with the exact size before giving up
+            cudaGetLastError();
+            new_cap = blocks;
+            e = cudaMalloc(&fresh, new_cap * block_bytes);
+        }
+        TV_CUDA(e);
+        const size_t used = ((h->n + kBlock - 1) / kBlock) * block_bytes;
+        if (used) TV_CUDA(cudaMemcpyAsync(fresh, h->d_codes, used, cudaMemcpyDeviceToDevice, h->stream));
+        TV_CUDA(cudaMemsetAsync(fresh + used, 0, new_cap * block_bytes - used, h->stream));
+        TV_CUDA(cudaStreamSynchronize(h->stream));
+        if (h->d_codes) cudaFree(h->d_codes);
+        h->d_codes = fresh;
+        h->code_blocks_cap = new_cap;
+    }
+    if (n_total > h->scales_cap) {
+        size_t new_cap = std::max(n_total, h->scales_cap + h->scales_cap / 2);
+        new_cap = std::max<size_t>(new_cap, 2048);
+        float *fresh = nullptr;
+        TV_CUDA(cudaMalloc(&fresh, new_cap * sizeof(float)));
+        if (h->n) TV_CUDA(cudaMemcpyAsync(fresh, h->d_scales, h->n * sizeof(float), cudaMemcpyDeviceToDevice, h->stream));
+        TV_CUDA(cudaStreamSynchronize(h->stream));
+        if (h->d_scales) cudaFree(h->d_scales);
+        h->d_scales = fresh;
+        h->scales_cap = new_cap;
+    }
+    return TV_OK;
+}
+
+__global__ void clear_slots_kernel(uint8_t *codes, int ng, int64_t slot_begin, int64_t slot_end) {
+    // zeroes the code bytes of slots [slot_begin, slot_end)
+    const int64_t total = (slot_end - slot_begin) * ng;
+    for (int64_t i = int64_t(blockIdx.x) * blockDim.x + threadIdx.x; i < total; i += int64_t(gridDim.x) * blockDim.x) {
+        const int64_t slot = slot_begin + i / ng;
+        const int g = int(i % ng);
+        codes[((slot / 32) * ng + g) * 32 + (slot % 32)] = 0;
+    }
+}
+
+// swap_remove on the blocked array: pack::move_lane + pack::zero_lane (pack.rs:174-246).
+__global__ void move_lane_kernel(uint8_t *codes, float *scales, int ng, int64_t src, int64_t dst) {
+    for (int g = blockIdx.x * blockDim.x + threadIdx.x; g < ng; g += gridDim.x * blockDim.x) {
+        uint8_t *s = codes + ((src / 32) * ng + g) * 32 + (src % 32);
+        if (src != dst) codes[((dst / 32) * ng + g) * 32 + (dst % 32)] = *s;
+        *s = 0;
+    }
+    if (blockIdx.x == 0 && threadIdx.x == 0 && src != dst) scales[dst] = scales[src];
+}
+
+int validate_dim_for_add(tv_index *h, size_t dim) {
+    // add_2d, lib.rs:1114-1133
+    if (h->dim != 0) {
+        if (h->dim != dim)
+            return fail(h, TV_ERR_DIM_MISMATCH, "dimension mismatch: index has dim " + std::to_string(h->dim) + ", got " + std::to_string(dim));
+        return TV_OK;
+    }
+    if (dim == 0) return fail(h, TV_ERR_ZERO_DIM, "dim must be non-zero");
+    if (dim % 8 != 0) return fail(h, TV_ERR_DIM_NOT_MULTIPLE_OF_8, "dim " + std::to_string(dim) + " is not a multiple of 8");
+    if (dim > size_t(kMaxDim)) return fail(h, TV_ERR_DIM_TOO_LARGE, "dim " + std::to_string(dim) + " exceeds " + std::to_string(kMaxDim));
+    return TV_OK;
+}
+
+// Encodes n rows (host or device memory) onto the end of the index.  All-or-nothing.
+int add_rows(tv_index *h, const float *x, size_t n, size_t dim, bool on_device) {
+    int rc = validate_dim_for_add(h, dim);
+    if (rc != TV_OK) return rc;
+    if (n == 0) return TV_OK;
+    if (h->n + n > 0xfffffff0ull) return fail(h, TV_ERR_UNSUPPORTED, "more than 2^32 - 16 vectors per device shard");
+    TV_CUDA(cudaSetDevice(h->device));
+    const bool was_lazy = h->dim == 0;
+    if (was_lazy) h->dim = dim;
+    rc = ensure_tables(h);
+    if (rc == TV_OK) rc = ensure_capacity(h, h->n + n);
+    if (rc != TV_OK) {
+        if (was_lazy) { h->dim = 0; h->tables_ready = false; }
+        return rc;
+    }
+    const int V = ingest_vectors_per_pass(int(dim), h->ngroups, h->smem_limit);
+    if (V == 0) return fail(h, TV_ERR_UNSUPPORTED, "dim too large for the ingest kernel's shared memory");
+
+    h->h_flags->first_invalid = ~0ull;
+    TV_CUDA(cudaMemcpyAsync(&h->d_flags->first_invalid, &h->h_flags->first_invalid, 8, cudaMemcpyHostToDevice, h->stream));
+
+    IngestParams p{};
+    p.dim = int(dim); p.bits = h->bits; p.ngroups = h->ngroups;
+    p.perm0 = h->d_perm.ptr; p.perm1 = h->d_perm.ptr + dim;
+    p.inv_sqrt_block = h->rot.inv_sqrt_block;
+    p.boundaries = h->d_codebook.ptr; p.centroids = h->d_codebook.ptr + 16;
+    if (!h->shift.empty()) { p.shift = h->d_calib.ptr; p.scale_tq = h->d_calib.ptr + dim; p.inv_scale_tq = h->d_calib.ptr + 2 * dim; }
+    p.codes = h->d_codes; p.scales = h->d_scales;
+    p.first_invalid = &h->d_flags->first_invalid;
+
+    // Host input goes through a device staging buffer in chunks of at most ~256 MB.
+    const size_t chunk_rows = on_device ? n : std::max<size_t>(1, std::min<size_t>(n, (size_t(256) << 20) / (dim * 4)));
+    if (!on_device) TV_CUDA(h->d_stage.reserve(chunk_rows * dim));
+    TV_CUDA(cudaEventRecord(h->ev0, h->stream));
+    for (size_t done = 0; done < n; done += chunk_rows) {
+        const size_t rows = std::min(chunk_rows, n - done);
+        const float *src = x + done * dim;
+        if (!on_device) {
+            TV_CUDA(cudaMemcpyAsync(h->d_stage.ptr, src, rows * dim * 4, cudaMemcpyHostToDevice, h->stream));
+            src = h->d_stage.ptr;
+        }
+        p.x = src; p.n = int64_t(rows); p.slot0 = int64_t(h->n + done); p.row_base = int64_t(done);
+        TV_CUDA(launch_ingest(p, V, h->stream));
+        h->launches++;
+    }
+    TV_CUDA(cudaEventRecord(h->ev1, h->stream));
+    TV_CUDA(cudaMemcpyAsync(&h->h_flags->first_invalid, &h->d_flags->first_invalid, 8, cudaMemcpyDeviceToHost, h->stream));
+    TV_CUDA(cudaStreamSynchronize(h->stream));
+    cudaEventElapsedTime(&h->last_ms, h->ev0, h->ev1);
+    if (h->h_flags->first_invalid != ~0ull) {
+        // roll back: the new lanes must read as zero again, nothing else was touched
+        const int64_t total = int64_t(n) * h->ngroups;
+        clear_slots_kernel<<<unsigned(std::min<int64_t>((total + 255) / 256, 65535)), 256, 0, h->stream>>>(
+            h->d_codes, h->ngroups, int64_t(h->n), int64_t(h->n + n));
+        cudaStreamSynchronize(h->stream);
+        const unsigned long long flat = h->h_flags->first_invalid;
+        h->err_vec = size_t(flat / dim); h->err_coord = size_t(flat % dim);
+        if (on_device) cudaMemcpy(&h->err_value, x + flat, 4, cudaMemcpyDeviceToHost);
+        else h->err_value = x[flat];
+        if (was_lazy) { h->dim = 0; h->tables_ready = false; }
+        return fail(h, TV_ERR_INVALID_INPUT_VALUE,
+                    "vector " + std::to_string(h->err_vec) + " coordinate " + std::to_string(h->err_coord) +
+                        " is not finite or exceeds 1e16 in magnitude (value " + std::to_string(h->err_value) + ")");
+    }
+    h->n += n;
+    return TV_OK;
+}
+
+struct MaskSpec {
+    const uint8_t *bool_host = nullptr; size_t bool_len = 0;
+    const uint64_t *words_host = nullptr; size_t n_words = 0;
+    const uint64_t *words_device = nullptr;
+    const uint32_t *slots_host = nullptr; size_t n_slots = 0;
+    bool any() const { return bool_host || words_host || words_device || slots_host; }
+};
+
+int candidate_capacity(size_t k) { return k <= 512 ? 4096 : 8192; }
+
+// The whole search on the handle's stream.  Results land in d_scores/d_slots (row stride k) unless
+// out_scores_dev is given (row stride k_eff).
+int search_core(tv_index *h, const float *queries, bool queries_on_device, size_t nq, size_t k, const MaskSpec &mask,
+                float *out_scores_dev, int64_t *out_slots_dev, size_t *k_eff_out) {
+    const size_t dim = h->dim, n = h->n;
+    const int ng = h->ngroups;
+    const int mode = resolve_mode(h);
+    const size_t kk = std::min(k, n);
+    *k_eff_out = 0;
+    if (nq == 0 || kk == 0) return TV_OK;
+    if (kk > 4096) return fail(h, TV_ERR_UNSUPPORTED, "k above 4096 is not supported by the device top-k");
+    TV_CUDA(cudaSetDevice(h->device));
+    cudaStream_t st = h->stream;
+    const int cap = candidate_capacity(kk);
+    const size_t nq_pad = (nq + 15) / 16 * 16;
+    const int mt_total = int(nq_pad / 16);
+    const size_t dim_pad = (dim + 127) / 128 * 128;
+    const int ksteps = (ng + 15) / 16;
+
+    // ---- buffers ----
+    if (!queries_on_device) TV_CUDA(h->d_stage.reserve(nq * dim));
+    TV_CUDA(h->d_qrot.reserve(nq * dim));
+    TV_CUDA(h->d_qscale.reserve(nq_pad));
+    TV_CUDA(h->d_qbias.reserve(nq_pad));
+    if (mode == TV_SCORE_PERMUTE_DOT) {
+        TV_CUDA(h->d_weights.reserve(nq_pad * dim_pad));
+        TV_CUDA(h->d_wfrag.reserve(size_t(ksteps) * mt_total * 32 * 4));
+    } else {
+        TV_CUDA(h->d_luts.reserve(nq * size_t(ng) * 32));
+    }
+    TV_CUDA(h->d_cand.reserve(nq * size_t(cap)));
+    TV_CUDA(h->d_cnt.reserve(nq));
+    TV_CUDA(h->d_thr.reserve(nq));
+    TV_CUDA(h->d_topk.reserve(nq * kk));
+    if (!out_scores_dev) {
+        TV_CUDA(h->d_scores.reserve(nq * kk));
+        TV_CUDA(h->d_slots.reserve(nq * kk));
+    }
+    const size_t n_blocks = (n + kBlock - 1) / kBlock;
+    const size_t n_words = (n + 63) / 64;
+
+    // ---- inputs ----
+    const float *dq = queries;
+    if (!queries_on_device) {
+        TV_CUDA(cudaMemcpyAsync(h->d_stage.ptr, queries, nq * dim * 4, cudaMemcpyHostToDevice, st));
+        dq = h->d_stage.ptr;
+    }
+    DeviceFlags init{};
+    init.first_invalid = ~0ull;
+    *h->h_flags = init;
+    TV_CUDA(cudaMemcpyAsync(h->d_flags, h->h_flags, sizeof(DeviceFlags), cudaMemcpyHostToDevice, st));
+    TV_CUDA(cudaEventRecord(h->ev0, st));
+
+    const uint64_t *d_mask = nullptr;
+    if (mask.any()) {
+        if (mask.words_device) {
+            TV_CUDA(h->d_mask.reserve(n_words));
+            TV_CUDA(cudaMemcpyAsync(h->d_mask.ptr, mask.words_device, n_words * 8, cudaMemcpyDeviceToDevice, st));
+        } else if (mask.words_host) {
+            TV_CUDA(h->d_mask.reserve(n_words));
+            TV_CUDA(cudaMemcpyAsync(h->d_mask.ptr, mask.words_host, n_words * 8, cudaMemcpyHostToDevice, st));
+        } else if (mask.bool_host) {
+            TV_CUDA(h->d_mask.reserve(n_words));
+            TV_CUDA(h->d_mask_bool.reserve(n));
+            TV_CUDA(cudaMemcpyAsync(h->d_mask_bool.ptr, mask.bool_host, n, cudaMemcpyHostToDevice, st));
+            TV_CUDA(launch_pack_bool_mask(h->d_mask_bool.ptr, int64_t(n), h->d_mask.ptr, st));
+            h->launches++;
+        } else {
+            TV_CUDA(h->d_mask.reserve(n_words));
+            TV_CUDA(h->d_slots_in.reserve(mask.n_slots));
+            TV_CUDA(cudaMemsetAsync(h->d_mask.ptr, 0, n_words * 8, st));
+            TV_CUDA(cudaMemcpyAsync(h->d_slots_in.ptr, mask.slots_host, mask.n_slots * 4, cudaMemcpyHostToDevice, st));
+            TV_CUDA(launch_scatter_slots(h->d_slots_in.ptr, int64_t(mask.n_slots), h->d_mask.ptr, st));
+            h->launches++;
+        }
+        TV_CUDA(h->d_live.reserve(n_blocks));
+        TV_CUDA(launch_mask_stats(h->d_mask.ptr, int64_t(n), &h->d_flags->n_allowed, h->d_live.ptr, &h->d_flags->n_live, st));
+        h->launches++;
+        d_mask = h->d_mask.ptr;
+    }
+
+    // ---- query preparation ----
+    QueryPrepParams qp{};
+    qp.queries = dq; qp.nq = int(nq); qp.dim = int(dim); qp.bits = h->bits; qp.ngroups = ng;
+    qp.mode = mode;
+    qp.perm0 = h->d_perm.ptr; qp.perm1 = h->d_perm.ptr + dim;
+    qp.inv_sqrt_block = h->rot.inv_sqrt_block;
+    qp.centroids = h->d_codebook.ptr + 16;
+    if (!h->shift.empty()) { qp.shift = h->d_calib.ptr; qp.scale_tq = h->d_calib.ptr + dim; }
+    qp.level_scale = h->level_scale;
+    qp.q_rot = h->d_qrot.ptr; qp.qscale = h->d_qscale.ptr; qp.qbias = h->d_qbias.ptr;
+    qp.luts = h->d_luts.ptr; qp.weights = h->d_weights.ptr; qp.dim_pad = int(dim_pad);
+    qp.wfrag = h->d_wfrag.ptr; qp.mtiles_total = mt_total;
+    qp.first_invalid = &h->d_flags->first_invalid;
+    if (mode == TV_SCORE_PERMUTE_DOT)
+        TV_CUDA(cudaMemsetAsync(h->d_wfrag.ptr, 0, size_t(ksteps) * mt_total * 32 * 16, st));
+    TV_CUDA(launch_query_prep(qp, st));
+    h->launches++;
+
+    // ---- scan + select over a geometric chunk schedule ----
+    CandidateBuffers cb{};
+    cb.cand = h->d_cand.ptr; cb.cnt = h->d_cnt.ptr; cb.thr = h->d_thr.ptr; cb.topk = h->d_topk.ptr;
+    cb.overflow = &h->d_flags->overflow; cb.error = &h->d_flags->error; cb.cap = cap; cb.k = int(kk);
+
+    ScanParams sp{};
+    sp.codes = h->d_codes; sp.vec_scales = h->d_scales; sp.n = int64_t(n); sp.ngroups = ng; sp.bits = h->bits;
+    sp.mode = mode; sp.qscale = h->d_qscale.ptr; sp.qbias = h->d_qbias.ptr;
+    sp.mask = d_mask; sp.live_blocks = d_mask ? h->d_live.ptr : nullptr; sp.n_live = d_mask ? &h->d_flags->n_live : nullptr;
+    sp.cb = cb; sp.wfrag = h->d_wfrag.ptr; sp.mtiles_total = mt_total; sp.luts = h->d_luts.ptr;
+    for (int w = 0; w < 4; ++w) {
+        uint32_t word = 0;
+        for (int b = 0; b < 4; ++b) word |= uint32_t(uint8_t(h->levels[4 * w + b])) << (8 * b);
+        sp.level_words[w] = word;
+    }
+
+    auto run_schedule = [&](bool careful) -> int {
+        TV_CUDA(cudaMemsetAsync(h->d_cnt.ptr, 0, nq * 4, st));
+        TV_CUDA(cudaMemsetAsync(h->d_thr.ptr, 0xff, nq * 8, st));
+        TV_CUDA(cudaMemsetAsync(h->d_topk.ptr, 0xff, nq * kk * 8, st));
+        // Chunk 0 holds at most `cap` vectors, so every one of them may pass.  Later chunks grow so that the
+        // expected number of candidates per query, k * |chunk| / |seen|, stays near cap / 4.  The careful
+        // schedule never lets a chunk exceed `cap` vectors and therefore cannot overflow.
+        const size_t first = size_t(cap) / kBlock;
+        const double growth = std::max(0.5, double(cap) / (4.0 * double(kk)));
+        size_t begin = 0;
+        while (begin < n_blocks) {
+            size_t len = first;
+            if (!careful && begin > 0) len = std::max<size_t>(first, size_t(double(begin) * growth));
+            const size_t end = std::min(n_blocks, begin + len);
+            sp.pos_begin = uint32_t(begin); sp.pos_end = uint32_t(end);
+            if (mode == TV_SCORE_PERMUTE_DOT) {
+                for (size_t q0 = 0; q0 < nq; q0 += 64) {
+                    sp.q_base = int(q0); sp.nq = int(std::min<size_t>(64, nq - q0)); sp.mtile_base = int(q0 / 16);
+                    TV_CUDA(launch_scan_pd(sp, h->sm_count, st));
+                    h->launches++;
+                }
+            } else {
+                for (size_t q0 = 0; q0 < nq; q0 += kLutQueriesPerLaunch) {
+                    sp.q_base = int(q0); sp.nq = int(std::min<size_t>(kLutQueriesPerLaunch, nq - q0));
+                    TV_CUDA(launch_scan_lut(sp, h->sm_count, st));
+                    h->launches++;
+                }
+            }
+            TV_CUDA(launch_select(cb, int(nq), st));
+            h->launches++;
+            begin = end;
+        }
+        return TV_OK;
+    };
+
+    uint32_t *d_keff = &h->d_flags->k_eff;
+    for (int attempt = 0; attempt < 2; ++attempt) {
+        const bool careful = attempt == 1 || h->force_careful;
+        int rc = run_schedule(careful);
+        if (rc != TV_OK) return rc;
+        const unsigned long long *d_allowed = d_mask ? &h->d_flags->n_allowed : nullptr;
+        if (out_scores_dev) TV_CUDA(launch_finalize(cb, int(nq), d_allowed, int64_t(n), out_scores_dev, out_slots_dev, d_keff, 0, st));
+        else TV_CUDA(launch_finalize(cb, int(nq), d_allowed, int64_t(n), h->d_scores.ptr, h->d_slots.ptr, d_keff, 1, st));
+        h->launches++;
+        TV_CUDA(cudaEventRecord(h->ev1, st));
+        TV_CUDA(cudaMemcpyAsync(h->h_flags, h->d_flags, sizeof(DeviceFlags), cudaMemcpyDeviceToHost, st));
+        if (!out_scores_dev) {
+            TV_CUDA(h->h_scores.reserve(nq * kk));
+            TV_CUDA(h->h_slots.reserve(nq * kk));
+            TV_CUDA(cudaMemcpyAsync(h->h_scores.ptr, h->d_scores.ptr, nq * kk * 4, cudaMemcpyDeviceToHost, st));
+            TV_CUDA(cudaMemcpyAsync(h->h_slots.ptr, h->d_slots.ptr, nq * kk * 8, cudaMemcpyDeviceToHost, st));
+        }
+        TV_CUDA(cudaStreamSynchronize(st));
+        cudaEventElapsedTime(&h->last_ms, h->ev0, h->ev1);
+        if (h->h_flags->error) return fail(h, TV_ERR_DEVICE_TIMEOUT, "a device-side wait ran out of polls");
+        if (h->h_flags->first_invalid != ~0ull) {
+            const unsigned long long flat = h->h_flags->first_invalid;
+            h->err_vec = size_t(flat / dim); h->err_coord = size_t(flat % dim);
+            if (queries_on_device) cudaMemcpy(&h->err_value, queries + flat, 4, cudaMemcpyDeviceToHost);
+            else h->err_value = queries[flat];
+            return fail(h, TV_ERR_INVALID_QUERY_VALUE,
+                        "query " + std::to_string(h->err_vec) + " coordinate " + std::to_string(h->err_coord) +
+                            " is not finite or exceeds 1e16 in magnitude");
+        }
+        if (!h->h_flags->overflow) break;
+        if (careful) return fail(h, TV_ERR_CUDA, "candidate overflow in the bounded schedule (internal error)");
+        // a chunk produced more candidates than the buffer holds: redo with bounded chunks
+        h->h_flags->overflow = 0;
+        TV_CUDA(cudaMemcpyAsync(&h->d_flags->overflow, &h->h_flags->overflow, 4, cudaMemcpyHostToDevice, st));
+    }
+    *k_eff_out = h->h_flags->k_eff;
+    return TV_OK;
+}
+
+// Shared front end of the host-memory search entry points (validation order of lib.rs:1345-1433).
+int search_host(tv_index *h, const float *queries, size_t nq, size_t dim, size_t k, const MaskSpec &mask,
+                float *scores_out, int64_t *slots_out, uint64_t *ids_out, size_t *k_eff) {
+    if (k_eff) *k_eff = 0;
+    if (h->dim == 0) return TV_OK;                                   // lazy index: empty result
+    if (dim != h->dim)
+        return fail(h, TV_ERR_QUERY_BUFFER_NOT_MULTIPLE_OF_DIM, "query dimension " + std::to_string(dim) + " does not match index dim " + std::to_string(h->dim));
+    if (h->n == 0) {
+        if (mask.bool_host && mask.bool_len != 0)
+            return fail(h, TV_ERR_MASK_LENGTH_MISMATCH, "mask length " + std::to_string(mask.bool_len) + " does not match index length 0");
+        return TV_OK;
+    }
+    if (mask.bool_host && mask.bool_len != h->n)
+        return fail(h, TV_ERR_MASK_LENGTH_MISMATCH, "mask length " + std::to_string(mask.bool_len) + " does not match index length " + std::to_string(h->n));
+    if (mask.words_host && mask.n_words != (h->n + 63) / 64)
+        return fail(h, TV_ERR_MASK_LENGTH_MISMATCH, "mask has " + std::to_string(mask.n_words) + " words, index needs " + std::to_string((h->n + 63) / 64));
+    if (nq == 0) return TV_OK;
+    size_t ke = 0;
+    int rc = search_core(h, queries, false, nq, k, mask, nullptr, nullptr, &ke);
+    if (rc != TV_OK) return rc;
+    const size_t kk = std::min(k, h->n);
+    for (size_t q = 0; q < nq; ++q) {
+        std::memcpy(scores_out + q * ke, h->h_scores.ptr + q * kk, ke * sizeof(float));
+        if (slots_out) std::memcpy(slots_out + q * ke, h->h_slots.ptr + q * kk, ke * sizeof(int64_t));
+        if (ids_out)
+            for (size_t j = 0; j < ke; ++j) ids_out[q * ke + j] = h->slot_to_id[size_t(h->h_slots.ptr[q * kk + j])];   // id_map.rs:695-705
+    }
+    if (k_eff) *k_eff = ke;
+    return TV_OK;
+}
+
+// ---- host layout conversion for import / export (pack.rs:264-334, 375-467) ----
+void packed_to_blocked(const uint8_t *packed, size_t n, int bits, int dim, std::vector<uint8_t> &blocked) {
+    const int bpp = dim / 8, cpb = 8 / bits, ng = dim / cpb, bpr = bits * bpp, field = bits == 3 ? 4 : bits;
+    blocked.assign(((n + 31) / 32) * size_t(ng) * 32, 0);
+    for (size_t v = 0; v < n; ++v) {
+        const uint8_t *row = packed + v * bpr;
+        uint8_t *out = blocked.data() + (v / 32) * size_t(ng) * 32 + (v % 32);
+        for (int j = 0; j < dim; ++j) {
+            int code = 0;
+            for (int p = 0; p < bits; ++p) code |= ((row[p * bpp + j / 8] >> (7 - j % 8)) & 1) << p;
+            out[size_t(j / cpb) * 32] |= uint8_t(code << ((cpb - 1 - j % cpb) * field));
+        }
+    }
+}
+void blocked_to_packed(const uint8_t *blocked, size_t n, int bits, int dim, uint8_t *packed) {
+    const int bpp = dim / 8, cpb = 8 / bits, ng = dim / cpb, bpr = bits * bpp, field = bits == 3 ? 4 : bits;
+    std::memset(packed, 0, n * size_t(bpr));
+    for (size_t v = 0; v < n; ++v) {
+        uint8_t *row = packed + v * bpr;
+        const uint8_t *in = blocked + (v / 32) * size_t(ng) * 32 + (v % 32);
+        for (int j = 0; j < dim; ++j) {
+            const int code = (in[size_t(j / cpb) * 32] >> ((cpb - 1 - j % cpb) * field)) & ((1 << bits) - 1);
+            for (int p = 0; p < bits; ++p) row[p * bpp + j / 8] |= uint8_t(((code >> p) & 1) << (7 - j % 8));
+        }
+    }
+}
+
+}  // namespace
+
+// =====================================================================================================
+// C ABI
+// =====================================================================================================
+extern "C" {
+
+const char *tv_version(void) { return "turbovec_b200 0.1 (sm_100a)"; }
+
+int tv_index_create(size_t dim, int bit_width, int kind, int device, tv_index **out) {
+    tv_index *h = nullptr;
+    if (!out) return fail(h, TV_ERR_INVALID_ARGUMENT, "out is null");
+    *out = nullptr;
+    if (bit_width < 2 || bit_width > 4) return fail(h, TV_ERR_BIT_WIDTH_OUT_OF_RANGE, "bit_width must be 2, 3 or 4, got " + std::to_string(bit_width));
+    if (dim != 0) {
+        if (dim % 8 != 0) return fail(h, TV_ERR_DIM_NOT_POSITIVE_MULTIPLE_OF_8, "dim must be a positive multiple of 8, got " + std::to_string(dim));
+        if (dim > size_t(kMaxDim)) return fail(h, TV_ERR_DIM_TOO_LARGE, "dim " + std::to_string(dim) + " exceeds " + std::to_string(kMaxDim));
+    }
+    if (kind != TV_KIND_POSITIONAL && kind != TV_KIND_IDMAP) return fail(h, TV_ERR_INVALID_ARGUMENT, "unknown index kind");
+    int count = 0;
+    cudaError_t e = cudaGetDeviceCount(&count);
+    if (e != cudaSuccess || count == 0) {
+        cudaGetLastError();
+        return fail(h, TV_ERR_CUDA, std::string("no CUDA device: this library has no CPU path (") + cudaGetErrorString(e) + ")");
+    }
+    if (device < 0 || device >= count) return fail(h, TV_ERR_INVALID_ARGUMENT, "device ordinal out of range");
+    h = new tv_index();
+    h->kind = kind; h->bits = bit_width; h->device = device; h->dim = dim;
+    auto bail = [&](const char *what, cudaError_t err) {
+        std::string msg = std::string(what) + ": " + cudaGetErrorString(err);
+        cudaGetLastError();
+        delete h;
+        g_create_error = msg;
+        return int(TV_ERR_CUDA);
+    };
+    if ((e = cudaSetDevice(device)) != cudaSuccess) return bail("cudaSetDevice", e);
+    cudaDeviceProp prop{};
+    if ((e = cudaGetDeviceProperties(&prop, device)) != cudaSuccess) return bail("cudaGetDeviceProperties", e);
+    h->sm_count = prop.multiProcessorCount;
+    h->smem_limit = prop.sharedMemPerBlockOptin;
+    if ((e = cudaStreamCreateWithFlags(&h->stream, cudaStreamNonBlocking)) != cudaSuccess) return bail("cudaStreamCreate", e);
+    if ((e = cudaEventCreate(&h->ev0)) != cudaSuccess) return bail("cudaEventCreate", e);
+    if ((e = cudaEventCreate(&h->ev1)) != cudaSuccess) return bail("cudaEventCreate", e);
+    if ((e = cudaMalloc(&h->d_flags, sizeof(DeviceFlags))) != cudaSuccess) return bail("cudaMalloc", e);
+    if ((e = cudaMallocHost(&h->h_flags, sizeof(DeviceFlags))) != cudaSuccess) return bail("cudaMallocHost", e);
+    *out = h;
+    return TV_OK;
+}
+
+void tv_index_destroy(tv_index *h) { delete h; }
+
+const char *tv_last_error(const tv_index *h) { return h ? h->last_error.c_str() : g_create_error.c_str(); }
+
+void tv_error_detail(const tv_index *h, size_t *vector_index, size_t *coord_index, float *value, uint64_t *id) {
+    if (!h) return;
+    if (vector_index) *vector_index = h->err_vec;
+    if (coord_index) *coord_index = h->err_coord;
+    if (value) *value = h->err_value;
+    if (id) *id = h->err_id;
+}
+
+size_t tv_len(const tv_index *h) { return h ? h->n : 0; }
+size_t tv_dim(const tv_index *h) { return h ? h->dim : 0; }
+int tv_bit_width(const tv_index *h) { return h ? h->bits : 0; }
+int tv_kind(const tv_index *h) { return h ? h->kind : -1; }
+uint64_t tv_launch_count(const tv_index *h) { return h ? h->launches : 0; }
+float tv_last_kernel_ms(const tv_index *h) { return h ? h->last_ms : 0.f; }
+
+int tv_set_option(tv_index *h, int option, int64_t value) {
+    if (!h) return TV_ERR_INVALID_ARGUMENT;
+    std::lock_guard<std::mutex> lock(h->mu);
+    switch (option) {
+        case TV_OPT_SCORE_MODE:
+            if (value < TV_SCORE_AUTO || value > TV_SCORE_LUT_FLUSH) return fail(h, TV_ERR_INVALID_ARGUMENT, "unknown score mode");
+            if (value == TV_SCORE_PERMUTE_DOT && h->bits != 4) return fail(h, TV_ERR_INVALID_ARGUMENT, "permute-dot scoring needs 4-bit codes");
+            h->score_mode = int(value);
+            return TV_OK;
+        case TV_OPT_MMA_MIN_BATCH: h->mma_min_batch = value; return TV_OK;
+        case TV_OPT_FORCE_CAREFUL: h->force_careful = value != 0; return TV_OK;
+        default: return fail(h, TV_ERR_INVALID_ARGUMENT, "unknown option");
+    }
+}
+
+int64_t tv_get_option(const tv_index *h, int option) {
+    if (!h) return -1;
+    switch (option) {
+        case TV_OPT_SCORE_MODE: return h->dim ? resolve_mode(h) : h->score_mode;
+        case TV_OPT_MMA_MIN_BATCH: return h->mma_min_batch;
+        case TV_OPT_FORCE_CAREFUL: return h->force_careful;
+        default: return -1;
+    }
+}
+
+int tv_add(tv_index *h, const float *vectors, size_t n, size_t dim) {
+    if (!h || (!vectors && n)) return TV_ERR_INVALID_ARGUMENT;
+    std::lock_guard<std::mutex> lock(h->mu);
+    if (h->kind != TV_KIND_POSITIONAL) return fail(h, TV_ERR_WRONG_INDEX_KIND, "tv_add on an id-mapped index; use tv_add_with_ids");
+    return add_rows(h, vectors, n, dim, false);
+}
+
+int tv_add_device(tv_index *h, const float *vectors_device, size_t n, size_t dim) {
+    if (!h || (!vectors_device && n)) return TV_ERR_INVALID_ARGUMENT;
+    std::lock_guard<std::mutex> lock(h->mu);
+    if (h->kind != TV_KIND_POSITIONAL) return fail(h, TV_ERR_WRONG_INDEX_KIND, "tv_add_device on an id-mapped index");
+    return add_rows(h, vectors_device, n, dim, true);
+}
+
+int tv_add_with_ids(tv_index *h, const float *vectors, size_t n, size_t dim, const uint64_t *ids) {
+    if (!h || (!vectors && n) || (!ids && n)) return TV_ERR_INVALID_ARGUMENT;
+    std::lock_guard<std::mutex> lock(h->mu);
+    if (h->kind != TV_KIND_IDMAP) return fail(h, TV_ERR_WRONG_INDEX_KIND, "tv_add_with_ids needs an id-mapped index");
+    if (dim == 0) return fail(h, TV_ERR_ZERO_DIM, "dim must be non-zero");          // id_map.rs:379-381
+    // per id, in order: already present, then duplicate within the batch (id_map.rs:396-434)
+    std::unordered_set<uint64_t> seen;
+    seen.reserve(n * 2);
+    for (size_t i = 0; i < n; ++i) {
+        if (h->id_to_slot.count(ids[i])) {
+            h->err_id = ids[i];
+            return fail(h, TV_ERR_ID_ALREADY_PRESENT, "id " + std::to_string(ids[i]) + " is already present");
+        }
+        if (!seen.insert(ids[i]).second) {
+            h->err_id = ids[i];
+            return fail(h, TV_ERR_DUPLICATE_ID_IN_BATCH, "id " + std::to_string(ids[i]) + " appears twice in the batch");
+        }
+    }
+    const size_t base = h->n;
+    int rc = add_rows(h, vectors, n, dim, false);
+    if (rc != TV_OK) return rc;
+    h->slot_to_id.insert(h->slot_to_id.end(), ids, ids + n);
+    h->id_to_slot.reserve(h->id_to_slot.size() + n);
+    for (size_t i = 0; i < n; ++i) h->id_to_slot.emplace(ids[i], uint32_t(base + i));
+    return TV_OK;
+}
+
+int tv_swap_remove(tv_index *h, size_t slot, size_t *moved_from) {
+    if (!h) return TV_ERR_INVALID_ARGUMENT;
+    std::lock_guard<std::mutex> lock(h->mu);
+    if (h->kind != TV_KIND_POSITIONAL) return fail(h, TV_ERR_WRONG_INDEX_KIND, "tv_swap_remove on an id-mapped index; use tv_remove");
+    if (slot >= h->n) return fail(h, TV_ERR_SLOT_OUT_OF_RANGE, "index " + std::to_string(slot) + " out of bounds (n_vectors = " + std::to_string(h->n) + ")");
+    TV_CUDA(cudaSetDevice(h->device));
+    const size_t last = h->n - 1;
+    move_lane_kernel<<<(h->ngroups + 255) / 256, 256, 0, h->stream>>>(h->d_codes, h->d_scales, h->ngroups, int64_t(last), int64_t(slot));
+    h->launches++;
+    TV_CUDA(cudaGetLastError());
+    TV_CUDA(cudaStreamSynchronize(h->stream));
+    h->n = last;
+    if (moved_from) *moved_from = last;
+    return TV_OK;
+}
+
+int tv_remove(tv_index *h, uint64_t id, int *removed) {
+    if (!h) return TV_ERR_INVALID_ARGUMENT;
+    std::lock_guard<std::mutex> lock(h->mu);
+    if (removed) *removed = 0;
+    if (h->kind != TV_KIND_IDMAP) return fail(h, TV_ERR_WRONG_INDEX_KIND, "tv_remove needs an id-mapped index");
+    auto it = h->id_to_slot.find(id);
+    if (it == h->id_to_slot.end()) return TV_OK;                       // id_map.rs:521-523
+    const size_t slot = it->second, last = h->n - 1;
+    TV_CUDA(cudaSetDevice(h->device));
+    move_lane_kernel<<<(h->ngroups + 255) / 256, 256, 0, h->stream>>>(h->d_codes, h->d_scales, h->ngroups, int64_t(last), int64_t(slot));
+    h->launches++;
+    TV_CUDA(cudaGetLastError());
+    TV_CUDA(cudaStreamSynchronize(h->stream));
+    h->n = last;
+    h->id_to_slot.erase(it);
+    if (slot != last) {                                                // id_map.rs:557-561
+        const uint64_t moved = h->slot_to_id[last];
+        h->slot_to_id[slot] = moved;
+        h->id_to_slot[moved] = uint32_t(slot);
+    }
+    h->slot_to_id.pop_back();
+    if (removed) *removed = 1;
+    return TV_OK;
+}
+
+int tv_contains(const tv_index *h, uint64_t id, int *present) {
+    if (!h || !present) return TV_ERR_INVALID_ARGUMENT;
+    *present = h->id_to_slot.count(id) ? 1 : 0;
+    return TV_OK;
+}
+
+int tv_ids(const tv_index *h, uint64_t *ids_out, size_t capacity) {
+    if (!h || (!ids_out && capacity)) return TV_ERR_INVALID_ARGUMENT;
+    if (capacity < h->slot_to_id.size()) return TV_ERR_INVALID_ARGUMENT;
+    std::copy(h->slot_to_id.begin(), h->slot_to_id.end(), ids_out);
+    return TV_OK;
+}
+
+int tv_search(tv_index *h, const float *queries, size_t nq, size_t dim, size_t k, const uint8_t *mask_bool,
+              size_t mask_len, float *scores_out, int64_t *slots_out, size_t *k_eff) {
+    if (!h || (!queries && nq)) return TV_ERR_INVALID_ARGUMENT;
+    std::lock_guard<std::mutex> lock(h->mu);
+    MaskSpec m;
+    m.bool_host = mask_bool; m.bool_len = mask_len;
+    return search_host(h, queries, nq, dim, k, m, scores_out, slots_out, nullptr, k_eff);
+}
+
+int tv_search_mask_words(tv_index *h, const float *queries, size_t nq, size_t dim, size_t k, const uint64_t *mask_words,
+                         size_t n_words, float *scores_out, int64_t *slots_out, size_t *k_eff) {
+    if (!h || (!queries && nq)) return TV_ERR_INVALID_ARGUMENT;
+    std::lock_guard<std::mutex> lock(h->mu);
+    MaskSpec m;
+    m.words_host = mask_words; m.n_words = n_words;
+    return search_host(h, queries, nq, dim, k, m, scores_out, slots_out, nullptr, k_eff);
+}
+
+int tv_search_allowlist(tv_index *h, const float *queries, size_t nq, size_t dim, size_t k, const uint64_t *allow_ids,
+                        size_t n_allow, float *scores_out, uint64_t *ids_out, size_t *k_eff) {
+    if (!h || (!queries && nq)) return TV_ERR_INVALID_ARGUMENT;
+    std::lock_guard<std::mutex> lock(h->mu);
+    if (h->kind != TV_KIND_IDMAP) return fail(h, TV_ERR_WRONG_INDEX_KIND, "tv_search_allowlist needs an id-mapped index");
+    if (k_eff) *k_eff = 0;
+    MaskSpec m;
+    std::vector<uint32_t> slots;
+    if (allow_ids) {                                                    // id_map.rs:670-683
+        if (n_allow == 0) return fail(h, TV_ERR_ALLOWLIST_EMPTY, "allowlist is empty");
+        slots.reserve(n_allow);
+        for (size_t i = 0; i < n_allow; ++i) {
+            auto it = h->id_to_slot.find(allow_ids[i]);
+            if (it == h->id_to_slot.end()) {
+                h->err_id = allow_ids[i];
+                return fail(h, TV_ERR_UNKNOWN_ID, "allowlist id " + std::to_string(allow_ids[i]) + " is not in the index");
+            }
+            slots.push_back(it->second);
+        }
+        m.slots_host = slots.data(); m.n_slots = slots.size();
+    }
+    return search_host(h, queries, nq, dim, k, m, scores_out, nullptr, ids_out, k_eff);
+}
+
+int tv_search_device(tv_index *h, const float *queries_device, size_t nq, size_t k, const uint64_t *mask_words_device,
+                     float *scores_out_device, int64_t *slots_out_device, size_t *k_eff) {
+    if (!h || (!queries_device && nq) || !scores_out_device || !slots_out_device) return TV_ERR_INVALID_ARGUMENT;
+    std::lock_guard<std::mutex> lock(h->mu);
+    if (k_eff) *k_eff = 0;
+    if (h->dim == 0 || h->n == 0 || nq == 0) return TV_OK;
+    MaskSpec m;
+    m.words_device = mask_words_device;
+    size_t ke = 0;
+    int rc = search_core(h, queries_device, true, nq, k, m, scores_out_device, slots_out_device, &ke);
+    if (rc == TV_OK && k_eff) *k_eff = ke;
+    return rc;
+}
+
+int tv_prepare(tv_index *h) {
+    if (!h) return TV_ERR_INVALID_ARGUMENT;
+    std::lock_guard<std::mutex> lock(h->mu);
+    if (h->dim == 0) return TV_OK;
+    TV_CUDA(cudaSetDevice(h->device));
+    return ensure_tables(h);
+}
+
+size_t tv_blocked_bytes(const tv_index *h) {
+    if (!h || h->dim == 0) return 0;
+    return ((h->n + kBlock - 1) / kBlock) * size_t(h->dim / (8 / h->bits)) * kBlock;
+}
+
+int tv_export_blocked(const tv_index *hc, uint8_t *blocked_out, size_t blocked_capacity, float *scales_out, size_t scales_capacity) {
+    tv_index *h = const_cast<tv_index *>(hc);
+    if (!h) return TV_ERR_INVALID_ARGUMENT;
+    std::lock_guard<std::mutex> lock(h->mu);
+    const size_t bytes = tv_blocked_bytes(h);
+    if ((blocked_out && blocked_capacity < bytes) || (scales_out && scales_capacity < h->n)) return fail(h, TV_ERR_INVALID_ARGUMENT, "output buffer too small");
+    if (h->n == 0) return TV_OK;
+    TV_CUDA(cudaSetDevice(h->device));
+    if (blocked_out) TV_CUDA(cudaMemcpyAsync(blocked_out, h->d_codes, bytes, cudaMemcpyDeviceToHost, h->stream));
+    if (scales_out) TV_CUDA(cudaMemcpyAsync(scales_out, h->d_scales, h->n * 4, cudaMemcpyDeviceToHost, h->stream));
+    TV_CUDA(cudaStreamSynchronize(h->stream));
+    return TV_OK;
+}
+
+int tv_export_packed(const tv_index *hc, uint8_t *packed_out, size_t capacity) {
+    tv_index *h = const_cast<tv_index *>(hc);
+    if (!h) return TV_ERR_INVALID_ARGUMENT;
+    if (h->n == 0) return TV_OK;
+    const size_t need = h->n * size_t(h->bits) * h->dim / 8;
+    if (!packed_out || capacity < need) return fail(h, TV_ERR_INVALID_ARGUMENT, "output buffer too small");
+    std::vector<uint8_t> blocked(tv_blocked_bytes(h));
+    int rc = tv_export_blocked(h, blocked.data(), blocked.size(), nullptr, 0);
+    if (rc != TV_OK) return rc;
+    blocked_to_packed(blocked.data(), h->n, h->bits, int(h->dim), packed_out);
+    return TV_OK;
+}
+
+int tv_import_packed(tv_index *h, size_t dim, const uint8_t *packed, size_t n, const float *scales, const uint64_t *ids) {
+    if (!h || (n && (!packed || !scales))) return TV_ERR_INVALID_ARGUMENT;
+    std::lock_guard<std::mutex> lock(h->mu);
+    if (h->n != 0) return fail(h, TV_ERR_PARTS_INVALID, "import needs an empty index");
+    int rc = validate_dim_for_add(h, dim);
+    if (rc != TV_OK) return rc;
+    if ((h->kind == TV_KIND_IDMAP) != (ids != nullptr) && n) return fail(h, TV_ERR_PARTS_INVALID, "ids must be given exactly for id-mapped indexes");
+    for (size_t i = 0; i < n; ++i)   // lib.rs:2460-2492: scales finite and non-negative
+        if (!(scales[i] >= 0.0f) || !std::isfinite(scales[i])) return fail(h, TV_ERR_PARTS_INVALID, "scale " + std::to_string(i) + " is negative or not finite");
+    if (ids) {
+        std::unordered_set<uint64_t> seen(ids, ids + n);
+        if (seen.size() != n) return fail(h, TV_ERR_PARTS_INVALID, "duplicate ids");
+    }
+    if (n == 0) { if (h->dim == 0) h->dim = dim; return TV_OK; }
+    TV_CUDA(cudaSetDevice(h->device));
+    const bool was_lazy = h->dim == 0;
+    h->dim = dim;
+    rc = ensure_tables(h);
+    if (rc == TV_OK) rc = ensure_capacity(h, n);
+    if (rc != TV_OK) { if (was_lazy) { h->dim = 0; h->tables_ready = false; } return rc; }
+    std::vector<uint8_t> blocked;
+    packed_to_blocked(packed, n, h->bits, int(dim), blocked);
+    TV_CUDA(cudaMemcpyAsync(h->d_codes, blocked.data(), blocked.size(), cudaMemcpyHostToDevice, h->stream));
+    TV_CUDA(cudaMemcpyAsync(h->d_scales, scales, n * 4, cudaMemcpyHostToDevice, h->stream));
+    TV_CUDA(cudaStreamSynchronize(h->stream));
+    h->n = n;
+    if (ids) {
+        h->slot_to_id.assign(ids, ids + n);
+        h->id_to_slot.clear();
+        for (size_t i = 0; i < n; ++i) h->id_to_slot.emplace(ids[i], uint32_t(i));
+    }
+    return TV_OK;
+}
+
+int tv_codebook(tv_index *h, float *boundaries_out, float *centroids_out) {
+    if (!h) return TV_ERR_INVALID_ARGUMENT;
+    std::lock_guard<std::mutex> lock(h->mu);
+    if (h->dim == 0) return fail(h, TV_ERR_DIM_NOT_SET, "dimension is not set yet");
+    const Codebook &cb = codebook(h->bits, int(h->dim));
+    if (boundaries_out) std::copy(cb.boundaries.begin(), cb.boundaries.end(), boundaries_out);
+    if (centroids_out) std::copy(cb.centroids.begin(), cb.centroids.end(), centroids_out);
+    return TV_OK;
+}
+
+int tv_rotate(tv_index *h, const float *rows, size_t n, size_t dim, float *rotated_out) {
+    if (!h || !rows || !rotated_out) return TV_ERR_INVALID_ARGUMENT;
+    std::lock_guard<std::mutex> lock(h->mu);
+    if (h->dim == 0 || dim != h->dim) return fail(h, TV_ERR_DIM_MISMATCH, "tv_rotate needs rows of the index dimension");
+    if (n == 0) return TV_OK;
+    TV_CUDA(cudaSetDevice(h->device));
+    int rc = ensure_tables(h);
+    if (rc != TV_OK) return rc;
+    cudaStream_t st = h->stream;
+    const size_t nq_pad = (n + 15) / 16 * 16;
+    TV_CUDA(h->d_stage.reserve(n * dim));
+    TV_CUDA(h->d_qrot.reserve(n * dim));
+    TV_CUDA(h->d_qscale.reserve(nq_pad));
+    TV_CUDA(h->d_qbias.reserve(nq_pad));
+    TV_CUDA(h->d_luts.reserve(n * size_t(h->ngroups) * 32));
+    TV_CUDA(cudaMemcpyAsync(h->d_stage.ptr, rows, n * dim * 4, cudaMemcpyHostToDevice, st));
+    QueryPrepParams qp{};
+    qp.queries = h->d_stage.ptr; qp.nq = int(n); qp.dim = int(dim); qp.bits = h->bits; qp.ngroups = h->ngroups;
+    qp.mode = kModeLutMulAdd;
+    qp.perm0 = h->d_perm.ptr; qp.perm1 = h->d_perm.ptr + dim; qp.inv_sqrt_block = h->rot.inv_sqrt_block;
+    qp.centroids = h->d_codebook.ptr + 16;
+    qp.q_rot = h->d_qrot.ptr; qp.qscale = h->d_qscale.ptr; qp.qbias = h->d_qbias.ptr; qp.luts = h->d_luts.ptr;
+    qp.first_invalid = &h->d_flags->first_invalid;
+    TV_CUDA(launch_query_prep(qp, st));
+    h->launches++;
+    TV_CUDA(cudaMemcpyAsync(rotated_out, h->d_qrot.ptr, n * dim * 4, cudaMemcpyDeviceToHost, st));
+    TV_CUDA(cudaStreamSynchronize(st));
+    return TV_OK;
+}
+
+int tv_set_calibration(tv_index *h, size_t dim, const float *shift, const float *scale) {
+    if (!h || !shift || !scale) return TV_ERR_INVALID_ARGUMENT;
+    std::lock_guard<std::mutex> lock(h->mu);
+    if (h->n != 0) return fail(h, TV_ERR_CALIBRATE_NOT_EMPTY, "calibration can only be set on an empty index");
+    int rc = validate_dim_for_add(h, dim);
+    if (rc != TV_OK) return rc;
+    for (size_t d = 0; d < dim; ++d)
+        if (!std::isfinite(shift[d]) || !std::isfinite(scale[d]) || !(scale[d] > 0.f))
+            return fail(h, TV_ERR_PARTS_INVALID, "calibration entry " + std::to_string(d) + " is not finite or scale is not positive");
+    TV_CUDA(cudaSetDevice(h->device));
+    h->dim = dim;
+    h->shift.assign(shift, shift + dim);
+    h->scale_tq.assign(scale, scale + dim);
+    rc = ensure_tables(h);
+    if (rc != TV_OK) return rc;
+    return upload_calibration(h);
+}
+
+int tv_calibration(const tv_index *h, float *shift_out, float *scale_out, size_t capacity, int *is_calibrated) {
+    if (!h) return TV_ERR_INVALID_ARGUMENT;
+    if (is_calibrated) *is_calibrated = h->shift.empty() ? 0 : 1;
+    if (h->shift.empty()) return TV_OK;
+    if (capacity < h->dim) return TV_ERR_INVALID_ARGUMENT;
+    if (shift_out) std::copy(h->shift.begin(), h->shift.end(), shift_out);
+    if (scale_out) std::copy(h->scale_tq.begin(), h->scale_tq.end(), scale_out);
+    return TV_OK;
+}
+
+int tv_calibrate(tv_index *h, const float *sample, size_t n, size_t dim) {
+    (void)sample; (void)n; (void)dim;
+    if (!h) return TV_ERR_INVALID_ARGUMENT;
+    return fail(h, TV_ERR_UNSUPPORTED, "tv_calibrate: the TQ+ fit is not built yet; fit on the host and use tv_set_calibration");
+}
+
+}  // extern "C"

@@ -1,0 +1,37 @@
+// Launch interface of the fused ingest kernel (see ingest.cu).
+#pragma once
+#include <cuda_runtime.h>
+
+#include <cstddef>
+#include <cstdint>
+
+namespace tv {
+
+constexpr int kBlockLanes = 32;              // vectors per code block (turbovec/src/lib.rs:89)
+constexpr float kMaxMagnitude = 1e16f;       // turbovec/src/lib.rs:109
+constexpr float kMinNorm = 1e-10f;           // turbovec/src/lib.rs:163
+
+struct IngestParams {
+    const float *x;                // [n][dim] device, row-major
+    int64_t n;                     // rows in this batch
+    int64_t slot0;                 // slot of the first row (= index length before the add)
+    int64_t row_base;              // index of x's first row within the caller's whole batch (for error reports)
+    int dim, bits, ngroups;
+    const uint16_t *perm0, *perm1; // packed rotation tables (host_tables.hpp)
+    float inv_sqrt_block;
+    const float *boundaries;       // 2^bits - 1
+    const float *centroids;        // 2^bits
+    const float *shift;            // TQ+ pair or nullptr (identity)
+    const float *scale_tq;
+    const float *inv_scale_tq;     // 1.0f / scale_tq[d], rounded once in f32 (encode.rs:593)
+    uint8_t *codes;                // sequential-blocked code array of the whole index
+    float *scales;                 // per-slot scales of the whole index
+    unsigned long long *first_invalid;  // min flat index of a coordinate failing |x| < 1e16 (init ~0ull)
+};
+
+size_t ingest_smem_bytes(int vectors_per_pass, int dim, int ngroups);
+// Largest supported vectors-per-pass whose shared memory fits `smem_limit`, 0 if none.
+int ingest_vectors_per_pass(int dim, int ngroups, size_t smem_limit);
+cudaError_t launch_ingest(const IngestParams &p, int vectors_per_pass, cudaStream_t stream);
+
+}  // namespace tv

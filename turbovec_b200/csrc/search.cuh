@@ -1,0 +1,92 @@
+// Launch interface of the search-side kernels (see search.cu).
+#pragma once
+#include <cuda_runtime.h>
+
+#include <cstddef>
+#include <cstdint>
+
+namespace tv {
+
+// Float epilogues of the reference's kernel families (turbovec/src/search.rs:1523, 1176, 1596).
+enum ScoreMode : int { kModePermuteDot = 1, kModeLutMulAdd = 2, kModeLutFlush = 3 };
+
+struct QueryPrepParams {
+    const float *queries;          // [nq][dim] device
+    int nq, dim, bits, ngroups;
+    int mode;                      // ScoreMode
+    const uint16_t *perm0, *perm1;
+    float inv_sqrt_block;
+    const float *centroids;        // 2^bits
+    const float *shift;            // TQ+ pair or nullptr
+    const float *scale_tq;
+    float level_scale;             // cs of search.rs:2815 (permute-dot only)
+    // outputs
+    float *q_rot;                  // [nq][dim] rotated (and TQ+-inverted) queries
+    float *qscale, *qbias;         // [nq]
+    uint8_t *luts;                 // [nq][ngroups*32]            (LUT modes)
+    int8_t *weights;               // [nq_pad][dim_pad] row-major  (permute-dot; tensor-core operand)
+    int dim_pad;                   // row pitch of `weights`
+    uint32_t *wfrag;               // mma.sync A fragments (permute-dot), see scan kernel
+    int mtiles_total;              // ceil(nq / 16)
+    unsigned long long *first_invalid;  // min flat index of a query coordinate failing |x| < 1e16
+};
+size_t query_prep_smem_bytes(int dim);
+cudaError_t launch_query_prep(const QueryPrepParams &p, cudaStream_t stream);
+
+// ---- allow-mask utilities: bit i of little-endian u64 word i/64 <=> slot i (search.rs:2996-3004) ----
+cudaError_t launch_pack_bool_mask(const uint8_t *mask_bool, int64_t n, uint64_t *words, cudaStream_t s);
+cudaError_t launch_scatter_slots(const uint32_t *slots, int64_t count, uint64_t *words, cudaStream_t s);
+// Clears bits >= n, counts allowed slots into *n_allowed, appends every block whose 32-bit half word is
+// non-zero (search.rs:3015-3029) to live_blocks and counts them in *n_live (both zeroed by the caller).
+cudaError_t launch_mask_stats(uint64_t *words, int64_t n, unsigned long long *n_allowed, uint32_t *live_blocks,
+                              uint32_t *n_live, cudaStream_t s);
+
+// ---- candidate machinery ----
+// Scan kernels append the key of every (query, slot) whose key is below thr[query] to
+// cand[query*cap ...]; cnt[query] counts appends (it may exceed cap: the excess is dropped and the
+// select kernel raises *overflow).  select merges candidates into topk[query*k ...] (ascending keys,
+// kEmptyKey padded), refreshes thr and zeroes cnt.
+struct CandidateBuffers {
+    uint64_t *cand;
+    uint32_t *cnt;
+    uint64_t *thr;
+    uint64_t *topk;
+    uint32_t *overflow;
+    uint32_t *error;               // device-side wait timeouts
+    int cap, k;
+};
+size_t select_smem_bytes(int cap, int k);
+cudaError_t launch_select(const CandidateBuffers &cb, int nq, cudaStream_t s);
+// topk keys -> scores / slots with row stride k_eff = min(k, n_allowed); *k_eff_out receives it.
+cudaError_t launch_finalize(const CandidateBuffers &cb, int nq, const unsigned long long *n_allowed_or_null,
+                            int64_t n, float *scores, int64_t *slots, uint32_t *k_eff_out, int out_stride_is_k,
+                            cudaStream_t s);
+
+struct ScanParams {
+    const uint8_t *codes;          // sequential-blocked
+    const float *vec_scales;
+    int64_t n;                     // vectors in the index
+    int ngroups, bits;
+    int mode;                      // ScoreMode
+    int nq;                        // queries of this launch
+    int q_base;                    // first query (offset into per-query arrays)
+    const float *qscale, *qbias;
+    const uint64_t *mask;          // or nullptr
+    const uint32_t *live_blocks;   // or nullptr: positions are block ids
+    const uint32_t *n_live;        // device count of live_blocks (when live_blocks != nullptr)
+    uint32_t pos_begin, pos_end;   // positions scanned by this launch
+    CandidateBuffers cb;
+    // permute-dot
+    const uint32_t *wfrag;
+    int mtiles_total, mtile_base;
+    uint32_t level_words[4];       // 16 int8 levels, entry c in byte c%4 of word c/4
+    // LUT
+    const uint8_t *luts;
+};
+// Permute-dot scan on mma.sync (int8 x int8 -> int32), up to 64 queries per launch.
+cudaError_t launch_scan_pd(const ScanParams &p, int sm_count, cudaStream_t s);
+// LUT scan on CUDA cores, up to kLutQueriesPerLaunch queries per launch.
+constexpr int kLutQueriesPerLaunch = 4;
+cudaError_t launch_scan_lut(const ScanParams &p, int sm_count, cudaStream_t s);
+
+}  // namespace tv
