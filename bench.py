@@ -1,0 +1,346 @@
+#!/usr/bin/env python
+"""Benchmark of the encode-and-scan hot path.
+
+  python bench.py [--gpus N] [--steps K] [--warmup W] [--impl ours|reference] [--n N_VECTORS] [--batch NQ]
+
+Workload (N = 1): 10,000,000 x 1536 fp32 rows (anisotropic Gaussian, L2-normalised; synthetic stand-in for the
+OpenAI-1536 embeddings the reference measures on), 4-bit codes, k = 10.  One step = one search batch of 1,024
+queries.  `value` is queries/s with queries and results resident in HBM; `e2e` is the same through the host
+API (pinned host queries in, host results out, copies inside the timed region).  Batch-1 latency, ingest rate
+and recall@10 ride along as extra keys.  With N > 1 (torchrun, one rank per GPU) the same 10 M vectors are
+slot-sharded over the ranks and the per-rank top-k lists are merged after one NCCL all-gather (strong scaling).
+
+`--impl reference` times the CPU restatement of the reference's algorithm (the reference is a Rust crate and
+cannot be built without a Rust toolchain) on all host threads, on a bounded sample of the same workload.
+"""
+from __future__ import annotations
+
+import argparse
+import json
+import os
+import subprocess
+import sys
+import threading
+import time
+
+import numpy as np
+
+ROOT = os.path.dirname(os.path.abspath(__file__))
+if ROOT not in sys.path:
+    sys.path.insert(0, ROOT)
+
+DIM, BITS, K = 1536, 4, 10
+METRIC = "search_qps_k10_10Mx1536_4bit_batch1024"
+UNIT = "queries/s"
+CHUNK = 1 << 18           # rows generated and ingested at a time (1.6 GB of fp32)
+
+
+def peaks():
+    path = os.path.join(ROOT, "MEASURED_PEAKS.json")
+    if os.path.exists(path):
+        p = json.load(open(path))
+        return {"hbm_gbs": p["hbm_gbs"], "tensor_tflops": p["bf16_tflops_sustained"], "source": "measured"}
+    return {"hbm_gbs": 6650.0, "tensor_tflops": 1400.0, "source": "fallback"}
+
+
+# ------------------------------------------------------------------------------------------ data
+def dim_scale(seed: int):
+    return np.exp(0.5 * np.random.default_rng(seed).standard_normal(DIM)).astype(np.float32)
+
+
+def gen_rows_torch(torch, device, scale_t, seed: int, chunk_id: int, rows: int):
+    """Rows of global chunk `chunk_id`: identical for any GPU count."""
+    g = torch.Generator(device=device)
+    g.manual_seed(seed * 1_000_003 + chunk_id)
+    x = torch.randn((rows, DIM), generator=g, device=device, dtype=torch.float32) * scale_t
+    x /= x.norm(dim=1, keepdim=True)
+    return x.contiguous()
+
+
+def gen_rows_numpy(seed: int, n: int, offset: int):
+    s = dim_scale(seed)
+    x = np.random.default_rng(seed * 7919 + 13 + offset).standard_normal((n, DIM)).astype(np.float32) * s
+    x /= np.linalg.norm(x, axis=1, keepdims=True)
+    return np.ascontiguousarray(x, dtype=np.float32)
+
+
+# ------------------------------------------------------------------------------------------ clocks
+class ClockSampler:
+    """Samples SM clocks and throttle reasons with nvidia-smi while the timed region runs."""
+
+    def __init__(self, gpu_index: int):
+        self.rows, self.proc, self.gpu = [], None, gpu_index
+
+    def start(self):
+        q = ("clocks.sm,clocks.max.sm,clocks_event_reasons.hw_slowdown,clocks_event_reasons.hw_thermal_slowdown,"
+             "clocks_event_reasons.sw_thermal_slowdown,clocks_event_reasons.sw_power_cap")
+        try:
+            self.proc = subprocess.Popen(["nvidia-smi", f"--query-gpu={q}", "--format=csv,noheader,nounits",
+                                          "-lms", "100", "-i", str(self.gpu)], stdout=subprocess.PIPE, text=True)
+            threading.Thread(target=self._pump, daemon=True).start()
+        except Exception:
+            self.proc = None
+
+    def _pump(self):
+        for line in self.proc.stdout:
+            self.rows.append([c.strip() for c in line.split(",")])
+
+    def stop(self):
+        if self.proc is None:
+            return {"sm_mhz": None, "sm_max_mhz": None, "reasons": ["nvidia-smi unavailable"]}
+        time.sleep(0.15)
+        self.proc.terminate()
+        sm = [float(r[0]) for r in self.rows if r and r[0].replace(".", "").isdigit()]
+        mx = [float(r[1]) for r in self.rows if len(r) > 1 and r[1].replace(".", "").isdigit()]
+        names = ["hw_slowdown", "hw_thermal_slowdown", "sw_thermal_slowdown", "sw_power_cap"]
+        reasons = [n for j, n in enumerate(names) if any(len(r) > 2 + j and r[2 + j].lower().startswith("active") for r in self.rows)]
+        return {"sm_mhz": float(np.median(sm)) if sm else None, "sm_max_mhz": max(mx) if mx else None,
+                "reasons": reasons, "samples": len(sm)}
+
+
+# ------------------------------------------------------------------------------------------ CPU arm
+def cpu_arm(n_sample: int, nq: int, steps: int, warmup: int, n_full: int):
+    """The oracle port on all host threads; returns (queries/s scaled to n_full vectors, ms/step, cores, text)."""
+    from oracle import oracle as O
+    cores = os.cpu_count() or 1
+    x = gen_rows_numpy(1, n_sample, 0)
+    q = gen_rows_numpy(1, nq, 10_000_000)
+    enc = O.encode(x, BITS)
+    blocked = O.packed_to_blocked(enc["packed"], BITS, DIM)
+    times = []
+    for it in range(warmup + steps):
+        t0 = time.perf_counter()
+        O.search(q, blocked, enc["scales"], n_sample, DIM, BITS, K)
+        if it >= warmup:
+            times.append(time.perf_counter() - t0)
+    sec = float(np.mean(times))
+    qps_sample = nq / sec
+    qps_full = qps_sample * n_sample / n_full      # the scan is linear in the number of vectors
+    sample = (f"{nq} queries x {n_sample} vectors (1/{n_full // n_sample} of the index) per step, {steps} steps; "
+              f"rate scaled linearly to {n_full} vectors")
+    return qps_full, sec * 1e3, cores, sample
+
+
+def run_reference(args):
+    rank = int(os.environ.get("RANK", "0"))
+    if rank != 0:
+        return
+    n_sample, nq = 100_000, 64
+    steps, warmup = max(1, min(args.steps, 5)), max(1, min(args.warmup, 2))
+    qps, ms, cores, sample = cpu_arm(n_sample, nq, steps, warmup, args.n)
+    line = {
+        "impl": "reference", "metric": METRIC, "value": qps, "unit": UNIT, "n_gpus": args.gpus, "steps": steps,
+        "warmup": warmup, "ms_per_step": ms, "higher_is_better": True, "scaling": "strong", "vs_baseline": None,
+        "dtype": "int8", "data": "synthetic",
+        "config": {"workload": f"{args.n} x {DIM} {BITS}-bit, k={K}, batch {args.batch} (CPU arm measured on a bounded sample)"},
+        "cpu_baseline": {"value": qps, "unit": UNIT, "cores": cores, "kind": "port", "sample": sample},
+        "e2e": {"value": qps, "unit": UNIT, "h2d_bytes_per_step": 0, "d2h_bytes_per_step": 0},
+        "note": "the reference is a Rust crate; no Rust toolchain on this box, so the C restatement of its algorithm is timed",
+    }
+    print(json.dumps(line))
+
+
+# ------------------------------------------------------------------------------------------ GPU arm
+def merge_topk(torch, scores, slots, k):
+    """Merge per-rank lists [nq, R*k] under (score desc, slot asc)."""
+    order = torch.argsort(slots, dim=1, stable=True)
+    s = torch.gather(scores, 1, order)
+    i = torch.gather(slots, 1, order)
+    order = torch.argsort(s, dim=1, descending=True, stable=True)
+    return torch.gather(s, 1, order)[:, :k], torch.gather(i, 1, order)[:, :k]
+
+
+def run_ours(args):
+    import torch
+    import torch.distributed as dist
+    import turbovec_b200 as T
+
+    world = int(os.environ.get("WORLD_SIZE", "1"))
+    rank = int(os.environ.get("RANK", "0"))
+    local_rank = int(os.environ.get("LOCAL_RANK", "0"))
+    if not torch.cuda.is_available():
+        raise SystemExit("bench.py needs a CUDA device: turbovec_b200 has no CPU path")
+    torch.cuda.set_device(local_rank)
+    device = torch.device("cuda", local_rank)
+    if world > 1:
+        dist.init_process_group("nccl", device_id=device)
+    pk = peaks()
+    n_total, nq = args.n, args.batch
+
+    # ---- build this rank's shard: global chunks dealt to ranks in contiguous runs ----
+    n_chunks = (n_total + CHUNK - 1) // CHUNK
+    per = (n_chunks + world - 1) // world
+    my_chunks = list(range(rank * per, min(n_chunks, (rank + 1) * per)))
+    slot_offset = my_chunks[0] * CHUNK if my_chunks else 0
+    scale_t = torch.from_numpy(dim_scale(1)).to(device)
+    idx = T.TurboQuantIndex(DIM, BITS, device=local_rank)
+    n_recall_q = 64
+    q_all = torch.from_numpy(gen_rows_numpy(1, max(nq, n_recall_q), 10_000_000)).to(device)
+    truth_s = torch.full((n_recall_q, K), -float("inf"), device=device)
+    truth_i = torch.zeros((n_recall_q, K), dtype=torch.int64, device=device)
+    ingest_ms, ingest_rows, ingest_launches = 0.0, 0, 0
+    launches0 = idx.launch_count
+    for c in my_chunks:
+        rows = min(CHUNK, n_total - c * CHUNK)
+        x = gen_rows_torch(torch, device, scale_t, 1, c, rows)
+        # exact fp32 ground truth for recall@10, kept as a running top-k
+        sc = q_all[:n_recall_q] @ x.T
+        s, i = torch.topk(sc, K, dim=1)
+        truth_s, sel = torch.topk(torch.cat([truth_s, s], 1), K, dim=1)
+        truth_i = torch.gather(torch.cat([truth_i, i + c * CHUNK], 1), 1, sel)
+        torch.cuda.synchronize()
+        idx.add_device(x.data_ptr(), rows, DIM)
+        ms, nl = idx.last_main_kernel()
+        if c != my_chunks[0]:          # first chunk pays table set-up and allocation
+            ingest_ms += ms
+            ingest_rows += rows
+            ingest_launches += nl
+        del x, sc
+    n_local = len(idx)
+
+    d_scores = torch.empty((nq, K), dtype=torch.float32, device=device)
+    d_slots = torch.empty((nq, K), dtype=torch.int64, device=device)
+    q_dev = q_all[:nq].contiguous()
+    q_host = q_dev.cpu().pin_memory()
+    h_scores = np.empty((nq, K), np.float32)
+
+    def step_device(qd, nqq):
+        ke = idx.search_device(qd.data_ptr(), nqq, K, d_scores.data_ptr(), d_slots.data_ptr())
+        if world == 1:
+            return d_scores[:nqq, :ke], d_slots[:nqq, :ke]
+        ls = d_scores.view(-1)[: nqq * ke].view(nqq, ke)
+        li = d_slots.view(-1)[: nqq * ke].view(nqq, ke) + slot_offset
+        gs = [torch.empty_like(ls) for _ in range(world)]
+        gi = [torch.empty_like(li) for _ in range(world)]
+        dist.all_gather(gs, ls.contiguous())
+        dist.all_gather(gi, li.contiguous())
+        return merge_topk(torch, torch.cat(gs, 1), torch.cat(gi, 1), K)
+
+    def step_host(qh, nqq):
+        if world == 1:
+            return idx.search(qh, K)
+        s, i = step_device(qh.to(device, non_blocking=True), nqq)
+        return s.cpu().numpy(), i.cpu().numpy()
+
+    def barrier():
+        torch.cuda.synchronize()
+        if world > 1:
+            dist.barrier()
+            torch.cuda.synchronize()
+
+    def timed(fn, steps, warmup):
+        for _ in range(warmup):
+            fn()
+        barrier()
+        scan_ms, scan_launches = 0.0, 0
+        l0 = idx.launch_count
+        t0 = time.perf_counter()
+        for _ in range(steps):
+            fn()
+            ms, nl = idx.last_main_kernel()
+            scan_ms += ms
+            scan_launches += nl
+        barrier()
+        dt = time.perf_counter() - t0
+        if world > 1:
+            t = torch.tensor([dt], device=device, dtype=torch.float64)
+            dist.all_reduce(t, op=dist.ReduceOp.MAX)
+            dt = float(t.item())
+        return dt, scan_ms, scan_launches, idx.launch_count - l0
+
+    # The code array of one shard (>= 0.9 GB) is far larger than L2 (126 MB), so every step streams it from HBM.
+    sampler = ClockSampler(local_rank)
+    sampler.start()
+    dt, scan_ms, scan_launches, launches = timed(lambda: step_device(q_dev, nq), args.steps, args.warmup)
+    clocks = sampler.stop()
+    dt_e2e, _, _, _ = timed(lambda: step_host(q_host.numpy(), nq), args.steps, max(1, args.warmup // 2))
+    q1_dev = q_dev[:1].contiguous()
+    b1_steps = max(args.steps, 20)
+    dt1, scan1_ms, scan1_launches, _ = timed(lambda: step_device(q1_dev, 1), b1_steps, args.warmup)
+    q1_host = q_host[:1].numpy()
+    dt1_e2e, _, _, _ = timed(lambda: step_host(q1_host, 1), b1_steps, 2)
+
+    # recall@10 of the first n_recall_q queries against exact fp32 inner products
+    rs, ri = step_device(q_all[:n_recall_q].contiguous(), n_recall_q)
+    if world > 1:
+        gs = [torch.empty_like(truth_s) for _ in range(world)]
+        gi = [torch.empty_like(truth_i) for _ in range(world)]
+        dist.all_gather(gs, truth_s)
+        dist.all_gather(gi, truth_i)
+        truth_s, sel = torch.topk(torch.cat(gs, 1), K, dim=1)
+        truth_i = torch.gather(torch.cat(gi, 1), 1, sel)
+    got, want = ri.cpu().numpy(), truth_i.cpu().numpy()
+    recall = float(np.mean([len(set(got[j]) & set(want[j])) / K for j in range(n_recall_q)]))
+
+    if rank != 0:
+        if world > 1:
+            dist.destroy_process_group()
+        return
+
+    ng = DIM * BITS // 8
+    qps = nq * args.steps / dt
+    # dominant kernel of the headline step: the permute-dot scan, an exact int8 contraction
+    ops_per_step = 2.0 * nq * n_local * DIM
+    scan_s = scan_ms / 1e3 / args.steps
+    achieved_tops = ops_per_step / scan_s / 1e12 if scan_s > 0 else None
+    bytes_b1 = n_local * (ng + 4)
+    scan1_s = scan1_ms / 1e3 / b1_steps
+    achieved_gbs = bytes_b1 / scan1_s / 1e9 if scan1_s > 0 else None
+    ingest_rate = ingest_rows / (ingest_ms / 1e3) if ingest_ms > 0 else None
+    ingest_bytes = 4 * DIM + ng + 4
+
+    cpu_qps, cpu_ms, cores, sample = cpu_arm(100_000, 64, 2, 1, n_total) if world == 1 and not args.no_cpu else (None, None, None, None)
+
+    line = {
+        "metric": METRIC, "value": qps, "unit": UNIT, "n_gpus": world, "steps": args.steps, "warmup": args.warmup,
+        "ms_per_step": dt / args.steps * 1e3, "higher_is_better": True, "scaling": "strong", "vs_baseline": None,
+        "dtype": "int8", "data": "synthetic",
+        "config": {"workload": f"{n_total} x {DIM} {BITS}-bit, k={K}, batch {nq}; index slot-sharded over {world} GPU(s)",
+                   "l2": "inputs larger than L2: each step streams the whole code array of the shard",
+                   "score_mode": "permute-dot int8 (what an AVX-512-VNNI host runs)", "vectors_per_gpu": n_local},
+        "e2e": {"value": nq * args.steps / dt_e2e, "unit": UNIT, "h2d_bytes_per_step": int(nq * DIM * 4),
+                "d2h_bytes_per_step": int(nq * K * 12)},
+        "gpu_launches": int(launches),
+        "clocks": clocks,
+        "roofline": {"bound": "tensor", "achieved": achieved_tops, "peak": pk["tensor_tflops"], "unit": "TFLOP/s",
+                     "frac": achieved_tops / pk["tensor_tflops"] if achieved_tops else None, "traffic": None,
+                     "kernel": "scan_pd_kernel", "launches_per_step": scan_launches / args.steps,
+                     "note": f"int8 multiply-adds counted as 2 ops against the {pk['source']} bf16 sustained peak"},
+        "batch1": {"value": b1_steps / dt1, "unit": UNIT, "ms_per_query": dt1 / b1_steps * 1e3,
+                   "e2e": {"value": b1_steps / dt1_e2e, "unit": UNIT, "h2d_bytes_per_step": DIM * 4, "d2h_bytes_per_step": K * 12},
+                   "roofline": {"bound": "hbm", "achieved": achieved_gbs, "peak": pk["hbm_gbs"], "unit": "GB/s",
+                                "frac": achieved_gbs / pk["hbm_gbs"] if achieved_gbs else None, "traffic": None,
+                                "kernel": "scan_pd_kernel", "launches_per_step": scan1_launches / b1_steps}},
+        "ingest": {"value": ingest_rate, "unit": "vectors/s", "rows": ingest_rows,
+                   "roofline": {"bound": "hbm", "achieved": ingest_rate * ingest_bytes / 1e9 if ingest_rate else None,
+                                "peak": pk["hbm_gbs"], "unit": "GB/s",
+                                "frac": ingest_rate * ingest_bytes / 1e9 / pk["hbm_gbs"] if ingest_rate else None,
+                                "traffic": None, "kernel": "ingest_kernel", "launches": ingest_launches}},
+        "recall_at_10": recall,
+    }
+    if cpu_qps is not None:
+        line["cpu_baseline"] = {"value": cpu_qps, "unit": UNIT, "cores": cores, "kind": "port", "sample": sample}
+    print(json.dumps(line))
+    if world > 1:
+        dist.destroy_process_group()
+
+
+def main():
+    ap = argparse.ArgumentParser()
+    ap.add_argument("--gpus", type=int, default=1)
+    ap.add_argument("--steps", type=int, default=10)
+    ap.add_argument("--warmup", type=int, default=3)
+    ap.add_argument("--impl", default="ours", choices=["ours", "reference"])
+    ap.add_argument("--n", type=int, default=10_000_000)
+    ap.add_argument("--batch", type=int, default=1024)
+    ap.add_argument("--no-cpu", action="store_true", help="skip the cpu_baseline leg")
+    args = ap.parse_args()
+    args.warmup = max(args.warmup, 3) if args.impl == "ours" else args.warmup
+    if args.impl == "reference":
+        run_reference(args)
+    else:
+        run_ours(args)
+
+
+if __name__ == "__main__":
+    main()

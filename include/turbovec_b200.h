@@ -180,6 +180,9 @@ int tv_set_calibration(tv_index *h, size_t dim, const float *shift, const float 
 uint64_t tv_launch_count(const tv_index *h);
 /* Device time of the kernels of the last search / add call, from CUDA events on the handle's stream (ms). */
 float tv_last_kernel_ms(const tv_index *h);
+/* Summed device time (ms) of the dominant kernel's launches in the last call — the block scan for a search,
+ * the ingest kernel for an add — each launch bracketed by its own pair of events; *launches = how many. */
+float tv_last_main_kernel_ms(const tv_index *h, int *launches);
 const char *tv_version(void);
 
 #ifdef __cplusplus

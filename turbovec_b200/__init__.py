@@ -120,6 +120,12 @@ class _Base:
     def last_kernel_ms(self) -> float:
         return float(self._lib.tv_last_kernel_ms(self._h))
 
+    def last_main_kernel(self):
+        """(summed ms, launches) of the dominant kernel (block scan / ingest) in the last call."""
+        n = C.c_int(0)
+        ms = float(self._lib.tv_last_main_kernel_ms(self._h, C.byref(n)))
+        return ms, int(n.value)
+
     def set_calibration(self, shift: np.ndarray, scale: np.ndarray) -> None:
         shift = _typed_1d("shift", shift, np.float32, "float32")
         scale = _typed_1d("scale", scale, np.float32, "float32")
@@ -173,6 +179,8 @@ class _Base:
         k_eff = C.c_size_t(0)
         self._check(fn(self._h, _ptr(queries), nq, ncols, k, *extra, _ptr(scores), _ptr(ids), C.byref(k_eff)))
         ke = int(k_eff.value)
+        if nq == 0:
+            return np.empty((0, ke), np.float32), np.empty((0, ke), out_dtype)
         return (scores.ravel()[: nq * ke].reshape(nq, ke).copy(), ids.ravel()[: nq * ke].reshape(nq, ke).copy())
 
 

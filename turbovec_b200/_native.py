@@ -55,6 +55,7 @@ SIGNATURES = {
     "tv_set_calibration": (C.c_int, [_H, C.c_size_t, C.c_void_p, C.c_void_p]),
     "tv_launch_count": (C.c_uint64, [_H]),
     "tv_last_kernel_ms": (C.c_float, [_H]),
+    "tv_last_main_kernel_ms": (C.c_float, [_H, _intp]),
 }
 
 _lib = None

@@ -95,6 +95,11 @@ struct tv_index {
     cudaEvent_t ev0 = nullptr, ev1 = nullptr;
     uint64_t launches = 0;
     float last_ms = 0.f;
+    // per-launch CUDA events around the dominant kernels (scan, ingest) of the last call
+    std::vector<cudaEvent_t> ev_pool;
+    size_t ev_used = 0;
+    float last_main_ms = 0.f;
+    int last_main_launches = 0;
 
     // tables (host + device)
     bool tables_ready = false;
@@ -144,6 +149,7 @@ struct tv_index {
         if (h_flags) cudaFreeHost(h_flags);
         if (ev0) cudaEventDestroy(ev0);
         if (ev1) cudaEventDestroy(ev1);
+        for (cudaEvent_t e : ev_pool) cudaEventDestroy(e);
         if (stream) cudaStreamDestroy(stream);
     }
 };
@@ -154,6 +160,34 @@ int fail(tv_index *h, int code, const std::string &msg) {
     if (h) h->last_error = msg;
     else g_create_error = msg;
     return code;
+}
+
+// Brackets one launch of a dominant kernel with two events from the handle's pool.
+void mark_begin(tv_index *h) {
+    if (h->ev_used + 2 > h->ev_pool.size()) {
+        for (int i = 0; i < 64; ++i) {
+            cudaEvent_t e;
+            if (cudaEventCreate(&e) != cudaSuccess) return;
+            h->ev_pool.push_back(e);
+        }
+    }
+    cudaEventRecord(h->ev_pool[h->ev_used], h->stream);
+}
+void mark_end(tv_index *h) {
+    if (h->ev_used + 2 > h->ev_pool.size()) return;
+    cudaEventRecord(h->ev_pool[h->ev_used + 1], h->stream);
+    h->ev_used += 2;
+}
+// After the stream has been synchronised: total time and count of the bracketed launches.
+void collect_marks(tv_index *h) {
+    float total = 0.f;
+    for (size_t i = 0; i + 1 < h->ev_used; i += 2) {
+        float ms = 0.f;
+        if (cudaEventElapsedTime(&ms, h->ev_pool[i], h->ev_pool[i + 1]) == cudaSuccess) total += ms;
+    }
+    h->last_main_ms = total;
+    h->last_main_launches = int(h->ev_used / 2);
+    h->ev_used = 0;
 }
 
 #define TV_CUDA(expr)                                                                              \
@@ -334,13 +368,16 @@ int add_rows(tv_index *h, const float *x, size_t n, size_t dim, bool on_device) 
             src = h->d_stage.ptr;
         }
         p.x = src; p.n = int64_t(rows); p.slot0 = int64_t(h->n + done); p.row_base = int64_t(done);
+        mark_begin(h);
         TV_CUDA(launch_ingest(p, V, h->stream));
+        mark_end(h);
         h->launches++;
     }
     TV_CUDA(cudaEventRecord(h->ev1, h->stream));
     TV_CUDA(cudaMemcpyAsync(&h->h_flags->first_invalid, &h->d_flags->first_invalid, 8, cudaMemcpyDeviceToHost, h->stream));
     TV_CUDA(cudaStreamSynchronize(h->stream));
     cudaEventElapsedTime(&h->last_ms, h->ev0, h->ev1);
+    collect_marks(h);
     if (h->h_flags->first_invalid != ~0ull) {
         // roll back: the new lanes must read as zero again, nothing else was touched
         const int64_t total = int64_t(n) * h->ngroups;
@@ -503,13 +540,17 @@ int search_core(tv_index *h, const float *queries, bool queries_on_device, size_
             if (mode == TV_SCORE_PERMUTE_DOT) {
                 for (size_t q0 = 0; q0 < nq; q0 += 64) {
                     sp.q_base = int(q0); sp.nq = int(std::min<size_t>(64, nq - q0)); sp.mtile_base = int(q0 / 16);
+                    mark_begin(h);
                     TV_CUDA(launch_scan_pd(sp, h->sm_count, st));
+                    mark_end(h);
                     h->launches++;
                 }
             } else {
                 for (size_t q0 = 0; q0 < nq; q0 += kLutQueriesPerLaunch) {
                     sp.q_base = int(q0); sp.nq = int(std::min<size_t>(kLutQueriesPerLaunch, nq - q0));
+                    mark_begin(h);
                     TV_CUDA(launch_scan_lut(sp, h->sm_count, st));
+                    mark_end(h);
                     h->launches++;
                 }
             }
@@ -539,6 +580,7 @@ int search_core(tv_index *h, const float *queries, bool queries_on_device, size_
         }
         TV_CUDA(cudaStreamSynchronize(st));
         cudaEventElapsedTime(&h->last_ms, h->ev0, h->ev1);
+        collect_marks(h);
         if (h->h_flags->error) return fail(h, TV_ERR_DEVICE_TIMEOUT, "a device-side wait ran out of polls");
         if (h->h_flags->first_invalid != ~0ull) {
             const unsigned long long flat = h->h_flags->first_invalid;
@@ -575,7 +617,22 @@ int search_host(tv_index *h, const float *queries, size_t nq, size_t dim, size_t
         return fail(h, TV_ERR_MASK_LENGTH_MISMATCH, "mask length " + std::to_string(mask.bool_len) + " does not match index length " + std::to_string(h->n));
     if (mask.words_host && mask.n_words != (h->n + 63) / 64)
         return fail(h, TV_ERR_MASK_LENGTH_MISMATCH, "mask has " + std::to_string(mask.n_words) + " words, index needs " + std::to_string((h->n + 63) / 64));
-    if (nq == 0) return TV_OK;
+    if (nq == 0) {
+        // no queries: empty result whose row width is still min(k, len, n_allowed) (lib.rs:1460)
+        size_t allowed = h->n;
+        if (mask.bool_host) {
+            allowed = 0;
+            for (size_t i = 0; i < h->n; ++i) allowed += mask.bool_host[i] != 0;
+        } else if (mask.words_host) {
+            allowed = 0;
+            for (size_t i = 0; i < h->n; ++i) allowed += (mask.words_host[i >> 6] >> (i & 63)) & 1ull;
+        } else if (mask.slots_host) {
+            std::unordered_set<uint32_t> distinct(mask.slots_host, mask.slots_host + mask.n_slots);
+            allowed = distinct.size();
+        }
+        if (k_eff) *k_eff = std::min(std::min(k, h->n), allowed);
+        return TV_OK;
+    }
     size_t ke = 0;
     int rc = search_core(h, queries, false, nq, k, mask, nullptr, nullptr, &ke);
     if (rc != TV_OK) return rc;
@@ -684,6 +741,11 @@ int tv_bit_width(const tv_index *h) { return h ? h->bits : 0; }
 int tv_kind(const tv_index *h) { return h ? h->kind : -1; }
 uint64_t tv_launch_count(const tv_index *h) { return h ? h->launches : 0; }
 float tv_last_kernel_ms(const tv_index *h) { return h ? h->last_ms : 0.f; }
+float tv_last_main_kernel_ms(const tv_index *h, int *launches) {
+    if (!h) return 0.f;
+    if (launches) *launches = h->last_main_launches;
+    return h->last_main_ms;
+}
 
 int tv_set_option(tv_index *h, int option, int64_t value) {
     if (!h) return TV_ERR_INVALID_ARGUMENT;

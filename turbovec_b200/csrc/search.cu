@@ -657,7 +657,10 @@ cudaError_t launch_scan_pd(const ScanParams &p, int sm_count, cudaStream_t s) {
 cudaError_t launch_scan_lut(const ScanParams &p, int sm_count, cudaStream_t s) {
     if (p.nq <= 0 || p.pos_end <= p.pos_begin) return cudaSuccess;
     const int nqh = p.nq < kLutQueriesPerLaunch ? p.nq : kLutQueriesPerLaunch;
-    const size_t smem = size_t(nqh) * p.ngroups * 32;
+    // sized by the kernel's template width: its inner loop reads all NQ tables (unused ones hold garbage
+    // whose sums are discarded), so the allocation must cover them
+    const int width = nqh == 1 ? 1 : (nqh == 2 ? 2 : 4);
+    const size_t smem = size_t(width) * p.ngroups * 32;
     const uint32_t blocks = p.pos_end - p.pos_begin;
     const unsigned grid = unsigned(min(uint32_t(sm_count) * 2u, (blocks + 7) / 8));
 #define TV_LAUNCH_LUT(N)                                                                                             \
