@@ -150,6 +150,20 @@ int tv_search_device(tv_index *h, const float *queries_device, size_t nq, size_t
                      const uint64_t *mask_words_device, float *scores_out_device, int64_t *slots_out_device,
                      size_t *k_eff);
 
+/* Search that performs no allocation of any kind.  This entry point has no counterpart in the reference:
+ * it exists for callers that must not reach the CUDA allocator while they serve — latency-critical loops
+ * (cudaMalloc locks the device and may synchronise it), processes whose device memory is fully handed out,
+ * frameworks that forbid allocator traffic after warm-up.  Same contract as tv_search_device (unfiltered;
+ * queries, scores and slots in device memory; output row stride *k_eff), but all scratch sits in one fixed
+ * 1.25 MiB array inside the library image, resident on every GPU that loads the library until exit.
+ * Limits: nq <= 8, k <= 128, index dim <= 4096; larger requests fail with TV_ERR_UNSUPPORTED and a message.
+ * The index tables must exist (tv_prepare or a previous add).  The first call on each device resolves the
+ * array's device address; make that call before any stream capture begins.  All calls share the array,
+ * which keeps whatever the previous call left; within a process calls are serialised, and work from other
+ * sources that touches the same array while a call is in flight would race with it. */
+int tv_search_device_noalloc(tv_index *h, const float *queries_device, size_t nq, size_t k,
+                             float *scores_out_device, int64_t *slots_out_device, size_t *k_eff);
+
 /* ---- warm-up: prepare (lib.rs:1496) — builds tables and caches the first search would build ---- */
 int tv_prepare(tv_index *h);
 

@@ -217,6 +217,15 @@ class TurboQuantIndex(_Base):
                                                 C.c_void_p(scores_ptr), C.c_void_p(slots_ptr), C.byref(k_eff)))
         return int(k_eff.value)
 
+    def search_device_noalloc(self, q_ptr: int, nq: int, k: int, scores_ptr: int, slots_ptr: int) -> int:
+        """Like search_device (unfiltered) but guaranteed not to allocate: scratch is a fixed array inside
+        the library.  For callers that must keep away from the CUDA allocator while serving.  Limits:
+        nq <= 8, k <= 128, dim <= 4096.  Returns k_eff."""
+        k_eff = C.c_size_t(0)
+        self._check(self._lib.tv_search_device_noalloc(self._h, C.c_void_p(q_ptr), nq, k, C.c_void_p(scores_ptr),
+                                                        C.c_void_p(slots_ptr), C.byref(k_eff)))
+        return int(k_eff.value)
+
     def swap_remove(self, idx: int) -> int:
         idx = _size("idx", idx)
         moved = C.c_size_t(0)

@@ -43,6 +43,7 @@ SIGNATURES = {
     "tv_search_allowlist": (C.c_int, [_H, C.c_void_p, C.c_size_t, C.c_size_t, C.c_size_t, C.c_void_p, C.c_size_t,
                                       C.c_void_p, C.c_void_p, _szp]),
     "tv_search_device": (C.c_int, [_H, C.c_void_p, C.c_size_t, C.c_size_t, C.c_void_p, C.c_void_p, C.c_void_p, _szp]),
+    "tv_search_device_noalloc": (C.c_int, [_H, C.c_void_p, C.c_size_t, C.c_size_t, C.c_void_p, C.c_void_p, _szp]),
     "tv_prepare": (C.c_int, [_H]),
     "tv_blocked_bytes": (C.c_size_t, [_H]),
     "tv_export_blocked": (C.c_int, [_H, C.c_void_p, C.c_size_t, C.c_void_p, C.c_size_t]),

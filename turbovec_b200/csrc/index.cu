@@ -923,6 +923,154 @@ int tv_search_device(tv_index *h, const float *queries_device, size_t nq, size_t
     return rc;
 }
 
+// -----------------------------------------------------------------------------------------------------
+// Search without any allocation.
+//
+// Who needs it: code that runs where the CUDA allocator must not be touched — a serving loop with a hard
+// latency budget (cudaMalloc takes a device-wide lock and may synchronise), a process whose memory pool
+// has been handed out completely to other tenants, or a caller that has promised its framework "no
+// allocator traffic after warm-up".  tv_search_device grows its scratch arrays on demand; this entry
+// point instead keeps every byte of scratch in one fixed array that is part of the loaded library image.
+//
+// The array lives in device memory of every GPU that loads the library (kNoAllocScratchBytes each) until
+// the process exits.  Its name is only a host-side handle: the device address is fetched once per device
+// with cudaGetSymbolAddress and it is that address the kernels receive.
+// -----------------------------------------------------------------------------------------------------
+constexpr size_t kNoAllocMaxQueries = 8;
+constexpr size_t kNoAllocMaxK = 128;
+constexpr size_t kNoAllocMaxDim = 4096;
+constexpr size_t kNoAllocCap = 4096;                     // candidate slots per query
+constexpr size_t kNoAllocScratchBytes = 1280 * 1024;     // 1.25 MiB, layout below
+static __device__ __align__(256) unsigned char g_noalloc_scratch[kNoAllocScratchBytes];
+
+namespace {
+std::mutex g_noalloc_mu;                                 // one call at a time per process: the array is shared
+void *g_noalloc_base[64] = {nullptr};                    // device address of the array, per device ordinal
+
+struct NoAllocLayout {
+    float *q_rot, *qscale, *qbias;
+    int8_t *weights;
+    uint32_t *wfrag;
+    uint8_t *luts;
+    uint64_t *cand, *thr, *topk;
+    uint32_t *cnt;
+};
+NoAllocLayout carve_noalloc(unsigned char *base) {
+    NoAllocLayout L;
+    size_t off = 0;
+    auto take = [&](size_t bytes) { unsigned char *p = base + off; off += (bytes + 255) & ~size_t(255); return p; };
+    L.q_rot = reinterpret_cast<float *>(take(kNoAllocMaxQueries * kNoAllocMaxDim * 4));          // 128 KiB
+    L.qscale = reinterpret_cast<float *>(take(16 * 4));
+    L.qbias = reinterpret_cast<float *>(take(16 * 4));
+    L.weights = reinterpret_cast<int8_t *>(take(16 * kNoAllocMaxDim));                           //  64 KiB
+    L.wfrag = reinterpret_cast<uint32_t *>(take((kNoAllocMaxDim / 2 / 16) * 32 * 16));           //  64 KiB
+    L.luts = reinterpret_cast<uint8_t *>(take(kNoAllocMaxQueries * (kNoAllocMaxDim / 2) * 32));  // 512 KiB
+    L.cand = reinterpret_cast<uint64_t *>(take(kNoAllocMaxQueries * kNoAllocCap * 8));           // 256 KiB
+    L.thr = reinterpret_cast<uint64_t *>(take(kNoAllocMaxQueries * 8));
+    L.topk = reinterpret_cast<uint64_t *>(take(kNoAllocMaxQueries * kNoAllocMaxK * 8));          //   8 KiB
+    L.cnt = reinterpret_cast<uint32_t *>(take(kNoAllocMaxQueries * 4));
+    static_assert(kNoAllocMaxQueries * kNoAllocMaxDim * 4 + 16 * kNoAllocMaxDim + (kNoAllocMaxDim / 32) * 512 +
+                          kNoAllocMaxQueries * (kNoAllocMaxDim / 2) * 32 + kNoAllocMaxQueries * kNoAllocCap * 8 +
+                          kNoAllocMaxQueries * kNoAllocMaxK * 8 + 8 * 256 <= kNoAllocScratchBytes,
+                  "scratch layout exceeds the static array");
+    return L;
+}
+}  // namespace
+
+int tv_search_device_noalloc(tv_index *h, const float *queries_device, size_t nq, size_t k, float *scores_out_device,
+                             int64_t *slots_out_device, size_t *k_eff) {
+    if (!h || (!queries_device && nq) || !scores_out_device || !slots_out_device) return TV_ERR_INVALID_ARGUMENT;
+    std::lock_guard<std::mutex> lock(h->mu);
+    std::lock_guard<std::mutex> scratch_lock(g_noalloc_mu);
+    if (k_eff) *k_eff = 0;
+    if (nq > kNoAllocMaxQueries)
+        return fail(h, TV_ERR_UNSUPPORTED, "tv_search_device_noalloc takes at most " + std::to_string(kNoAllocMaxQueries) + " queries per call, got " + std::to_string(nq));
+    if (k > kNoAllocMaxK)
+        return fail(h, TV_ERR_UNSUPPORTED, "tv_search_device_noalloc takes k up to " + std::to_string(kNoAllocMaxK) + ", got " + std::to_string(k));
+    if (h->dim > kNoAllocMaxDim)
+        return fail(h, TV_ERR_UNSUPPORTED, "tv_search_device_noalloc supports dim up to " + std::to_string(kNoAllocMaxDim) + ", index has " + std::to_string(h->dim));
+    if (h->dim == 0 || h->n == 0 || nq == 0 || k == 0) return TV_OK;
+    if (!h->tables_ready) return fail(h, TV_ERR_INVALID_ARGUMENT, "index tables are not built yet: call tv_prepare (or add rows) before tv_search_device_noalloc");
+    if (h->device < 0 || h->device >= 64) return fail(h, TV_ERR_UNSUPPORTED, "device ordinal above 63");
+    TV_CUDA(cudaSetDevice(h->device));
+    if (g_noalloc_base[h->device] == nullptr) {
+        // one-time set-up on this device (device current): resolve the array's device address
+        void *ptr = nullptr;
+        TV_CUDA(cudaGetSymbolAddress(&ptr, g_noalloc_scratch));
+        g_noalloc_base[h->device] = ptr;
+    }
+    const NoAllocLayout L = carve_noalloc(static_cast<unsigned char *>(g_noalloc_base[h->device]));
+
+    const size_t dim = h->dim, n = h->n;
+    const int ng = h->ngroups, mode = resolve_mode(h);
+    const size_t kk = std::min(k, n);
+    const int ksteps = (ng + 15) / 16;
+    cudaStream_t st = h->stream;
+
+    DeviceFlags init{};
+    init.first_invalid = ~0ull;
+    *h->h_flags = init;
+    TV_CUDA(cudaMemcpyAsync(h->d_flags, h->h_flags, sizeof(DeviceFlags), cudaMemcpyHostToDevice, st));
+
+    // the array still holds the previous call's data: reset everything that must start from a known state
+    TV_CUDA(cudaMemsetAsync(L.wfrag, 0, size_t(ksteps) * 32 * 16, st));
+    TV_CUDA(cudaMemsetAsync(L.cnt, 0, nq * 4, st));
+    TV_CUDA(cudaMemsetAsync(L.thr, 0xff, nq * 8, st));
+    TV_CUDA(cudaMemsetAsync(L.topk, 0xff, nq * kk * 8, st));
+
+    QueryPrepParams qp{};
+    qp.queries = queries_device; qp.nq = int(nq); qp.dim = int(dim); qp.bits = h->bits; qp.ngroups = ng; qp.mode = mode;
+    qp.perm0 = h->d_perm.ptr; qp.perm1 = h->d_perm.ptr + dim; qp.inv_sqrt_block = h->rot.inv_sqrt_block;
+    qp.centroids = h->d_codebook.ptr + 16;
+    if (!h->shift.empty()) { qp.shift = h->d_calib.ptr; qp.scale_tq = h->d_calib.ptr + dim; }
+    qp.level_scale = h->level_scale;
+    qp.q_rot = L.q_rot; qp.qscale = L.qscale; qp.qbias = L.qbias; qp.luts = L.luts; qp.weights = L.weights;
+    qp.dim_pad = int(kNoAllocMaxDim); qp.wfrag = L.wfrag; qp.mtiles_total = 1;
+    qp.first_invalid = &h->d_flags->first_invalid;
+    TV_CUDA(launch_query_prep(qp, st));
+    h->launches++;
+
+    CandidateBuffers cb{};
+    cb.cand = L.cand; cb.cnt = L.cnt; cb.thr = L.thr; cb.topk = L.topk;
+    cb.overflow = &h->d_flags->overflow; cb.error = &h->d_flags->error; cb.cap = int(kNoAllocCap); cb.k = int(kk);
+    ScanParams sp{};
+    sp.codes = h->d_codes; sp.vec_scales = h->d_scales; sp.n = int64_t(n); sp.ngroups = ng; sp.bits = h->bits;
+    sp.mode = mode; sp.qscale = L.qscale; sp.qbias = L.qbias; sp.cb = cb; sp.wfrag = L.wfrag; sp.mtiles_total = 1;
+    sp.luts = L.luts;
+    for (int w = 0; w < 4; ++w) {
+        uint32_t word = 0;
+        for (int b = 0; b < 4; ++b) word |= uint32_t(uint8_t(h->levels[4 * w + b])) << (8 * b);
+        sp.level_words[w] = word;
+    }
+    // Chunks never exceed the candidate capacity, so the fixed buffer cannot overflow whatever the data order.
+    const size_t n_blocks = (n + kBlock - 1) / kBlock, step = kNoAllocCap / kBlock;
+    for (size_t begin = 0; begin < n_blocks; begin += step) {
+        sp.pos_begin = uint32_t(begin); sp.pos_end = uint32_t(std::min(n_blocks, begin + step));
+        if (mode == TV_SCORE_PERMUTE_DOT) {
+            sp.q_base = 0; sp.nq = int(nq); sp.mtile_base = 0;
+            TV_CUDA(launch_scan_pd(sp, h->sm_count, st));
+            h->launches++;
+        } else {
+            for (size_t q0 = 0; q0 < nq; q0 += kLutQueriesPerLaunch) {
+                sp.q_base = int(q0); sp.nq = int(std::min<size_t>(kLutQueriesPerLaunch, nq - q0));
+                TV_CUDA(launch_scan_lut(sp, h->sm_count, st));
+                h->launches++;
+            }
+        }
+        TV_CUDA(launch_select(cb, int(nq), st));
+        h->launches++;
+    }
+    TV_CUDA(launch_finalize(cb, int(nq), nullptr, int64_t(n), scores_out_device, slots_out_device, &h->d_flags->k_eff, 0, st));
+    h->launches++;
+    TV_CUDA(cudaMemcpyAsync(h->h_flags, h->d_flags, sizeof(DeviceFlags), cudaMemcpyDeviceToHost, st));
+    TV_CUDA(cudaStreamSynchronize(st));
+    if (h->h_flags->error) return fail(h, TV_ERR_DEVICE_TIMEOUT, "a device-side wait ran out of polls");
+    if (h->h_flags->first_invalid != ~0ull) return fail(h, TV_ERR_INVALID_QUERY_VALUE, "a query coordinate is not finite or exceeds 1e16 in magnitude");
+    if (h->h_flags->overflow) return fail(h, TV_ERR_CUDA, "candidate overflow in the bounded schedule (internal error)");
+    if (k_eff) *k_eff = h->h_flags->k_eff;
+    return TV_OK;
+}
+
 int tv_prepare(tv_index *h) {
     if (!h) return TV_ERR_INVALID_ARGUMENT;
     std::lock_guard<std::mutex> lock(h->mu);
