@@ -126,6 +126,10 @@ int tv_add_device(tv_index *h, const float *vectors_device, size_t n, size_t dim
 /* ---- removal: swap_remove (lib.rs:2864-3028), IdMapIndex::remove (id_map.rs:520-567) ---- */
 int tv_swap_remove(tv_index *h, size_t slot, size_t *moved_from);
 int tv_remove(tv_index *h, uint64_t id, int *removed);
+/* One stored row as its byte-groups in group order plus its scale: pack::read_code / write_code over a lane
+ * (pack.rs:1113-1160).  Used to move a row between device shards when swap_remove crosses GPUs. */
+int tv_get_row(const tv_index *h, size_t slot, uint8_t *groups_out, size_t capacity, float *scale_out);
+int tv_set_row(tv_index *h, size_t slot, const uint8_t *groups, size_t count, float scale);
 int tv_contains(const tv_index *h, uint64_t id, int *present);         /* id_map.rs:593 */
 /* Copies slot_to_id[0..len) (id_map.rs:631 iter_ids order). */
 int tv_ids(const tv_index *h, uint64_t *ids_out, size_t capacity);

@@ -166,6 +166,21 @@ class _Base:
         self._check(self._lib.tv_export_packed(self._h, _ptr(out), out.size))
         return out
 
+    def row_bytes(self) -> int:
+        d = self.dim or 0
+        return d // (8 // self.bit_width)
+
+    def get_row(self, slot: int):
+        """(byte-groups uint8[ngroups], scale) of one stored row."""
+        out = np.empty(self.row_bytes(), np.uint8)
+        scale = C.c_float(0)
+        self._check(self._lib.tv_get_row(self._h, _size("slot", slot), _ptr(out), out.size, C.byref(scale)))
+        return out, float(scale.value)
+
+    def set_row(self, slot: int, groups: np.ndarray, scale: float) -> None:
+        groups = np.ascontiguousarray(groups, np.uint8)
+        self._check(self._lib.tv_set_row(self._h, _size("slot", slot), _ptr(groups), groups.size, float(scale)))
+
     def _search_raw(self, queries, k, fn, extra, out_dtype):
         queries = _f32_2d("queries", queries)
         k = _size("k", k)

@@ -34,6 +34,8 @@ SIGNATURES = {
     "tv_add_device": (C.c_int, [_H, C.c_void_p, C.c_size_t, C.c_size_t]),
     "tv_swap_remove": (C.c_int, [_H, C.c_size_t, _szp]),
     "tv_remove": (C.c_int, [_H, C.c_uint64, _intp]),
+    "tv_get_row": (C.c_int, [_H, C.c_size_t, C.c_void_p, C.c_size_t, _f32p]),
+    "tv_set_row": (C.c_int, [_H, C.c_size_t, C.c_void_p, C.c_size_t, C.c_float]),
     "tv_contains": (C.c_int, [_H, C.c_uint64, _intp]),
     "tv_ids": (C.c_int, [_H, C.c_void_p, C.c_size_t]),
     "tv_search": (C.c_int, [_H, C.c_void_p, C.c_size_t, C.c_size_t, C.c_size_t, C.c_void_p, C.c_size_t,

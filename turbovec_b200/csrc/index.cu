@@ -313,6 +313,16 @@ __global__ void move_lane_kernel(uint8_t *codes, float *scales, int ng, int64_t 
     if (blockIdx.x == 0 && threadIdx.x == 0 && src != dst) scales[dst] = scales[src];
 }
 
+// One row's byte-groups <-> a contiguous buffer (pack::read_code / write_code over a lane, pack.rs:1113-1160).
+__global__ void gather_row_kernel(const uint8_t *codes, int ng, int64_t slot, uint8_t *out) {
+    for (int g = blockIdx.x * blockDim.x + threadIdx.x; g < ng; g += gridDim.x * blockDim.x)
+        out[g] = codes[((slot / 32) * ng + g) * 32 + (slot % 32)];
+}
+__global__ void scatter_row_kernel(uint8_t *codes, int ng, int64_t slot, const uint8_t *in) {
+    for (int g = blockIdx.x * blockDim.x + threadIdx.x; g < ng; g += gridDim.x * blockDim.x)
+        codes[((slot / 32) * ng + g) * 32 + (slot % 32)] = in[g];
+}
+
 int validate_dim_for_add(tv_index *h, size_t dim) {
     // add_2d, lib.rs:1114-1133
     if (h->dim != 0) {
@@ -851,6 +861,40 @@ int tv_remove(tv_index *h, uint64_t id, int *removed) {
     }
     h->slot_to_id.pop_back();
     if (removed) *removed = 1;
+    return TV_OK;
+}
+
+int tv_get_row(const tv_index *hc, size_t slot, uint8_t *groups_out, size_t capacity, float *scale_out) {
+    tv_index *h = const_cast<tv_index *>(hc);
+    if (!h || !groups_out || !scale_out) return TV_ERR_INVALID_ARGUMENT;
+    std::lock_guard<std::mutex> lock(h->mu);
+    if (slot >= h->n) return fail(h, TV_ERR_SLOT_OUT_OF_RANGE, "index " + std::to_string(slot) + " out of bounds (n_vectors = " + std::to_string(h->n) + ")");
+    if (capacity < size_t(h->ngroups)) return fail(h, TV_ERR_INVALID_ARGUMENT, "output buffer too small");
+    TV_CUDA(cudaSetDevice(h->device));
+    TV_CUDA(h->d_mask_bool.reserve(size_t(h->ngroups)));
+    gather_row_kernel<<<(h->ngroups + 255) / 256, 256, 0, h->stream>>>(h->d_codes, h->ngroups, int64_t(slot), h->d_mask_bool.ptr);
+    h->launches++;
+    TV_CUDA(cudaGetLastError());
+    TV_CUDA(cudaMemcpyAsync(groups_out, h->d_mask_bool.ptr, size_t(h->ngroups), cudaMemcpyDeviceToHost, h->stream));
+    TV_CUDA(cudaMemcpyAsync(scale_out, h->d_scales + slot, 4, cudaMemcpyDeviceToHost, h->stream));
+    TV_CUDA(cudaStreamSynchronize(h->stream));
+    return TV_OK;
+}
+
+int tv_set_row(tv_index *h, size_t slot, const uint8_t *groups, size_t count, float scale) {
+    if (!h || !groups) return TV_ERR_INVALID_ARGUMENT;
+    std::lock_guard<std::mutex> lock(h->mu);
+    if (slot >= h->n) return fail(h, TV_ERR_SLOT_OUT_OF_RANGE, "index " + std::to_string(slot) + " out of bounds (n_vectors = " + std::to_string(h->n) + ")");
+    if (count != size_t(h->ngroups)) return fail(h, TV_ERR_INVALID_ARGUMENT, "a row has " + std::to_string(h->ngroups) + " byte-groups, got " + std::to_string(count));
+    if (!(scale >= 0.0f) || !std::isfinite(scale)) return fail(h, TV_ERR_PARTS_INVALID, "scale is negative or not finite");
+    TV_CUDA(cudaSetDevice(h->device));
+    TV_CUDA(h->d_mask_bool.reserve(count));
+    TV_CUDA(cudaMemcpyAsync(h->d_mask_bool.ptr, groups, count, cudaMemcpyHostToDevice, h->stream));
+    scatter_row_kernel<<<(h->ngroups + 255) / 256, 256, 0, h->stream>>>(h->d_codes, h->ngroups, int64_t(slot), h->d_mask_bool.ptr);
+    h->launches++;
+    TV_CUDA(cudaGetLastError());
+    TV_CUDA(cudaMemcpyAsync(h->d_scales + slot, &scale, 4, cudaMemcpyHostToDevice, h->stream));
+    TV_CUDA(cudaStreamSynchronize(h->stream));
     return TV_OK;
 }
 

@@ -285,7 +285,7 @@ __device__ __forceinline__ void expand4(uint32_t x, const uint32_t (&T)[4], uint
 }
 
 template <int MT>
-__global__ void __launch_bounds__((kConsumerWarps + 1) * 32, 1) scan_pd_kernel(ScanParams p) {
+__global__ void __launch_bounds__((kConsumerWarps + 1) * 32, MT <= 2 ? 2 : 1) scan_pd_kernel(ScanParams p) {
     extern __shared__ __align__(128) unsigned char smem_raw[];
     uint8_t *stage_mem = smem_raw;
     __shared__ uint64_t full_bar[kStages], empty_bar[kStages];
@@ -638,7 +638,8 @@ cudaError_t launch_scan_pd(const ScanParams &p, int sm_count, cudaStream_t s) {
     const int mt = (p.nq + 15) / 16;
     const size_t smem = size_t(kStages) * kStageBytes;
     const uint32_t tiles = (p.pos_end - p.pos_begin + kConsumerWarps - 1) / kConsumerWarps;
-    const unsigned grid = unsigned(min(uint32_t(sm_count), tiles));
+    const unsigned per_sm = mt <= 2 ? 2 : 1;                 // resident CTAs per SM (register budget)
+    const unsigned grid = unsigned(min(uint32_t(sm_count) * per_sm, tiles));
     const unsigned threads = (kConsumerWarps + 1) * 32;
 #define TV_LAUNCH_PD(M)                                                                                             \
     {                                                                                                               \
