@@ -88,7 +88,7 @@ struct tv_index {
 
     // options
     int score_mode = TV_SCORE_AUTO;
-    int64_t mma_min_batch = 0;
+    int64_t mma_min_batch = 0;   // 0 = tensor-memory path off (set by tv_set_option until measured)
     int force_careful = 0;
 
     cudaStream_t stream = nullptr;
@@ -441,8 +441,11 @@ int search_core(tv_index *h, const float *queries, bool queries_on_device, size_
     TV_CUDA(h->d_qrot.reserve(nq * dim));
     TV_CUDA(h->d_qscale.reserve(nq_pad));
     TV_CUDA(h->d_qbias.reserve(nq_pad));
+    const size_t w_rows = (nq + 255) / 256 * 256;
+    const bool use_tc = mode == TV_SCORE_PERMUTE_DOT && h->mma_min_batch > 0 && int64_t(nq) >= h->mma_min_batch &&
+                        scan_tc_supported(h->bits, mode);
     if (mode == TV_SCORE_PERMUTE_DOT) {
-        TV_CUDA(h->d_weights.reserve(nq_pad * dim_pad));
+        TV_CUDA(h->d_weights.reserve(w_rows * dim_pad));
         TV_CUDA(h->d_wfrag.reserve(size_t(ksteps) * mt_total * 32 * 4));
     } else {
         TV_CUDA(h->d_luts.reserve(nq * size_t(ng) * 32));
@@ -511,8 +514,10 @@ int search_core(tv_index *h, const float *queries, bool queries_on_device, size_
     qp.luts = h->d_luts.ptr; qp.weights = h->d_weights.ptr; qp.dim_pad = int(dim_pad);
     qp.wfrag = h->d_wfrag.ptr; qp.mtiles_total = mt_total;
     qp.first_invalid = &h->d_flags->first_invalid;
-    if (mode == TV_SCORE_PERMUTE_DOT)
+    if (mode == TV_SCORE_PERMUTE_DOT) {
         TV_CUDA(cudaMemsetAsync(h->d_wfrag.ptr, 0, size_t(ksteps) * mt_total * 32 * 16, st));
+        if (use_tc) TV_CUDA(cudaMemsetAsync(h->d_weights.ptr, 0, w_rows * dim_pad, st));
+    }
     TV_CUDA(launch_query_prep(qp, st));
     h->launches++;
 
@@ -547,7 +552,13 @@ int search_core(tv_index *h, const float *queries, bool queries_on_device, size_
             if (!careful && begin > 0) len = std::max<size_t>(first, size_t(double(begin) * growth));
             const size_t end = std::min(n_blocks, begin + len);
             sp.pos_begin = uint32_t(begin); sp.pos_end = uint32_t(end);
-            if (mode == TV_SCORE_PERMUTE_DOT) {
+            if (use_tc) {
+                sp.q_base = 0; sp.nq = int(nq); sp.mtile_base = 0;
+                mark_begin(h);
+                TV_CUDA(launch_scan_tc(sp, h->d_weights.ptr, int(w_rows), int(dim_pad), h->sm_count, st));
+                mark_end(h);
+                h->launches++;
+            } else if (mode == TV_SCORE_PERMUTE_DOT) {
                 for (size_t q0 = 0; q0 < nq; q0 += 64) {
                     sp.q_base = int(q0); sp.nq = int(std::min<size_t>(64, nq - q0)); sp.mtile_base = int(q0 / 16);
                     mark_begin(h);

@@ -1,0 +1,377 @@
+// Permute-dot scan on the 5th-generation tensor cores (tcgen05.mma kind::i8, accumulators in TMEM).
+//
+// Same arithmetic as scan_pd_kernel (search.cu): S[q][v] = sum_d W[q][d] * level[code[v][d]] exactly in
+// int32 (turbovec/src/search.rs:1392-1543), then fma((f32)S, scale_q, bias_q) * vec_scale[v]
+// (search.rs:1523, 1793) and the candidate push against the query's current k-th key.
+//
+// One work item = 128 vectors (4 code blocks) x 256 queries.  MMA shape M = 128 (vectors) x N = 256
+// (queries) x K = 32, both operands K-major in shared memory with the 128-byte swizzle:
+//   A (vectors): 4-bit codes are read from global memory and expanded to int8 levels by 8 CUDA-core warps,
+//      one 128-dimension slab (128 rows x 128 B) per pipeline stage;
+//   B (queries): int8 weights, one 256 x 128 B box per stage, loaded by TMA (no multicast).
+// D (128 lanes x 256 int32 columns) lives in TMEM, double buffered (512 columns), so the epilogue of one
+// work item overlaps the MMAs of the next.  Warp roles: 0 = TMA producer, 1 = MMA issuer (+ TMEM
+// alloc/dealloc), 2-5 = epilogue (one TMEM lane quarter each), 6-13 = code expansion.
+//
+// Every wait is bounded; a wait that runs out records an error word and makes its role leave its loop.
+#include <cuda.h>
+
+#include "search.cuh"
+#include "tv_common.cuh"
+
+namespace tv {
+namespace {
+
+constexpr int kTileVectors = 128;
+constexpr int kTileQueries = 256;
+constexpr int kSlabK = 128;                                   // int8 elements (bytes) of K per stage
+constexpr int kStagesTc = 4;
+constexpr int kABytes = kTileVectors * kSlabK;                // 16 KB
+constexpr int kBBytes = kTileQueries * kSlabK;                // 32 KB
+constexpr int kStageBytesTc = kABytes + kBBytes;              // 48 KB
+constexpr int kExpandWarps = 8;
+constexpr int kEpilogueWarps = 4;
+constexpr int kThreadsTc = (2 + kEpilogueWarps + kExpandWarps) * 32;   // 448
+constexpr uint32_t kTmemCols = 512;
+constexpr uint32_t kWaitLimitTc = 1u << 22;
+
+__device__ __forceinline__ uint32_t smem_u32(const void *p) { return uint32_t(__cvta_generic_to_shared(p)); }
+__device__ __forceinline__ void mbar_init(uint64_t *bar, uint32_t count) {
+    asm volatile("mbarrier.init.shared::cta.b64 [%0], %1;" ::"r"(smem_u32(bar)), "r"(count));
+}
+__device__ __forceinline__ void mbar_arrive(uint64_t *bar) {
+    asm volatile("mbarrier.arrive.shared::cta.b64 _, [%0];" ::"r"(smem_u32(bar)) : "memory");
+}
+__device__ __forceinline__ void mbar_arrive_expect_tx(uint64_t *bar, uint32_t bytes) {
+    asm volatile("mbarrier.arrive.expect_tx.shared::cta.b64 _, [%0], %1;" ::"r"(smem_u32(bar)), "r"(bytes) : "memory");
+}
+__device__ __forceinline__ bool mbar_try_wait(uint64_t *bar, uint32_t parity) {
+    uint32_t ok;
+    asm volatile(
+        "{\n\t.reg .pred p;\n\t"
+        "mbarrier.try_wait.parity.shared::cta.b64 p, [%1], %2;\n\t"
+        "selp.u32 %0, 1, 0, p;\n\t}"
+        : "=r"(ok) : "r"(smem_u32(bar)), "r"(parity) : "memory");
+    return ok != 0;
+}
+__device__ __forceinline__ bool mbar_wait(uint64_t *bar, uint32_t parity, uint32_t *error_flag) {
+    for (uint32_t i = 0; i < kWaitLimitTc; ++i)
+        if (mbar_try_wait(bar, parity)) return true;
+    atomicExch(error_flag, 2u);
+    return false;
+}
+__device__ __forceinline__ uint32_t prmt(uint32_t a, uint32_t b, uint32_t sel) {
+    uint32_t d;
+    asm("prmt.b32 %0, %1, %2, %3;" : "=r"(d) : "r"(a), "r"(b), "r"(sel));
+    return d;
+}
+// Eight nibbles of x -> eight int8 levels; output byte i of (lo, hi) belongs to nibble i / i+4 of x.
+__device__ __forceinline__ void expand8(uint32_t x, const uint32_t (&T)[4], uint32_t &lo, uint32_t &hi) {
+    const uint32_t idx = x & 0x77777777u;
+    const uint32_t pick = ((x >> 1) & 0x44444444u) | 0x32103210u;
+    lo = prmt(prmt(T[0], T[1], idx), prmt(T[2], T[3], idx), pick);
+    hi = prmt(prmt(T[0], T[1], idx >> 16), prmt(T[2], T[3], idx >> 16), pick >> 16);
+}
+
+// K-major, 128-byte swizzle, 8-row groups 1024 B apart; version 1 (sm_100), base offset 0.
+__device__ __forceinline__ uint64_t umma_desc(uint32_t smem_byte_addr) {
+    uint64_t d = 0;
+    d |= uint64_t((smem_byte_addr >> 4) & 0x3fffu);           // start address
+    d |= uint64_t(1) << 16;                                    // leading byte offset (unused for swizzled K-major)
+    d |= uint64_t(1024 >> 4) << 32;                            // stride byte offset
+    d |= uint64_t(1) << 46;                                    // descriptor version
+    d |= uint64_t(2) << 61;                                    // SWIZZLE_128B
+    return d;
+}
+// kind::i8: D = S32, A = B = signed 8-bit, both K-major, N = 256, M = 128.
+constexpr uint32_t kIdesc = (2u << 4) | (1u << 7) | (1u << 10) | (uint32_t(kTileQueries >> 3) << 17) |
+                            (uint32_t(kTileVectors >> 4) << 24);
+
+__device__ __forceinline__ void umma_i8(uint32_t d_tmem, uint64_t a_desc, uint64_t b_desc, uint32_t accumulate) {
+    asm volatile(
+        "{\n\t.reg .pred p;\n\t"
+        "setp.ne.b32 p, %4, 0;\n\t"
+        "tcgen05.mma.cta_group::1.kind::i8 [%0], %1, %2, %3, {%5, %6, %7, %8}, p;\n\t}"
+        ::"r"(d_tmem), "l"(a_desc), "l"(b_desc), "r"(kIdesc), "r"(accumulate), "r"(0u), "r"(0u), "r"(0u), "r"(0u)
+        : "memory");
+}
+__device__ __forceinline__ void umma_commit(uint64_t *bar) {
+    asm volatile("tcgen05.commit.cta_group::1.mbarrier::arrive::one.shared::cluster.b64 [%0];" ::"r"(smem_u32(bar)) : "memory");
+}
+__device__ __forceinline__ void tma_load_2d(void *dst, const CUtensorMap *map, int x, int y, uint64_t *bar) {
+    asm volatile(
+        "cp.async.bulk.tensor.2d.shared::cluster.global.tile.mbarrier::complete_tx::bytes [%0], [%1, {%3, %4}], [%2];"
+        ::"r"(smem_u32(dst)), "l"(map), "r"(smem_u32(bar)), "r"(x), "r"(y) : "memory");
+}
+__device__ __forceinline__ void tmem_ld32(uint32_t taddr, uint32_t (&r)[32]) {
+    asm volatile(
+        "tcgen05.ld.sync.aligned.32x32b.x32.b32 "
+        "{%0, %1, %2, %3, %4, %5, %6, %7, %8, %9, %10, %11, %12, %13, %14, %15, "
+        "%16, %17, %18, %19, %20, %21, %22, %23, %24, %25, %26, %27, %28, %29, %30, %31}, [%32];"
+        : "=r"(r[0]), "=r"(r[1]), "=r"(r[2]), "=r"(r[3]), "=r"(r[4]), "=r"(r[5]), "=r"(r[6]), "=r"(r[7]), "=r"(r[8]),
+          "=r"(r[9]), "=r"(r[10]), "=r"(r[11]), "=r"(r[12]), "=r"(r[13]), "=r"(r[14]), "=r"(r[15]), "=r"(r[16]),
+          "=r"(r[17]), "=r"(r[18]), "=r"(r[19]), "=r"(r[20]), "=r"(r[21]), "=r"(r[22]), "=r"(r[23]), "=r"(r[24]),
+          "=r"(r[25]), "=r"(r[26]), "=r"(r[27]), "=r"(r[28]), "=r"(r[29]), "=r"(r[30]), "=r"(r[31])
+        : "r"(taddr));
+}
+
+struct TcShared {
+    uint64_t full[kStagesTc];      // stage filled: 8 expansion warps + the TMA transaction
+    uint64_t empty[kStagesTc];     // stage drained by the MMAs (tcgen05.commit)
+    uint64_t d_full[2];            // accumulator buffer complete
+    uint64_t d_empty[2];           // accumulator buffer read out by the 4 epilogue warps
+    uint32_t tmem_base;
+    uint32_t pad;
+    float qscale[2][kTileQueries];
+    float qbias[2][kTileQueries];
+    float qthr[2][kTileQueries];   // score of the current k-th key (-inf while fewer than k results exist)
+};
+
+__global__ void __launch_bounds__(kThreadsTc, 1)
+scan_tc_kernel(ScanParams p, const __grid_constant__ CUtensorMap wmap, int n_slabs, int n_qgroups) {
+    extern __shared__ __align__(1024) unsigned char smem_raw[];
+    // stages first (1024-byte aligned for the swizzle), bookkeeping after them
+    unsigned char *stages = reinterpret_cast<unsigned char *>((reinterpret_cast<uintptr_t>(smem_raw) + 1023) & ~uintptr_t(1023));
+    TcShared *sh = reinterpret_cast<TcShared *>(stages + size_t(kStagesTc) * kStageBytesTc);
+
+    const int tid = threadIdx.x, warp = tid >> 5, lane = tid & 31;
+    const int ng = p.ngroups;
+    uint32_t pos_end = p.pos_end;
+    if (p.live_blocks != nullptr) pos_end = min(pos_end, *p.n_live);
+    const uint32_t pos_begin = min(p.pos_begin, pos_end);
+    const uint32_t n_vtiles = (pos_end - pos_begin + 3) / 4;
+    const uint32_t n_items = n_vtiles * uint32_t(n_qgroups);
+
+    if (tid == 0) {
+        for (int s = 0; s < kStagesTc; ++s) { mbar_init(&sh->full[s], kExpandWarps + 1); mbar_init(&sh->empty[s], 1); }
+        for (int b = 0; b < 2; ++b) { mbar_init(&sh->d_full[b], 1); mbar_init(&sh->d_empty[b], kEpilogueWarps); }
+        asm volatile("fence.mbarrier_init.release.cluster;" ::: "memory");
+    }
+    if (warp == 1) {
+        asm volatile("tcgen05.alloc.cta_group::1.sync.aligned.shared::cta.b32 [%0], %1;" ::"r"(smem_u32(&sh->tmem_base)), "r"(kTmemCols) : "memory");
+        asm volatile("tcgen05.relinquish_alloc_permit.cta_group::1.sync.aligned;" ::: "memory");
+    }
+    asm volatile("tcgen05.fence::before_thread_sync;" ::: "memory");
+    __syncthreads();
+    asm volatile("tcgen05.fence::after_thread_sync;" ::: "memory");
+    const uint32_t tmem_base = sh->tmem_base;
+
+    if (warp == 0) {
+        // ------------------------------------------------ TMA producer: query weights ------------
+        if (lane == 0) {
+            uint32_t it = 0;
+            bool ok = true;
+            for (uint32_t item = blockIdx.x; item < n_items && ok; item += gridDim.x) {
+                const int qg = int(item % uint32_t(n_qgroups));
+                for (int s = 0; s < n_slabs && ok; ++s, ++it) {
+                    const int st = it % kStagesTc;
+                    ok = mbar_wait(&sh->empty[st], ((it / kStagesTc) & 1) ^ 1, p.cb.error);
+                    if (!ok) break;
+                    mbar_arrive_expect_tx(&sh->full[st], kBBytes);
+                    tma_load_2d(stages + size_t(st) * kStageBytesTc + kABytes, &wmap, s * kSlabK, qg * kTileQueries, &sh->full[st]);
+                }
+            }
+        }
+    } else if (warp == 1) {
+        // ------------------------------------------------ MMA issuer -----------------------------
+        if (lane == 0) {
+            uint32_t it = 0, local_item = 0;
+            bool ok = true;
+            for (uint32_t item = blockIdx.x; item < n_items && ok; item += gridDim.x, ++local_item) {
+                const int buf = local_item & 1;
+                ok = mbar_wait(&sh->d_empty[buf], ((local_item >> 1) & 1) ^ 1, p.cb.error);
+                if (!ok) break;
+                asm volatile("tcgen05.fence::after_thread_sync;" ::: "memory");
+                const uint32_t d_tmem = tmem_base + uint32_t(buf) * kTileQueries;
+                for (int s = 0; s < n_slabs && ok; ++s, ++it) {
+                    const int st = it % kStagesTc;
+                    ok = mbar_wait(&sh->full[st], (it / kStagesTc) & 1, p.cb.error);
+                    if (!ok) break;
+                    asm volatile("tcgen05.fence::after_thread_sync;" ::: "memory");
+                    const uint32_t a_addr = smem_u32(stages + size_t(st) * kStageBytesTc);
+                    const uint32_t b_addr = a_addr + kABytes;
+#pragma unroll
+                    for (int k = 0; k < kSlabK / 32; ++k)
+                        umma_i8(d_tmem, umma_desc(a_addr + k * 32), umma_desc(b_addr + k * 32), (s | k) != 0);
+                    umma_commit(&sh->empty[st]);          // the stage may be refilled once these MMAs have read it
+                }
+                if (ok) umma_commit(&sh->d_full[buf]);
+            }
+        }
+    } else if (warp < 2 + kEpilogueWarps) {
+        // ------------------------------------------------ epilogue -------------------------------
+        const int quarter = warp & 3;                     // TMEM lanes 32*quarter .. +31 are this warp's
+        const int row = quarter * 32 + lane;              // vector within the tile
+        const int et = (warp - 2) * 32 + lane;            // 0..127 among the epilogue threads
+        uint32_t local_item = 0;
+        bool ok = true;
+        for (uint32_t item = blockIdx.x; item < n_items && ok; item += gridDim.x, ++local_item) {
+            const int buf = local_item & 1;
+            const uint32_t vt = item / uint32_t(n_qgroups);
+            const int qg = int(item % uint32_t(n_qgroups));
+            // per-query parameters of this item (double buffered with the accumulators)
+            for (int c = et; c < kTileQueries; c += kEpilogueWarps * 32) {
+                const int ql = qg * kTileQueries + c;
+                float qs = 0.f, qb = 0.f, th = INFINITY;
+                if (ql < p.q_base + p.nq) {
+                    qs = p.qscale[ql]; qb = p.qbias[ql];
+                    const uint64_t key = p.cb.thr[ql];
+                    th = key == kEmptyKey ? -INFINITY : desc_bits_to_score(uint32_t(key >> 32));
+                }
+                sh->qscale[buf][c] = qs; sh->qbias[buf][c] = qb; sh->qthr[buf][c] = th;
+            }
+            asm volatile("bar.sync 1, %0;" ::"r"(kEpilogueWarps * 32) : "memory");
+            const uint32_t pos = pos_begin + vt * 4 + uint32_t(row >> 5);
+            const bool have = pos < pos_end;
+            uint32_t blk = 0;
+            if (have) blk = p.live_blocks ? p.live_blocks[pos] : pos;
+            const int64_t slot = int64_t(blk) * 32 + (row & 31);
+            bool live = have && slot < p.n;
+            if (live && p.mask) live = (p.mask[slot >> 6] >> (slot & 63)) & 1ull;
+            const float vs = live ? p.vec_scales[slot] : 0.0f;
+
+            ok = mbar_wait(&sh->d_full[buf], (local_item >> 1) & 1, p.cb.error);
+            if (!ok) break;
+            asm volatile("tcgen05.fence::after_thread_sync;" ::: "memory");
+            const uint32_t taddr = tmem_base + (uint32_t(quarter * 32) << 16) + uint32_t(buf) * kTileQueries;
+            for (int c0 = 0; c0 < kTileQueries; c0 += 32) {
+                uint32_t acc[32];
+                tmem_ld32(taddr + c0, acc);
+                asm volatile("tcgen05.wait::ld.sync.aligned;" ::: "memory");
+                if (live) {
+#pragma unroll
+                    for (int j = 0; j < 32; ++j) {
+                        const int c = c0 + j;
+                        const float score = __fmul_rn(fmaf(float(int(acc[j])), sh->qscale[buf][c], sh->qbias[buf][c]), vs);
+                        if (score >= sh->qthr[buf][c]) {
+                            const int ql = qg * kTileQueries + c;
+                            const uint64_t key = make_key(score, uint32_t(slot));
+                            if (key < p.cb.thr[ql]) {
+                                const uint32_t at = atomicAdd(&p.cb.cnt[ql], 1u);
+                                if (at < uint32_t(p.cb.cap)) p.cb.cand[size_t(ql) * p.cb.cap + at] = key;
+                            }
+                        }
+                    }
+                }
+            }
+            asm volatile("tcgen05.fence::before_thread_sync;" ::: "memory");
+            __syncwarp();
+            if (lane == 0) mbar_arrive(&sh->d_empty[buf]);
+        }
+    } else {
+        // ------------------------------------------------ expansion: codes -> int8 A slabs -------
+        const int ew = warp - (2 + kEpilogueWarps);       // 0..7
+        const int octet = lane & 7;                       // which 8-group run of the slab = 16-byte chunk index
+        const int blk_in_tile = ew >> 1;
+        const int quad = (ew & 1) * 4 + (lane >> 3);      // 4 vectors 4*quad .. 4*quad+3 of the block
+        const uint32_t T[4] = {p.level_words[0], p.level_words[1], p.level_words[2], p.level_words[3]};
+        uint32_t it = 0;
+        bool ok = true;
+        for (uint32_t item = blockIdx.x; item < n_items && ok; item += gridDim.x) {
+            const uint32_t vt = item / uint32_t(n_qgroups);
+            const uint32_t pos = pos_begin + vt * 4 + uint32_t(blk_in_tile);
+            const bool have = pos < pos_end;
+            uint32_t blk = 0;
+            if (have) blk = p.live_blocks ? p.live_blocks[pos] : pos;
+            const uint32_t *src = reinterpret_cast<const uint32_t *>(p.codes + size_t(blk) * ng * 32) + quad;
+            uint32_t w[8];
+            auto fetch = [&](int s) {
+                const int g0 = s * (kSlabK / 2) + octet * 8;
+#pragma unroll
+                for (int r = 0; r < 8; ++r) w[r] = (have && g0 + r < ng) ? __ldg(src + size_t(g0 + r) * 8) : 0u;
+            };
+            fetch(0);
+            for (int s = 0; s < n_slabs && ok; ++s, ++it) {
+                const int st = it % kStagesTc;
+                // 4x4 byte transposes: x[j] = bytes of vector 4*quad+j in groups g0..g0+3 (lo) and g0+4..g0+7 (hi)
+                const uint32_t t0 = prmt(w[0], w[1], 0x5140), t1 = prmt(w[0], w[1], 0x7362);
+                const uint32_t t2 = prmt(w[2], w[3], 0x5140), t3 = prmt(w[2], w[3], 0x7362);
+                const uint32_t u0 = prmt(w[4], w[5], 0x5140), u1 = prmt(w[4], w[5], 0x7362);
+                const uint32_t u2 = prmt(w[6], w[7], 0x5140), u3 = prmt(w[6], w[7], 0x7362);
+                const uint32_t xlo[4] = {prmt(t0, t2, 0x5410), prmt(t0, t2, 0x7632), prmt(t1, t3, 0x5410), prmt(t1, t3, 0x7632)};
+                const uint32_t xhi[4] = {prmt(u0, u2, 0x5410), prmt(u0, u2, 0x7632), prmt(u1, u3, 0x5410), prmt(u1, u3, 0x7632)};
+                if (s + 1 < n_slabs) fetch(s + 1);        // next slab's codes fly while this one is expanded
+                ok = mbar_wait(&sh->empty[st], ((it / kStagesTc) & 1) ^ 1, p.cb.error);
+                if (!ok) break;
+                unsigned char *a_stage = stages + size_t(st) * kStageBytesTc;
+#pragma unroll
+                for (int j = 0; j < 4; ++j) {
+                    uint4 v;
+                    expand8(xlo[j], T, v.x, v.y);
+                    expand8(xhi[j], T, v.z, v.w);
+                    const int row = blk_in_tile * 32 + quad * 4 + j;
+                    // 128-byte swizzle: 16-byte chunk c of row r sits at chunk position c ^ (r % 8)
+                    *reinterpret_cast<uint4 *>(a_stage + (row >> 3) * 1024 + (row & 7) * 128 + ((octet ^ (row & 7)) << 4)) = v;
+                }
+                asm volatile("fence.proxy.async.shared::cta;" ::: "memory");   // generic writes -> visible to the MMA
+                __syncwarp();
+                if (lane == 0) mbar_arrive(&sh->full[st]);
+            }
+        }
+    }
+
+    asm volatile("tcgen05.fence::before_thread_sync;" ::: "memory");
+    __syncthreads();
+    if (warp == 1) {
+        asm volatile("tcgen05.fence::after_thread_sync;" ::: "memory");
+        asm volatile("tcgen05.dealloc.cta_group::1.sync.aligned.b32 %0, %1;" ::"r"(tmem_base), "r"(kTmemCols) : "memory");
+    }
+}
+
+typedef CUresult (*EncodeTiledFn)(CUtensorMap *, CUtensorMapDataType, cuuint32_t, void *, const cuuint64_t *,
+                                  const cuuint64_t *, const cuuint32_t *, const cuuint32_t *, CUtensorMapInterleave,
+                                  CUtensorMapSwizzle, CUtensorMapL2promotion, CUtensorMapFloatOOBfill);
+
+EncodeTiledFn encode_fn() {
+    static EncodeTiledFn fn = nullptr;
+    if (!fn) {
+        void *sym = nullptr;
+        cudaDriverEntryPointQueryResult q;
+        if (cudaGetDriverEntryPoint("cuTensorMapEncodeTiled", &sym, cudaEnableDefault, &q) == cudaSuccess &&
+            q == cudaDriverEntryPointSuccess)
+            fn = reinterpret_cast<EncodeTiledFn>(sym);
+    }
+    return fn;
+}
+
+}  // namespace
+
+size_t scan_tc_smem_bytes() { return size_t(kStagesTc) * kStageBytesTc + sizeof(TcShared) + 1024; }
+
+bool scan_tc_supported(int bits, int mode) { return bits == 4 && mode == kModePermuteDot && encode_fn() != nullptr; }
+
+// weights: [rows][pitch] int8, pitch a multiple of 128, rows a multiple of 256, coordinates pair-swapped
+// (byte 2g = coordinate 2g+1, byte 2g+1 = coordinate 2g) to match the nibble order of a code byte.
+cudaError_t launch_scan_tc(const ScanParams &p, const int8_t *weights, int rows, int pitch, int sm_count, cudaStream_t s) {
+    if (p.nq <= 0 || p.pos_end <= p.pos_begin) return cudaSuccess;
+    EncodeTiledFn enc = encode_fn();
+    if (!enc) return cudaErrorNotSupported;
+    CUtensorMap map;
+    const cuuint64_t dims[2] = {cuuint64_t(pitch), cuuint64_t(rows)};
+    const cuuint64_t strides[1] = {cuuint64_t(pitch)};
+    const cuuint32_t box[2] = {cuuint32_t(kSlabK), cuuint32_t(kTileQueries)};
+    const cuuint32_t estr[2] = {1, 1};
+    if (enc(&map, CU_TENSOR_MAP_DATA_TYPE_UINT8, 2, const_cast<int8_t *>(weights), dims, strides, box, estr,
+            CU_TENSOR_MAP_INTERLEAVE_NONE, CU_TENSOR_MAP_SWIZZLE_128B, CU_TENSOR_MAP_L2_PROMOTION_L2_256B,
+            CU_TENSOR_MAP_FLOAT_OOB_FILL_NONE) != CUDA_SUCCESS)
+        return cudaErrorInvalidValue;
+    const int n_slabs = pitch / kSlabK;
+    const int n_qgroups = (p.q_base + p.nq + kTileQueries - 1) / kTileQueries;
+    const size_t smem = scan_tc_smem_bytes();
+    static bool attr_set = false;
+    if (!attr_set) {
+        cudaError_t e = cudaFuncSetAttribute(scan_tc_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, int(smem));
+        if (e != cudaSuccess) return e;
+        attr_set = true;
+    }
+    const uint32_t vtiles = (p.pos_end - p.pos_begin + 3) / 4;
+    const uint64_t items = uint64_t(vtiles) * n_qgroups;
+    // a multiple of the query-group count keeps the CTAs that share a vector tile in step (codes hit L2)
+    unsigned grid = unsigned(sm_count - sm_count % n_qgroups);
+    if (grid == 0) grid = unsigned(sm_count);
+    if (items < grid) grid = unsigned(items);
+    scan_tc_kernel<<<grid, kThreadsTc, smem, s>>>(p, map, n_slabs, n_qgroups);
+    return cudaGetLastError();
+}
+
+}  // namespace tv

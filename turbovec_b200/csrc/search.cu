@@ -91,7 +91,7 @@ __global__ void __launch_bounds__(128) query_prep_kernel(QueryPrepParams p) {
             p.qbias[q] = __fadd_rn(0.0f, bias_corr);
         }
         int8_t *wrow = p.weights + size_t(q) * p.dim_pad;
-        for (int d = tid; d < dim; d += blockDim.x) wrow[d] = round_clamp_i8(__fmul_rn(rowA[d], inv_qs));
+        for (int d = tid; d < dim; d += blockDim.x) wrow[d ^ 1] = round_clamp_i8(__fmul_rn(rowA[d], inv_qs));
         // mma.sync A fragments.  k-step ks covers byte-groups 16ks..16ks+15; thread t of a quad owns
         // groups 16ks + t + {0,4,8,12}; register byte order follows the nibble order of a code byte
         // (low nibble = odd coordinate 2g+1, high nibble = even coordinate 2g; search.rs:2787-2790).

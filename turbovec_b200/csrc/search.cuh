@@ -24,7 +24,8 @@ struct QueryPrepParams {
     float *q_rot;                  // [nq][dim] rotated (and TQ+-inverted) queries
     float *qscale, *qbias;         // [nq]
     uint8_t *luts;                 // [nq][ngroups*32]            (LUT modes)
-    int8_t *weights;               // [nq_pad][dim_pad] row-major  (permute-dot; tensor-core operand)
+    int8_t *weights;               // [rows][dim_pad] row-major, byte d^1 = weight of coordinate d (permute-dot;
+                                   // tensor-core operand: the swap matches the nibble order of a code byte)
     int dim_pad;                   // row pitch of `weights`
     uint32_t *wfrag;               // mma.sync A fragments (permute-dot), see scan kernel
     int mtiles_total;              // ceil(nq / 16)
@@ -85,6 +86,10 @@ struct ScanParams {
 };
 // Permute-dot scan on mma.sync (int8 x int8 -> int32), up to 64 queries per launch.
 cudaError_t launch_scan_pd(const ScanParams &p, int sm_count, cudaStream_t s);
+// Permute-dot scan on tcgen05 tensor cores with TMEM accumulators (scan_tc.cu); all queries in one launch.
+// weights: [rows][pitch] int8 with rows % 256 == 0, pitch % 128 == 0, adjacent coordinates swapped.
+bool scan_tc_supported(int bits, int mode);
+cudaError_t launch_scan_tc(const ScanParams &p, const int8_t *weights, int rows, int pitch, int sm_count, cudaStream_t s);
 // LUT scan on CUDA cores, up to kLutQueriesPerLaunch queries per launch.
 constexpr int kLutQueriesPerLaunch = 4;
 cudaError_t launch_scan_lut(const ScanParams &p, int sm_count, cudaStream_t s);
