@@ -249,3 +249,54 @@ def query_tables(queries, dim, bits, shift=None, scale=None, mode=MODE_AUTO):
                             _p(weights, C.c_int8), _p(levels, C.c_int8), _p(sc, C.c_float), _p(bi, C.c_float))
     return {"q_rot": q_rot, "luts": luts, "weights": weights, "levels": levels, "scale": sc, "bias": bi,
             "mode": resolve_mode(mode, bits, dim)}
+
+
+# ---------------------------------------------------------------------------------------------------
+# AVX-512 VNNI restatement of the reference's permute-dot scan (cpu_simd_baseline.cpp): CPU arm only.
+# ---------------------------------------------------------------------------------------------------
+_SIMD_SO = os.path.join(_HERE, "libtv_cpu_simd.so")
+
+
+@lru_cache(maxsize=1)
+def _simd_lib():
+    src = os.path.join(_HERE, "cpu_simd_baseline.cpp")
+    if not os.path.exists(_SIMD_SO) or os.path.getmtime(_SIMD_SO) < os.path.getmtime(src):
+        subprocess.check_call(["make", "-C", _HERE, "-s", "libtv_cpu_simd.so"])
+    lib = C.CDLL(_SIMD_SO)
+    u8p, f32p, i8p = C.POINTER(C.c_uint8), C.POINTER(C.c_float), C.POINTER(C.c_int8)
+    lib.tvs_available.restype = C.c_int
+    lib.tvs_to_vector_major.argtypes = [u8p, C.c_int64, C.c_int, u8p]
+    lib.tvs_search_pd.argtypes = [u8p, f32p, C.c_int64, C.c_int, i8p, i8p, f32p, f32p, C.c_int64, C.c_int64,
+                                  C.POINTER(C.c_uint64), C.c_int, f32p, C.POINTER(C.c_int64)]
+    lib.tvs_search_pd.restype = C.c_int64
+    return lib
+
+
+def simd_available() -> bool:
+    try:
+        return bool(_simd_lib().tvs_available())
+    except Exception:
+        return False
+
+
+def to_vector_major(blocked: np.ndarray, n: int, dim: int) -> np.ndarray:
+    blocked = np.ascontiguousarray(blocked, dtype=np.uint8)
+    out = np.empty_like(blocked)
+    _simd_lib().tvs_to_vector_major(_p(blocked, C.c_uint8), (n + 31) // 32, dim // 2, _p(out, C.c_uint8))
+    return out
+
+
+def search_simd(queries, vm_codes, scales, n, dim, k, mask_words=None, threads=None):
+    """4-bit permute-dot search on the vector-major layout with AVX-512 VNNI, all host threads by default."""
+    tabs = query_tables(queries, dim, 4, mode=MODE_PD)
+    nq = tabs["weights"].shape[0]
+    scales = _f32(scales)
+    kk = max(min(k, n), 1)
+    s_out = np.empty((nq, kk), np.float32)
+    i_out = np.empty((nq, kk), np.int64)
+    mw = None if mask_words is None else np.ascontiguousarray(mask_words, dtype=np.uint64)
+    threads = threads or (os.cpu_count() or 1)
+    ke = int(_simd_lib().tvs_search_pd(_p(vm_codes, C.c_uint8), _p(scales, C.c_float), n, dim, _p(tabs["levels"], C.c_int8),
+                                       _p(tabs["weights"], C.c_int8), _p(tabs["scale"], C.c_float), _p(tabs["bias"], C.c_float),
+                                       nq, min(k, n), _p(mw, C.c_uint64), threads, _p(s_out, C.c_float), _p(i_out, C.c_int64)))
+    return (s_out.ravel()[: nq * ke].reshape(nq, ke).copy(), i_out.ravel()[: nq * ke].reshape(nq, ke).copy())

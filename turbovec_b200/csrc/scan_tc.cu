@@ -260,48 +260,62 @@ scan_tc_kernel(ScanParams p, const __grid_constant__ CUtensorMap wmap, int n_sla
         }
     } else {
         // ------------------------------------------------ expansion: codes -> int8 A slabs -------
+        // The (item, slab) pairs of this CTA form one flat sequence; the code words of four slabs ahead are
+        // kept in flight in registers so that global-load latency never reaches the expansion itself.
         const int ew = warp - (2 + kEpilogueWarps);       // 0..7
         const int octet = lane & 7;                       // which 8-group run of the slab = 16-byte chunk index
         const int blk_in_tile = ew >> 1;
         const int quad = (ew & 1) * 4 + (lane >> 3);      // 4 vectors 4*quad .. 4*quad+3 of the block
+        const int row0 = blk_in_tile * 32 + quad * 4;
         const uint32_t T[4] = {p.level_words[0], p.level_words[1], p.level_words[2], p.level_words[3]};
-        uint32_t it = 0;
-        bool ok = true;
-        for (uint32_t item = blockIdx.x; item < n_items && ok; item += gridDim.x) {
-            const uint32_t vt = item / uint32_t(n_qgroups);
-            const uint32_t pos = pos_begin + vt * 4 + uint32_t(blk_in_tile);
-            const bool have = pos < pos_end;
+        const uint32_t my_items = blockIdx.x < n_items ? (n_items - blockIdx.x + gridDim.x - 1) / gridDim.x : 0;
+        const uint32_t total = my_items * uint32_t(n_slabs);
+        constexpr int kAhead = 4;
+        uint32_t w[kAhead][8];
+        auto fetch = [&](uint32_t f, uint32_t (&dst)[8]) {
+            const bool in_range = f < total;
+            const uint32_t item = blockIdx.x + (in_range ? f / uint32_t(n_slabs) : 0u) * gridDim.x;
+            const int sl = int(f % uint32_t(n_slabs));
+            const uint32_t pos = pos_begin + (item / uint32_t(n_qgroups)) * 4 + uint32_t(blk_in_tile);
+            const bool have = in_range && pos < pos_end;
             uint32_t blk = 0;
             if (have) blk = p.live_blocks ? p.live_blocks[pos] : pos;
             const uint32_t *src = reinterpret_cast<const uint32_t *>(p.codes + size_t(blk) * ng * 32) + quad;
-            uint32_t w[8];
-            auto fetch = [&](int s) {
-                const int g0 = s * (kSlabK / 2) + octet * 8;
+            const int g0 = sl * (kSlabK / 2) + octet * 8;
 #pragma unroll
-                for (int r = 0; r < 8; ++r) w[r] = (have && g0 + r < ng) ? __ldg(src + size_t(g0 + r) * 8) : 0u;
-            };
-            fetch(0);
-            for (int s = 0; s < n_slabs && ok; ++s, ++it) {
-                const int st = it % kStagesTc;
-                // 4x4 byte transposes: x[j] = bytes of vector 4*quad+j in groups g0..g0+3 (lo) and g0+4..g0+7 (hi)
-                const uint32_t t0 = prmt(w[0], w[1], 0x5140), t1 = prmt(w[0], w[1], 0x7362);
-                const uint32_t t2 = prmt(w[2], w[3], 0x5140), t3 = prmt(w[2], w[3], 0x7362);
-                const uint32_t u0 = prmt(w[4], w[5], 0x5140), u1 = prmt(w[4], w[5], 0x7362);
-                const uint32_t u2 = prmt(w[6], w[7], 0x5140), u3 = prmt(w[6], w[7], 0x7362);
+            for (int r = 0; r < 8; ++r) dst[r] = (have && g0 + r < ng) ? __ldg(src + size_t(g0 + r) * 8) : 0u;
+        };
+#pragma unroll
+        for (int u = 0; u < kAhead; ++u) fetch(uint32_t(u), w[u]);
+        bool ok = true;
+        for (uint32_t f0 = 0; f0 < total && ok; f0 += kAhead) {
+#pragma unroll
+            for (int u = 0; u < kAhead; ++u) {
+                const uint32_t f = f0 + uint32_t(u);
+                if (f >= total || !ok) break;
+                const int st = f % kStagesTc;
+                // 4x4 byte transposes: bytes of vector row0+j in groups g0..g0+3 (xlo) and g0+4..g0+7 (xhi)
+                const uint32_t t0 = prmt(w[u][0], w[u][1], 0x5140), t1 = prmt(w[u][0], w[u][1], 0x7362);
+                const uint32_t t2 = prmt(w[u][2], w[u][3], 0x5140), t3 = prmt(w[u][2], w[u][3], 0x7362);
+                const uint32_t u0 = prmt(w[u][4], w[u][5], 0x5140), u1 = prmt(w[u][4], w[u][5], 0x7362);
+                const uint32_t u2 = prmt(w[u][6], w[u][7], 0x5140), u3 = prmt(w[u][6], w[u][7], 0x7362);
                 const uint32_t xlo[4] = {prmt(t0, t2, 0x5410), prmt(t0, t2, 0x7632), prmt(t1, t3, 0x5410), prmt(t1, t3, 0x7632)};
                 const uint32_t xhi[4] = {prmt(u0, u2, 0x5410), prmt(u0, u2, 0x7632), prmt(u1, u3, 0x5410), prmt(u1, u3, 0x7632)};
-                if (s + 1 < n_slabs) fetch(s + 1);        // next slab's codes fly while this one is expanded
-                ok = mbar_wait(&sh->empty[st], ((it / kStagesTc) & 1) ^ 1, p.cb.error);
+                fetch(f + kAhead, w[u]);                  // refill this ring slot
+                uint4 v[4];
+#pragma unroll
+                for (int j = 0; j < 4; ++j) {
+                    expand8(xlo[j], T, v[j].x, v[j].y);
+                    expand8(xhi[j], T, v[j].z, v[j].w);
+                }
+                ok = mbar_wait(&sh->empty[st], ((f / kStagesTc) & 1) ^ 1, p.cb.error);
                 if (!ok) break;
                 unsigned char *a_stage = stages + size_t(st) * kStageBytesTc;
 #pragma unroll
                 for (int j = 0; j < 4; ++j) {
-                    uint4 v;
-                    expand8(xlo[j], T, v.x, v.y);
-                    expand8(xhi[j], T, v.z, v.w);
-                    const int row = blk_in_tile * 32 + quad * 4 + j;
+                    const int row = row0 + j;
                     // 128-byte swizzle: 16-byte chunk c of row r sits at chunk position c ^ (r % 8)
-                    *reinterpret_cast<uint4 *>(a_stage + (row >> 3) * 1024 + (row & 7) * 128 + ((octet ^ (row & 7)) << 4)) = v;
+                    *reinterpret_cast<uint4 *>(a_stage + (row >> 3) * 1024 + (row & 7) * 128 + ((octet ^ (row & 7)) << 4)) = v[j];
                 }
                 asm volatile("fence.proxy.async.shared::cta;" ::: "memory");   // generic writes -> visible to the MMA
                 __syncwarp();
