@@ -181,6 +181,8 @@ def run_ours(args):
     slot_offset = my_chunks[0] * CHUNK if my_chunks else 0
     scale_t = torch.from_numpy(dim_scale(1)).to(device)
     idx = T.TurboQuantIndex(DIM, BITS, device=local_rank)
+    if args.tc_min_batch is not None:
+        idx.set_option(T.OPT_MMA_MIN_BATCH, args.tc_min_batch)
     n_recall_q = 64
     q_all = torch.from_numpy(gen_rows_numpy(1, max(nq, n_recall_q), 10_000_000)).to(device)
     truth_s = torch.full((n_recall_q, K), -float("inf"), device=device)
@@ -341,6 +343,8 @@ def main():
     ap.add_argument("--n", type=int, default=10_000_000)
     ap.add_argument("--batch", type=int, default=1024)
     ap.add_argument("--no-cpu", action="store_true", help="skip the cpu_baseline leg")
+    ap.add_argument("--tc-min-batch", type=int, default=None,
+                    help="query batches of at least this size use the tcgen05 scan (library default if omitted; 0 = never)")
     args = ap.parse_args()
     args.warmup = max(args.warmup, 3) if args.impl == "ours" else args.warmup
     if args.impl == "reference":

@@ -88,7 +88,7 @@ struct tv_index {
 
     // options
     int score_mode = TV_SCORE_AUTO;
-    int64_t mma_min_batch = 0;   // 0 = tensor-memory path off (set by tv_set_option until measured)
+    int64_t mma_min_batch = 65;  // measured switch point: mma.sync covers 64 queries per pass, tcgen05 wins beyond
     int force_careful = 0;
 
     cudaStream_t stream = nullptr;

@@ -11,10 +11,12 @@
 //   B (queries): int8 weights, one 256 x 128 B box per stage, loaded by TMA (no multicast).
 // D (128 lanes x 256 int32 columns) lives in TMEM, double buffered (512 columns), so the epilogue of one
 // work item overlaps the MMAs of the next.  Warp roles: 0 = TMA producer, 1 = MMA issuer (+ TMEM
-// alloc/dealloc), 2-5 = epilogue (one TMEM lane quarter each), 6-13 = code expansion.
+// alloc/dealloc), 2-9 = epilogue (two per TMEM lane quarter, half the columns each), 10-17 = code expansion.
 //
 // Every wait is bounded; a wait that runs out records an error word and makes its role leave its loop.
 #include <cuda.h>
+
+#include <cstddef>
 
 #include "search.cuh"
 #include "tv_common.cuh"
@@ -30,8 +32,8 @@ constexpr int kABytes = kTileVectors * kSlabK;                // 16 KB
 constexpr int kBBytes = kTileQueries * kSlabK;                // 32 KB
 constexpr int kStageBytesTc = kABytes + kBBytes;              // 48 KB
 constexpr int kExpandWarps = 8;
-constexpr int kEpilogueWarps = 4;
-constexpr int kThreadsTc = (2 + kEpilogueWarps + kExpandWarps) * 32;   // 448
+constexpr int kEpilogueWarps = 8;                             // two per TMEM lane quarter, 128 columns each
+constexpr int kThreadsTc = (2 + kEpilogueWarps + kExpandWarps) * 32;   // 576
 constexpr uint32_t kTmemCols = 512;
 constexpr uint32_t kWaitLimitTc = 1u << 22;
 
@@ -121,11 +123,13 @@ struct TcShared {
     uint64_t d_full[2];            // accumulator buffer complete
     uint64_t d_empty[2];           // accumulator buffer read out by the 4 epilogue warps
     uint32_t tmem_base;
-    uint32_t pad;
+    uint32_t pad[3];
+    // per-query parameters of an item, double buffered with the accumulators; 16-byte aligned for float4 loads
     float qscale[2][kTileQueries];
     float qbias[2][kTileQueries];
     float qthr[2][kTileQueries];   // score of the current k-th key (-inf while fewer than k results exist)
 };
+static_assert(offsetof(TcShared, qscale) % 16 == 0, "parameter arrays must be 16-byte aligned");
 
 __global__ void __launch_bounds__(kThreadsTc, 1)
 scan_tc_kernel(ScanParams p, const __grid_constant__ CUtensorMap wmap, int n_slabs, int n_qgroups) {
@@ -201,24 +205,27 @@ scan_tc_kernel(ScanParams p, const __grid_constant__ CUtensorMap wmap, int n_sla
     } else if (warp < 2 + kEpilogueWarps) {
         // ------------------------------------------------ epilogue -------------------------------
         const int quarter = warp & 3;                     // TMEM lanes 32*quarter .. +31 are this warp's
+        const int half = (warp - 2) >> 2;                 // which 128 of the item's 256 query columns
         const int row = quarter * 32 + lane;              // vector within the tile
-        const int et = (warp - 2) * 32 + lane;            // 0..127 among the epilogue threads
+        const int et = (warp - 2) * 32 + lane;            // 0..255 among the epilogue threads
         uint32_t local_item = 0;
+        uint32_t vt = blockIdx.x / uint32_t(n_qgroups);
+        int qg = int(blockIdx.x % uint32_t(n_qgroups));
+        const uint32_t vt_step = gridDim.x / uint32_t(n_qgroups);
+        const int qg_step = int(gridDim.x % uint32_t(n_qgroups));
         bool ok = true;
         for (uint32_t item = blockIdx.x; item < n_items && ok; item += gridDim.x, ++local_item) {
             const int buf = local_item & 1;
-            const uint32_t vt = item / uint32_t(n_qgroups);
-            const int qg = int(item % uint32_t(n_qgroups));
-            // per-query parameters of this item (double buffered with the accumulators)
-            for (int c = et; c < kTileQueries; c += kEpilogueWarps * 32) {
-                const int ql = qg * kTileQueries + c;
+            // per-query parameters of this item: one query per epilogue thread
+            {
+                const int ql = qg * kTileQueries + et;
                 float qs = 0.f, qb = 0.f, th = INFINITY;
                 if (ql < p.q_base + p.nq) {
                     qs = p.qscale[ql]; qb = p.qbias[ql];
                     const uint64_t key = p.cb.thr[ql];
                     th = key == kEmptyKey ? -INFINITY : desc_bits_to_score(uint32_t(key >> 32));
                 }
-                sh->qscale[buf][c] = qs; sh->qbias[buf][c] = qb; sh->qthr[buf][c] = th;
+                sh->qscale[buf][et] = qs; sh->qbias[buf][et] = qb; sh->qthr[buf][et] = th;
             }
             asm volatile("bar.sync 1, %0;" ::"r"(kEpilogueWarps * 32) : "memory");
             const uint32_t pos = pos_begin + vt * 4 + uint32_t(row >> 5);
@@ -233,22 +240,30 @@ scan_tc_kernel(ScanParams p, const __grid_constant__ CUtensorMap wmap, int n_sla
             ok = mbar_wait(&sh->d_full[buf], (local_item >> 1) & 1, p.cb.error);
             if (!ok) break;
             asm volatile("tcgen05.fence::after_thread_sync;" ::: "memory");
-            const uint32_t taddr = tmem_base + (uint32_t(quarter * 32) << 16) + uint32_t(buf) * kTileQueries;
-            for (int c0 = 0; c0 < kTileQueries; c0 += 32) {
+            const int cbase = half * (kTileQueries / 2);
+            const uint32_t taddr = tmem_base + (uint32_t(quarter * 32) << 16) + uint32_t(buf) * kTileQueries + uint32_t(cbase);
+            const float4 *ps = reinterpret_cast<const float4 *>(&sh->qscale[buf][cbase]);
+            const float4 *pb = reinterpret_cast<const float4 *>(&sh->qbias[buf][cbase]);
+            const float4 *pt = reinterpret_cast<const float4 *>(&sh->qthr[buf][cbase]);
+            for (int c0 = 0; c0 < kTileQueries / 2; c0 += 32) {
                 uint32_t acc[32];
                 tmem_ld32(taddr + c0, acc);
                 asm volatile("tcgen05.wait::ld.sync.aligned;" ::: "memory");
                 if (live) {
 #pragma unroll
-                    for (int j = 0; j < 32; ++j) {
-                        const int c = c0 + j;
-                        const float score = __fmul_rn(fmaf(float(int(acc[j])), sh->qscale[buf][c], sh->qbias[buf][c]), vs);
-                        if (score >= sh->qthr[buf][c]) {
-                            const int ql = qg * kTileQueries + c;
-                            const uint64_t key = make_key(score, uint32_t(slot));
-                            if (key < p.cb.thr[ql]) {
-                                const uint32_t at = atomicAdd(&p.cb.cnt[ql], 1u);
-                                if (at < uint32_t(p.cb.cap)) p.cb.cand[size_t(ql) * p.cb.cap + at] = key;
+                    for (int j4 = 0; j4 < 8; ++j4) {
+                        const float4 s4 = ps[(c0 >> 2) + j4], b4 = pb[(c0 >> 2) + j4], t4 = pt[(c0 >> 2) + j4];
+                        const float sc[4] = {s4.x, s4.y, s4.z, s4.w}, bi[4] = {b4.x, b4.y, b4.z, b4.w}, th[4] = {t4.x, t4.y, t4.z, t4.w};
+#pragma unroll
+                        for (int e = 0; e < 4; ++e) {
+                            const float score = __fmul_rn(fmaf(float(int(acc[4 * j4 + e])), sc[e], bi[e]), vs);
+                            if (score >= th[e]) {         // rare: exact key comparison and append
+                                const int ql = qg * kTileQueries + cbase + c0 + 4 * j4 + e;
+                                const uint64_t key = make_key(score, uint32_t(slot));
+                                if (key < p.cb.thr[ql]) {
+                                    const uint32_t at = atomicAdd(&p.cb.cnt[ql], 1u);
+                                    if (at < uint32_t(p.cb.cap)) p.cb.cand[size_t(ql) * p.cb.cap + at] = key;
+                                }
                             }
                         }
                     }
@@ -257,6 +272,8 @@ scan_tc_kernel(ScanParams p, const __grid_constant__ CUtensorMap wmap, int n_sla
             asm volatile("tcgen05.fence::before_thread_sync;" ::: "memory");
             __syncwarp();
             if (lane == 0) mbar_arrive(&sh->d_empty[buf]);
+            vt += vt_step; qg += qg_step;
+            if (qg >= n_qgroups) { qg -= n_qgroups; ++vt; }
         }
     } else {
         // ------------------------------------------------ expansion: codes -> int8 A slabs -------
@@ -272,21 +289,38 @@ scan_tc_kernel(ScanParams p, const __grid_constant__ CUtensorMap wmap, int n_sla
         const uint32_t total = my_items * uint32_t(n_slabs);
         constexpr int kAhead = 4;
         uint32_t w[kAhead][8];
-        auto fetch = [&](uint32_t f, uint32_t (&dst)[8]) {
-            const bool in_range = f < total;
-            const uint32_t item = blockIdx.x + (in_range ? f / uint32_t(n_slabs) : 0u) * gridDim.x;
-            const int sl = int(f % uint32_t(n_slabs));
-            const uint32_t pos = pos_begin + (item / uint32_t(n_qgroups)) * 4 + uint32_t(blk_in_tile);
-            const bool have = in_range && pos < pos_end;
-            uint32_t blk = 0;
-            if (have) blk = p.live_blocks ? p.live_blocks[pos] : pos;
-            const uint32_t *src = reinterpret_cast<const uint32_t *>(p.codes + size_t(blk) * ng * 32) + quad;
-            const int g0 = sl * (kSlabK / 2) + octet * 8;
+        // fetch cursor: walks the same (item, slab) sequence as the consumers, without divisions
+        uint32_t f_item = blockIdx.x, f_vt = blockIdx.x / uint32_t(n_qgroups);
+        int f_qg = int(blockIdx.x % uint32_t(n_qgroups)), f_slab = 0;
+        const uint32_t vt_step = gridDim.x / uint32_t(n_qgroups);
+        const int qg_step = int(gridDim.x % uint32_t(n_qgroups));
+        const uint32_t *f_src = nullptr;
+        bool f_have = false;
+        auto fetch = [&](uint32_t (&dst)[8]) {
+            if (f_slab == 0) {                            // first slab of an item: locate its code block
+                const uint32_t pos = pos_begin + f_vt * 4 + uint32_t(blk_in_tile);
+                f_have = f_item < n_items && pos < pos_end;
+                uint32_t blk = 0;
+                if (f_have) blk = p.live_blocks ? p.live_blocks[pos] : pos;
+                f_src = reinterpret_cast<const uint32_t *>(p.codes + size_t(blk) * ng * 32) + quad;
+            }
+            const int g0 = f_slab * (kSlabK / 2) + octet * 8;
+            const uint32_t *src = f_src + size_t(g0) * 8;
+            if (f_have && g0 + 8 <= ng) {
 #pragma unroll
-            for (int r = 0; r < 8; ++r) dst[r] = (have && g0 + r < ng) ? __ldg(src + size_t(g0 + r) * 8) : 0u;
+                for (int r = 0; r < 8; ++r) dst[r] = __ldg(src + r * 8);
+            } else {
+#pragma unroll
+                for (int r = 0; r < 8; ++r) dst[r] = (f_have && g0 + r < ng) ? __ldg(src + r * 8) : 0u;
+            }
+            if (++f_slab == n_slabs) {
+                f_slab = 0;
+                f_item += gridDim.x; f_vt += vt_step; f_qg += qg_step;
+                if (f_qg >= n_qgroups) { f_qg -= n_qgroups; ++f_vt; }
+            }
         };
 #pragma unroll
-        for (int u = 0; u < kAhead; ++u) fetch(uint32_t(u), w[u]);
+        for (int u = 0; u < kAhead; ++u) fetch(w[u]);
         bool ok = true;
         for (uint32_t f0 = 0; f0 < total && ok; f0 += kAhead) {
 #pragma unroll
@@ -301,7 +335,7 @@ scan_tc_kernel(ScanParams p, const __grid_constant__ CUtensorMap wmap, int n_sla
                 const uint32_t u2 = prmt(w[u][6], w[u][7], 0x5140), u3 = prmt(w[u][6], w[u][7], 0x7362);
                 const uint32_t xlo[4] = {prmt(t0, t2, 0x5410), prmt(t0, t2, 0x7632), prmt(t1, t3, 0x5410), prmt(t1, t3, 0x7632)};
                 const uint32_t xhi[4] = {prmt(u0, u2, 0x5410), prmt(u0, u2, 0x7632), prmt(u1, u3, 0x5410), prmt(u1, u3, 0x7632)};
-                fetch(f + kAhead, w[u]);                  // refill this ring slot
+                fetch(w[u]);                              // refill this ring slot (slab f + kAhead)
                 uint4 v[4];
 #pragma unroll
                 for (int j = 0; j < 4; ++j) {
