@@ -1,7 +1,7 @@
 #!/usr/bin/env python
 """Benchmark of the encode-and-scan hot path.
 
-  python bench.py [--gpus N] [--steps K] [--warmup W] [--impl ours|reference] [--n N_VECTORS] [--batch NQ]
+  python bench.py [--gpus N] [--steps K] [--warmup W] [--impl ours|reference] [--vectors N_VECTORS] [--batch NQ]
 
 Workload (N = 1): 10,000,000 x 1536 fp32 rows (anisotropic Gaussian, L2-normalised; synthetic stand-in for the
 OpenAI-1536 embeddings the reference measures on), 4-bit codes, k = 10.  One step = one search batch of 1,024
@@ -226,9 +226,12 @@ def run_ours(args):
         return merge_topk(torch, torch.cat(gs, 1), torch.cat(gi, 1), K)
 
     def step_host(qh, nqq):
+        """qh: pinned host tensor.  Host buffers in, host results out."""
         if world == 1:
-            return idx.search(qh, K)
-        s, i = step_device(qh.to(device, non_blocking=True), nqq)
+            return idx.search(qh.numpy(), K)
+        qd = qh.to(device, non_blocking=True)
+        torch.cuda.synchronize()
+        s, i = step_device(qd, nqq)
         return s.cpu().numpy(), i.cpu().numpy()
 
     def barrier():
@@ -262,11 +265,11 @@ def run_ours(args):
     sampler.start()
     dt, scan_ms, scan_launches, launches = timed(lambda: step_device(q_dev, nq), args.steps, args.warmup)
     clocks = sampler.stop()
-    dt_e2e, _, _, _ = timed(lambda: step_host(q_host.numpy(), nq), args.steps, max(1, args.warmup // 2))
+    dt_e2e, _, _, _ = timed(lambda: step_host(q_host, nq), args.steps, max(1, args.warmup // 2))
     q1_dev = q_dev[:1].contiguous()
     b1_steps = max(args.steps, 20)
     dt1, scan1_ms, scan1_launches, _ = timed(lambda: step_device(q1_dev, 1), b1_steps, args.warmup)
-    q1_host = q_host[:1].numpy()
+    q1_host = q_host[:1].contiguous().pin_memory()
     dt1_e2e, _, _, _ = timed(lambda: step_host(q1_host, 1), b1_steps, 2)
 
     # recall@10 of the first n_recall_q queries against exact fp32 inner products
@@ -298,6 +301,8 @@ def run_ours(args):
     ingest_rate = ingest_rows / (ingest_ms / 1e3) if ingest_ms > 0 else None
     ingest_bytes = 4 * DIM + ng + 4
 
+    tc_min = idx.get_option(T.OPT_MMA_MIN_BATCH)
+    main_kernel = "scan_tc_kernel (tcgen05)" if tc_min > 0 and nq >= tc_min else "scan_pd_kernel (mma.sync)"
     cpu_qps, cpu_ms, cores, sample, _ = cpu_arm(200_000, 1000, 2, 1, n_total) if world == 1 and not args.no_cpu else (None,) * 5
 
     line = {
@@ -313,7 +318,7 @@ def run_ours(args):
         "clocks": clocks,
         "roofline": {"bound": "tensor", "achieved": achieved_tops, "peak": pk["tensor_tflops"], "unit": "TFLOP/s",
                      "frac": achieved_tops / pk["tensor_tflops"] if achieved_tops else None, "traffic": None,
-                     "kernel": "scan_pd_kernel", "launches_per_step": scan_launches / args.steps,
+                     "kernel": main_kernel, "launches_per_step": scan_launches / args.steps,
                      "note": f"int8 multiply-adds counted as 2 ops against the {pk['source']} bf16 sustained peak"},
         "batch1": {"value": b1_steps / dt1, "unit": UNIT, "ms_per_query": dt1 / b1_steps * 1e3,
                    "e2e": {"value": b1_steps / dt1_e2e, "unit": UNIT, "h2d_bytes_per_step": DIM * 4, "d2h_bytes_per_step": K * 12},
@@ -340,9 +345,9 @@ def main():
     ap.add_argument("--steps", type=int, default=10)
     ap.add_argument("--warmup", type=int, default=3)
     ap.add_argument("--impl", default="ours", choices=["ours", "reference"])
-    ap.add_argument("--n", type=int, default=10_000_000)
+    ap.add_argument("--vectors", dest="n", type=int, default=10_000_000)
     ap.add_argument("--batch", type=int, default=1024)
-    ap.add_argument("--no-cpu", action="store_true", help="skip the cpu_baseline leg")
+    ap.add_argument("--skip-cpu", dest="no_cpu", action="store_true", help="skip the cpu_baseline leg")
     ap.add_argument("--tc-min-batch", type=int, default=None,
                     help="query batches of at least this size use the tcgen05 scan (library default if omitted; 0 = never)")
     args = ap.parse_args()
