@@ -83,15 +83,25 @@ __global__ void __launch_bounds__(256) ingest_kernel(IngestParams p) {
         if (active) {
             const int64_t row = my_slot - slot_lo;
             const float4 *src = reinterpret_cast<const float4 *>(p.x + row * dim);
-            for (int i = lane; i < dim / 4; i += 32) {
-                const float4 v = src[i];
-                reinterpret_cast<float4 *>(rowA)[i] = v;
-                const bool bad = !(fabsf(v.x) < kMaxMagnitude) || !(fabsf(v.y) < kMaxMagnitude) ||
-                                 !(fabsf(v.z) < kMaxMagnitude) || !(fabsf(v.w) < kMaxMagnitude);
-                if (bad) {
-                    int c = !(fabsf(v.x) < kMaxMagnitude) ? 0 : !(fabsf(v.y) < kMaxMagnitude) ? 1
-                          : !(fabsf(v.z) < kMaxMagnitude) ? 2 : 3;
-                    atomicMin(p.first_invalid, (unsigned long long)((p.row_base + row) * dim + 4 * i + c));
+            const int nvec = dim / 4;
+            for (int i0 = lane; i0 < nvec; i0 += 32 * 4) {
+                float4 v[4];
+#pragma unroll
+                for (int u = 0; u < 4; ++u) {             // four loads in flight per lane before any use
+                    const int i = i0 + 32 * u;
+                    v[u] = i < nvec ? __ldcs(src + i) : make_float4(0.f, 0.f, 0.f, 0.f);
+                }
+#pragma unroll
+                for (int u = 0; u < 4; ++u) {
+                    const int i = i0 + 32 * u;
+                    if (i >= nvec) break;
+                    reinterpret_cast<float4 *>(rowA)[i] = v[u];
+                    const bool bx = !(fabsf(v[u].x) < kMaxMagnitude), by = !(fabsf(v[u].y) < kMaxMagnitude);
+                    const bool bz = !(fabsf(v[u].z) < kMaxMagnitude), bw = !(fabsf(v[u].w) < kMaxMagnitude);
+                    if (bx | by | bz | bw) {
+                        const int c = bx ? 0 : by ? 1 : bz ? 2 : 3;
+                        atomicMin(p.first_invalid, (unsigned long long)((p.row_base + row) * dim + 4 * i + c));
+                    }
                 }
             }
         }
@@ -104,6 +114,7 @@ __global__ void __launch_bounds__(256) ingest_kernel(IngestParams p) {
             const unsigned peers = V * 8 >= 32 ? kFullMask : ((1u << (V * 8)) - 1u);
             const float *row = s.rowA + size_t(v) * stride;
             float acc = 0.0f;
+#pragma unroll 8
             for (int j = c; j < dim; j += 8) {
                 const float x = row[j];
                 acc = __fadd_rn(acc, __fmul_rn(x, x));
@@ -122,6 +133,7 @@ __global__ void __launch_bounds__(256) ingest_kernel(IngestParams p) {
         // 3. rotate (A -> B -> A), quantise, one code per coordinate
         if (active) {
             rotate_row<LOG2B>(rowA, rowB, s.perm0, s.perm1, dim, p.inv_sqrt_block, true, s.inv[warp], lane);
+#pragma unroll 4
             for (int j = lane; j < dim; j += 32) {
                 float calib = rowA[j];
                 if (calibrated) calib = __fmul_rn(__fadd_rn(calib, p.shift[j]), p.scale_tq[j]);
@@ -147,6 +159,7 @@ __global__ void __launch_bounds__(256) ingest_kernel(IngestParams p) {
             if (!live) {
                 // nothing to sum; the shuffles below still need this thread
             } else if (!calibrated) {
+#pragma unroll 8
                 for (int j = c; j < dim; j += 4)
                     acc = __dadd_rn(acc, __dmul_rn(double(row[j]), s.cent64[cd[j]]));
             } else {
@@ -162,7 +175,9 @@ __global__ void __launch_bounds__(256) ingest_kernel(IngestParams p) {
                 p.scales[slot] = acc > 0.1 ? __fdiv_rn(s.norm[v], __double2float_rn(acc)) : 0.0f;
         }
 
+       
         // 5. group bytes: coordinate g*cpb + k at shift (cpb-1-k)*field (pack.rs:264-282)
+#pragma unroll 4
         for (int g = lane; g < ng; g += 32) {
             unsigned byte = 0;
             if (active)

@@ -8,10 +8,11 @@
 // fused (explicit __f*_rn intrinsics).  A multiply by a +-1 sign is exact, so it is done as a
 // conditional negation.
 //
-// One warp rotates one row held in shared memory.  A B-block is spread over the warp as
-// R = B/32 consecutive coordinates per lane: stages with len < R are register-local, stages
-// len = R*m (m = 1..16) exchange registers between lanes `lane` and `lane ^ m`.  For B < 32 a
-// lane owns whole blocks; for B > 2048 the transform runs in shared memory.
+// One warp rotates one row held in shared memory.  Coordinate e of a B-block sits in lane e % 32,
+// register e / 32: consecutive lanes touch consecutive shared-memory words (no bank conflicts), stages
+// len < 32 exchange values between lanes `lane` and `lane ^ len`, stages len >= 32 pair registers — the
+// stage order stays len = 1, 2, 4, ...  For B < 32 several blocks share a warp pass; for B > 2048 the
+// transform runs in shared memory.
 #pragma once
 #include "tv_common.cuh"
 
@@ -33,10 +34,11 @@ __device__ __forceinline__ void wht_in_registers(float (&v)[R]) {
     }
 }
 
-template <int R>
+// Stages len = 1 .. MAXLEN/2 between lanes: the lane with bit `len` clear holds the lower element.
+template <int R, int MAXLEN>
 __device__ __forceinline__ void wht_across_lanes(float (&v)[R], int lane) {
 #pragma unroll
-    for (int m = 1; m < 32; m <<= 1) {
+    for (int m = 1; m < MAXLEN; m <<= 1) {
         const bool upper = (lane & m) != 0;
 #pragma unroll
         for (int r = 0; r < R; ++r) {
@@ -60,29 +62,29 @@ template <int LOG2B>
 __device__ __forceinline__ void rotation_round(const float *src, float *dst, const uint16_t *perm, int dim,
                                                float inv_sqrt_block, bool use_inv, float inv, int lane) {
     if constexpr (LOG2B <= 4) {
+        // 32 / B whole blocks per pass of the warp; B divides 32 and dim, so a ragged last pass still
+        // holds whole blocks and the idle lanes only feed shuffles nobody reads
         constexpr int B = 1 << LOG2B;
-        const int nblk = dim >> LOG2B;
-        for (int blk = lane; blk < nblk; blk += 32) {
-            float v[B];
-#pragma unroll
-            for (int r = 0; r < B; ++r) v[r] = gather_one(src, perm[blk * B + r], use_inv, inv);
-            wht_in_registers<B>(v);
-#pragma unroll
-            for (int r = 0; r < B; ++r) dst[blk * B + r] = __fmul_rn(v[r], inv_sqrt_block);
+        for (int base = 0; base < dim; base += 32) {
+            const int idx = base + lane;
+            const bool active = idx < dim;
+            float v[1] = {active ? gather_one(src, perm[idx], use_inv, inv) : 0.0f};
+            wht_across_lanes<1, B>(v, lane);
+            if (active) dst[idx] = __fmul_rn(v[0], inv_sqrt_block);
         }
     } else if constexpr (LOG2B <= 11) {
         constexpr int B = 1 << LOG2B;
         constexpr int R = B / 32;
         const int nblk = dim >> LOG2B;
         for (int blk = 0; blk < nblk; ++blk) {
-            const int base = blk * B + lane * R;
+            const int base = blk * B + lane;
             float v[R];
 #pragma unroll
-            for (int r = 0; r < R; ++r) v[r] = gather_one(src, perm[base + r], use_inv, inv);
-            wht_in_registers<R>(v);
-            wht_across_lanes<R>(v, lane);
+            for (int r = 0; r < R; ++r) v[r] = gather_one(src, perm[base + r * 32], use_inv, inv);
+            wht_across_lanes<R, 32>(v, lane);     // len = 1 .. 16
+            wht_in_registers<R>(v);               // len = 32 .. B/2 (register r holds coordinates r*32 + lane)
 #pragma unroll
-            for (int r = 0; r < R; ++r) dst[base + r] = __fmul_rn(v[r], inv_sqrt_block);
+            for (int r = 0; r < R; ++r) dst[base + r * 32] = __fmul_rn(v[r], inv_sqrt_block);
         }
     } else {
         const int B = dim & -dim;
