@@ -207,8 +207,8 @@ def run_ours(args):
         del x, sc
     n_local = len(idx)
 
-    d_scores = torch.empty((nq, K), dtype=torch.float32, device=device)
-    d_slots = torch.empty((nq, K), dtype=torch.int64, device=device)
+    d_scores = torch.empty((max(nq, n_recall_q), K), dtype=torch.float32, device=device)
+    d_slots = torch.empty((max(nq, n_recall_q), K), dtype=torch.int64, device=device)
     q_dev = q_all[:nq].contiguous()
     q_host = q_dev.cpu().pin_memory()
     h_scores = np.empty((nq, K), np.float32)

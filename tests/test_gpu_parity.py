@@ -104,6 +104,43 @@ def test_add_rejects_invalid_and_leaves_index_unchanged(T):
     assert np.array_equal(idx.codes_blocked_seq(), O.packed_to_blocked(enc["packed"], 4, 128))
 
 
+@pytest.mark.parametrize("row", G.ENCODE_FINGERPRINT, ids=lambda r: f"d{r[0]}b{r[1]}")
+def test_calibrate_then_add_reproduces_the_frozen_fingerprint(T, row):
+    """calibrate(sample) + add(sample), the reference's own fixture: calibration, codes and scales hashes."""
+    dim, bits, _b, _c, g_cal, g_codes, g_scales, _ = row
+    x = O.lcg_vectors(2000, dim, G.cell_seed(dim, bits))
+    idx = T.TurboQuantIndex(dim, bits)
+    assert idx.calibration_state == "uncalibrated"
+    idx.calibrate(x)
+    assert idx.calibration_state == "calibrated"
+    shift, scale = idx.calibration()
+    assert O.fnv1a(np.concatenate([shift, scale])) == g_cal
+    idx.add(x)
+    assert O.fnv1a(idx.packed_codes()) == g_codes
+    assert O.fnv1a(idx.scales()) == g_scales
+
+
+def test_calibrated_search_matches_oracle(T):
+    dim, bits, n = 512, 4, 3000
+    x = anisotropic(n, dim, seed=51) * np.float32(3.0)
+    x[:, ::7] *= np.float32(2.5)                       # heavy coordinates so the fit is far from identity
+    q = anisotropic(9, dim, seed=51, offset=3)
+    shift, scale = O.fit_calibration(x, bits)
+    for mode_bits in (4, 2):
+        sh, sc = O.fit_calibration(x, mode_bits)
+        idx = T.TurboQuantIndex(dim, mode_bits)
+        idx.calibrate(x)
+        idx.add(x)
+        enc = O.encode(x, mode_bits, sh, sc)
+        blocked = O.packed_to_blocked(enc["packed"], mode_bits, dim)
+        assert np.array_equal(idx.codes_blocked_seq(), blocked)
+        s, i = idx.search(q, 10)
+        rs, ri = O.search(q, blocked, enc["scales"], n, dim, mode_bits, 10, shift=sh, scale=sc)
+        assert np.array_equal(i, ri) and np.array_equal(s, rs)
+    with pytest.raises(ValueError):
+        idx.calibrate(x)                                 # not empty any more
+
+
 # ---------------------------------------------------------------- search
 def _build(T, x, bits, kind="pos", ids=None):
     dim = x.shape[1]

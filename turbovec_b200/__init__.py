@@ -137,6 +137,14 @@ class _Base:
         sample = _f32_2d("sample", sample)
         self._check(self._lib.tv_calibrate(self._h, _ptr(sample), sample.shape[0], sample.shape[1]))
 
+    def calibration(self):
+        """(shift, scale) of the TQ+ pair, or None while uncalibrated (tqplus_shift / tqplus_scale)."""
+        d = self.dim or 0
+        shift, scale = np.empty(d, np.float32), np.empty(d, np.float32)
+        flag = C.c_int(0)
+        self._check(self._lib.tv_calibration(self._h, _ptr(shift), _ptr(scale), d, C.byref(flag)))
+        return (shift, scale) if flag.value else None
+
     def codebook(self):
         bits = self.bit_width
         b = np.empty((1 << bits) - 1, np.float32)

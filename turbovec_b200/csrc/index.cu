@@ -1268,10 +1268,80 @@ int tv_calibration(const tv_index *h, float *shift_out, float *scale_out, size_t
     return TV_OK;
 }
 
+// TQ+ fit: encode::fit_calibration (encode.rs:470-480) = rotate the unit-normalised sample on the device, then
+// per coordinate map the empirical [p_lo, p_hi] quantiles onto the codebook's outer centroids
+// (tqplus_anchor encode.rs:364-369, compute_tqplus_calibration :737-857).  Validation order of lib.rs:2599-2640.
 int tv_calibrate(tv_index *h, const float *sample, size_t n, size_t dim) {
-    (void)sample; (void)n; (void)dim;
-    if (!h) return TV_ERR_INVALID_ARGUMENT;
-    return fail(h, TV_ERR_UNSUPPORTED, "tv_calibrate: the TQ+ fit is not built yet; fit on the host and use tv_set_calibration");
+    if (!h || (!sample && n)) return TV_ERR_INVALID_ARGUMENT;
+    std::lock_guard<std::mutex> lock(h->mu);
+    int rc = validate_dim_for_add(h, dim);
+    if (rc != TV_OK) return rc;
+    if (n < 2) return fail(h, TV_ERR_CALIBRATE_SAMPLE_TOO_SMALL, "calibration needs at least 2 rows, got " + std::to_string(n));
+    if (h->n != 0) return fail(h, TV_ERR_CALIBRATE_NOT_EMPTY, "re-encoding stored rows under a new calibration is not built: calibrate before the first add");
+    for (size_t i = 0; i < n * dim; ++i)
+        if (!(std::fabs(sample[i]) < kMaxInputMagnitude)) {
+            h->err_vec = i / dim; h->err_coord = i % dim; h->err_value = sample[i];
+            return fail(h, TV_ERR_INVALID_INPUT_VALUE, "sample row " + std::to_string(i / dim) + " coordinate " + std::to_string(i % dim) + " is not finite or exceeds 1e16 in magnitude");
+        }
+    TV_CUDA(cudaSetDevice(h->device));
+    const bool was_lazy = h->dim == 0;
+    if (was_lazy) h->dim = dim;
+    auto undo = [&]() { if (was_lazy) { h->dim = 0; h->tables_ready = false; } };
+    rc = ensure_tables(h);
+    if (rc != TV_OK) { undo(); return rc; }
+    const int V = ingest_vectors_per_pass(int(dim), h->ngroups, h->smem_limit);
+    if (V == 0) { undo(); return fail(h, TV_ERR_UNSUPPORTED, "dim too large for the ingest kernel's shared memory"); }
+
+    std::vector<float> rotated(n * dim);
+    DeviceArray<float> d_rot;
+    const size_t chunk_rows = std::max<size_t>(1, std::min<size_t>(n, (size_t(128) << 20) / (dim * 4)));
+    TV_CUDA(h->d_stage.reserve(chunk_rows * dim));
+    TV_CUDA(d_rot.reserve(chunk_rows * dim));
+    h->h_flags->first_invalid = ~0ull;
+    TV_CUDA(cudaMemcpyAsync(&h->d_flags->first_invalid, &h->h_flags->first_invalid, 8, cudaMemcpyHostToDevice, h->stream));
+    IngestParams p{};
+    p.dim = int(dim); p.bits = h->bits; p.ngroups = h->ngroups;
+    p.perm0 = h->d_perm.ptr; p.perm1 = h->d_perm.ptr + dim; p.inv_sqrt_block = h->rot.inv_sqrt_block;
+    p.boundaries = h->d_codebook.ptr; p.centroids = h->d_codebook.ptr + 16;
+    p.first_invalid = &h->d_flags->first_invalid;
+    p.rot_out = d_rot.ptr;
+    for (size_t done = 0; done < n; done += chunk_rows) {
+        const size_t rows = std::min(chunk_rows, n - done);
+        TV_CUDA(cudaMemcpyAsync(h->d_stage.ptr, sample + done * dim, rows * dim * 4, cudaMemcpyHostToDevice, h->stream));
+        p.x = h->d_stage.ptr; p.n = int64_t(rows); p.slot0 = 0; p.row_base = int64_t(done);
+        TV_CUDA(launch_ingest(p, V, h->stream));
+        h->launches++;
+        TV_CUDA(cudaMemcpyAsync(rotated.data() + done * dim, d_rot.ptr, rows * dim * 4, cudaMemcpyDeviceToHost, h->stream));
+        TV_CUDA(cudaStreamSynchronize(h->stream));
+    }
+
+    // anchor: probability mass inside the outermost centroid (encode.rs:364-369)
+    const double a = (double(dim) - 1.0) / 2.0;
+    float c_outer = 0.f;
+    for (float c : h->cb.centroids) c_outer = std::fmax(c_outer, std::fabs(c));
+    const double p_hi = beta_cdf(a, a, (double(c_outer) + 1.0) / 2.0), p_lo = 1.0 - p_hi;
+    const float qc_lo = -c_outer, qc_span = c_outer - qc_lo;
+    const size_t lo_idx = size_t(double(n) * p_lo);
+    const size_t hi_idx = std::max(std::min(size_t(double(n) * p_hi), n - 1), lo_idx + 1);
+    std::vector<float> shift(dim, 0.f), scale(dim, 1.f), col(n);
+    bool identity = true;
+    for (size_t d = 0; d < dim; ++d) {
+        for (size_t i = 0; i < n; ++i) col[i] = rotated[i * dim + d];
+        std::nth_element(col.begin(), col.begin() + lo_idx, col.end());
+        const float qe_lo = col[lo_idx];
+        std::nth_element(col.begin() + lo_idx + 1, col.begin() + hi_idx, col.end());
+        const float qe_hi = col[hi_idx];
+        const float qe_span = qe_hi - qe_lo;
+        if (qe_span > 1e-6f) {                                       // encode.rs:846-850
+            scale[d] = qc_span / qe_span;
+            shift[d] = qc_lo / scale[d] - qe_lo;
+        }
+        if (shift[d] != 0.f || scale[d] != 1.f) identity = false;
+    }
+    if (identity) { undo(); return fail(h, TV_ERR_CALIBRATE_DEGENERATE_SAMPLE, "the sample yields the identity calibration (degenerate sample)"); }
+    h->shift = shift;
+    h->scale_tq = scale;
+    return upload_calibration(h);
 }
 
 }  // extern "C"

@@ -131,6 +131,15 @@ __global__ void __launch_bounds__(256) ingest_kernel(IngestParams p) {
         __syncthreads();
 
         // 3. rotate (A -> B -> A), quantise, one code per coordinate
+        if (p.rot_out != nullptr) {                       // rotate-only mode (uniform across the grid)
+            if (active) {
+                rotate_row<LOG2B>(rowA, rowB, s.perm0, s.perm1, dim, p.inv_sqrt_block, true, s.inv[warp], lane);
+                float *out = p.rot_out + (my_slot - slot_lo) * dim;
+                for (int j = lane; j < dim; j += 32) out[j] = rowA[j];
+            }
+            __syncthreads();
+            continue;
+        }
         if (active) {
             rotate_row<LOG2B>(rowA, rowB, s.perm0, s.perm1, dim, p.inv_sqrt_block, true, s.inv[warp], lane);
 #pragma unroll 4

@@ -26,6 +26,8 @@ struct IngestParams {
     const float *inv_scale_tq;     // 1.0f / scale_tq[d], rounded once in f32 (encode.rs:593)
     uint8_t *codes;                // sequential-blocked code array of the whole index
     float *scales;                 // per-slot scales of the whole index
+    float *rot_out;                // when set: write the rotated unit rows [n][dim] here and encode nothing
+                                   // (input of the TQ+ fit, encode.rs:470-480)
     unsigned long long *first_invalid;  // min flat index of a coordinate failing |x| < 1e16 (init ~0ull)
 };
 

@@ -255,7 +255,7 @@ __device__ __forceinline__ uint32_t prmt(uint32_t a, uint32_t b, uint32_t sel) {
     return d;
 }
 __device__ __forceinline__ void mma_s8(int (&c)[4], const uint4 &a, uint32_t b0, uint32_t b1) {
-    asm volatile(
+    asm(
         "mma.sync.aligned.m16n8k32.row.col.s32.s8.s8.s32 {%0,%1,%2,%3}, {%4,%5,%6,%7}, {%8,%9}, {%0,%1,%2,%3};"
         : "+r"(c[0]), "+r"(c[1]), "+r"(c[2]), "+r"(c[3])
         : "r"(a.x), "r"(a.y), "r"(a.z), "r"(a.w), "r"(b0), "r"(b1));
@@ -285,7 +285,7 @@ __device__ __forceinline__ void expand4(uint32_t x, const uint32_t (&T)[4], uint
 }
 
 template <int MT>
-__global__ void __launch_bounds__((kConsumerWarps + 1) * 32, MT <= 2 ? 2 : 1) scan_pd_kernel(ScanParams p) {
+__global__ void __launch_bounds__((kConsumerWarps + 1) * 32, MT == 1 ? 3 : (MT == 2 ? 2 : 1)) scan_pd_kernel(ScanParams p) {
     extern __shared__ __align__(128) unsigned char smem_raw[];
     uint8_t *stage_mem = smem_raw;
     __shared__ uint64_t full_bar[kStages], empty_bar[kStages];
@@ -360,6 +360,7 @@ __global__ void __launch_bounds__((kConsumerWarps + 1) * 32, MT <= 2 ? 2 : 1) sc
                     reinterpret_cast<const uint32_t *>(stage_mem + size_t(s) * kStageBytes + size_t(warp) * kChunkRows * kLanes);
                 const int rows_here = min(kChunkRows, ng - ch * kChunkRows);
                 const int ksteps = (rows_here + 15) / 16;
+#pragma unroll 2
                 for (int ks = 0; ks < ksteps; ++ks) {
                     // rows 16ks + t + {0,4,8,12}, word `quad` of each 32-byte row: conflict-free
                     const uint32_t *r0 = rows + (16 * ks + t) * 8 + quad;
@@ -638,7 +639,7 @@ cudaError_t launch_scan_pd(const ScanParams &p, int sm_count, cudaStream_t s) {
     const int mt = (p.nq + 15) / 16;
     const size_t smem = size_t(kStages) * kStageBytes;
     const uint32_t tiles = (p.pos_end - p.pos_begin + kConsumerWarps - 1) / kConsumerWarps;
-    const unsigned per_sm = mt <= 2 ? 2 : 1;                 // resident CTAs per SM (register budget)
+    const unsigned per_sm = mt == 1 ? 3 : (mt == 2 ? 2 : 1);   // resident CTAs per SM (register budget)
     const unsigned grid = unsigned(min(uint32_t(sm_count) * per_sm, tiles));
     const unsigned threads = (kConsumerWarps + 1) * 32;
 #define TV_LAUNCH_PD(M)                                                                                             \
