@@ -67,12 +67,19 @@ __device__ __forceinline__ uint32_t prmt(uint32_t a, uint32_t b, uint32_t sel) {
     asm("prmt.b32 %0, %1, %2, %3;" : "=r"(d) : "r"(a), "r"(b), "r"(sel));
     return d;
 }
+// high 32 bits of a * b + c on the FMA pipe: a right shift that does not load the ALU pipe
+__device__ __forceinline__ uint32_t mad_hi(uint32_t a, uint32_t b, uint32_t c) {
+    uint32_t d;
+    asm("mad.hi.u32 %0, %1, %2, %3;" : "=r"(d) : "r"(a), "r"(b), "r"(c));
+    return d;
+}
 // Eight nibbles of x -> eight int8 levels; output byte i of (lo, hi) belongs to nibble i / i+4 of x.
 __device__ __forceinline__ void expand8(uint32_t x, const uint32_t (&T)[4], uint32_t &lo, uint32_t &hi) {
     const uint32_t idx = x & 0x77777777u;
-    const uint32_t pick = ((x >> 1) & 0x44444444u) | 0x32103210u;
+    const uint32_t pick = mad_hi(x & 0x88888888u, 0x80000000u, 0x32103210u);   // ((x >> 1) & 0x4..4) | 0x3210..
     lo = prmt(prmt(T[0], T[1], idx), prmt(T[2], T[3], idx), pick);
-    hi = prmt(prmt(T[0], T[1], idx >> 16), prmt(T[2], T[3], idx >> 16), pick >> 16);
+    const uint32_t idx_h = mad_hi(idx, 0x10000u, 0u), pick_h = mad_hi(pick, 0x10000u, 0u);
+    hi = prmt(prmt(T[0], T[1], idx_h), prmt(T[2], T[3], idx_h), pick_h);
 }
 
 // K-major, 128-byte swizzle, 8-row groups 1024 B apart; version 1 (sm_100), base offset 0.

@@ -277,11 +277,19 @@ constexpr int kChunkRows = 64;                                // byte-group rows
 constexpr int kStageBytes = kConsumerWarps * kChunkRows * kLanes;
 constexpr int kStages = 4;
 
+// high 32 bits of a * b + c on the FMA pipe: a right shift that does not load the (saturated) ALU pipe
+__device__ __forceinline__ uint32_t mad_hi(uint32_t a, uint32_t b, uint32_t c) {
+    uint32_t d;
+    asm("mad.hi.u32 %0, %1, %2, %3;" : "=r"(d) : "r"(a), "r"(b), "r"(c));
+    return d;
+}
 __device__ __forceinline__ void expand4(uint32_t x, const uint32_t (&T)[4], uint32_t &b0, uint32_t &b1) {
     const uint32_t idx = x & 0x77777777u;                     // low three bits of every nibble
-    const uint32_t pick = ((x >> 1) & 0x44444444u) | 0x32103210u;   // byte i from the low or the high half-table
+    // byte i from the low or the high half-table: nibble i = i + 4 * (bit 3 of code i); (x & 8..8) >> 1 + 0x3210..
+    const uint32_t pick = mad_hi(x & 0x88888888u, 0x80000000u, 0x32103210u);
     b0 = prmt(prmt(T[0], T[1], idx), prmt(T[2], T[3], idx), pick);
-    b1 = prmt(prmt(T[0], T[1], idx >> 16), prmt(T[2], T[3], idx >> 16), pick >> 16);
+    const uint32_t idx_h = mad_hi(idx, 0x10000u, 0u), pick_h = mad_hi(pick, 0x10000u, 0u);   // >> 16
+    b1 = prmt(prmt(T[0], T[1], idx_h), prmt(T[2], T[3], idx_h), pick_h);
 }
 
 template <int MT>
