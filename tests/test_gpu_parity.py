@@ -376,12 +376,14 @@ def test_recall_at_10_matches_reference_floor(T):
 # ---------------------------------------------------------------- tcgen05 / TMEM scan
 @pytest.mark.parametrize("dim,n,nq", [(1536, 3000, 1), (1536, 5003, 70), (1536, 4100, 300), (256, 4100, 257), (200, 2000, 5),
                                       (64, 70000, 600)])
-def test_tensor_memory_scan_matches_oracle(T, dim, n, nq):
-    """The tcgen05 path (forced for every batch size) returns exactly what the oracle returns."""
+@pytest.mark.parametrize("tiles", [1, 2])
+def test_tensor_memory_scan_matches_oracle(T, dim, n, nq, tiles):
+    """The tcgen05 path (forced for every batch size, both work-item shapes) returns exactly what the oracle returns."""
     x = anisotropic(n, dim, seed=41)
     q = anisotropic(nq, dim, seed=41, offset=77)
     idx = _build(T, x, 4)
     idx.set_option(T.OPT_MMA_MIN_BATCH, 1)
+    idx.set_option(T.OPT_TC_TILES, tiles)
     for k in (1, 10, 100):
         s, i = idx.search(q, k)
         rs, ri = _oracle_search(x, q, 4, k)

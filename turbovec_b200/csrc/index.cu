@@ -90,6 +90,7 @@ struct tv_index {
     int score_mode = TV_SCORE_AUTO;
     int64_t mma_min_batch = 65;  // measured switch point: mma.sync covers 64 queries per pass, tcgen05 wins beyond
     int force_careful = 0;
+    int tc_tiles = 1;            // accumulator tiles per B slab in the tcgen05 scan (1 or 2); 1 measured faster
 
     cudaStream_t stream = nullptr;
     cudaEvent_t ev0 = nullptr, ev1 = nullptr;
@@ -555,7 +556,7 @@ int search_core(tv_index *h, const float *queries, bool queries_on_device, size_
             if (use_tc) {
                 sp.q_base = 0; sp.nq = int(nq); sp.mtile_base = 0;
                 mark_begin(h);
-                TV_CUDA(launch_scan_tc(sp, h->d_weights.ptr, int(w_rows), int(dim_pad), h->sm_count, st));
+                TV_CUDA(launch_scan_tc(sp, h->d_weights.ptr, int(w_rows), int(dim_pad), h->sm_count, h->tc_tiles, st));
                 mark_end(h);
                 h->launches++;
             } else if (mode == TV_SCORE_PERMUTE_DOT) {
@@ -779,6 +780,7 @@ int tv_set_option(tv_index *h, int option, int64_t value) {
             return TV_OK;
         case TV_OPT_MMA_MIN_BATCH: h->mma_min_batch = value; return TV_OK;
         case TV_OPT_FORCE_CAREFUL: h->force_careful = value != 0; return TV_OK;
+        case TV_OPT_TC_TILES: h->tc_tiles = value == 1 ? 1 : 2; return TV_OK;
         default: return fail(h, TV_ERR_INVALID_ARGUMENT, "unknown option");
     }
 }
@@ -789,6 +791,7 @@ int64_t tv_get_option(const tv_index *h, int option) {
         case TV_OPT_SCORE_MODE: return h->dim ? resolve_mode(h) : h->score_mode;
         case TV_OPT_MMA_MIN_BATCH: return h->mma_min_batch;
         case TV_OPT_FORCE_CAREFUL: return h->force_careful;
+        case TV_OPT_TC_TILES: return h->tc_tiles;
         default: return -1;
     }
 }

@@ -24,13 +24,12 @@
 namespace tv {
 namespace {
 
-constexpr int kTileVectors = 128;
-constexpr int kTileQueries = 256;
+constexpr int kMmaM = 128;                                    // vectors per accumulator tile (TMEM lanes)
+constexpr int kTileQueries = 256;                             // MMA N
 constexpr int kSlabK = 128;                                   // int8 elements (bytes) of K per stage
-constexpr int kStagesTc = 4;
-constexpr int kABytes = kTileVectors * kSlabK;                // 16 KB
+constexpr int kATileBytes = kMmaM * kSlabK;                   // 16 KB per accumulator tile and stage
 constexpr int kBBytes = kTileQueries * kSlabK;                // 32 KB
-constexpr int kStageBytesTc = kABytes + kBBytes;              // 48 KB
+constexpr int kMaxStageBytes = 2 * kATileBytes + kBBytes;     // 64 KB (two accumulator tiles)
 constexpr int kExpandWarps = 8;
 constexpr int kEpilogueWarps = 8;                             // two per TMEM lane quarter, 128 columns each
 constexpr int kThreadsTc = (2 + kEpilogueWarps + kExpandWarps) * 32;   // 576
@@ -94,7 +93,7 @@ __device__ __forceinline__ uint64_t umma_desc(uint32_t smem_byte_addr) {
 }
 // kind::i8: D = S32, A = B = signed 8-bit, both K-major, N = 256, M = 128.
 constexpr uint32_t kIdesc = (2u << 4) | (1u << 7) | (1u << 10) | (uint32_t(kTileQueries >> 3) << 17) |
-                            (uint32_t(kTileVectors >> 4) << 24);
+                            (uint32_t(kMmaM >> 4) << 24);
 
 __device__ __forceinline__ void umma_i8(uint32_t d_tmem, uint64_t a_desc, uint64_t b_desc, uint32_t accumulate) {
     asm volatile(
@@ -124,37 +123,53 @@ __device__ __forceinline__ void tmem_ld32(uint32_t taddr, uint32_t (&r)[32]) {
         : "r"(taddr));
 }
 
+__device__ __forceinline__ void tmem_ld8(uint32_t taddr, uint32_t (&r)[8]) {
+    asm volatile("tcgen05.ld.sync.aligned.32x32b.x8.b32 {%0, %1, %2, %3, %4, %5, %6, %7}, [%8];"
+                 : "=r"(r[0]), "=r"(r[1]), "=r"(r[2]), "=r"(r[3]), "=r"(r[4]), "=r"(r[5]), "=r"(r[6]), "=r"(r[7])
+                 : "r"(taddr));
+}
+
 struct TcShared {
-    uint64_t full[kStagesTc];      // stage filled: 8 expansion warps + the TMA transaction
-    uint64_t empty[kStagesTc];     // stage drained by the MMAs (tcgen05.commit)
+    uint64_t full[4];              // stage filled: 8 expansion warps + the TMA transaction
+    uint64_t empty[4];             // stage drained by the MMAs (tcgen05.commit)
     uint64_t d_full[2];            // accumulator buffer complete
-    uint64_t d_empty[2];           // accumulator buffer read out by the 4 epilogue warps
+    uint64_t d_empty[2];           // accumulator buffer read out by the epilogue warps
     uint32_t tmem_base;
     uint32_t pad[3];
-    // per-query parameters of an item, double buffered with the accumulators; 16-byte aligned for float4 loads
+    // per-query parameters of an item, double buffered; 16-byte aligned for float4 loads
     float qscale[2][kTileQueries];
     float qbias[2][kTileQueries];
     float qthr[2][kTileQueries];   // score of the current k-th key (-inf while fewer than k results exist)
 };
 static_assert(offsetof(TcShared, qscale) % 16 == 0, "parameter arrays must be 16-byte aligned");
 
+// MT = accumulator tiles (of 128 vectors) that share one B slab.  MT = 1: work item 128 x 256, four stages,
+// two accumulator buffers (the epilogue of an item overlaps the MMAs of the next).  MT = 2: work item
+// 256 x 256, three stages, both 256-column halves of TMEM hold one item — half the B traffic per
+// multiply-add, at the price of the MMA pipe idling while the epilogue drains the accumulators.
+template <int MT>
 __global__ void __launch_bounds__(kThreadsTc, 1)
 scan_tc_kernel(ScanParams p, const __grid_constant__ CUtensorMap wmap, int n_slabs, int n_qgroups) {
+    constexpr int kStages = MT == 1 ? 4 : 3;
+    constexpr int kABytes = MT * kATileBytes;
+    constexpr int kStageBytes = kABytes + kBBytes;
+    constexpr int kBufs = MT == 1 ? 2 : 1;                    // accumulator buffers
+    constexpr int kBlocksPerItem = 4 * MT;
     extern __shared__ __align__(1024) unsigned char smem_raw[];
     // stages first (1024-byte aligned for the swizzle), bookkeeping after them
     unsigned char *stages = reinterpret_cast<unsigned char *>((reinterpret_cast<uintptr_t>(smem_raw) + 1023) & ~uintptr_t(1023));
-    TcShared *sh = reinterpret_cast<TcShared *>(stages + size_t(kStagesTc) * kStageBytesTc);
+    TcShared *sh = reinterpret_cast<TcShared *>(stages + size_t(kStages) * kStageBytes);
 
     const int tid = threadIdx.x, warp = tid >> 5, lane = tid & 31;
     const int ng = p.ngroups;
     uint32_t pos_end = p.pos_end;
     if (p.live_blocks != nullptr) pos_end = min(pos_end, *p.n_live);
     const uint32_t pos_begin = min(p.pos_begin, pos_end);
-    const uint32_t n_vtiles = (pos_end - pos_begin + 3) / 4;
+    const uint32_t n_vtiles = (pos_end - pos_begin + kBlocksPerItem - 1) / kBlocksPerItem;
     const uint32_t n_items = n_vtiles * uint32_t(n_qgroups);
 
     if (tid == 0) {
-        for (int s = 0; s < kStagesTc; ++s) { mbar_init(&sh->full[s], kExpandWarps + 1); mbar_init(&sh->empty[s], 1); }
+        for (int s = 0; s < kStages; ++s) { mbar_init(&sh->full[s], kExpandWarps + 1); mbar_init(&sh->empty[s], 1); }
         for (int b = 0; b < 2; ++b) { mbar_init(&sh->d_full[b], 1); mbar_init(&sh->d_empty[b], kEpilogueWarps); }
         asm volatile("fence.mbarrier_init.release.cluster;" ::: "memory");
     }
@@ -166,21 +181,26 @@ scan_tc_kernel(ScanParams p, const __grid_constant__ CUtensorMap wmap, int n_sla
     __syncthreads();
     asm volatile("tcgen05.fence::after_thread_sync;" ::: "memory");
     const uint32_t tmem_base = sh->tmem_base;
+    // item -> (vector tile, query group), advanced without divisions
+    const uint32_t vt_step = gridDim.x / uint32_t(n_qgroups);
+    const int qg_step = int(gridDim.x % uint32_t(n_qgroups));
 
     if (warp == 0) {
         // ------------------------------------------------ TMA producer: query weights ------------
         if (lane == 0) {
             uint32_t it = 0;
+            int qg = int(blockIdx.x % uint32_t(n_qgroups));
             bool ok = true;
             for (uint32_t item = blockIdx.x; item < n_items && ok; item += gridDim.x) {
-                const int qg = int(item % uint32_t(n_qgroups));
                 for (int s = 0; s < n_slabs && ok; ++s, ++it) {
-                    const int st = it % kStagesTc;
-                    ok = mbar_wait(&sh->empty[st], ((it / kStagesTc) & 1) ^ 1, p.cb.error);
+                    const int st = it % kStages;
+                    ok = mbar_wait(&sh->empty[st], ((it / kStages) & 1) ^ 1, p.cb.error);
                     if (!ok) break;
                     mbar_arrive_expect_tx(&sh->full[st], kBBytes);
-                    tma_load_2d(stages + size_t(st) * kStageBytesTc + kABytes, &wmap, s * kSlabK, qg * kTileQueries, &sh->full[st]);
+                    tma_load_2d(stages + size_t(st) * kStageBytes + kABytes, &wmap, s * kSlabK, qg * kTileQueries, &sh->full[st]);
                 }
+                qg += qg_step;
+                if (qg >= n_qgroups) qg -= n_qgroups;
             }
         }
     } else if (warp == 1) {
@@ -189,21 +209,25 @@ scan_tc_kernel(ScanParams p, const __grid_constant__ CUtensorMap wmap, int n_sla
             uint32_t it = 0, local_item = 0;
             bool ok = true;
             for (uint32_t item = blockIdx.x; item < n_items && ok; item += gridDim.x, ++local_item) {
-                const int buf = local_item & 1;
-                ok = mbar_wait(&sh->d_empty[buf], ((local_item >> 1) & 1) ^ 1, p.cb.error);
+                const int buf = local_item % kBufs;
+                ok = mbar_wait(&sh->d_empty[buf], ((local_item / kBufs) & 1) ^ 1, p.cb.error);
                 if (!ok) break;
                 asm volatile("tcgen05.fence::after_thread_sync;" ::: "memory");
-                const uint32_t d_tmem = tmem_base + uint32_t(buf) * kTileQueries;
+                const uint32_t d_tmem = tmem_base + uint32_t(buf * MT) * kTileQueries;
                 for (int s = 0; s < n_slabs && ok; ++s, ++it) {
-                    const int st = it % kStagesTc;
-                    ok = mbar_wait(&sh->full[st], (it / kStagesTc) & 1, p.cb.error);
+                    const int st = it % kStages;
+                    ok = mbar_wait(&sh->full[st], (it / kStages) & 1, p.cb.error);
                     if (!ok) break;
                     asm volatile("tcgen05.fence::after_thread_sync;" ::: "memory");
-                    const uint32_t a_addr = smem_u32(stages + size_t(st) * kStageBytesTc);
+                    const uint32_t a_addr = smem_u32(stages + size_t(st) * kStageBytes);
                     const uint32_t b_addr = a_addr + kABytes;
 #pragma unroll
-                    for (int k = 0; k < kSlabK / 32; ++k)
-                        umma_i8(d_tmem, umma_desc(a_addr + k * 32), umma_desc(b_addr + k * 32), (s | k) != 0);
+                    for (int k = 0; k < kSlabK / 32; ++k) {
+                        const uint64_t bd = umma_desc(b_addr + k * 32);
+#pragma unroll
+                        for (int m = 0; m < MT; ++m)
+                            umma_i8(d_tmem + uint32_t(m) * kTileQueries, umma_desc(a_addr + m * kATileBytes + k * 32), bd, (s | k) != 0);
+                    }
                     umma_commit(&sh->empty[st]);          // the stage may be refilled once these MMAs have read it
                 }
                 if (ok) umma_commit(&sh->d_full[buf]);
@@ -213,16 +237,13 @@ scan_tc_kernel(ScanParams p, const __grid_constant__ CUtensorMap wmap, int n_sla
         // ------------------------------------------------ epilogue -------------------------------
         const int quarter = warp & 3;                     // TMEM lanes 32*quarter .. +31 are this warp's
         const int half = (warp - 2) >> 2;                 // which 128 of the item's 256 query columns
-        const int row = quarter * 32 + lane;              // vector within the tile
         const int et = (warp - 2) * 32 + lane;            // 0..255 among the epilogue threads
         uint32_t local_item = 0;
         uint32_t vt = blockIdx.x / uint32_t(n_qgroups);
         int qg = int(blockIdx.x % uint32_t(n_qgroups));
-        const uint32_t vt_step = gridDim.x / uint32_t(n_qgroups);
-        const int qg_step = int(gridDim.x % uint32_t(n_qgroups));
         bool ok = true;
         for (uint32_t item = blockIdx.x; item < n_items && ok; item += gridDim.x, ++local_item) {
-            const int buf = local_item & 1;
+            const int buf = local_item % kBufs, pb = local_item & 1;
             // per-query parameters of this item: one query per epilogue thread
             {
                 const int ql = qg * kTileQueries + et;
@@ -232,44 +253,71 @@ scan_tc_kernel(ScanParams p, const __grid_constant__ CUtensorMap wmap, int n_sla
                     const uint64_t key = p.cb.thr[ql];
                     th = key == kEmptyKey ? -INFINITY : desc_bits_to_score(uint32_t(key >> 32));
                 }
-                sh->qscale[buf][et] = qs; sh->qbias[buf][et] = qb; sh->qthr[buf][et] = th;
+                sh->qscale[pb][et] = qs; sh->qbias[pb][et] = qb; sh->qthr[pb][et] = th;
             }
             asm volatile("bar.sync 1, %0;" ::"r"(kEpilogueWarps * 32) : "memory");
-            const uint32_t pos = pos_begin + vt * 4 + uint32_t(row >> 5);
-            const bool have = pos < pos_end;
-            uint32_t blk = 0;
-            if (have) blk = p.live_blocks ? p.live_blocks[pos] : pos;
-            const int64_t slot = int64_t(blk) * 32 + (row & 31);
-            bool live = have && slot < p.n;
-            if (live && p.mask) live = (p.mask[slot >> 6] >> (slot & 63)) & 1ull;
-            const float vs = live ? p.vec_scales[slot] : 0.0f;
+            int64_t slot[MT];
+            float vs[MT];
+            bool live[MT];
+#pragma unroll
+            for (int m = 0; m < MT; ++m) {
+                const int row = m * kMmaM + quarter * 32 + lane;        // vector within the item
+                const uint32_t pos = pos_begin + vt * kBlocksPerItem + uint32_t(row >> 5);
+                const bool have = pos < pos_end;
+                uint32_t blk = 0;
+                if (have) blk = p.live_blocks ? p.live_blocks[pos] : pos;
+                slot[m] = int64_t(blk) * 32 + (row & 31);
+                live[m] = have && slot[m] < p.n;
+                if (live[m] && p.mask) live[m] = (p.mask[slot[m] >> 6] >> (slot[m] & 63)) & 1ull;
+                vs[m] = live[m] ? p.vec_scales[slot[m]] : 0.0f;
+            }
 
-            ok = mbar_wait(&sh->d_full[buf], (local_item >> 1) & 1, p.cb.error);
+            ok = mbar_wait(&sh->d_full[buf], (local_item / kBufs) & 1, p.cb.error);
             if (!ok) break;
             asm volatile("tcgen05.fence::after_thread_sync;" ::: "memory");
             const int cbase = half * (kTileQueries / 2);
-            const uint32_t taddr = tmem_base + (uint32_t(quarter * 32) << 16) + uint32_t(buf) * kTileQueries + uint32_t(cbase);
-            const float4 *ps = reinterpret_cast<const float4 *>(&sh->qscale[buf][cbase]);
-            const float4 *pb = reinterpret_cast<const float4 *>(&sh->qbias[buf][cbase]);
-            const float4 *pt = reinterpret_cast<const float4 *>(&sh->qthr[buf][cbase]);
-            for (int c0 = 0; c0 < kTileQueries / 2; c0 += 32) {
-                uint32_t acc[32];
-                tmem_ld32(taddr + c0, acc);
-                asm volatile("tcgen05.wait::ld.sync.aligned;" ::: "memory");
-                if (live) {
+            const float4 *ps = reinterpret_cast<const float4 *>(&sh->qscale[pb][cbase]);
+            const float4 *pbias = reinterpret_cast<const float4 *>(&sh->qbias[pb][cbase]);
+            const float4 *pt = reinterpret_cast<const float4 *>(&sh->qthr[pb][cbase]);
+#pragma unroll
+            for (int m = 0; m < MT; ++m) {
+                const uint32_t taddr = tmem_base + (uint32_t(quarter * 32) << 16) + uint32_t(buf * MT + m) * kTileQueries + uint32_t(cbase);
+                for (int c0 = 0; c0 < kTileQueries / 2; c0 += 32) {
+                    uint32_t acc[32];
+                    tmem_ld32(taddr + c0, acc);
+                    asm volatile("tcgen05.wait::ld.sync.aligned;" ::: "memory");
+                    // hot loop: four instructions per score, the comparison folded into one predicate
+                    bool any = false;
 #pragma unroll
                     for (int j4 = 0; j4 < 8; ++j4) {
-                        const float4 s4 = ps[(c0 >> 2) + j4], b4 = pb[(c0 >> 2) + j4], t4 = pt[(c0 >> 2) + j4];
-                        const float sc[4] = {s4.x, s4.y, s4.z, s4.w}, bi[4] = {b4.x, b4.y, b4.z, b4.w}, th[4] = {t4.x, t4.y, t4.z, t4.w};
+                        const float4 s4 = ps[(c0 >> 2) + j4], b4 = pbias[(c0 >> 2) + j4], t4 = pt[(c0 >> 2) + j4];
+                        any |= __fmul_rn(fmaf(float(int(acc[4 * j4 + 0])), s4.x, b4.x), vs[m]) >= t4.x;
+                        any |= __fmul_rn(fmaf(float(int(acc[4 * j4 + 1])), s4.y, b4.y), vs[m]) >= t4.y;
+                        any |= __fmul_rn(fmaf(float(int(acc[4 * j4 + 2])), s4.z, b4.z), vs[m]) >= t4.z;
+                        any |= __fmul_rn(fmaf(float(int(acc[4 * j4 + 3])), s4.w, b4.w), vs[m]) >= t4.w;
+                    }
+                    any = any && live[m];
+                    // rare, warp-uniform: some lane has a score at or above its query's k-th score.  Re-read the
+                    // 32 columns in pieces of 8 and append the keys that really beat the k-th key.
+                    if (__any_sync(kFullMask, any)) {
+#pragma unroll 1
+                        for (int c1 = 0; c1 < 32; c1 += 8) {
+                            uint32_t a8[8];
+                            tmem_ld8(taddr + c0 + c1, a8);
+                            asm volatile("tcgen05.wait::ld.sync.aligned;" ::: "memory");
+                            if (any) {
 #pragma unroll
-                        for (int e = 0; e < 4; ++e) {
-                            const float score = __fmul_rn(fmaf(float(int(acc[4 * j4 + e])), sc[e], bi[e]), vs);
-                            if (score >= th[e]) {         // rare: exact key comparison and append
-                                const int ql = qg * kTileQueries + cbase + c0 + 4 * j4 + e;
-                                const uint64_t key = make_key(score, uint32_t(slot));
-                                if (key < p.cb.thr[ql]) {
-                                    const uint32_t at = atomicAdd(&p.cb.cnt[ql], 1u);
-                                    if (at < uint32_t(p.cb.cap)) p.cb.cand[size_t(ql) * p.cb.cap + at] = key;
+                                for (int e = 0; e < 8; ++e) {
+                                    const int c = cbase + c0 + c1 + e;
+                                    const float score = __fmul_rn(fmaf(float(int(a8[e])), sh->qscale[pb][c], sh->qbias[pb][c]), vs[m]);
+                                    if (score >= sh->qthr[pb][c]) {
+                                        const int ql = qg * kTileQueries + c;
+                                        const uint64_t key = make_key(score, uint32_t(slot[m]));
+                                        if (key < p.cb.thr[ql]) {
+                                            const uint32_t at = atomicAdd(&p.cb.cnt[ql], 1u);
+                                            if (at < uint32_t(p.cb.cap)) p.cb.cand[size_t(ql) * p.cb.cap + at] = key;
+                                        }
+                                    }
                                 }
                             }
                         }
@@ -284,42 +332,40 @@ scan_tc_kernel(ScanParams p, const __grid_constant__ CUtensorMap wmap, int n_sla
         }
     } else {
         // ------------------------------------------------ expansion: codes -> int8 A slabs -------
-        // The (item, slab) pairs of this CTA form one flat sequence; the code words of four slabs ahead are
-        // kept in flight in registers so that global-load latency never reaches the expansion itself.
+        // The (item, slab) pairs of this CTA form one flat sequence; the code words of the next kAhead slabs
+        // are kept in flight in registers so that global-load latency never reaches the expansion itself.
+        // A unit = 4 vectors (one 32-bit column of a code block) x 8 byte-groups (one 16-byte chunk of a row).
+        constexpr int kUnits = MT;                        // units per thread and slab
+        constexpr int kAhead = MT == 1 ? 4 : 3;
         const int ew = warp - (2 + kEpilogueWarps);       // 0..7
         const int octet = lane & 7;                       // which 8-group run of the slab = 16-byte chunk index
-        const int blk_in_tile = ew >> 1;
-        const int quad = (ew & 1) * 4 + (lane >> 3);      // 4 vectors 4*quad .. 4*quad+3 of the block
-        const int row0 = blk_in_tile * 32 + quad * 4;
+        const int blk_in_item = MT == 1 ? (ew >> 1) : ew;
+        const int quad0 = (MT == 1 ? (ew & 1) * 4 : 0) + (lane >> 3);   // unit u handles quad0 + 4u
         const uint32_t T[4] = {p.level_words[0], p.level_words[1], p.level_words[2], p.level_words[3]};
         const uint32_t my_items = blockIdx.x < n_items ? (n_items - blockIdx.x + gridDim.x - 1) / gridDim.x : 0;
         const uint32_t total = my_items * uint32_t(n_slabs);
-        constexpr int kAhead = 4;
-        uint32_t w[kAhead][8];
-        // fetch cursor: walks the same (item, slab) sequence as the consumers, without divisions
+        uint32_t w[kAhead][kUnits][8];
+        // fetch cursor: walks the same (item, slab) sequence as the consumers
         uint32_t f_item = blockIdx.x, f_vt = blockIdx.x / uint32_t(n_qgroups);
         int f_qg = int(blockIdx.x % uint32_t(n_qgroups)), f_slab = 0;
-        const uint32_t vt_step = gridDim.x / uint32_t(n_qgroups);
-        const int qg_step = int(gridDim.x % uint32_t(n_qgroups));
         const uint32_t *f_src = nullptr;
         bool f_have = false;
-        auto fetch = [&](uint32_t (&dst)[8]) {
+        auto fetch = [&](uint32_t (&dst)[kUnits][8]) {
             if (f_slab == 0) {                            // first slab of an item: locate its code block
-                const uint32_t pos = pos_begin + f_vt * 4 + uint32_t(blk_in_tile);
+                const uint32_t pos = pos_begin + f_vt * kBlocksPerItem + uint32_t(blk_in_item);
                 f_have = f_item < n_items && pos < pos_end;
                 uint32_t blk = 0;
                 if (f_have) blk = p.live_blocks ? p.live_blocks[pos] : pos;
-                f_src = reinterpret_cast<const uint32_t *>(p.codes + size_t(blk) * ng * 32) + quad;
+                f_src = reinterpret_cast<const uint32_t *>(p.codes + size_t(blk) * ng * 32) + quad0;
             }
             const int g0 = f_slab * (kSlabK / 2) + octet * 8;
             const uint32_t *src = f_src + size_t(g0) * 8;
-            if (f_have && g0 + 8 <= ng) {
+            const bool whole = f_have && g0 + 8 <= ng;
 #pragma unroll
-                for (int r = 0; r < 8; ++r) dst[r] = __ldg(src + r * 8);
-            } else {
+            for (int u = 0; u < kUnits; ++u)
 #pragma unroll
-                for (int r = 0; r < 8; ++r) dst[r] = (f_have && g0 + r < ng) ? __ldg(src + r * 8) : 0u;
-            }
+                for (int r = 0; r < 8; ++r)
+                    dst[u][r] = (whole || (f_have && g0 + r < ng)) ? __ldg(src + r * 8 + u * 4) : 0u;
             if (++f_slab == n_slabs) {
                 f_slab = 0;
                 f_item += gridDim.x; f_vt += vt_step; f_qg += qg_step;
@@ -327,37 +373,44 @@ scan_tc_kernel(ScanParams p, const __grid_constant__ CUtensorMap wmap, int n_sla
             }
         };
 #pragma unroll
-        for (int u = 0; u < kAhead; ++u) fetch(w[u]);
+        for (int a = 0; a < kAhead; ++a) fetch(w[a]);
         bool ok = true;
         for (uint32_t f0 = 0; f0 < total && ok; f0 += kAhead) {
 #pragma unroll
-            for (int u = 0; u < kAhead; ++u) {
-                const uint32_t f = f0 + uint32_t(u);
+            for (int a = 0; a < kAhead; ++a) {
+                const uint32_t f = f0 + uint32_t(a);
                 if (f >= total || !ok) break;
-                const int st = f % kStagesTc;
-                // 4x4 byte transposes: bytes of vector row0+j in groups g0..g0+3 (xlo) and g0+4..g0+7 (xhi)
-                const uint32_t t0 = prmt(w[u][0], w[u][1], 0x5140), t1 = prmt(w[u][0], w[u][1], 0x7362);
-                const uint32_t t2 = prmt(w[u][2], w[u][3], 0x5140), t3 = prmt(w[u][2], w[u][3], 0x7362);
-                const uint32_t u0 = prmt(w[u][4], w[u][5], 0x5140), u1 = prmt(w[u][4], w[u][5], 0x7362);
-                const uint32_t u2 = prmt(w[u][6], w[u][7], 0x5140), u3 = prmt(w[u][6], w[u][7], 0x7362);
-                const uint32_t xlo[4] = {prmt(t0, t2, 0x5410), prmt(t0, t2, 0x7632), prmt(t1, t3, 0x5410), prmt(t1, t3, 0x7632)};
-                const uint32_t xhi[4] = {prmt(u0, u2, 0x5410), prmt(u0, u2, 0x7632), prmt(u1, u3, 0x5410), prmt(u1, u3, 0x7632)};
-                fetch(w[u]);                              // refill this ring slot (slab f + kAhead)
-                uint4 v[4];
+                const int st = f % kStages;
+                uint4 v[kUnits][4];
 #pragma unroll
-                for (int j = 0; j < 4; ++j) {
-                    expand8(xlo[j], T, v[j].x, v[j].y);
-                    expand8(xhi[j], T, v[j].z, v[j].w);
+                for (int u = 0; u < kUnits; ++u) {
+                    // 4x4 byte transposes: bytes of vector j of the unit in groups g0..g0+3 (xlo) and g0+4..g0+7 (xhi)
+                    const uint32_t *x = w[a][u];
+                    const uint32_t t0 = prmt(x[0], x[1], 0x5140), t1 = prmt(x[0], x[1], 0x7362);
+                    const uint32_t t2 = prmt(x[2], x[3], 0x5140), t3 = prmt(x[2], x[3], 0x7362);
+                    const uint32_t u0 = prmt(x[4], x[5], 0x5140), u1 = prmt(x[4], x[5], 0x7362);
+                    const uint32_t u2 = prmt(x[6], x[7], 0x5140), u3 = prmt(x[6], x[7], 0x7362);
+                    const uint32_t xlo[4] = {prmt(t0, t2, 0x5410), prmt(t0, t2, 0x7632), prmt(t1, t3, 0x5410), prmt(t1, t3, 0x7632)};
+                    const uint32_t xhi[4] = {prmt(u0, u2, 0x5410), prmt(u0, u2, 0x7632), prmt(u1, u3, 0x5410), prmt(u1, u3, 0x7632)};
+#pragma unroll
+                    for (int j = 0; j < 4; ++j) {
+                        expand8(xlo[j], T, v[u][j].x, v[u][j].y);
+                        expand8(xhi[j], T, v[u][j].z, v[u][j].w);
+                    }
                 }
-                ok = mbar_wait(&sh->empty[st], ((f / kStagesTc) & 1) ^ 1, p.cb.error);
+                fetch(w[a]);                              // refill this ring slot (slab f + kAhead)
+                ok = mbar_wait(&sh->empty[st], ((f / kStages) & 1) ^ 1, p.cb.error);
                 if (!ok) break;
-                unsigned char *a_stage = stages + size_t(st) * kStageBytesTc;
+                unsigned char *a_stage = stages + size_t(st) * kStageBytes;
 #pragma unroll
-                for (int j = 0; j < 4; ++j) {
-                    const int row = row0 + j;
-                    // 128-byte swizzle: 16-byte chunk c of row r sits at chunk position c ^ (r % 8)
-                    *reinterpret_cast<uint4 *>(a_stage + (row >> 3) * 1024 + (row & 7) * 128 + ((octet ^ (row & 7)) << 4)) = v[j];
-                }
+                for (int u = 0; u < kUnits; ++u)
+#pragma unroll
+                    for (int j = 0; j < 4; ++j) {
+                        const int row = blk_in_item * 32 + (quad0 + 4 * u) * 4 + j;   // vector within the item
+                        const int r = row & (kMmaM - 1);
+                        // accumulator tile row>>7; 128-byte swizzle: 16-byte chunk c of row r sits at chunk position c ^ (r % 8)
+                        *reinterpret_cast<uint4 *>(a_stage + (row >> 7) * kATileBytes + (r >> 3) * 1024 + (r & 7) * 128 + ((octet ^ (r & 7)) << 4)) = v[u][j];
+                    }
                 asm volatile("fence.proxy.async.shared::cta;" ::: "memory");   // generic writes -> visible to the MMA
                 __syncwarp();
                 if (lane == 0) mbar_arrive(&sh->full[st]);
@@ -391,13 +444,15 @@ EncodeTiledFn encode_fn() {
 
 }  // namespace
 
-size_t scan_tc_smem_bytes() { return size_t(kStagesTc) * kStageBytesTc + sizeof(TcShared) + 1024; }
+size_t scan_tc_smem_bytes() { return size_t(4) * (kATileBytes + kBBytes) + sizeof(TcShared) + 1024; }   // = 3 * 64 KB too
 
 bool scan_tc_supported(int bits, int mode) { return bits == 4 && mode == kModePermuteDot && encode_fn() != nullptr; }
 
 // weights: [rows][pitch] int8, pitch a multiple of 128, rows a multiple of 256, coordinates pair-swapped
 // (byte 2g = coordinate 2g+1, byte 2g+1 = coordinate 2g) to match the nibble order of a code byte.
-cudaError_t launch_scan_tc(const ScanParams &p, const int8_t *weights, int rows, int pitch, int sm_count, cudaStream_t s) {
+// tiles_per_item: 1 or 2 accumulator tiles of 128 vectors per B slab (see the kernel).
+cudaError_t launch_scan_tc(const ScanParams &p, const int8_t *weights, int rows, int pitch, int sm_count, int tiles_per_item,
+                           cudaStream_t s) {
     if (p.nq <= 0 || p.pos_end <= p.pos_begin) return cudaSuccess;
     EncodeTiledFn enc = encode_fn();
     if (!enc) return cudaErrorNotSupported;
@@ -415,17 +470,20 @@ cudaError_t launch_scan_tc(const ScanParams &p, const int8_t *weights, int rows,
     const size_t smem = scan_tc_smem_bytes();
     static bool attr_set = false;
     if (!attr_set) {
-        cudaError_t e = cudaFuncSetAttribute(scan_tc_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, int(smem));
+        cudaError_t e = cudaFuncSetAttribute(scan_tc_kernel<1>, cudaFuncAttributeMaxDynamicSharedMemorySize, int(smem));
+        if (e == cudaSuccess) e = cudaFuncSetAttribute(scan_tc_kernel<2>, cudaFuncAttributeMaxDynamicSharedMemorySize, int(smem));
         if (e != cudaSuccess) return e;
         attr_set = true;
     }
-    const uint32_t vtiles = (p.pos_end - p.pos_begin + 3) / 4;
+    const int mt = tiles_per_item == 2 ? 2 : 1;
+    const uint32_t vtiles = (p.pos_end - p.pos_begin + 4 * mt - 1) / (4 * mt);
     const uint64_t items = uint64_t(vtiles) * n_qgroups;
     // a multiple of the query-group count keeps the CTAs that share a vector tile in step (codes hit L2)
     unsigned grid = unsigned(sm_count - sm_count % n_qgroups);
     if (grid == 0) grid = unsigned(sm_count);
     if (items < grid) grid = unsigned(items);
-    scan_tc_kernel<<<grid, kThreadsTc, smem, s>>>(p, map, n_slabs, n_qgroups);
+    if (mt == 2) scan_tc_kernel<2><<<grid, kThreadsTc, smem, s>>>(p, map, n_slabs, n_qgroups);
+    else scan_tc_kernel<1><<<grid, kThreadsTc, smem, s>>>(p, map, n_slabs, n_qgroups);
     return cudaGetLastError();
 }
 

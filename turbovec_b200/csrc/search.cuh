@@ -89,7 +89,8 @@ cudaError_t launch_scan_pd(const ScanParams &p, int sm_count, cudaStream_t s);
 // Permute-dot scan on tcgen05 tensor cores with TMEM accumulators (scan_tc.cu); all queries in one launch.
 // weights: [rows][pitch] int8 with rows % 256 == 0, pitch % 128 == 0, adjacent coordinates swapped.
 bool scan_tc_supported(int bits, int mode);
-cudaError_t launch_scan_tc(const ScanParams &p, const int8_t *weights, int rows, int pitch, int sm_count, cudaStream_t s);
+cudaError_t launch_scan_tc(const ScanParams &p, const int8_t *weights, int rows, int pitch, int sm_count,
+                           int tiles_per_item, cudaStream_t s);
 // LUT scan on CUDA cores, up to kLutQueriesPerLaunch queries per launch.
 constexpr int kLutQueriesPerLaunch = 4;
 cudaError_t launch_scan_lut(const ScanParams &p, int sm_count, cudaStream_t s);
