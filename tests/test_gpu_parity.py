@@ -393,3 +393,23 @@ def test_tensor_memory_scan_matches_oracle(T, dim, n, nq, tiles):
     s, i = idx.search(q, 10, mask=mask)
     rs, ri = _oracle_search(x, q, 4, 10, mask=mask)
     assert np.array_equal(i, ri) and np.array_equal(s, rs)
+
+
+@pytest.mark.parametrize("dim,bits,n,nq", [(1536, 2, 3000, 9), (3072, 2, 1500, 300), (1024, 3, 1500, 70), (256, 4, 4100, 33),
+                                           (64, 2, 40000, 513)])
+def test_tensor_memory_lut_scan_matches_oracle(T, dim, bits, n, nq):
+    """The u8-LUT scan as a one-hot int8 contraction on tcgen05 returns exactly the oracle's LUT results."""
+    x = anisotropic(n, dim, seed=43)
+    q = anisotropic(nq, dim, seed=43, offset=7)
+    idx = _build(T, x, bits)
+    idx.set_option(T.OPT_SCORE_MODE, T.SCORE_LUT_MULADD)
+    idx.set_option(T.OPT_MMA_MIN_BATCH, 1)
+    for k in (1, 10, 100):
+        s, i = idx.search(q, k)
+        rs, ri = _oracle_search(x, q, bits, k, mode=O.MODE_LUT_MULADD)
+        assert np.array_equal(i, ri), f"k={k}: id lists differ"
+        assert np.array_equal(s, rs), f"k={k}: scores differ"
+    mask = np.random.default_rng(5).random(n) < 0.05
+    s, i = idx.search(q, 10, mask=mask)
+    rs, ri = _oracle_search(x, q, bits, 10, mask=mask, mode=O.MODE_LUT_MULADD)
+    assert np.array_equal(i, ri) and np.array_equal(s, rs)

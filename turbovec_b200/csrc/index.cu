@@ -443,13 +443,12 @@ int search_core(tv_index *h, const float *queries, bool queries_on_device, size_
     TV_CUDA(h->d_qscale.reserve(nq_pad));
     TV_CUDA(h->d_qbias.reserve(nq_pad));
     const size_t w_rows = (nq + 255) / 256 * 256;
-    const bool use_tc = mode == TV_SCORE_PERMUTE_DOT && h->mma_min_batch > 0 && int64_t(nq) >= h->mma_min_batch &&
-                        scan_tc_supported(h->bits, mode);
+    const bool use_tc = h->mma_min_batch > 0 && int64_t(nq) >= h->mma_min_batch && scan_tc_supported(h->bits, mode, ng);
     if (mode == TV_SCORE_PERMUTE_DOT) {
         TV_CUDA(h->d_weights.reserve(w_rows * dim_pad));
         TV_CUDA(h->d_wfrag.reserve(size_t(ksteps) * mt_total * 32 * 4));
     } else {
-        TV_CUDA(h->d_luts.reserve(nq * size_t(ng) * 32));
+        TV_CUDA(h->d_luts.reserve(w_rows * size_t(ng) * 32));     // padded to whole query groups for the tensor path
     }
     TV_CUDA(h->d_cand.reserve(nq * size_t(cap)));
     TV_CUDA(h->d_cnt.reserve(nq));
@@ -518,6 +517,8 @@ int search_core(tv_index *h, const float *queries, bool queries_on_device, size_
     if (mode == TV_SCORE_PERMUTE_DOT) {
         TV_CUDA(cudaMemsetAsync(h->d_wfrag.ptr, 0, size_t(ksteps) * mt_total * 32 * 16, st));
         if (use_tc) TV_CUDA(cudaMemsetAsync(h->d_weights.ptr, 0, w_rows * dim_pad, st));
+    } else if (use_tc) {
+        TV_CUDA(cudaMemsetAsync(h->d_luts.ptr, 0, w_rows * size_t(ng) * 32, st));
     }
     TV_CUDA(launch_query_prep(qp, st));
     h->launches++;
@@ -556,7 +557,10 @@ int search_core(tv_index *h, const float *queries, bool queries_on_device, size_
             if (use_tc) {
                 sp.q_base = 0; sp.nq = int(nq); sp.mtile_base = 0;
                 mark_begin(h);
-                TV_CUDA(launch_scan_tc(sp, h->d_weights.ptr, int(w_rows), int(dim_pad), h->sm_count, h->tc_tiles, st));
+                if (mode == TV_SCORE_PERMUTE_DOT)
+                    TV_CUDA(launch_scan_tc(sp, h->d_weights.ptr, int(w_rows), int(dim_pad), h->sm_count, h->tc_tiles, st));
+                else
+                    TV_CUDA(launch_scan_tc(sp, reinterpret_cast<const int8_t *>(h->d_luts.ptr), int(w_rows), ng * 32, h->sm_count, 1, st));
                 mark_end(h);
                 h->launches++;
             } else if (mode == TV_SCORE_PERMUTE_DOT) {

@@ -129,6 +129,14 @@ __device__ __forceinline__ void tmem_ld8(uint32_t taddr, uint32_t (&r)[8]) {
                  : "r"(taddr));
 }
 
+// Float epilogue of the two score families; the integer sum is exact in both.
+template <bool ONEHOT>
+__device__ __forceinline__ float final_score(uint32_t isum, float qs, float qb, float vs) {
+    const float f = float(int(isum));
+    if constexpr (ONEHOT) return __fmul_rn(__fadd_rn(__fmul_rn(f, qs), qb), vs);   // search.rs:1176, then x vec_scale
+    else return __fmul_rn(fmaf(f, qs, qb), vs);                                    // search.rs:1523, 1793
+}
+
 struct TcShared {
     uint64_t full[4];              // stage filled: 8 expansion warps + the TMA transaction
     uint64_t empty[4];             // stage drained by the MMAs (tcgen05.commit)
@@ -143,11 +151,17 @@ struct TcShared {
 };
 static_assert(offsetof(TcShared, qscale) % 16 == 0, "parameter arrays must be 16-byte aligned");
 
+// ONEHOT = false: permute-dot.  A rows hold the int8 levels of the codes, B rows the int8 query weights
+// (K = dim).  ONEHOT = true: the u8-LUT scan as a contraction (K = 32 * ngroups): A rows hold, per
+// byte-group, a one-hot of the high nibble (16 bytes) then a one-hot of the low nibble (16 bytes); B rows are
+// the per-query u8 tables exactly as query preparation lays them out ([g][hi 16 | lo 16], entries <= 127),
+// so the int32 accumulator is the reference's integer LUT sum (search.rs:1071-1195) and the epilogue applies
+// (f32)isum * scale + bias (search.rs:1176).
 // MT = accumulator tiles (of 128 vectors) that share one B slab.  MT = 1: work item 128 x 256, four stages,
 // two accumulator buffers (the epilogue of an item overlaps the MMAs of the next).  MT = 2: work item
 // 256 x 256, three stages, both 256-column halves of TMEM hold one item — half the B traffic per
 // multiply-add, at the price of the MMA pipe idling while the epilogue drains the accumulators.
-template <int MT>
+template <int MT, bool ONEHOT>
 __global__ void __launch_bounds__(kThreadsTc, 1)
 scan_tc_kernel(ScanParams p, const __grid_constant__ CUtensorMap wmap, int n_slabs, int n_qgroups) {
     constexpr int kStages = MT == 1 ? 4 : 3;
@@ -291,10 +305,10 @@ scan_tc_kernel(ScanParams p, const __grid_constant__ CUtensorMap wmap, int n_sla
 #pragma unroll
                     for (int j4 = 0; j4 < 8; ++j4) {
                         const float4 s4 = ps[(c0 >> 2) + j4], b4 = pbias[(c0 >> 2) + j4], t4 = pt[(c0 >> 2) + j4];
-                        any |= __fmul_rn(fmaf(float(int(acc[4 * j4 + 0])), s4.x, b4.x), vs[m]) >= t4.x;
-                        any |= __fmul_rn(fmaf(float(int(acc[4 * j4 + 1])), s4.y, b4.y), vs[m]) >= t4.y;
-                        any |= __fmul_rn(fmaf(float(int(acc[4 * j4 + 2])), s4.z, b4.z), vs[m]) >= t4.z;
-                        any |= __fmul_rn(fmaf(float(int(acc[4 * j4 + 3])), s4.w, b4.w), vs[m]) >= t4.w;
+                        any |= final_score<ONEHOT>(acc[4 * j4 + 0], s4.x, b4.x, vs[m]) >= t4.x;
+                        any |= final_score<ONEHOT>(acc[4 * j4 + 1], s4.y, b4.y, vs[m]) >= t4.y;
+                        any |= final_score<ONEHOT>(acc[4 * j4 + 2], s4.z, b4.z, vs[m]) >= t4.z;
+                        any |= final_score<ONEHOT>(acc[4 * j4 + 3], s4.w, b4.w, vs[m]) >= t4.w;
                     }
                     any = any && live[m];
                     // rare, warp-uniform: some lane has a score at or above its query's k-th score.  Re-read the
@@ -309,7 +323,7 @@ scan_tc_kernel(ScanParams p, const __grid_constant__ CUtensorMap wmap, int n_sla
 #pragma unroll
                                 for (int e = 0; e < 8; ++e) {
                                     const int c = cbase + c0 + c1 + e;
-                                    const float score = __fmul_rn(fmaf(float(int(a8[e])), sh->qscale[pb][c], sh->qbias[pb][c]), vs[m]);
+                                    const float score = final_score<ONEHOT>(a8[e], sh->qscale[pb][c], sh->qbias[pb][c], vs[m]);
                                     if (score >= sh->qthr[pb][c]) {
                                         const int ql = qg * kTileQueries + c;
                                         const uint64_t key = make_key(score, uint32_t(slot[m]));
@@ -344,13 +358,14 @@ scan_tc_kernel(ScanParams p, const __grid_constant__ CUtensorMap wmap, int n_sla
         const uint32_t T[4] = {p.level_words[0], p.level_words[1], p.level_words[2], p.level_words[3]};
         const uint32_t my_items = blockIdx.x < n_items ? (n_items - blockIdx.x + gridDim.x - 1) / gridDim.x : 0;
         const uint32_t total = my_items * uint32_t(n_slabs);
-        uint32_t w[kAhead][kUnits][8];
+        constexpr int kWords = ONEHOT ? 1 : 8;            // code words per unit and slab
+        uint32_t w[kAhead][kUnits][kWords];
         // fetch cursor: walks the same (item, slab) sequence as the consumers
         uint32_t f_item = blockIdx.x, f_vt = blockIdx.x / uint32_t(n_qgroups);
         int f_qg = int(blockIdx.x % uint32_t(n_qgroups)), f_slab = 0;
         const uint32_t *f_src = nullptr;
         bool f_have = false;
-        auto fetch = [&](uint32_t (&dst)[kUnits][8]) {
+        auto fetch = [&](uint32_t (&dst)[kUnits][kWords]) {
             if (f_slab == 0) {                            // first slab of an item: locate its code block
                 const uint32_t pos = pos_begin + f_vt * kBlocksPerItem + uint32_t(blk_in_item);
                 f_have = f_item < n_items && pos < pos_end;
@@ -358,14 +373,21 @@ scan_tc_kernel(ScanParams p, const __grid_constant__ CUtensorMap wmap, int n_sla
                 if (f_have) blk = p.live_blocks ? p.live_blocks[pos] : pos;
                 f_src = reinterpret_cast<const uint32_t *>(p.codes + size_t(blk) * ng * 32) + quad0;
             }
-            const int g0 = f_slab * (kSlabK / 2) + octet * 8;
-            const uint32_t *src = f_src + size_t(g0) * 8;
-            const bool whole = f_have && g0 + 8 <= ng;
+            if constexpr (ONEHOT) {
+                // a slab is 4 byte-groups x 32 table entries; chunk `octet` = group octet/2, nibble octet%2
+                const int g = f_slab * 4 + (octet >> 1);
 #pragma unroll
-            for (int u = 0; u < kUnits; ++u)
+                for (int u = 0; u < kUnits; ++u) dst[u][0] = (f_have && g < ng) ? __ldg(f_src + size_t(g) * 8 + u * 4) : 0u;
+            } else {
+                const int g0 = f_slab * (kSlabK / 2) + octet * 8;
+                const uint32_t *src = f_src + size_t(g0) * 8;
+                const bool whole = f_have && g0 + 8 <= ng;
 #pragma unroll
-                for (int r = 0; r < 8; ++r)
-                    dst[u][r] = (whole || (f_have && g0 + r < ng)) ? __ldg(src + r * 8 + u * 4) : 0u;
+                for (int u = 0; u < kUnits; ++u)
+#pragma unroll
+                    for (int r = 0; r < 8; ++r)
+                        dst[u][r] = (whole || (f_have && g0 + r < ng)) ? __ldg(src + r * 8 + u * 4) : 0u;
+            }
             if (++f_slab == n_slabs) {
                 f_slab = 0;
                 f_item += gridDim.x; f_vt += vt_step; f_qg += qg_step;
@@ -384,18 +406,33 @@ scan_tc_kernel(ScanParams p, const __grid_constant__ CUtensorMap wmap, int n_sla
                 uint4 v[kUnits][4];
 #pragma unroll
                 for (int u = 0; u < kUnits; ++u) {
-                    // 4x4 byte transposes: bytes of vector j of the unit in groups g0..g0+3 (xlo) and g0+4..g0+7 (xhi)
-                    const uint32_t *x = w[a][u];
-                    const uint32_t t0 = prmt(x[0], x[1], 0x5140), t1 = prmt(x[0], x[1], 0x7362);
-                    const uint32_t t2 = prmt(x[2], x[3], 0x5140), t3 = prmt(x[2], x[3], 0x7362);
-                    const uint32_t u0 = prmt(x[4], x[5], 0x5140), u1 = prmt(x[4], x[5], 0x7362);
-                    const uint32_t u2 = prmt(x[6], x[7], 0x5140), u3 = prmt(x[6], x[7], 0x7362);
-                    const uint32_t xlo[4] = {prmt(t0, t2, 0x5410), prmt(t0, t2, 0x7632), prmt(t1, t3, 0x5410), prmt(t1, t3, 0x7632)};
-                    const uint32_t xhi[4] = {prmt(u0, u2, 0x5410), prmt(u0, u2, 0x7632), prmt(u1, u3, 0x5410), prmt(u1, u3, 0x7632)};
+                    if constexpr (ONEHOT) {
+                        // byte j of the word = code byte of vector j in this chunk's group; its high (even chunk)
+                        // or low (odd chunk) nibble n becomes a 16-byte one-hot: byte n = 1
+                        const uint32_t word = w[a][u][0];
+                        const uint32_t nibs = (octet & 1) ? (word & 0x0f0f0f0fu) : ((word >> 4) & 0x0f0f0f0fu);
 #pragma unroll
-                    for (int j = 0; j < 4; ++j) {
-                        expand8(xlo[j], T, v[u][j].x, v[u][j].y);
-                        expand8(xhi[j], T, v[u][j].z, v[u][j].w);
+                        for (int j = 0; j < 4; ++j) {
+                            const uint32_t n = (nibs >> (8 * j)) & 15u;
+                            const uint32_t bit = 1u << ((n & 3u) * 8u);
+                            const uint32_t q = n >> 2;
+                            v[u][j].x = q == 0 ? bit : 0u; v[u][j].y = q == 1 ? bit : 0u;
+                            v[u][j].z = q == 2 ? bit : 0u; v[u][j].w = q == 3 ? bit : 0u;
+                        }
+                    } else {
+                        // 4x4 byte transposes: bytes of vector j of the unit in groups g0..g0+3 (xlo) and g0+4..g0+7 (xhi)
+                        const uint32_t *x = w[a][u];
+                        const uint32_t t0 = prmt(x[0], x[1], 0x5140), t1 = prmt(x[0], x[1], 0x7362);
+                        const uint32_t t2 = prmt(x[2], x[3], 0x5140), t3 = prmt(x[2], x[3], 0x7362);
+                        const uint32_t u0 = prmt(x[4], x[5], 0x5140), u1 = prmt(x[4], x[5], 0x7362);
+                        const uint32_t u2 = prmt(x[6], x[7], 0x5140), u3 = prmt(x[6], x[7], 0x7362);
+                        const uint32_t xlo[4] = {prmt(t0, t2, 0x5410), prmt(t0, t2, 0x7632), prmt(t1, t3, 0x5410), prmt(t1, t3, 0x7632)};
+                        const uint32_t xhi[4] = {prmt(u0, u2, 0x5410), prmt(u0, u2, 0x7632), prmt(u1, u3, 0x5410), prmt(u1, u3, 0x7632)};
+#pragma unroll
+                        for (int j = 0; j < 4; ++j) {
+                            expand8(xlo[j], T, v[u][j].x, v[u][j].y);
+                            expand8(xhi[j], T, v[u][j].z, v[u][j].w);
+                        }
                     }
                 }
                 fetch(w[a]);                              // refill this ring slot (slab f + kAhead)
@@ -446,10 +483,15 @@ EncodeTiledFn encode_fn() {
 
 size_t scan_tc_smem_bytes() { return size_t(4) * (kATileBytes + kBBytes) + sizeof(TcShared) + 1024; }   // = 3 * 64 KB too
 
-bool scan_tc_supported(int bits, int mode) { return bits == 4 && mode == kModePermuteDot && encode_fn() != nullptr; }
+bool scan_tc_supported(int bits, int mode, int ngroups) {
+    if (encode_fn() == nullptr) return false;
+    if (mode == kModePermuteDot) return bits == 4;
+    return mode == kModeLutMulAdd && ngroups % 4 == 0;       // the per-256-group fma of the flush family needs partial sums
+}
 
-// weights: [rows][pitch] int8, pitch a multiple of 128, rows a multiple of 256, coordinates pair-swapped
-// (byte 2g = coordinate 2g+1, byte 2g+1 = coordinate 2g) to match the nibble order of a code byte.
+// Permute-dot: weights = [rows][pitch] int8, pitch a multiple of 128, rows a multiple of 256, coordinates
+// pair-swapped (byte 2g = coordinate 2g+1, byte 2g+1 = coordinate 2g) to match the nibble order of a code byte.
+// LUT: weights = the u8 tables [rows][pitch = 32 * ngroups].
 // tiles_per_item: 1 or 2 accumulator tiles of 128 vectors per B slab (see the kernel).
 cudaError_t launch_scan_tc(const ScanParams &p, const int8_t *weights, int rows, int pitch, int sm_count, int tiles_per_item,
                            cudaStream_t s) {
@@ -470,20 +512,22 @@ cudaError_t launch_scan_tc(const ScanParams &p, const int8_t *weights, int rows,
     const size_t smem = scan_tc_smem_bytes();
     static bool attr_set = false;
     if (!attr_set) {
-        cudaError_t e = cudaFuncSetAttribute(scan_tc_kernel<1>, cudaFuncAttributeMaxDynamicSharedMemorySize, int(smem));
-        if (e == cudaSuccess) e = cudaFuncSetAttribute(scan_tc_kernel<2>, cudaFuncAttributeMaxDynamicSharedMemorySize, int(smem));
+        cudaError_t e = cudaFuncSetAttribute(scan_tc_kernel<1, false>, cudaFuncAttributeMaxDynamicSharedMemorySize, int(smem));
+        if (e == cudaSuccess) e = cudaFuncSetAttribute(scan_tc_kernel<2, false>, cudaFuncAttributeMaxDynamicSharedMemorySize, int(smem));
+        if (e == cudaSuccess) e = cudaFuncSetAttribute(scan_tc_kernel<1, true>, cudaFuncAttributeMaxDynamicSharedMemorySize, int(smem));
         if (e != cudaSuccess) return e;
         attr_set = true;
     }
-    const int mt = tiles_per_item == 2 ? 2 : 1;
+    const int mt = (tiles_per_item == 2 && p.mode == kModePermuteDot) ? 2 : 1;
     const uint32_t vtiles = (p.pos_end - p.pos_begin + 4 * mt - 1) / (4 * mt);
     const uint64_t items = uint64_t(vtiles) * n_qgroups;
     // a multiple of the query-group count keeps the CTAs that share a vector tile in step (codes hit L2)
     unsigned grid = unsigned(sm_count - sm_count % n_qgroups);
     if (grid == 0) grid = unsigned(sm_count);
     if (items < grid) grid = unsigned(items);
-    if (mt == 2) scan_tc_kernel<2><<<grid, kThreadsTc, smem, s>>>(p, map, n_slabs, n_qgroups);
-    else scan_tc_kernel<1><<<grid, kThreadsTc, smem, s>>>(p, map, n_slabs, n_qgroups);
+    if (p.mode != kModePermuteDot) scan_tc_kernel<1, true><<<grid, kThreadsTc, smem, s>>>(p, map, n_slabs, n_qgroups);
+    else if (mt == 2) scan_tc_kernel<2, false><<<grid, kThreadsTc, smem, s>>>(p, map, n_slabs, n_qgroups);
+    else scan_tc_kernel<1, false><<<grid, kThreadsTc, smem, s>>>(p, map, n_slabs, n_qgroups);
     return cudaGetLastError();
 }
 

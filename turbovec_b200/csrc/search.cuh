@@ -87,8 +87,9 @@ struct ScanParams {
 // Permute-dot scan on mma.sync (int8 x int8 -> int32), up to 64 queries per launch.
 cudaError_t launch_scan_pd(const ScanParams &p, int sm_count, cudaStream_t s);
 // Permute-dot scan on tcgen05 tensor cores with TMEM accumulators (scan_tc.cu); all queries in one launch.
-// weights: [rows][pitch] int8 with rows % 256 == 0, pitch % 128 == 0, adjacent coordinates swapped.
-bool scan_tc_supported(int bits, int mode);
+// Permute-dot: weights [rows][pitch] int8, rows % 256 == 0, pitch % 128 == 0, adjacent coordinates swapped.
+// LUT (mul-add family, ngroups % 4 == 0): weights = the u8 tables [rows][32 * ngroups], rows % 256 == 0.
+bool scan_tc_supported(int bits, int mode, int ngroups);
 cudaError_t launch_scan_tc(const ScanParams &p, const int8_t *weights, int rows, int pitch, int sm_count,
                            int tiles_per_item, cudaStream_t s);
 // LUT scan on CUDA cores, up to kLutQueriesPerLaunch queries per launch.
