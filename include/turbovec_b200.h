@@ -189,6 +189,19 @@ int tv_codebook(tv_index *h, float *boundaries_out, float *centroids_out);
 /* Rotate rows exactly as queries are rotated (Rotation::apply, rotation.rs:202) — diagnostic entry point. */
 int tv_rotate(tv_index *h, const float *rows, size_t n, size_t dim, float *rotated_out);
 
+/* ---- persistence: to_bytes / from_bytes / write / load (lib.rs:2167, 2207, 2055, 2235) ----
+ * The image is the reference's v7 container (turbovec/src/io_v7.rs), byte for byte the snapshot the
+ * reference's to_bytes()/write() produce for the same index state, so files interchange.  Incremental
+ * sync journals are read (pending redo ops are applied on load) but never written. */
+/* The container's checksum: CRC-32C, and for inputs of 4096 bytes or more the CRC-32C of the three CRCs of the
+ * input's thirds (io_v7.rs:128-141). */
+uint32_t tv_crc32c(const uint8_t *data, size_t len);
+size_t tv_image_bytes(const tv_index *h);
+int tv_to_bytes(const tv_index *h, uint8_t *out, size_t capacity);
+int tv_from_bytes(const uint8_t *data, size_t len, int expect_kind, int device, tv_index **out);
+int tv_write(const tv_index *h, const char *path);
+int tv_load(const char *path, int expect_kind, int device, tv_index **out);
+
 /* ---- TQ+ calibration: calibrate_2d (lib.rs:2599-2723) on an EMPTY index; tqplus_shift/scale (lib.rs:2535-2545) ---- */
 int tv_calibrate(tv_index *h, const float *sample, size_t n, size_t dim);
 int tv_calibration(const tv_index *h, float *shift_out, float *scale_out, size_t capacity, int *is_calibrated);

@@ -85,3 +85,26 @@ def test_key_order_matches_reference_order():
     dedup = [k for j, k in enumerate(keys) if j != 3]
     assert dedup == sorted(dedup, reverse=True)                 # larger score -> smaller key
     assert ((desc_bits(np.float32(1.0)) << 32) | 3) < ((desc_bits(np.float32(1.0)) << 32) | 4)
+
+
+def test_container_checksum(lib):
+    """CRC-32C check value, and the three-way split the reference uses from 4096 bytes on (io_v7.rs:128-141)."""
+    import zlib  # noqa: F401  (zlib has CRC-32 only; the Castagnoli reference below is bitwise)
+
+    def crc32c(data: bytes) -> int:
+        crc = 0xFFFFFFFF
+        for b in data:
+            crc ^= b
+            for _ in range(8):
+                crc = (crc >> 1) ^ 0x82F63B78 if crc & 1 else crc >> 1
+        return crc ^ 0xFFFFFFFF
+
+    msg = np.frombuffer(b"123456789", np.uint8)
+    assert lib.tv_crc32c(msg.ctypes.data_as(ctypes.c_void_p), msg.size) == 0xE3069283
+    big = np.random.default_rng(0).integers(0, 256, 5000, dtype=np.uint8)
+    third = 5000 // 3
+    parts = [crc32c(big[:third].tobytes()), crc32c(big[third:2 * third].tobytes()), crc32c(big[2 * third:].tobytes())]
+    want = crc32c(b"".join(int(p).to_bytes(4, "little") for p in parts))
+    assert lib.tv_crc32c(big.ctypes.data_as(ctypes.c_void_p), big.size) == want
+    small = big[:4095].copy()
+    assert lib.tv_crc32c(small.ctypes.data_as(ctypes.c_void_p), small.size) == crc32c(small.tobytes())

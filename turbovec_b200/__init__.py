@@ -189,6 +189,46 @@ class _Base:
         groups = np.ascontiguousarray(groups, np.uint8)
         self._check(self._lib.tv_set_row(self._h, _size("slot", slot), _ptr(groups), groups.size, float(scale)))
 
+    # ---- persistence (the reference's v7 container) ----
+    def to_bytes(self) -> bytes:
+        buf = np.empty(int(self._lib.tv_image_bytes(self._h)), np.uint8)
+        self._check(self._lib.tv_to_bytes(self._h, _ptr(buf), buf.size))
+        return buf.tobytes()
+
+    def write(self, path: str, *, durable: bool = True) -> None:
+        self._check(self._lib.tv_write(self._h, str(path).encode()))
+
+    @classmethod
+    def _adopt(cls, handle):
+        self = cls.__new__(cls)
+        self._lib = _native.load()
+        self._h = handle
+        return self
+
+    @classmethod
+    def from_bytes(cls, data, *, device: int = 0):
+        if not isinstance(data, (bytes, bytearray, memoryview)):
+            raise TypeError(f"data must be bytes-like, got {type(data).__name__}")
+        lib = _native.load()
+        buf = np.frombuffer(bytes(data), np.uint8)
+        h = C.c_void_p()
+        rc = lib.tv_from_bytes(_ptr(buf), buf.size, cls._KIND, int(device), C.byref(h))
+        if rc != 0:
+            raise (RuntimeError if rc >= 90 else ValueError)(lib.tv_last_error(None).decode())
+        return cls._adopt(h)
+
+    @classmethod
+    def load(cls, path: str, *, device: int = 0):
+        lib = _native.load()
+        h = C.c_void_p()
+        rc = lib.tv_load(str(path).encode(), cls._KIND, int(device), C.byref(h))
+        if rc != 0:
+            raise (RuntimeError if rc >= 91 else ValueError)(lib.tv_last_error(None).decode())
+        return cls._adopt(h)
+
+    def __reduce__(self):
+        return (type(self).from_bytes, (self.to_bytes(),))
+
     def _search_raw(self, queries, k, fn, extra, out_dtype):
         queries = _f32_2d("queries", queries)
         k = _size("k", k)

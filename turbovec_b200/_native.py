@@ -51,6 +51,12 @@ SIGNATURES = {
     "tv_export_blocked": (C.c_int, [_H, C.c_void_p, C.c_size_t, C.c_void_p, C.c_size_t]),
     "tv_export_packed": (C.c_int, [_H, C.c_void_p, C.c_size_t]),
     "tv_import_packed": (C.c_int, [_H, C.c_size_t, C.c_void_p, C.c_size_t, C.c_void_p, C.c_void_p]),
+    "tv_crc32c": (C.c_uint32, [C.c_void_p, C.c_size_t]),
+    "tv_image_bytes": (C.c_size_t, [_H]),
+    "tv_to_bytes": (C.c_int, [_H, C.c_void_p, C.c_size_t]),
+    "tv_from_bytes": (C.c_int, [C.c_void_p, C.c_size_t, C.c_int, C.c_int, C.POINTER(_H)]),
+    "tv_write": (C.c_int, [_H, C.c_char_p]),
+    "tv_load": (C.c_int, [C.c_char_p, C.c_int, C.c_int, C.POINTER(_H)]),
     "tv_codebook": (C.c_int, [_H, C.c_void_p, C.c_void_p]),
     "tv_rotate": (C.c_int, [_H, C.c_void_p, C.c_size_t, C.c_size_t, C.c_void_p]),
     "tv_calibrate": (C.c_int, [_H, C.c_void_p, C.c_size_t, C.c_size_t]),

@@ -5,6 +5,7 @@
 
 #include <algorithm>
 #include <cmath>
+#include <cstdio>
 #include <cstring>
 #include <mutex>
 #include <string>
@@ -15,6 +16,7 @@
 #include "../../include/turbovec_b200.h"
 #include "host_tables.hpp"
 #include "ingest.cuh"
+#include "io_v7.hpp"
 #include "search.cuh"
 #include "tv_common.cuh"
 
@@ -209,16 +211,8 @@ int resolve_mode(const tv_index *h) {
     return m;
 }
 
-// Builds rotation tables, codebook and the permute-dot level table for the (now fixed) dimension.
-int ensure_tables(tv_index *h) {
-    if (h->tables_ready) return TV_OK;
-    const int dim = int(h->dim);
-    h->ngroups = dim / (8 / h->bits);
-    h->rot = build_rotation_tables(dim);
-    h->cb = codebook(h->bits, dim);
-    TV_CUDA(h->d_perm.reserve(size_t(2) * dim));
-    TV_CUDA(cudaMemcpyAsync(h->d_perm.ptr, h->rot.packed[0].data(), size_t(dim) * 2, cudaMemcpyHostToDevice, h->stream));
-    TV_CUDA(cudaMemcpyAsync(h->d_perm.ptr + dim, h->rot.packed[1].data(), size_t(dim) * 2, cudaMemcpyHostToDevice, h->stream));
+// Uploads h->cb and derives the permute-dot level table from it.
+int upload_codebook(tv_index *h) {
     float cbuf[32] = {0};
     for (size_t i = 0; i < h->cb.boundaries.size(); ++i) cbuf[i] = h->cb.boundaries[i];
     for (size_t i = 0; i < h->cb.centroids.size(); ++i) cbuf[16 + i] = h->cb.centroids[i];
@@ -237,6 +231,21 @@ int ensure_tables(tv_index *h) {
         }
         h->level_scale = cs;
     }
+    return TV_OK;
+}
+
+// Builds rotation tables, codebook and the permute-dot level table for the (now fixed) dimension.
+int ensure_tables(tv_index *h) {
+    if (h->tables_ready) return TV_OK;
+    const int dim = int(h->dim);
+    h->ngroups = dim / (8 / h->bits);
+    h->rot = build_rotation_tables(dim);
+    h->cb = codebook(h->bits, dim);
+    TV_CUDA(h->d_perm.reserve(size_t(2) * dim));
+    TV_CUDA(cudaMemcpyAsync(h->d_perm.ptr, h->rot.packed[0].data(), size_t(dim) * 2, cudaMemcpyHostToDevice, h->stream));
+    TV_CUDA(cudaMemcpyAsync(h->d_perm.ptr + dim, h->rot.packed[1].data(), size_t(dim) * 2, cudaMemcpyHostToDevice, h->stream));
+    int rc = upload_codebook(h);
+    if (rc != TV_OK) return rc;
     h->tables_ready = true;
     return TV_OK;
 }
@@ -1205,6 +1214,135 @@ int tv_import_packed(tv_index *h, size_t dim, const uint8_t *packed, size_t n, c
         for (size_t i = 0; i < n; ++i) h->id_to_slot.emplace(ids[i], uint32_t(i));
     }
     return TV_OK;
+}
+
+// ---- v7 container: to_bytes / from_bytes / write / load (lib.rs:2167, 2207, 2055, 2235; io_v7.rs) ----
+namespace {
+int gather_parts(tv_index *h, V7Parts &p) {
+    p.kind = h->kind; p.bits = h->bits; p.dim = h->dim; p.n = h->n;
+    if (h->dim) {
+        const Codebook &cb = h->tables_ready ? h->cb : codebook(h->bits, int(h->dim));
+        p.boundaries = cb.boundaries; p.centroids = cb.centroids;
+    } else {                                   // lazy index: the reference writes a zero placeholder codebook
+        p.boundaries.assign((size_t(1) << h->bits) - 1, 0.f);
+        p.centroids.assign(size_t(1) << h->bits, 0.f);
+    }
+    p.shift = h->shift; p.scale = h->scale_tq;
+    p.blocked.resize(h->dim ? ((h->n + kBlock - 1) / kBlock) * size_t(h->dim / (8 / h->bits)) * kBlock : 0);
+    p.scales.resize(h->n);
+    if (h->n) {
+        TV_CUDA(cudaSetDevice(h->device));
+        TV_CUDA(cudaMemcpyAsync(p.blocked.data(), h->d_codes, p.blocked.size(), cudaMemcpyDeviceToHost, h->stream));
+        TV_CUDA(cudaMemcpyAsync(p.scales.data(), h->d_scales, h->n * 4, cudaMemcpyDeviceToHost, h->stream));
+        TV_CUDA(cudaStreamSynchronize(h->stream));
+    }
+    if (h->kind == TV_KIND_IDMAP) p.ids = h->slot_to_id;
+    return TV_OK;
+}
+}  // namespace
+
+uint32_t tv_crc32c(const uint8_t *data, size_t len) { return crc32c_split(data, len); }
+
+size_t tv_image_bytes(const tv_index *h) {
+    if (!h) return 0;
+    V7Parts p;
+    p.kind = h->kind; p.bits = h->bits; p.dim = h->dim; p.n = h->n; p.shift = h->shift;
+    return v7_image_len(p);
+}
+
+int tv_to_bytes(const tv_index *hc, uint8_t *out, size_t capacity) {
+    tv_index *h = const_cast<tv_index *>(hc);
+    if (!h || !out) return TV_ERR_INVALID_ARGUMENT;
+    std::lock_guard<std::mutex> lock(h->mu);
+    V7Parts p;
+    int rc = gather_parts(h, p);
+    if (rc != TV_OK) return rc;
+    std::vector<uint8_t> img;
+    v7_write_image(p, img);
+    if (capacity < img.size()) return fail(h, TV_ERR_INVALID_ARGUMENT, "output buffer too small");
+    std::memcpy(out, img.data(), img.size());
+    return TV_OK;
+}
+
+int tv_from_bytes(const uint8_t *data, size_t len, int expect_kind, int device, tv_index **out) {
+    tv_index *h = nullptr;
+    if (!data || !out) return fail(h, TV_ERR_INVALID_ARGUMENT, "null argument");
+    *out = nullptr;
+    V7Parts p;
+    std::string err;
+    if (!v7_read_image(data, len, p, err)) return fail(h, TV_ERR_PARTS_INVALID, err);
+    if (p.kind != expect_kind)
+        return fail(h, TV_ERR_WRONG_INDEX_KIND, p.kind == 1 ? "this v7 image holds an IdMapIndex" : "this v7 image holds a TurboQuantIndex");
+    if (p.kind == 1) {
+        std::unordered_set<uint64_t> seen(p.ids.begin(), p.ids.end());
+        if (seen.size() != p.n) return fail(h, TV_ERR_PARTS_INVALID, "duplicate ids in the image");
+    }
+    int rc = tv_index_create(p.dim, p.bits, p.kind, device, &h);
+    if (rc != TV_OK) return rc;
+    auto bail = [&](int code) { g_create_error = h->last_error; delete h; return code; };
+    if (p.dim == 0) { *out = h; return TV_OK; }
+    if (cudaSetDevice(h->device) != cudaSuccess) return bail(TV_ERR_CUDA);
+    h->shift = p.shift; h->scale_tq = p.scale;
+    rc = ensure_tables(h);
+    if (rc != TV_OK) return bail(rc);
+    if (p.boundaries != h->cb.boundaries || p.centroids != h->cb.centroids) {
+        // the image carries the codebook it was encoded against; it wins over a re-solve (io_v7.rs load)
+        h->cb.boundaries = p.boundaries; h->cb.centroids = p.centroids;
+        rc = upload_codebook(h);
+        if (rc != TV_OK) return bail(rc);
+    }
+    rc = upload_calibration(h);
+    if (rc == TV_OK && p.n) rc = ensure_capacity(h, p.n);
+    if (rc != TV_OK) return bail(rc);
+    if (p.n) {
+        if (cudaMemcpyAsync(h->d_codes, p.blocked.data(), p.blocked.size(), cudaMemcpyHostToDevice, h->stream) != cudaSuccess ||
+            cudaMemcpyAsync(h->d_scales, p.scales.data(), p.n * 4, cudaMemcpyHostToDevice, h->stream) != cudaSuccess ||
+            cudaStreamSynchronize(h->stream) != cudaSuccess) {
+            h->last_error = "upload of the image failed";
+            return bail(TV_ERR_CUDA);
+        }
+    }
+    h->n = p.n;
+    if (p.kind == 1) {
+        h->slot_to_id = p.ids;
+        for (size_t i = 0; i < p.n; ++i) h->id_to_slot.emplace(p.ids[i], uint32_t(i));
+    }
+    *out = h;
+    return TV_OK;
+}
+
+// Atomic replace: write a temp file beside the destination, fsync it, rename over it (io.rs:14-27).
+int tv_write(const tv_index *hc, const char *path) {
+    tv_index *h = const_cast<tv_index *>(hc);
+    if (!h || !path) return TV_ERR_INVALID_ARGUMENT;
+    std::vector<uint8_t> img(tv_image_bytes(h));
+    int rc = tv_to_bytes(h, img.data(), img.size());
+    if (rc != TV_OK) return rc;
+    const std::string tmp = std::string(path) + ".tmp";
+    FILE *f = std::fopen(tmp.c_str(), "wb");
+    if (!f) return fail(h, TV_ERR_INVALID_ARGUMENT, "cannot create " + tmp);
+    const bool ok = std::fwrite(img.data(), 1, img.size(), f) == img.size() && std::fflush(f) == 0;
+    std::fclose(f);
+    if (!ok || std::rename(tmp.c_str(), path) != 0) {
+        std::remove(tmp.c_str());
+        return fail(h, TV_ERR_INVALID_ARGUMENT, std::string("cannot write ") + path);
+    }
+    return TV_OK;
+}
+
+int tv_load(const char *path, int expect_kind, int device, tv_index **out) {
+    tv_index *h = nullptr;
+    if (!path || !out) return fail(h, TV_ERR_INVALID_ARGUMENT, "null argument");
+    FILE *f = std::fopen(path, "rb");
+    if (!f) return fail(h, TV_ERR_INVALID_ARGUMENT, std::string("cannot open ") + path);
+    std::fseek(f, 0, SEEK_END);
+    const long sz = std::ftell(f);
+    std::fseek(f, 0, SEEK_SET);
+    std::vector<uint8_t> buf(sz > 0 ? size_t(sz) : 0);
+    const bool ok = std::fread(buf.data(), 1, buf.size(), f) == buf.size();
+    std::fclose(f);
+    if (!ok) return fail(h, TV_ERR_INVALID_ARGUMENT, std::string("cannot read ") + path);
+    return tv_from_bytes(buf.data(), buf.size(), expect_kind, device, out);
 }
 
 int tv_codebook(tv_index *h, float *boundaries_out, float *centroids_out) {
