@@ -413,3 +413,30 @@ def test_tensor_memory_lut_scan_matches_oracle(T, dim, bits, n, nq):
     s, i = idx.search(q, 10, mask=mask)
     rs, ri = _oracle_search(x, q, bits, 10, mask=mask, mode=O.MODE_LUT_MULADD)
     assert np.array_equal(i, ri) and np.array_equal(s, rs)
+
+
+def test_sharded_index_single_rank_on_device(T):
+    """The slot-sharded wrapper around a real device index (one rank): same answers as the plain index."""
+    from turbovec_b200.sharded import ShardedIndex
+    dim, n = 128, 5000
+    x = anisotropic(n, dim, seed=71)
+    q = anisotropic(6, dim, seed=71, offset=2)
+    sh = ShardedIndex(dim, 4, chunk_blocks=16)
+    for a, b in ((0, 700), (700, 701), (701, n)):
+        sh.add(x[a:b])
+    ref = _build(T, x, 4)
+    s, i = sh.search(q, 10)
+    rs, ri = ref.search(q, 10)
+    assert np.array_equal(i, ri) and np.array_equal(s, rs)
+    mask = np.random.default_rng(1).random(n) < 0.01
+    s, i = sh.search(q, 10, mask=mask)
+    rs, ri = ref.search(q, 10, mask=mask)
+    assert np.array_equal(i, ri) and np.array_equal(s, rs)
+    assert sh.swap_remove(17) == ref.swap_remove(17)
+    s, i = sh.search(q, 10)
+    rs, ri = ref.search(q, 10)
+    assert np.array_equal(i, ri) and np.array_equal(s, rs)
+    codes, scale = ref.get_row(17)
+    ref.set_row(3, codes, scale)
+    c2, s2 = ref.get_row(3)
+    assert np.array_equal(c2, codes) and s2 == scale
