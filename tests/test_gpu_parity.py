@@ -86,6 +86,47 @@ def test_ingest_zero_and_tiny_rows(T):
     assert np.array_equal(idx.packed_codes(), enc["packed"])
 
 
+@pytest.mark.parametrize("dim,bits", [(128, 4), (256, 2), (384, 3), (512, 4), (768, 4), (1024, 2), (1536, 3), (1536, 4),
+                                      (2048, 4), (2048, 2)])
+def test_pipelined_ingest_matches_oracle_and_block_kernel(T, dim, bits):
+    """Whole code blocks go through the pipelined kernel, a partial head block through the block-at-a-time
+    one; both must produce the oracle's bytes and scales, and so must the block-at-a-time kernel alone."""
+    n = 1500 + 13
+    x = anisotropic(n, dim, seed=7 * dim + bits)
+    x[5] = 0.0
+    x[700] = 1e-23
+    enc = O.encode(x, bits)
+    want_blocked = O.packed_to_blocked(enc["packed"], bits, dim)
+    a = T.TurboQuantIndex(dim, bits)
+    assert a.get_option(T.OPT_INGEST_PIPELINE) == 1
+    a.add(x[:3])            # leaves a partly filled block
+    a.add(x[3:1000])        # head rows complete it, the rest are whole blocks plus a ragged tail
+    a.add(x[1000:])
+    b = T.TurboQuantIndex(dim, bits)
+    b.set_option(T.OPT_INGEST_PIPELINE, 0)
+    b.add(x)
+    for idx in (a, b):
+        assert np.array_equal(idx.codes_blocked_seq(), want_blocked)
+        assert np.array_equal(idx.scales().view(np.uint32), enc["scales"].view(np.uint32))
+        assert np.array_equal(idx.packed_codes(), enc["packed"])
+
+
+def test_pipelined_ingest_reports_first_invalid_coordinate(T):
+    x = anisotropic(400, 256, seed=12)
+    idx = T.TurboQuantIndex(256, 4)
+    bad = x.copy()
+    bad[333, 200] = -np.inf
+    bad[150, 9] = 2e16
+    bad[150, 77] = np.nan
+    with pytest.raises(ValueError, match="vector 150 coordinate 9"):
+        idx.add(bad)
+    assert len(idx) == 0
+    idx.add(x)
+    enc = O.encode(x, 4)
+    assert np.array_equal(idx.codes_blocked_seq(), O.packed_to_blocked(enc["packed"], 4, 256))
+    assert np.array_equal(idx.scales().view(np.uint32), enc["scales"].view(np.uint32))
+
+
 def test_add_rejects_invalid_and_leaves_index_unchanged(T):
     x = anisotropic(70, 128, seed=2)
     idx = T.TurboQuantIndex(128, 4)

@@ -92,6 +92,7 @@ struct tv_index {
     int score_mode = TV_SCORE_AUTO;
     int64_t mma_min_batch = 65;  // measured switch point: mma.sync covers 64 queries per pass, tcgen05 wins beyond
     int force_careful = 0;
+    int ingest_pipeline = 1;     // 1: whole code blocks of an uncalibrated add go through the pipelined ingest kernel
     int tc_tiles = 1;            // accumulator tiles per B slab in the tcgen05 scan (1 or 2); 1 measured faster
 
     cudaStream_t stream = nullptr;
@@ -365,7 +366,9 @@ int add_rows(tv_index *h, const float *x, size_t n, size_t dim, bool on_device) 
     if (V == 0) return fail(h, TV_ERR_UNSUPPORTED, "dim too large for the ingest kernel's shared memory");
 
     h->h_flags->first_invalid = ~0ull;
+    h->h_flags->error = 0;
     TV_CUDA(cudaMemcpyAsync(&h->d_flags->first_invalid, &h->h_flags->first_invalid, 8, cudaMemcpyHostToDevice, h->stream));
+    TV_CUDA(cudaMemcpyAsync(&h->d_flags->error, &h->h_flags->error, 4, cudaMemcpyHostToDevice, h->stream));
 
     IngestParams p{};
     p.dim = int(dim); p.bits = h->bits; p.ngroups = h->ngroups;
@@ -388,16 +391,36 @@ int add_rows(tv_index *h, const float *x, size_t n, size_t dim, bool on_device) 
             src = h->d_stage.ptr;
         }
         p.x = src; p.n = int64_t(rows); p.slot0 = int64_t(h->n + done); p.row_base = int64_t(done);
-        mark_begin(h);
-        TV_CUDA(launch_ingest(p, V, h->stream));
-        mark_end(h);
-        h->launches++;
+        // rows that complete a partly filled block go through the block-at-a-time kernel, whole blocks
+        // through the pipelined one where it applies
+        int64_t head = rows;
+        if (h->ingest_pipeline && ingest_fast_supported(int(dim), h->bits, p.shift != nullptr, src))
+            head = std::min<int64_t>(int64_t(rows), (kBlockLanes - p.slot0 % kBlockLanes) % kBlockLanes);
+        if (head > 0) {
+            p.n = head;
+            mark_begin(h);
+            TV_CUDA(launch_ingest(p, V, h->stream));
+            mark_end(h);
+            h->launches++;
+        }
+        if (int64_t(rows) > head) {
+            p.x = src + head * int64_t(dim); p.n = int64_t(rows) - head; p.slot0 += head; p.row_base += head;
+            mark_begin(h);
+            TV_CUDA(launch_ingest_fast(p, h->cb.boundaries.data(), h->sm_count, h->smem_limit, &h->d_flags->error, h->stream));
+            mark_end(h);
+            h->launches++;
+        }
     }
     TV_CUDA(cudaEventRecord(h->ev1, h->stream));
     TV_CUDA(cudaMemcpyAsync(&h->h_flags->first_invalid, &h->d_flags->first_invalid, 8, cudaMemcpyDeviceToHost, h->stream));
+    TV_CUDA(cudaMemcpyAsync(&h->h_flags->error, &h->d_flags->error, 4, cudaMemcpyDeviceToHost, h->stream));
     TV_CUDA(cudaStreamSynchronize(h->stream));
     cudaEventElapsedTime(&h->last_ms, h->ev0, h->ev1);
     collect_marks(h);
+    if (h->h_flags->error != 0) {
+        if (was_lazy) { h->dim = 0; h->tables_ready = false; }
+        return fail(h, TV_ERR_DEVICE_TIMEOUT, "the ingest kernel gave up waiting for a staged row (code " + std::to_string(h->h_flags->error) + ")");
+    }
     if (h->h_flags->first_invalid != ~0ull) {
         // roll back: the new lanes must read as zero again, nothing else was touched
         const int64_t total = int64_t(n) * h->ngroups;
@@ -794,6 +817,7 @@ int tv_set_option(tv_index *h, int option, int64_t value) {
         case TV_OPT_MMA_MIN_BATCH: h->mma_min_batch = value; return TV_OK;
         case TV_OPT_FORCE_CAREFUL: h->force_careful = value != 0; return TV_OK;
         case TV_OPT_TC_TILES: h->tc_tiles = value == 1 ? 1 : 2; return TV_OK;
+        case TV_OPT_INGEST_PIPELINE: h->ingest_pipeline = value != 0; return TV_OK;
         default: return fail(h, TV_ERR_INVALID_ARGUMENT, "unknown option");
     }
 }
@@ -805,6 +829,7 @@ int64_t tv_get_option(const tv_index *h, int option) {
         case TV_OPT_MMA_MIN_BATCH: return h->mma_min_batch;
         case TV_OPT_FORCE_CAREFUL: return h->force_careful;
         case TV_OPT_TC_TILES: return h->tc_tiles;
+        case TV_OPT_INGEST_PIPELINE: return h->ingest_pipeline;
         default: return -1;
     }
 }

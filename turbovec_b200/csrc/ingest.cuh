@@ -36,4 +36,12 @@ size_t ingest_smem_bytes(int vectors_per_pass, int dim, int ngroups);
 int ingest_vectors_per_pass(int dim, int ngroups, size_t smem_limit);
 cudaError_t launch_ingest(const IngestParams &p, int vectors_per_pass, cudaStream_t stream);
 
+// Pipelined form (ingest_fast.cu) for whole code blocks: p.slot0 a multiple of 32, no calibration, no
+// rotate-only mode, x 16-byte aligned, dim one of the instantiated sizes.  `error` receives a non-zero
+// code if a bounded wait inside the kernel gives up.
+bool ingest_fast_supported(int dim, int bits, bool calibrated, const void *x);
+// `host_boundaries`: the 2^bits - 1 codebook boundaries in host memory (they travel as kernel arguments).
+cudaError_t launch_ingest_fast(const IngestParams &p, const float *host_boundaries, int sm_count, size_t smem_limit, uint32_t *error,
+                               cudaStream_t stream);
+
 }  // namespace tv
