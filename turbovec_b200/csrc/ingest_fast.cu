@@ -3,17 +3,20 @@
 // :560-652 / fused_quantize_scale_pack_scalar :1418-1476, blocked layout pack.rs:340-361), reorganised so
 // that the order-fixed sequential sums no longer stall the data-parallel work.
 //
-// One CTA walks a contiguous range of code blocks in waves of V vectors (V = 4 or 8) and runs three stages
-// concurrently, one wave apart, with one CTA barrier per step:
+// One CTA of three warpgroups walks a contiguous range of code blocks in waves of 8 vectors and runs its
+// stages concurrently, one wave apart, with one CTA barrier per step:
 //   norm warp      wave i     8 sequential f32 chains per vector straight from global memory (4 lanes per
 //                             vector, two chains per lane), fixed combine tree, sqrt, reciprocal
-//   V rotation     wave i-1   one warp per vector, the whole vector in registers: both rounds of permutation,
+//   8 rotation     wave i-1   one warp per vector, the whole vector in registers: both rounds of permutation,
 //   warps                     sign flip and Walsh-Hadamard butterflies (rotation.cuh states the order rules),
 //                             Lloyd-Max quantisation by a register binary search, packing into the block tile
 //   sum warp       wave i-2   4 sequential f64 chains per vector over the rotated row and the codes, scale;
 //                             then issues the bulk copies that stage wave i's rows into shared memory
-// Rows arrive by cp.async.bulk with an mbarrier transaction count; the finished tile of a block (ngroups x 32
-// bytes, word-swizzled so that the byte stores of a warp never share a bank) is copied out linearly.
+//   2 copy warps              write the finished tile of a block (ngroups x 32 bytes, word-swizzled so that the
+//                             byte stores of a warp never share a bank) to the code array
+// Rows arrive by cp.async.bulk with an mbarrier transaction count.  The two rotation warpgroups take the
+// registers the third one gives up (setmaxnreg), so a 2048-coordinate vector and its permutation entries
+// stay in registers.
 #include <algorithm>
 #include <cmath>
 
@@ -55,26 +58,43 @@ __device__ __forceinline__ void bulk_load(void *dst, const void *src, uint32_t b
     asm volatile("cp.async.bulk.shared::cluster.global.mbarrier::complete_tx::bytes [%0], [%1], %2, [%3];"
                  ::"r"(smem_u32(dst)), "l"(src), "r"(bytes), "r"(smem_u32(bar)) : "memory");
 }
+// shared-memory accesses by 32-bit shared address: keeps the address arithmetic of the fully unrolled
+// rotation in one register per access
+__device__ __forceinline__ float lds_f32(uint32_t addr) {
+    float v;
+    asm volatile("ld.shared.f32 %0, [%1];" : "=f"(v) : "r"(addr));
+    return v;
+}
+__device__ __forceinline__ void sts_f32(uint32_t addr, float v) {
+    asm volatile("st.shared.f32 [%0], %1;" ::"r"(addr), "f"(v) : "memory");
+}
+__device__ __forceinline__ void sts_u8(uint32_t addr, uint32_t v) {
+    asm volatile("st.shared.u8 [%0], %1;" ::"r"(addr), "r"(v) : "memory");
+}
 __device__ __forceinline__ float max_nan(float a, float b) {   // NaN wins, unlike fmaxf
     float d;
     asm("max.NaN.f32 %0, %1, %2;" : "=f"(d) : "f"(a), "f"(b));
     return d;
 }
 
+constexpr int kWave = 8;                 // vectors per wave = rotation warps
+constexpr int kWavesPerBlock = kBlockLanes / kWave;
+constexpr int kFastThreads = 384;        // 8 rotation warps, norm warp, sum warp, 2 copy warps
+constexpr int kRotationRegs = 208, kServiceRegs = 88;   // 8*32*208 + 4*32*88 <= 384 * 168
+
 struct FastLayout {
     int stride;          // floats per staged row: dim + 4 keeps the sum warp's 4-lane reads on distinct banks
-    size_t rows, tile, perm, cent, norm, inv, bars, total;
+    size_t rows, tile, table, norm, inv, bars, total;
 };
-__host__ __device__ inline FastLayout fast_layout(int V, int dim, int ngroups, bool perm_in_smem) {
+__host__ __device__ inline FastLayout fast_layout(int dim, int ngroups, int cpb) {
     FastLayout L;
     L.stride = dim + 4;
     size_t off = 0;
-    L.rows = off; off += size_t(2) * V * L.stride * 4;
+    L.rows = off; off += size_t(2) * kWave * L.stride * 4;
     L.tile = off; off += size_t(2) * ngroups * 32;
-    L.perm = off; off += perm_in_smem ? size_t(dim) * 4 : 0;
-    L.cent = off; off += 16 * 8;
-    L.norm = off; off += 3 * 8 * 4;
-    L.inv = off; off += 3 * 8 * 4;
+    L.table = off; off += size_t(cpb) * 256 * 8;     // centroid (as f64) of field k of every byte value
+    L.norm = off; off += 3 * kWave * 4;
+    L.inv = off; off += 3 * kWave * 4;
     L.bars = off; off += 2 * 8;
     L.total = off;
     return L;
@@ -125,27 +145,53 @@ __device__ __forceinline__ void wht_blocks(float (&v)[R * NBLK], const float (&s
     }
 }
 
+// The 4 sequential f64 chains of 8 vectors: lane = (vector vv, chain c), chain c sums
+// rotated[j] * centroid[code[j]] over j = c (mod 4) in ascending j (encode.rs:1418-1476).  `tab` maps a
+// tile byte straight to the centroid of this chain's field; the word swizzle of the tile repeats every 32
+// groups, so inside a window of 32 groups every offset is a compile-time constant.
+template <int CPB, int DIM>
+__device__ __forceinline__ double sum_chain(const float *row_c, const unsigned char *tile_lane, int wsel, const double *tab) {
+    constexpr int GS = 4 / CPB;                 // groups advanced per step
+    constexpr int SW = 32 / GS;                 // steps per window of 32 groups
+    const unsigned char *ps[8];
+#pragma unroll
+    for (int s = 0; s < 8; ++s) ps[s] = tile_lane + (((wsel ^ s) & 7) << 2);
+    double acc = 0.0;
+#pragma unroll 1
+    for (int wnd = 0; wnd < DIM / 4 / SW; ++wnd) {
+#pragma unroll
+        for (int u = 0; u < SW; ++u) {
+            const uint32_t byte = ps[((GS * u) >> 2) & 7][GS * u * 32];
+            acc = __dadd_rn(acc, __dmul_rn(double(row_c[4 * u]), tab[byte]));
+        }
+#pragma unroll
+        for (int s = 0; s < 8; ++s) ps[s] += 1024;
+        row_c += 4 * SW;
+    }
+    return acc;
+}
+
 template <int LOG2B, int NBLK>
-__global__ void __launch_bounds__(320, 1) ingest_fast_kernel(IngestParams p, Boundaries15 bnd, uint32_t *error, int V) {
+__global__ void __launch_bounds__(kFastThreads, 1) ingest_fast_kernel(IngestParams p, Boundaries15 bnd, uint32_t *error) {
     constexpr int R = 1 << (LOG2B - 5);               // registers per Hadamard block and lane
     constexpr int T = R * NBLK;                       // registers per vector and lane
     constexpr int DIM = T * 32;
+    constexpr int V = kWave, wpb = kWavesPerBlock;
     static_assert(T % 4 == 0, "the packing below handles whole groups of four registers");
     extern __shared__ __align__(128) unsigned char smem[];
     const int ng = p.ngroups;
-    const FastLayout L = fast_layout(V, DIM, ng, false);
+    const int cpb = p.bits == 2 ? 4 : 2;              // codes per byte (3-bit codes sit in 4-bit fields)
+    const int field = 8 / cpb;
+    const FastLayout L = fast_layout(DIM, ng, cpb);
     float *rows = reinterpret_cast<float *>(smem + L.rows);
     unsigned char *tiles = smem + L.tile;
-    double *cent64 = reinterpret_cast<double *>(smem + L.cent);
+    double *table = reinterpret_cast<double *>(smem + L.table);   // [cpb][256]
     float *norm_s = reinterpret_cast<float *>(smem + L.norm);     // [3][8]
     float *inv_s = reinterpret_cast<float *>(smem + L.inv);       // [3][8]
     uint64_t *full = reinterpret_cast<uint64_t *>(smem + L.bars); // [2]
     const int tid = threadIdx.x, warp = tid >> 5, lane = tid & 31;
     const int stride = L.stride;
     const int tile_bytes = ng * 32;
-    const int wpb = 32 / V;                           // waves per code block
-    const int cpb = p.bits == 2 ? 4 : 2;              // codes per byte (3-bit codes sit in 4-bit fields)
-    const int field = 8 / cpb;
 
     const int64_t slot_lo = p.slot0, slot_hi = p.slot0 + p.n;       // slot_lo is a multiple of 32
     const int64_t nblocks = (p.n + 31) / 32;
@@ -158,7 +204,10 @@ __global__ void __launch_bounds__(320, 1) ingest_fast_kernel(IngestParams p, Bou
         mbar_init(&full[1], 1);
         asm volatile("fence.mbarrier_init.release.cluster;" ::: "memory");
     }
-    if (tid < (1 << p.bits)) cent64[tid] = double(p.centroids[tid]);
+    for (int i = tid; i < cpb * 256; i += kFastThreads) {
+        const int k = i >> 8, byte = i & 255;
+        table[i] = double(p.centroids[(byte >> ((cpb - 1 - k) * field)) & ((1 << field) - 1)]);   // the codebook array has 16 slots
+    }
     __syncthreads();
 
     // slot of vector `v` of wave `w`, or -1 past the new rows (padding lanes of the last block)
@@ -168,6 +217,7 @@ __global__ void __launch_bounds__(320, 1) ingest_fast_kernel(IngestParams p, Bou
     };
 
     if (warp < V) {
+        asm volatile("setmaxnreg.inc.sync.aligned.u32 %0;" ::"n"(kRotationRegs) : "memory");
         // ------------------------------------------------ rotation + quantisation: one vector per warp
         uint32_t pk[T];          // per register: round-1 byte offset | sign << 15, round-2 the same in the high half
 #pragma unroll
@@ -182,16 +232,6 @@ __global__ void __launch_bounds__(320, 1) ingest_fast_kernel(IngestParams p, Bou
         const int q = lane & (cpb - 1);               // this lane packs the registers k = q (mod cpb)
 
         for (int it = 0; it <= nw + 1; ++it) {
-            // copy out the tile of the block whose last wave was packed in the previous step
-            const int wf = it - 2;
-            if (wf >= 0 && wf % wpb == wpb - 1) {
-                const uint32_t *t32 = reinterpret_cast<const uint32_t *>(tiles + ((wf / wpb) & 1) * tile_bytes);
-                uint32_t *dst = reinterpret_cast<uint32_t *>(p.codes + size_t(first_block + wf / wpb) * tile_bytes);
-                for (int idx = tid; idx < ng * 8; idx += V * 32) {
-                    const int g = idx >> 3, wl = idx & 7;
-                    dst[idx] = t32[g * 8 + (wl ^ ((g >> 2) & 7))];
-                }
-            }
             const int w = it - 1;
             if (w >= 0 && w < nw) {
                 const int64_t slot = wave_slot(w, warp);
@@ -200,14 +240,18 @@ __global__ void __launch_bounds__(320, 1) ingest_fast_kernel(IngestParams p, Bou
                 for (int i = 0; i < (T + 7) / 8; ++i) cw[i] = 0;
                 float *row = rows + size_t((w & 1) * V + warp) * stride;
                 if (slot >= 0 && mbar_wait(&full[w & 1], (w >> 1) & 1, error)) {
-                    const unsigned char *rb = reinterpret_cast<const unsigned char *>(row);
-                    const float inv = inv_s[(w % 3) * 8 + warp];
+                    const uint32_t rb = smem_u32(row), rl = rb + lane * 4;
+                    const float inv = inv_s[(w % 3) * V + warp];
+                    // keeps the masks and offsets derived from pk from being hoisted out of the wave loop into
+                    // four registers per entry
+#pragma unroll
+                    for (int k = 0; k < T; ++k) asm volatile("" : "+r"(pk[k]));
                     float v[T];
                     // round 1: (x[perm] * inv) * sign (rotation.rs:384); |x| < 1e16 checked on the way (encode.rs:58-74)
                     float big = 0.0f;
 #pragma unroll
                     for (int k = 0; k < T; ++k) {
-                        const float x = *reinterpret_cast<const float *>(rb + (pk[k] & 0x7ffcu));
+                        const float x = lds_f32(rb + (pk[k] & 0x7ffcu));
                         big = max_nan(big, fabsf(x));
                         v[k] = __uint_as_float(__float_as_uint(__fmul_rn(x, inv)) ^ ((pk[k] << 16) & 0x80000000u));
                     }
@@ -221,12 +265,12 @@ __global__ void __launch_bounds__(320, 1) ingest_fast_kernel(IngestParams p, Bou
                     }
                     wht_blocks<R, NBLK>(v, sgn);
 #pragma unroll
-                    for (int k = 0; k < T; ++k) row[k * 32 + lane] = __fmul_rn(v[k], isb);
+                    for (int k = 0; k < T; ++k) sts_f32(rl + k * 128, __fmul_rn(v[k], isb));
                     __syncwarp();
                     // round 2
 #pragma unroll
                     for (int k = 0; k < T; ++k) {
-                        const float x = *reinterpret_cast<const float *>(rb + ((pk[k] >> 16) & 0x7ffcu));
+                        const float x = lds_f32(rb + ((pk[k] >> 16) & 0x7ffcu));
                         v[k] = __uint_as_float(__float_as_uint(x) ^ (pk[k] & 0x80000000u));
                     }
                     __syncwarp();
@@ -234,16 +278,16 @@ __global__ void __launch_bounds__(320, 1) ingest_fast_kernel(IngestParams p, Bou
 #pragma unroll
                     for (int k = 0; k < T; ++k) {
                         const float y = __fmul_rn(v[k], isb);
-                        row[k * 32 + lane] = y;                       // rotated row, read by the sum warp
+                        sts_f32(rl + k * 128, y);                     // rotated row, read by the sum warp
                         cw[k >> 3] |= quantise15(y, bnd.b) << (4 * (k & 7));
                     }
                 }
                 // pack: byte of group g = codes of coordinates g*cpb .. g*cpb+cpb-1, first one in the top field
                 // (pack.rs:264-282); the cpb lanes of a group exchange code words, lane q stores k = q (mod cpb)
                 const int vabs = (w % wpb) * V + warp;                // lane of this vector in its block
-                unsigned char *tile = tiles + ((w / wpb) & 1) * tile_bytes;
+                const uint32_t tile = smem_u32(tiles) + ((w / wpb) & 1) * tile_bytes;
                 if (cpb == 2) {
-                    unsigned char *dst = tile + q * 512 + (lane >> 1) * 32 + ((((vabs >> 2) ^ (4 * q + (lane >> 3))) & 7) << 2) + (vabs & 3);
+                    const uint32_t dst = tile + q * 512 + (lane >> 1) * 32 + ((((vabs >> 2) ^ (4 * q + (lane >> 3))) & 7) << 2) + (vabs & 3);
 #pragma unroll
                     for (int wd = 0; wd < (T + 7) / 8; ++wd) {
                         const uint32_t other = __shfl_xor_sync(kFullMask, cw[wd], 1);
@@ -251,10 +295,10 @@ __global__ void __launch_bounds__(320, 1) ingest_fast_kernel(IngestParams p, Bou
                         const uint32_t bytes = (((ev >> (4 * q)) & 0x0f0f0f0fu) << 4) | ((od >> (4 * q)) & 0x0f0f0f0fu);
 #pragma unroll
                         for (int i = 0; i < 4; ++i)
-                            if (8 * wd + 2 * i < T) dst[(8 * wd + 2 * i) * 512] = (unsigned char)(bytes >> (8 * i));
+                            if (8 * wd + 2 * i < T) sts_u8(dst + (8 * wd + 2 * i) * 512, bytes >> (8 * i));
                     }
                 } else {
-                    unsigned char *dst = tile + q * 256 + (lane >> 2) * 32 + ((((vabs >> 2) ^ (2 * q + (lane >> 4))) & 7) << 2) + (vabs & 3);
+                    const uint32_t dst = tile + q * 256 + (lane >> 2) * 32 + ((((vabs >> 2) ^ (2 * q + (lane >> 4))) & 7) << 2) + (vabs & 3);
 #pragma unroll
                     for (int wd = 0; wd < (T + 7) / 8; ++wd) {
                         uint32_t bytes = 0;
@@ -263,87 +307,110 @@ __global__ void __launch_bounds__(320, 1) ingest_fast_kernel(IngestParams p, Bou
                             const uint32_t xj = __shfl_sync(kFullMask, cw[wd], (lane & ~3) + j);
                             bytes |= ((xj >> (4 * q)) & 0x00030003u) << (6 - 2 * j);
                         }
-                        dst[(8 * wd) * 256] = (unsigned char)bytes;
-                        if (8 * wd + 4 < T) dst[(8 * wd + 4) * 256] = (unsigned char)(bytes >> 16);
+                        sts_u8(dst + (8 * wd) * 256, bytes);
+                        if (8 * wd + 4 < T) sts_u8(dst + (8 * wd + 4) * 256, bytes >> 16);
                     }
                 }
             }
             asm volatile("fence.proxy.async.shared::cta;" ::: "memory");
             __syncthreads();
         }
-    } else if (warp == V) {
-        // ------------------------------------------------ norms, one wave ahead of the rotation
-        const int vv = lane >> 2, pp = lane & 3;
-        for (int it = 0; it <= nw + 1; ++it) {
-            if (it < nw) {
-                const int64_t slot = vv < V ? wave_slot(it, vv) : -1;
-                float a0 = 0.0f, a1 = 0.0f;
-                if (slot >= 0) {
-                    // chains 2pp and 2pp+1: x[j]^2 summed over j = chain (mod 8) in ascending j (encode.rs:900-932)
-                    const float2 *src = reinterpret_cast<const float2 *>(p.x + (slot - slot_lo) * DIM + 2 * pp);
-#pragma unroll 16
-                    for (int t = 0; t < DIM / 8; ++t) {
-                        const float2 x = __ldg(src + 4 * t);
-                        a0 = __fadd_rn(a0, __fmul_rn(x.x, x.x));
-                        a1 = __fadd_rn(a1, __fmul_rn(x.y, x.y));
-                    }
-                }
-                float s = __fadd_rn(a0, a1);                                  // (c0+c1), (c2+c3), (c4+c5), (c6+c7)
-                s = __fadd_rn(s, __shfl_down_sync(kFullMask, s, 1));          // valid on pp = 0 and pp = 2
-                s = __fadd_rn(s, __shfl_down_sync(kFullMask, s, 2));          // valid on pp = 0
-                if (pp == 0 && vv < V) {
-                    const float nv = __fsqrt_rn(s);
-                    norm_s[(it % 3) * 8 + vv] = nv;
-                    inv_s[(it % 3) * 8 + vv] = nv > kMinNorm ? __fdiv_rn(1.0f, nv) : 0.0f;    // encode.rs:446
-                }
-            }
-            __syncthreads();
-        }
     } else {
-        // ------------------------------------------------ reconstruction sums two waves behind; row staging
-        const int vv = lane >> 2, c = lane & 3;
-        const int gs = 4 / cpb, g0 = c / cpb;                 // group of coordinate c + 4t = gs*t + g0
-        const int shift = (cpb - 1 - (c % cpb)) * field;
-        const uint32_t mask = p.bits == 2 ? 3u : 15u;
-        for (int it = 0; it <= nw + 1; ++it) {
-            const int w = it - 2;
-            if (w >= 0) {
-                const int64_t slot = vv < V ? wave_slot(w, vv) : -1;
-                double acc = 0.0;
-                if (slot >= 0) {
-                    // chain c: rotated[j] * centroid[code[j]] over j = c (mod 4), ascending (encode.rs:1418-1476)
-                    const int vabs = (w % wpb) * V + vv;
-                    const float *row = rows + size_t((w & 1) * V + vv) * stride + c;
-                    const unsigned char *tile = tiles + ((w / wpb) & 1) * tile_bytes + (vabs & 3);
-                    const int wsel = vabs >> 2;
-#pragma unroll 8
-                    for (int t = 0; t < DIM / 4; ++t) {
-                        const int g = gs * t + g0;
-                        const uint32_t byte = tile[g * 32 + (((wsel ^ (g >> 2)) & 7) << 2)];
-                        const double cen = cent64[(byte >> shift) & mask];
-                        acc = __dadd_rn(acc, __dmul_rn(double(row[4 * t]), cen));
+        asm volatile("setmaxnreg.dec.sync.aligned.u32 %0;" ::"n"(kServiceRegs) : "memory");
+        if (warp == V) {
+            // -------------------------------------------- norms, one wave ahead of the rotation
+            const int vv = lane >> 2, pp = lane & 3;
+            for (int it = 0; it <= nw + 1; ++it) {
+                if (it + 1 < nw && lane < V) {
+                    // pull the rows of the next wave into L2: this warp reads them in the next step, the
+                    // bulk copies one step later
+                    const int64_t slot = wave_slot(it + 1, lane);
+                    if (slot >= 0)
+                        asm volatile("cp.async.bulk.prefetch.L2.global [%0], %1;" ::"l"(p.x + (slot - slot_lo) * DIM), "r"(DIM * 4) : "memory");
+                }
+                if (it < nw) {
+                    const int64_t slot = wave_slot(it, vv);
+                    float a0 = 0.0f, a1 = 0.0f;
+                    if (slot >= 0) {
+                        // chains 2pp and 2pp+1: x[j]^2 summed over j = chain (mod 8) in ascending j (encode.rs:900-932)
+                        const float2 *src = reinterpret_cast<const float2 *>(p.x + (slot - slot_lo) * DIM + 2 * pp);
+#pragma unroll 1
+                        for (int t0 = 0; t0 < DIM / 8; t0 += 16) {
+                            float2 x[16];
+#pragma unroll
+                            for (int u = 0; u < 16; ++u) x[u] = __ldg(src + 4 * (t0 + u));
+#pragma unroll
+                            for (int u = 0; u < 16; ++u) {
+                                a0 = __fadd_rn(a0, __fmul_rn(x[u].x, x[u].x));
+                                a1 = __fadd_rn(a1, __fmul_rn(x[u].y, x[u].y));
+                            }
+                        }
+                    }
+                    float s = __fadd_rn(a0, a1);                                  // (c0+c1), (c2+c3), (c4+c5), (c6+c7)
+                    s = __fadd_rn(s, __shfl_down_sync(kFullMask, s, 1));          // valid on pp = 0 and pp = 2
+                    s = __fadd_rn(s, __shfl_down_sync(kFullMask, s, 2));          // valid on pp = 0
+                    if (pp == 0) {
+                        const float nv = __fsqrt_rn(s);
+                        norm_s[(it % 3) * V + vv] = nv;
+                        inv_s[(it % 3) * V + vv] = nv > kMinNorm ? __fdiv_rn(1.0f, nv) : 0.0f;    // encode.rs:446
                     }
                 }
-                acc = __dadd_rn(acc, __shfl_down_sync(kFullMask, acc, 1));
-                acc = __dadd_rn(acc, __shfl_down_sync(kFullMask, acc, 2));    // (c0+c1)+(c2+c3) on c = 0
-                if (c == 0 && slot >= 0)
-                    p.scales[slot] = acc > 0.1 ? __fdiv_rn(norm_s[(w % 3) * 8 + vv], __double2float_rn(acc)) : 0.0f;
+                __syncthreads();
             }
-            __syncwarp();
-            if (it < nw && lane == 0) {
-                // stage the rows of wave `it` into the row set this warp has just finished reading
-                asm volatile("fence.proxy.async.shared::cta;" ::: "memory");
-                uint32_t bytes = 0;
-                for (int v = 0; v < V; ++v) bytes += wave_slot(it, v) >= 0 ? uint32_t(DIM * 4) : 0u;
-                if (bytes) mbar_arrive_expect_tx(&full[it & 1], bytes);
-                else mbar_arrive(&full[it & 1]);
-                for (int v = 0; v < V; ++v) {
-                    const int64_t slot = wave_slot(it, v);
-                    if (slot >= 0)
-                        bulk_load(rows + size_t((it & 1) * V + v) * stride, p.x + (slot - slot_lo) * DIM, DIM * 4, &full[it & 1]);
+        } else if (warp == V + 1) {
+            // -------------------------------------------- reconstruction sums two waves behind; row staging
+            const int vv = lane >> 2, c = lane & 3;
+            const double *tab = table + (c % cpb) * 256;
+            for (int it = 0; it <= nw + 1; ++it) {
+                const int w = it - 2;
+                if (w >= 0) {
+                    const int64_t slot = wave_slot(w, vv);
+                    double acc = 0.0;
+                    if (slot >= 0) {
+                        const int vabs = (w % wpb) * V + vv;
+                        const float *row_c = rows + size_t((w & 1) * V + vv) * stride + c;
+                        const unsigned char *tile_lane = tiles + ((w / wpb) & 1) * tile_bytes + (c / cpb) * 32 + (vabs & 3);
+                        acc = cpb == 2 ? sum_chain<2, DIM>(row_c, tile_lane, vabs >> 2, tab)
+                                       : sum_chain<4, DIM>(row_c, tile_lane, vabs >> 2, tab);
+                    }
+                    acc = __dadd_rn(acc, __shfl_down_sync(kFullMask, acc, 1));
+                    acc = __dadd_rn(acc, __shfl_down_sync(kFullMask, acc, 2));    // (c0+c1)+(c2+c3) on c = 0
+                    if (c == 0 && slot >= 0)
+                        p.scales[slot] = acc > 0.1 ? __fdiv_rn(norm_s[(w % 3) * V + vv], __double2float_rn(acc)) : 0.0f;
                 }
+                __syncwarp();
+                if (it < nw && lane == 0) {
+                    // stage the rows of wave `it` into the row set this warp has just finished reading
+                    asm volatile("fence.proxy.async.shared::cta;" ::: "memory");
+                    uint32_t bytes = 0;
+                    for (int v = 0; v < V; ++v) bytes += wave_slot(it, v) >= 0 ? uint32_t(DIM * 4) : 0u;
+                    if (bytes) mbar_arrive_expect_tx(&full[it & 1], bytes);
+                    else mbar_arrive(&full[it & 1]);
+                    for (int v = 0; v < V; ++v) {
+                        const int64_t slot = wave_slot(it, v);
+                        if (slot >= 0)
+                            bulk_load(rows + size_t((it & 1) * V + v) * stride, p.x + (slot - slot_lo) * DIM, DIM * 4, &full[it & 1]);
+                    }
+                }
+                __syncthreads();
             }
-            __syncthreads();
+        } else {
+            // -------------------------------------------- copy-out of finished tiles
+            const int ct = tid - (V + 2) * 32;                // 0..63
+            for (int it = 0; it <= nw + 1; ++it) {
+                const int wf = it - 2;                        // the wave packed in the previous step
+                if (wf >= 0 && wf % wpb == wpb - 1) {
+                    const uint32_t *t32 = reinterpret_cast<const uint32_t *>(tiles + ((wf / wpb) & 1) * tile_bytes);
+                    uint4 *dst = reinterpret_cast<uint4 *>(p.codes + size_t(first_block + wf / wpb) * tile_bytes);
+#pragma unroll 4
+                    for (int ch = ct; ch < ng * 2; ch += 64) {        // 16-byte chunk ch = half h of row g
+                        const int g = ch >> 1, h4 = (ch & 1) * 4, s = (g >> 2) & 7;
+                        const uint32_t *rowp = t32 + g * 8;
+                        dst[ch] = make_uint4(rowp[(h4 + 0) ^ s], rowp[(h4 + 1) ^ s], rowp[(h4 + 2) ^ s], rowp[(h4 + 3) ^ s]);
+                    }
+                }
+                __syncthreads();
+            }
         }
     }
 }
@@ -363,21 +430,17 @@ cudaError_t launch_ingest_fast(const IngestParams &p, const float *host_boundari
                                cudaStream_t stream) {
     if (p.n <= 0) return cudaSuccess;
     if (p.slot0 % kBlockLanes != 0) return cudaErrorInvalidValue;
-    int V = 8;
-    if (fast_layout(V, p.dim, p.ngroups, false).total > smem_limit) V = 4;
-    const size_t smem = fast_layout(V, p.dim, p.ngroups, false).total;
+    const size_t smem = fast_layout(p.dim, p.ngroups, p.bits == 2 ? 4 : 2).total;
     if (smem > smem_limit) return cudaErrorInvalidValue;
     const int64_t nblocks = (p.n + kBlockLanes - 1) / kBlockLanes;
-    const int per_sm = int(std::max<size_t>(1, std::min<size_t>(4, smem_limit / (smem + 1024))));
-    const unsigned grid = unsigned(std::min<int64_t>(nblocks, int64_t(sm_count) * per_sm));
-    const int threads = (V + 2) * 32;
+    const unsigned grid = unsigned(std::min<int64_t>(nblocks, int64_t(sm_count)));   // one CTA per SM: it owns the register file
     Boundaries15 bnd;
     for (int i = 0; i < 15; ++i) bnd.b[i] = i < (1 << p.bits) - 1 ? host_boundaries[i] : INFINITY;
 #define TV_LAUNCH_FAST(D, L2B, NB)                                                                                   \
     case D: {                                                                                                        \
         cudaError_t e = cudaFuncSetAttribute(ingest_fast_kernel<L2B, NB>, cudaFuncAttributeMaxDynamicSharedMemorySize, int(smem)); \
         if (e != cudaSuccess) return e;                                                                              \
-        ingest_fast_kernel<L2B, NB><<<grid, threads, smem, stream>>>(p, bnd, error, V);                                   \
+        ingest_fast_kernel<L2B, NB><<<grid, kFastThreads, smem, stream>>>(p, bnd, error);                            \
         break;                                                                                                       \
     }
     switch (p.dim) {
