@@ -217,6 +217,12 @@ float tv_last_kernel_ms(const tv_index *h);
  * the ingest kernel for an add — each launch bracketed by its own pair of events; *launches = how many. */
 float tv_last_main_kernel_ms(const tv_index *h, int *launches);
 const char *tv_version(void);
+/* Host-side evaluation of the quantisation grid that the pipelined ingest kernel builds from a codebook's
+ * boundaries (`count` ascending values, at most 15): codes_out[i] = number of boundaries strictly below
+ * values[i] (encode.rs:1447-1451), looked up exactly as the kernel does.  Returns TV_ERR_UNSUPPORTED when the
+ * boundaries admit no grid (the kernel is then not used).  No reference counterpart: it exists so that the
+ * table construction can be checked against a plain count without a device. */
+int tv_quantise_grid_lookup(const float *boundaries, int count, const float *values, size_t n, uint8_t *codes_out);
 
 #ifdef __cplusplus
 }

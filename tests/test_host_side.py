@@ -108,3 +108,38 @@ def test_container_checksum(lib):
     assert lib.tv_crc32c(big.ctypes.data_as(ctypes.c_void_p), big.size) == want
     small = big[:4095].copy()
     assert lib.tv_crc32c(small.ctypes.data_as(ctypes.c_void_p), small.size) == crc32c(small.tobytes())
+
+
+@pytest.mark.parametrize("dim,bits", [(128, 4), (256, 2), (384, 3), (768, 4), (1024, 2), (1536, 4), (1536, 3), (2048, 4), (2048, 2)])
+def test_quantisation_grid_counts_boundaries_exactly(lib, dim, bits):
+    """The pipelined ingest kernel quantises through a grid table; its lookup must equal the plain count of
+    boundaries strictly below the value for every float, in particular at and next to each boundary."""
+    from oracle import oracle as O
+    b, _ = O.codebook(bits, dim)
+    rng = np.random.default_rng(dim * 10 + bits)
+    near = np.concatenate([np.nextafter(b, np.float32(-np.inf)), b, np.nextafter(b, np.float32(np.inf))])
+    for _ in range(3):
+        near = np.concatenate([near, np.nextafter(near, np.float32(-np.inf)), np.nextafter(near, np.float32(np.inf))])
+    spread = (rng.standard_normal(200_000) / np.sqrt(dim)).astype(np.float32)
+    wide = rng.uniform(-1.5, 1.5, 20_000).astype(np.float32)
+    edge = np.array([0.0, -0.0, 1.0, -1.0, 1e-30, -1e-30, 3e16, -3e16, 1e-45, -1e-45], dtype=np.float32)
+    mids = ((b[:-1].astype(np.float64) + b[1:]) / 2).astype(np.float32)
+    x = np.ascontiguousarray(np.concatenate([near, spread, wide, edge, mids]).astype(np.float32))
+    want = (x[:, None] > b[None, :]).sum(axis=1).astype(np.uint8)
+    got = np.empty(x.size, dtype=np.uint8)
+    bb = np.ascontiguousarray(b)
+    rc = lib.tv_quantise_grid_lookup(bb.ctypes.data_as(ctypes.POINTER(ctypes.c_float)), bb.size,
+                                     x.ctypes.data_as(ctypes.POINTER(ctypes.c_float)), x.size,
+                                     got.ctypes.data_as(ctypes.POINTER(ctypes.c_uint8)))
+    assert rc == 0
+    assert np.array_equal(got, want), np.flatnonzero(got != want)[:10]
+
+
+def test_quantisation_grid_refuses_crowded_boundaries(lib):
+    b = np.array([0.0, 1e-9, 1.0], dtype=np.float32)     # two boundaries inside one cell
+    out = np.empty(1, dtype=np.uint8)
+    x = np.zeros(1, dtype=np.float32)
+    rc = lib.tv_quantise_grid_lookup(b.ctypes.data_as(ctypes.POINTER(ctypes.c_float)), 3,
+                                     x.ctypes.data_as(ctypes.POINTER(ctypes.c_float)), 1,
+                                     out.ctypes.data_as(ctypes.POINTER(ctypes.c_uint8)))
+    assert rc == 93   # TV_ERR_UNSUPPORTED: the index then keeps to the block-at-a-time kernel

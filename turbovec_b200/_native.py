@@ -19,6 +19,7 @@ _H = C.c_void_p
 # name -> (restype, argtypes); every symbol declared in include/turbovec_b200.h
 SIGNATURES = {
     "tv_version": (C.c_char_p, []),
+    "tv_quantise_grid_lookup": (C.c_int, [C.POINTER(C.c_float), C.c_int, C.POINTER(C.c_float), C.c_size_t, C.POINTER(C.c_uint8)]),
     "tv_index_create": (C.c_int, [C.c_size_t, C.c_int, C.c_int, C.c_int, C.POINTER(_H)]),
     "tv_index_destroy": (None, [_H]),
     "tv_last_error": (C.c_char_p, [_H]),

@@ -112,6 +112,8 @@ struct tv_index {
     std::vector<float> shift, scale_tq;      // empty = uncalibrated
     DeviceArray<uint16_t> d_perm;            // [2][dim]
     DeviceArray<float> d_codebook;           // boundaries (16 slots) then centroids (16 slots)
+    DeviceArray<uint2> d_qgrid;              // quantisation grid of the pipelined ingest kernel
+    QuantGrid qgrid;                         // cells == nullptr: the codebook has no valid grid
     DeviceArray<float> d_calib;              // shift, scale, inv_scale  [3][dim]
     float level_scale = 1.f;                 // cs of the permute-dot level table
     int8_t levels[16] = {0};
@@ -219,6 +221,14 @@ int upload_codebook(tv_index *h) {
     for (size_t i = 0; i < h->cb.centroids.size(); ++i) cbuf[16 + i] = h->cb.centroids[i];
     TV_CUDA(h->d_codebook.reserve(32));
     TV_CUDA(cudaMemcpyAsync(h->d_codebook.ptr, cbuf, sizeof cbuf, cudaMemcpyHostToDevice, h->stream));
+    QuantGridHost grid;
+    h->qgrid = QuantGrid{};
+    if (build_quant_grid(h->cb.boundaries.data(), int(h->cb.boundaries.size()), grid)) {
+        static_assert(sizeof(QuantCell) == sizeof(uint2), "grid cells are uploaded as they are");
+        TV_CUDA(h->d_qgrid.reserve(grid.cells.size()));
+        TV_CUDA(cudaMemcpyAsync(h->d_qgrid.ptr, grid.cells.data(), grid.cells.size() * sizeof(uint2), cudaMemcpyHostToDevice, h->stream));
+        h->qgrid.cells = h->d_qgrid.ptr; h->qgrid.a = grid.a; h->qgrid.b = grid.b;
+    }
     TV_CUDA(cudaStreamSynchronize(h->stream));
     if (h->bits == 4) {
         // search.rs:2812-2819: cs = cmax/127, level = clamp(round(c/cs), +-127)
@@ -394,7 +404,8 @@ int add_rows(tv_index *h, const float *x, size_t n, size_t dim, bool on_device) 
         // rows that complete a partly filled block go through the block-at-a-time kernel, whole blocks
         // through the pipelined one where it applies
         int64_t head = rows;
-        if (h->ingest_pipeline && ingest_fast_supported(int(dim), h->bits, p.shift != nullptr, src))
+        if (h->ingest_pipeline && h->qgrid.cells != nullptr &&
+            ingest_fast_supported(int(dim), h->bits, h->ngroups, p.shift != nullptr, src, h->smem_limit))
             head = std::min<int64_t>(int64_t(rows), (kBlockLanes - p.slot0 % kBlockLanes) % kBlockLanes);
         if (head > 0) {
             p.n = head;
@@ -406,7 +417,7 @@ int add_rows(tv_index *h, const float *x, size_t n, size_t dim, bool on_device) 
         if (int64_t(rows) > head) {
             p.x = src + head * int64_t(dim); p.n = int64_t(rows) - head; p.slot0 += head; p.row_base += head;
             mark_begin(h);
-            TV_CUDA(launch_ingest_fast(p, h->cb.boundaries.data(), h->sm_count, h->smem_limit, &h->d_flags->error, h->stream));
+            TV_CUDA(launch_ingest_fast(p, h->qgrid, h->sm_count, h->smem_limit, &h->d_flags->error, h->stream));
             mark_end(h);
             h->launches++;
         }
@@ -740,6 +751,14 @@ void blocked_to_packed(const uint8_t *blocked, size_t n, int bits, int dim, uint
 extern "C" {
 
 const char *tv_version(void) { return "turbovec_b200 0.1 (sm_100a)"; }
+
+int tv_quantise_grid_lookup(const float *boundaries, int count, const float *values, size_t n, uint8_t *codes_out) {
+    if (!boundaries || (n && (!values || !codes_out))) return TV_ERR_INVALID_ARGUMENT;
+    QuantGridHost grid;
+    if (!build_quant_grid(boundaries, count, grid)) return TV_ERR_UNSUPPORTED;
+    for (size_t i = 0; i < n; ++i) codes_out[i] = uint8_t(quant_grid_code(grid, values[i]));
+    return TV_OK;
+}
 
 int tv_index_create(size_t dim, int bit_width, int kind, int device, tv_index **out) {
     tv_index *h = nullptr;

@@ -4,6 +4,7 @@
 
 #include <cstddef>
 #include <cstdint>
+#include <vector>
 
 namespace tv {
 
@@ -37,11 +38,25 @@ int ingest_vectors_per_pass(int dim, int ngroups, size_t smem_limit);
 cudaError_t launch_ingest(const IngestParams &p, int vectors_per_pass, cudaStream_t stream);
 
 // Pipelined form (ingest_fast.cu) for whole code blocks: p.slot0 a multiple of 32, no calibration, no
-// rotate-only mode, x 16-byte aligned, dim one of the instantiated sizes.  `error` receives a non-zero
-// code if a bounded wait inside the kernel gives up.
-bool ingest_fast_supported(int dim, int bits, bool calibrated, const void *x);
-// `host_boundaries`: the 2^bits - 1 codebook boundaries in host memory (they travel as kernel arguments).
-cudaError_t launch_ingest_fast(const IngestParams &p, const float *host_boundaries, int sm_count, size_t smem_limit, uint32_t *error,
+// rotate-only mode, x 16-byte aligned, dim one of the instantiated sizes, shared memory within the limit.
+// It quantises through a grid table built once per codebook: cell c holds the number of boundaries in lower
+// cells (times 8) and the one boundary inside the cell (f32 bits; FLT_MAX when there is none).
+struct QuantCell { uint32_t boundary_bits, code8; };
+struct QuantGridHost {
+    float a = 0.f, b = 0.f;              // cell of x = f(sat(x * a + b)), see grid_offset
+    std::vector<QuantCell> cells;        // 1024 entries
+};
+struct QuantGrid {                       // device view, passed to the kernel by value
+    const uint2 *cells = nullptr;
+    float a = 0.f, b = 0.f;
+};
+// False when two boundaries share a cell or the boundaries are not strictly ascending and finite; the
+// caller then keeps to launch_ingest.
+bool build_quant_grid(const float *boundaries, int count, QuantGridHost &out);
+uint32_t quant_grid_code(const QuantGridHost &grid, float x);   // host evaluation, the kernel's lookup
+bool ingest_fast_supported(int dim, int bits, int ngroups, bool calibrated, const void *x, size_t smem_limit);
+// `error` receives a non-zero code if a bounded wait inside the kernel gives up.
+cudaError_t launch_ingest_fast(const IngestParams &p, const QuantGrid &grid, int sm_count, size_t smem_limit, uint32_t *error,
                                cudaStream_t stream);
 
 }  // namespace tv

@@ -5,20 +5,25 @@
 //
 // One CTA of three warpgroups walks a contiguous range of code blocks in waves of 8 vectors and runs its
 // stages concurrently, one wave apart, with one CTA barrier per step:
-//   norm warp      wave i     8 sequential f32 chains per vector straight from global memory (4 lanes per
+//   norm warps     wave i     8 sequential f32 chains per vector straight from global memory (4 lanes per
 //                             vector, two chains per lane), fixed combine tree, sqrt, reciprocal
 //   8 rotation     wave i-1   one warp per vector, the whole vector in registers: both rounds of permutation,
 //   warps                     sign flip and Walsh-Hadamard butterflies (rotation.cuh states the order rules),
-//                             Lloyd-Max quantisation by a register binary search, packing into the block tile
+//                             Lloyd-Max quantisation through a grid table (QuantGrid), packing into the block tile
 //   sum warp       wave i-2   4 sequential f64 chains per vector over the rotated row and the codes, scale;
 //                             then issues the bulk copies that stage wave i's rows into shared memory
-//   2 copy warps              write the finished tile of a block (ngroups x 32 bytes, word-swizzled so that the
+//   copy warp                 writes the finished tile of a block (ngroups x 32 bytes, word-swizzled so that the
 //                             byte stores of a warp never share a bank) to the code array
+// The norm stage alternates between two warps (even and odd waves), each starting a step early: its loads
+// come from global memory and the chains of a wave need a dozen dependent round trips.
 // Rows arrive by cp.async.bulk with an mbarrier transaction count.  The two rotation warpgroups take the
 // registers the third one gives up (setmaxnreg), so a 2048-coordinate vector and its permutation entries
 // stay in registers.
 #include <algorithm>
 #include <cmath>
+#include <cstring>
+#include <limits>
+#include <vector>
 
 #include "ingest.cuh"
 #include "tv_common.cuh"
@@ -68,6 +73,16 @@ __device__ __forceinline__ float lds_f32(uint32_t addr) {
 __device__ __forceinline__ void sts_f32(uint32_t addr, float v) {
     asm volatile("st.shared.f32 [%0], %1;" ::"r"(addr), "f"(v) : "memory");
 }
+__device__ __forceinline__ uint2 lds_u2(uint32_t addr) {
+    uint2 v;
+    asm volatile("ld.shared.v2.u32 {%0, %1}, [%2];" : "=r"(v.x), "=r"(v.y) : "r"(addr));
+    return v;
+}
+__device__ __forceinline__ double lds_f64(uint32_t addr) {
+    double v;
+    asm volatile("ld.shared.f64 %0, [%1];" : "=d"(v) : "r"(addr));
+    return v;
+}
 __device__ __forceinline__ void sts_u8(uint32_t addr, uint32_t v) {
     asm volatile("st.shared.u8 [%0], %1;" ::"r"(addr), "r"(v) : "memory");
 }
@@ -77,42 +92,51 @@ __device__ __forceinline__ float max_nan(float a, float b) {   // NaN wins, unli
     return d;
 }
 
+
 constexpr int kWave = 8;                 // vectors per wave = rotation warps
 constexpr int kWavesPerBlock = kBlockLanes / kWave;
-constexpr int kFastThreads = 384;        // 8 rotation warps, norm warp, sum warp, 2 copy warps
+constexpr int kFastThreads = 384;        // 8 rotation warps; norm (even waves), sum, norm (odd waves), copy
 constexpr int kRotationRegs = 208, kServiceRegs = 88;   // 8*32*208 + 4*32*88 <= 384 * 168
+constexpr int kGridCells = 1024;         // cells of the quantisation grid
+constexpr float kGridTop = 8.0f * (kGridCells - 1);
+constexpr float kGridMagic = 8388608.0f; // 2^23: adding it leaves the rounded integer in the low mantissa bits
+
+// Byte offset (cell * 8) of x in the quantisation grid.  Any monotone non-decreasing map works for the
+// argument in build_quant_grid; this one costs two FMAs and a mask.
+__host__ __device__ inline uint32_t grid_offset(float x, float a, float b) {
+#ifdef __CUDA_ARCH__
+    const float u = __saturatef(__fmaf_rn(x, a, b));
+    return __float_as_uint(__fmaf_rn(u, kGridTop, kGridMagic)) & (8u * (kGridCells - 1));
+#else
+    float u = std::fmaf(x, a, b);
+    u = u > 0.0f ? (u < 1.0f ? u : 1.0f) : 0.0f;        // NaN -> 0, like the saturating FMA
+    const float v = std::fmaf(u, kGridTop, kGridMagic);
+    uint32_t bits;
+    std::memcpy(&bits, &v, 4);
+    return bits & (8u * (kGridCells - 1));
+#endif
+}
 
 struct FastLayout {
     int stride;          // floats per staged row: dim + 4 keeps the sum warp's 4-lane reads on distinct banks
-    size_t rows, tile, table, norm, inv, bars, total;
+    int cstride;         // bytes per row of centroid offsets: dim + 16 does the same for its byte reads
+    size_t grid, cent, rows, tile, coff, norm, inv, bars, total;
 };
-__host__ __device__ inline FastLayout fast_layout(int dim, int ngroups, int cpb) {
+__host__ __device__ inline FastLayout fast_layout(int dim, int ngroups) {
     FastLayout L;
     L.stride = dim + 4;
+    L.cstride = dim + 16;
     size_t off = 0;
+    L.grid = off; off += size_t(kGridCells) * 8;       // first, so that its address is a link-time constant
+    L.cent = off; off += 16 * 8;                       // centroids as f64
     L.rows = off; off += size_t(2) * kWave * L.stride * 4;
     L.tile = off; off += size_t(2) * ngroups * 32;
-    L.table = off; off += size_t(cpb) * 256 * 8;     // centroid (as f64) of field k of every byte value
-    L.norm = off; off += 3 * kWave * 4;
-    L.inv = off; off += 3 * kWave * 4;
+    L.coff = off; off += size_t(2) * kWave * L.cstride; // per coordinate: 8 * code = byte offset into `cent`
+    L.norm = off; off += 4 * kWave * 4;
+    L.inv = off; off += 4 * kWave * 4;
     L.bars = off; off += 2 * 8;
     L.total = off;
     return L;
-}
-
-// Register binary search: number of boundaries strictly below x (encode.rs:1447-1451).  b holds the
-// boundaries of a 2-, 3- or 4-bit codebook padded to 15 entries with +inf, which steers the upper levels
-// of the search into the populated part.
-struct Boundaries15 { float b[15]; };   // passed by value: the search then takes them as constant-bank operands
-__device__ __forceinline__ uint32_t quantise15(float x, const float (&b)[15]) {
-    const bool p1 = x > b[7];
-    const bool p2 = x > (p1 ? b[11] : b[3]);
-    const float u0 = p2 ? b[5] : b[1], u1 = p2 ? b[13] : b[9];
-    const bool p3 = x > (p1 ? u1 : u0);
-    const float w0 = p3 ? b[2] : b[0], w1 = p3 ? b[6] : b[4], w2 = p3 ? b[10] : b[8], w3 = p3 ? b[14] : b[12];
-    const float y0 = p2 ? w1 : w0, y1 = p2 ? w3 : w2;
-    const bool p4 = x > (p1 ? y1 : y0);
-    return (p1 ? 8u : 0u) + (p2 ? 4u : 0u) + (p3 ? 2u : 0u) + (p4 ? 1u : 0u);
 }
 
 // Walsh-Hadamard transform of NBLK blocks of 32*R coordinates; v[b*R + r] holds coordinate r*32 + lane of
@@ -145,34 +169,9 @@ __device__ __forceinline__ void wht_blocks(float (&v)[R * NBLK], const float (&s
     }
 }
 
-// The 4 sequential f64 chains of 8 vectors: lane = (vector vv, chain c), chain c sums
-// rotated[j] * centroid[code[j]] over j = c (mod 4) in ascending j (encode.rs:1418-1476).  `tab` maps a
-// tile byte straight to the centroid of this chain's field; the word swizzle of the tile repeats every 32
-// groups, so inside a window of 32 groups every offset is a compile-time constant.
-template <int CPB, int DIM>
-__device__ __forceinline__ double sum_chain(const float *row_c, const unsigned char *tile_lane, int wsel, const double *tab) {
-    constexpr int GS = 4 / CPB;                 // groups advanced per step
-    constexpr int SW = 32 / GS;                 // steps per window of 32 groups
-    const unsigned char *ps[8];
-#pragma unroll
-    for (int s = 0; s < 8; ++s) ps[s] = tile_lane + (((wsel ^ s) & 7) << 2);
-    double acc = 0.0;
-#pragma unroll 1
-    for (int wnd = 0; wnd < DIM / 4 / SW; ++wnd) {
-#pragma unroll
-        for (int u = 0; u < SW; ++u) {
-            const uint32_t byte = ps[((GS * u) >> 2) & 7][GS * u * 32];
-            acc = __dadd_rn(acc, __dmul_rn(double(row_c[4 * u]), tab[byte]));
-        }
-#pragma unroll
-        for (int s = 0; s < 8; ++s) ps[s] += 1024;
-        row_c += 4 * SW;
-    }
-    return acc;
-}
 
 template <int LOG2B, int NBLK>
-__global__ void __launch_bounds__(kFastThreads, 1) ingest_fast_kernel(IngestParams p, Boundaries15 bnd, uint32_t *error) {
+__global__ void __launch_bounds__(kFastThreads, 1) ingest_fast_kernel(IngestParams p, QuantGrid grid, uint32_t *error) {
     constexpr int R = 1 << (LOG2B - 5);               // registers per Hadamard block and lane
     constexpr int T = R * NBLK;                       // registers per vector and lane
     constexpr int DIM = T * 32;
@@ -181,16 +180,15 @@ __global__ void __launch_bounds__(kFastThreads, 1) ingest_fast_kernel(IngestPara
     extern __shared__ __align__(128) unsigned char smem[];
     const int ng = p.ngroups;
     const int cpb = p.bits == 2 ? 4 : 2;              // codes per byte (3-bit codes sit in 4-bit fields)
-    const int field = 8 / cpb;
-    const FastLayout L = fast_layout(DIM, ng, cpb);
+    const FastLayout L = fast_layout(DIM, ng);
     float *rows = reinterpret_cast<float *>(smem + L.rows);
     unsigned char *tiles = smem + L.tile;
-    double *table = reinterpret_cast<double *>(smem + L.table);   // [cpb][256]
-    float *norm_s = reinterpret_cast<float *>(smem + L.norm);     // [3][8]
-    float *inv_s = reinterpret_cast<float *>(smem + L.inv);       // [3][8]
+    unsigned char *coffs = smem + L.coff;
+    float *norm_s = reinterpret_cast<float *>(smem + L.norm);     // [4][8]
+    float *inv_s = reinterpret_cast<float *>(smem + L.inv);       // [4][8]
     uint64_t *full = reinterpret_cast<uint64_t *>(smem + L.bars); // [2]
     const int tid = threadIdx.x, warp = tid >> 5, lane = tid & 31;
-    const int stride = L.stride;
+    const int stride = L.stride, cstride = L.cstride;
     const int tile_bytes = ng * 32;
 
     const int64_t slot_lo = p.slot0, slot_hi = p.slot0 + p.n;       // slot_lo is a multiple of 32
@@ -204,10 +202,8 @@ __global__ void __launch_bounds__(kFastThreads, 1) ingest_fast_kernel(IngestPara
         mbar_init(&full[1], 1);
         asm volatile("fence.mbarrier_init.release.cluster;" ::: "memory");
     }
-    for (int i = tid; i < cpb * 256; i += kFastThreads) {
-        const int k = i >> 8, byte = i & 255;
-        table[i] = double(p.centroids[(byte >> ((cpb - 1 - k) * field)) & ((1 << field) - 1)]);   // the codebook array has 16 slots
-    }
+    for (int i = tid; i < kGridCells; i += kFastThreads) reinterpret_cast<uint2 *>(smem + L.grid)[i] = grid.cells[i];
+    if (tid < 16) reinterpret_cast<double *>(smem + L.cent)[tid] = double(p.centroids[tid]);   // the array has 16 slots
     __syncthreads();
 
     // slot of vector `v` of wave `w`, or -1 past the new rows (padding lanes of the last block)
@@ -229,6 +225,8 @@ __global__ void __launch_bounds__(kFastThreads, 1) ingest_fast_kernel(IngestPara
 #pragma unroll
         for (int s = 0; s < 5; ++s) sgn[s] = (lane >> s) & 1 ? -1.0f : 1.0f;
         const float isb = p.inv_sqrt_block;
+        const float ga = grid.a, gb = grid.b;
+        const uint32_t grid_base = smem_u32(smem + L.grid);
         const int q = lane & (cpb - 1);               // this lane packs the registers k = q (mod cpb)
 
         for (int it = 0; it <= nw + 1; ++it) {
@@ -241,7 +239,8 @@ __global__ void __launch_bounds__(kFastThreads, 1) ingest_fast_kernel(IngestPara
                 float *row = rows + size_t((w & 1) * V + warp) * stride;
                 if (slot >= 0 && mbar_wait(&full[w & 1], (w >> 1) & 1, error)) {
                     const uint32_t rb = smem_u32(row), rl = rb + lane * 4;
-                    const float inv = inv_s[(w % 3) * V + warp];
+                    const uint32_t cl = smem_u32(coffs + size_t((w & 1) * V + warp) * cstride) + lane;
+                    const float inv = inv_s[(w & 3) * V + warp];
                     // keeps the masks and offsets derived from pk from being hoisted out of the wave loop into
                     // four registers per entry
 #pragma unroll
@@ -279,7 +278,12 @@ __global__ void __launch_bounds__(kFastThreads, 1) ingest_fast_kernel(IngestPara
                     for (int k = 0; k < T; ++k) {
                         const float y = __fmul_rn(v[k], isb);
                         sts_f32(rl + k * 128, y);                     // rotated row, read by the sum warp
-                        cw[k >> 3] |= quantise15(y, bnd.b) << (4 * (k & 7));
+                        // code = number of boundaries strictly below y (encode.rs:1447-1451): the cell of y
+                        // knows how many lie in lower cells and the one boundary, if any, inside the cell
+                        const uint2 cell = lds_u2(grid_base + grid_offset(y, ga, gb));
+                        const uint32_t code8 = cell.y + (y > __uint_as_float(cell.x) ? 8u : 0u);   // 8 * code
+                        sts_u8(cl + k * 32, code8);
+                        cw[k >> 3] += (k & 7) == 0 ? code8 >> 3 : code8 * (1u << (4 * (k & 7) - 3));
                     }
                 }
                 // pack: byte of group g = codes of coordinates g*cpb .. g*cpb+cpb-1, first one in the top field
@@ -317,93 +321,118 @@ __global__ void __launch_bounds__(kFastThreads, 1) ingest_fast_kernel(IngestPara
         }
     } else {
         asm volatile("setmaxnreg.dec.sync.aligned.u32 %0;" ::"n"(kServiceRegs) : "memory");
-        if (warp == V) {
-            // -------------------------------------------- norms, one wave ahead of the rotation
+        if (warp == V || warp == V + 2) {
+            // -------------------------------------------- norms: this warp takes the waves of one parity and
+            // spreads each over two steps (first half of the chains in step w - 1, second half in step w)
+            const int parity = warp == V ? 0 : 1;
             const int vv = lane >> 2, pp = lane & 3;
+            float a0 = 0.0f, a1 = 0.0f;
             for (int it = 0; it <= nw + 1; ++it) {
-                if (it + 1 < nw && lane < V) {
-                    // pull the rows of the next wave into L2: this warp reads them in the next step, the
-                    // bulk copies one step later
-                    const int64_t slot = wave_slot(it + 1, lane);
-                    if (slot >= 0)
-                        asm volatile("cp.async.bulk.prefetch.L2.global [%0], %1;" ::"l"(p.x + (slot - slot_lo) * DIM), "r"(DIM * 4) : "memory");
-                }
-                if (it < nw) {
-                    const int64_t slot = wave_slot(it, vv);
-                    float a0 = 0.0f, a1 = 0.0f;
+                const bool second = (it & 1) == parity;               // else: first half of wave it + 1
+                const int w = second ? it : it + 1;
+                if (w < nw) {
+                    if (!second && w + 2 < nw && lane < V) {
+                        // pull this warp's next wave into L2
+                        const int64_t slot = wave_slot(w + 2, lane);
+                        if (slot >= 0)
+                            asm volatile("cp.async.bulk.prefetch.L2.global [%0], %1;" ::"l"(p.x + (slot - slot_lo) * DIM), "r"(DIM * 4) : "memory");
+                    }
+                    const int64_t slot = wave_slot(w, vv);
+                    // chains 2pp and 2pp+1: x[j]^2 summed over j = chain (mod 8) in ascending j (encode.rs:900-932)
+                    const bool whole = second && it == 0;             // wave 0 has no earlier step
+                    if (!second || whole) { a0 = 0.0f; a1 = 0.0f; }
                     if (slot >= 0) {
-                        // chains 2pp and 2pp+1: x[j]^2 summed over j = chain (mod 8) in ascending j (encode.rs:900-932)
                         const float2 *src = reinterpret_cast<const float2 *>(p.x + (slot - slot_lo) * DIM + 2 * pp);
+                        const int t_begin = second && !whole ? DIM / 16 : 0, t_end = second ? DIM / 8 : DIM / 16;
 #pragma unroll 1
-                        for (int t0 = 0; t0 < DIM / 8; t0 += 16) {
-                            float2 x[16];
+                        for (int t0 = t_begin; t0 < t_end; t0 += 8) {
+                            float2 x[8];
 #pragma unroll
-                            for (int u = 0; u < 16; ++u) x[u] = __ldg(src + 4 * (t0 + u));
+                            for (int u = 0; u < 8; ++u) x[u] = __ldg(src + 4 * (t0 + u));
 #pragma unroll
-                            for (int u = 0; u < 16; ++u) {
+                            for (int u = 0; u < 8; ++u) {
                                 a0 = __fadd_rn(a0, __fmul_rn(x[u].x, x[u].x));
                                 a1 = __fadd_rn(a1, __fmul_rn(x[u].y, x[u].y));
                             }
                         }
                     }
-                    float s = __fadd_rn(a0, a1);                                  // (c0+c1), (c2+c3), (c4+c5), (c6+c7)
-                    s = __fadd_rn(s, __shfl_down_sync(kFullMask, s, 1));          // valid on pp = 0 and pp = 2
-                    s = __fadd_rn(s, __shfl_down_sync(kFullMask, s, 2));          // valid on pp = 0
-                    if (pp == 0) {
-                        const float nv = __fsqrt_rn(s);
-                        norm_s[(it % 3) * V + vv] = nv;
-                        inv_s[(it % 3) * V + vv] = nv > kMinNorm ? __fdiv_rn(1.0f, nv) : 0.0f;    // encode.rs:446
+                    if (second) {
+                        float s = __fadd_rn(a0, a1);                              // (c0+c1), (c2+c3), (c4+c5), (c6+c7)
+                        s = __fadd_rn(s, __shfl_down_sync(kFullMask, s, 1));      // valid on pp = 0 and pp = 2
+                        s = __fadd_rn(s, __shfl_down_sync(kFullMask, s, 2));      // valid on pp = 0
+                        if (pp == 0) {
+                            const float nv = __fsqrt_rn(s);
+                            norm_s[(w & 3) * V + vv] = nv;
+                            inv_s[(w & 3) * V + vv] = nv > kMinNorm ? __fdiv_rn(1.0f, nv) : 0.0f;    // encode.rs:446
+                        }
                     }
                 }
                 __syncthreads();
             }
         } else if (warp == V + 1) {
             // -------------------------------------------- reconstruction sums two waves behind; row staging
+            // lane = (vector vv, chain c); chain c sums rotated[j] * centroid[code[j]] over j = c (mod 4) in
+            // ascending j, the four chains combine as (c0+c1)+(c2+c3) (encode.rs:1418-1476).  Both factors are
+            // f32 values, so their f64 product is exact and one fused multiply-add rounds exactly like the
+            // reference's multiply followed by an add.
             const int vv = lane >> 2, c = lane & 3;
-            const double *tab = table + (c % cpb) * 256;
+            const uint32_t cent_base = smem_u32(smem + L.cent);
             for (int it = 0; it <= nw + 1; ++it) {
                 const int w = it - 2;
                 if (w >= 0) {
                     const int64_t slot = wave_slot(w, vv);
                     double acc = 0.0;
                     if (slot >= 0) {
-                        const int vabs = (w % wpb) * V + vv;
                         const float *row_c = rows + size_t((w & 1) * V + vv) * stride + c;
-                        const unsigned char *tile_lane = tiles + ((w / wpb) & 1) * tile_bytes + (c / cpb) * 32 + (vabs & 3);
-                        acc = cpb == 2 ? sum_chain<2, DIM>(row_c, tile_lane, vabs >> 2, tab)
-                                       : sum_chain<4, DIM>(row_c, tile_lane, vabs >> 2, tab);
+                        const unsigned char *off_c = coffs + size_t((w & 1) * V + vv) * cstride + c;
+                        uint32_t o[8];
+                        float x[8];
+#pragma unroll
+                        for (int u = 0; u < 8; ++u) { o[u] = off_c[4 * u]; x[u] = row_c[4 * u]; }
+#pragma unroll 1
+                        for (int t0 = 0; t0 < DIM / 4; t0 += 8) {
+                            double cen[8];
+                            float xc[8];
+#pragma unroll
+                            for (int u = 0; u < 8; ++u) { cen[u] = lds_f64(cent_base + o[u]); xc[u] = x[u]; }
+                            if (t0 + 8 < DIM / 4) {
+#pragma unroll
+                                for (int u = 0; u < 8; ++u) { o[u] = off_c[4 * (t0 + 8 + u)]; x[u] = row_c[4 * (t0 + 8 + u)]; }
+                            }
+#pragma unroll
+                            for (int u = 0; u < 8; ++u) acc = __fma_rn(double(xc[u]), cen[u], acc);
+                        }
                     }
                     acc = __dadd_rn(acc, __shfl_down_sync(kFullMask, acc, 1));
                     acc = __dadd_rn(acc, __shfl_down_sync(kFullMask, acc, 2));    // (c0+c1)+(c2+c3) on c = 0
                     if (c == 0 && slot >= 0)
-                        p.scales[slot] = acc > 0.1 ? __fdiv_rn(norm_s[(w % 3) * V + vv], __double2float_rn(acc)) : 0.0f;
+                        p.scales[slot] = acc > 0.1 ? __fdiv_rn(norm_s[(w & 3) * V + vv], __double2float_rn(acc)) : 0.0f;
                 }
                 __syncwarp();
-                if (it < nw && lane == 0) {
+                if (it < nw) {
                     // stage the rows of wave `it` into the row set this warp has just finished reading
-                    asm volatile("fence.proxy.async.shared::cta;" ::: "memory");
-                    uint32_t bytes = 0;
-                    for (int v = 0; v < V; ++v) bytes += wave_slot(it, v) >= 0 ? uint32_t(DIM * 4) : 0u;
-                    if (bytes) mbar_arrive_expect_tx(&full[it & 1], bytes);
-                    else mbar_arrive(&full[it & 1]);
-                    for (int v = 0; v < V; ++v) {
-                        const int64_t slot = wave_slot(it, v);
-                        if (slot >= 0)
-                            bulk_load(rows + size_t((it & 1) * V + v) * stride, p.x + (slot - slot_lo) * DIM, DIM * 4, &full[it & 1]);
+                    const int64_t slot = lane < V ? wave_slot(it, lane) : -1;
+                    const uint32_t live = __ballot_sync(kFullMask, slot >= 0);
+                    if (lane == 0) {
+                        asm volatile("fence.proxy.async.shared::cta;" ::: "memory");
+                        if (live) mbar_arrive_expect_tx(&full[it & 1], uint32_t(__popc(live)) * uint32_t(DIM * 4));
+                        else mbar_arrive(&full[it & 1]);
                     }
+                    __syncwarp();
+                    if (slot >= 0)
+                        bulk_load(rows + size_t((it & 1) * V + lane) * stride, p.x + (slot - slot_lo) * DIM, DIM * 4, &full[it & 1]);
                 }
                 __syncthreads();
             }
         } else {
             // -------------------------------------------- copy-out of finished tiles
-            const int ct = tid - (V + 2) * 32;                // 0..63
             for (int it = 0; it <= nw + 1; ++it) {
                 const int wf = it - 2;                        // the wave packed in the previous step
                 if (wf >= 0 && wf % wpb == wpb - 1) {
                     const uint32_t *t32 = reinterpret_cast<const uint32_t *>(tiles + ((wf / wpb) & 1) * tile_bytes);
                     uint4 *dst = reinterpret_cast<uint4 *>(p.codes + size_t(first_block + wf / wpb) * tile_bytes);
 #pragma unroll 4
-                    for (int ch = ct; ch < ng * 2; ch += 64) {        // 16-byte chunk ch = half h of row g
+                    for (int ch = lane; ch < ng * 2; ch += 32) {      // 16-byte chunk ch = half h of row g
                         const int g = ch >> 1, h4 = (ch & 1) * 4, s = (g >> 2) & 7;
                         const uint32_t *rowp = t32 + g * 8;
                         dst[ch] = make_uint4(rowp[(h4 + 0) ^ s], rowp[(h4 + 1) ^ s], rowp[(h4 + 2) ^ s], rowp[(h4 + 3) ^ s]);
@@ -417,30 +446,70 @@ __global__ void __launch_bounds__(kFastThreads, 1) ingest_fast_kernel(IngestPara
 
 }  // namespace
 
-bool ingest_fast_supported(int dim, int bits, bool calibrated, const void *x) {
+// For every boundary: the grid cell it falls in.  grid_offset is monotone non-decreasing in x, so for a
+// value x in cell c every boundary in a lower cell is below x and every boundary in a higher cell is not;
+// only a boundary in cell c itself needs the exact comparison.  The table is valid when no two boundaries
+// share a cell; then code(x) = lower[c] + (x > inside[c]).
+bool build_quant_grid(const float *boundaries, int count, QuantGridHost &out) {
+    if (count < 1 || count > 15) return false;
+    for (int i = 0; i + 1 < count; ++i)
+        if (!(boundaries[i] < boundaries[i + 1])) return false;
+    const float lo = boundaries[0], hi = boundaries[count - 1];
+    const float pad = count > 1 ? (hi - lo) / 64.0f : 1.0f;
+    const float span = (hi - lo) + 2.0f * pad;
+    if (!(span > 0.0f) || !std::isfinite(span)) return false;
+    out.a = 1.0f / span;
+    out.b = -(lo - pad) / span;
+    std::vector<int> cell_of(count);
+    for (int i = 0; i < count; ++i) {
+        cell_of[i] = int(grid_offset(boundaries[i], out.a, out.b) / 8);
+        if (i > 0 && cell_of[i] == cell_of[i - 1]) return false;
+    }
+    out.cells.assign(kGridCells, QuantCell{});
+    int below = 0;       // boundaries in cells lower than c
+    for (int c = 0, i = 0; c < kGridCells; ++c) {
+        float inside = std::numeric_limits<float>::max();     // finite inputs never exceed it
+        if (i < count && cell_of[i] == c) inside = boundaries[i];
+        std::memcpy(&out.cells[c].boundary_bits, &inside, 4);
+        out.cells[c].code8 = uint32_t(below) * 8u;
+        if (i < count && cell_of[i] == c) { ++i; ++below; }
+    }
+    return true;
+}
+
+// Host evaluation of a grid, the same lookup the kernel performs.
+uint32_t quant_grid_code(const QuantGridHost &g, float x) {
+    const QuantCell &c = g.cells[grid_offset(x, g.a, g.b) / 8];
+    float inside;
+    std::memcpy(&inside, &c.boundary_bits, 4);
+    return c.code8 / 8 + (x > inside ? 1u : 0u);
+}
+
+size_t ingest_fast_smem_bytes(int dim, int ngroups) { return fast_layout(dim, ngroups).total; }
+
+bool ingest_fast_supported(int dim, int bits, int ngroups, bool calibrated, const void *x, size_t smem_limit) {
     if (calibrated || (reinterpret_cast<uintptr_t>(x) & 15) != 0) return false;
     if (bits != 2 && bits != 3 && bits != 4) return false;
     switch (dim) {
-        case 128: case 256: case 384: case 512: case 768: case 1024: case 1536: case 2048: return true;
+        case 128: case 256: case 384: case 512: case 768: case 1024: case 1536: case 2048: break;
         default: return false;
     }
+    return fast_layout(dim, ngroups).total <= smem_limit;
 }
 
-cudaError_t launch_ingest_fast(const IngestParams &p, const float *host_boundaries, int sm_count, size_t smem_limit, uint32_t *error,
+cudaError_t launch_ingest_fast(const IngestParams &p, const QuantGrid &grid, int sm_count, size_t smem_limit, uint32_t *error,
                                cudaStream_t stream) {
     if (p.n <= 0) return cudaSuccess;
-    if (p.slot0 % kBlockLanes != 0) return cudaErrorInvalidValue;
-    const size_t smem = fast_layout(p.dim, p.ngroups, p.bits == 2 ? 4 : 2).total;
+    if (p.slot0 % kBlockLanes != 0 || grid.cells == nullptr) return cudaErrorInvalidValue;
+    const size_t smem = fast_layout(p.dim, p.ngroups).total;
     if (smem > smem_limit) return cudaErrorInvalidValue;
     const int64_t nblocks = (p.n + kBlockLanes - 1) / kBlockLanes;
-    const unsigned grid = unsigned(std::min<int64_t>(nblocks, int64_t(sm_count)));   // one CTA per SM: it owns the register file
-    Boundaries15 bnd;
-    for (int i = 0; i < 15; ++i) bnd.b[i] = i < (1 << p.bits) - 1 ? host_boundaries[i] : INFINITY;
+    const unsigned nctas = unsigned(std::min<int64_t>(nblocks, int64_t(sm_count)));   // one CTA per SM: it owns the register file
 #define TV_LAUNCH_FAST(D, L2B, NB)                                                                                   \
     case D: {                                                                                                        \
         cudaError_t e = cudaFuncSetAttribute(ingest_fast_kernel<L2B, NB>, cudaFuncAttributeMaxDynamicSharedMemorySize, int(smem)); \
         if (e != cudaSuccess) return e;                                                                              \
-        ingest_fast_kernel<L2B, NB><<<grid, kFastThreads, smem, stream>>>(p, bnd, error);                            \
+        ingest_fast_kernel<L2B, NB><<<nctas, kFastThreads, smem, stream>>>(p, grid, error);                          \
         break;                                                                                                       \
     }
     switch (p.dim) {
