@@ -95,7 +95,8 @@ enum {
     TV_OPT_MMA_MIN_BATCH = 2,   /* query batches of at least this size use the expanded-int8 tensor path (0 = never) */
     TV_OPT_FORCE_CAREFUL = 3,   /* 1: run the candidate-overflow recovery schedule always (testing) */
     TV_OPT_TC_TILES = 4,        /* accumulator tiles of 128 vectors per query slab in the tensor-memory scan: 1 or 2 */
-    TV_OPT_INGEST_PIPELINE = 5  /* 1 (default): whole code blocks are encoded by the pipelined ingest kernel; 0: never */
+    TV_OPT_INGEST_PIPELINE = 5  /* 1 (default): whole code blocks are encoded by the pipelined ingest kernel; 0: never;
+                                 * 2: pipelined, and every reconstruction sum walks the sequential chains (testing) */
 };
 
 /* ---- construction: TurboQuantIndex::new / new_lazy (lib.rs:629, 670), IdMapIndex::new (id_map.rs:278) ---- */

@@ -90,7 +90,8 @@ def test_ingest_zero_and_tiny_rows(T):
                                       (2048, 4), (2048, 2)])
 def test_pipelined_ingest_matches_oracle_and_block_kernel(T, dim, bits):
     """Whole code blocks go through the pipelined kernel, a partial head block through the block-at-a-time
-    one; both must produce the oracle's bytes and scales, and so must the block-at-a-time kernel alone."""
+    one; both must produce the oracle's bytes and scales, and so must the block-at-a-time kernel alone and
+    the pipelined kernel with its certified parallel sum switched off."""
     n = 1500 + 13
     x = anisotropic(n, dim, seed=7 * dim + bits)
     x[5] = 0.0
@@ -105,7 +106,10 @@ def test_pipelined_ingest_matches_oracle_and_block_kernel(T, dim, bits):
     b = T.TurboQuantIndex(dim, bits)
     b.set_option(T.OPT_INGEST_PIPELINE, 0)
     b.add(x)
-    for idx in (a, b):
+    c = T.TurboQuantIndex(dim, bits)
+    c.set_option(T.OPT_INGEST_PIPELINE, 2)      # every reconstruction sum walks the sequential chains
+    c.add(x)
+    for idx in (a, b, c):
         assert np.array_equal(idx.codes_blocked_seq(), want_blocked)
         assert np.array_equal(idx.scales().view(np.uint32), enc["scales"].view(np.uint32))
         assert np.array_equal(idx.packed_codes(), enc["packed"])

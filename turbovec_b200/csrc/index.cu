@@ -416,6 +416,7 @@ int add_rows(tv_index *h, const float *x, size_t n, size_t dim, bool on_device) 
         }
         if (int64_t(rows) > head) {
             p.x = src + head * int64_t(dim); p.n = int64_t(rows) - head; p.slot0 += head; p.row_base += head;
+            p.exact_sums = h->ingest_pipeline == 2;
             mark_begin(h);
             TV_CUDA(launch_ingest_fast(p, h->qgrid, h->sm_count, h->smem_limit, &h->d_flags->error, h->stream));
             mark_end(h);
@@ -836,7 +837,7 @@ int tv_set_option(tv_index *h, int option, int64_t value) {
         case TV_OPT_MMA_MIN_BATCH: h->mma_min_batch = value; return TV_OK;
         case TV_OPT_FORCE_CAREFUL: h->force_careful = value != 0; return TV_OK;
         case TV_OPT_TC_TILES: h->tc_tiles = value == 1 ? 1 : 2; return TV_OK;
-        case TV_OPT_INGEST_PIPELINE: h->ingest_pipeline = value != 0; return TV_OK;
+        case TV_OPT_INGEST_PIPELINE: h->ingest_pipeline = value < 0 || value > 2 ? 1 : int(value); return TV_OK;
         default: return fail(h, TV_ERR_INVALID_ARGUMENT, "unknown option");
     }
 }

@@ -30,6 +30,7 @@ struct IngestParams {
     float *rot_out;                // when set: write the rotated unit rows [n][dim] here and encode nothing
                                    // (input of the TQ+ fit, encode.rs:470-480)
     unsigned long long *first_invalid;  // min flat index of a coordinate failing |x| < 1e16 (init ~0ull)
+    int exact_sums;                // pipelined kernel only: 1 = always walk the reference's sequential f64 chains (testing)
 };
 
 size_t ingest_smem_bytes(int vectors_per_pass, int dim, int ngroups);

@@ -6,19 +6,28 @@
 // One CTA of three warpgroups walks a contiguous range of code blocks in waves of 8 vectors and runs its
 // stages concurrently, one wave apart, with one CTA barrier per step:
 //   norm warps     wave i     8 sequential f32 chains per vector straight from global memory (4 lanes per
-//                             vector, two chains per lane), fixed combine tree, sqrt, reciprocal
+//                             vector, two chains per lane), fixed combine tree, sqrt, reciprocal.  Two warps
+//                             alternate (even and odd waves) and spread a wave over two steps: the loads come
+//                             from global memory and the chains need a dozen dependent round trips.
+//   staging warp   wave i     issues the bulk copies (cp.async.bulk + mbarrier transaction count) of the rows
 //   8 rotation     wave i-1   one warp per vector, the whole vector in registers: both rounds of permutation,
 //   warps                     sign flip and Walsh-Hadamard butterflies (rotation.cuh states the order rules),
-//                             Lloyd-Max quantisation through a grid table (QuantGrid), packing into the block tile
-//   sum warp       wave i-2   4 sequential f64 chains per vector over the rotated row and the codes, scale;
-//                             then issues the bulk copies that stage wave i's rows into shared memory
+//                             Lloyd-Max quantisation through a grid table (QuantGrid), packing into the block
+//                             tile, reconstruction inner product and scale
 //   copy warp                 writes the finished tile of a block (ngroups x 32 bytes, word-swizzled so that the
 //                             byte stores of a warp never share a bank) to the code array
-// The norm stage alternates between two warps (even and odd waves), each starting a step early: its loads
-// come from global memory and the chains of a wave need a dozen dependent round trips.
-// Rows arrive by cp.async.bulk with an mbarrier transaction count.  The two rotation warpgroups take the
-// registers the third one gives up (setmaxnreg), so a 2048-coordinate vector and its permutation entries
-// stay in registers.
+// The two rotation warpgroups take the registers the third one gives up (setmaxnreg), so a 2048-coordinate
+// vector and its permutation entries stay in registers.
+//
+// Reconstruction inner product.  The reference sums rotated[j] * centroid[code[j]] in f64 along four
+// sequential chains (encode.rs:1418-1476) and uses the result rounded to f32, and a dependent f64 add takes
+// some 45 cycles here.  The products are exact in f64 (both factors are f32 values), so every summation order
+// lands within gamma * sum|products| of the exact sum (gamma_m = m u / (1 - m u), u = 2^-53, m = additions a
+// term goes through).  The rotation warp therefore sums in parallel, brackets the reference's value by
+// S +- 1e-13 * A with A >= sum|products| (1e-13 > gamma_(dim/4+2) + gamma_64 for dim <= 3300), and accepts
+// S when both ends of the bracket round to the same f32 and fall on the same side of the 0.1 threshold:
+// rounding is monotone, so the reference's value rounds there too.  Otherwise, a few vectors in a million,
+// the warp walks the four chains in the reference's order.
 #include <algorithm>
 #include <cmath>
 #include <cstring>
@@ -95,11 +104,12 @@ __device__ __forceinline__ float max_nan(float a, float b) {   // NaN wins, unli
 
 constexpr int kWave = 8;                 // vectors per wave = rotation warps
 constexpr int kWavesPerBlock = kBlockLanes / kWave;
-constexpr int kFastThreads = 384;        // 8 rotation warps; norm (even waves), sum, norm (odd waves), copy
+constexpr int kFastThreads = 384;        // 8 rotation warps; norm (even waves), staging, norm (odd waves), copy
 constexpr int kRotationRegs = 208, kServiceRegs = 88;   // 8*32*208 + 4*32*88 <= 384 * 168
 constexpr int kGridCells = 1024;         // cells of the quantisation grid
 constexpr float kGridTop = 8.0f * (kGridCells - 1);
 constexpr float kGridMagic = 8388608.0f; // 2^23: adding it leaves the rounded integer in the low mantissa bits
+constexpr double kSumBracket = 1.0e-13;  // see the head of this file
 
 // Byte offset (cell * 8) of x in the quantisation grid.  Any monotone non-decreasing map works for the
 // argument in build_quant_grid; this one costs two FMAs and a mask.
@@ -118,20 +128,17 @@ __host__ __device__ inline uint32_t grid_offset(float x, float a, float b) {
 }
 
 struct FastLayout {
-    int stride;          // floats per staged row: dim + 4 keeps the sum warp's 4-lane reads on distinct banks
-    int cstride;         // bytes per row of centroid offsets: dim + 16 does the same for its byte reads
-    size_t grid, cent, rows, tile, coff, norm, inv, bars, total;
+    int stride;          // floats per staged row (16-byte multiple for the bulk copies)
+    size_t grid, cent, rows, tile, norm, inv, bars, total;
 };
 __host__ __device__ inline FastLayout fast_layout(int dim, int ngroups) {
     FastLayout L;
     L.stride = dim + 4;
-    L.cstride = dim + 16;
     size_t off = 0;
     L.grid = off; off += size_t(kGridCells) * 8;       // first, so that its address is a link-time constant
     L.cent = off; off += 16 * 8;                       // centroids as f64
     L.rows = off; off += size_t(2) * kWave * L.stride * 4;
     L.tile = off; off += size_t(2) * ngroups * 32;
-    L.coff = off; off += size_t(2) * kWave * L.cstride; // per coordinate: 8 * code = byte offset into `cent`
     L.norm = off; off += 4 * kWave * 4;
     L.inv = off; off += 4 * kWave * 4;
     L.bars = off; off += 2 * 8;
@@ -183,12 +190,11 @@ __global__ void __launch_bounds__(kFastThreads, 1) ingest_fast_kernel(IngestPara
     const FastLayout L = fast_layout(DIM, ng);
     float *rows = reinterpret_cast<float *>(smem + L.rows);
     unsigned char *tiles = smem + L.tile;
-    unsigned char *coffs = smem + L.coff;
     float *norm_s = reinterpret_cast<float *>(smem + L.norm);     // [4][8]
     float *inv_s = reinterpret_cast<float *>(smem + L.inv);       // [4][8]
     uint64_t *full = reinterpret_cast<uint64_t *>(smem + L.bars); // [2]
     const int tid = threadIdx.x, warp = tid >> 5, lane = tid & 31;
-    const int stride = L.stride, cstride = L.cstride;
+    const int stride = L.stride;
     const int tile_bytes = ng * 32;
 
     const int64_t slot_lo = p.slot0, slot_hi = p.slot0 + p.n;       // slot_lo is a multiple of 32
@@ -226,7 +232,9 @@ __global__ void __launch_bounds__(kFastThreads, 1) ingest_fast_kernel(IngestPara
         for (int s = 0; s < 5; ++s) sgn[s] = (lane >> s) & 1 ? -1.0f : 1.0f;
         const float isb = p.inv_sqrt_block;
         const float ga = grid.a, gb = grid.b;
-        const uint32_t grid_base = smem_u32(smem + L.grid);
+        const uint32_t grid_base = smem_u32(smem + L.grid), cent_base = smem_u32(smem + L.cent);
+        float cmax = 0.0f;                            // largest |centroid|
+        for (int i = 0; i < (1 << p.bits); ++i) cmax = fmaxf(cmax, fabsf(p.centroids[i]));
         const int q = lane & (cpb - 1);               // this lane packs the registers k = q (mod cpb)
 
         for (int it = 0; it <= nw + 1; ++it) {
@@ -239,7 +247,6 @@ __global__ void __launch_bounds__(kFastThreads, 1) ingest_fast_kernel(IngestPara
                 float *row = rows + size_t((w & 1) * V + warp) * stride;
                 if (slot >= 0 && mbar_wait(&full[w & 1], (w >> 1) & 1, error)) {
                     const uint32_t rb = smem_u32(row), rl = rb + lane * 4;
-                    const uint32_t cl = smem_u32(coffs + size_t((w & 1) * V + warp) * cstride) + lane;
                     const float inv = inv_s[(w & 3) * V + warp];
                     // keeps the masks and offsets derived from pk from being hoisted out of the wave loop into
                     // four registers per entry
@@ -274,17 +281,57 @@ __global__ void __launch_bounds__(kFastThreads, 1) ingest_fast_kernel(IngestPara
                     }
                     __syncwarp();
                     wht_blocks<R, NBLK>(v, sgn);
+                    double sacc[8];                                   // independent partial sums hide the f64 latency
+#pragma unroll
+                    for (int i = 0; i < 8; ++i) sacc[i] = 0.0;
+                    float aacc = 0.0f;                                // sum |y| of this lane
 #pragma unroll
                     for (int k = 0; k < T; ++k) {
                         const float y = __fmul_rn(v[k], isb);
-                        sts_f32(rl + k * 128, y);                     // rotated row, read by the sum warp
+                        v[k] = y;
                         // code = number of boundaries strictly below y (encode.rs:1447-1451): the cell of y
                         // knows how many lie in lower cells and the one boundary, if any, inside the cell
                         const uint2 cell = lds_u2(grid_base + grid_offset(y, ga, gb));
                         const uint32_t code8 = cell.y + (y > __uint_as_float(cell.x) ? 8u : 0u);   // 8 * code
-                        sts_u8(cl + k * 32, code8);
                         cw[k >> 3] += (k & 7) == 0 ? code8 >> 3 : code8 * (1u << (4 * (k & 7) - 3));
+                        sacc[k & 7] = __fma_rn(double(y), lds_f64(cent_base + code8), sacc[k & 7]);
+                        aacc += fabsf(y);
                     }
+                    double S = ((sacc[0] + sacc[1]) + (sacc[2] + sacc[3])) + ((sacc[4] + sacc[5]) + (sacc[6] + sacc[7]));
+#pragma unroll
+                    for (int m = 1; m < 32; m <<= 1) {
+                        S += __shfl_xor_sync(kFullMask, S, m);        // commutative: every lane ends with the same bits
+                        aacc += __shfl_xor_sync(kFullMask, aacc, m);
+                    }
+                    // A >= sum |y| * max|centroid| >= sum |products|; the factor covers the f32 rounding of aacc
+                    const double A = double(aacc) * double(cmax) * 1.0001;
+                    const double lo = S - kSumBracket * A, hi = S + kSumBracket * A;
+                    const float flo = __double2float_rn(lo), fhi = __double2float_rn(hi);
+                    const bool certain = flo == fhi && (lo > 0.1) == (hi > 0.1) && p.exact_sums == 0;
+                    float inner_f = flo;
+                    bool above = lo > 0.1;
+                    if (!certain) {
+                        // the reference's own order: chain c over j = c (mod 4) ascending, (c0+c1)+(c2+c3)
+#pragma unroll
+                        for (int k = 0; k < T; ++k) sts_f32(rl + k * 128, v[k]);
+                        __syncwarp();
+                        double acc = 0.0;
+                        if (lane < 4) {
+                            for (int j = lane; j < DIM; j += 4) {
+                                const float y = row[j];
+                                const uint2 cell = lds_u2(grid_base + grid_offset(y, ga, gb));
+                                const uint32_t code8 = cell.y + (y > __uint_as_float(cell.x) ? 8u : 0u);
+                                acc = __fma_rn(double(y), lds_f64(cent_base + code8), acc);   // exact product: one rounding
+                            }
+                        }
+                        acc = __dadd_rn(acc, __shfl_down_sync(kFullMask, acc, 1));
+                        acc = __dadd_rn(acc, __shfl_down_sync(kFullMask, acc, 2));
+                        acc = __shfl_sync(kFullMask, acc, 0);
+                        inner_f = __double2float_rn(acc);
+                        above = acc > 0.1;
+                        __syncwarp();
+                    }
+                    if (lane == 0) p.scales[slot] = above ? __fdiv_rn(norm_s[(w & 3) * V + warp], inner_f) : 0.0f;
                 }
                 // pack: byte of group g = codes of coordinates g*cpb .. g*cpb+cpb-1, first one in the top field
                 // (pack.rs:264-282); the cpb lanes of a group exchange code words, lane q stores k = q (mod cpb)
@@ -370,47 +417,10 @@ __global__ void __launch_bounds__(kFastThreads, 1) ingest_fast_kernel(IngestPara
                 __syncthreads();
             }
         } else if (warp == V + 1) {
-            // -------------------------------------------- reconstruction sums two waves behind; row staging
-            // lane = (vector vv, chain c); chain c sums rotated[j] * centroid[code[j]] over j = c (mod 4) in
-            // ascending j, the four chains combine as (c0+c1)+(c2+c3) (encode.rs:1418-1476).  Both factors are
-            // f32 values, so their f64 product is exact and one fused multiply-add rounds exactly like the
-            // reference's multiply followed by an add.
-            const int vv = lane >> 2, c = lane & 3;
-            const uint32_t cent_base = smem_u32(smem + L.cent);
+            // -------------------------------------------- row staging: wave `it` lands while wave it - 1 rotates;
+            // its row set was last read by the rotation of wave it - 2, one barrier ago
             for (int it = 0; it <= nw + 1; ++it) {
-                const int w = it - 2;
-                if (w >= 0) {
-                    const int64_t slot = wave_slot(w, vv);
-                    double acc = 0.0;
-                    if (slot >= 0) {
-                        const float *row_c = rows + size_t((w & 1) * V + vv) * stride + c;
-                        const unsigned char *off_c = coffs + size_t((w & 1) * V + vv) * cstride + c;
-                        uint32_t o[8];
-                        float x[8];
-#pragma unroll
-                        for (int u = 0; u < 8; ++u) { o[u] = off_c[4 * u]; x[u] = row_c[4 * u]; }
-#pragma unroll 1
-                        for (int t0 = 0; t0 < DIM / 4; t0 += 8) {
-                            double cen[8];
-                            float xc[8];
-#pragma unroll
-                            for (int u = 0; u < 8; ++u) { cen[u] = lds_f64(cent_base + o[u]); xc[u] = x[u]; }
-                            if (t0 + 8 < DIM / 4) {
-#pragma unroll
-                                for (int u = 0; u < 8; ++u) { o[u] = off_c[4 * (t0 + 8 + u)]; x[u] = row_c[4 * (t0 + 8 + u)]; }
-                            }
-#pragma unroll
-                            for (int u = 0; u < 8; ++u) acc = __fma_rn(double(xc[u]), cen[u], acc);
-                        }
-                    }
-                    acc = __dadd_rn(acc, __shfl_down_sync(kFullMask, acc, 1));
-                    acc = __dadd_rn(acc, __shfl_down_sync(kFullMask, acc, 2));    // (c0+c1)+(c2+c3) on c = 0
-                    if (c == 0 && slot >= 0)
-                        p.scales[slot] = acc > 0.1 ? __fdiv_rn(norm_s[(w & 3) * V + vv], __double2float_rn(acc)) : 0.0f;
-                }
-                __syncwarp();
                 if (it < nw) {
-                    // stage the rows of wave `it` into the row set this warp has just finished reading
                     const int64_t slot = lane < V ? wave_slot(it, lane) : -1;
                     const uint32_t live = __ballot_sync(kFullMask, slot >= 0);
                     if (lane == 0) {
