@@ -184,6 +184,7 @@ __global__ void __launch_bounds__(kFastThreads, 1) ingest_fast_kernel(IngestPara
     constexpr int DIM = T * 32;
     constexpr int V = kWave, wpb = kWavesPerBlock;
     static_assert(T % 4 == 0, "the packing below handles whole groups of four registers");
+    constexpr int kNormBatch = (DIM / 16) % 16 == 0 ? 16 : 8;   // chain steps per load batch; a half wave has DIM / 16 steps
     extern __shared__ __align__(128) unsigned char smem[];
     const int ng = p.ngroups;
     const int cpb = p.bits == 2 ? 4 : 2;              // codes per byte (3-bit codes sit in 4-bit fields)
@@ -392,12 +393,12 @@ __global__ void __launch_bounds__(kFastThreads, 1) ingest_fast_kernel(IngestPara
                         const float2 *src = reinterpret_cast<const float2 *>(p.x + (slot - slot_lo) * DIM + 2 * pp);
                         const int t_begin = second && !whole ? DIM / 16 : 0, t_end = second ? DIM / 8 : DIM / 16;
 #pragma unroll 1
-                        for (int t0 = t_begin; t0 < t_end; t0 += 8) {
-                            float2 x[8];
+                        for (int t0 = t_begin; t0 < t_end; t0 += kNormBatch) {
+                            float2 x[kNormBatch];                     // loads in flight per lane
 #pragma unroll
-                            for (int u = 0; u < 8; ++u) x[u] = __ldg(src + 4 * (t0 + u));
+                            for (int u = 0; u < kNormBatch; ++u) x[u] = __ldg(src + 4 * (t0 + u));
 #pragma unroll
-                            for (int u = 0; u < 8; ++u) {
+                            for (int u = 0; u < kNormBatch; ++u) {
                                 a0 = __fadd_rn(a0, __fmul_rn(x[u].x, x[u].x));
                                 a1 = __fadd_rn(a1, __fmul_rn(x[u].y, x[u].y));
                             }
