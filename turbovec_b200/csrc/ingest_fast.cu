@@ -146,19 +146,34 @@ __host__ __device__ inline FastLayout fast_layout(int dim, int ngroups) {
     return L;
 }
 
-// Walsh-Hadamard transform of NBLK blocks of 32*R coordinates; v[b*R + r] holds coordinate r*32 + lane of
-// block b.  Stage order len = 1, 2, 4, ...: lane exchanges first, register pairs after.  fma(v, +-1, other)
-// rounds once, exactly like the add or subtract it stands for.
+// Walsh-Hadamard transform of NBLK blocks of 32*R coordinates in registers, stage order len = 1, 2, 4, ...
+// On entry v[b*R + r] of lane l holds coordinate l*R + r of block b: the first log2(R) stages pair registers.
+// Each of the five remaining stages pairs lanes l and l ^ m.  Instead of fetching the partner's copy of every
+// register, the two lanes swap one register of each pair (lane bit <-> register bit t): the lower lane ends
+// up with both inputs of the pair's first register, the upper lane with both inputs of its second, each
+// computes sum and difference, and the coordinate bit just processed now lives in register bit t while the
+// lanes hold an already processed bit.  That halves the shuffles.  The upper lane sends its value negated, so
+// that both results are single fused multiply-adds by +-1, rounded once like the add or subtract they stand
+// for.  With t = stage % log2(R) the lane bits end as coordinate bits 0..4: on exit v[b*R + r] of lane l
+// holds coordinate wht_row<R>(r) * 32 + l.
+template <int R>
+__host__ __device__ constexpr int log2_of() { int l = 0; while ((1 << l) < R) ++l; return l; }
+template <int R>
+__host__ __device__ constexpr int wht_row(int r) {
+    constexpr int RHO = log2_of<R>();
+    int bit_of[8] = {0, 1, 2, 3, 4, 5, 6, 7};         // coordinate bit held by register bit j
+    for (int i = 0; i < 5; ++i) bit_of[i % RHO] = RHO + i;
+    int row = 0;
+    for (int j = 0; j < RHO; ++j) row |= ((r >> j) & 1) << (bit_of[j] - 5);
+    return row;
+}
+// register k = block * R + r of a vector: its coordinates after wht_blocks are row_of(k) * 32 + lane
+template <int R>
+__host__ __device__ constexpr int row_of(int k) { return (k / R) * R + wht_row<R>(k % R); }
 template <int R, int NBLK>
-__device__ __forceinline__ void wht_blocks(float (&v)[R * NBLK], const float (&sgn)[5]) {
-#pragma unroll
-    for (int s = 0; s < 5; ++s) {
-#pragma unroll
-        for (int k = 0; k < R * NBLK; ++k) {
-            const float other = __shfl_xor_sync(kFullMask, v[k], 1 << s);
-            v[k] = __fmaf_rn(v[k], sgn[s], other);   // lower lane: v + other; upper lane: other - v
-        }
-    }
+__device__ __forceinline__ void wht_blocks(float (&v)[R * NBLK], int lane) {
+    constexpr int RHO = log2_of<R>();
+    static_assert(RHO >= 1 && (1 << RHO) == R, "R is a power of two, at least 2");
 #pragma unroll
     for (int len = 1; len < R; len <<= 1) {
 #pragma unroll
@@ -174,8 +189,27 @@ __device__ __forceinline__ void wht_blocks(float (&v)[R * NBLK], const float (&s
             }
         }
     }
+#pragma unroll
+    for (int i = 0; i < 5; ++i) {
+        const int t = 1 << (i % RHO);
+        const bool upper = (lane >> i) & 1;
+        const float cs = upper ? 1.0f : -1.0f;
+#pragma unroll
+        for (int b = 0; b < NBLK; ++b) {
+#pragma unroll
+            for (int r0 = 0; r0 < R; ++r0) {
+                if (r0 & t) continue;
+                const int r1 = r0 | t;
+                const float keep = upper ? v[b * R + r1] : v[b * R + r0];
+                const float send = upper ? -v[b * R + r0] : v[b * R + r1];
+                const float recv = __shfl_xor_sync(kFullMask, send, 1 << i);
+                // lower lane: keep = a, recv = -b; upper lane: keep = b, recv = a
+                v[b * R + r0] = __fmaf_rn(recv, cs, keep);        // a + b
+                v[b * R + r1] = __fmaf_rn(keep, -cs, recv);       // a - b
+            }
+        }
+    }
 }
-
 
 template <int LOG2B, int NBLK>
 __global__ void __launch_bounds__(kFastThreads, 1) ingest_fast_kernel(IngestParams p, QuantGrid grid, uint32_t *error) {
@@ -225,12 +259,10 @@ __global__ void __launch_bounds__(kFastThreads, 1) ingest_fast_kernel(IngestPara
         uint32_t pk[T];          // per register: round-1 byte offset | sign << 15, round-2 the same in the high half
 #pragma unroll
         for (int k = 0; k < T; ++k) {
-            const uint32_t e0 = p.perm0[k * 32 + lane], e1 = p.perm1[k * 32 + lane];
+            const int dst = (k / R) * (32 * R) + lane * R + (k % R);       // coordinate this register gathers (see wht_blocks)
+            const uint32_t e0 = p.perm0[dst], e1 = p.perm1[dst];
             pk[k] = ((e0 & 0x7fffu) << 2) | (e0 & 0x8000u) | ((((e1 & 0x7fffu) << 2) | (e1 & 0x8000u)) << 16);
         }
-        float sgn[5];
-#pragma unroll
-        for (int s = 0; s < 5; ++s) sgn[s] = (lane >> s) & 1 ? -1.0f : 1.0f;
         const float isb = p.inv_sqrt_block;
         const float ga = grid.a, gb = grid.b;
         const uint32_t grid_base = smem_u32(smem + L.grid), cent_base = smem_u32(smem + L.cent);
@@ -242,7 +274,7 @@ __global__ void __launch_bounds__(kFastThreads, 1) ingest_fast_kernel(IngestPara
             const int w = it - 1;
             if (w >= 0 && w < nw) {
                 const int64_t slot = wave_slot(w, warp);
-                uint32_t cw[(T + 7) / 8];             // 4-bit code of register k in nibble k % 8 of word k / 8
+                uint32_t cw[(T + 7) / 8];             // 4-bit code of coordinates kk*32 + lane in nibble kk % 8 of word kk / 8
 #pragma unroll
                 for (int i = 0; i < (T + 7) / 8; ++i) cw[i] = 0;
                 float *row = rows + size_t((w & 1) * V + warp) * stride;
@@ -270,9 +302,9 @@ __global__ void __launch_bounds__(kFastThreads, 1) ingest_fast_kernel(IngestPara
                                 atomicMin(p.first_invalid, (unsigned long long)((p.row_base + r) * DIM + j));
                         __syncwarp();
                     }
-                    wht_blocks<R, NBLK>(v, sgn);
+                    wht_blocks<R, NBLK>(v, lane);
 #pragma unroll
-                    for (int k = 0; k < T; ++k) sts_f32(rl + k * 128, __fmul_rn(v[k], isb));
+                    for (int k = 0; k < T; ++k) sts_f32(rl + row_of<R>(k) * 128, __fmul_rn(v[k], isb));
                     __syncwarp();
                     // round 2
 #pragma unroll
@@ -281,7 +313,7 @@ __global__ void __launch_bounds__(kFastThreads, 1) ingest_fast_kernel(IngestPara
                         v[k] = __uint_as_float(__float_as_uint(x) ^ (pk[k] & 0x80000000u));
                     }
                     __syncwarp();
-                    wht_blocks<R, NBLK>(v, sgn);
+                    wht_blocks<R, NBLK>(v, lane);
                     double sacc[8];                                   // independent partial sums hide the f64 latency
 #pragma unroll
                     for (int i = 0; i < 8; ++i) sacc[i] = 0.0;
@@ -294,7 +326,8 @@ __global__ void __launch_bounds__(kFastThreads, 1) ingest_fast_kernel(IngestPara
                         // knows how many lie in lower cells and the one boundary, if any, inside the cell
                         const uint2 cell = lds_u2(grid_base + grid_offset(y, ga, gb));
                         const uint32_t code8 = cell.y + (y > __uint_as_float(cell.x) ? 8u : 0u);   // 8 * code
-                        cw[k >> 3] += (k & 7) == 0 ? code8 >> 3 : code8 * (1u << (4 * (k & 7) - 3));
+                        const int kk = row_of<R>(k);               // this register holds coordinate kk * 32 + lane
+                        cw[kk >> 3] += (kk & 7) == 0 ? code8 >> 3 : code8 * (1u << (4 * (kk & 7) - 3));
                         sacc[k & 7] = __fma_rn(double(y), lds_f64(cent_base + code8), sacc[k & 7]);
                         aacc += fabsf(y);
                     }
@@ -314,7 +347,7 @@ __global__ void __launch_bounds__(kFastThreads, 1) ingest_fast_kernel(IngestPara
                     if (!certain) {
                         // the reference's own order: chain c over j = c (mod 4) ascending, (c0+c1)+(c2+c3)
 #pragma unroll
-                        for (int k = 0; k < T; ++k) sts_f32(rl + k * 128, v[k]);
+                        for (int k = 0; k < T; ++k) sts_f32(rl + row_of<R>(k) * 128, v[k]);
                         __syncwarp();
                         double acc = 0.0;
                         if (lane < 4) {
