@@ -333,7 +333,7 @@ def run_ours(args):
                    "roofline": {"bound": "hbm", "achieved": ingest_rate * ingest_bytes / 1e9 if ingest_rate else None,
                                 "peak": pk["hbm_gbs"], "unit": "GB/s",
                                 "frac": ingest_rate * ingest_bytes / 1e9 / pk["hbm_gbs"] if ingest_rate else None,
-                                "traffic": None, "kernel": "ingest_kernel", "launches": ingest_launches}},
+                                "traffic": None, "kernel": "ingest_fast_kernel (pipelined; whole 32-slot blocks)", "launches": ingest_launches}},
         "recall_at_10": recall,
     }
     if cpu_qps is not None:
