@@ -272,6 +272,34 @@ def run_ours(args):
     q1_host = q_host[:1].contiguous().pin_memory()
     dt1_e2e, _, _, _ = timed(lambda: step_host(q1_host, 1), b1_steps, 2)
 
+    # filtered search (slot bitmask resident on the device): selectivity x layout of the allowed slots
+    filtered = []
+    if world == 1 and not args.no_filtered:
+        rng = np.random.default_rng(7)
+        nb_total = (n_local + 31) // 32
+        for sel, kind in [(0.001, "random"), (0.01, "random"), (0.1, "random"), (0.5, "random"), (0.01, "range"), (0.1, "range")]:
+            allowed = np.zeros(((n_local + 63) // 64) * 64, dtype=bool)
+            if kind == "random":
+                allowed[:n_local] = rng.random(n_local) < sel
+            else:
+                lo = int(rng.integers(0, max(1, n_local - int(sel * n_local))))
+                allowed[lo: lo + int(sel * n_local)] = True
+            live_blocks = int(allowed[: nb_total * 32].reshape(-1, 32).any(axis=1).sum())
+            words = torch.from_numpy(np.packbits(allowed, bitorder="little").view(np.uint64).copy().view(np.int64)).to(device)
+            f_steps = max(2, args.steps // 3)
+
+            def step_f(qd, nqq):
+                return idx.search_device(qd.data_ptr(), nqq, K, d_scores.data_ptr(), d_slots.data_ptr(), words.data_ptr())
+            dtf, scanf_ms, _, _ = timed(lambda: step_f(q_dev, nq), f_steps, 1)
+            dtf1, scanf1_ms, _, _ = timed(lambda: step_f(q1_dev, 1), 10, 2)
+            live_bytes = live_blocks * 32 * (DIM * BITS // 8 + 4)
+            filtered.append({"selectivity": sel, "layout": kind, "n_allowed": int(allowed.sum()),
+                             "live_block_fraction": live_blocks / nb_total,
+                             "batch": {"size": nq, "value": nq * f_steps / dtf, "unit": UNIT},
+                             "batch1": {"value": 10 / dtf1, "unit": UNIT, "ms_per_query": dtf1 / 10 * 1e3,
+                                        "scan_gbs_over_live_blocks": live_bytes / (scanf1_ms / 10 / 1e3) / 1e9 if scanf1_ms > 0 else None}})
+            del words
+
     # recall@10 of the first n_recall_q queries against exact fp32 inner products
     rs, ri = step_device(q_all[:n_recall_q].contiguous(), n_recall_q)
     if world > 1:
@@ -336,6 +364,8 @@ def run_ours(args):
                                 "traffic": None, "kernel": "ingest_fast_kernel (pipelined; whole 32-slot blocks)", "launches": ingest_launches}},
         "recall_at_10": recall,
     }
+    if filtered:
+        line["filtered"] = filtered
     if cpu_qps is not None:
         line["cpu_baseline"] = {"value": cpu_qps, "unit": UNIT, "cores": cores, "kind": "port", "sample": sample}
     print(json.dumps(line))
@@ -352,6 +382,7 @@ def main():
     ap.add_argument("--vectors", dest="n", type=int, default=10_000_000)
     ap.add_argument("--batch", type=int, default=1024)
     ap.add_argument("--skip-cpu", dest="no_cpu", action="store_true", help="skip the cpu_baseline leg")
+    ap.add_argument("--skip-filtered", dest="no_filtered", action="store_true", help="skip the filtered-search legs")
     ap.add_argument("--tc-min-batch", type=int, default=None,
                     help="query batches of at least this size use the tcgen05 scan (library default if omitted; 0 = never)")
     args = ap.parse_args()
