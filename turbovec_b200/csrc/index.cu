@@ -590,14 +590,27 @@ int search_core(tv_index *h, const float *queries, bool queries_on_device, size_
         // Chunk 0 holds at most `cap` vectors, so every one of them may pass.  Later chunks grow so that the
         // expected number of candidates per query, k * |chunk| / |seen|, stays near cap / 4.  The careful
         // schedule never lets a chunk exceed `cap` vectors and therefore cannot overflow.
+        // The tensor-memory scan pays for dense candidates (its epilogue re-reads a 32 x 32 tile of scores
+        // whenever one of them passes), so its chunks grow gently at first: x24, x10, then the list-capacity rule.
         const size_t first = size_t(cap) / kBlock;
         const double growth = std::max(0.5, double(cap) / (4.0 * double(kk)));
         size_t begin = 0;
+        int stage = 0;
         while (begin < n_blocks) {
             size_t len = first;
-            if (!careful && begin > 0) len = std::max<size_t>(first, size_t(double(begin) * growth));
+            if (!careful && begin > 0) {
+                double g = growth;
+                if (use_tc) g = std::min(g, stage == 1 ? 24.0 : (stage == 2 ? 10.0 : g));
+                len = std::max<size_t>(first, size_t(double(begin) * g));
+                if (begin + len + len / 2 >= n_blocks) len = n_blocks - begin;   // no short tail chunk
+            }
             const size_t end = std::min(n_blocks, begin + len);
             sp.pos_begin = uint32_t(begin); sp.pos_end = uint32_t(end);
+            // first chunk on the tensor-memory path without a filter (the host then knows how many vectors
+            // the chunk holds): every key is written in place, nothing is counted
+            const bool dense = use_tc && stage == 0 && !careful && d_mask == nullptr;
+            sp.dense = dense ? 1 : 0;
+            ++stage;
             if (use_tc) {
                 sp.q_base = 0; sp.nq = int(nq); sp.mtile_base = 0;
                 mark_begin(h);
@@ -624,7 +637,7 @@ int search_core(tv_index *h, const float *queries, bool queries_on_device, size_
                     h->launches++;
                 }
             }
-            TV_CUDA(launch_select(cb, int(nq), st));
+            TV_CUDA(launch_select(cb, int(nq), dense ? int((end - sp.pos_begin) * kBlock) : 0, st));
             h->launches++;
             begin = end;
         }
@@ -1173,7 +1186,7 @@ int tv_search_device_noalloc(tv_index *h, const float *queries_device, size_t nq
                 h->launches++;
             }
         }
-        TV_CUDA(launch_select(cb, int(nq), st));
+        TV_CUDA(launch_select(cb, int(nq), 0, st));
         h->launches++;
     }
     TV_CUDA(launch_finalize(cb, int(nq), nullptr, int64_t(n), scores_out_device, slots_out_device, &h->d_flags->k_eff, 0, st));

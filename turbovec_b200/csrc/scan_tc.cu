@@ -272,12 +272,13 @@ scan_tc_kernel(ScanParams p, const __grid_constant__ CUtensorMap wmap, int n_sla
             asm volatile("bar.sync 1, %0;" ::"r"(kEpilogueWarps * 32) : "memory");
             int64_t slot[MT];
             float vs[MT];
-            bool live[MT];
+            bool live[MT], have_row[MT];
 #pragma unroll
             for (int m = 0; m < MT; ++m) {
                 const int row = m * kMmaM + quarter * 32 + lane;        // vector within the item
                 const uint32_t pos = pos_begin + vt * kBlocksPerItem + uint32_t(row >> 5);
                 const bool have = pos < pos_end;
+                have_row[m] = have;
                 uint32_t blk = 0;
                 if (have) blk = p.live_blocks ? p.live_blocks[pos] : pos;
                 slot[m] = int64_t(blk) * 32 + (row & 31);
@@ -300,6 +301,25 @@ scan_tc_kernel(ScanParams p, const __grid_constant__ CUtensorMap wmap, int n_sla
                     uint32_t acc[32];
                     tmem_ld32(taddr + c0, acc);
                     asm volatile("tcgen05.wait::ld.sync.aligned;" ::: "memory");
+                    if (p.dense) {
+                        // first chunk of a search: no threshold exists yet and the chunk fits the candidate lists,
+                        // so every vector's key goes to the list position of its place in the chunk — no counting;
+                        // filtered-out and padding lanes leave the empty key.  A warp writes 256 contiguous bytes
+                        // per query.
+                        const uint32_t at = (vt * kBlocksPerItem) * 32u + uint32_t(m * kMmaM + quarter * 32 + lane);
+                        if (have_row[m]) {
+#pragma unroll
+                            for (int j = 0; j < 32; ++j) {
+                                const int c = cbase + c0 + j;
+                                const int ql = qg * kTileQueries + c;
+                                if (ql < p.q_base + p.nq) {
+                                    const float score = final_score<ONEHOT>(acc[j], sh->qscale[pb][c], sh->qbias[pb][c], vs[m]);
+                                    p.cb.cand[size_t(ql) * p.cb.cap + at] = live[m] ? make_key(score, uint32_t(slot[m])) : kEmptyKey;
+                                }
+                            }
+                        }
+                        continue;
+                    }
                     // hot loop: four instructions per score, the comparison folded into one predicate
                     bool any = false;
 #pragma unroll

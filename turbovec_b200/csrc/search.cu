@@ -505,14 +505,24 @@ __global__ void __launch_bounds__(256) scan_lut_kernel(ScanParams p) {
 }
 
 // =====================================================================================================
-// Selection: one CTA per query merges the previous top-k with the new candidates by a bitonic sort of
-// their keys in shared memory.
+// Selection: one CTA per query merges the previous top-k with the new candidates in shared memory.
+// With few entries it is a plain bitonic sort.  With many more entries than k it is a bitonic top-k: sort
+// runs of m = 2^ceil(log2 k) (at least 32) entries in alternating directions, then repeatedly take the
+// element-wise minimum of each ascending/descending pair of runs (the m smallest of the pair, as a bitonic
+// sequence), drop the other half, and re-sort the survivors' runs with one bitonic merge pass; the work is
+// about n (log^2 m / 4 + 2 log m) compare-exchanges instead of n log^2 n / 4.  `dense_count` > 0 means the
+// scan wrote exactly that many candidates per query without counting them (first chunk, see scan_tc.cu).
 // =====================================================================================================
-__global__ void __launch_bounds__(256) select_kernel(CandidateBuffers cb, int sort_n) {
+__device__ __forceinline__ void compare_exchange(uint64_t *keys, int lo, int hi, bool ascending) {
+    const uint64_t a = keys[lo], b = keys[hi];
+    if ((a > b) == ascending) { keys[lo] = b; keys[hi] = a; }
+}
+
+__global__ void __launch_bounds__(256) select_kernel(CandidateBuffers cb, int sort_n, int dense_count) {
     extern __shared__ __align__(16) unsigned char smem_raw[];
     uint64_t *keys = reinterpret_cast<uint64_t *>(smem_raw);
     const int q = blockIdx.x, tid = threadIdx.x;
-    const uint32_t raw = cb.cnt[q];
+    const uint32_t raw = dense_count > 0 ? uint32_t(dense_count) : cb.cnt[q];
     const int ncand = int(min(raw, uint32_t(cb.cap)));
     if (tid == 0 && raw > uint32_t(cb.cap)) atomicExch(cb.overflow, 1u);
     const int total = cb.k + ncand;
@@ -527,14 +537,36 @@ __global__ void __launch_bounds__(256) select_kernel(CandidateBuffers cb, int so
         keys[i] = v;
     }
     __syncthreads();
-    for (int size = 2; size <= n2; size <<= 1) {
+    int m = 32;
+    while (m < cb.k) m <<= 1;
+    if (n2 <= 2 * m) m = n2;                                  // nothing to gain: full sort
+    // runs of m entries, ascending where (index & m) == 0, descending otherwise (m == n2: one ascending run)
+    for (int size = 2; size <= m; size <<= 1) {
         for (int stride = size >> 1; stride > 0; stride >>= 1) {
             for (int i = tid; i < n2 / 2; i += blockDim.x) {
                 const int lo = 2 * i - (i & (stride - 1));
-                const int hi = lo + stride;
-                const bool ascending = (lo & size) == 0;
-                const uint64_t a = keys[lo], b = keys[hi];
-                if ((a > b) == ascending) { keys[lo] = b; keys[hi] = a; }
+                compare_exchange(keys, lo, lo + stride, (lo & size) == 0);
+            }
+            __syncthreads();
+        }
+    }
+    // halving rounds: live runs sit at multiples of `step` entries; run r pairs with run r + 1 (r even)
+    for (int step = m; step * 2 <= n2 && m < n2; step <<= 1) {
+        const int pairs = n2 / (2 * step);
+        // minimum of entry j of the first run and entry j of the second: the first run keeps the m smallest
+        for (int i = tid; i < pairs * m; i += blockDim.x) {
+            const int pr = i / m, j = i - pr * m;
+            const int lo = pr * 2 * step + j, hi = lo + step;
+            const uint64_t a = keys[lo], b = keys[hi];
+            if (b < a) keys[lo] = b;
+        }
+        __syncthreads();
+        // the survivors are bitonic: one merge pass sorts them, alternating directions for the next round
+        for (int stride = m >> 1; stride > 0; stride >>= 1) {
+            for (int i = tid; i < pairs * (m / 2); i += blockDim.x) {
+                const int pr = i / (m / 2), j = i - pr * (m / 2);
+                const int lo = pr * 2 * step + 2 * j - (j & (stride - 1));
+                compare_exchange(keys, lo, lo + stride, (pr & 1) == 0);
             }
             __syncthreads();
         }
@@ -620,7 +652,7 @@ static int sort_capacity(int cap, int k) {
 }
 size_t select_smem_bytes(int cap, int k) { return size_t(sort_capacity(cap, k)) * 8; }
 
-cudaError_t launch_select(const CandidateBuffers &cb, int nq, cudaStream_t s) {
+cudaError_t launch_select(const CandidateBuffers &cb, int nq, int dense_count, cudaStream_t s) {
     if (nq <= 0) return cudaSuccess;
     const int sort_n = sort_capacity(cb.cap, cb.k);
     const size_t smem = size_t(sort_n) * 8;
@@ -630,7 +662,7 @@ cudaError_t launch_select(const CandidateBuffers &cb, int nq, cudaStream_t s) {
         if (e != cudaSuccess) return e;
         attr_set = true;
     }
-    select_kernel<<<nq, 256, smem, s>>>(cb, sort_n);
+    select_kernel<<<nq, 256, smem, s>>>(cb, sort_n, dense_count);
     return cudaGetLastError();
 }
 

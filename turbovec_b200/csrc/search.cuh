@@ -57,7 +57,8 @@ struct CandidateBuffers {
     int cap, k;
 };
 size_t select_smem_bytes(int cap, int k);
-cudaError_t launch_select(const CandidateBuffers &cb, int nq, cudaStream_t s);
+// dense_count > 0: every query has exactly that many candidates (written without counting, ScanParams::dense).
+cudaError_t launch_select(const CandidateBuffers &cb, int nq, int dense_count, cudaStream_t s);
 // topk keys -> scores / slots with row stride k_eff = min(k, n_allowed); *k_eff_out receives it.
 cudaError_t launch_finalize(const CandidateBuffers &cb, int nq, const unsigned long long *n_allowed_or_null,
                             int64_t n, float *scores, int64_t *slots, uint32_t *k_eff_out, int out_stride_is_k,
@@ -76,6 +77,8 @@ struct ScanParams {
     const uint32_t *live_blocks;   // or nullptr: positions are block ids
     const uint32_t *n_live;        // device count of live_blocks (when live_blocks != nullptr)
     uint32_t pos_begin, pos_end;   // positions scanned by this launch
+    int dense;                     // tcgen05 scan only: write every key to cand[q][place in chunk] without counting
+                                   // (the chunk holds at most cb.cap vectors; the selection is told the count)
     CandidateBuffers cb;
     // permute-dot
     const uint32_t *wfrag;
