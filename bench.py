@@ -330,6 +330,7 @@ def run_ours(args):
     ingest_bytes = 4 * DIM + ng + 4
 
     tc_min = idx.get_option(T.OPT_MMA_MIN_BATCH)
+    tc_min = 33 if tc_min < 0 else tc_min       # library default for the permute-dot family
     main_kernel = "scan_tc_kernel (tcgen05)" if tc_min > 0 and nq >= tc_min else "scan_pd_kernel (mma.sync)"
     cpu_qps, cpu_ms, cores, sample, _ = cpu_arm(200_000, 1000, 2, 1, n_total) if world == 1 and not args.no_cpu else (None,) * 5
 

@@ -222,6 +222,22 @@ def test_search_matches_oracle(T, dim, bits, n, nq):
         assert np.array_equal(s, rs), f"k={k}: scores differ"
 
 
+@pytest.mark.parametrize("dim,bits,n,nq", [(1536, 4, 5003, 70), (256, 4, 4100, 50), (1536, 2, 3000, 9), (1024, 3, 1500, 12)])
+def test_search_without_tensor_memory_path_matches_oracle(T, dim, bits, n, nq):
+    """The tensor-memory scan switched off: every batch size runs on the mma.sync / CUDA-core scans (passes of
+    up to 64 and 4 queries), which the default switch points would only use for small batches."""
+    x = anisotropic(n, dim, seed=13)
+    q = anisotropic(nq, dim, seed=13, offset=1000)
+    idx = _build(T, x, bits)
+    assert idx.get_option(T.OPT_MMA_MIN_BATCH) == -1
+    idx.set_option(T.OPT_MMA_MIN_BATCH, 0)
+    for k in (1, 10):
+        s, i = idx.search(q, k)
+        rs, ri = _oracle_search(x, q, bits, k)
+        assert np.array_equal(i, ri), f"k={k}: id lists differ"
+        assert np.array_equal(s, rs), f"k={k}: scores differ"
+
+
 def test_search_large_n_chunk_schedule(T):
     """Enough vectors for several growing chunks, and the bounded recovery schedule gives the same answer."""
     n, dim, nq = 200_000, 64, 12

@@ -90,7 +90,7 @@ struct tv_index {
 
     // options
     int score_mode = TV_SCORE_AUTO;
-    int64_t mma_min_batch = 65;  // measured switch point: mma.sync covers 64 queries per pass, tcgen05 wins beyond
+    int64_t mma_min_batch = -1;  // -1: measured switch points (permute-dot 33 queries, u8-LUT 8); 0 never; else as set
     int force_careful = 0;
     int ingest_pipeline = 1;     // 1: whole code blocks of an uncalibrated add go through the pipelined ingest kernel
     int tc_tiles = 1;            // accumulator tiles per B slab in the tcgen05 scan (1 or 2); 1 measured faster
@@ -487,7 +487,11 @@ int search_core(tv_index *h, const float *queries, bool queries_on_device, size_
     TV_CUDA(h->d_qscale.reserve(nq_pad));
     TV_CUDA(h->d_qbias.reserve(nq_pad));
     const size_t w_rows = (nq + 255) / 256 * 256;
-    const bool use_tc = h->mma_min_batch > 0 && int64_t(nq) >= h->mma_min_batch && scan_tc_supported(h->bits, mode, ng);
+    // measured on 1.25 M and 10 M x 1536 4-bit: mma.sync 0.67 / 3.6 ms up to 32 queries, 0.89 / 5.1 ms from 33 on,
+    // tcgen05 0.83 / 5.1 ms flat; on 1 M x 3072 2-bit the CUDA-core LUT scan costs 0.5 ms per query beyond 4,
+    // tcgen05 4.2 ms flat
+    const int64_t tc_from = h->mma_min_batch >= 0 ? h->mma_min_batch : (mode == TV_SCORE_PERMUTE_DOT ? 33 : 8);
+    const bool use_tc = tc_from > 0 && int64_t(nq) >= tc_from && scan_tc_supported(h->bits, mode, ng);
     if (mode == TV_SCORE_PERMUTE_DOT) {
         TV_CUDA(h->d_weights.reserve(w_rows * dim_pad));
         TV_CUDA(h->d_wfrag.reserve(size_t(ksteps) * mt_total * 32 * 4));
