@@ -148,15 +148,6 @@ def run_reference(args):
 
 
 # ------------------------------------------------------------------------------------------ GPU arm
-def merge_topk(torch, scores, slots, k):
-    """Merge per-rank lists [nq, R*k] under (score desc, slot asc)."""
-    order = torch.argsort(slots, dim=1, stable=True)
-    s = torch.gather(scores, 1, order)
-    i = torch.gather(slots, 1, order)
-    order = torch.argsort(s, dim=1, descending=True, stable=True)
-    return torch.gather(s, 1, order)[:, :k], torch.gather(i, 1, order)[:, :k]
-
-
 def run_ours(args):
     import torch
     import torch.distributed as dist
@@ -174,11 +165,14 @@ def run_ours(args):
     pk = peaks()
     n_total, nq = args.n, args.batch
 
-    # ---- build this rank's shard: global chunks dealt to ranks in contiguous runs ----
+    # ---- build this rank's shard: a contiguous range of global slots, the same number of 32-slot blocks
+    # (within one) on every rank; rows are generated in fixed global chunks so that the data does not depend
+    # on the number of ranks ----
     n_chunks = (n_total + CHUNK - 1) // CHUNK
-    per = (n_chunks + world - 1) // world
-    my_chunks = list(range(rank * per, min(n_chunks, (rank + 1) * per)))
-    slot_offset = my_chunks[0] * CHUNK if my_chunks else 0
+    blocks_total = (n_total + 31) // 32
+    lo = min(n_total, (blocks_total * rank // world) * 32)
+    hi = min(n_total, (blocks_total * (rank + 1) // world) * 32)
+    slot_offset = lo
     scale_t = torch.from_numpy(dim_scale(1)).to(device)
     idx = T.TurboQuantIndex(DIM, BITS, device=local_rank)
     if args.tc_min_batch is not None:
@@ -189,21 +183,27 @@ def run_ours(args):
     truth_i = torch.zeros((n_recall_q, K), dtype=torch.int64, device=device)
     ingest_ms, ingest_rows, ingest_launches = 0.0, 0, 0
     launches0 = idx.launch_count
-    for c in my_chunks:
-        rows = min(CHUNK, n_total - c * CHUNK)
-        x = gen_rows_torch(torch, device, scale_t, 1, c, rows)
+    first = True
+    for c in range(n_chunks):
+        c_lo, c_hi = c * CHUNK, min(n_total, (c + 1) * CHUNK)
+        a, b = max(lo, c_lo), min(hi, c_hi)
+        if a >= b:
+            continue
+        x = gen_rows_torch(torch, device, scale_t, 1, c, c_hi - c_lo)[a - c_lo: b - c_lo].contiguous()
+        rows = b - a
         # exact fp32 ground truth for recall@10, kept as a running top-k
         sc = q_all[:n_recall_q] @ x.T
         s, i = torch.topk(sc, K, dim=1)
         truth_s, sel = torch.topk(torch.cat([truth_s, s], 1), K, dim=1)
-        truth_i = torch.gather(torch.cat([truth_i, i + c * CHUNK], 1), 1, sel)
+        truth_i = torch.gather(torch.cat([truth_i, i + a], 1), 1, sel)
         torch.cuda.synchronize()
         idx.add_device(x.data_ptr(), rows, DIM)
         ms, nl = idx.last_main_kernel()
-        if c != my_chunks[0]:          # first chunk pays table set-up and allocation
-            ingest_ms += ms
+        if not first and rows == CHUNK:   # the first chunk pays table set-up and allocation; partial chunks
+            ingest_ms += ms               # add a launch of the block-at-a-time kernel for a ragged head
             ingest_rows += rows
             ingest_launches += nl
+        first = False
         del x, sc
     n_local = len(idx)
 
@@ -213,17 +213,23 @@ def run_ours(args):
     q_host = q_dev.cpu().pin_memory()
     h_scores = np.empty((nq, K), np.float32)
 
+    keys_local = torch.empty((max(nq, n_recall_q), K), dtype=torch.int64, device=device) if world > 1 else None
+    keys_all = torch.empty((world, max(nq, n_recall_q), K), dtype=torch.int64, device=device) if world > 1 else None
+
     def step_device(qd, nqq):
-        ke = idx.search_device(qd.data_ptr(), nqq, K, d_scores.data_ptr(), d_slots.data_ptr())
         if world == 1:
+            ke = idx.search_device(qd.data_ptr(), nqq, K, d_scores.data_ptr(), d_slots.data_ptr())
             return d_scores[:nqq, :ke], d_slots[:nqq, :ke]
-        ls = d_scores.view(-1)[: nqq * ke].view(nqq, ke)
-        li = d_slots.view(-1)[: nqq * ke].view(nqq, ke) + slot_offset
-        gs = [torch.empty_like(ls) for _ in range(world)]
-        gi = [torch.empty_like(li) for _ in range(world)]
-        dist.all_gather(gs, ls.contiguous())
-        dist.all_gather(gi, li.contiguous())
-        return merge_topk(torch, torch.cat(gs, 1), torch.cat(gi, 1), K)
+        # per-rank scan -> one all-gather of the result keys -> one merge kernel, all on the device
+        kl, ka = keys_local[:nqq], keys_all[:, :nqq]
+        if nqq != keys_local.shape[0]:
+            kl = keys_local.view(-1)[: nqq * K].view(nqq, K)
+            ka = keys_all.view(-1)[: world * nqq * K].view(world, nqq, K)
+        idx.search_device_keys(qd.data_ptr(), nqq, K, kl.data_ptr(), slot_offset)
+        dist.all_gather_into_tensor(ka, kl)
+        T.merge_keys_device(ka.data_ptr(), world, nqq, K, d_scores.data_ptr(), d_slots.data_ptr(), device=local_rank,
+                            stream=torch.cuda.current_stream().cuda_stream)
+        return d_scores.view(-1)[: nqq * K].view(nqq, K), d_slots.view(-1)[: nqq * K].view(nqq, K)
 
     def step_host(qh, nqq):
         """qh: pinned host tensor.  Host buffers in, host results out."""

@@ -158,6 +158,22 @@ int tv_search_device(tv_index *h, const float *queries_device, size_t nq, size_t
                      const uint64_t *mask_words_device, float *scores_out_device, int64_t *slots_out_device,
                      size_t *k_eff);
 
+/* ---- slot-sharded search over several GPUs (one process per GPU).  No reference counterpart: the reference
+ * is a single-host library; these two calls are the per-rank half and the merge half of a sharded search. ----
+ * tv_search_device_keys: like tv_search_device, but each result is one 64-bit key = (order-preserving image of
+ * the score, descending) << 32 | (slot + slot_offset); ascending key order is the reference's result order
+ * (score descending, slot ascending, search.rs:236-252).  Rows are k keys wide, padded with TV_EMPTY_KEY.
+ * slot_offset = the shard's first global slot; slot_offset + len must not exceed 2^32.
+ * tv_merge_keys_device: keys[n_lists][nq][k] (e.g. the all-gathered rows of every rank) -> per query the k
+ * best, decoded to scores and global slots (rows of k; unused places hold (-inf, 0)); runs on `stream`
+ * (a cudaStream_t, may be null) of `device` without synchronising; n_lists * k <= 8192. */
+#define TV_EMPTY_KEY 0xffffffffffffffffull
+int tv_search_device_keys(tv_index *h, const float *queries_device, size_t nq, size_t k,
+                          const uint64_t *mask_words_device, uint64_t slot_offset, uint64_t *keys_out_device,
+                          size_t *k_eff);
+int tv_merge_keys_device(int device, const uint64_t *keys_device, size_t n_lists, size_t nq, size_t k,
+                         float *scores_out_device, int64_t *slots_out_device, void *stream);
+
 /* Search that performs no allocation of any kind.  This entry point has no counterpart in the reference:
  * it exists for callers that must not reach the CUDA allocator while they serve — latency-critical loops
  * (cudaMalloc locks the device and may synchronise it), processes whose device memory is fully handed out,

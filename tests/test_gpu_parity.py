@@ -501,3 +501,35 @@ def test_sharded_index_single_rank_on_device(T):
     ref.set_row(3, codes, scale)
     c2, s2 = ref.get_row(3)
     assert np.array_equal(c2, codes) and s2 == scale
+
+
+@pytest.mark.parametrize("nq,k", [(5, 10), (70, 100), (3, 1200)])
+def test_keyed_shard_search_and_device_merge_equal_the_whole_index(T, nq, k):
+    """Two shards searched with result keys and global slot offsets, merged on the device, give exactly the
+    scores and slots of one index holding all vectors (a vector's score does not depend on its neighbours)."""
+    import torch
+    n, dim = 2000, 256
+    x = anisotropic(n, dim, seed=21)
+    q = anisotropic(nq, dim, seed=21, offset=500)
+    whole = T.TurboQuantIndex(dim, 4)
+    whole.add(x)
+    want_s, want_i = whole.search(q, k)
+    cut = 1120
+    shards = [T.TurboQuantIndex(dim, 4), T.TurboQuantIndex(dim, 4)]
+    shards[0].add(x[:cut])
+    shards[1].add(x[cut:])
+    qd = torch.from_numpy(q).cuda()
+    keys = torch.empty((2, nq, k), dtype=torch.int64, device="cuda")
+    for r, (idx, off) in enumerate(zip(shards, (0, cut))):
+        ke = idx.search_device_keys(qd.data_ptr(), nq, k, keys[r].data_ptr(), off)
+        assert ke == min(k, len(idx))
+    s = torch.empty((nq, k), dtype=torch.float32, device="cuda")
+    i = torch.empty((nq, k), dtype=torch.int64, device="cuda")
+    T.merge_keys_device(keys.data_ptr(), 2, nq, k, s.data_ptr(), i.data_ptr(), device=0,
+                        stream=torch.cuda.current_stream().cuda_stream)
+    torch.cuda.synchronize()
+    ke = want_s.shape[1]
+    assert np.array_equal(i.cpu().numpy()[:, :ke], want_i)
+    assert np.array_equal(s.cpu().numpy()[:, :ke], want_s)
+    if ke < k:                                      # places past the number of vectors: (-inf, 0) padding
+        assert np.all(np.isneginf(s.cpu().numpy()[:, ke:])) and np.all(i.cpu().numpy()[:, ke:] == 0)

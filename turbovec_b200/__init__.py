@@ -280,6 +280,18 @@ class TurboQuantIndex(_Base):
                                                 C.c_void_p(scores_ptr), C.c_void_p(slots_ptr), C.byref(k_eff)))
         return int(k_eff.value)
 
+    def search_device_keys(self, q_ptr: int, nq: int, k: int, keys_ptr: int, slot_offset: int = 0,
+                           mask_words_ptr: int = 0) -> int:
+        """Device-resident search of one shard of a slot-sharded index: writes rows of k 64-bit result keys
+        (ascending key = score descending, then global slot ascending; padded with EMPTY_KEY) with
+        `slot_offset` added to every slot.  All-gather the rows of every rank and pass them to
+        merge_keys_device.  Returns this shard's k_eff."""
+        k_eff = C.c_size_t(0)
+        self._check(self._lib.tv_search_device_keys(self._h, C.c_void_p(q_ptr), nq, k,
+                                                     C.c_void_p(mask_words_ptr) if mask_words_ptr else None,
+                                                     C.c_uint64(slot_offset), C.c_void_p(keys_ptr), C.byref(k_eff)))
+        return int(k_eff.value)
+
     def search_device_noalloc(self, q_ptr: int, nq: int, k: int, scores_ptr: int, slots_ptr: int) -> int:
         """Like search_device (unfiltered) but guaranteed not to allocate: scratch is a fixed array inside
         the library.  For callers that must keep away from the CUDA allocator while serving.  Limits:
@@ -354,3 +366,18 @@ class IdMapIndex(_Base):
 
     def __repr__(self):
         return f"IdMapIndex(dim={self.dim}, bit_width={self.bit_width}, len={len(self)})"
+
+
+EMPTY_KEY = 0xFFFFFFFFFFFFFFFF
+
+
+def merge_keys_device(keys_ptr: int, n_lists: int, nq: int, k: int, scores_ptr: int, slots_ptr: int, *, device: int = 0,
+                      stream: int = 0) -> None:
+    """keys[n_lists][nq][k] (device memory, e.g. all-gathered search_device_keys rows) -> per query the k best,
+    decoded into scores[nq][k] (float32) and global slots[nq][k] (int64).  Enqueued on `stream` (a raw
+    cudaStream_t value, 0 = default stream) without synchronising."""
+    lib = _native.load()
+    rc = lib.tv_merge_keys_device(device, C.c_void_p(keys_ptr), n_lists, nq, k, C.c_void_p(scores_ptr), C.c_void_p(slots_ptr),
+                                  C.c_void_p(stream) if stream else None)
+    if rc != 0:
+        raise RuntimeError(lib.tv_last_error(None).decode() or f"tv_merge_keys_device failed with status {rc}")

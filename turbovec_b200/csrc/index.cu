@@ -113,6 +113,7 @@ struct tv_index {
     DeviceArray<uint16_t> d_perm;            // [2][dim]
     DeviceArray<float> d_codebook;           // boundaries (16 slots) then centroids (16 slots)
     DeviceArray<uint2> d_qgrid;              // quantisation grid of the pipelined ingest kernel
+    DeviceArray<uint64_t> d_keys_tmp;        // staging of tv_search_device_keys when the shard holds fewer than k vectors
     QuantGrid qgrid;                         // cells == nullptr: the codebook has no valid grid
     DeviceArray<float> d_calib;              // shift, scale, inv_scale  [3][dim]
     float level_scale = 1.f;                 // cs of the permute-dot level table
@@ -465,7 +466,8 @@ int candidate_capacity(size_t k) { return k <= 512 ? 4096 : 8192; }
 // The whole search on the handle's stream.  Results land in d_scores/d_slots (row stride k) unless
 // out_scores_dev is given (row stride k_eff).
 int search_core(tv_index *h, const float *queries, bool queries_on_device, size_t nq, size_t k, const MaskSpec &mask,
-                float *out_scores_dev, int64_t *out_slots_dev, size_t *k_eff_out) {
+                float *out_scores_dev, int64_t *out_slots_dev, size_t *k_eff_out, uint64_t *out_keys_dev = nullptr,
+                uint64_t key_offset = 0) {
     const size_t dim = h->dim, n = h->n;
     const int ng = h->ngroups;
     const int mode = resolve_mode(h);
@@ -654,12 +656,13 @@ int search_core(tv_index *h, const float *queries, bool queries_on_device, size_
         int rc = run_schedule(careful);
         if (rc != TV_OK) return rc;
         const unsigned long long *d_allowed = d_mask ? &h->d_flags->n_allowed : nullptr;
+        if (out_keys_dev) TV_CUDA(launch_export_keys(cb.topk, int64_t(nq * kk), key_offset, out_keys_dev, st));
         if (out_scores_dev) TV_CUDA(launch_finalize(cb, int(nq), d_allowed, int64_t(n), out_scores_dev, out_slots_dev, d_keff, 0, st));
         else TV_CUDA(launch_finalize(cb, int(nq), d_allowed, int64_t(n), h->d_scores.ptr, h->d_slots.ptr, d_keff, 1, st));
         h->launches++;
         TV_CUDA(cudaEventRecord(h->ev1, st));
         TV_CUDA(cudaMemcpyAsync(h->h_flags, h->d_flags, sizeof(DeviceFlags), cudaMemcpyDeviceToHost, st));
-        if (!out_scores_dev) {
+        if (!out_scores_dev && !out_keys_dev) {
             TV_CUDA(h->h_scores.reserve(nq * kk));
             TV_CUDA(h->h_slots.reserve(nq * kk));
             TV_CUDA(cudaMemcpyAsync(h->h_scores.ptr, h->d_scores.ptr, nq * kk * 4, cudaMemcpyDeviceToHost, st));
@@ -1054,6 +1057,52 @@ int tv_search_device(tv_index *h, const float *queries_device, size_t nq, size_t
     int rc = search_core(h, queries_device, true, nq, k, m, scores_out_device, slots_out_device, &ke);
     if (rc == TV_OK && k_eff) *k_eff = ke;
     return rc;
+}
+
+int tv_search_device_keys(tv_index *h, const float *queries_device, size_t nq, size_t k, const uint64_t *mask_words_device,
+                          uint64_t slot_offset, uint64_t *keys_out_device, size_t *k_eff) {
+    if (!h || (!queries_device && nq) || !keys_out_device) return TV_ERR_INVALID_ARGUMENT;
+    std::lock_guard<std::mutex> lock(h->mu);
+    if (k_eff) *k_eff = 0;
+    if (nq == 0 || k == 0) return TV_OK;
+    if (slot_offset + h->n > 0x100000000ull) return fail(h, TV_ERR_UNSUPPORTED, "slot_offset + len exceeds 2^32: the key holds 32 slot bits");
+    TV_CUDA(cudaSetDevice(h->device));
+    const size_t kk = std::min(k, h->n);
+    if (h->dim == 0 || h->n == 0 || kk < k) {
+        // rows are k wide whatever the shard holds: fill with empty keys first
+        TV_CUDA(cudaMemsetAsync(keys_out_device, 0xff, nq * k * 8, h->stream));
+        TV_CUDA(cudaStreamSynchronize(h->stream));
+        if (h->dim == 0 || h->n == 0) return TV_OK;
+    }
+    MaskSpec m;
+    m.words_device = mask_words_device;
+    size_t ke = 0;
+    int rc;
+    if (kk == k) {
+        rc = search_core(h, queries_device, true, nq, k, m, nullptr, nullptr, &ke, keys_out_device, slot_offset);
+    } else {
+        // fewer vectors than k: the search yields rows of kk keys; spread them over rows of k
+        TV_CUDA(h->d_keys_tmp.reserve(nq * kk));
+        rc = search_core(h, queries_device, true, nq, k, m, nullptr, nullptr, &ke, h->d_keys_tmp.ptr, slot_offset);
+        if (rc == TV_OK) {
+            TV_CUDA(cudaMemcpy2DAsync(keys_out_device, k * 8, h->d_keys_tmp.ptr, kk * 8, kk * 8, nq, cudaMemcpyDeviceToDevice, h->stream));
+            TV_CUDA(cudaStreamSynchronize(h->stream));
+        }
+    }
+    if (rc == TV_OK && k_eff) *k_eff = ke;
+    return rc;
+}
+
+int tv_merge_keys_device(int device, const uint64_t *keys_device, size_t n_lists, size_t nq, size_t k, float *scores_out_device,
+                         int64_t *slots_out_device, void *stream) {
+    if (!keys_device || !scores_out_device || !slots_out_device) return TV_ERR_INVALID_ARGUMENT;
+    if (n_lists == 0 || nq == 0 || k == 0) return TV_OK;
+    if (n_lists * k > size_t(kMergeMaxKeys)) { g_create_error = "n_lists * k exceeds 8192 keys per query"; return TV_ERR_UNSUPPORTED; }
+    if (cudaSetDevice(device) != cudaSuccess) { g_create_error = "cudaSetDevice failed"; return TV_ERR_CUDA; }
+    cudaError_t e = launch_merge_keys(keys_device, int(n_lists), int(nq), int(k), scores_out_device, slots_out_device,
+                                      static_cast<cudaStream_t>(stream));
+    if (e != cudaSuccess) { g_create_error = std::string("merge kernel launch: ") + cudaGetErrorString(e); return TV_ERR_CUDA; }
+    return TV_OK;
 }
 
 // -----------------------------------------------------------------------------------------------------

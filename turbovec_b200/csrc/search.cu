@@ -596,6 +596,47 @@ __global__ void finalize_kernel(CandidateBuffers cb, int nq, const unsigned long
     slots[size_t(q) * stride + j] = slot;
 }
 
+// Keys of a finished search with a slot offset added (the shard's first global slot); empty entries stay empty.
+__global__ void export_keys_kernel(const uint64_t *topk, int64_t count, uint64_t offset, uint64_t *out) {
+    const int64_t i = int64_t(blockIdx.x) * blockDim.x + threadIdx.x;
+    if (i >= count) return;
+    const uint64_t key = topk[i];
+    out[i] = key == kEmptyKey ? key : key + offset;
+}
+
+// Merge of the per-shard result lists of one query: keys[list][q][k] -> the k best keys, decoded.  One CTA per
+// query, bitonic sort of n_lists * k keys in shared memory (ascending keys = score descending, slot ascending).
+__global__ void __launch_bounds__(256) merge_keys_kernel(const uint64_t *keys_in, int n_lists, int nq, int k, int n2,
+                                                         float *scores, int64_t *slots) {
+    extern __shared__ __align__(16) unsigned char smem_raw[];
+    uint64_t *keys = reinterpret_cast<uint64_t *>(smem_raw);
+    const int q = blockIdx.x, tid = threadIdx.x;
+    const int total = n_lists * k;
+    for (int i = tid; i < n2; i += blockDim.x) {
+        uint64_t v = kEmptyKey;
+        if (i < total) v = keys_in[(size_t(i / k) * nq + q) * k + (i % k)];
+        keys[i] = v;
+    }
+    __syncthreads();
+    for (int size = 2; size <= n2; size <<= 1) {
+        for (int stride = size >> 1; stride > 0; stride >>= 1) {
+            for (int i = tid; i < n2 / 2; i += blockDim.x) {
+                const int lo = 2 * i - (i & (stride - 1));
+                compare_exchange(keys, lo, lo + stride, (lo & size) == 0);
+            }
+            __syncthreads();
+        }
+    }
+    for (int j = tid; j < k; j += blockDim.x) {
+        const uint64_t key = keys[j];
+        float s = -INFINITY;
+        int64_t slot = 0;                 // (-inf, 0) padding, as finalize_kernel
+        if (key != kEmptyKey) { s = desc_bits_to_score(uint32_t(key >> 32)); slot = int64_t(key & 0xffffffffu); }
+        scores[size_t(q) * k + j] = s;
+        slots[size_t(q) * k + j] = slot;
+    }
+}
+
 }  // namespace
 
 // =====================================================================================================
@@ -663,6 +704,27 @@ cudaError_t launch_select(const CandidateBuffers &cb, int nq, int dense_count, c
         attr_set = true;
     }
     select_kernel<<<nq, 256, smem, s>>>(cb, sort_n, dense_count);
+    return cudaGetLastError();
+}
+
+cudaError_t launch_export_keys(const uint64_t *topk, int64_t count, uint64_t offset, uint64_t *out, cudaStream_t s) {
+    if (count <= 0) return cudaSuccess;
+    export_keys_kernel<<<unsigned((count + 255) / 256), 256, 0, s>>>(topk, count, offset, out);
+    return cudaGetLastError();
+}
+
+cudaError_t launch_merge_keys(const uint64_t *keys, int n_lists, int nq, int k, float *scores, int64_t *slots, cudaStream_t s) {
+    if (nq <= 0 || k <= 0 || n_lists <= 0) return cudaSuccess;
+    int n2 = 32;
+    while (n2 < n_lists * k) n2 <<= 1;
+    if (n2 > kMergeMaxKeys) return cudaErrorInvalidValue;
+    static bool attr_set = false;
+    if (!attr_set) {
+        cudaError_t e = cudaFuncSetAttribute(merge_keys_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, kMergeMaxKeys * 8);
+        if (e != cudaSuccess) return e;
+        attr_set = true;
+    }
+    merge_keys_kernel<<<nq, 256, size_t(n2) * 8, s>>>(keys, n_lists, nq, k, n2, scores, slots);
     return cudaGetLastError();
 }
 
