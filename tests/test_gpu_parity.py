@@ -87,7 +87,7 @@ def test_ingest_zero_and_tiny_rows(T):
 
 
 @pytest.mark.parametrize("dim,bits", [(128, 4), (256, 2), (384, 3), (512, 4), (768, 4), (1024, 2), (1536, 3), (1536, 4),
-                                      (2048, 4), (2048, 2)])
+                                      (2048, 4), (2048, 2), (3072, 2), (3072, 4)])
 def test_pipelined_ingest_matches_oracle_and_block_kernel(T, dim, bits):
     """Whole code blocks go through the pipelined kernel, a partial head block through the block-at-a-time
     one; both must produce the oracle's bytes and scales, and so must the block-at-a-time kernel alone and

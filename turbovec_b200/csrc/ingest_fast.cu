@@ -102,10 +102,10 @@ __device__ __forceinline__ float max_nan(float a, float b) {   // NaN wins, unli
 }
 
 
-constexpr int kWave = 8;                 // vectors per wave = rotation warps
-constexpr int kWavesPerBlock = kBlockLanes / kWave;
-constexpr int kFastThreads = 384;        // 8 rotation warps; norm (even waves), staging, norm (odd waves), copy
-constexpr int kRotationRegs = 208, kServiceRegs = 88;   // 8*32*208 + 4*32*88 <= 384 * 168
+// Vectors per wave = rotation warps: 8 (three warpgroups, 384 threads), or 4 (two warpgroups, 256 threads) for
+// dimensions whose rows would not fit twice eight times in shared memory.  Warps V .. V+3 are the service
+// warps: norm (even waves), staging, norm (odd waves), copy.
+constexpr int kRotationRegs = 208, kServiceRegs = 88;   // wave of 8: 8*32*208 + 4*32*88 <= 384 * 168
 constexpr int kGridCells = 1024;         // cells of the quantisation grid
 constexpr float kGridTop = 8.0f * (kGridCells - 1);
 constexpr float kGridMagic = 8388608.0f; // 2^23: adding it leaves the rounded integer in the low mantissa bits
@@ -131,16 +131,16 @@ struct FastLayout {
     int stride;          // floats per staged row (16-byte multiple for the bulk copies)
     size_t grid, cent, rows, tile, norm, inv, bars, total;
 };
-__host__ __device__ inline FastLayout fast_layout(int dim, int ngroups) {
+__host__ __device__ inline FastLayout fast_layout(int wave, int dim, int ngroups) {
     FastLayout L;
     L.stride = dim + 4;
     size_t off = 0;
     L.grid = off; off += size_t(kGridCells) * 8;       // first, so that its address is a link-time constant
     L.cent = off; off += 16 * 8;                       // centroids as f64
-    L.rows = off; off += size_t(2) * kWave * L.stride * 4;
+    L.rows = off; off += size_t(2) * wave * L.stride * 4;
     L.tile = off; off += size_t(2) * ngroups * 32;
-    L.norm = off; off += 4 * kWave * 4;
-    L.inv = off; off += 4 * kWave * 4;
+    L.norm = off; off += 4 * wave * 4;
+    L.inv = off; off += 4 * wave * 4;
     L.bars = off; off += 2 * 8;
     L.total = off;
     return L;
@@ -211,18 +211,20 @@ __device__ __forceinline__ void wht_blocks(float (&v)[R * NBLK], int lane) {
     }
 }
 
-template <int LOG2B, int NBLK>
-__global__ void __launch_bounds__(kFastThreads, 1) ingest_fast_kernel(IngestParams p, QuantGrid grid, uint32_t *error) {
+template <int LOG2B, int NBLK, int V>
+__global__ void __launch_bounds__((V + 4) * 32, 1) ingest_fast_kernel(IngestParams p, QuantGrid grid, uint32_t *error) {
     constexpr int R = 1 << (LOG2B - 5);               // registers per Hadamard block and lane
     constexpr int T = R * NBLK;                       // registers per vector and lane
     constexpr int DIM = T * 32;
-    constexpr int V = kWave, wpb = kWavesPerBlock;
+    constexpr int wpb = kBlockLanes / V;
+    constexpr int kFastThreads = (V + 4) * 32;
+    static_assert(V == 8 || V == 4, "waves of 8 or 4 vectors");
     static_assert(T % 4 == 0, "the packing below handles whole groups of four registers");
     constexpr int kNormBatch = (DIM / 16) % 16 == 0 ? 16 : 8;   // chain steps per load batch; a half wave has DIM / 16 steps
     extern __shared__ __align__(128) unsigned char smem[];
     const int ng = p.ngroups;
     const int cpb = p.bits == 2 ? 4 : 2;              // codes per byte (3-bit codes sit in 4-bit fields)
-    const FastLayout L = fast_layout(DIM, ng);
+    const FastLayout L = fast_layout(V, DIM, ng);
     float *rows = reinterpret_cast<float *>(smem + L.rows);
     unsigned char *tiles = smem + L.tile;
     float *norm_s = reinterpret_cast<float *>(smem + L.norm);     // [4][8]
@@ -254,7 +256,7 @@ __global__ void __launch_bounds__(kFastThreads, 1) ingest_fast_kernel(IngestPara
     };
 
     if (warp < V) {
-        asm volatile("setmaxnreg.inc.sync.aligned.u32 %0;" ::"n"(kRotationRegs) : "memory");
+        if constexpr (V == 8) asm volatile("setmaxnreg.inc.sync.aligned.u32 %0;" ::"n"(kRotationRegs) : "memory");
         // ------------------------------------------------ rotation + quantisation: one vector per warp
         uint32_t pk[T];          // per register: round-1 byte offset | sign << 15, round-2 the same in the high half
 #pragma unroll
@@ -401,7 +403,7 @@ __global__ void __launch_bounds__(kFastThreads, 1) ingest_fast_kernel(IngestPara
             __syncthreads();
         }
     } else {
-        asm volatile("setmaxnreg.dec.sync.aligned.u32 %0;" ::"n"(kServiceRegs) : "memory");
+        if constexpr (V == 8) asm volatile("setmaxnreg.dec.sync.aligned.u32 %0;" ::"n"(kServiceRegs) : "memory");
         if (warp == V || warp == V + 2) {
             // -------------------------------------------- norms: this warp takes the waves of one parity and
             // spreads each over two steps (first half of the chains in step w - 1, second half in step w)
@@ -418,7 +420,7 @@ __global__ void __launch_bounds__(kFastThreads, 1) ingest_fast_kernel(IngestPara
                         if (slot >= 0)
                             asm volatile("cp.async.bulk.prefetch.L2.global [%0], %1;" ::"l"(p.x + (slot - slot_lo) * DIM), "r"(DIM * 4) : "memory");
                     }
-                    const int64_t slot = wave_slot(w, vv);
+                    const int64_t slot = vv < V ? wave_slot(w, vv) : -1;
                     // chains 2pp and 2pp+1: x[j]^2 summed over j = chain (mod 8) in ascending j (encode.rs:900-932)
                     const bool whole = second && it == 0;             // wave 0 has no earlier step
                     if (!second || whole) { a0 = 0.0f; a1 = 0.0f; }
@@ -441,7 +443,7 @@ __global__ void __launch_bounds__(kFastThreads, 1) ingest_fast_kernel(IngestPara
                         float s = __fadd_rn(a0, a1);                              // (c0+c1), (c2+c3), (c4+c5), (c6+c7)
                         s = __fadd_rn(s, __shfl_down_sync(kFullMask, s, 1));      // valid on pp = 0 and pp = 2
                         s = __fadd_rn(s, __shfl_down_sync(kFullMask, s, 2));      // valid on pp = 0
-                        if (pp == 0) {
+                        if (pp == 0 && vv < V) {
                             const float nv = __fsqrt_rn(s);
                             norm_s[(w & 3) * V + vv] = nv;
                             inv_s[(w & 3) * V + vv] = nv > kMinNorm ? __fdiv_rn(1.0f, nv) : 0.0f;    // encode.rs:446
@@ -529,39 +531,54 @@ uint32_t quant_grid_code(const QuantGridHost &g, float x) {
     return c.code8 / 8 + (x > inside ? 1u : 0u);
 }
 
-size_t ingest_fast_smem_bytes(int dim, int ngroups) { return fast_layout(dim, ngroups).total; }
+namespace {
+// 8 vectors per wave where two row sets of 8 fit into shared memory next to the tiles, else 4
+int wave_for(int dim, int ngroups, size_t smem_limit) {
+    if (dim <= 2048 && fast_layout(8, dim, ngroups).total <= smem_limit) return 8;
+    return fast_layout(4, dim, ngroups).total <= smem_limit ? 4 : 0;
+}
+}  // namespace
 
 bool ingest_fast_supported(int dim, int bits, int ngroups, bool calibrated, const void *x, size_t smem_limit) {
     if (calibrated || (reinterpret_cast<uintptr_t>(x) & 15) != 0) return false;
     if (bits != 2 && bits != 3 && bits != 4) return false;
     switch (dim) {
-        case 128: case 256: case 384: case 512: case 768: case 1024: case 1536: case 2048: break;
+        case 128: case 256: case 384: case 512: case 768: case 1024: case 1536: case 2048: case 3072: break;
         default: return false;
     }
-    return fast_layout(dim, ngroups).total <= smem_limit;
+    return wave_for(dim, ngroups, smem_limit) != 0;
 }
 
 cudaError_t launch_ingest_fast(const IngestParams &p, const QuantGrid &grid, int sm_count, size_t smem_limit, uint32_t *error,
                                cudaStream_t stream) {
     if (p.n <= 0) return cudaSuccess;
     if (p.slot0 % kBlockLanes != 0 || grid.cells == nullptr) return cudaErrorInvalidValue;
-    const size_t smem = fast_layout(p.dim, p.ngroups).total;
-    if (smem > smem_limit) return cudaErrorInvalidValue;
+    const int wave = wave_for(p.dim, p.ngroups, smem_limit);
+    if (wave == 0) return cudaErrorInvalidValue;
+    const size_t smem = fast_layout(wave, p.dim, p.ngroups).total;
     const int64_t nblocks = (p.n + kBlockLanes - 1) / kBlockLanes;
     const unsigned nctas = unsigned(std::min<int64_t>(nblocks, int64_t(sm_count)));   // one CTA per SM: it owns the register file
-#define TV_LAUNCH_FAST(D, L2B, NB)                                                                                   \
-    case D: {                                                                                                        \
-        cudaError_t e = cudaFuncSetAttribute(ingest_fast_kernel<L2B, NB>, cudaFuncAttributeMaxDynamicSharedMemorySize, int(smem)); \
+#define TV_LAUNCH_FAST_V(L2B, NB, VV)                                                                                \
+    {                                                                                                                \
+        cudaError_t e = cudaFuncSetAttribute(ingest_fast_kernel<L2B, NB, VV>, cudaFuncAttributeMaxDynamicSharedMemorySize, int(smem)); \
         if (e != cudaSuccess) return e;                                                                              \
-        ingest_fast_kernel<L2B, NB><<<nctas, kFastThreads, smem, stream>>>(p, grid, error);                          \
-        break;                                                                                                       \
+        ingest_fast_kernel<L2B, NB, VV><<<nctas, (VV + 4) * 32, smem, stream>>>(p, grid, error);                     \
     }
+#define TV_LAUNCH_FAST(D, L2B, NB)                                                                                   \
+    case D:                                                                                                          \
+        if (wave == 8) TV_LAUNCH_FAST_V(L2B, NB, 8) else TV_LAUNCH_FAST_V(L2B, NB, 4)                                \
+        break;
     switch (p.dim) {
         TV_LAUNCH_FAST(128, 7, 1) TV_LAUNCH_FAST(256, 8, 1) TV_LAUNCH_FAST(384, 7, 3) TV_LAUNCH_FAST(512, 9, 1)
-        TV_LAUNCH_FAST(768, 8, 3) TV_LAUNCH_FAST(1024, 10, 1) TV_LAUNCH_FAST(1536, 9, 3) TV_LAUNCH_FAST(2048, 11, 1)
+        TV_LAUNCH_FAST(768, 8, 3) TV_LAUNCH_FAST(1024, 10, 1) TV_LAUNCH_FAST(1536, 9, 3)
+        case 2048:
+            if (wave == 8) TV_LAUNCH_FAST_V(11, 1, 8) else TV_LAUNCH_FAST_V(11, 1, 4)
+            break;
+        case 3072: TV_LAUNCH_FAST_V(10, 3, 4) break;
         default: return cudaErrorInvalidValue;
     }
 #undef TV_LAUNCH_FAST
+#undef TV_LAUNCH_FAST_V
     return cudaGetLastError();
 }
 
