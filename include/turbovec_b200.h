@@ -241,6 +241,11 @@ const char *tv_version(void);
  * boundaries admit no grid (the kernel is then not used).  No reference counterpart: it exists so that the
  * table construction can be checked against a plain count without a device. */
 int tv_quantise_grid_lookup(const float *boundaries, int count, const float *values, size_t n, uint8_t *codes_out);
+/* Host-side check of the shared-memory layout through which the two rotation rounds of the pipelined ingest
+ * kernel exchange a row (built per dimension by edge-colouring the store/gather instruction graph): the
+ * largest number of lanes of one warp instruction that fall on one bank, for the stores and for the round-2
+ * gathers, with plain rows and with the layout (1 = conflict-free).  No reference counterpart; for tests. */
+int tv_exchange_layout_conflicts(size_t dim, int *store_plain, int *gather_plain, int *store_layout, int *gather_layout);
 
 #ifdef __cplusplus
 }

@@ -143,3 +143,14 @@ def test_quantisation_grid_refuses_crowded_boundaries(lib):
                                      x.ctypes.data_as(ctypes.POINTER(ctypes.c_float)), 1,
                                      out.ctypes.data_as(ctypes.POINTER(ctypes.c_uint8)))
     assert rc == 93   # TV_ERR_UNSUPPORTED: the index then keeps to the block-at-a-time kernel
+
+
+@pytest.mark.parametrize("dim", [128, 256, 384, 512, 768, 1024, 1536, 2048, 3072])
+def test_exchange_layout_is_conflict_free(lib, dim):
+    """Edge colouring of the store/gather instruction graph: with the layout no warp instruction of the
+    pipelined ingest kernel's round-1 store or round-2 gather has two lanes on one shared-memory bank."""
+    v = [ctypes.c_int(0) for _ in range(4)]
+    assert lib.tv_exchange_layout_conflicts(dim, *[ctypes.byref(x) for x in v]) == 0
+    store_plain, gather_plain, store_layout, gather_layout = [x.value for x in v]
+    assert store_plain == 1 and gather_plain >= 2      # plain rows: contiguous stores, random gathers
+    assert store_layout == 1 and gather_layout == 1

@@ -19,6 +19,7 @@ _H = C.c_void_p
 # name -> (restype, argtypes); every symbol declared in include/turbovec_b200.h
 SIGNATURES = {
     "tv_version": (C.c_char_p, []),
+    "tv_exchange_layout_conflicts": (C.c_int, [C.c_size_t] + [C.POINTER(C.c_int)] * 4),
     "tv_search_device_keys": (C.c_int, [_H, C.c_void_p, C.c_size_t, C.c_size_t, C.c_void_p, C.c_uint64, C.c_void_p, C.POINTER(C.c_size_t)]),
     "tv_merge_keys_device": (C.c_int, [C.c_int, C.c_void_p, C.c_size_t, C.c_size_t, C.c_size_t, C.c_void_p, C.c_void_p, C.c_void_p]),
     "tv_quantise_grid_lookup": (C.c_int, [C.POINTER(C.c_float), C.c_int, C.POINTER(C.c_float), C.c_size_t, C.POINTER(C.c_uint8)]),

@@ -115,6 +115,9 @@ struct tv_index {
     DeviceArray<uint2> d_qgrid;              // quantisation grid of the pipelined ingest kernel
     DeviceArray<uint64_t> d_keys_tmp;        // staging of tv_search_device_keys when the shard holds fewer than k vectors
     QuantGrid qgrid;                         // cells == nullptr: the codebook has no valid grid
+    DeviceArray<uint8_t> d_store_bank;       // exchange layout of the pipelined ingest kernel (empty: plain rows)
+    DeviceArray<uint16_t> d_perm1_exchange;
+    bool exchange_ready = false;
     DeviceArray<float> d_calib;              // shift, scale, inv_scale  [3][dim]
     float level_scale = 1.f;                 // cs of the permute-dot level table
     int8_t levels[16] = {0};
@@ -256,6 +259,17 @@ int ensure_tables(tv_index *h) {
     TV_CUDA(h->d_perm.reserve(size_t(2) * dim));
     TV_CUDA(cudaMemcpyAsync(h->d_perm.ptr, h->rot.packed[0].data(), size_t(dim) * 2, cudaMemcpyHostToDevice, h->stream));
     TV_CUDA(cudaMemcpyAsync(h->d_perm.ptr + dim, h->rot.packed[1].data(), size_t(dim) * 2, cudaMemcpyHostToDevice, h->stream));
+    // bank-conflict-free exchange layout of the pipelined ingest kernel (vectors of up to 48 registers per lane: beyond that the kernel has no registers for the offsets)
+    h->exchange_ready = false;
+    ExchangeLayoutHost ex;
+    if (dim % 32 == 0 && dim / 32 <= 48 && build_exchange_layout(int(dim), h->rot.packed[1].data(), ex)) {
+        TV_CUDA(h->d_store_bank.reserve(dim));
+        TV_CUDA(h->d_perm1_exchange.reserve(dim));
+        TV_CUDA(cudaMemcpyAsync(h->d_store_bank.ptr, ex.store_bank.data(), dim, cudaMemcpyHostToDevice, h->stream));
+        TV_CUDA(cudaMemcpyAsync(h->d_perm1_exchange.ptr, ex.perm1_exchange.data(), size_t(dim) * 2, cudaMemcpyHostToDevice, h->stream));
+        TV_CUDA(cudaStreamSynchronize(h->stream));     // `ex` goes out of scope
+        h->exchange_ready = true;
+    }
     int rc = upload_codebook(h);
     if (rc != TV_OK) return rc;
     h->tables_ready = true;
@@ -418,6 +432,7 @@ int add_rows(tv_index *h, const float *x, size_t n, size_t dim, bool on_device) 
         if (int64_t(rows) > head) {
             p.x = src + head * int64_t(dim); p.n = int64_t(rows) - head; p.slot0 += head; p.row_base += head;
             p.exact_sums = h->ingest_pipeline == 2;
+            if (h->exchange_ready) { p.store_bank = h->d_store_bank.ptr; p.perm1_exchange = h->d_perm1_exchange.ptr; }
             mark_begin(h);
             TV_CUDA(launch_ingest_fast(p, h->qgrid, h->sm_count, h->smem_limit, &h->d_flags->error, h->stream));
             mark_end(h);
@@ -772,6 +787,17 @@ void blocked_to_packed(const uint8_t *blocked, size_t n, int bits, int dim, uint
 extern "C" {
 
 const char *tv_version(void) { return "turbovec_b200 0.1 (sm_100a)"; }
+
+int tv_exchange_layout_conflicts(size_t dim, int *store_plain, int *gather_plain, int *store_layout, int *gather_layout) {
+    if (!store_plain || !gather_plain || !store_layout || !gather_layout) return TV_ERR_INVALID_ARGUMENT;
+    if (dim == 0 || dim % 32 != 0 || dim > size_t(kMaxDim)) return TV_ERR_UNSUPPORTED;
+    const RotationTables rot = build_rotation_tables(int(dim));
+    ExchangeLayoutHost ex;
+    if (!build_exchange_layout(int(dim), rot.packed[1].data(), ex)) return TV_ERR_UNSUPPORTED;
+    exchange_layout_conflicts(int(dim), rot.packed[1].data(), nullptr, store_plain, gather_plain);
+    exchange_layout_conflicts(int(dim), rot.packed[1].data(), &ex, store_layout, gather_layout);
+    return TV_OK;
+}
 
 int tv_quantise_grid_lookup(const float *boundaries, int count, const float *values, size_t n, uint8_t *codes_out) {
     if (!boundaries || (n && (!values || !codes_out))) return TV_ERR_INVALID_ARGUMENT;

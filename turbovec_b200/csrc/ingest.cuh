@@ -31,6 +31,8 @@ struct IngestParams {
                                    // (input of the TQ+ fit, encode.rs:470-480)
     unsigned long long *first_invalid;  // min flat index of a coordinate failing |x| < 1e16 (init ~0ull)
     int exact_sums;                // pipelined kernel only: 1 = always walk the reference's sequential f64 chains (testing)
+    const uint8_t *store_bank;     // pipelined kernel only: exchange layout (ExchangeLayoutHost), or nullptr = linear rows
+    const uint16_t *perm1_exchange;
 };
 
 size_t ingest_smem_bytes(int vectors_per_pass, int dim, int ngroups);
@@ -55,6 +57,17 @@ struct QuantGrid {                       // device view, passed to the kernel by
 // caller then keeps to launch_ingest.
 bool build_quant_grid(const float *boundaries, int count, QuantGridHost &out);
 uint32_t quant_grid_code(const QuantGridHost &grid, float x);   // host evaluation, the kernel's lookup
+// Conflict-free layout of the row through which the two rotation rounds of the pipelined kernel exchange
+// data (built once per dimension, see ingest_fast.cu): byte offset within its 128-byte row of every stored
+// register [k*32 + lane], and the round-2 table with source positions in that layout (same packing as perm1).
+struct ExchangeLayoutHost {
+    int T = 0;
+    std::vector<uint8_t> store_bank;
+    std::vector<uint16_t> perm1_exchange;
+};
+bool build_exchange_layout(int dim, const uint16_t *perm1_packed, ExchangeLayoutHost &out);
+void exchange_layout_conflicts(int dim, const uint16_t *perm1_packed, const ExchangeLayoutHost *layout_or_null, int *store_max,
+                               int *gather_max);
 bool ingest_fast_supported(int dim, int bits, int ngroups, bool calibrated, const void *x, size_t smem_limit);
 // `error` receives a non-zero code if a bounded wait inside the kernel gives up.
 cudaError_t launch_ingest_fast(const IngestParams &p, const QuantGrid &grid, int sm_count, size_t smem_limit, uint32_t *error,

@@ -262,8 +262,22 @@ __global__ void __launch_bounds__((V + 4) * 32, 1) ingest_fast_kernel(IngestPara
 #pragma unroll
         for (int k = 0; k < T; ++k) {
             const int dst = (k / R) * (32 * R) + lane * R + (k % R);       // coordinate this register gathers (see wht_blocks)
-            const uint32_t e0 = p.perm0[dst], e1 = p.perm1[dst];
+            const uint32_t e0 = p.perm0[dst], e1 = (p.perm1_exchange ? p.perm1_exchange : p.perm1)[dst];
             pk[k] = ((e0 & 0x7fffu) << 2) | (e0 & 0x8000u) | ((((e1 & 0x7fffu) << 2) | (e1 & 0x8000u)) << 16);
+        }
+        // byte offset of each register's place within its row of the exchange layout, four per word
+        // (lane * 4 for plain rows); not kept for the largest vectors, which have no registers to spare
+        constexpr bool kExchange = T <= 48;
+        uint32_t sbank[kExchange ? T / 4 : 1];
+        if constexpr (kExchange) {
+#pragma unroll
+            for (int j = 0; j < T / 4; ++j) {
+                uint32_t wd = 0;
+#pragma unroll
+                for (int i = 0; i < 4; ++i)
+                    wd |= (p.store_bank ? uint32_t(p.store_bank[(4 * j + i) * 32 + lane]) : uint32_t(lane * 4)) << (8 * i);
+                sbank[j] = wd;
+            }
         }
         const float isb = p.inv_sqrt_block;
         const float ga = grid.a, gb = grid.b;
@@ -306,7 +320,11 @@ __global__ void __launch_bounds__((V + 4) * 32, 1) ingest_fast_kernel(IngestPara
                     }
                     wht_blocks<R, NBLK>(v, lane);
 #pragma unroll
-                    for (int k = 0; k < T; ++k) sts_f32(rl + row_of<R>(k) * 128, __fmul_rn(v[k], isb));
+                    for (int k = 0; k < T; ++k) {
+                        uint32_t at = rl;
+                        if constexpr (kExchange) at = rb + __byte_perm(sbank[k >> 2], 0, 0x4440 + (k & 3));
+                        sts_f32(at + row_of<R>(k) * 128, __fmul_rn(v[k], isb));
+                    }
                     __syncwarp();
                     // round 2
 #pragma unroll
@@ -521,6 +539,113 @@ bool build_quant_grid(const float *boundaries, int count, QuantGridHost &out) {
         if (i < count && cell_of[i] == c) { ++i; ++below; }
     }
     return true;
+}
+
+// Edge colouring of a bipartite multigraph in which every vertex has degree `colours`: colour[e] in
+// [0, colours) such that no two edges at a vertex share a colour (Koenig).  Alternating-path algorithm.
+static void colour_edges(int n_left, int n_right, int colours, const std::vector<int> &left, const std::vector<int> &right,
+                         std::vector<int> &colour) {
+    const int m = int(left.size());
+    colour.assign(m, -1);
+    std::vector<int> at_l(size_t(n_left) * colours, -1), at_r(size_t(n_right) * colours, -1);   // edge with colour c at a vertex
+    for (int e = 0; e < m; ++e) {
+        const int u = left[e], v = right[e];
+        int a = 0, b = 0;
+        while (at_l[size_t(u) * colours + a] >= 0) ++a;      // free at u
+        while (at_r[size_t(v) * colours + b] >= 0) ++b;      // free at v
+        if (a != b) {
+            // colour a is taken at v: walk the a/b alternating path that starts at v and swap its colours;
+            // it cannot come back to u, where a is free
+            std::vector<int> path;
+            int x = v, want = a;
+            bool on_right = true;
+            for (;;) {
+                const int f = on_right ? at_r[size_t(x) * colours + want] : at_l[size_t(x) * colours + want];
+                if (f < 0) break;
+                path.push_back(f);
+                x = on_right ? left[f] : right[f];
+                on_right = !on_right;
+                want = want == a ? b : a;
+            }
+            for (int f : path) {
+                const int c = colour[f];
+                at_l[size_t(left[f]) * colours + c] = -1;
+                at_r[size_t(right[f]) * colours + c] = -1;
+            }
+            for (int f : path) {
+                const int c = colour[f] == a ? b : a;
+                colour[f] = c;
+                at_l[size_t(left[f]) * colours + c] = f;
+                at_r[size_t(right[f]) * colours + c] = f;
+            }
+        }
+        colour[e] = a;
+        at_l[size_t(u) * colours + a] = e;
+        at_r[size_t(v) * colours + a] = e;
+    }
+}
+
+static int wht_row_rt(int R, int r) {
+    int rho = 0;
+    while ((1 << rho) < R) ++rho;
+    int bit_of[8] = {0, 1, 2, 3, 4, 5, 6, 7};
+    for (int i = 0; i < 5; ++i) bit_of[i % rho] = rho + i;
+    int row = 0;
+    for (int j = 0; j < rho; ++j) row |= ((r >> j) & 1) << (bit_of[j] - 5);
+    return row;
+}
+
+// Layout of the row through which the two rotation rounds exchange data.  Store instruction k of the warp
+// writes the 32 coordinates row_of(k)*32 + lane, gather instruction k' of round 2 reads the 32 coordinates
+// perm1[dst(k', lane)]; each coordinate is an edge between its store and its gather instruction, and a
+// 32-colouring of the edges gives every coordinate a bank such that neither kind of instruction has two lanes
+// on one bank.  Coordinate e then lives in word (e / 32) * 32 + bank(e): still in the 128-byte row of its
+// store instruction, at another place.
+bool build_exchange_layout(int dim, const uint16_t *perm1_packed, ExchangeLayoutHost &out) {
+    const int block = dim & -dim;
+    const int R = block / 32, T = dim / 32;
+    if (R < 2 || dim % 32 != 0 || dim > 8192) return false;
+    std::vector<int> store_of(dim), gather_of(dim, -1), lane_of_store(dim), row_of_store(dim);
+    for (int k = 0; k < T; ++k)
+        for (int l = 0; l < 32; ++l) {
+            const int e = ((k / R) * R + wht_row_rt(R, k % R)) * 32 + l;
+            store_of[e] = k;
+            lane_of_store[e] = l;
+            row_of_store[e] = e / 32;
+            const int dst = (k / R) * (32 * R) + l * R + (k % R);
+            const int src = perm1_packed[dst] & 0x7fff;
+            if (src >= dim || gather_of[src] >= 0) return false;
+            gather_of[src] = k;
+        }
+    std::vector<int> colour;
+    colour_edges(T, T, 32, store_of, gather_of, colour);
+    out.T = T;
+    out.store_bank.assign(dim, 0);
+    out.perm1_exchange.assign(dim, 0);
+    for (int e = 0; e < dim; ++e) out.store_bank[store_of[e] * 32 + lane_of_store[e]] = uint8_t(colour[e] * 4);   // byte offset in the row
+    for (int dst = 0; dst < dim; ++dst) {
+        const int src = perm1_packed[dst] & 0x7fff;
+        out.perm1_exchange[dst] = uint16_t((row_of_store[src] * 32 + colour[src]) | (perm1_packed[dst] & 0x8000));
+    }
+    return true;
+}
+
+// Worst number of lanes of one instruction on one bank: (stores, gathers) of the layout, and of the
+// linear layout for comparison.  1 = conflict-free.
+void exchange_layout_conflicts(int dim, const uint16_t *perm1_packed, const ExchangeLayoutHost *layout, int *store_max, int *gather_max) {
+    const int block = dim & -dim, R = block / 32, T = dim / 32;
+    *store_max = *gather_max = 0;
+    for (int k = 0; k < T; ++k) {
+        int sb[32] = {0}, gb[32] = {0};
+        for (int l = 0; l < 32; ++l) {
+            const int dst = (k / R) * (32 * R) + l * R + (k % R);
+            int s_bank, g_bank;
+            if (layout) { s_bank = layout->store_bank[k * 32 + l] / 4; g_bank = (layout->perm1_exchange[dst] & 0x7fff) % 32; }
+            else { s_bank = l; g_bank = (perm1_packed[dst] & 0x7fff) % 32; }
+            *store_max = std::max(*store_max, ++sb[s_bank]);
+            *gather_max = std::max(*gather_max, ++gb[g_bank]);
+        }
+    }
 }
 
 // Host evaluation of a grid, the same lookup the kernel performs.
