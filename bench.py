@@ -298,7 +298,7 @@ def run_ours(args):
                 return idx.search_device(qd.data_ptr(), nqq, K, d_scores.data_ptr(), d_slots.data_ptr(), words.data_ptr())
             dtf, scanf_ms, _, _ = timed(lambda: step_f(q_dev, nq), f_steps, 1)
             dtf1, scanf1_ms, _, _ = timed(lambda: step_f(q1_dev, 1), 10, 2)
-            live_bytes = live_blocks * 32 * (DIM * BITS // 8 + 4)
+            live_bytes = live_blocks * 32 * (DIM // (4 if BITS == 2 else 2) + 4)
             filtered.append({"selectivity": sel, "layout": kind, "n_allowed": int(allowed.sum()),
                              "live_block_fraction": live_blocks / nb_total,
                              "batch": {"size": nq, "value": nq * f_steps / dtf, "unit": UNIT},
@@ -323,7 +323,7 @@ def run_ours(args):
             dist.destroy_process_group()
         return
 
-    ng = DIM * BITS // 8
+    ng = DIM // (4 if BITS == 2 else 2)          # byte groups per vector (3-bit codes sit in 4-bit fields)
     qps = nq * args.steps / dt
     # dominant kernel of the headline step: the permute-dot scan, an exact int8 contraction
     ops_per_step = 2.0 * nq * n_local * DIM
@@ -336,8 +336,11 @@ def run_ours(args):
     ingest_bytes = 4 * DIM + ng + 4
 
     tc_min = idx.get_option(T.OPT_MMA_MIN_BATCH)
-    tc_min = 33 if tc_min < 0 else tc_min       # library default for the permute-dot family
-    main_kernel = "scan_tc_kernel (tcgen05)" if tc_min > 0 and nq >= tc_min else "scan_pd_kernel (mma.sync)"
+    permute_dot = BITS == 4 and ng % 4 == 0
+    tc_min = (33 if permute_dot else 8) if tc_min < 0 else tc_min       # library defaults
+    small_kernel = "scan_pd_kernel (mma.sync)" if permute_dot else "scan_lut_kernel (CUDA cores)"
+    tc_kernel = "scan_tc_kernel (tcgen05)" if permute_dot else "scan_tc_kernel (tcgen05, one-hot u8 LUT)"
+    main_kernel = tc_kernel if tc_min > 0 and nq >= tc_min and ng % 4 == 0 else small_kernel
     cpu_qps, cpu_ms, cores, sample, _ = cpu_arm(200_000, 1000, 2, 1, n_total) if world == 1 and not args.no_cpu else (None,) * 5
 
     line = {
@@ -346,7 +349,7 @@ def run_ours(args):
         "dtype": "int8", "data": "synthetic",
         "config": {"workload": f"{n_total} x {DIM} {BITS}-bit, k={K}, batch {nq}; index slot-sharded over {world} GPU(s)",
                    "l2": "inputs larger than L2: each step streams the whole code array of the shard",
-                   "score_mode": "permute-dot int8 (what an AVX-512-VNNI host runs)", "vectors_per_gpu": n_local},
+                   "score_mode": "permute-dot int8 (what an AVX-512-VNNI host runs)" if permute_dot else "u8 LUT (the reference's 2/3-bit and odd-geometry family)", "vectors_per_gpu": n_local},
         "e2e": {"value": nq * args.steps / dt_e2e, "unit": UNIT, "h2d_bytes_per_step": int(nq * DIM * 4),
                 "d2h_bytes_per_step": int(nq * K * 12)},
         "gpu_launches": int(launches),
@@ -363,12 +366,14 @@ def run_ours(args):
                    "roofline": {"bound": "hbm", "achieved": achieved_gbs, "peak": pk["hbm_gbs"], "unit": "GB/s",
                                 "frac": achieved_gbs / pk["hbm_gbs"] if achieved_gbs else None,
                                 "traffic": 1.004 * bytes_b1,   # ncu: 323.9 MB read for 322.5 MB algorithmic, scaled
-                                "kernel": "scan_pd_kernel (mma.sync)", "launches_per_step": scan1_launches / b1_steps}},
+                                "kernel": small_kernel, "launches_per_step": scan1_launches / b1_steps}},
         "ingest": {"value": ingest_rate, "unit": "vectors/s", "rows": ingest_rows,
                    "roofline": {"bound": "hbm", "achieved": ingest_rate * ingest_bytes / 1e9 if ingest_rate else None,
                                 "peak": pk["hbm_gbs"], "unit": "GB/s",
                                 "frac": ingest_rate * ingest_bytes / 1e9 / pk["hbm_gbs"] if ingest_rate else None,
-                                "traffic": None, "kernel": "ingest_fast_kernel (pipelined; whole 32-slot blocks)", "launches": ingest_launches}},
+                                "traffic": None, "launches": ingest_launches,
+                                "kernel": "ingest_fast_kernel (pipelined; whole 32-slot blocks)"
+                                if DIM in (128, 256, 384, 512, 768, 1024, 1536, 2048, 3072) else "ingest_kernel (block at a time)"}},
         "recall_at_10": recall,
     }
     if filtered:
@@ -388,11 +393,19 @@ def main():
     ap.add_argument("--impl", default="ours", choices=["ours", "reference"])
     ap.add_argument("--vectors", dest="n", type=int, default=10_000_000)
     ap.add_argument("--batch", type=int, default=1024)
+    ap.add_argument("--dim", type=int, default=1536, help="other shapes of the baseline (3072, 200, ...); the headline is 1536")
+    ap.add_argument("--bits", type=int, default=4, choices=[2, 3, 4])
     ap.add_argument("--skip-cpu", dest="no_cpu", action="store_true", help="skip the cpu_baseline leg")
     ap.add_argument("--skip-filtered", dest="no_filtered", action="store_true", help="skip the filtered-search legs")
     ap.add_argument("--tc-min-batch", type=int, default=None,
                     help="query batches of at least this size use the tcgen05 scan (library default if omitted; 0 = never)")
     args = ap.parse_args()
+    global DIM, BITS, METRIC
+    DIM, BITS = args.dim, args.bits
+    if (DIM, BITS) != (1536, 4) or args.n != 10_000_000 or args.batch != 1024:
+        METRIC = f"search_qps_k10_{args.n}x{DIM}_{BITS}bit_batch{args.batch}"
+        if (DIM, BITS) != (1536, 4):
+            args.no_cpu = True          # the restated CPU kernel covers the 4-bit permute-dot family only
     args.warmup = max(args.warmup, 3) if args.impl == "ours" else args.warmup
     if args.impl == "reference":
         run_reference(args)

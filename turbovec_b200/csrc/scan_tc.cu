@@ -25,15 +25,12 @@ namespace tv {
 namespace {
 
 constexpr int kMmaM = 128;                                    // vectors per accumulator tile (TMEM lanes)
-constexpr int kTileQueries = 256;                             // MMA N
+constexpr int kMaxTileQueries = 256;                          // largest MMA N (query columns of a work item)
 constexpr int kSlabK = 128;                                   // int8 elements (bytes) of K per stage
 constexpr int kATileBytes = kMmaM * kSlabK;                   // 16 KB per accumulator tile and stage
-constexpr int kBBytes = kTileQueries * kSlabK;                // 32 KB
-constexpr int kMaxStageBytes = 2 * kATileBytes + kBBytes;     // 64 KB (two accumulator tiles)
 constexpr int kExpandWarps = 8;
 constexpr int kEpilogueWarps = 8;                             // two per TMEM lane quarter, 128 columns each
 constexpr int kThreadsTc = (2 + kEpilogueWarps + kExpandWarps) * 32;   // 576
-constexpr uint32_t kTmemCols = 512;
 constexpr uint32_t kWaitLimitTc = 1u << 22;
 
 __device__ __forceinline__ uint32_t smem_u32(const void *p) { return uint32_t(__cvta_generic_to_shared(p)); }
@@ -91,11 +88,10 @@ __device__ __forceinline__ uint64_t umma_desc(uint32_t smem_byte_addr) {
     d |= uint64_t(2) << 61;                                    // SWIZZLE_128B
     return d;
 }
-// kind::i8: D = S32, A = B = signed 8-bit, both K-major, N = 256, M = 128.
-constexpr uint32_t kIdesc = (2u << 4) | (1u << 7) | (1u << 10) | (uint32_t(kTileQueries >> 3) << 17) |
-                            (uint32_t(kMmaM >> 4) << 24);
-
+// kind::i8: D = S32, A = B = signed 8-bit, both K-major, M = 128, N = NQT.
+template <int NQT>
 __device__ __forceinline__ void umma_i8(uint32_t d_tmem, uint64_t a_desc, uint64_t b_desc, uint32_t accumulate) {
+    constexpr uint32_t kIdesc = (2u << 4) | (1u << 7) | (1u << 10) | (uint32_t(NQT >> 3) << 17) | (uint32_t(kMmaM >> 4) << 24);
     asm volatile(
         "{\n\t.reg .pred p;\n\t"
         "setp.ne.b32 p, %4, 0;\n\t"
@@ -145,9 +141,9 @@ struct TcShared {
     uint32_t tmem_base;
     uint32_t pad[3];
     // per-query parameters of an item, double buffered; 16-byte aligned for float4 loads
-    float qscale[2][kTileQueries];
-    float qbias[2][kTileQueries];
-    float qthr[2][kTileQueries];   // score of the current k-th key (-inf while fewer than k results exist)
+    float qscale[2][kMaxTileQueries];
+    float qbias[2][kMaxTileQueries];
+    float qthr[2][kMaxTileQueries];   // score of the current k-th key (-inf while fewer than k results exist)
 };
 static_assert(offsetof(TcShared, qscale) % 16 == 0, "parameter arrays must be 16-byte aligned");
 
@@ -161,12 +157,17 @@ static_assert(offsetof(TcShared, qscale) % 16 == 0, "parameter arrays must be 16
 // two accumulator buffers (the epilogue of an item overlaps the MMAs of the next).  MT = 2: work item
 // 256 x 256, three stages, both 256-column halves of TMEM hold one item — half the B traffic per
 // multiply-add, at the price of the MMA pipe idling while the epilogue drains the accumulators.
-template <int MT, bool ONEHOT>
+// NQT = query columns of a work item (MMA N): 256, or 64 / 32 for small batches, where a full-width item
+// would spend three quarters or more of its tensor time on columns that hold no query.
+template <int MT, bool ONEHOT, int NQT>
 __global__ void __launch_bounds__(kThreadsTc, 1)
 scan_tc_kernel(ScanParams p, const __grid_constant__ CUtensorMap wmap, int n_slabs, int n_qgroups) {
     constexpr int kStages = MT == 1 ? 4 : 3;
     constexpr int kABytes = MT * kATileBytes;
+    constexpr int kBBytes = NQT * kSlabK;                     // 32 KB at 256 columns
     constexpr int kStageBytes = kABytes + kBBytes;
+    constexpr uint32_t kTmemCols = (MT == 1 ? 2 : 1) * MT * NQT < 32 ? 32 : (MT == 1 ? 2 : 1) * MT * NQT;   // 512 / 128 / 64: powers of two
+    constexpr int kTileQueries = NQT;
     constexpr int kBufs = MT == 1 ? 2 : 1;                    // accumulator buffers
     constexpr int kBlocksPerItem = 4 * MT;
     extern __shared__ __align__(1024) unsigned char smem_raw[];
@@ -240,7 +241,7 @@ scan_tc_kernel(ScanParams p, const __grid_constant__ CUtensorMap wmap, int n_sla
                         const uint64_t bd = umma_desc(b_addr + k * 32);
 #pragma unroll
                         for (int m = 0; m < MT; ++m)
-                            umma_i8(d_tmem + uint32_t(m) * kTileQueries, umma_desc(a_addr + m * kATileBytes + k * 32), bd, (s | k) != 0);
+                            umma_i8<NQT>(d_tmem + uint32_t(m) * kTileQueries, umma_desc(a_addr + m * kATileBytes + k * 32), bd, (s | k) != 0);
                     }
                     umma_commit(&sh->empty[st]);          // the stage may be refilled once these MMAs have read it
                 }
@@ -262,7 +263,7 @@ scan_tc_kernel(ScanParams p, const __grid_constant__ CUtensorMap wmap, int n_sla
             {
                 const int ql = qg * kTileQueries + et;
                 float qs = 0.f, qb = 0.f, th = INFINITY;
-                if (ql < p.q_base + p.nq) {
+                if (et < kTileQueries && ql < p.q_base + p.nq) {
                     qs = p.qscale[ql]; qb = p.qbias[ql];
                     const uint64_t key = p.cb.thr[ql];
                     th = key == kEmptyKey ? -INFINITY : desc_bits_to_score(uint32_t(key >> 32));
@@ -290,14 +291,17 @@ scan_tc_kernel(ScanParams p, const __grid_constant__ CUtensorMap wmap, int n_sla
             ok = mbar_wait(&sh->d_full[buf], (local_item / kBufs) & 1, p.cb.error);
             if (!ok) break;
             asm volatile("tcgen05.fence::after_thread_sync;" ::: "memory");
-            const int cbase = half * (kTileQueries / 2);
+            // the two warps of a lane quarter split the columns; below 64 columns the second one has none
+            constexpr int kColsPerHalf = kTileQueries >= 64 ? kTileQueries / 2 : kTileQueries;
+            const int cbase = half * kColsPerHalf;
+            const bool has_columns = cbase < kTileQueries;
             const float4 *ps = reinterpret_cast<const float4 *>(&sh->qscale[pb][cbase]);
             const float4 *pbias = reinterpret_cast<const float4 *>(&sh->qbias[pb][cbase]);
             const float4 *pt = reinterpret_cast<const float4 *>(&sh->qthr[pb][cbase]);
 #pragma unroll
             for (int m = 0; m < MT; ++m) {
                 const uint32_t taddr = tmem_base + (uint32_t(quarter * 32) << 16) + uint32_t(buf * MT + m) * kTileQueries + uint32_t(cbase);
-                for (int c0 = 0; c0 < kTileQueries / 2; c0 += 32) {
+                for (int c0 = 0; c0 < (has_columns ? kColsPerHalf : 0); c0 += 32) {
                     uint32_t acc[32];
                     tmem_ld32(taddr + c0, acc);
                     asm volatile("tcgen05.wait::ld.sync.aligned;" ::: "memory");
@@ -501,7 +505,7 @@ EncodeTiledFn encode_fn() {
 
 }  // namespace
 
-size_t scan_tc_smem_bytes() { return size_t(4) * (kATileBytes + kBBytes) + sizeof(TcShared) + 1024; }   // = 3 * 64 KB too
+static size_t scan_tc_smem_bytes(int nqt) { return size_t(4) * (kATileBytes + nqt * kSlabK) + sizeof(TcShared) + 1024; }   // MT = 2: 3 x 64 KB, the same
 
 bool scan_tc_supported(int bits, int mode, int ngroups) {
     if (encode_fn() == nullptr) return false;
@@ -518,36 +522,52 @@ cudaError_t launch_scan_tc(const ScanParams &p, const int8_t *weights, int rows,
     if (p.nq <= 0 || p.pos_end <= p.pos_begin) return cudaSuccess;
     EncodeTiledFn enc = encode_fn();
     if (!enc) return cudaErrorNotSupported;
+    const bool onehot = p.mode != kModePermuteDot;
+    const int nq_all = p.q_base + p.nq;
+    // query columns per work item: the tensor time of an item grows with them whether they hold queries or not
+    const int nqt = nq_all <= 32 && onehot ? 32 : (nq_all <= 64 ? 64 : kMaxTileQueries);
     CUtensorMap map;
     const cuuint64_t dims[2] = {cuuint64_t(pitch), cuuint64_t(rows)};
     const cuuint64_t strides[1] = {cuuint64_t(pitch)};
-    const cuuint32_t box[2] = {cuuint32_t(kSlabK), cuuint32_t(kTileQueries)};
+    const cuuint32_t box[2] = {cuuint32_t(kSlabK), cuuint32_t(nqt)};
     const cuuint32_t estr[2] = {1, 1};
     if (enc(&map, CU_TENSOR_MAP_DATA_TYPE_UINT8, 2, const_cast<int8_t *>(weights), dims, strides, box, estr,
             CU_TENSOR_MAP_INTERLEAVE_NONE, CU_TENSOR_MAP_SWIZZLE_128B, CU_TENSOR_MAP_L2_PROMOTION_L2_256B,
             CU_TENSOR_MAP_FLOAT_OOB_FILL_NONE) != CUDA_SUCCESS)
         return cudaErrorInvalidValue;
     const int n_slabs = pitch / kSlabK;
-    const int n_qgroups = (p.q_base + p.nq + kTileQueries - 1) / kTileQueries;
-    const size_t smem = scan_tc_smem_bytes();
+    const int n_qgroups = (nq_all + nqt - 1) / nqt;
+    const size_t smem = scan_tc_smem_bytes(nqt);
     static bool attr_set = false;
     if (!attr_set) {
-        cudaError_t e = cudaFuncSetAttribute(scan_tc_kernel<1, false>, cudaFuncAttributeMaxDynamicSharedMemorySize, int(smem));
-        if (e == cudaSuccess) e = cudaFuncSetAttribute(scan_tc_kernel<2, false>, cudaFuncAttributeMaxDynamicSharedMemorySize, int(smem));
-        if (e == cudaSuccess) e = cudaFuncSetAttribute(scan_tc_kernel<1, true>, cudaFuncAttributeMaxDynamicSharedMemorySize, int(smem));
+        const int big = int(scan_tc_smem_bytes(kMaxTileQueries));
+        cudaError_t e = cudaFuncSetAttribute(scan_tc_kernel<1, false, 256>, cudaFuncAttributeMaxDynamicSharedMemorySize, big);
+        if (e == cudaSuccess) e = cudaFuncSetAttribute(scan_tc_kernel<2, false, 256>, cudaFuncAttributeMaxDynamicSharedMemorySize, big);
+        if (e == cudaSuccess) e = cudaFuncSetAttribute(scan_tc_kernel<1, true, 256>, cudaFuncAttributeMaxDynamicSharedMemorySize, big);
+        if (e == cudaSuccess) e = cudaFuncSetAttribute(scan_tc_kernel<1, false, 64>, cudaFuncAttributeMaxDynamicSharedMemorySize, big);
+        if (e == cudaSuccess) e = cudaFuncSetAttribute(scan_tc_kernel<1, true, 64>, cudaFuncAttributeMaxDynamicSharedMemorySize, big);
+        if (e == cudaSuccess) e = cudaFuncSetAttribute(scan_tc_kernel<1, true, 32>, cudaFuncAttributeMaxDynamicSharedMemorySize, big);
         if (e != cudaSuccess) return e;
         attr_set = true;
     }
-    const int mt = (tiles_per_item == 2 && p.mode == kModePermuteDot) ? 2 : 1;
+    const int mt = (tiles_per_item == 2 && !onehot && nqt == kMaxTileQueries) ? 2 : 1;
     const uint32_t vtiles = (p.pos_end - p.pos_begin + 4 * mt - 1) / (4 * mt);
     const uint64_t items = uint64_t(vtiles) * n_qgroups;
     // a multiple of the query-group count keeps the CTAs that share a vector tile in step (codes hit L2)
     unsigned grid = unsigned(sm_count - sm_count % n_qgroups);
     if (grid == 0) grid = unsigned(sm_count);
     if (items < grid) grid = unsigned(items);
-    if (p.mode != kModePermuteDot) scan_tc_kernel<1, true><<<grid, kThreadsTc, smem, s>>>(p, map, n_slabs, n_qgroups);
-    else if (mt == 2) scan_tc_kernel<2, false><<<grid, kThreadsTc, smem, s>>>(p, map, n_slabs, n_qgroups);
-    else scan_tc_kernel<1, false><<<grid, kThreadsTc, smem, s>>>(p, map, n_slabs, n_qgroups);
+    if (onehot) {
+        if (nqt == 32) scan_tc_kernel<1, true, 32><<<grid, kThreadsTc, smem, s>>>(p, map, n_slabs, n_qgroups);
+        else if (nqt == 64) scan_tc_kernel<1, true, 64><<<grid, kThreadsTc, smem, s>>>(p, map, n_slabs, n_qgroups);
+        else scan_tc_kernel<1, true, 256><<<grid, kThreadsTc, smem, s>>>(p, map, n_slabs, n_qgroups);
+    } else if (mt == 2) {
+        scan_tc_kernel<2, false, 256><<<grid, kThreadsTc, smem, s>>>(p, map, n_slabs, n_qgroups);
+    } else if (nqt == 64) {
+        scan_tc_kernel<1, false, 64><<<grid, kThreadsTc, smem, s>>>(p, map, n_slabs, n_qgroups);
+    } else {
+        scan_tc_kernel<1, false, 256><<<grid, kThreadsTc, smem, s>>>(p, map, n_slabs, n_qgroups);
+    }
     return cudaGetLastError();
 }
 
