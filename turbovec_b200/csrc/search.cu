@@ -6,6 +6,8 @@
 //   (score desc, slot asc) (:236-252, :4285-4298).
 // Integer sums are exact here as they are in every reference kernel; the float epilogue reproduces the
 // reference's rounding sequence for the selected score mode.
+#include <algorithm>
+
 #include "search.cuh"
 
 #include <cfloat>
@@ -432,8 +434,8 @@ __global__ void __launch_bounds__((kConsumerWarps + 1) * 32, MT == 1 ? 3 : (MT =
 // isum = sum_g U[g][byte>>4] + U[g][16 + (byte&15)] exactly; float epilogue per mode:
 //   kModeLutMulAdd: (f32)isum * scale + bias                      (search.rs:1176)
 //   kModeLutFlush : acc = bias; per 256 groups acc = fma(scale, (f32)isum_batch, acc)   (search.rs:1596)
-// One warp per code block, lane = vector; the tables of up to kLutQueriesPerLaunch queries sit in shared
-// memory (a 16-byte sub-table spans four banks, so a warp's lookups never conflict).
+// One warp per code block; the tables of up to kLutQueriesPerLaunch queries sit in shared memory (the four
+// group rows a warp instruction touches are 32 consecutive words, so its lookups never conflict).
 // =====================================================================================================
 template <int NQ>
 __global__ void __launch_bounds__(256) scan_lut_kernel(ScanParams p) {
@@ -459,10 +461,16 @@ __global__ void __launch_bounds__(256) scan_lut_kernel(ScanParams p) {
         qs[q] = p.qscale[ql]; qb[q] = p.qbias[ql]; thr[q] = p.cb.thr[ql];
     }
     const int warps = blockDim.x >> 5;
+    // A warp instruction reads 128 contiguous bytes = four group rows of the block: lane = (row r = lane / 8,
+    // vectors 4 * (lane % 8) .. + 3).  Each lane sums its quarter of the groups for its four vectors; the
+    // integer partial sums of the four lanes that share a vector quad are added by two shuffles (integer
+    // addition: the order does not matter), then lane (quad, r) finishes vector 4 * quad + r.
+    const int row = lane >> 3, quad = lane & 7;
+    const int my_vec = 4 * quad + row;
     for (uint32_t pos = pos_begin + blockIdx.x * warps + warp; pos < pos_end; pos += gridDim.x * warps) {
         const uint32_t blk = p.live_blocks ? p.live_blocks[pos] : pos;
-        const uint8_t *codes = p.codes + size_t(blk) * ng * kLanes + lane;
-        const int64_t slot = int64_t(blk) * kLanes + lane;
+        const uint32_t *codes32 = reinterpret_cast<const uint32_t *>(p.codes + size_t(blk) * ng * kLanes) + lane;
+        const int64_t slot = int64_t(blk) * kLanes + my_vec;
         float facc[NQ];
 #pragma unroll
         for (int q = 0; q < NQ; ++q) facc[q] = qb[q];
@@ -471,21 +479,35 @@ __global__ void __launch_bounds__(256) scan_lut_kernel(ScanParams p) {
         for (int q = 0; q < NQ; ++q) total[q] = 0;
         for (int g0 = 0; g0 < ng; g0 += 256) {
             const int g1 = min(g0 + 256, ng);
-            uint32_t isum[NQ];
+            uint32_t isum[NQ][4];
 #pragma unroll
-            for (int q = 0; q < NQ; ++q) isum[q] = 0;
+            for (int q = 0; q < NQ; ++q)
+#pragma unroll
+                for (int j = 0; j < 4; ++j) isum[q][j] = 0;
 #pragma unroll 4
-            for (int g = g0; g < g1; ++g) {
-                const uint32_t byte = codes[size_t(g) * kLanes];
+            for (int g = g0 + row; g < g1; g += 4) {
+                const uint32_t word = codes32[size_t(g - row) * 8];      // bytes of vectors 4*quad .. +3 in group g
                 const int o = g * 32;
 #pragma unroll
-                for (int q = 0; q < NQ; ++q)
-                    isum[q] += uint32_t(lut[q * ng * 32 + o + (byte >> 4)]) + uint32_t(lut[q * ng * 32 + o + 16 + (byte & 15)]);
+                for (int j = 0; j < 4; ++j) {
+                    const uint32_t byte = (word >> (8 * j)) & 255u;
+#pragma unroll
+                    for (int q = 0; q < NQ; ++q)
+                        isum[q][j] += uint32_t(lut[q * ng * 32 + o + (byte >> 4)]) + uint32_t(lut[q * ng * 32 + o + 16 + (byte & 15)]);
+                }
             }
 #pragma unroll
             for (int q = 0; q < NQ; ++q) {
-                facc[q] = fmaf(qs[q], float(int(isum[q])), facc[q]);
-                total[q] += isum[q];
+                uint32_t mine = 0;
+#pragma unroll
+                for (int j = 0; j < 4; ++j) {
+                    uint32_t v = isum[q][j];
+                    v += __shfl_xor_sync(kFullMask, v, 8);
+                    v += __shfl_xor_sync(kFullMask, v, 16);
+                    if (j == row) mine = v;
+                }
+                facc[q] = fmaf(qs[q], float(int(mine)), facc[q]);
+                total[q] += mine;
             }
         }
         if (slot < p.n) {
@@ -766,7 +788,9 @@ cudaError_t launch_scan_lut(const ScanParams &p, int sm_count, cudaStream_t s) {
     const int width = nqh == 1 ? 1 : (nqh == 2 ? 2 : 4);
     const size_t smem = size_t(width) * p.ngroups * 32;
     const uint32_t blocks = p.pos_end - p.pos_begin;
-    const unsigned grid = unsigned(min(uint32_t(sm_count) * 2u, (blocks + 7) / 8));
+    // resident CTAs per SM: as many as the tables leave room for (the scan hides its lookup latency with warps)
+    const uint32_t per_sm = uint32_t(std::max<size_t>(2, std::min<size_t>(6, (size_t(200) << 10) / (smem + 1024))));
+    const unsigned grid = unsigned(min(uint32_t(sm_count) * per_sm, (blocks + 7) / 8));
 #define TV_LAUNCH_LUT(N)                                                                                             \
     {                                                                                                                \
         cudaError_t e = cudaFuncSetAttribute(scan_lut_kernel<N>, cudaFuncAttributeMaxDynamicSharedMemorySize, int(smem)); \
