@@ -547,15 +547,18 @@ __global__ void __launch_bounds__(256) select_kernel(CandidateBuffers cb, int so
     const uint32_t raw = dense_count > 0 ? uint32_t(dense_count) : cb.cnt[q];
     const int ncand = int(min(raw, uint32_t(cb.cap)));
     if (tid == 0 && raw > uint32_t(cb.cap)) atomicExch(cb.overflow, 1u);
-    const int total = cb.k + ncand;
-    // smallest power of two holding k + ncand entries
+    // a dense first chunk has no earlier results to merge with: leaving them out keeps 4096 candidates in a
+    // 4096-entry network instead of an 8192-entry one
+    const int nprev = dense_count > 0 ? 0 : cb.k;
+    const int total = nprev + ncand;
+    // smallest power of two holding the entries
     int n2 = 32;
     while (n2 < total) n2 <<= 1;
     if (n2 > sort_n) n2 = sort_n;
     for (int i = tid; i < n2; i += blockDim.x) {
         uint64_t v = kEmptyKey;
-        if (i < cb.k) v = cb.topk[size_t(q) * cb.k + i];
-        else if (i < total) v = cb.cand[size_t(q) * cb.cap + (i - cb.k)];
+        if (i < nprev) v = cb.topk[size_t(q) * cb.k + i];
+        else if (i < total) v = cb.cand[size_t(q) * cb.cap + (i - nprev)];
         keys[i] = v;
     }
     __syncthreads();
