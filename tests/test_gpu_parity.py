@@ -533,3 +533,25 @@ def test_keyed_shard_search_and_device_merge_equal_the_whole_index(T, nq, k):
     assert np.array_equal(s.cpu().numpy()[:, :ke], want_s)
     if ke < k:                                      # places past the number of vectors: (-inf, 0) padding
         assert np.all(np.isneginf(s.cpu().numpy()[:, ke:])) and np.all(i.cpu().numpy()[:, ke:] == 0)
+
+
+def test_large_allowlist_resolved_by_host_threads(T):
+    """Allowlists of 65,536 ids and more are resolved by several host threads; the result and the unknown id
+    that is reported (the first one in list order) are those of a sequential walk."""
+    n, dim = 140_000, 64
+    rng = np.random.default_rng(3)
+    x = anisotropic(n, dim, seed=31)
+    ids = (rng.permutation(n).astype(np.uint64) + np.uint64(10 ** 9))
+    idx = T.IdMapIndex(dim, 4)
+    idx.add_with_ids(x, ids)
+    q = anisotropic(4, dim, seed=31, offset=77)
+    allow = ids[rng.permutation(n)[:100_000]].copy()
+    s, got = idx.search(q, 10, allowlist=allow)
+    mask = np.isin(ids, allow)
+    rs, ri = _oracle_search(x, q, 4, 10, mask=mask)
+    assert np.array_equal(got, ids[ri]) and np.array_equal(s, rs)
+    bad = allow.copy()
+    bad[70_000] = np.uint64(5)
+    bad[90_001] = np.uint64(6)
+    with pytest.raises(KeyError, match="5"):
+        idx.search(q, 10, allowlist=bad)

@@ -9,6 +9,7 @@
 #include <cstring>
 #include <mutex>
 #include <string>
+#include <thread>
 #include <unordered_map>
 #include <unordered_set>
 #include <vector>
@@ -1057,14 +1058,30 @@ int tv_search_allowlist(tv_index *h, const float *queries, size_t nq, size_t dim
     std::vector<uint32_t> slots;
     if (allow_ids) {                                                    // id_map.rs:670-683
         if (n_allow == 0) return fail(h, TV_ERR_ALLOWLIST_EMPTY, "allowlist is empty");
-        slots.reserve(n_allow);
-        for (size_t i = 0; i < n_allow; ++i) {
-            auto it = h->id_to_slot.find(allow_ids[i]);
-            if (it == h->id_to_slot.end()) {
-                h->err_id = allow_ids[i];
-                return fail(h, TV_ERR_UNKNOWN_ID, "allowlist id " + std::to_string(allow_ids[i]) + " is not in the index");
+        // one hash lookup per id (id_map.rs:670-683); large lists are split over host threads (lookups only read
+        // the table) and the first unknown id in list order is the one reported, as in a sequential walk
+        slots.resize(n_allow);
+        const size_t n_threads = n_allow < (size_t(1) << 16) ? 1 : std::min<size_t>(16, std::max(1u, std::thread::hardware_concurrency()));
+        std::vector<size_t> first_unknown(n_threads, n_allow);
+        auto resolve = [&](size_t t) {
+            const size_t lo = n_allow * t / n_threads, hi = n_allow * (t + 1) / n_threads;
+            for (size_t i = lo; i < hi; ++i) {
+                auto it = h->id_to_slot.find(allow_ids[i]);
+                if (it == h->id_to_slot.end()) { first_unknown[t] = i; return; }
+                slots[i] = it->second;
             }
-            slots.push_back(it->second);
+        };
+        if (n_threads == 1) {
+            resolve(0);
+        } else {
+            std::vector<std::thread> pool;
+            for (size_t t = 0; t < n_threads; ++t) pool.emplace_back(resolve, t);
+            for (auto &th : pool) th.join();
+        }
+        const size_t bad = *std::min_element(first_unknown.begin(), first_unknown.end());
+        if (bad < n_allow) {
+            h->err_id = allow_ids[bad];
+            return fail(h, TV_ERR_UNKNOWN_ID, "allowlist id " + std::to_string(allow_ids[bad]) + " is not in the index");
         }
         m.slots_host = slots.data(); m.n_slots = slots.size();
     }
