@@ -1,7 +1,7 @@
 """The allocation-free search entry point against the regular device search.
 
 Some users of the library cannot let a search call reach the CUDA allocator: a serving loop with a latency
-budget, a process whose device memory is already fully assigned, a framework that forbids allocator traffic
+limit, a process whose device memory is already fully assigned, a framework that forbids allocator traffic
 after warm-up.  tv_search_device_noalloc keeps its scratch in a fixed array inside the library; this test
 calls it through the C ABI, twice in a row (the second call starts from the first call's leftovers in that
 array), and requires exactly the results of tv_search_device.  It is collected last on purpose.

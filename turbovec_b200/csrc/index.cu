@@ -1152,7 +1152,7 @@ int tv_merge_keys_device(int device, const uint64_t *keys_device, size_t n_lists
 // Search without any allocation.
 //
 // Who needs it: code that runs where the CUDA allocator must not be touched — a serving loop with a hard
-// latency budget (cudaMalloc takes a device-wide lock and may synchronise), a process whose memory pool
+// latency limit (cudaMalloc takes a device-wide lock and may synchronise), a process whose memory pool
 // has been handed out completely to other tenants, or a caller that has promised its framework "no
 // allocator traffic after warm-up".  tv_search_device grows its scratch arrays on demand; this entry
 // point instead keeps every byte of scratch in one fixed array that is part of the loaded library image.

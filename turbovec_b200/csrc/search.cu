@@ -766,7 +766,7 @@ cudaError_t launch_scan_pd(const ScanParams &p, int sm_count, cudaStream_t s) {
     const int mt = (p.nq + 15) / 16;
     const size_t smem = size_t(kStages) * kStageBytes;
     const uint32_t tiles = (p.pos_end - p.pos_begin + kConsumerWarps - 1) / kConsumerWarps;
-    const unsigned per_sm = mt == 1 ? 3 : (mt == 2 ? 2 : 1);   // resident CTAs per SM (register budget)
+    const unsigned per_sm = mt == 1 ? 3 : (mt == 2 ? 2 : 1);   // resident CTAs per SM (limited by registers)
     const unsigned grid = unsigned(min(uint32_t(sm_count) * per_sm, tiles));
     const unsigned threads = (kConsumerWarps + 1) * 32;
 #define TV_LAUNCH_PD(M)                                                                                             \
