@@ -318,6 +318,28 @@ def run_ours(args):
     got, want = ri.cpu().numpy(), truth_i.cpu().numpy()
     recall = float(np.mean([len(set(got[j]) & set(want[j])) / K for j in range(n_recall_q)]))
 
+    # online mutation on one GPU: adds of 10,000 device-resident rows and single-slot removals, wall clock
+    mutation = None
+    if world == 1 and not args.no_filtered:
+        rows_m = 10_000
+        xm = gen_rows_torch(torch, device, scale_t, 3, 0, rows_m)
+        torch.cuda.synchronize()
+        idx.add_device(xm.data_ptr(), rows_m, DIM)                      # warm-up (may grow the arrays)
+        t0 = time.perf_counter()
+        km = 0.0
+        for _ in range(20):
+            idx.add_device(xm.data_ptr(), rows_m, DIM)
+            km += idx.last_main_kernel()[0]
+        t_add = (time.perf_counter() - t0) / 20
+        rng_m = np.random.default_rng(11)
+        victims = [int(v) for v in rng_m.integers(0, len(idx) - 2000, 1000)]
+        t0 = time.perf_counter()
+        for v in victims:
+            idx.swap_remove(v)
+        t_rm = (time.perf_counter() - t0) / len(victims)
+        mutation = {"add_batch_rows": rows_m, "add_ms_per_batch": t_add * 1e3, "add_kernel_ms_per_batch": km / 20,
+                    "add_vectors_per_s": rows_m / t_add, "swap_remove_us": t_rm * 1e6}
+
     if rank != 0:
         if world > 1:
             dist.destroy_process_group()
@@ -378,6 +400,8 @@ def run_ours(args):
     }
     if filtered:
         line["filtered"] = filtered
+    if mutation:
+        line["mutation"] = mutation
     if cpu_qps is not None:
         line["cpu_baseline"] = {"value": cpu_qps, "unit": UNIT, "cores": cores, "kind": "port", "sample": sample}
     print(json.dumps(line))
