@@ -177,6 +177,8 @@ def run_ours(args):
     idx = T.TurboQuantIndex(DIM, BITS, device=local_rank)
     if args.tc_min_batch is not None:
         idx.set_option(T.OPT_MMA_MIN_BATCH, args.tc_min_batch)
+    if args.ingest_pipeline is not None:
+        idx.set_option(T.OPT_INGEST_PIPELINE, args.ingest_pipeline)
     n_recall_q = 64
     q_all = torch.from_numpy(gen_rows_numpy(1, max(nq, n_recall_q), 10_000_000)).to(device)
     truth_s = torch.full((n_recall_q, K), -float("inf"), device=device)
@@ -395,7 +397,8 @@ def run_ours(args):
                                 "frac": ingest_rate * ingest_bytes / 1e9 / pk["hbm_gbs"] if ingest_rate else None,
                                 "traffic": None, "launches": ingest_launches,
                                 "kernel": "ingest_fast_kernel (pipelined; whole 32-slot blocks)"
-                                if DIM in (128, 256, 384, 512, 768, 1024, 1536, 2048, 3072) else "ingest_kernel (block at a time)"}},
+                                if DIM in (128, 256, 384, 512, 768, 1024, 1536, 2048, 3072) and args.ingest_pipeline != 0
+                                else "ingest_kernel (block at a time)"}},
         "recall_at_10": recall,
     }
     if filtered:
@@ -419,6 +422,8 @@ def main():
     ap.add_argument("--batch", type=int, default=1024)
     ap.add_argument("--dim", type=int, default=1536, help="other shapes of the baseline (3072, 200, ...); the headline is 1536")
     ap.add_argument("--bits", type=int, default=4, choices=[2, 3, 4])
+    ap.add_argument("--ingest-pipeline", type=int, default=None, choices=[0, 1, 2],
+                    help="TV_OPT_INGEST_PIPELINE: 0 = block-at-a-time ingest kernel only (default: library default, 1)")
     ap.add_argument("--skip-cpu", dest="no_cpu", action="store_true", help="skip the cpu_baseline leg")
     ap.add_argument("--skip-filtered", dest="no_filtered", action="store_true", help="skip the filtered-search legs")
     ap.add_argument("--tc-min-batch", type=int, default=None,
