@@ -3,21 +3,24 @@
 // :560-652 / fused_quantize_scale_pack_scalar :1418-1476, blocked layout pack.rs:340-361), reorganised so
 // that the order-fixed sequential sums no longer stall the data-parallel work.
 //
-// One CTA of three warpgroups walks a contiguous range of code blocks in waves of 8 vectors and runs its
-// stages concurrently, one wave apart, with one CTA barrier per step:
+// One CTA walks a contiguous range of code blocks in waves of V vectors (V = 8: three warpgroups; V = 4: two,
+// for rows of which two sets of eight do not fit in shared memory) and runs its stages concurrently, one wave
+// apart, with one CTA barrier per step:
 //   norm warps     wave i     8 sequential f32 chains per vector straight from global memory (4 lanes per
 //                             vector, two chains per lane), fixed combine tree, sqrt, reciprocal.  Two warps
 //                             alternate (even and odd waves) and spread a wave over two steps: the loads come
 //                             from global memory and the chains need a dozen dependent round trips.
 //   staging warp   wave i     issues the bulk copies (cp.async.bulk + mbarrier transaction count) of the rows
-//   8 rotation     wave i-1   one warp per vector, the whole vector in registers: both rounds of permutation,
+//   V rotation     wave i-1   one warp per vector, the whole vector in registers: both rounds of permutation,
 //   warps                     sign flip and Walsh-Hadamard butterflies (rotation.cuh states the order rules),
 //                             Lloyd-Max quantisation through a grid table (QuantGrid), packing into the block
 //                             tile, reconstruction inner product and scale
 //   copy warp                 writes the finished tile of a block (ngroups x 32 bytes, word-swizzled so that the
 //                             byte stores of a warp never share a bank) to the code array
-// The two rotation warpgroups take the registers the third one gives up (setmaxnreg), so a 2048-coordinate
-// vector and its permutation entries stay in registers.
+// With V = 8 the two rotation warpgroups take the registers the third one gives up (setmaxnreg), so a
+// 2048-coordinate vector and its permutation entries stay in registers; with V = 4 every thread may use 255.
+// The row through which the two rounds exchange data uses a bank layout found by edge colouring
+// (build_exchange_layout), so that neither the round-1 stores nor the round-2 gathers conflict.
 //
 // Reconstruction inner product.  The reference sums rotated[j] * centroid[code[j]] in f64 along four
 // sequential chains (encode.rs:1418-1476) and uses the result rounded to f32, and a dependent f64 add takes
