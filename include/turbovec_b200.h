@@ -127,7 +127,9 @@ int tv_add_with_ids(tv_index *h, const float *vectors, size_t n, size_t dim, con
  * encode.rs:58-74 runs on the device.  Used when the producer already lives on the GPU. */
 int tv_add_device(tv_index *h, const float *vectors_device, size_t n, size_t dim);
 
-/* ---- removal: swap_remove (lib.rs:2864-3028), IdMapIndex::remove (id_map.rs:520-567) ---- */
+/* ---- removal: swap_remove (lib.rs:2864-3028), IdMapIndex::remove (id_map.rs:520-567) ----
+ * Both return once the move of the last row into the freed slot is enqueued on the handle's stream; every
+ * later call on the handle is ordered after it. */
 int tv_swap_remove(tv_index *h, size_t slot, size_t *moved_from);
 int tv_remove(tv_index *h, uint64_t id, int *removed);
 /* One stored row as its byte-groups in group order plus its scale: pack::read_code / write_code over a lane

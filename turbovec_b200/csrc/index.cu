@@ -952,7 +952,8 @@ int tv_swap_remove(tv_index *h, size_t slot, size_t *moved_from) {
     move_lane_kernel<<<(h->ngroups + 255) / 256, 256, 0, h->stream>>>(h->d_codes, h->d_scales, h->ngroups, int64_t(last), int64_t(slot));
     h->launches++;
     TV_CUDA(cudaGetLastError());
-    TV_CUDA(cudaStreamSynchronize(h->stream));
+    // no synchronisation: the result is known on the host, and every later call on this handle runs on the
+    // same stream, after the move
     h->n = last;
     if (moved_from) *moved_from = last;
     return TV_OK;
@@ -970,8 +971,7 @@ int tv_remove(tv_index *h, uint64_t id, int *removed) {
     move_lane_kernel<<<(h->ngroups + 255) / 256, 256, 0, h->stream>>>(h->d_codes, h->d_scales, h->ngroups, int64_t(last), int64_t(slot));
     h->launches++;
     TV_CUDA(cudaGetLastError());
-    TV_CUDA(cudaStreamSynchronize(h->stream));
-    h->n = last;
+    h->n = last;                                                       // enqueued, not awaited (see tv_swap_remove)
     h->id_to_slot.erase(it);
     if (slot != last) {                                                // id_map.rs:557-561
         const uint64_t moved = h->slot_to_id[last];
