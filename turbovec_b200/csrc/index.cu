@@ -131,6 +131,11 @@ struct tv_index {
 
     // scratch
     DeviceArray<float> d_stage;              // ingest staging / query upload
+    // host-memory adds: two pinned + two device staging buffers, a copy stream and per-buffer events
+    PinnedArray<float> h_add[2];
+    DeviceArray<float> d_add[2];
+    cudaStream_t copy_stream = nullptr;
+    cudaEvent_t ev_copied[2] = {nullptr, nullptr}, ev_consumed[2] = {nullptr, nullptr};
     DeviceArray<float> d_qrot, d_qscale, d_qbias;
     DeviceArray<uint8_t> d_luts;
     DeviceArray<int8_t> d_weights;
@@ -161,6 +166,11 @@ struct tv_index {
         if (ev0) cudaEventDestroy(ev0);
         if (ev1) cudaEventDestroy(ev1);
         for (cudaEvent_t e : ev_pool) cudaEventDestroy(e);
+        for (int b = 0; b < 2; ++b) {
+            if (ev_copied[b]) cudaEventDestroy(ev_copied[b]);
+            if (ev_consumed[b]) cudaEventDestroy(ev_consumed[b]);
+        }
+        if (copy_stream) cudaStreamDestroy(copy_stream);
         if (stream) cudaStreamDestroy(stream);
     }
 };
@@ -405,16 +415,57 @@ int add_rows(tv_index *h, const float *x, size_t n, size_t dim, bool on_device) 
     p.codes = h->d_codes; p.scales = h->d_scales;
     p.first_invalid = &h->d_flags->first_invalid;
 
-    // Host input goes through a device staging buffer in chunks of at most ~256 MB.
-    const size_t chunk_rows = on_device ? n : std::max<size_t>(1, std::min<size_t>(n, (size_t(256) << 20) / (dim * 4)));
-    if (!on_device) TV_CUDA(h->d_stage.reserve(chunk_rows * dim));
+    // Device input is encoded in place.  Host input goes through pinned staging in chunks of about 64 MB,
+    // double buffered: host threads copy chunk i+1 into pinned memory while chunk i crosses the bus on the copy
+    // stream and chunk i-1 is encoded on the handle's stream.
+    const size_t chunk_rows = on_device ? n : std::max<size_t>(1, std::min<size_t>(n, (size_t(64) << 20) / (dim * 4)));
+    if (!on_device) {
+        if (!h->copy_stream) {
+            TV_CUDA(cudaStreamCreateWithFlags(&h->copy_stream, cudaStreamNonBlocking));
+            for (int b = 0; b < 2; ++b) {
+                TV_CUDA(cudaEventCreateWithFlags(&h->ev_copied[b], cudaEventDisableTiming));
+                TV_CUDA(cudaEventCreateWithFlags(&h->ev_consumed[b], cudaEventDisableTiming));
+            }
+        }
+        for (int b = 0; b < 2; ++b) {
+            TV_CUDA(h->h_add[b].reserve(chunk_rows * dim));
+            TV_CUDA(h->d_add[b].reserve(chunk_rows * dim));
+        }
+    }
+    const size_t copy_threads = std::min<size_t>(16, std::max(1u, std::thread::hardware_concurrency()));
+    // page-locked input (cudaHostAlloc / cudaHostRegister) is read by the copy engine directly
+    bool src_pinned = false;
+    if (!on_device) {
+        cudaPointerAttributes attr{};
+        if (cudaPointerGetAttributes(&attr, x) == cudaSuccess) src_pinned = attr.type == cudaMemoryTypeHost;
+        else cudaGetLastError();
+    }
     TV_CUDA(cudaEventRecord(h->ev0, h->stream));
-    for (size_t done = 0; done < n; done += chunk_rows) {
+    size_t chunk_index = 0;
+    for (size_t done = 0; done < n; done += chunk_rows, ++chunk_index) {
         const size_t rows = std::min(chunk_rows, n - done);
         const float *src = x + done * dim;
         if (!on_device) {
-            TV_CUDA(cudaMemcpyAsync(h->d_stage.ptr, src, rows * dim * 4, cudaMemcpyHostToDevice, h->stream));
-            src = h->d_stage.ptr;
+            const int b = int(chunk_index & 1);
+            if (chunk_index >= 2) TV_CUDA(cudaEventSynchronize(h->ev_consumed[b]));   // the encode of chunk i-2 has read d_add[b]
+            const size_t bytes = rows * dim * 4;
+            const float *h_src = h->h_add[b].ptr;
+            if (src_pinned) {
+                h_src = src;
+            } else if (bytes < (size_t(4) << 20) || copy_threads == 1) {
+                std::memcpy(h->h_add[b].ptr, src, bytes);
+            } else {
+                std::vector<std::thread> pool;
+                for (size_t t = 0; t < copy_threads; ++t) {
+                    const size_t lo = bytes * t / copy_threads / 64 * 64, hi = t + 1 == copy_threads ? bytes : bytes * (t + 1) / copy_threads / 64 * 64;
+                    pool.emplace_back([=] { std::memcpy(reinterpret_cast<char *>(h->h_add[b].ptr) + lo, reinterpret_cast<const char *>(src) + lo, hi - lo); });
+                }
+                for (auto &th : pool) th.join();
+            }
+            TV_CUDA(cudaMemcpyAsync(h->d_add[b].ptr, h_src, bytes, cudaMemcpyHostToDevice, h->copy_stream));
+            TV_CUDA(cudaEventRecord(h->ev_copied[b], h->copy_stream));
+            TV_CUDA(cudaStreamWaitEvent(h->stream, h->ev_copied[b], 0));
+            src = h->d_add[b].ptr;
         }
         p.x = src; p.n = int64_t(rows); p.slot0 = int64_t(h->n + done); p.row_base = int64_t(done);
         // rows that complete a partly filled block go through the block-at-a-time kernel, whole blocks
@@ -439,6 +490,7 @@ int add_rows(tv_index *h, const float *x, size_t n, size_t dim, bool on_device) 
             mark_end(h);
             h->launches++;
         }
+        if (!on_device) TV_CUDA(cudaEventRecord(h->ev_consumed[chunk_index & 1], h->stream));
     }
     TV_CUDA(cudaEventRecord(h->ev1, h->stream));
     TV_CUDA(cudaMemcpyAsync(&h->h_flags->first_invalid, &h->d_flags->first_invalid, 8, cudaMemcpyDeviceToHost, h->stream));
