@@ -555,3 +555,22 @@ def test_large_allowlist_resolved_by_host_threads(T):
     bad[90_001] = np.uint64(6)
     with pytest.raises(KeyError, match="5"):
         idx.search(q, 10, allowlist=bad)
+
+
+def test_host_add_through_several_staging_chunks(T):
+    """A host-memory add larger than the staging buffers (64 MB each, two of them in rotation): every chunk but
+    the first starts in the middle of a code block; codes and scales must still be the oracle's."""
+    n, dim = 35_017, 1536
+    x = anisotropic(n, dim, seed=51)
+    idx = T.TurboQuantIndex(dim, 4)
+    idx.add(x[:7])
+    idx.add(x[7:])
+    enc = O.encode(x, 4)
+    assert np.array_equal(idx.codes_blocked_seq(), O.packed_to_blocked(enc["packed"], 4, dim))
+    assert np.array_equal(idx.scales().view(np.uint32), enc["scales"].view(np.uint32))
+    bad = x.copy()
+    bad[30_123, 77] = np.inf                      # in the fourth chunk
+    idx2 = T.TurboQuantIndex(dim, 4)
+    with pytest.raises(ValueError, match="vector 30123 coordinate 77"):
+        idx2.add(bad)
+    assert len(idx2) == 0
