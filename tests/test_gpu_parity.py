@@ -574,3 +574,26 @@ def test_host_add_through_several_staging_chunks(T):
     with pytest.raises(ValueError, match="vector 30123 coordinate 77"):
         idx2.add(bad)
     assert len(idx2) == 0
+
+
+def test_pipelined_ingest_block_and_wave_boundaries(T):
+    """Batch sizes around the boundaries of the pipelined kernel: fewer blocks than CTAs, a single wave,
+    one block per CTA exactly, a ragged last block, adds that start on and off a block boundary."""
+    dim = 128
+    x = anisotropic(9_600, dim, seed=61)
+    enc = O.encode(x, 4)
+    want_blocked = O.packed_to_blocked(enc["packed"], 4, dim)
+    for n in (1, 7, 8, 9, 31, 32, 33, 63, 64, 65, 255, 256, 257, 4_735, 4_736, 4_737, 9_473):
+        for first in (0, 5, 32):
+            if first >= n:
+                continue
+            idx = T.TurboQuantIndex(dim, 4)
+            if first:
+                idx.add(x[:first])
+            idx.add(x[first:n])
+            sub = O.encode(x[:n], 4)
+            assert np.array_equal(idx.packed_codes(), sub["packed"]), (n, first)
+            assert np.array_equal(idx.scales().view(np.uint32), sub["scales"].view(np.uint32)), (n, first)
+    idx = T.TurboQuantIndex(dim, 4)
+    idx.add(x)
+    assert np.array_equal(idx.codes_blocked_seq(), want_blocked)
