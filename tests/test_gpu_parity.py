@@ -597,3 +597,19 @@ def test_pipelined_ingest_block_and_wave_boundaries(T):
     idx = T.TurboQuantIndex(dim, 4)
     idx.add(x)
     assert np.array_equal(idx.codes_blocked_seq(), want_blocked)
+
+
+@pytest.mark.parametrize("n", [1, 31, 33, 4095, 4096, 4097, 4129, 12_000, 110_000])
+def test_tensor_memory_scan_chunk_boundaries(T, n):
+    """Index sizes around the first chunk (written in place, 4,096 or 8,192 vectors) and the growth steps of
+    the tensor-memory path's chunk schedule, for k below and above the 512 that doubles the list capacity."""
+    dim, nq = 64, 40
+    x = anisotropic(n, dim, seed=71)
+    q = anisotropic(nq, dim, seed=71, offset=3)
+    idx = _build(T, x, 4)
+    for k in (1, 10, 600):
+        s, i = idx.search(q, k)
+        rs, ri = _oracle_search(x, q, 4, k)
+        assert s.shape == (nq, min(k, n))
+        assert np.array_equal(i, ri), f"n={n} k={k}: id lists differ"
+        assert np.array_equal(s, rs), f"n={n} k={k}: scores differ"
