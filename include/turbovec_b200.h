@@ -62,7 +62,7 @@ typedef enum tv_status {
     /* CalibrateError, error.rs:516-588 */
     TV_ERR_CALIBRATE_SAMPLE_TOO_SMALL = 50,
     TV_ERR_CALIBRATE_DEGENERATE_SAMPLE = 51,
-    TV_ERR_CALIBRATE_NOT_EMPTY = 52,
+    TV_ERR_CALIBRATE_NOT_EMPTY = 52,    /* no longer returned: a populated index is refitted */
     /* this library */
     TV_ERR_INVALID_ARGUMENT = 90,
     TV_ERR_CUDA = 91,
@@ -223,7 +223,8 @@ int tv_from_bytes(const uint8_t *data, size_t len, int expect_kind, int device, 
 int tv_write(const tv_index *h, const char *path);
 int tv_load(const char *path, int expect_kind, int device, tv_index **out);
 
-/* ---- TQ+ calibration: calibrate_2d (lib.rs:2599-2723) on an EMPTY index; tqplus_shift/scale (lib.rs:2535-2545) ---- */
+/* ---- TQ+ calibration: calibrate_2d (lib.rs:2599-2723); on a populated index every stored row is re-encoded from
+ * its own codes under the new pair (reencode_stored_rows, lib.rs:2760-2832); tqplus_shift/scale (lib.rs:2535-2545) ---- */
 int tv_calibrate(tv_index *h, const float *sample, size_t n, size_t dim);
 int tv_calibration(const tv_index *h, float *shift_out, float *scale_out, size_t capacity, int *is_calibrated);
 int tv_set_calibration(tv_index *h, size_t dim, const float *shift, const float *scale);

@@ -45,6 +45,7 @@ def _lib():
     lib.tvo_rotate_batch.argtypes = [f32p, C.c_int64, C.c_int, f32p, f32p]
     lib.tvo_fit_calibration.argtypes = [f32p, C.c_int64, C.c_int, f32p, C.c_int, f32p, f32p]
     lib.tvo_encode.argtypes = [f32p, C.c_int64, C.c_int, C.c_int, f32p, f32p, f32p, f32p, u8p, f32p, u8p, f32p]
+    lib.tvo_reencode.argtypes = [u8p, f32p, C.c_int64, C.c_int, C.c_int, f32p, f32p, f32p, f32p, f32p, f32p, u8p, f32p]
     lib.tvo_boundary_distance.argtypes = [f32p, C.c_int64, C.c_int, C.c_int, f32p, f32p, f32p, f32p]
     lib.tvo_extract_codes_flat.argtypes = [u8p, C.c_int64, C.c_int, C.c_int, u8p]
     lib.tvo_pack_blocked_seq.argtypes = [u8p, C.c_int64, C.c_int, u8p]
@@ -161,6 +162,22 @@ def encode(x: np.ndarray, bits: int, shift=None, scale=None, want_codes=False, w
     if want_rotated:
         out["rotated"] = rot
     return out
+
+
+def reencode(codes: np.ndarray, scales: np.ndarray, bits: int, old_shift=None, old_scale=None, new_shift=None,
+             new_scale=None):
+    """Stored rows (one code per coordinate, [n, dim]) re-encoded under a new TQ+ pair; returns (codes, scales)."""
+    codes = np.ascontiguousarray(codes, dtype=np.uint8)
+    n, dim = codes.shape
+    bnd, cent = (np.array(a) for a in codebook(bits, dim))
+    scales = _f32(scales)
+    out_codes = np.empty_like(codes)
+    out_scales = np.empty(n, dtype=np.float32)
+    os_, osc, ns, nsc = _f32(old_shift), _f32(old_scale), _f32(new_shift), _f32(new_scale)
+    _lib().tvo_reencode(_p(codes, C.c_uint8), _p(scales, C.c_float), n, dim, bits, _p(bnd, C.c_float), _p(cent, C.c_float),
+                        _p(os_, C.c_float), _p(osc, C.c_float), _p(ns, C.c_float), _p(nsc, C.c_float),
+                        _p(out_codes, C.c_uint8), _p(out_scales, C.c_float))
+    return out_codes, out_scales
 
 
 def boundary_distance(rotated: np.ndarray, bits: int, shift=None, scale=None) -> np.ndarray:

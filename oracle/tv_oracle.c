@@ -439,6 +439,39 @@ void tvo_encode(const float *vectors, int64_t n, int dim, int bits, const float 
 }
 
 /*
+ * Re-encoding of stored rows under a new TQ+ pair: lib.rs:2760-2832 (reencode_stored_rows).
+ * Each row is reconstructed from its codes under the committed pair (NULL = identity),
+ * x[d] = centroids[code] * old_inv[d] - old_shift[d] in f32, its squared length is summed in one
+ * f64 chain in coordinate order, the effective norm is (f64(scale_old) * sumsq) as f32, and the
+ * reconstruction goes through the same quantise + scale as a fresh row under the new pair.
+ * codes_in / codes_out: one code per coordinate, n * dim.
+ */
+void tvo_reencode(const uint8_t *codes_in, const float *scales_in, int64_t n, int dim, int bits,
+                  const float *boundaries, const float *centroids, const float *old_shift,
+                  const float *old_scale, const float *new_shift, const float *new_scale,
+                  uint8_t *codes_out, float *scales_out) {
+#pragma omp parallel
+    {
+        float *recon = malloc(sizeof(float) * dim);
+#pragma omp for schedule(static)
+        for (int64_t i = 0; i < n; i++) {
+            double sumsq = 0.0;
+            for (int d = 0; d < dim; d++) {
+                float inv = old_scale ? 1.0f / old_scale[d] : 1.0f;
+                float sh = old_shift ? old_shift[d] : 0.0f;
+                float x = centroids[codes_in[(size_t)i * dim + d]] * inv - sh;
+                recon[d] = x;
+                sumsq += (double)x * (double)x;
+            }
+            float norm = (float)((double)scales_in[i] * sumsq);
+            scales_out[i] = tvo_quantize_row(recon, dim, bits, boundaries, centroids, new_shift, new_scale,
+                                             norm, codes_out + (size_t)i * dim);
+        }
+        free(recon);
+    }
+}
+
+/*
  * Per-coordinate distance to the nearest quantiser decision boundary, for the
  * classification of code mismatches (a mismatch is tolerated only within
  * 1e-6 of a boundary).  Same calib expression as tvo_quantize_row.

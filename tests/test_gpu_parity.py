@@ -182,8 +182,76 @@ def test_calibrated_search_matches_oracle(T):
         s, i = idx.search(q, 10)
         rs, ri = O.search(q, blocked, enc["scales"], n, dim, mode_bits, 10, shift=sh, scale=sc)
         assert np.array_equal(i, ri) and np.array_equal(s, rs)
-    with pytest.raises(ValueError):
-        idx.calibrate(x)                                 # not empty any more
+
+
+@pytest.mark.parametrize("dim,bits", [(512, 4), (256, 2), (384, 3), (1536, 4)])
+def test_calibrate_on_populated_index_reencodes_stored_rows(T, dim, bits):
+    """calibrate() on an index that already holds rows re-encodes every stored row from its own codes under
+    the new pair (the reference's refit): first from the identity pair, then from a committed pair."""
+    n = 1000 + 21
+    x = anisotropic(n, dim, seed=57) * np.float32(2.0)
+    x[:, ::5] *= np.float32(3.0)
+    x[11] = 0.0                                          # a degenerate row stays degenerate
+    idx = T.TurboQuantIndex(dim, bits)
+    idx.add(x)
+    enc = O.encode(x, bits, want_codes=True)
+    sample1 = x[:600]
+    sh1, sc1 = O.fit_calibration(sample1, bits)
+    idx.calibrate(sample1)
+    got_sh, got_sc = idx.calibration()
+    assert np.array_equal(got_sh, sh1) and np.array_equal(got_sc, sc1)
+    codes1, scales1 = O.reencode(enc["codes"], enc["scales"], bits, None, None, sh1, sc1)
+    want1 = O.packed_to_blocked(_pack_bitplanes(codes1, bits), bits, dim)
+    assert np.array_equal(idx.codes_blocked_seq(), want1)
+    assert np.array_equal(idx.scales().view(np.uint32), scales1.view(np.uint32))
+    assert idx.scales()[11] == 0.0
+    # second refit, now from a committed pair
+    sample2 = x[300:] * np.float32(1.5)
+    sh2, sc2 = O.fit_calibration(sample2, bits)
+    idx.calibrate(sample2)
+    codes2, scales2 = O.reencode(codes1, scales1, bits, sh1, sc1, sh2, sc2)
+    assert np.array_equal(idx.codes_blocked_seq(), O.packed_to_blocked(_pack_bitplanes(codes2, bits), bits, dim))
+    assert np.array_equal(idx.scales().view(np.uint32), scales2.view(np.uint32))
+    # rows added afterwards are encoded under the new pair, and searches see one consistent index
+    y = anisotropic(100, dim, seed=58)
+    idx.add(y)
+    enc_y = O.encode(y, bits, sh2, sc2, want_codes=True)
+    all_codes = np.concatenate([codes2, enc_y["codes"]])
+    all_scales = np.concatenate([scales2, enc_y["scales"]])
+    blocked = O.packed_to_blocked(_pack_bitplanes(all_codes, bits), bits, dim)
+    assert np.array_equal(idx.codes_blocked_seq(), blocked)
+    q = anisotropic(6, dim, seed=59)
+    s, i = idx.search(q, 10)
+    rs, ri = O.search(q, blocked, all_scales, n + 100, dim, bits, 10, shift=sh2, scale=sc2)
+    assert np.array_equal(i, ri) and np.array_equal(s, rs)
+
+
+def test_refit_under_the_committed_pair_keeps_the_codes(T):
+    """The property the reference states for its refit (lib.rs:2776-2782): re-quantising an exact centroid
+    value lands in its own cell, so calibrating again with the sample that produced the committed pair
+    reproduces every stored code."""
+    dim, bits, n = 768, 4, 700
+    x = anisotropic(n, dim, seed=63) * np.float32(2.0)
+    idx = T.TurboQuantIndex(dim, bits)
+    idx.calibrate(x)
+    idx.add(x)
+    before = idx.codes_blocked_seq()
+    idx.calibrate(x)
+    assert np.array_equal(idx.codes_blocked_seq(), before)
+    assert np.allclose(idx.scales(), O.encode(x, bits, *O.fit_calibration(x, bits))["scales"], rtol=1e-5)
+
+
+def _pack_bitplanes(codes, bits):
+    """[n, dim] codes -> the reference's bit-plane rows (encode.rs:1464-1470)."""
+    n, dim = codes.shape
+    out = np.zeros((n, bits * dim // 8), dtype=np.uint8)
+    c = codes.reshape(n, dim // 8, 8)
+    for p in range(bits):
+        plane = np.zeros((n, dim // 8), dtype=np.uint8)
+        for k in range(8):
+            plane |= (((c[:, :, k] >> p) & 1) << (7 - k)).astype(np.uint8)
+        out[:, p * (dim // 8):(p + 1) * (dim // 8)] = plane
+    return out
 
 
 # ---------------------------------------------------------------- search

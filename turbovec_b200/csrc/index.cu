@@ -1628,7 +1628,6 @@ int tv_calibrate(tv_index *h, const float *sample, size_t n, size_t dim) {
     int rc = validate_dim_for_add(h, dim);
     if (rc != TV_OK) return rc;
     if (n < 2) return fail(h, TV_ERR_CALIBRATE_SAMPLE_TOO_SMALL, "calibration needs at least 2 rows, got " + std::to_string(n));
-    if (h->n != 0) return fail(h, TV_ERR_CALIBRATE_NOT_EMPTY, "re-encoding stored rows under a new calibration is not built: calibrate before the first add");
     for (size_t i = 0; i < n * dim; ++i)
         if (!(std::fabs(sample[i]) < kMaxInputMagnitude)) {
             h->err_vec = i / dim; h->err_coord = i % dim; h->err_value = sample[i];
@@ -1690,6 +1689,23 @@ int tv_calibrate(tv_index *h, const float *sample, size_t n, size_t dim) {
         if (shift[d] != 0.f || scale[d] != 1.f) identity = false;
     }
     if (identity) { undo(); return fail(h, TV_ERR_CALIBRATE_DEGENERATE_SAMPLE, "the sample yields the identity calibration (degenerate sample)"); }
+    if (h->n > 0) {
+        // refit: every stored row is re-encoded under the new pair from its own codes (lib.rs:2697-2700, 2760-2832)
+        std::vector<float> pair(3 * dim);
+        for (size_t d = 0; d < dim; ++d) { pair[d] = shift[d]; pair[dim + d] = scale[d]; pair[2 * dim + d] = 1.0f / scale[d]; }
+        DeviceArray<float> d_new;
+        TV_CUDA(d_new.reserve(3 * dim));
+        TV_CUDA(cudaMemcpyAsync(d_new.ptr, pair.data(), pair.size() * 4, cudaMemcpyHostToDevice, h->stream));
+        ReencodeParams rp{};
+        rp.codes = h->d_codes; rp.scales = h->d_scales; rp.n = int64_t(h->n);
+        rp.dim = int(dim); rp.bits = h->bits; rp.ngroups = h->ngroups;
+        rp.boundaries = h->d_codebook.ptr; rp.centroids = h->d_codebook.ptr + 16;
+        if (!h->shift.empty()) { rp.old_shift = h->d_calib.ptr; rp.old_inv = h->d_calib.ptr + 2 * dim; }
+        rp.new_shift = d_new.ptr; rp.new_scale = d_new.ptr + dim; rp.new_inv = d_new.ptr + 2 * dim;
+        TV_CUDA(launch_reencode(rp, h->stream));
+        h->launches++;
+        TV_CUDA(cudaStreamSynchronize(h->stream));
+    }
     h->shift = shift;
     h->scale_tq = scale;
     return upload_calibration(h);

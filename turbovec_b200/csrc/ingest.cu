@@ -220,6 +220,62 @@ __global__ void __launch_bounds__(256) ingest_kernel(IngestParams p) {
     }
 }
 
+// Re-encoding of stored rows under a new TQ+ pair (reencode_stored_rows, turbovec/src/lib.rs:2760-2832), in
+// place.  One warp per code block, lane = vector.  Pass 1 reconstructs the row from its codes under the
+// committed pair, x[d] = centroids[code] * old_inv[d] - old_shift[d] (f32, two roundings), and sums x^2 in one
+// f64 chain in coordinate order; the effective norm is (f64(scale_old) * sumsq) as f32.  Pass 2 is the fresh-row
+// quantise + scale of encode_prerotated (encode.rs:560-652, 1418-1476) on that reconstruction under the new
+// pair: four f64 chains over d % 4, (c0+c1)+(c2+c3), scale = norm / (f32)inner if inner > 0.1.
+__global__ void __launch_bounds__(256) reencode_kernel(ReencodeParams p) {
+    const int lane = threadIdx.x & 31;
+    const int64_t blk = int64_t(blockIdx.x) * (blockDim.x >> 5) + (threadIdx.x >> 5);
+    const int64_t slot = blk * kBlockLanes + lane;
+    if (slot >= p.n) return;
+    const int ng = p.ngroups, cpb = 8 / p.bits, field = p.bits == 3 ? 4 : p.bits;
+    const uint32_t mask = (1u << p.bits) - 1u;
+    const int nb = (1 << p.bits) - 1;
+    uint8_t *codes = p.codes + size_t(blk) * ng * kBlockLanes + lane;
+    double sumsq = 0.0;
+    for (int g = 0; g < ng; ++g) {
+        const uint32_t byte = codes[size_t(g) * kBlockLanes];
+        for (int k = 0; k < cpb; ++k) {
+            const int d = g * cpb + k;
+            const uint32_t code = (byte >> ((cpb - 1 - k) * field)) & mask;
+            const float inv = p.old_inv ? p.old_inv[d] : 1.0f, sh = p.old_shift ? p.old_shift[d] : 0.0f;
+            const float x = __fsub_rn(__fmul_rn(p.centroids[code], inv), sh);
+            sumsq = __dadd_rn(sumsq, __dmul_rn(double(x), double(x)));
+        }
+    }
+    const float norm = __double2float_rn(__dmul_rn(double(p.scales[slot]), sumsq));
+    double c0 = 0.0, c1 = 0.0, c2 = 0.0, c3 = 0.0;       // chain d % 4 (kept in registers: no indexed array)
+    for (int g = 0; g < ng; ++g) {
+        const uint32_t byte = codes[size_t(g) * kBlockLanes];
+        uint32_t out = 0;
+        for (int k = 0; k < cpb; ++k) {
+            const int d = g * cpb + k;
+            const uint32_t code = (byte >> ((cpb - 1 - k) * field)) & mask;
+            const float inv = p.old_inv ? p.old_inv[d] : 1.0f, sh = p.old_shift ? p.old_shift[d] : 0.0f;
+            const float x = __fsub_rn(__fmul_rn(p.centroids[code], inv), sh);
+            const float nsh = p.new_shift[d];
+            const float calib = __fmul_rn(__fadd_rn(x, nsh), p.new_scale[d]);
+            uint32_t v = 0;
+            for (int bi = 0; bi < nb; ++bi) v += calib > p.boundaries[bi] ? 1u : 0u;
+            const double recon = __dsub_rn(__dmul_rn(double(p.centroids[v]), double(p.new_inv[d])), double(nsh));
+            const double term = __dmul_rn(double(x), recon);
+            switch (d & 3) {
+                case 0: c0 = __dadd_rn(c0, term); break;
+                case 1: c1 = __dadd_rn(c1, term); break;
+                case 2: c2 = __dadd_rn(c2, term); break;
+                default: c3 = __dadd_rn(c3, term); break;
+            }
+            out |= v << ((cpb - 1 - k) * field);
+        }
+        codes[size_t(g) * kBlockLanes] = uint8_t(out);
+    }
+    const double inner = __dadd_rn(__dadd_rn(c0, c1), __dadd_rn(c2, c3));
+    p.scales[slot] = inner > 0.1 ? __fdiv_rn(norm, __double2float_rn(inner)) : 0.0f;
+}
+
 }  // namespace
 
 size_t ingest_smem_bytes(int V, int dim, int ngroups) {
@@ -260,6 +316,13 @@ cudaError_t launch_ingest(const IngestParams &p, int V, cudaStream_t stream) {
         default: return cudaErrorInvalidValue;
     }
 #undef TV_LAUNCH_INGEST
+    return cudaGetLastError();
+}
+
+cudaError_t launch_reencode(const ReencodeParams &p, cudaStream_t stream) {
+    if (p.n <= 0) return cudaSuccess;
+    const int64_t blocks = (p.n + kBlockLanes - 1) / kBlockLanes;
+    reencode_kernel<<<unsigned((blocks + 7) / 8), 256, 0, stream>>>(p);
     return cudaGetLastError();
 }
 

@@ -40,6 +40,18 @@ size_t ingest_smem_bytes(int vectors_per_pass, int dim, int ngroups);
 int ingest_vectors_per_pass(int dim, int ngroups, size_t smem_limit);
 cudaError_t launch_ingest(const IngestParams &p, int vectors_per_pass, cudaStream_t stream);
 
+// Stored rows re-encoded in place under a new TQ+ pair (see reencode_kernel in ingest.cu).
+struct ReencodeParams {
+    uint8_t *codes;                // sequential-blocked code array of the whole index
+    float *scales;
+    int64_t n;
+    int dim, bits, ngroups;
+    const float *boundaries, *centroids;
+    const float *old_shift, *old_inv;          // committed pair (1 / scale rounded in f32), or nullptr = identity
+    const float *new_shift, *new_scale, *new_inv;
+};
+cudaError_t launch_reencode(const ReencodeParams &p, cudaStream_t stream);
+
 // Pipelined form (ingest_fast.cu) for whole code blocks: p.slot0 a multiple of 32, no calibration, no
 // rotate-only mode, x 16-byte aligned, dim one of the instantiated sizes, shared memory within the limit.
 // It quantises through a grid table built once per codebook: cell c holds the number of boundaries in lower
