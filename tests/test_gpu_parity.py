@@ -681,3 +681,33 @@ def test_tensor_memory_scan_chunk_boundaries(T, n):
         assert s.shape == (nq, min(k, n))
         assert np.array_equal(i, ri), f"n={n} k={k}: id lists differ"
         assert np.array_equal(s, rs), f"n={n} k={k}: scores differ"
+
+
+def test_chunk_size_keyword_gives_the_unsliced_results(T):
+    """search / add / add_with_ids accept the reference binding's chunk_size= keyword; slicing changes nothing."""
+    dim, n = 64, 3000
+    x = anisotropic(n, dim, seed=81)
+    q = anisotropic(70, dim, seed=81, offset=9)
+    a, b = T.TurboQuantIndex(dim, 4), T.TurboQuantIndex(dim, 4)
+    a.add(x)
+    b.add(x, chunk_size=999)
+    assert np.array_equal(a.codes_blocked_seq(), b.codes_blocked_seq()) and np.array_equal(a.scales(), b.scales())
+    s0, i0 = a.search(q, 10)
+    for cs in (1, 7, 64, 0, -3, 1000):
+        s1, i1 = a.search(q, 10, chunk_size=cs)
+        assert np.array_equal(s0, s1) and np.array_equal(i0, i1)
+    bad = x.copy()
+    bad[2500, 3] = np.nan
+    c = T.TurboQuantIndex(dim, 4)
+    with pytest.raises(ValueError, match="vector 2500 coordinate 3"):
+        c.add(bad, chunk_size=100)
+    assert len(c) == 0                                   # rejected whole: no slice was committed
+    ids = np.arange(n, dtype=np.uint64) + np.uint64(10)
+    m = T.IdMapIndex(dim, 4)
+    m.add_with_ids(x, ids, chunk_size=512)
+    s2, g2 = m.search(q, 10, chunk_size=16, allowlist=ids[::3].copy())
+    s3, g3 = m.search(q, 10, allowlist=ids[::3].copy())
+    assert np.array_equal(s2, s3) and np.array_equal(g2, g3)
+    with pytest.raises(ValueError, match="already present"):
+        m.add_with_ids(x[:600], ids[:600].copy(), chunk_size=100)
+    assert len(m) == n

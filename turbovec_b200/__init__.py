@@ -229,6 +229,17 @@ class _Base:
     def __reduce__(self):
         return (type(self).from_bytes, (self.to_bytes(),))
 
+    def _search_sliced(self, queries, k, fn, extra, out_dtype, chunk_size):
+        """Per-query results do not depend on the other queries of a batch, so slices concatenate to exactly
+        the result of one call."""
+        slices = None
+        if isinstance(queries, np.ndarray) and queries.ndim == 2:
+            slices = _slice_rows(chunk_size, queries.shape[0])
+        if slices is None:
+            return self._search_raw(queries, k, fn, extra, out_dtype)
+        parts = [self._search_raw(queries[a:b], k, fn, extra, out_dtype) for a, b in slices]
+        return np.concatenate([p[0] for p in parts]), np.concatenate([p[1] for p in parts])
+
     def _search_raw(self, queries, k, fn, extra, out_dtype):
         queries = _f32_2d("queries", queries)
         k = _size("k", k)
@@ -247,26 +258,46 @@ class _Base:
         return (scores.ravel()[: nq * ke].reshape(nq, ke).copy(), ids.ravel()[: nq * ke].reshape(nq, ke).copy())
 
 
+def _slice_rows(chunk_size, n_rows):
+    """Slices of a batch for the `chunk_size=` keyword of search / add / add_with_ids
+    (turbovec-python/python/turbovec/_interruptible.py): a value > 0 makes the call go through the library in
+    slices of that many rows, so that a pending KeyboardInterrupt is raised between slices; None, 0 or a
+    negative value runs the call whole.  Unlike the reference, whose default slices at BATCH_CHUNK_SIZE rows,
+    the default here is one call: the library already works through large batches in bounded chunks on the
+    device, and a call of that size returns in milliseconds."""
+    cs = 0 if chunk_size is None else int(chunk_size)
+    if cs <= 0 or n_rows <= cs:
+        return None
+    return [(a, min(a + cs, n_rows)) for a in range(0, n_rows, cs)]
+
+
 class TurboQuantIndex(_Base):
     """Positional index: results are slot numbers.  Mirrors turbovec-python/src/lib.rs:416-947."""
     _KIND = 0
 
-    def add(self, vectors: np.ndarray) -> None:
+    def add(self, vectors: np.ndarray, *, chunk_size=None) -> None:
         vectors = _f32_2d("vectors", vectors)
+        slices = _slice_rows(chunk_size, vectors.shape[0])
+        if slices is not None and bool(np.all(np.abs(vectors) < np.float32(1e16))):
+            # a batch that would be rejected goes to the library whole, so that nothing is committed
+            for a, b in slices:
+                part = vectors[a:b]
+                self._check(self._lib.tv_add(self._h, _ptr(part), part.shape[0], part.shape[1]))
+            return
         self._check(self._lib.tv_add(self._h, _ptr(vectors), vectors.shape[0], vectors.shape[1]))
 
     def add_device(self, device_ptr: int, n: int, dim: int) -> None:
         """Adds n rows that already sit in device memory (row-major float32 at `device_ptr`)."""
         self._check(self._lib.tv_add_device(self._h, C.c_void_p(device_ptr), n, dim))
 
-    def search(self, queries: np.ndarray, k: int, *, mask=None):
+    def search(self, queries: np.ndarray, k: int, *, mask=None, chunk_size=None):
         extra = (None, 0)
         if mask is not None:
             mask = _typed_1d("mask", mask, np.bool_, "bool")
             if mask.size != len(self):
                 raise ValueError(f"mask length {mask.size} does not match index size {len(self)}")
             extra = (_ptr(mask), mask.size)
-        return self._search_raw(queries, k, self._lib.tv_search, extra, np.int64)
+        return self._search_sliced(queries, k, self._lib.tv_search, extra, np.int64, chunk_size)
 
     def search_mask_words(self, queries: np.ndarray, k: int, words: np.ndarray):
         words = _typed_1d("words", words, np.uint64, "uint64")
@@ -323,11 +354,20 @@ class IdMapIndex(_Base):
     """Index addressed by caller-chosen uint64 ids.  Mirrors turbovec-python/src/lib.rs:952-1540."""
     _KIND = 1
 
-    def add_with_ids(self, vectors: np.ndarray, ids: np.ndarray) -> None:
+    def add_with_ids(self, vectors: np.ndarray, ids: np.ndarray, *, chunk_size=None) -> None:
         vectors = _f32_2d("vectors", vectors)
         ids = _typed_1d("ids", ids, np.uint64, "uint64")
         if ids.size != vectors.shape[0]:
             raise ValueError(f"ids length {ids.size} does not match number of vectors {vectors.shape[0]}")
+        slices = _slice_rows(chunk_size, vectors.shape[0])
+        if slices is not None and bool(np.all(np.abs(vectors) < np.float32(1e16))) and np.unique(ids).size == ids.size \
+                and not any(self.contains(int(i)) for i in ids):
+            # pre-validated like the library's own up-front check: a batch that would be rejected goes to it
+            # whole, so that nothing is committed
+            for a, b in slices:
+                part, part_ids = vectors[a:b], ids[a:b]
+                self._check(self._lib.tv_add_with_ids(self._h, _ptr(part), part.shape[0], part.shape[1], _ptr(part_ids)))
+            return
         self._check(self._lib.tv_add_with_ids(self._h, _ptr(vectors), vectors.shape[0], vectors.shape[1], _ptr(ids)))
 
     def remove(self, id) -> bool:
@@ -355,14 +395,14 @@ class IdMapIndex(_Base):
         self._check(self._lib.tv_ids(self._h, _ptr(out), out.size))
         return out
 
-    def search(self, queries: np.ndarray, k: int, *, allowlist=None):
+    def search(self, queries: np.ndarray, k: int, *, allowlist=None, chunk_size=None):
         extra = (None, 0)
         if allowlist is not None:
             allowlist = _typed_1d("allowlist", allowlist, np.uint64, "uint64")
             if allowlist.size == 0:
                 raise ValueError("allowlist is empty")
             extra = (_ptr(allowlist), allowlist.size)
-        return self._search_raw(queries, k, self._lib.tv_search_allowlist, extra, np.uint64)
+        return self._search_sliced(queries, k, self._lib.tv_search_allowlist, extra, np.uint64, chunk_size)
 
     def __repr__(self):
         return f"IdMapIndex(dim={self.dim}, bit_width={self.bit_width}, len={len(self)})"
