@@ -115,6 +115,26 @@ def test_pipelined_ingest_matches_oracle_and_block_kernel(T, dim, bits):
         assert np.array_equal(idx.packed_codes(), enc["packed"])
 
 
+@pytest.mark.parametrize("dim,bits", [(256, 4), (768, 2), (1024, 3), (1536, 4), (3072, 2)])
+def test_pipelined_ingest_with_calibration(T, dim, bits):
+    """A committed TQ+ pair: the pipelined kernel (with its certified sum and with the sequential chains
+    forced) and the block-at-a-time kernel all produce the oracle's calibrated codes and scales."""
+    n = 1200 + 9
+    x = anisotropic(n, dim, seed=5 * dim + bits) * np.float32(2.0)
+    x[:, ::9] *= np.float32(3.0)
+    sh, sc = O.fit_calibration(x[:700], bits)
+    enc = O.encode(x, bits, sh, sc)
+    want_blocked = O.packed_to_blocked(enc["packed"], bits, dim)
+    for mode in (1, 0, 2):
+        idx = T.TurboQuantIndex(dim, bits)
+        idx.set_option(T.OPT_INGEST_PIPELINE, mode)
+        idx.calibrate(x[:700])
+        idx.add(x[:3])
+        idx.add(x[3:])
+        assert np.array_equal(idx.codes_blocked_seq(), want_blocked), mode
+        assert np.array_equal(idx.scales().view(np.uint32), enc["scales"].view(np.uint32)), mode
+
+
 def test_pipelined_ingest_reports_first_invalid_coordinate(T):
     x = anisotropic(400, 256, seed=12)
     idx = T.TurboQuantIndex(256, 4)

@@ -1,4 +1,4 @@
-// Pipelined ingest kernel for whole 32-slot code blocks of an uncalibrated index: the same arithmetic as
+// Pipelined ingest kernel for whole 32-slot code blocks (with or without a TQ+ pair): the same arithmetic as
 // ingest.cu (encode::encode, turbovec/src/encode.rs:510-541 = rotate_batch_into :406-458 + encode_prerotated
 // :560-652 / fused_quantize_scale_pack_scalar :1418-1476, blocked layout pack.rs:340-361), reorganised so
 // that the order-fixed sequential sums no longer stall the data-parallel work.
@@ -24,8 +24,8 @@
 //
 // Reconstruction inner product.  The reference sums rotated[j] * centroid[code[j]] in f64 along four
 // sequential chains (encode.rs:1418-1476) and uses the result rounded to f32, and a dependent f64 add takes
-// some 45 cycles here.  The products are exact in f64 (both factors are f32 values), so every summation order
-// lands within gamma * sum|products| of the exact sum (gamma_m = m u / (1 - m u), u = 2^-53, m = additions a
+// some 45 cycles here.  The terms are the same numbers in any order (without a TQ+ pair they are even exact
+// products of two f32 values), so every summation order lands within gamma * sum|terms| of their exact sum (gamma_m = m u / (1 - m u), u = 2^-53, m = additions a
 // term goes through).  The rotation warp therefore sums in parallel, brackets the reference's value by
 // S +- 1e-13 * A with A >= sum|products| (1e-13 > gamma_(dim/4+2) + gamma_64 for dim <= 3300), and accepts
 // S when both ends of the bracket round to the same f32 and fall on the same side of the 0.1 threshold:
@@ -132,9 +132,9 @@ __host__ __device__ inline uint32_t grid_offset(float x, float a, float b) {
 
 struct FastLayout {
     int stride;          // floats per staged row (16-byte multiple for the bulk copies)
-    size_t grid, cent, rows, tile, norm, inv, bars, total;
+    size_t grid, cent, rows, tile, calib, norm, inv, bars, total;
 };
-__host__ __device__ inline FastLayout fast_layout(int wave, int dim, int ngroups) {
+__host__ __device__ inline FastLayout fast_layout(int wave, int dim, int ngroups, bool calibrated) {
     FastLayout L;
     L.stride = dim + 4;
     size_t off = 0;
@@ -142,6 +142,7 @@ __host__ __device__ inline FastLayout fast_layout(int wave, int dim, int ngroups
     L.cent = off; off += 16 * 8;                       // centroids as f64
     L.rows = off; off += size_t(2) * wave * L.stride * 4;
     L.tile = off; off += size_t(2) * ngroups * 32;
+    L.calib = off; off += calibrated ? size_t(3) * dim * 4 : 0;   // TQ+ shift, scale, 1 / scale per coordinate
     L.norm = off; off += 4 * wave * 4;
     L.inv = off; off += 4 * wave * 4;
     L.bars = off; off += 2 * 8;
@@ -214,7 +215,7 @@ __device__ __forceinline__ void wht_blocks(float (&v)[R * NBLK], int lane) {
     }
 }
 
-template <int LOG2B, int NBLK, int V>
+template <int LOG2B, int NBLK, int V, bool CALIB>
 __global__ void __launch_bounds__((V + 4) * 32, 1) ingest_fast_kernel(IngestParams p, QuantGrid grid, uint32_t *error) {
     constexpr int R = 1 << (LOG2B - 5);               // registers per Hadamard block and lane
     constexpr int T = R * NBLK;                       // registers per vector and lane
@@ -227,7 +228,7 @@ __global__ void __launch_bounds__((V + 4) * 32, 1) ingest_fast_kernel(IngestPara
     extern __shared__ __align__(128) unsigned char smem[];
     const int ng = p.ngroups;
     const int cpb = p.bits == 2 ? 4 : 2;              // codes per byte (3-bit codes sit in 4-bit fields)
-    const FastLayout L = fast_layout(V, DIM, ng);
+    const FastLayout L = fast_layout(V, DIM, ng, CALIB);
     float *rows = reinterpret_cast<float *>(smem + L.rows);
     unsigned char *tiles = smem + L.tile;
     float *norm_s = reinterpret_cast<float *>(smem + L.norm);     // [4][8]
@@ -250,6 +251,12 @@ __global__ void __launch_bounds__((V + 4) * 32, 1) ingest_fast_kernel(IngestPara
     }
     for (int i = tid; i < kGridCells; i += kFastThreads) reinterpret_cast<uint2 *>(smem + L.grid)[i] = grid.cells[i];
     if (tid < 16) reinterpret_cast<double *>(smem + L.cent)[tid] = double(p.centroids[tid]);   // the array has 16 slots
+    if constexpr (CALIB) {
+        float *cal = reinterpret_cast<float *>(smem + L.calib);
+        for (int i = tid; i < DIM; i += kFastThreads) {
+            cal[i] = p.shift[i]; cal[DIM + i] = p.scale_tq[i]; cal[2 * DIM + i] = p.inv_scale_tq[i];
+        }
+    }
     __syncthreads();
 
     // slot of vector `v` of wave `w`, or -1 past the new rows (padding lanes of the last block)
@@ -285,6 +292,7 @@ __global__ void __launch_bounds__((V + 4) * 32, 1) ingest_fast_kernel(IngestPara
         const float isb = p.inv_sqrt_block;
         const float ga = grid.a, gb = grid.b;
         const uint32_t grid_base = smem_u32(smem + L.grid), cent_base = smem_u32(smem + L.cent);
+        const uint32_t cal_lane = smem_u32(smem + L.calib) + lane * 4;   // TQ+ tables at this lane's coordinates
         float cmax = 0.0f;                            // largest |centroid|
         for (int i = 0; i < (1 << p.bits); ++i) cmax = fmaxf(cmax, fabsf(p.centroids[i]));
         const int q = lane & (cpb - 1);               // this lane packs the registers k = q (mod cpb)
@@ -340,28 +348,45 @@ __global__ void __launch_bounds__((V + 4) * 32, 1) ingest_fast_kernel(IngestPara
                     double sacc[8];                                   // independent partial sums hide the f64 latency
 #pragma unroll
                     for (int i = 0; i < 8; ++i) sacc[i] = 0.0;
-                    float aacc = 0.0f;                                // sum |y| of this lane
+                    float aacc = 0.0f;                                // sum |y| of this lane (uncalibrated)
+                    double tabs = 0.0;                                // sum |term| of this lane (calibrated)
 #pragma unroll
                     for (int k = 0; k < T; ++k) {
                         const float y = __fmul_rn(v[k], isb);
                         v[k] = y;
-                        // code = number of boundaries strictly below y (encode.rs:1447-1451): the cell of y
-                        // knows how many lie in lower cells and the one boundary, if any, inside the cell
-                        const uint2 cell = lds_u2(grid_base + grid_offset(y, ga, gb));
-                        const uint32_t code8 = cell.y + (y > __uint_as_float(cell.x) ? 8u : 0u);   // 8 * code
                         const int kk = row_of<R>(k);               // this register holds coordinate kk * 32 + lane
+                        float c = y, sh = 0.0f;
+                        if constexpr (CALIB) {                     // (rot + shift) * scale, encode.rs:1447
+                            sh = lds_f32(cal_lane + kk * 128);
+                            c = __fmul_rn(__fadd_rn(y, sh), lds_f32(cal_lane + DIM * 4 + kk * 128));
+                        }
+                        // code = number of boundaries strictly below c (encode.rs:1447-1451): the cell of c
+                        // knows how many lie in lower cells and the one boundary, if any, inside the cell
+                        const uint2 cell = lds_u2(grid_base + grid_offset(c, ga, gb));
+                        const uint32_t code8 = cell.y + (c > __uint_as_float(cell.x) ? 8u : 0u);   // 8 * code
                         cw[kk >> 3] += (kk & 7) == 0 ? code8 >> 3 : code8 * (1u << (4 * (kk & 7) - 3));
-                        sacc[k & 7] = __fma_rn(double(y), lds_f64(cent_base + code8), sacc[k & 7]);
-                        aacc += fabsf(y);
+                        if constexpr (CALIB) {
+                            // rot * (centroid / scale - shift) in f64, every operation rounded as in encode.rs:276-278, 1455
+                            const double recon = __dsub_rn(__dmul_rn(lds_f64(cent_base + code8), double(lds_f32(cal_lane + 2 * DIM * 4 + kk * 128))), double(sh));
+                            const double term = __dmul_rn(double(y), recon);
+                            sacc[k & 7] = __dadd_rn(sacc[k & 7], term);
+                            tabs = __dadd_rn(tabs, fabs(term));
+                        } else {
+                            sacc[k & 7] = __fma_rn(double(y), lds_f64(cent_base + code8), sacc[k & 7]);
+                            aacc += fabsf(y);
+                        }
                     }
                     double S = ((sacc[0] + sacc[1]) + (sacc[2] + sacc[3])) + ((sacc[4] + sacc[5]) + (sacc[6] + sacc[7]));
 #pragma unroll
                     for (int m = 1; m < 32; m <<= 1) {
                         S += __shfl_xor_sync(kFullMask, S, m);        // commutative: every lane ends with the same bits
-                        aacc += __shfl_xor_sync(kFullMask, aacc, m);
+                        if constexpr (CALIB) tabs += __shfl_xor_sync(kFullMask, tabs, m);
+                        else aacc += __shfl_xor_sync(kFullMask, aacc, m);
                     }
-                    // A >= sum |y| * max|centroid| >= sum |products|; the factor covers the f32 rounding of aacc
-                    const double A = double(aacc) * double(cmax) * 1.0001;
+                    // A >= sum |terms|.  Uncalibrated: sum |y| * max|centroid| (the factor covers the f32 rounding of
+                    // aacc).  Calibrated: the terms are rounded values, the same in any order, and their absolute
+                    // sum in f64 is off by far less than the factor.
+                    const double A = CALIB ? tabs * 1.000001 : double(aacc) * double(cmax) * 1.0001;
                     const double lo = S - kSumBracket * A, hi = S + kSumBracket * A;
                     const float flo = __double2float_rn(lo), fhi = __double2float_rn(hi);
                     const bool certain = flo == fhi && (lo > 0.1) == (hi > 0.1) && p.exact_sums == 0;
@@ -374,11 +399,19 @@ __global__ void __launch_bounds__((V + 4) * 32, 1) ingest_fast_kernel(IngestPara
                         __syncwarp();
                         double acc = 0.0;
                         if (lane < 4) {
+                            const float *cal = reinterpret_cast<const float *>(smem + L.calib);
                             for (int j = lane; j < DIM; j += 4) {
                                 const float y = row[j];
-                                const uint2 cell = lds_u2(grid_base + grid_offset(y, ga, gb));
-                                const uint32_t code8 = cell.y + (y > __uint_as_float(cell.x) ? 8u : 0u);
-                                acc = __fma_rn(double(y), lds_f64(cent_base + code8), acc);   // exact product: one rounding
+                                float c = y, sh = 0.0f;
+                                if constexpr (CALIB) { sh = cal[j]; c = __fmul_rn(__fadd_rn(y, sh), cal[DIM + j]); }
+                                const uint2 cell = lds_u2(grid_base + grid_offset(c, ga, gb));
+                                const uint32_t code8 = cell.y + (c > __uint_as_float(cell.x) ? 8u : 0u);
+                                if constexpr (CALIB) {
+                                    const double recon = __dsub_rn(__dmul_rn(lds_f64(cent_base + code8), double(cal[2 * DIM + j])), double(sh));
+                                    acc = __dadd_rn(acc, __dmul_rn(double(y), recon));
+                                } else {
+                                    acc = __fma_rn(double(y), lds_f64(cent_base + code8), acc);   // exact product: one rounding
+                                }
                             }
                         }
                         acc = __dadd_rn(acc, __shfl_down_sync(kFullMask, acc, 1));
@@ -661,36 +694,41 @@ uint32_t quant_grid_code(const QuantGridHost &g, float x) {
 
 namespace {
 // 8 vectors per wave where two row sets of 8 fit into shared memory next to the tiles, else 4
-int wave_for(int dim, int ngroups, size_t smem_limit) {
-    if (dim <= 2048 && fast_layout(8, dim, ngroups).total <= smem_limit) return 8;
-    return fast_layout(4, dim, ngroups).total <= smem_limit ? 4 : 0;
+int wave_for(int dim, int ngroups, bool calibrated, size_t smem_limit) {
+    if (dim <= 2048 && fast_layout(8, dim, ngroups, calibrated).total <= smem_limit) return 8;
+    return fast_layout(4, dim, ngroups, calibrated).total <= smem_limit ? 4 : 0;
 }
 }  // namespace
 
 bool ingest_fast_supported(int dim, int bits, int ngroups, bool calibrated, const void *x, size_t smem_limit) {
-    if (calibrated || (reinterpret_cast<uintptr_t>(x) & 15) != 0) return false;
+    if ((reinterpret_cast<uintptr_t>(x) & 15) != 0) return false;
     if (bits != 2 && bits != 3 && bits != 4) return false;
     switch (dim) {
         case 128: case 256: case 384: case 512: case 768: case 1024: case 1536: case 2048: case 3072: break;
         default: return false;
     }
-    return wave_for(dim, ngroups, smem_limit) != 0;
+    return wave_for(dim, ngroups, calibrated, smem_limit) != 0;
 }
 
 cudaError_t launch_ingest_fast(const IngestParams &p, const QuantGrid &grid, int sm_count, size_t smem_limit, uint32_t *error,
                                cudaStream_t stream) {
     if (p.n <= 0) return cudaSuccess;
     if (p.slot0 % kBlockLanes != 0 || grid.cells == nullptr) return cudaErrorInvalidValue;
-    const int wave = wave_for(p.dim, p.ngroups, smem_limit);
+    const bool calibrated = p.shift != nullptr;
+    const int wave = wave_for(p.dim, p.ngroups, calibrated, smem_limit);
     if (wave == 0) return cudaErrorInvalidValue;
-    const size_t smem = fast_layout(wave, p.dim, p.ngroups).total;
+    const size_t smem = fast_layout(wave, p.dim, p.ngroups, calibrated).total;
     const int64_t nblocks = (p.n + kBlockLanes - 1) / kBlockLanes;
     const unsigned nctas = unsigned(std::min<int64_t>(nblocks, int64_t(sm_count)));   // one CTA per SM: it owns the register file
+#define TV_LAUNCH_FAST_VC(L2B, NB, VV, CC)                                                                           \
+    {                                                                                                                \
+        cudaError_t e = cudaFuncSetAttribute(ingest_fast_kernel<L2B, NB, VV, CC>, cudaFuncAttributeMaxDynamicSharedMemorySize, int(smem)); \
+        if (e != cudaSuccess) return e;                                                                              \
+        ingest_fast_kernel<L2B, NB, VV, CC><<<nctas, (VV + 4) * 32, smem, stream>>>(p, grid, error);                 \
+    }
 #define TV_LAUNCH_FAST_V(L2B, NB, VV)                                                                                \
     {                                                                                                                \
-        cudaError_t e = cudaFuncSetAttribute(ingest_fast_kernel<L2B, NB, VV>, cudaFuncAttributeMaxDynamicSharedMemorySize, int(smem)); \
-        if (e != cudaSuccess) return e;                                                                              \
-        ingest_fast_kernel<L2B, NB, VV><<<nctas, (VV + 4) * 32, smem, stream>>>(p, grid, error);                     \
+        if (calibrated) TV_LAUNCH_FAST_VC(L2B, NB, VV, true) else TV_LAUNCH_FAST_VC(L2B, NB, VV, false)              \
     }
 #define TV_LAUNCH_FAST(D, L2B, NB)                                                                                   \
     case D:                                                                                                          \
@@ -707,6 +745,7 @@ cudaError_t launch_ingest_fast(const IngestParams &p, const QuantGrid &grid, int
     }
 #undef TV_LAUNCH_FAST
 #undef TV_LAUNCH_FAST_V
+#undef TV_LAUNCH_FAST_VC
     return cudaGetLastError();
 }
 
