@@ -68,7 +68,9 @@ typedef enum tv_status {
     TV_ERR_CUDA = 91,
     TV_ERR_OUT_OF_MEMORY = 92,
     TV_ERR_UNSUPPORTED = 93,
-    TV_ERR_DEVICE_TIMEOUT = 94
+    TV_ERR_DEVICE_TIMEOUT = 94,
+    TV_ERR_IO = 95,                     /* a file could not be opened, read, written or made durable */
+    TV_ERR_SYNC_FOREIGN_FILE = 96       /* tv_sync: another writer advanced or replaced the bound file */
 } tv_status;
 
 /* Index kinds: turbovec/src/lib.rs:295 (TurboQuantIndex), id_map.rs:221 (IdMapIndex). */
@@ -212,8 +214,8 @@ int tv_rotate(tv_index *h, const float *rows, size_t n, size_t dim, float *rotat
 
 /* ---- persistence: to_bytes / from_bytes / write / load (lib.rs:2167, 2207, 2055, 2235) ----
  * The image is the reference's v7 container (turbovec/src/io_v7.rs), byte for byte the snapshot the
- * reference's to_bytes()/write() produce for the same index state, so files interchange.  Incremental
- * sync journals are read (pending redo ops are applied on load) but never written. */
+ * reference's to_bytes()/write() produce for the same index state, so files interchange.  Files that
+ * incremental syncs have advanced load with their pending redo ops applied. */
 /* The container's checksum: CRC-32C, and for inputs of 4096 bytes or more the CRC-32C of the three CRCs of the
  * input's thirds (io_v7.rs:128-141). */
 uint32_t tv_crc32c(const uint8_t *data, size_t len);
@@ -222,6 +224,21 @@ int tv_to_bytes(const tv_index *h, uint8_t *out, size_t capacity);
 int tv_from_bytes(const uint8_t *data, size_t len, int expect_kind, int device, tv_index **out);
 int tv_write(const tv_index *h, const char *path);
 int tv_load(const char *path, int expect_kind, int device, tv_index **out);
+/* Incremental persistence (lib.rs:1737 `sync`, id_map.rs:867; io_v7.rs plan_incremental :674, run_sync :865,
+ * cursor_state :1604).  The first sync of a path - or a sync to another path than the last one, after a
+ * calibration, over a file that was replaced, or with more than 1,024 dirtied committed slots - writes the whole
+ * index as a fresh container under a new random file identity (temporary file, fsync, rename).  Every other
+ * sync is one batch of positioned writes and one fsync: the 32-row units completed since the last commit,
+ * the units whose pending redo ops can now be written into place, and the alternate commit header with the
+ * tail rows, the redo ops of units dirtied since the last commit and the digest of the units just written.
+ * An index loaded by tv_load from a file that a sync has claimed is bound to it; a snapshot written by
+ * tv_write is not.  Returns TV_ERR_SYNC_FOREIGN_FILE when the bound file carries another identity or a commit
+ * this index did not write, TV_ERR_IO when the file cannot be written (the binding is dropped: the next sync
+ * rewrites the file whole), TV_ERR_DIM_NOT_SET for a lazy index. */
+int tv_sync(tv_index *h, const char *path);
+/* The binding tv_sync keeps (tests): whether the index is bound to a file, the generation of its last commit,
+ * how many slots ride that commit's header as redo ops, how many committed slots were dirtied since. */
+int tv_sync_state(const tv_index *h, int *bound, uint64_t *generation, size_t *n_pending, size_t *n_fresh);
 
 /* ---- TQ+ calibration: calibrate_2d (lib.rs:2599-2723); on a populated index every stored row is re-encoded from
  * its own codes under the new pair (reencode_stored_rows, lib.rs:2760-2832); tqplus_shift/scale (lib.rs:2535-2545) ---- */

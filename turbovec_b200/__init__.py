@@ -198,6 +198,21 @@ class _Base:
     def write(self, path: str, *, durable: bool = True) -> None:
         self._check(self._lib.tv_write(self._h, str(path).encode()))
 
+    def sync(self, path: str) -> None:
+        """Persist the changes since the last sync to `path` incrementally (`sync`, turbovec-python/src/lib.rs:744,
+        1378): the first sync of a path writes the whole index, later ones only completed blocks, redo records of
+        removals and a commit header.  File errors raise OSError, as the reference's binding does."""
+        rc = self._lib.tv_sync(self._h, str(path).encode())
+        if rc in (30, 95, 96):
+            raise OSError(f"{self._lib.tv_last_error(self._h).decode()}: {path}")
+        self._check(rc)
+
+    def _sync_state(self):
+        """(bound, generation, pending redo slots, dirtied slots) of the sync binding; for tests."""
+        b, g, p, f = C.c_int(), C.c_uint64(), C.c_size_t(), C.c_size_t()
+        self._check(self._lib.tv_sync_state(self._h, C.byref(b), C.byref(g), C.byref(p), C.byref(f)))
+        return bool(b.value), int(g.value), int(p.value), int(f.value)
+
     @classmethod
     def _adopt(cls, handle):
         self = cls.__new__(cls)

@@ -156,6 +156,17 @@ struct tv_index {
     std::vector<uint64_t> slot_to_id;
     std::unordered_map<uint64_t, uint32_t> id_to_slot;
 
+    // binding to the file last synced to or loaded from (lib.rs:364-400)
+    bool sync_bound = false;
+    std::string sync_path;
+    V7Cursor sync_cursor;
+    std::unordered_set<size_t> sync_pending;   // slots whose redo ops ride the committed header
+    std::unordered_set<size_t> sync_fresh;     // committed slots dirtied since that commit
+    uint64_t calib_gen = 0;                    // bumped by every committed calibration
+    void mark_dirty(size_t slot) {             // lib.rs:1575-1579
+        if (sync_bound && slot < size_t(sync_cursor.n_synced) / kBlock * kBlock) sync_fresh.insert(slot);
+    }
+
     ~tv_index() {
         cudaSetDevice(device);
         if (stream) cudaStreamSynchronize(stream);
@@ -1006,6 +1017,8 @@ int tv_swap_remove(tv_index *h, size_t slot, size_t *moved_from) {
     TV_CUDA(cudaGetLastError());
     // no synchronisation: the result is known on the host, and every later call on this handle runs on the
     // same stream, after the move
+    h->mark_dirty(slot);                      // lib.rs:2879-2885: the hole and the moved-from slot diverge
+    if (last != slot) h->mark_dirty(last);
     h->n = last;
     if (moved_from) *moved_from = last;
     return TV_OK;
@@ -1023,6 +1036,8 @@ int tv_remove(tv_index *h, uint64_t id, int *removed) {
     move_lane_kernel<<<(h->ngroups + 255) / 256, 256, 0, h->stream>>>(h->d_codes, h->d_scales, h->ngroups, int64_t(last), int64_t(slot));
     h->launches++;
     TV_CUDA(cudaGetLastError());
+    h->mark_dirty(slot);
+    if (last != slot) h->mark_dirty(last);
     h->n = last;                                                       // enqueued, not awaited (see tv_swap_remove)
     h->id_to_slot.erase(it);
     if (slot != last) {                                                // id_map.rs:557-561
@@ -1066,6 +1081,7 @@ int tv_set_row(tv_index *h, size_t slot, const uint8_t *groups, size_t count, fl
     TV_CUDA(cudaGetLastError());
     TV_CUDA(cudaMemcpyAsync(h->d_scales + slot, &scale, 4, cudaMemcpyHostToDevice, h->stream));
     TV_CUDA(cudaStreamSynchronize(h->stream));
+    h->mark_dirty(slot);
     return TV_OK;
 }
 
@@ -1401,6 +1417,8 @@ int tv_import_packed(tv_index *h, size_t dim, const uint8_t *packed, size_t n, c
         std::unordered_set<uint64_t> seen(ids, ids + n);
         if (seen.size() != n) return fail(h, TV_ERR_PARTS_INVALID, "duplicate ids");
     }
+    h->sync_bound = false;                     // the content is replaced: the next sync rewrites its file whole
+    h->sync_path.clear();
     if (n == 0) { if (h->dim == 0) h->dim = dim; return TV_OK; }
     TV_CUDA(cudaSetDevice(h->device));
     const bool was_lazy = h->dim == 0;
@@ -1470,7 +1488,10 @@ int tv_to_bytes(const tv_index *hc, uint8_t *out, size_t capacity) {
     return TV_OK;
 }
 
-int tv_from_bytes(const uint8_t *data, size_t len, int expect_kind, int device, tv_index **out) {
+namespace {
+// `bind_path` non-null: the image was read from that file, and an index loaded from a file that a sync has
+// claimed stays bound to it, so that its next sync writes only the delta (lib.rs load_v7).
+int index_from_image(const uint8_t *data, size_t len, int expect_kind, int device, tv_index **out, const char *bind_path) {
     tv_index *h = nullptr;
     if (!data || !out) return fail(h, TV_ERR_INVALID_ARGUMENT, "null argument");
     *out = nullptr;
@@ -1513,8 +1534,19 @@ int tv_from_bytes(const uint8_t *data, size_t len, int expect_kind, int device, 
         h->slot_to_id = p.ids;
         for (size_t i = 0; i < p.n; ++i) h->id_to_slot.emplace(p.ids[i], uint32_t(i));
     }
+    if (bind_path && p.nonce != 0) {           // an unclaimed snapshot is loaded unbound: the first sync claims it
+        h->sync_bound = true;
+        h->sync_path = bind_path;
+        h->sync_cursor = V7Cursor{p.gen, uint64_t(p.n), h->calib_gen, p.nonce};
+        h->sync_pending.insert(p.pending_slots.begin(), p.pending_slots.end());
+    }
     *out = h;
     return TV_OK;
+}
+}  // namespace
+
+int tv_from_bytes(const uint8_t *data, size_t len, int expect_kind, int device, tv_index **out) {
+    return index_from_image(data, len, expect_kind, device, out, nullptr);
 }
 
 // Atomic replace: write a temp file beside the destination, fsync it, rename over it (io.rs:14-27).
@@ -1524,15 +1556,8 @@ int tv_write(const tv_index *hc, const char *path) {
     std::vector<uint8_t> img(tv_image_bytes(h));
     int rc = tv_to_bytes(h, img.data(), img.size());
     if (rc != TV_OK) return rc;
-    const std::string tmp = std::string(path) + ".tmp";
-    FILE *f = std::fopen(tmp.c_str(), "wb");
-    if (!f) return fail(h, TV_ERR_INVALID_ARGUMENT, "cannot create " + tmp);
-    const bool ok = std::fwrite(img.data(), 1, img.size(), f) == img.size() && std::fflush(f) == 0;
-    std::fclose(f);
-    if (!ok || std::rename(tmp.c_str(), path) != 0) {
-        std::remove(tmp.c_str());
-        return fail(h, TV_ERR_INVALID_ARGUMENT, std::string("cannot write ") + path);
-    }
+    std::string err;
+    if (!v7_write_file_atomic(path, img.data(), img.size(), err)) return fail(h, TV_ERR_INVALID_ARGUMENT, err);
     return TV_OK;
 }
 
@@ -1548,7 +1573,101 @@ int tv_load(const char *path, int expect_kind, int device, tv_index **out) {
     const bool ok = std::fread(buf.data(), 1, buf.size(), f) == buf.size();
     std::fclose(f);
     if (!ok) return fail(h, TV_ERR_INVALID_ARGUMENT, std::string("cannot read ") + path);
-    return tv_from_bytes(buf.data(), buf.size(), expect_kind, device, out);
+    return index_from_image(buf.data(), buf.size(), expect_kind, device, out, path);
+}
+
+// Incremental persistence (lib.rs sync :1737, sync_v7_impl :1813-1955).
+int tv_sync(tv_index *h, const char *path) {
+    if (!h || !path) return TV_ERR_INVALID_ARGUMENT;
+    std::lock_guard<std::mutex> lock(h->mu);
+    if (h->dim == 0) return fail(h, TV_ERR_DIM_NOT_SET, "cannot sync a lazy index that has never seen an add or calibrate");
+    int rc = ensure_tables(h);
+    if (rc != TV_OK) return rc;
+    TV_CUDA(cudaSetDevice(h->device));
+    const size_t rb = size_t(h->ngroups);
+    V7SyncSource src;
+    src.kind = h->kind; src.bits = h->bits; src.dim = h->dim; src.n = h->n; src.n_calib = h->shift.size();
+    src.ids = h->kind == TV_KIND_IDMAP ? h->slot_to_id.data() : nullptr;
+
+    // The identity check runs whenever this index is bound to the path, also when a calibration has queued
+    // a compaction: a rewrite over a file that another writer has taken over would destroy its commits.
+    const bool bound = h->sync_bound && h->sync_path == path;
+    V7CursorState state = V7_CURSOR_REPLACED;
+    size_t stale_used = 0;
+    std::string err;
+    if (bound) {
+        state = v7_cursor_state(path, h->sync_cursor, src, stale_used, err);
+        if (state == V7_CURSOR_IO_ERROR) return fail(h, TV_ERR_IO, err);
+        if (state == V7_CURSOR_FOREIGN)
+            return fail(h, TV_ERR_SYNC_FOREIGN_FILE, std::string("the v7 file at ") + path + " no longer matches this index's last sync "
+                        "(another writer advanced or replaced it); load the file to adopt its state, or choose a different path");
+    }
+    const bool incremental = bound && state == V7_CURSOR_INTACT && h->sync_cursor.calib_gen == h->calib_gen;
+    auto unbind = [&]() {                      // a failed sync may have landed bytes: the next one rewrites whole
+        h->sync_bound = false;
+        h->sync_path.clear();
+    };
+
+    V7SyncPlan plan;
+    if (incremental && v7_plan_sync(src, h->sync_cursor, h->sync_pending, h->sync_fresh, plan)) {
+        // fetch the blocks the plan reads: runs of consecutive blocks, one copy each
+        const std::vector<size_t> &need = plan.blocks_needed;
+        std::vector<uint8_t> codes(need.size() * rb * kBlock);
+        std::vector<float> scales(need.size() * kBlock, 0.0f);
+        for (size_t i = 0; i < need.size();) {
+            size_t j = i + 1;
+            while (j < need.size() && need[j] == need[j - 1] + 1) ++j;
+            const size_t first = need[i], rows_end = std::min(h->n, (need[j - 1] + 1) * kBlock);
+            TV_CUDA(cudaMemcpyAsync(codes.data() + i * rb * kBlock, h->d_codes + first * rb * kBlock, (j - i) * rb * kBlock,
+                                    cudaMemcpyDeviceToHost, h->stream));
+            if (rows_end > first * kBlock)
+                TV_CUDA(cudaMemcpyAsync(scales.data() + i * kBlock, h->d_scales + first * kBlock, (rows_end - first * kBlock) * 4,
+                                        cudaMemcpyDeviceToHost, h->stream));
+            i = j;
+        }
+        TV_CUDA(cudaStreamSynchronize(h->stream));
+        src.block = [&](size_t block, const uint8_t *&c, const float *&sc) {
+            const size_t i = size_t(std::lower_bound(need.begin(), need.end(), block) - need.begin());
+            c = codes.data() + i * rb * kBlock;
+            sc = scales.data() + i * kBlock;
+        };
+        std::vector<V7Batch> batches;
+        v7_build_sync(src, h->sync_cursor, plan, stale_used, batches);
+        if (!v7_run_sync(path, batches, err)) { unbind(); return fail(h, TV_ERR_IO, err); }
+        h->sync_cursor.gen += 1;
+        h->sync_cursor.n_synced = h->n;
+        h->sync_pending.clear();
+        h->sync_pending.insert(plan.carried.begin(), plan.carried.end());
+        h->sync_fresh.clear();
+        return TV_OK;
+    }
+
+    // First sync of this path, another path than last time, a refit since the last commit, a file that was
+    // replaced, or more removals than one header can carry: the whole index as a fresh container, claimed
+    // with a new file identity (io_v7.rs write_full :961-1032).
+    V7Parts p;
+    rc = gather_parts(h, p);
+    if (rc != TV_OK) return rc;
+    p.nonce = v7_fresh_nonce();
+    std::vector<uint8_t> img;
+    v7_write_image(p, img);
+    if (!v7_write_file_atomic(path, img.data(), img.size(), err)) { unbind(); return fail(h, TV_ERR_IO, err); }
+    h->sync_bound = true;
+    h->sync_path = path;
+    h->sync_cursor = V7Cursor{0, uint64_t(h->n), h->calib_gen, p.nonce};
+    h->sync_pending.clear();
+    h->sync_fresh.clear();
+    return TV_OK;
+}
+
+// Introspection of the sync binding (tests): bound flag, generation and the sizes of the two dirty sets.
+int tv_sync_state(const tv_index *h, int *bound, uint64_t *generation, size_t *n_pending, size_t *n_fresh) {
+    if (!h) return TV_ERR_INVALID_ARGUMENT;
+    if (bound) *bound = h->sync_bound ? 1 : 0;
+    if (generation) *generation = h->sync_cursor.gen;
+    if (n_pending) *n_pending = h->sync_pending.size();
+    if (n_fresh) *n_fresh = h->sync_fresh.size();
+    return TV_OK;
 }
 
 int tv_codebook(tv_index *h, float *boundaries_out, float *centroids_out) {
@@ -1604,6 +1723,7 @@ int tv_set_calibration(tv_index *h, size_t dim, const float *shift, const float 
     h->dim = dim;
     h->shift.assign(shift, shift + dim);
     h->scale_tq.assign(scale, scale + dim);
+    h->calib_gen++;
     rc = ensure_tables(h);
     if (rc != TV_OK) return rc;
     return upload_calibration(h);
@@ -1708,6 +1828,7 @@ int tv_calibrate(tv_index *h, const float *sample, size_t n, size_t dim) {
     }
     h->shift = shift;
     h->scale_tq = scale;
+    h->calib_gen++;                            // a refit rewrites every stored code: the next sync compacts
     return upload_calibration(h);
 }
 

@@ -1,7 +1,16 @@
 #include "io_v7.hpp"
 
+#include <algorithm>
+#include <cerrno>
+#include <chrono>
 #include <cmath>
+#include <cstdio>
 #include <cstring>
+#include <random>
+
+#include <fcntl.h>
+#include <sys/stat.h>
+#include <unistd.h>
 
 namespace tv {
 namespace {
@@ -117,7 +126,7 @@ void v7_write_image(const V7Parts &p, std::vector<uint8_t> &out) {
     out.push_back(uint8_t(p.bits));
     out.push_back(uint8_t(p.kind));
     put<uint32_t>(out, uint32_t(p.dim));
-    put<uint64_t>(out, 0);                                   // unclaimed snapshot
+    put<uint64_t>(out, p.nonce);                             // 0 = unclaimed snapshot
     put<uint32_t>(out, uint32_t(kMaxOps));
     for (float v : p.boundaries) put<float>(out, v);
     for (float v : p.centroids) put<float>(out, v);
@@ -160,22 +169,20 @@ void v7_write_image(const V7Parts &p, std::vector<uint8_t> &out) {
 namespace {
 struct ParsedHeader {
     uint64_t gen = 0;
-    size_t n = 0, tail_at = 0;
+    size_t n = 0, tail_at = 0, used = 0;
     std::vector<std::pair<size_t, size_t>> ops;              // (slot, offset of codes in the file)
     std::vector<size_t> delta_units;
     uint32_t delta_crc = 0;
 };
 
-bool parse_header(const uint8_t *d, size_t len, const Geo &g, size_t slot, ParsedHeader &h) {
-    const size_t at = g.hdr_at(slot);
-    if (at + g.hdr_len() > len) return false;
-    const uint8_t *b = d + at;
-    const size_t cap = g.hdr_len();
+// Structure and checksum of one header slot (io_v7.rs parse_header_at).  `b` points at the slot's bytes, of
+// which `cap` are present; `at` is the slot's file offset and `file_len` the length the units must fit in.
+bool parse_header_bytes(const uint8_t *b, size_t cap, size_t at, const Geo &g, size_t slot, size_t file_len, ParsedHeader &h) {
     uint64_t gen, n64;
     if (!get(b, cap, 0, gen) || !get(b, cap, 8, n64)) return false;
     if (gen % 2 != slot) return false;
     const size_t n = size_t(n64);
-    if (g.unit_at(n / kBlk) > len) return false;
+    if (n / kBlk > (SIZE_MAX - g.unit_at(0)) / g.unit_len() || g.unit_at(n / kBlk) > file_len) return false;
     const size_t tail_row = g.row_bytes() + 4 + g.id_bytes(1);
     size_t p = 16 + (n % kBlk) * tail_row;
     uint32_t n_groups;
@@ -208,18 +215,33 @@ bool parse_header(const uint8_t *d, size_t len, const Geo &g, size_t slot, Parse
     if (!get(b, cap, p, from) || !get(b, cap, p + 4, to) || !get(b, cap, p + 8, h.delta_crc)) return false;
     p += 12;
     if (!get(b, cap, p, stored) || crc32c_split(b, p) != stored) return false;
+    if (to > from && size_t(to - from) > file_len / g.unit_len() + 1) return false;   // cannot all be in the file
     for (uint32_t u = from; u < to; ++u) h.delta_units.push_back(u);
-    h.gen = gen; h.n = n; h.tail_at = at + 16;
-    // delta check: the units this commit wrote are on disk as it wrote them (io_v7.rs:843-858)
+    h.gen = gen; h.n = n; h.tail_at = at + 16; h.used = p + 4;
+    return true;
+}
+
+// The delta check: the units this commit wrote are in the file as it wrote them (io_v7.rs delta_verified).
+// `unit(u)` returns the unit's bytes or null when they are not there.
+template <typename F>
+bool delta_verified(const ParsedHeader &h, const Geo &g, F &&unit) {
     PieceDigest dg(8 + h.delta_units.size() * (4 + g.unit_len()));
-    dg.push(reinterpret_cast<const uint8_t *>(&gen), 8);
+    dg.push(reinterpret_cast<const uint8_t *>(&h.gen), 8);
     for (size_t u : h.delta_units) {
-        if (g.unit_at(u + 1) > len) return false;
+        const uint8_t *bytes = unit(u);
+        if (!bytes) return false;
         const uint32_t u32 = uint32_t(u);
         dg.push(reinterpret_cast<const uint8_t *>(&u32), 4);
-        dg.push(d + g.unit_at(u), g.unit_len());
+        dg.push(bytes, g.unit_len());
     }
     return dg.finish() == h.delta_crc;
+}
+
+bool parse_header(const uint8_t *d, size_t len, const Geo &g, size_t slot, ParsedHeader &h) {
+    const size_t at = g.hdr_at(slot);
+    if (at + g.hdr_len() > len) return false;
+    if (!parse_header_bytes(d + at, g.hdr_len(), at, g, slot, len, h)) return false;
+    return delta_verified(h, g, [&](size_t u) -> const uint8_t * { return g.unit_at(u + 1) <= len ? d + g.unit_at(u) : nullptr; });
 }
 }  // namespace
 
@@ -261,6 +283,10 @@ bool v7_read_image(const uint8_t *d, size_t len, V7Parts &out, std::string &erro
     const ParsedHeader &hd = (ok0 && ok1) ? (h[0].gen > h[1].gen ? h[0] : h[1]) : (ok0 ? h[0] : h[1]);
     const size_t n = hd.n, rb = dim ? g.row_bytes() : 0, n_full = n / kBlk;
     out.n = n;
+    out.gen = hd.gen;
+    std::memcpy(&out.nonce, d + 11, 8);
+    out.pending_slots.clear();
+    for (const auto &op : hd.ops) out.pending_slots.push_back(op.first);
     out.blocked.assign(((n + kBlk - 1) / kBlk) * rb * kBlk, 0);
     out.scales.assign(n, 0.f);
     out.ids.assign(out.kind == 1 ? n : 0, 0);
@@ -281,6 +307,256 @@ bool v7_read_image(const uint8_t *d, size_t len, V7Parts &out, std::string &erro
     for (const auto &op : hd.ops) place_row(op.first, d + op.second);   // pending redo writes (io_v7.rs:64-69)
     for (size_t i = 0; i < n; ++i)
         if (!std::isfinite(out.scales[i]) || !(out.scales[i] >= 0.f) || out.scales[i] > 1e22f) { error = "stored scale " + std::to_string(i) + " invalid"; return false; }
+    return true;
+}
+
+
+// ---- incremental sync ----
+
+namespace {
+Geo geo_of(const V7SyncSource &src) { return Geo{src.kind, src.bits, src.dim, src.n_calib}; }
+
+// codes | scale | id of one slot, as a tail row or a redo op carries them (io_v7.rs header_slot :560-583)
+void put_row(std::vector<uint8_t> &out, const V7SyncSource &src, const Geo &g, size_t slot) {
+    const uint8_t *codes;
+    const float *scales;
+    src.block(slot / kBlk, codes, scales);
+    const size_t rb = g.row_bytes(), lane = slot % kBlk;
+    for (size_t gi = 0; gi < rb; ++gi) out.push_back(codes[gi * kBlk + lane]);
+    put<float>(out, scales[lane]);
+    if (src.kind == 1) put<uint64_t>(out, src.ids[slot]);
+}
+}  // namespace
+
+bool v7_plan_sync(const V7SyncSource &src, const V7Cursor &cursor, const std::unordered_set<size_t> &pending,
+                  const std::unordered_set<size_t> &fresh, V7SyncPlan &plan) {
+    const size_t old_blocks = size_t(cursor.n_synced) / kBlk, new_blocks = src.n / kBlk;
+    const size_t live_rows = (old_blocks < new_blocks ? old_blocks : new_blocks) * kBlk;
+    // Ops matter only for units committed under both states; a unit dirtied since the commit is never
+    // touched on disk, all its ops (old and new) ride the new header instead.
+    std::unordered_set<size_t> fresh_units;
+    for (size_t s : fresh) if (s < live_rows) fresh_units.insert(s / kBlk);
+    plan = V7SyncPlan();
+    for (size_t s : pending)
+        if (s < live_rows && !fresh_units.count(s / kBlk)) plan.materialise.push_back(s / kBlk);
+    std::sort(plan.materialise.begin(), plan.materialise.end());
+    plan.materialise.erase(std::unique(plan.materialise.begin(), plan.materialise.end()), plan.materialise.end());
+    for (size_t s : pending) if (s < live_rows && fresh_units.count(s / kBlk)) plan.carried.push_back(s);
+    for (size_t s : fresh) if (s < live_rows) plan.carried.push_back(s);
+    std::sort(plan.carried.begin(), plan.carried.end());
+    plan.carried.erase(std::unique(plan.carried.begin(), plan.carried.end()), plan.carried.end());
+    if (plan.carried.size() > kMaxOps) return false;
+    for (size_t s : plan.carried) {
+        if (plan.groups.empty() || plan.groups.back().first != s / kBlk) plan.groups.push_back({s / kBlk, {}});
+        plan.groups.back().second.push_back(s);
+    }
+    plan.append_from = old_blocks;
+    plan.append_to = new_blocks;            // below append_from after a shrink: an empty range, written as it is
+    plan.blocks_needed = plan.materialise;
+    for (size_t b = plan.append_from; b < plan.append_to; ++b) plan.blocks_needed.push_back(b);
+    for (const auto &grp : plan.groups) plan.blocks_needed.push_back(grp.first);
+    if (src.n % kBlk) plan.blocks_needed.push_back(src.n / kBlk);
+    std::sort(plan.blocks_needed.begin(), plan.blocks_needed.end());
+    plan.blocks_needed.erase(std::unique(plan.blocks_needed.begin(), plan.blocks_needed.end()), plan.blocks_needed.end());
+    return true;
+}
+
+void v7_build_sync(const V7SyncSource &src, const V7Cursor &cursor, const V7SyncPlan &plan, size_t clear_used,
+                   std::vector<V7Batch> &batches) {
+    const Geo g = geo_of(src);
+    const uint64_t gen = cursor.gen + 1;
+    const size_t rb = g.row_bytes();
+    // One batch, one fsync: the header's delta descriptor names every unit written here and the digest of
+    // their bytes, so a commit that reaches the disk before its data is detected at load.
+    const size_t n_written = plan.materialise.size() + (plan.append_to > plan.append_from ? plan.append_to - plan.append_from : 0);
+    PieceDigest digest(8 + n_written * (4 + g.unit_len()));
+    digest.push(reinterpret_cast<const uint8_t *>(&gen), 8);
+    V7Batch batch;
+    auto write_unit = [&](size_t b) {
+        const uint8_t *codes;
+        const float *scales;
+        src.block(b, codes, scales);
+        V7Write w;
+        w.offset = g.unit_at(b);
+        w.bytes.reserve(g.unit_len());
+        w.bytes.insert(w.bytes.end(), codes, codes + rb * kBlk);
+        for (size_t l = 0; l < kBlk; ++l) put<float>(w.bytes, scales[l]);
+        if (src.kind == 1)
+            for (size_t l = 0; l < kBlk; ++l) put<uint64_t>(w.bytes, src.ids[b * kBlk + l]);
+        const uint32_t b32 = uint32_t(b);
+        digest.push(reinterpret_cast<const uint8_t *>(&b32), 4);
+        digest.push(w.bytes.data(), w.bytes.size());
+        batch.push_back(std::move(w));
+    };
+    for (size_t b : plan.materialise) write_unit(b);
+    for (size_t b = plan.append_from; b < plan.append_to; ++b) write_unit(b);
+    const uint32_t delta_crc = digest.finish();
+
+    // The commit: generation g lives in slot g % 2, so this only ever overwrites the slot of generation g - 1.
+    const size_t slot = size_t(gen % 2);
+    V7Write hdr;
+    hdr.offset = g.hdr_at(slot);
+    std::vector<uint8_t> &h = hdr.bytes;
+    put<uint64_t>(h, gen);
+    put<uint64_t>(h, uint64_t(src.n));
+    for (size_t r = src.n - src.n % kBlk; r < src.n; ++r) put_row(h, src, g, r);
+    put<uint32_t>(h, uint32_t(plan.groups.size()));
+    for (const auto &grp : plan.groups) {
+        put<uint32_t>(h, uint32_t(grp.first));
+        h.push_back(uint8_t(grp.second.size()));
+        for (size_t s : grp.second) {
+            h.push_back(uint8_t(s % kBlk));
+            put_row(h, src, g, s);
+        }
+    }
+    put<uint32_t>(h, uint32_t(plan.materialise.size()));
+    for (size_t b : plan.materialise) put<uint32_t>(h, uint32_t(b));
+    put<uint32_t>(h, uint32_t(plan.append_from));
+    put<uint32_t>(h, uint32_t(plan.append_to));
+    put<uint32_t>(h, delta_crc);
+    put<uint32_t>(h, crc32c_split(h.data(), h.size()));
+    batch.push_back(std::move(hdr));
+
+    batches.clear();
+    if (clear_used) {
+        // A rejected header of this generation still sits in the slot: wipe all it occupies behind a barrier
+        // of its own, and leave a generation whose parity disagrees with the slot so that the wiped slot is
+        // refused outright (io_v7.rs:775-803).
+        size_t len = clear_used < 8 ? 8 : clear_used;
+        if (len > g.hdr_len()) len = g.hdr_len();
+        V7Write wipe;
+        wipe.offset = g.hdr_at(slot);
+        wipe.bytes.assign(len, 0);
+        const uint64_t wrong = (gen % 2) ^ 1;
+        std::memcpy(wipe.bytes.data(), &wrong, 8);
+        batches.push_back(V7Batch{std::move(wipe)});
+    }
+    batches.push_back(std::move(batch));
+}
+
+namespace {
+bool pwrite_all(int fd, const uint8_t *d, size_t n, uint64_t off) {
+    while (n) {
+        const ssize_t w = ::pwrite(fd, d, n, off_t(off));
+        if (w <= 0) return false;
+        d += w; n -= size_t(w); off += uint64_t(w);
+    }
+    return true;
+}
+bool pread_all(int fd, uint8_t *d, size_t n, uint64_t off) {
+    while (n) {
+        const ssize_t r = ::pread(fd, d, n, off_t(off));
+        if (r <= 0) return false;
+        d += r; n -= size_t(r); off += uint64_t(r);
+    }
+    return true;
+}
+struct Fd {
+    int fd;
+    ~Fd() { if (fd >= 0) ::close(fd); }
+};
+}  // namespace
+
+bool v7_run_sync(const char *path, const std::vector<V7Batch> &batches, std::string &error) {
+    Fd f{::open(path, O_RDWR)};
+    if (f.fd < 0) { error = std::string("cannot open ") + path; return false; }
+    for (const V7Batch &batch : batches) {
+        for (const V7Write &w : batch)
+            if (!pwrite_all(f.fd, w.bytes.data(), w.bytes.size(), w.offset)) { error = std::string("write to ") + path + " failed"; return false; }
+        if (::fsync(f.fd) != 0) { error = std::string("fsync of ") + path + " failed"; return false; }
+    }
+    return true;
+}
+
+V7CursorState v7_cursor_state(const char *path, const V7Cursor &cursor, const V7SyncSource &geometry, size_t &stale_used,
+                              std::string &error) {
+    stale_used = 0;
+    const Geo g = geo_of(geometry);
+    Fd f{::open(path, O_RDONLY)};
+    if (f.fd < 0) {
+        if (errno == ENOENT) return V7_CURSOR_REPLACED;
+        error = std::string("cannot open ") + path;
+        return V7_CURSOR_IO_ERROR;
+    }
+    struct stat st;
+    if (::fstat(f.fd, &st) != 0) { error = std::string("cannot stat ") + path; return V7_CURSOR_IO_ERROR; }
+    const size_t file_len = size_t(st.st_size);
+    uint8_t head[19];
+    if (file_len < sizeof head || !pread_all(f.fd, head, sizeof head, 0)) return V7_CURSOR_REPLACED;
+    if (std::memcmp(head, kMagic, 4) != 0 || head[4] != kRevision) return V7_CURSOR_REPLACED;
+    uint64_t file_nonce;
+    std::memcpy(&file_nonce, head + 11, 8);
+    if (file_nonce != cursor.nonce) return file_nonce == 0 ? V7_CURSOR_REPLACED : V7_CURSOR_FOREIGN;
+
+    // Both header slots, newest first.
+    std::vector<ParsedHeader> cands;
+    std::vector<uint8_t> buf;
+    for (size_t slot = 0; slot < 2; ++slot) {
+        const size_t at = g.hdr_at(slot);
+        if (at >= file_len) continue;
+        const size_t want = g.hdr_len() < file_len - at ? g.hdr_len() : file_len - at;
+        buf.resize(want);
+        if (!pread_all(f.fd, buf.data(), want, at)) continue;
+        ParsedHeader h;
+        if (parse_header_bytes(buf.data(), want, at, g, slot, file_len, h)) cands.push_back(std::move(h));
+    }
+    std::sort(cands.begin(), cands.end(), [](const ParsedHeader &a, const ParsedHeader &b) { return a.gen > b.gen; });
+    if (!cands.empty() && cands.front().gen == cursor.gen) return V7_CURSOR_INTACT;
+    // A header ahead of the cursor is either a sync of this index that did not finish (its delta fails and
+    // the cursor's own commit is the adoptable one) or another writer's commit.
+    for (const ParsedHeader &h : cands)
+        if (h.gen > cursor.gen && h.used > stale_used) stale_used = h.used;
+    std::vector<uint8_t> unit(g.unit_len());
+    for (const ParsedHeader &h : cands) {
+        const bool ok = delta_verified(h, g, [&](size_t u) -> const uint8_t * {
+            if (g.unit_at(u) + g.unit_len() > file_len) return nullptr;
+            return pread_all(f.fd, unit.data(), unit.size(), g.unit_at(u)) ? unit.data() : nullptr;
+        });
+        if (ok) {
+            if (h.gen == cursor.gen) return V7_CURSOR_INTACT;
+            stale_used = 0;
+            return V7_CURSOR_FOREIGN;
+        }
+    }
+    stale_used = 0;
+    return V7_CURSOR_REPLACED;
+}
+
+uint64_t v7_fresh_nonce() {
+    std::random_device rd;
+    const uint64_t now = uint64_t(std::chrono::steady_clock::now().time_since_epoch().count());
+    for (;;) {
+        const uint64_t n = ((uint64_t(rd()) << 32) | rd()) ^ (now * 0x9E3779B97F4A7C15ull);
+        if (n != 0) return n;                                  // zero marks a snapshot nobody syncs to
+    }
+}
+
+bool v7_write_file_atomic(const char *path, const uint8_t *data, size_t len, std::string &error) {
+    std::random_device rd;
+    std::string tmp;
+    int fd = -1;
+    for (int attempt = 0; attempt < 8 && fd < 0; ++attempt) {
+        char suffix[64];
+        std::snprintf(suffix, sizeof suffix, ".tmp.%ld.%d.%08x", long(::getpid()), attempt, unsigned(rd()));
+        tmp = std::string(path) + suffix;
+        fd = ::open(tmp.c_str(), O_WRONLY | O_CREAT | O_EXCL, 0644);
+        if (fd < 0 && errno != EEXIST) break;
+    }
+    if (fd < 0) { error = "cannot create a temporary file beside " + std::string(path); return false; }
+    bool ok = pwrite_all(fd, data, len, 0) && ::fsync(fd) == 0;
+    ok = (::close(fd) == 0) && ok;
+    if (ok && std::rename(tmp.c_str(), path) != 0) ok = false;
+    if (!ok) {
+        std::remove(tmp.c_str());
+        error = std::string("cannot write ") + path;
+        return false;
+    }
+    // the rename itself is durable once the directory entry is (io.rs sync_parent_dir_after_commit)
+    std::string dir(path);
+    const size_t cut = dir.find_last_of('/');
+    dir = cut == std::string::npos ? "." : (cut == 0 ? "/" : dir.substr(0, cut));
+    const int dfd = ::open(dir.c_str(), O_RDONLY | O_DIRECTORY);
+    if (dfd >= 0) { ::fsync(dfd); ::close(dfd); }
     return true;
 }
 
