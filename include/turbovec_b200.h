@@ -239,6 +239,14 @@ int tv_sync(tv_index *h, const char *path);
 /* The binding tv_sync keeps (tests): whether the index is bound to a file, the generation of its last commit,
  * how many slots ride that commit's header as redo ops, how many committed slots were dirtied since. */
 int tv_sync_state(const tv_index *h, int *bound, uint64_t *generation, size_t *n_pending, size_t *n_fresh);
+/* The planner of an incremental sync on plain arrays, host only (tests; io_v7.rs plan_incremental :674-735):
+ * from the rows of the last commit, the live row count, the slots whose redo ops ride the committed header and
+ * the committed slots dirtied since, the units to write into place and the slots the new header carries (both
+ * ascending; the arrays' capacities come in through *n_materialise / *n_carried) and the appended unit range.
+ * TV_ERR_UNSUPPORTED when more than 1,024 slots would be carried (the caller rewrites the file whole). */
+int tv_v7_plan_sync(size_t n_synced, size_t n, const size_t *pending, size_t n_pending, const size_t *fresh,
+                    size_t n_fresh, size_t *materialise_out, size_t *n_materialise, size_t *carried_out,
+                    size_t *n_carried, size_t *append_from, size_t *append_to);
 
 /* ---- TQ+ calibration: calibrate_2d (lib.rs:2599-2723); on a populated index every stored row is re-encoded from
  * its own codes under the new pair (reencode_stored_rows, lib.rs:2760-2832); tqplus_shift/scale (lib.rs:2535-2545) ---- */

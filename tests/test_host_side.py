@@ -154,3 +154,37 @@ def test_exchange_layout_is_conflict_free(lib, dim):
     store_plain, gather_plain, store_layout, gather_layout = [x.value for x in v]
     assert store_plain == 1 and gather_plain >= 2      # plain rows: contiguous stores, random gathers
     assert store_layout == 1 and gather_layout == 1
+
+
+def test_sync_planner_matches_a_restatement():
+    """`plan_incremental` (io_v7.rs:674-735) restated with Python sets against the library's planner."""
+    import ctypes as C
+    from turbovec_b200 import _native
+    lib = _native.load()
+    rng = np.random.default_rng(5)
+
+    def plan(n_synced, n, pending, fresh):
+        pa, fa = np.array(sorted(pending), np.uint64), np.array(sorted(fresh), np.uint64)
+        mat, car = np.zeros(4096, np.uint64), np.zeros(4096, np.uint64)
+        nm, nc, a0, a1 = C.c_size_t(mat.size), C.c_size_t(car.size), C.c_size_t(), C.c_size_t()
+        rc = lib.tv_v7_plan_sync(n_synced, n, pa.ctypes.data, pa.size, fa.ctypes.data, fa.size, mat.ctypes.data, C.byref(nm),
+                                 car.ctypes.data, C.byref(nc), C.byref(a0), C.byref(a1))
+        if rc != 0:
+            return rc
+        return list(map(int, mat[: nm.value])), list(map(int, car[: nc.value])), a0.value, a1.value
+
+    for case in range(300):
+        n_synced = int(rng.integers(0, 2000))
+        n = int(rng.integers(0, 2000))
+        watermark = n_synced // 32 * 32
+        pending = set(map(int, rng.integers(0, max(1, watermark), int(rng.integers(0, 40))))) if watermark else set()
+        fresh = set(map(int, rng.integers(0, max(1, watermark), int(rng.integers(0, 40))))) if watermark else set()
+        live = min(n_synced // 32, n // 32) * 32
+        fresh_units = {s // 32 for s in fresh if s < live}
+        want_mat = sorted({s // 32 for s in pending if s < live and s // 32 not in fresh_units})
+        want_car = sorted({s for s in pending | fresh if s < live and s // 32 in fresh_units})
+        assert plan(n_synced, n, pending, fresh) == (want_mat, want_car, n_synced // 32, n // 32), case
+    # one header carries at most 1,024 redo ops
+    many = set(range(0, 4000, 3))
+    assert len(many) > 1024 and plan(4096, 4096, set(), many) == 93
+    assert plan(4096, 4096, set(), set(list(many)[:1024]))[1] == sorted(list(many)[:1024])

@@ -62,6 +62,8 @@ SIGNATURES = {
     "tv_write": (C.c_int, [_H, C.c_char_p]),
     "tv_load": (C.c_int, [C.c_char_p, C.c_int, C.c_int, C.POINTER(_H)]),
     "tv_sync": (C.c_int, [_H, C.c_char_p]),
+    "tv_v7_plan_sync": (C.c_int, [C.c_size_t, C.c_size_t, C.c_void_p, C.c_size_t, C.c_void_p, C.c_size_t, C.c_void_p,
+                                 C.POINTER(C.c_size_t), C.c_void_p, C.POINTER(C.c_size_t), C.POINTER(C.c_size_t), C.POINTER(C.c_size_t)]),
     "tv_sync_state": (C.c_int, [_H, C.POINTER(C.c_int), C.POINTER(C.c_uint64), C.POINTER(C.c_size_t), C.POINTER(C.c_size_t)]),
     "tv_codebook": (C.c_int, [_H, C.c_void_p, C.c_void_p]),
     "tv_rotate": (C.c_int, [_H, C.c_void_p, C.c_size_t, C.c_size_t, C.c_void_p]),

@@ -1660,6 +1660,29 @@ int tv_sync(tv_index *h, const char *path) {
     return TV_OK;
 }
 
+// The planner of an incremental sync on plain arrays (host only; tests).  Outputs: units written into place,
+// slots carried by the new header; returns TV_ERR_UNSUPPORTED when the carried ops exceed one header.
+int tv_v7_plan_sync(size_t n_synced, size_t n, const size_t *pending, size_t n_pending, const size_t *fresh, size_t n_fresh,
+                    size_t *materialise_out, size_t *n_materialise, size_t *carried_out, size_t *n_carried,
+                    size_t *append_from, size_t *append_to) {
+    if (!n_materialise || !n_carried || (n_pending && !pending) || (n_fresh && !fresh)) return TV_ERR_INVALID_ARGUMENT;
+    V7SyncSource src;
+    src.n = n;
+    V7Cursor cursor;
+    cursor.n_synced = n_synced;
+    V7SyncPlan plan;
+    const std::unordered_set<size_t> ps(pending, pending + n_pending), fs(fresh, fresh + n_fresh);
+    if (!v7_plan_sync(src, cursor, ps, fs, plan)) return TV_ERR_UNSUPPORTED;
+    if (plan.materialise.size() > *n_materialise || plan.carried.size() > *n_carried) return TV_ERR_INVALID_ARGUMENT;
+    std::copy(plan.materialise.begin(), plan.materialise.end(), materialise_out);
+    std::copy(plan.carried.begin(), plan.carried.end(), carried_out);
+    *n_materialise = plan.materialise.size();
+    *n_carried = plan.carried.size();
+    if (append_from) *append_from = plan.append_from;
+    if (append_to) *append_to = plan.append_to;
+    return TV_OK;
+}
+
 // Introspection of the sync binding (tests): bound flag, generation and the sizes of the two dirty sets.
 int tv_sync_state(const tv_index *h, int *bound, uint64_t *generation, size_t *n_pending, size_t *n_fresh) {
     if (!h) return TV_ERR_INVALID_ARGUMENT;
