@@ -731,3 +731,32 @@ def test_chunk_size_keyword_gives_the_unsliced_results(T):
     with pytest.raises(ValueError, match="already present"):
         m.add_with_ids(x[:600], ids[:600].copy(), chunk_size=100)
     assert len(m) == n
+
+
+def test_concurrent_searches_from_host_threads(T):
+    """`search(&self)` is concurrent-safe in the reference (lib.rs:22-52, tests/concurrent_search.rs): searches
+    issued from several host threads on one handle return what the same searches return one after another."""
+    import threading
+    dim, n = 256, 20_000
+    idx = T.TurboQuantIndex(dim, 4)
+    idx.add(anisotropic(n, dim, seed=71))
+    batches = [anisotropic(b, dim, seed=72, offset=100 * j) for j, b in enumerate([1, 7, 40, 300, 3, 64, 1, 130])]
+    want = [idx.search(q, 10) for q in batches]
+    got = [None] * len(batches)
+    errors = []
+
+    def work(j):
+        try:
+            for _ in range(5):
+                got[j] = idx.search(batches[j], 10)
+        except Exception as e:            # noqa: BLE001 - reported below
+            errors.append(e)
+
+    threads = [threading.Thread(target=work, args=(j,)) for j in range(len(batches))]
+    for t in threads:
+        t.start()
+    for t in threads:
+        t.join()
+    assert not errors
+    for (s0, i0), (s1, i1) in zip(want, got):
+        assert np.array_equal(i0, i1) and np.array_equal(s0, s1)

@@ -494,3 +494,16 @@ def test_every_sampled_tear_recovers_the_old_or_the_new_commit(T, tmp_path):
                 back = T.IdMapIndex.load(str(torn_path))
                 assert len(back) == want["n"] and np.array_equal(back.ids(), want["ids"])
                 assert np.array_equal(np.asarray(back.scales()), want["scales"])
+
+
+def test_sync_errors_name_the_path(T, tmp_path):
+    """turbovec-python/tests/test_sync.py:67-80"""
+    idx = fresh_index(T, calib_seed=10)
+    idx.add(anisotropic(8, DIM, seed=11))
+    missing = str(tmp_path / "no-such-dir" / "index.tv")
+    with pytest.raises(OSError) as exc:
+        idx.sync(missing)
+    assert "no-such-dir" in str(exc.value)
+    assert idx._sync_state()[0] is False
+    with pytest.raises(OSError):
+        T.TurboQuantIndex(bit_width=4).sync(str(tmp_path / "never-written.tv"))
