@@ -128,6 +128,8 @@ int tv_add_with_ids(tv_index *h, const float *vectors, size_t n, size_t dim, con
 /* Same as tv_add but `vectors` is device memory on the handle's device.  The finite/|x|<1e16 check of
  * encode.rs:58-74 runs on the device.  Used when the producer already lives on the GPU. */
 int tv_add_device(tv_index *h, const float *vectors_device, size_t n, size_t dim);
+/* tv_add_with_ids with the rows in device memory; `ids` stays a host array (ids never reach the device). */
+int tv_add_with_ids_device(tv_index *h, const float *vectors_device, size_t n, size_t dim, const uint64_t *ids);
 
 /* ---- removal: swap_remove (lib.rs:2864-3028), IdMapIndex::remove (id_map.rs:520-567) ----
  * Both return once the move of the last row into the freed slot is enqueued on the handle's stream; every

@@ -760,3 +760,20 @@ def test_concurrent_searches_from_host_threads(T):
     assert not errors
     for (s0, i0), (s1, i1) in zip(want, got):
         assert np.array_equal(i0, i1) and np.array_equal(s0, s1)
+
+
+def test_add_with_ids_from_device_memory(T):
+    """Rows that already live on the GPU enter an id-mapped index exactly as host rows do."""
+    import torch
+    dim, n = 384, 5000
+    x = anisotropic(n, dim, seed=81)
+    ids = (np.arange(n, dtype=np.uint64) * 5 + 77)
+    a, b = T.IdMapIndex(dim, 4), T.IdMapIndex(dim, 4)
+    a.add_with_ids(x, ids)
+    xd = torch.from_numpy(x).cuda()
+    b.add_with_ids_device(xd.data_ptr(), 3000, dim, ids[:3000])
+    b.add_with_ids_device(xd[3000:].contiguous().data_ptr(), n - 3000, dim, ids[3000:])
+    assert a.to_bytes() == b.to_bytes()
+    with pytest.raises(ValueError, match="already present"):
+        b.add_with_ids_device(xd.data_ptr(), 1, dim, ids[:1])
+    assert len(b) == n

@@ -385,6 +385,13 @@ class IdMapIndex(_Base):
             return
         self._check(self._lib.tv_add_with_ids(self._h, _ptr(vectors), vectors.shape[0], vectors.shape[1], _ptr(ids)))
 
+    def add_with_ids_device(self, device_ptr: int, n: int, dim: int, ids: np.ndarray) -> None:
+        """Adds n rows that already sit in device memory (row-major float32 at `device_ptr`) under host `ids`."""
+        ids = _typed_1d("ids", ids, np.uint64, "uint64")
+        if ids.size != n:
+            raise ValueError(f"ids length {ids.size} does not match number of vectors {n}")
+        self._check(self._lib.tv_add_with_ids_device(self._h, C.c_void_p(device_ptr), n, dim, _ptr(ids)))
+
     def remove(self, id) -> bool:
         if isinstance(id, bool) or not isinstance(id, (int, np.integer)):
             raise TypeError(f"id must be an int, got {type(id).__name__}")

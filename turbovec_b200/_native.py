@@ -36,6 +36,7 @@ SIGNATURES = {
     "tv_add": (C.c_int, [_H, C.c_void_p, C.c_size_t, C.c_size_t]),
     "tv_add_with_ids": (C.c_int, [_H, C.c_void_p, C.c_size_t, C.c_size_t, C.c_void_p]),
     "tv_add_device": (C.c_int, [_H, C.c_void_p, C.c_size_t, C.c_size_t]),
+    "tv_add_with_ids_device": (C.c_int, [_H, C.c_void_p, C.c_size_t, C.c_size_t, C.c_void_p]),
     "tv_swap_remove": (C.c_int, [_H, C.c_size_t, _szp]),
     "tv_remove": (C.c_int, [_H, C.c_uint64, _intp]),
     "tv_get_row": (C.c_int, [_H, C.c_size_t, C.c_void_p, C.c_size_t, _f32p]),

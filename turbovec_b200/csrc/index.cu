@@ -978,7 +978,17 @@ int tv_add_device(tv_index *h, const float *vectors_device, size_t n, size_t dim
     return add_rows(h, vectors_device, n, dim, true);
 }
 
+namespace {
+int add_rows_with_ids(tv_index *h, const float *vectors, size_t n, size_t dim, const uint64_t *ids, bool on_device);
+}
 int tv_add_with_ids(tv_index *h, const float *vectors, size_t n, size_t dim, const uint64_t *ids) {
+    return add_rows_with_ids(h, vectors, n, dim, ids, false);
+}
+int tv_add_with_ids_device(tv_index *h, const float *vectors_device, size_t n, size_t dim, const uint64_t *ids) {
+    return add_rows_with_ids(h, vectors_device, n, dim, ids, true);
+}
+namespace {
+int add_rows_with_ids(tv_index *h, const float *vectors, size_t n, size_t dim, const uint64_t *ids, bool on_device) {
     if (!h || (!vectors && n) || (!ids && n)) return TV_ERR_INVALID_ARGUMENT;
     std::lock_guard<std::mutex> lock(h->mu);
     if (h->kind != TV_KIND_IDMAP) return fail(h, TV_ERR_WRONG_INDEX_KIND, "tv_add_with_ids needs an id-mapped index");
@@ -997,13 +1007,14 @@ int tv_add_with_ids(tv_index *h, const float *vectors, size_t n, size_t dim, con
         }
     }
     const size_t base = h->n;
-    int rc = add_rows(h, vectors, n, dim, false);
+    int rc = add_rows(h, vectors, n, dim, on_device);
     if (rc != TV_OK) return rc;
     h->slot_to_id.insert(h->slot_to_id.end(), ids, ids + n);
     h->id_to_slot.reserve(h->id_to_slot.size() + n);
     for (size_t i = 0; i < n; ++i) h->id_to_slot.emplace(ids[i], uint32_t(base + i));
     return TV_OK;
 }
+}  // namespace
 
 int tv_swap_remove(tv_index *h, size_t slot, size_t *moved_from) {
     if (!h) return TV_ERR_INVALID_ARGUMENT;
