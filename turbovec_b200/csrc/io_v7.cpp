@@ -494,11 +494,18 @@ V7CursorState v7_cursor_state(const char *path, const V7Cursor &cursor, const V7
     for (size_t slot = 0; slot < 2; ++slot) {
         const size_t at = g.hdr_at(slot);
         if (at >= file_len) continue;
-        const size_t want = g.hdr_len() < file_len - at ? g.hdr_len() : file_len - at;
-        buf.resize(want);
-        if (!pread_all(f.fd, buf.data(), want, at)) continue;
-        ParsedHeader h;
-        if (parse_header_bytes(buf.data(), want, at, g, slot, file_len, h)) cands.push_back(std::move(h));
+        // A commit that carries no redo ops uses only a short prefix of its slot: read that much first and the
+        // whole slot only when the parse needs more (io_v7.rs hdr_probe_len :389-397).
+        const size_t avail = file_len - at;
+        const size_t full = g.hdr_len() < avail ? g.hdr_len() : avail;
+        const size_t probe = 16 + 31 * (g.row_bytes() + 4 + g.id_bytes(1)) + 4 + 4 + kMaxOps * 4 + 12 + 4;
+        for (size_t want = probe < full ? probe : full;; want = full) {
+            buf.resize(want);
+            if (!pread_all(f.fd, buf.data(), want, at)) break;
+            ParsedHeader h;
+            if (parse_header_bytes(buf.data(), want, at, g, slot, file_len, h)) { cands.push_back(std::move(h)); break; }
+            if (want >= full) break;
+        }
     }
     std::sort(cands.begin(), cands.end(), [](const ParsedHeader &a, const ParsedHeader &b) { return a.gen > b.gen; });
     if (!cands.empty() && cands.front().gen == cursor.gen) return V7_CURSOR_INTACT;
