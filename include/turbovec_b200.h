@@ -98,8 +98,11 @@ enum {
                                  * -1 (default) = measured switch points: 33 (permute-dot), 8 (u8-LUT families) */
     TV_OPT_FORCE_CAREFUL = 3,   /* 1: run the candidate-overflow recovery schedule always (testing) */
     TV_OPT_TC_TILES = 4,        /* accumulator tiles of 128 vectors per query slab in the tensor-memory scan: 1 or 2 */
-    TV_OPT_INGEST_PIPELINE = 5  /* 1 (default): whole code blocks are encoded by the pipelined ingest kernel; 0: never;
+    TV_OPT_INGEST_PIPELINE = 5, /* 1 (default): whole code blocks are encoded by the pipelined ingest kernel; 0: never;
                                  * 2: pipelined, and every reconstruction sum walks the sequential chains (testing) */
+    TV_OPT_PD_SPLIT = 6         /* 1 (default): batches of up to 32 queries on 4-bit permute-dot indexes look the int8
+                                 * levels up with one byte-permute per four codes and half-table (two exact integer
+                                 * contractions, subtracted); 0: merged lookup, one contraction (testing) */
 };
 
 /* ---- construction: TurboQuantIndex::new / new_lazy (lib.rs:629, 670), IdMapIndex::new (id_map.rs:278) ---- */

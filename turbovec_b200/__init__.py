@@ -11,7 +11,7 @@ import ctypes as C
 import numpy as np
 
 from . import _native
-from ._native import (OPT_FORCE_CAREFUL, OPT_INGEST_PIPELINE, OPT_MMA_MIN_BATCH, OPT_SCORE_MODE, OPT_TC_TILES, SCORE_AUTO, SCORE_LUT_FLUSH,
+from ._native import (OPT_FORCE_CAREFUL, OPT_INGEST_PIPELINE, OPT_MMA_MIN_BATCH, OPT_PD_SPLIT, OPT_SCORE_MODE, OPT_TC_TILES, SCORE_AUTO, SCORE_LUT_FLUSH,
                       SCORE_LUT_MULADD, SCORE_PERMUTE_DOT)
 
 __all__ = ["TurboQuantIndex", "IdMapIndex", "BATCH_CHUNK_SIZE"]

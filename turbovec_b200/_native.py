@@ -102,4 +102,4 @@ OK = 0
 ERR_ID_KEYERROR = {21}
 ERR_INDEXERROR = {31}
 SCORE_AUTO, SCORE_PERMUTE_DOT, SCORE_LUT_MULADD, SCORE_LUT_FLUSH = 0, 1, 2, 3
-OPT_SCORE_MODE, OPT_MMA_MIN_BATCH, OPT_FORCE_CAREFUL, OPT_TC_TILES, OPT_INGEST_PIPELINE = 1, 2, 3, 4, 5
+OPT_SCORE_MODE, OPT_MMA_MIN_BATCH, OPT_FORCE_CAREFUL, OPT_TC_TILES, OPT_INGEST_PIPELINE, OPT_PD_SPLIT = 1, 2, 3, 4, 5, 6

@@ -93,6 +93,7 @@ struct tv_index {
     int score_mode = TV_SCORE_AUTO;
     int64_t mma_min_batch = -1;  // -1: measured switch points (permute-dot 33 queries, u8-LUT 8); 0 never; else as set
     int force_careful = 0;
+    int pd_split = 1;            // 1: the small-batch permute-dot scan uses the split level lookup where the codebook allows it
     int ingest_pipeline = 1;     // 1: whole code blocks of an uncalibrated add go through the pipelined ingest kernel
     int tc_tiles = 1;            // accumulator tiles per B slab in the tcgen05 scan (1 or 2); 1 measured faster
 
@@ -667,6 +668,7 @@ int search_core(tv_index *h, const float *queries, bool queries_on_device, size_
         for (int b = 0; b < 4; ++b) word |= uint32_t(uint8_t(h->levels[4 * w + b])) << (8 * b);
         sp.level_words[w] = word;
     }
+    sp.pd_split = h->pd_split;
 
     auto run_schedule = [&](bool careful) -> int {
         TV_CUDA(cudaMemsetAsync(h->d_cnt.ptr, 0, nq * 4, st));
@@ -948,6 +950,7 @@ int tv_set_option(tv_index *h, int option, int64_t value) {
         case TV_OPT_FORCE_CAREFUL: h->force_careful = value != 0; return TV_OK;
         case TV_OPT_TC_TILES: h->tc_tiles = value == 1 ? 1 : 2; return TV_OK;
         case TV_OPT_INGEST_PIPELINE: h->ingest_pipeline = value < 0 || value > 2 ? 1 : int(value); return TV_OK;
+        case TV_OPT_PD_SPLIT: h->pd_split = value != 0; return TV_OK;
         default: return fail(h, TV_ERR_INVALID_ARGUMENT, "unknown option");
     }
 }
@@ -960,6 +963,7 @@ int64_t tv_get_option(const tv_index *h, int option) {
         case TV_OPT_FORCE_CAREFUL: return h->force_careful;
         case TV_OPT_TC_TILES: return h->tc_tiles;
         case TV_OPT_INGEST_PIPELINE: return h->ingest_pipeline;
+        case TV_OPT_PD_SPLIT: return h->pd_split;
         default: return -1;
     }
 }
@@ -1346,6 +1350,7 @@ int tv_search_device_noalloc(tv_index *h, const float *queries_device, size_t nq
         for (int b = 0; b < 4; ++b) word |= uint32_t(uint8_t(h->levels[4 * w + b])) << (8 * b);
         sp.level_words[w] = word;
     }
+    sp.pd_split = h->pd_split;
     // Chunks never exceed the candidate capacity, so the fixed buffer cannot overflow whatever the data order.
     const size_t n_blocks = (n + kBlock - 1) / kBlock, step = kNoAllocCap / kBlock;
     for (size_t begin = 0; begin < n_blocks; begin += step) {

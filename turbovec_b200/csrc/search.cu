@@ -294,8 +294,39 @@ __device__ __forceinline__ void expand4(uint32_t x, const uint32_t (&T)[4], uint
     b1 = prmt(prmt(T[0], T[1], idx_h), prmt(T[2], T[3], idx_h), pick_h);
 }
 
-template <int MT>
-__global__ void __launch_bounds__((kConsumerWarps + 1) * 32, MT == 1 ? 3 : (MT == 2 ? 2 : 1)) scan_pd_kernel(ScanParams p) {
+// Split lookup for a codebook whose levels 0..7 are <= 0 and 8..15 are >= 0 (every Lloyd-Max codebook of the
+// reference is symmetric).  A packed nibble is a `prmt` selector as it stands: values 0..7 pick a byte of the
+// 8-byte table, values 8..15 ask for the sign of that byte replicated - 0x00 when the table holds
+// non-negative bytes.  So `prmt(Tn, x)` yields -level[c] where c < 8 and 0 elsewhere, `prmt(Tp, x ^ 8..8)`
+// yields level[c] where c >= 8 and 0 elsewhere, with no masking and no merge: S = W.pos - W.neg, both exact
+// int32 contractions.  Five ALU-pipe operations per eight codes against eight in expand4; the second MMA is
+// paid by the tensor pipe, which this scan leaves mostly idle.
+__device__ __forceinline__ void expand4_split(uint32_t x, const uint32_t (&Tp)[2], const uint32_t (&Tn)[2], uint32_t &p0,
+                                              uint32_t &p1, uint32_t &n0, uint32_t &n1) {
+    const uint32_t y = x ^ 0x88888888u;
+    const uint32_t xh = mad_hi(x, 0x10000u, 0u), yh = mad_hi(y, 0x10000u, 0u);   // >> 16 on the FMA pipe
+    n0 = prmt(Tn[0], Tn[1], x);
+    p0 = prmt(Tp[0], Tp[1], y);
+    n1 = prmt(Tn[0], Tn[1], xh);
+    p1 = prmt(Tp[0], Tp[1], yh);
+}
+__host__ __device__ inline uint32_t negate_bytes(uint32_t w) {                   // per-byte two's complement
+    uint32_t r = 0;
+    for (int b = 0; b < 4; ++b) r |= uint32_t(uint8_t(-int(int8_t(w >> (8 * b))))) << (8 * b);
+    return r;
+}
+// whether the level table allows the split lookup
+inline bool levels_split_ok(const uint32_t (&words)[4]) {
+    for (int c = 0; c < 16; ++c) {
+        const int v = int8_t(words[c / 4] >> (8 * (c % 4)));
+        if (c < 8 ? (v > 0 || v == -128) : v < 0) return false;
+    }
+    return true;
+}
+
+template <int MT, bool SPLIT>
+__global__ void __launch_bounds__((kConsumerWarps + 1) * 32, MT == 1 ? 3 : (MT == 2 && !SPLIT ? 2 : 1))
+scan_pd_kernel(ScanParams p) {
     extern __shared__ __align__(128) unsigned char smem_raw[];
     uint8_t *stage_mem = smem_raw;
     __shared__ uint64_t full_bar[kStages], empty_bar[kStages];
@@ -349,6 +380,8 @@ __global__ void __launch_bounds__((kConsumerWarps + 1) * 32, MT == 1 ? 3 : (MT =
     // ---------------- consumers ----------------
     const int quad = lane >> 2, t = lane & 3;
     const uint32_t T[4] = {p.level_words[0], p.level_words[1], p.level_words[2], p.level_words[3]};
+    const uint32_t Tp[2] = {p.level_words[2], p.level_words[3]};
+    const uint32_t Tn[2] = {negate_bytes(p.level_words[0]), negate_bytes(p.level_words[1])};
     const uint4 *wfrag = reinterpret_cast<const uint4 *>(p.wfrag);
     uint32_t it = 0;
     for (uint32_t tile = blockIdx.x; tile < n_tiles; tile += gridDim.x) {
@@ -361,6 +394,13 @@ __global__ void __launch_bounds__((kConsumerWarps + 1) * 32, MT == 1 ? 3 : (MT =
             for (int j = 0; j < 4; ++j)
 #pragma unroll
                 for (int e = 0; e < 4; ++e) acc[m][j][e] = 0;
+        int accn[SPLIT ? MT : 1][4][4];                       // the c < 8 half of the contraction, subtracted at the end
+#pragma unroll
+        for (int m = 0; m < (SPLIT ? MT : 1); ++m)
+#pragma unroll
+            for (int j = 0; j < 4; ++j)
+#pragma unroll
+                for (int e = 0; e < 4; ++e) accn[m][j][e] = 0;
 
         for (int ch = 0; ch < n_chunks; ++ch, ++it) {
             const int s = it % kStages;
@@ -370,8 +410,10 @@ __global__ void __launch_bounds__((kConsumerWarps + 1) * 32, MT == 1 ? 3 : (MT =
                     reinterpret_cast<const uint32_t *>(stage_mem + size_t(s) * kStageBytes + size_t(warp) * kChunkRows * kLanes);
                 const int rows_here = min(kChunkRows, ng - ch * kChunkRows);
                 const int ksteps = (rows_here + 15) / 16;
-#pragma unroll 2
-                for (int ks = 0; ks < ksteps; ++ks) {
+                // query fragments of this chunk's k-steps: one pointer per chunk, constant strides inside
+                const uint4 *wf = wfrag + (size_t(ch) * (kChunkRows / 16) * p.mtiles_total + p.mtile_base) * 32 + lane;
+                const size_t wf_step = size_t(p.mtiles_total) * 32;
+                auto kstep = [&](int ks) {
                     // rows 16ks + t + {0,4,8,12}, word `quad` of each 32-byte row: conflict-free
                     const uint32_t *r0 = rows + (16 * ks + t) * 8 + quad;
                     const uint32_t wa = r0[0], wb = r0[32], wc = r0[64], wd = r0[96];
@@ -380,16 +422,27 @@ __global__ void __launch_bounds__((kConsumerWarps + 1) * 32, MT == 1 ? 3 : (MT =
                     const uint32_t t2 = prmt(wc, wd, 0x5140), t3 = prmt(wc, wd, 0x7362);
                     const uint32_t x[4] = {prmt(t0, t2, 0x5410), prmt(t0, t2, 0x7632), prmt(t1, t3, 0x5410),
                                            prmt(t1, t3, 0x7632)};
-                    uint32_t b0[4], b1[4];
+                    uint32_t b0[4], b1[4], n0[SPLIT ? 4 : 1], n1[SPLIT ? 4 : 1];
 #pragma unroll
-                    for (int j = 0; j < 4; ++j) expand4(x[j], T, b0[j], b1[j]);
-                    const int gks = ch * (kChunkRows / 16) + ks;
+                    for (int j = 0; j < 4; ++j) {
+                        if constexpr (SPLIT) expand4_split(x[j], Tp, Tn, b0[j], b1[j], n0[j], n1[j]);
+                        else expand4(x[j], T, b0[j], b1[j]);
+                    }
 #pragma unroll
                     for (int m = 0; m < MT; ++m) {
-                        const uint4 a = __ldg(&wfrag[(size_t(gks) * p.mtiles_total + p.mtile_base + m) * 32 + lane]);
+                        const uint4 a = __ldg(wf + ks * wf_step + m * 32);
 #pragma unroll
-                        for (int j = 0; j < 4; ++j) mma_s8(acc[m][j], a, b0[j], b1[j]);
+                        for (int j = 0; j < 4; ++j) {
+                            mma_s8(acc[m][j], a, b0[j], b1[j]);
+                            if constexpr (SPLIT) mma_s8(accn[m][j], a, n0[j], n1[j]);
+                        }
                     }
+                };
+                if (ksteps == kChunkRows / 16) {               // a whole chunk: no loop control, constant offsets
+#pragma unroll
+                    for (int ks = 0; ks < kChunkRows / 16; ++ks) kstep(ks);
+                } else {
+                    for (int ks = 0; ks < ksteps; ++ks) kstep(ks);
                 }
             }
             __syncwarp();
@@ -419,7 +472,8 @@ __global__ void __launch_bounds__((kConsumerWarps + 1) * 32, MT == 1 ? 3 : (MT =
                         for (int c = 0; c < 2; ++c) {
                             const int vl = 4 * (2 * t + c) + j;
                             if (base + vl >= p.n || !((allow >> vl) & 1u)) continue;
-                            const float score = __fmul_rn(fmaf(float(acc[m][j][2 * half + c]), qs, qb), vs[4 * c + j]);
+                            const int isum = SPLIT ? acc[m][j][2 * half + c] - accn[SPLIT ? m : 0][j][2 * half + c] : acc[m][j][2 * half + c];
+                            const float score = __fmul_rn(fmaf(float(isum), qs, qb), vs[4 * c + j]);
                             push_candidate(p.cb, ql, score, uint32_t(base + vl), thr);
                         }
                     }
@@ -766,18 +820,20 @@ cudaError_t launch_scan_pd(const ScanParams &p, int sm_count, cudaStream_t s) {
     const int mt = (p.nq + 15) / 16;
     const size_t smem = size_t(kStages) * kStageBytes;
     const uint32_t tiles = (p.pos_end - p.pos_begin + kConsumerWarps - 1) / kConsumerWarps;
-    const unsigned per_sm = mt == 1 ? 3 : (mt == 2 ? 2 : 1);   // resident CTAs per SM (limited by registers)
+    // the split lookup doubles the accumulators: one and two query tiles only
+    const bool split = p.pd_split != 0 && mt <= 2 && levels_split_ok(p.level_words);
+    const unsigned per_sm = mt == 1 ? 3 : (mt == 2 && !split ? 2 : 1);   // resident CTAs per SM (registers)
     const unsigned grid = unsigned(min(uint32_t(sm_count) * per_sm, tiles));
     const unsigned threads = (kConsumerWarps + 1) * 32;
-#define TV_LAUNCH_PD(M)                                                                                             \
+#define TV_LAUNCH_PD(M, S)                                                                                          \
     {                                                                                                               \
-        cudaError_t e = cudaFuncSetAttribute(scan_pd_kernel<M>, cudaFuncAttributeMaxDynamicSharedMemorySize, int(smem)); \
+        cudaError_t e = cudaFuncSetAttribute(scan_pd_kernel<M, S>, cudaFuncAttributeMaxDynamicSharedMemorySize, int(smem)); \
         if (e != cudaSuccess) return e;                                                                             \
-        scan_pd_kernel<M><<<grid, threads, smem, s>>>(p);                                                           \
+        scan_pd_kernel<M, S><<<grid, threads, smem, s>>>(p);                                                        \
     }
-    if (mt <= 1) TV_LAUNCH_PD(1)
-    else if (mt <= 2) TV_LAUNCH_PD(2)
-    else if (mt <= 4) TV_LAUNCH_PD(4)
+    if (mt <= 1) { if (split) TV_LAUNCH_PD(1, true) else TV_LAUNCH_PD(1, false) }
+    else if (mt <= 2) { if (split) TV_LAUNCH_PD(2, true) else TV_LAUNCH_PD(2, false) }
+    else if (mt <= 4) TV_LAUNCH_PD(4, false)
     else return cudaErrorInvalidValue;
 #undef TV_LAUNCH_PD
     return cudaGetLastError();

@@ -89,6 +89,7 @@ struct ScanParams {
     const uint32_t *wfrag;
     int mtiles_total, mtile_base;
     uint32_t level_words[4];       // 16 int8 levels, entry c in byte c%4 of word c/4
+    int pd_split;                  // permute-dot scan on CUDA-core MMAs: 1 = split lookup where the levels allow it
     // LUT
     const uint8_t *luts;
 };
