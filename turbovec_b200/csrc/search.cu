@@ -310,6 +310,19 @@ __device__ __forceinline__ void expand4_split(uint32_t x, const uint32_t (&Tp)[2
     n1 = prmt(Tn[0], Tn[1], xh);
     p1 = prmt(Tp[0], Tp[1], yh);
 }
+// The same lookups for two vectors at once: `lo` holds rows (r, r+4) of vector a in its low half and of vector b
+// in its high half, `hi` rows (r+8, r+12) of the same two vectors.
+__device__ __forceinline__ void expand4_split_halves(uint32_t lo, uint32_t hi, const uint32_t (&Tp)[2], const uint32_t (&Tn)[2],
+                                                     uint32_t &pa0, uint32_t &pa1, uint32_t &na0, uint32_t &na1,
+                                                     uint32_t &pb0, uint32_t &pb1, uint32_t &nb0, uint32_t &nb1) {
+    const uint32_t ylo = lo ^ 0x88888888u, yhi = hi ^ 0x88888888u;
+    const uint32_t lo_b = mad_hi(lo, 0x10000u, 0u), hi_b = mad_hi(hi, 0x10000u, 0u);       // >> 16 on the FMA pipe
+    const uint32_t ylo_b = mad_hi(ylo, 0x10000u, 0u), yhi_b = mad_hi(yhi, 0x10000u, 0u);
+    na0 = prmt(Tn[0], Tn[1], lo);   pa0 = prmt(Tp[0], Tp[1], ylo);
+    na1 = prmt(Tn[0], Tn[1], hi);   pa1 = prmt(Tp[0], Tp[1], yhi);
+    nb0 = prmt(Tn[0], Tn[1], lo_b); pb0 = prmt(Tp[0], Tp[1], ylo_b);
+    nb1 = prmt(Tn[0], Tn[1], hi_b); pb1 = prmt(Tp[0], Tp[1], yhi_b);
+}
 __host__ __device__ inline uint32_t negate_bytes(uint32_t w) {                   // per-byte two's complement
     uint32_t r = 0;
     for (int b = 0; b < 4; ++b) r |= uint32_t(uint8_t(-int(int8_t(w >> (8 * b))))) << (8 * b);
@@ -325,7 +338,7 @@ inline bool levels_split_ok(const uint32_t (&words)[4]) {
 }
 
 template <int MT, bool SPLIT>
-__global__ void __launch_bounds__((kConsumerWarps + 1) * 32, MT == 1 ? 3 : (MT == 2 && !SPLIT ? 2 : 1))
+__global__ void __launch_bounds__((kConsumerWarps + 1) * 32, MT == 1 ? 3 : (MT == 2 ? 2 : 1))
 scan_pd_kernel(ScanParams p) {
     extern __shared__ __align__(128) unsigned char smem_raw[];
     uint8_t *stage_mem = smem_raw;
@@ -417,16 +430,21 @@ scan_pd_kernel(ScanParams p) {
                     // rows 16ks + t + {0,4,8,12}, word `quad` of each 32-byte row: conflict-free
                     const uint32_t *r0 = rows + (16 * ks + t) * 8 + quad;
                     const uint32_t wa = r0[0], wb = r0[32], wc = r0[64], wd = r0[96];
-                    // 4x4 byte transpose: x[j] = bytes j of (wa, wb, wc, wd)
+                    // pair the bytes of one vector: t0 = (v0: rows t, t+4 | v1: rows t, t+4), t2 the same vectors for
+                    // rows t+8, t+12; t1 / t3 hold vectors 2 and 3
                     const uint32_t t0 = prmt(wa, wb, 0x5140), t1 = prmt(wa, wb, 0x7362);
                     const uint32_t t2 = prmt(wc, wd, 0x5140), t3 = prmt(wc, wd, 0x7362);
-                    const uint32_t x[4] = {prmt(t0, t2, 0x5410), prmt(t0, t2, 0x7632), prmt(t1, t3, 0x5410),
-                                           prmt(t1, t3, 0x7632)};
                     uint32_t b0[4], b1[4], n0[SPLIT ? 4 : 1], n1[SPLIT ? 4 : 1];
+                    if constexpr (SPLIT) {
+                        // a lookup reads the low 16 bits of its selector, so the half-words serve as they are: the
+                        // second level of the 4x4 transpose is not needed
+                        expand4_split_halves(t0, t2, Tp, Tn, b0[0], b1[0], n0[0], n1[0], b0[1], b1[1], n0[1], n1[1]);
+                        expand4_split_halves(t1, t3, Tp, Tn, b0[2], b1[2], n0[2], n1[2], b0[3], b1[3], n0[3], n1[3]);
+                    } else {
+                        const uint32_t x[4] = {prmt(t0, t2, 0x5410), prmt(t0, t2, 0x7632), prmt(t1, t3, 0x5410),
+                                               prmt(t1, t3, 0x7632)};
 #pragma unroll
-                    for (int j = 0; j < 4; ++j) {
-                        if constexpr (SPLIT) expand4_split(x[j], Tp, Tn, b0[j], b1[j], n0[j], n1[j]);
-                        else expand4(x[j], T, b0[j], b1[j]);
+                        for (int j = 0; j < 4; ++j) expand4(x[j], T, b0[j], b1[j]);
                     }
 #pragma unroll
                     for (int m = 0; m < MT; ++m) {
@@ -820,9 +838,10 @@ cudaError_t launch_scan_pd(const ScanParams &p, int sm_count, cudaStream_t s) {
     const int mt = (p.nq + 15) / 16;
     const size_t smem = size_t(kStages) * kStageBytes;
     const uint32_t tiles = (p.pos_end - p.pos_begin + kConsumerWarps - 1) / kConsumerWarps;
-    // the split lookup doubles the accumulators: one and two query tiles only
-    const bool split = p.pd_split != 0 && mt <= 2 && levels_split_ok(p.level_words);
-    const unsigned per_sm = mt == 1 ? 3 : (mt == 2 && !split ? 2 : 1);   // resident CTAs per SM (registers)
+    // the split lookup doubles the accumulators: with two query tiles the kernel needs 168 registers, one CTA per
+    // SM, and is slower than the merged lookup (1.76 against 1.46 ms on 4 M vectors), so one tile only
+    const bool split = p.pd_split != 0 && mt <= 1 && levels_split_ok(p.level_words);
+    const unsigned per_sm = mt == 1 ? 3 : (mt == 2 ? 2 : 1);   // resident CTAs per SM (registers)
     const unsigned grid = unsigned(min(uint32_t(sm_count) * per_sm, tiles));
     const unsigned threads = (kConsumerWarps + 1) * 32;
 #define TV_LAUNCH_PD(M, S)                                                                                          \
@@ -832,7 +851,7 @@ cudaError_t launch_scan_pd(const ScanParams &p, int sm_count, cudaStream_t s) {
         scan_pd_kernel<M, S><<<grid, threads, smem, s>>>(p);                                                        \
     }
     if (mt <= 1) { if (split) TV_LAUNCH_PD(1, true) else TV_LAUNCH_PD(1, false) }
-    else if (mt <= 2) { if (split) TV_LAUNCH_PD(2, true) else TV_LAUNCH_PD(2, false) }
+    else if (mt <= 2) TV_LAUNCH_PD(2, false)
     else if (mt <= 4) TV_LAUNCH_PD(4, false)
     else return cudaErrorInvalidValue;
 #undef TV_LAUNCH_PD
