@@ -777,3 +777,25 @@ def test_add_with_ids_from_device_memory(T):
     with pytest.raises(ValueError, match="already present"):
         b.add_with_ids_device(xd.data_ptr(), 1, dim, ids[:1])
     assert len(b) == n
+
+
+@pytest.mark.parametrize("nq", [1, 5, 16, 17, 32])
+def test_split_and_merged_level_lookups_agree_with_the_oracle(T, nq):
+    """The small-batch permute-dot scan looks levels up in two half-tables (two exact contractions, subtracted) or
+    in one merged table (`TV_OPT_PD_SPLIT`); both must reproduce the oracle bit for bit, masked or not."""
+    dim, n, k = 512, 9000, 10
+    x = anisotropic(n, dim, seed=91)
+    q = anisotropic(nq, dim, seed=91, offset=7)
+    enc = O.encode(x, 4)
+    blocked = O.packed_to_blocked(enc["packed"], 4, dim)
+    mask = np.random.default_rng(3).random(n) < 0.3
+    idx = T.TurboQuantIndex(dim, 4)
+    idx.add(x)
+    for m in (None, mask):
+        words = None if m is None else O.pack_mask(m)
+        want_s, want_i = O.search(q, blocked, enc["scales"], n, dim, 4, k, mask_words=words)
+        for split in (1, 0):
+            idx.set_option(T.OPT_PD_SPLIT, split)
+            assert idx.get_option(T.OPT_PD_SPLIT) == split
+            s, i = idx.search(q, k, mask=m)
+            assert np.array_equal(i, want_i) and np.array_equal(s.view(np.uint32), want_s.view(np.uint32))
