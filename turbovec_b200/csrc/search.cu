@@ -256,6 +256,15 @@ __device__ __forceinline__ uint32_t prmt(uint32_t a, uint32_t b, uint32_t sel) {
     asm("prmt.b32 %0, %1, %2, %3;" : "=r"(d) : "r"(a), "r"(b), "r"(sel));
     return d;
 }
+// Two 16 x 16 byte matrices, transposed by the load unit: lane 4*q + t receives in x[2*i + h] the bytes of column
+// q + 8*h of matrix i from its rows 4t .. 4t+3 (byte r of the word = row 4t + r).  Lanes 0..15 give the row
+// addresses of matrix 0, lanes 16..31 those of matrix 1 (16-byte aligned, 16 bytes each).
+__device__ __forceinline__ void ldmatrix_x2_trans_b8(uint32_t (&x)[4], uint32_t row_addr) {
+    asm volatile("ldmatrix.sync.aligned.m16n16.x2.trans.shared.b8 {%0, %1, %2, %3}, [%4];"
+                 : "=r"(x[0]), "=r"(x[1]), "=r"(x[2]), "=r"(x[3])
+                 : "r"(row_addr)
+                 : "memory");
+}
 __device__ __forceinline__ void mma_s8(int (&c)[4], const uint4 &a, uint32_t b0, uint32_t b1) {
     asm(
         "mma.sync.aligned.m16n8k32.row.col.s32.s8.s8.s32 {%0,%1,%2,%3}, {%4,%5,%6,%7}, {%8,%9}, {%0,%1,%2,%3};"
@@ -309,19 +318,6 @@ __device__ __forceinline__ void expand4_split(uint32_t x, const uint32_t (&Tp)[2
     p0 = prmt(Tp[0], Tp[1], y);
     n1 = prmt(Tn[0], Tn[1], xh);
     p1 = prmt(Tp[0], Tp[1], yh);
-}
-// The same lookups for two vectors at once: `lo` holds rows (r, r+4) of vector a in its low half and of vector b
-// in its high half, `hi` rows (r+8, r+12) of the same two vectors.
-__device__ __forceinline__ void expand4_split_halves(uint32_t lo, uint32_t hi, const uint32_t (&Tp)[2], const uint32_t (&Tn)[2],
-                                                     uint32_t &pa0, uint32_t &pa1, uint32_t &na0, uint32_t &na1,
-                                                     uint32_t &pb0, uint32_t &pb1, uint32_t &nb0, uint32_t &nb1) {
-    const uint32_t ylo = lo ^ 0x88888888u, yhi = hi ^ 0x88888888u;
-    const uint32_t lo_b = mad_hi(lo, 0x10000u, 0u), hi_b = mad_hi(hi, 0x10000u, 0u);       // >> 16 on the FMA pipe
-    const uint32_t ylo_b = mad_hi(ylo, 0x10000u, 0u), yhi_b = mad_hi(yhi, 0x10000u, 0u);
-    na0 = prmt(Tn[0], Tn[1], lo);   pa0 = prmt(Tp[0], Tp[1], ylo);
-    na1 = prmt(Tn[0], Tn[1], hi);   pa1 = prmt(Tp[0], Tp[1], yhi);
-    nb0 = prmt(Tn[0], Tn[1], lo_b); pb0 = prmt(Tp[0], Tp[1], ylo_b);
-    nb1 = prmt(Tn[0], Tn[1], hi_b); pb1 = prmt(Tp[0], Tp[1], yhi_b);
 }
 __host__ __device__ inline uint32_t negate_bytes(uint32_t w) {                   // per-byte two's complement
     uint32_t r = 0;
@@ -419,32 +415,25 @@ scan_pd_kernel(ScanParams p) {
             const int s = it % kStages;
             if (!mbar_wait(&full_bar[s], (it / kStages) & 1, p.cb.error)) return;
             if (have) {
-                const uint32_t *rows =
-                    reinterpret_cast<const uint32_t *>(stage_mem + size_t(s) * kStageBytes + size_t(warp) * kChunkRows * kLanes);
+                // lane L < 16 addresses matrix row L of the vector half 0..15, lane L >= 16 that of the half 16..31
+                const uint32_t rows_addr = smem_addr(stage_mem + size_t(s) * kStageBytes + size_t(warp) * kChunkRows * kLanes) +
+                                           uint32_t((((lane & 15) >> 2) + 4 * (lane & 3)) * kLanes + (lane >> 4) * 16);
                 const int rows_here = min(kChunkRows, ng - ch * kChunkRows);
                 const int ksteps = (rows_here + 15) / 16;
                 // query fragments of this chunk's k-steps: one pointer per chunk, constant strides inside
                 const uint4 *wf = wfrag + (size_t(ch) * (kChunkRows / 16) * p.mtiles_total + p.mtile_base) * 32 + lane;
                 const size_t wf_step = size_t(p.mtiles_total) * 32;
                 auto kstep = [&](int ks) {
-                    // rows 16ks + t + {0,4,8,12}, word `quad` of each 32-byte row: conflict-free
-                    const uint32_t *r0 = rows + (16 * ks + t) * 8 + quad;
-                    const uint32_t wa = r0[0], wb = r0[32], wc = r0[64], wd = r0[96];
-                    // pair the bytes of one vector: t0 = (v0: rows t, t+4 | v1: rows t, t+4), t2 the same vectors for
-                    // rows t+8, t+12; t1 / t3 hold vectors 2 and 3
-                    const uint32_t t0 = prmt(wa, wb, 0x5140), t1 = prmt(wa, wb, 0x7362);
-                    const uint32_t t2 = prmt(wc, wd, 0x5140), t3 = prmt(wc, wd, 0x7362);
+                    // x[j] = the byte-groups of rows 16ks + t + {0, 4, 8, 12} (bytes 0..3) of vector 8j + quad: the
+                    // load unit transposes, matrix row 4t + r being pointed at row t + 4r so that the k order of the
+                    // query fragments holds
+                    uint32_t x[4];
+                    ldmatrix_x2_trans_b8(x, rows_addr + ks * (16 * kLanes));
                     uint32_t b0[4], b1[4], n0[SPLIT ? 4 : 1], n1[SPLIT ? 4 : 1];
-                    if constexpr (SPLIT) {
-                        // a lookup reads the low 16 bits of its selector, so the half-words serve as they are: the
-                        // second level of the 4x4 transpose is not needed
-                        expand4_split_halves(t0, t2, Tp, Tn, b0[0], b1[0], n0[0], n1[0], b0[1], b1[1], n0[1], n1[1]);
-                        expand4_split_halves(t1, t3, Tp, Tn, b0[2], b1[2], n0[2], n1[2], b0[3], b1[3], n0[3], n1[3]);
-                    } else {
-                        const uint32_t x[4] = {prmt(t0, t2, 0x5410), prmt(t0, t2, 0x7632), prmt(t1, t3, 0x5410),
-                                               prmt(t1, t3, 0x7632)};
 #pragma unroll
-                        for (int j = 0; j < 4; ++j) expand4(x[j], T, b0[j], b1[j]);
+                    for (int j = 0; j < 4; ++j) {
+                        if constexpr (SPLIT) expand4_split(x[j], Tp, Tn, b0[j], b1[j], n0[j], n1[j]);
+                        else expand4(x[j], T, b0[j], b1[j]);
                     }
 #pragma unroll
                     for (int m = 0; m < MT; ++m) {
@@ -470,10 +459,13 @@ scan_pd_kernel(ScanParams p) {
         if (have) {
             const uint32_t blk = p.live_blocks ? p.live_blocks[pos] : pos;
             const int64_t base = int64_t(blk) * kLanes;
-            // accumulator columns 2t, 2t+1 of n-tile j are vectors 4*(2t)+j and 4*(2t+1)+j
+            // accumulator columns 2t, 2t+1 of n-tile j are vectors 8j + 2t and 8j + 2t + 1
             float vs[8];
 #pragma unroll
-            for (int e = 0; e < 8; ++e) vs[e] = (base + 8 * t + e < p.n) ? p.vec_scales[base + 8 * t + e] : 0.0f;
+            for (int e = 0; e < 8; ++e) {
+                const int v = 8 * (e >> 1) + 2 * t + (e & 1);
+                vs[e] = (base + v < p.n) ? p.vec_scales[base + v] : 0.0f;
+            }
             uint32_t allow = 0xffffffffu;
             if (p.mask) allow = reinterpret_cast<const uint32_t *>(p.mask)[blk];
 #pragma unroll
@@ -488,10 +480,10 @@ scan_pd_kernel(ScanParams p) {
                     for (int j = 0; j < 4; ++j) {
 #pragma unroll
                         for (int c = 0; c < 2; ++c) {
-                            const int vl = 4 * (2 * t + c) + j;
+                            const int vl = 8 * j + 2 * t + c;
                             if (base + vl >= p.n || !((allow >> vl) & 1u)) continue;
                             const int isum = SPLIT ? acc[m][j][2 * half + c] - accn[SPLIT ? m : 0][j][2 * half + c] : acc[m][j][2 * half + c];
-                            const float score = __fmul_rn(fmaf(float(isum), qs, qb), vs[4 * c + j]);
+                            const float score = __fmul_rn(fmaf(float(isum), qs, qb), vs[2 * j + c]);
                             push_candidate(p.cb, ql, score, uint32_t(base + vl), thr);
                         }
                     }
