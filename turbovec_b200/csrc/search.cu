@@ -334,7 +334,7 @@ inline bool levels_split_ok(const uint32_t (&words)[4]) {
 }
 
 template <int MT, bool SPLIT>
-__global__ void __launch_bounds__((kConsumerWarps + 1) * 32, MT == 1 ? 3 : (MT == 2 ? 2 : 1))
+__global__ void __launch_bounds__((kConsumerWarps + 1) * 32, MT == 1 ? (SPLIT ? 2 : 3) : (MT == 2 ? 2 : 1))
 scan_pd_kernel(ScanParams p) {
     extern __shared__ __align__(128) unsigned char smem_raw[];
     uint8_t *stage_mem = smem_raw;
@@ -833,7 +833,7 @@ cudaError_t launch_scan_pd(const ScanParams &p, int sm_count, cudaStream_t s) {
     // the split lookup doubles the accumulators: with two query tiles the kernel needs 168 registers, one CTA per
     // SM, and is slower than the merged lookup (1.76 against 1.46 ms on 4 M vectors), so one tile only
     const bool split = p.pd_split != 0 && mt <= 1 && levels_split_ok(p.level_words);
-    const unsigned per_sm = mt == 1 ? 3 : (mt == 2 ? 2 : 1);   // resident CTAs per SM (registers)
+    const unsigned per_sm = mt == 1 ? (split ? 2 : 3) : (mt == 2 ? 2 : 1);   // resident CTAs per SM (registers)
     const unsigned grid = unsigned(min(uint32_t(sm_count) * per_sm, tiles));
     const unsigned threads = (kConsumerWarps + 1) * 32;
 #define TV_LAUNCH_PD(M, S)                                                                                          \
