@@ -15,8 +15,11 @@
  *    index exactly as it was (the reference's all-or-nothing contract,
  *    turbovec/src/lib.rs:889-930).  tv_last_error() gives the message.
  *  - Calls are synchronous: results are complete when the call returns.
- *  - A handle may be used from several threads; mutating calls are exclusive,
- *    searches are serialised per handle on the handle's stream.
+ *  - A handle may be used from several threads, like the reference's index
+ *    (`search(&self)`, mutation through `&mut self`; turbovec/src/lib.rs:22-52):
+ *    searches hold the handle shared and overlap on the device (two at a
+ *    time, each on its own stream and scratch; further ones wait), every
+ *    call that changes the index is exclusive.
  *  - There is no CPU fallback: every compute entry point needs a CUDA device.
  */
 #ifndef TURBOVEC_B200_H
@@ -100,9 +103,14 @@ enum {
     TV_OPT_TC_TILES = 4,        /* accumulator tiles of 128 vectors per query slab in the tensor-memory scan: 1 or 2 */
     TV_OPT_INGEST_PIPELINE = 5, /* 1 (default): whole code blocks are encoded by the pipelined ingest kernel; 0: never;
                                  * 2: pipelined, and every reconstruction sum walks the sequential chains (testing) */
-    TV_OPT_PD_SPLIT = 6         /* 1 (default): batches of up to 32 queries on 4-bit permute-dot indexes look the int8
+    TV_OPT_PD_SPLIT = 6,        /* 1 (default): batches of up to 32 queries on 4-bit permute-dot indexes look the int8
                                  * levels up with one byte-permute per four codes and half-table (two exact integer
                                  * contractions, subtracted); 0: merged lookup, one contraction (testing) */
+    TV_OPT_SMALL_SCAN = 7,      /* permute-dot batches of up to 16 queries: -1 = the general small-batch kernel; otherwise
+                                 * a variant of the stream-shaped kernel (bits 0-1: ring depth 3 / 4 / 6 stages per warp,
+                                 * bit 2: swizzled tensor copies instead of plain bulk copies; default 5).  Results are identical. */
+    TV_OPT_FAIL_NEXT = 8        /* testing: the n-th guarded device allocation / upload from now on reports an
+                                 * out-of-memory failure instead of running (1 = the next one); 0 disarms */
 };
 
 /* ---- construction: TurboQuantIndex::new / new_lazy (lib.rs:629, 670), IdMapIndex::new (id_map.rs:278) ---- */
@@ -167,6 +175,23 @@ int tv_search_device(tv_index *h, const float *queries_device, size_t nq, size_t
                      const uint64_t *mask_words_device, float *scores_out_device, int64_t *slots_out_device,
                      size_t *k_eff);
 
+/* ---- one filter, many searches.  The reference rebuilds the slot mask from the allowlist on every call
+ * (id_map.rs:670-683, lib.rs:1435-1456: |allowlist| hash lookups plus a pass over all slots); these entry
+ * points do that work once and keep the packed mask, the list of code blocks that hold an allowed slot and
+ * the allowed count on the device.  Any call that changes the index drops the prepared mask; searching with
+ * a dropped or missing one fails with TV_ERR_INVALID_ARGUMENT.  No reference counterpart.
+ * tv_mask_prepare_device: packed words in device memory (bit i of word i/64 = slot i, ceil(len/64) words).
+ * tv_mask_prepare_words: the same words in host memory.  tv_mask_prepare_allowlist: ids (TV_KIND_IDMAP), with
+ * the allowlist errors of tv_search_allowlist.  tv_search_prepared / tv_search_device_prepared: as tv_search /
+ * tv_search_device under the prepared mask; ids_out (may be NULL) needs an id-mapped index. ---- */
+int tv_mask_prepare_device(tv_index *h, const uint64_t *mask_words_device);
+int tv_mask_prepare_words(tv_index *h, const uint64_t *mask_words, size_t n_words);
+int tv_mask_prepare_allowlist(tv_index *h, const uint64_t *allow_ids, size_t n_allow);
+int tv_search_prepared(tv_index *h, const float *queries, size_t nq, size_t dim, size_t k, float *scores_out,
+                       int64_t *slots_out, uint64_t *ids_out, size_t *k_eff);
+int tv_search_device_prepared(tv_index *h, const float *queries_device, size_t nq, size_t k,
+                              float *scores_out_device, int64_t *slots_out_device, size_t *k_eff);
+
 /* ---- slot-sharded search over several GPUs (one process per GPU).  No reference counterpart: the reference
  * is a single-host library; these two calls are the per-rank half and the merge half of a sharded search. ----
  * tv_search_device_keys: like tv_search_device, but each result is one 64-bit key = (order-preserving image of
@@ -189,11 +214,17 @@ int tv_merge_keys_device(int device, const uint64_t *keys_device, size_t n_lists
  * frameworks that forbid allocator traffic after warm-up.  Same contract as tv_search_device (unfiltered;
  * queries, scores and slots in device memory; output row stride *k_eff), but all scratch sits in one fixed
  * 1.25 MiB array inside the library image, resident on every GPU that loads the library until exit.
- * Limits: nq <= 8, k <= 128, index dim <= 4096; larger requests fail with TV_ERR_UNSUPPORTED and a message.
- * The index tables must exist (tv_prepare or a previous add).  The first call on each device resolves the
- * array's device address; make that call before any stream capture begins.  All calls share the array,
- * which keeps whatever the previous call left; within a process calls are serialised, and work from other
- * sources that touches the same array while a call is in flight would race with it. */
+ * Limits: nq <= 8, k <= 128, index dim <= 4096 (and, for 2/3-bit and other u8-LUT geometries, tables of one
+ * query that fit in shared memory: 32 * ngroups bytes <= 226 KB); larger requests fail with TV_ERR_UNSUPPORTED
+ * and a message.  It runs the chunk schedule of tv_search_device on the CUDA-core scan kernels (a handful of
+ * launches whatever the index size; a 10 M x 1536 4-bit index answers in about the time of tv_search_device
+ * at the same batch), and an adversarial vector order that overflows a candidate list is redone in bounded
+ * chunks, still without memory beyond the array.  The index tables must exist (tv_prepare or a previous add).
+ * The first call on each device resolves the array's device address, and the first call with a given batch
+ * size and score mode loads that kernel: warm up with the batch sizes you serve, before any stream capture
+ * begins.  All calls share the array, which keeps whatever the previous call left; within a process calls are
+ * serialised, and work from other sources that touches the same array while a call is in flight would race
+ * with it. */
 int tv_search_device_noalloc(tv_index *h, const float *queries_device, size_t nq, size_t k,
                              float *scores_out_device, int64_t *slots_out_device, size_t *k_eff);
 
@@ -268,6 +299,11 @@ float tv_last_kernel_ms(const tv_index *h);
  * the ingest kernel for an add — each launch bracketed by its own pair of events; *launches = how many. */
 float tv_last_main_kernel_ms(const tv_index *h, int *launches);
 const char *tv_version(void);
+/* Measures the device's int8 tensor rate for this library's MMA form (tcgen05 kind::i8, M = 128, N = 256, K = 32,
+ * operands in shared memory, accumulators in tensor memory; no loads, no epilogue): ops per second with a
+ * multiply-add counted as 2.  About 25 ms.  The roofline the large-batch permute-dot scan is reported against;
+ * no reference counterpart. */
+int tv_measure_int8_peak(int device, double *ops_per_second);
 /* Host-side evaluation of the quantisation grid that the pipelined ingest kernel builds from a codebook's
  * boundaries (`count` ascending values, at most 15): codes_out[i] = number of boundaries strictly below
  * values[i] (encode.rs:1447-1451), looked up exactly as the kernel does.  Returns TV_ERR_UNSUPPORTED when the

@@ -1,0 +1,265 @@
+"""Search paths beyond the defaults, each through the C ABI and against the CPU oracle on the same inputs:
+every variant of the stream-shaped small-batch scan, paged top-k for k above one selection pass, u8-LUT
+geometries whose tables crowd shared memory, prepared masks, searches that overlap on one handle, two devices
+in one process, and the all-or-nothing contract under an injected allocation / upload failure."""
+import threading
+
+import numpy as np
+import pytest
+
+from oracle import oracle as O
+from tests.util import anisotropic
+
+pytestmark = pytest.mark.gpu
+
+
+@pytest.fixture(scope="module")
+def T():
+    import turbovec_b200
+    return turbovec_b200
+
+
+def oracle_index(x, bits):
+    enc = O.encode(x, bits)
+    return O.packed_to_blocked(enc["packed"], bits, x.shape[1]), enc["scales"]
+
+
+def oracle_search(x, q, bits, k, mask=None, mode=O.MODE_AUTO, pre=None):
+    blocked, scales = pre if pre is not None else oracle_index(x, bits)
+    words = None if mask is None else O.pack_mask(mask)
+    return O.search(q, blocked, scales, x.shape[0], x.shape[1], bits, k, mask_words=words, mode=mode)
+
+
+# ------------------------------------------------------------------ stream-shaped small-batch scan
+@pytest.mark.parametrize("dim,n", [(1536, 9000), (200, 5000), (64, 4500), (4096, 1200), (1000, 3000)])
+def test_small_scan_variants_match_oracle(T, dim, n):
+    """All ring depths, plain and swizzled stage fills, 1..16 queries, with and without a mask: bit-identical to
+    the oracle.  dim 200 has a 36-row tail chunk, dim 64 a single half-filled chunk, dim 1000 an 8-point rotation."""
+    x = anisotropic(n, dim, seed=41)
+    pre = oracle_index(x, 4)
+    idx = T.TurboQuantIndex(dim, 4)
+    idx.add(x)
+    mask = np.random.default_rng(3).random(n) < 0.3
+    for nq in (1, 3, 8, 9, 16):
+        q = anisotropic(nq, dim, seed=41, offset=700 + nq)
+        want = oracle_search(x, q, 4, 10, pre=pre)
+        want_m = oracle_search(x, q, 4, 10, mask=mask, pre=pre)
+        for variant in (-1, 0, 1, 2, 4, 5, 6):
+            idx.set_option(T.OPT_SMALL_SCAN, variant)
+            s, i = idx.search(q, 10)
+            assert np.array_equal(i, want[1]) and np.array_equal(s, want[0]), f"variant {variant}, {nq} queries"
+            s, i = idx.search(q, 10, mask=mask)
+            assert np.array_equal(i, want_m[1]) and np.array_equal(s, want_m[0]), f"variant {variant}, {nq} queries, masked"
+
+
+def test_small_scan_many_chunks_and_recovery(T):
+    n, dim = 150_000, 128
+    x = anisotropic(n, dim, seed=8)
+    q = anisotropic(4, dim, seed=8, offset=3)
+    order = np.argsort(x @ q[0])                       # adversarial order for query 0: overflows, then recovers
+    x = np.ascontiguousarray(x[order])
+    idx = T.TurboQuantIndex(dim, 4)
+    idx.add(x)
+    want = oracle_search(x, q, 4, 10)
+    for variant in (0, 6):
+        idx.set_option(T.OPT_SMALL_SCAN, variant)
+        s, i = idx.search(q, 10)
+        assert np.array_equal(i, want[1]) and np.array_equal(s, want[0])
+
+
+# ------------------------------------------------------------------ k above one selection pass
+@pytest.mark.parametrize("bits,dim", [(4, 64), (2, 64)])
+def test_paged_topk_beyond_4096(T, bits, dim):
+    n = 21_000
+    x = anisotropic(n, dim, seed=51)
+    q = anisotropic(3, dim, seed=51, offset=9)
+    idx = T.TurboQuantIndex(dim, bits)
+    idx.add(x)
+    pre = oracle_index(x, bits)
+    for k in (4097, 9000, n, n + 5):
+        s, i = idx.search(q, k)
+        rs, ri = oracle_search(x, q, bits, k, pre=pre)
+        assert s.shape == (3, min(k, n))
+        assert np.array_equal(i, ri) and np.array_equal(s, rs), f"k={k}"
+    mask = np.random.default_rng(5).random(n) < 0.5
+    s, i = idx.search(q, 6000, mask=mask)
+    rs, ri = oracle_search(x, q, bits, 6000, mask=mask, pre=pre)
+    assert np.array_equal(i, ri) and np.array_equal(s, rs)
+
+
+# ------------------------------------------------------------------ u8-LUT tables against the shared-memory limit
+@pytest.mark.parametrize("dim,bits", [(4096, 3), (8192, 2), (16384, 2), (16384, 3)])
+def test_lut_scan_with_large_tables(T, dim, bits):
+    n = 700
+    x = anisotropic(n, dim, seed=61)
+    idx = T.TurboQuantIndex(dim, bits)
+    idx.add(x)
+    pre = oracle_index(x, bits)
+    for nq in (1, 3, 7):
+        q = anisotropic(nq, dim, seed=61, offset=40 + nq)
+        s, i = idx.search(q, 10)
+        rs, ri = oracle_search(x, q, bits, 10, pre=pre)
+        assert np.array_equal(i, ri) and np.array_equal(s, rs), f"{nq} queries"
+
+
+def test_lut_flush_mode_without_room_for_one_table_is_refused(T):
+    dim = 16384
+    idx = T.TurboQuantIndex(dim, 3)
+    idx.add(anisotropic(64, dim, seed=1))
+    idx.set_option(T.OPT_SCORE_MODE, T.SCORE_LUT_FLUSH)
+    with pytest.raises(RuntimeError, match="exceed shared memory"):
+        idx.search(anisotropic(1, dim, seed=1, offset=5), 5)
+
+
+# ------------------------------------------------------------------ prepared masks
+def test_prepared_mask_equals_mask_per_call(T):
+    import torch
+    n, dim, nq = 50_000, 256, 5
+    x = anisotropic(n, dim, seed=71)
+    q = anisotropic(nq, dim, seed=71, offset=11)
+    idx = T.TurboQuantIndex(dim, 4)
+    idx.add(x)
+    mask = np.random.default_rng(2).random(n) < 0.02
+    want = idx.search(q, 20, mask=mask)
+    rs, ri = oracle_search(x, q, 4, 20, mask=mask)
+    assert np.array_equal(want[1], ri) and np.array_equal(want[0], rs)
+    words = O.pack_mask(mask)
+    idx.prepare_mask_words(words)
+    for _ in range(2):
+        s, i = idx.search_prepared(q, 20)
+        assert np.array_equal(i, ri) and np.array_equal(s, rs)
+    d_words = torch.from_numpy(words.view(np.int64)).cuda()
+    idx.prepare_mask_device(d_words.data_ptr())
+    qd = torch.from_numpy(q).cuda()
+    out_s = torch.empty((nq, 20), dtype=torch.float32, device="cuda")
+    out_i = torch.empty((nq, 20), dtype=torch.int64, device="cuda")
+    ke = idx.search_device_prepared(qd.data_ptr(), nq, 20, out_s.data_ptr(), out_i.data_ptr())
+    assert ke == 20 and np.array_equal(out_i.cpu().numpy(), ri) and np.array_equal(out_s.cpu().numpy(), rs)
+    # a change of the index drops the prepared mask
+    idx.swap_remove(3)
+    with pytest.raises(RuntimeError, match="no prepared mask"):
+        idx.search_prepared(q, 20)
+
+
+def test_prepared_allowlist_on_idmap(T):
+    n, dim = 4000, 128
+    x = anisotropic(n, dim, seed=72)
+    ids = (np.random.default_rng(4).permutation(n) + 10**9).astype(np.uint64)
+    idx = T.IdMapIndex(dim, 4)
+    idx.add_with_ids(x, ids)
+    allow = np.ascontiguousarray(ids[::7])
+    q = anisotropic(3, dim, seed=72, offset=2)
+    want = idx.search(q, 50, allowlist=allow)
+    idx.prepare_allowlist(allow)
+    got = idx.search_prepared(q, 50)
+    assert np.array_equal(got[1], want[1]) and np.array_equal(got[0], want[0])
+    with pytest.raises(KeyError):
+        idx.prepare_allowlist(np.array([5], np.uint64))
+
+
+# ------------------------------------------------------------------ overlapping searches on one handle
+def test_searches_from_several_threads_overlap_and_agree(T):
+    n, dim = 60_000, 256
+    x = anisotropic(n, dim, seed=81)
+    idx = T.TurboQuantIndex(dim, 4)
+    idx.add(x)
+    queries = [anisotropic(nq, dim, seed=81, offset=100 + t) for t, nq in enumerate([1, 5, 40, 3, 70, 2])]
+    want = [idx.search(q, 10) for q in queries]
+    errors = []
+
+    def worker(t):
+        try:
+            for _ in range(8):
+                s, i = idx.search(queries[t], 10)
+                assert np.array_equal(i, want[t][1]) and np.array_equal(s, want[t][0])
+        except Exception as e:  # noqa: BLE001
+            errors.append(e)
+
+    threads = [threading.Thread(target=worker, args=(t,)) for t in range(len(queries))]
+    for th in threads:
+        th.start()
+    for th in threads:
+        th.join()
+    assert not errors, errors
+
+
+# ------------------------------------------------------------------ two devices in one process
+def test_indexes_on_two_devices_in_one_process(T):
+    import torch
+    if torch.cuda.device_count() < 2:
+        pytest.skip("needs two GPUs")
+    n, dim = 5000, 256
+    x = anisotropic(n, dim, seed=91)
+    pre = oracle_index(x, 4)
+    for nq, k in [(3, 10), (70, 10), (2, 600)]:
+        q = anisotropic(nq, dim, seed=91, offset=nq)
+        want = oracle_search(x, q, 4, k, pre=pre)
+        for dev in (0, 1):
+            idx = T.TurboQuantIndex(dim, 4, device=dev)
+            idx.add(x)
+            s, i = idx.search(q, k)
+            assert np.array_equal(i, want[1]) and np.array_equal(s, want[0]), f"device {dev}"
+
+
+# ------------------------------------------------------------------ failure before / between launches
+def test_injected_failure_leaves_the_index_unchanged(T):
+    """The reference's unwind guards restore the pre-call state when an encode step fails
+    (turbovec/src/lib.rs:889-930, exercised by its FORCE_ENCODE_PANIC tests).  Here the failure is injected on the
+    host: the n-th guarded allocation or upload of the call reports out-of-memory instead of running."""
+    dim, n0 = 1536, 5000
+    x0 = anisotropic(n0, dim, seed=95)
+    ids0 = np.arange(n0, dtype=np.uint64) + 7
+    idx = T.IdMapIndex(dim, 4)
+    idx.add_with_ids(x0, ids0)
+    codes, scales = idx.codes_blocked_seq(), idx.scales()
+    more = anisotropic(25_000, dim, seed=96)              # 154 MB: three staging chunks from host memory
+    more_ids = np.arange(25_000, dtype=np.uint64) + 10**6
+    for nth in (1, 2, 3):                                  # capacity growth, first upload, second upload
+        idx.set_option(T.OPT_FAIL_NEXT, nth)
+        with pytest.raises(RuntimeError):
+            idx.add_with_ids(more, more_ids)
+        assert idx.get_option(T.OPT_FAIL_NEXT) == 0
+        assert len(idx) == n0 and np.array_equal(idx.ids(), ids0) and not idx.contains(10**6)
+        assert np.array_equal(idx.codes_blocked_seq(), codes) and np.array_equal(idx.scales(), scales)
+    q = anisotropic(2, dim, seed=95, offset=1)
+    want = idx.search(q, 5)
+    idx.set_option(T.OPT_FAIL_NEXT, 1)
+    with pytest.raises(RuntimeError):
+        idx.search(q, 5)
+    got = idx.search(q, 5)
+    assert np.array_equal(got[0], want[0]) and np.array_equal(got[1], want[1])
+    # and the add goes through once nothing fails
+    idx.add_with_ids(more, more_ids)
+    assert len(idx) == n0 + 25_000 and idx.contains(10**6)
+    full = (n0 // 32) * 32 * (dim // 2)                    # the complete blocks of the first add
+    assert np.array_equal(idx.codes_blocked_seq()[:full], codes[:full])
+
+
+# ------------------------------------------------------------------ BASELINE configuration 1 at its stated size
+def test_reference_workload_config1_full_size(T):
+    """100,000 x 1536 4-bit, 1,000 queries, k = 10, single queries and one batch of 1,000: ids and scores against the
+    multithreaded CPU restatement of the reference's permute-dot kernel on every query, and against the scalar
+    oracle on a sample of them."""
+    n, dim, nq, k = 100_000, 1536, 1000, 10
+    x = anisotropic(n, dim, seed=1)
+    q = anisotropic(nq, dim, seed=1, offset=10_000_000)
+    idx = T.TurboQuantIndex(dim, 4)
+    idx.add(x)
+    enc = O.encode(x, 4)
+    blocked = O.packed_to_blocked(enc["packed"], 4, dim)
+    assert np.array_equal(idx.codes_blocked_seq(), blocked)
+    assert np.array_equal(idx.scales().view(np.uint32), enc["scales"].view(np.uint32))
+    bs, bi = idx.search(q, k)                                   # one batch of 1,000: the tensor-memory scan
+    singles = [idx.search(q[j:j + 1], k) for j in range(0, nq, 25)]   # single queries: the stream-shaped scan
+    for j, (s, i) in zip(range(0, nq, 25), singles):
+        assert np.array_equal(i[0], bi[j]) and np.array_equal(s[0], bs[j])
+    if O.simd_available():
+        vm = O.to_vector_major(blocked, n, dim)
+        rs, ri = O.search_simd(q, vm, enc["scales"], n, dim, k)
+        assert np.array_equal(bi, ri) and np.array_equal(bs, rs)
+    sample = np.arange(0, nq, 50)
+    rs, ri = O.search(q[sample], blocked, enc["scales"], n, dim, 4, k)
+    assert np.array_equal(bi[sample], ri) and np.array_equal(bs[sample], rs)
+    truth = np.argsort(-(q[:100] @ x.T), axis=1)[:, :k]
+    recall = np.mean([len(set(bi[j]) & set(truth[j])) / k for j in range(100)])
+    assert recall >= 0.70                                       # the reference's 4-bit floor (tests/recall_sanity.rs:97-118)

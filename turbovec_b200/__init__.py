@@ -11,8 +11,8 @@ import ctypes as C
 import numpy as np
 
 from . import _native
-from ._native import (OPT_FORCE_CAREFUL, OPT_INGEST_PIPELINE, OPT_MMA_MIN_BATCH, OPT_PD_SPLIT, OPT_SCORE_MODE, OPT_TC_TILES, SCORE_AUTO, SCORE_LUT_FLUSH,
-                      SCORE_LUT_MULADD, SCORE_PERMUTE_DOT)
+from ._native import (OPT_FAIL_NEXT, OPT_FORCE_CAREFUL, OPT_INGEST_PIPELINE, OPT_MMA_MIN_BATCH, OPT_PD_SPLIT, OPT_SCORE_MODE, OPT_SMALL_SCAN,
+                      OPT_TC_TILES, SCORE_AUTO, SCORE_LUT_FLUSH, SCORE_LUT_MULADD, SCORE_PERMUTE_DOT)
 
 __all__ = ["TurboQuantIndex", "IdMapIndex", "BATCH_CHUNK_SIZE"]
 
@@ -244,6 +244,70 @@ class _Base:
     def __reduce__(self):
         return (type(self).from_bytes, (self.to_bytes(),))
 
+    def search_device(self, q_ptr: int, nq: int, k: int, scores_ptr: int, slots_ptr: int, mask_words_ptr: int = 0) -> int:
+        """Device-resident search; returns k_eff.  Output rows have stride k_eff."""
+        k_eff = C.c_size_t(0)
+        self._check(self._lib.tv_search_device(self._h, C.c_void_p(q_ptr), nq, k,
+                                                C.c_void_p(mask_words_ptr) if mask_words_ptr else None,
+                                                C.c_void_p(scores_ptr), C.c_void_p(slots_ptr), C.byref(k_eff)))
+        return int(k_eff.value)
+
+    def search_device_keys(self, q_ptr: int, nq: int, k: int, keys_ptr: int, slot_offset: int = 0,
+                           mask_words_ptr: int = 0) -> int:
+        """Device-resident search of one shard of a slot-sharded index: writes rows of k 64-bit result keys
+        (ascending key = score descending, then global slot ascending; padded with EMPTY_KEY) with
+        `slot_offset` added to every slot.  All-gather the rows of every rank and pass them to
+        merge_keys_device.  Returns this shard's k_eff."""
+        k_eff = C.c_size_t(0)
+        self._check(self._lib.tv_search_device_keys(self._h, C.c_void_p(q_ptr), nq, k,
+                                                     C.c_void_p(mask_words_ptr) if mask_words_ptr else None,
+                                                     C.c_uint64(slot_offset), C.c_void_p(keys_ptr), C.byref(k_eff)))
+        return int(k_eff.value)
+
+    def search_device_noalloc(self, q_ptr: int, nq: int, k: int, scores_ptr: int, slots_ptr: int) -> int:
+        """Like search_device (unfiltered) but guaranteed not to allocate: scratch is a fixed array inside
+        the library.  For callers that must keep away from the CUDA allocator while serving.  Limits:
+        nq <= 8, k <= 128, dim <= 4096.  Returns k_eff."""
+        k_eff = C.c_size_t(0)
+        self._check(self._lib.tv_search_device_noalloc(self._h, C.c_void_p(q_ptr), nq, k, C.c_void_p(scores_ptr),
+                                                        C.c_void_p(slots_ptr), C.byref(k_eff)))
+        return int(k_eff.value)
+
+    # ---- one filter, many searches (no counterpart in the reference, which rebuilds the mask on every call) ----
+    def prepare_mask_device(self, mask_words_ptr: int) -> None:
+        """Keeps the packed slot mask at `mask_words_ptr` (device memory, ceil(len/64) uint64 words, bit i of word
+        i // 64 = slot i) prepared on the device: its live code blocks are compacted once, and search_prepared /
+        search_device_prepared reuse them until the index changes."""
+        self._check(self._lib.tv_mask_prepare_device(self._h, C.c_void_p(mask_words_ptr)))
+
+    def prepare_mask_words(self, words: np.ndarray) -> None:
+        words = _typed_1d("words", words, np.uint64, "uint64")
+        self._check(self._lib.tv_mask_prepare_words(self._h, _ptr(words), words.size))
+
+    def search_prepared(self, queries: np.ndarray, k: int):
+        """search() under the prepared mask.  Returns (scores, slots) on a positional index, (scores, ids) on an
+        id-mapped one."""
+        idmap = self._KIND == 1
+        extra_fn = self._lib.tv_search_prepared
+        queries = _f32_2d("queries", queries)
+        k = _size("k", k)
+        nq, ncols = queries.shape
+        kk = min(k, len(self))
+        scores = np.empty((nq, max(kk, 1)), np.float32)
+        out = np.empty((nq, max(kk, 1)), np.uint64 if idmap else np.int64)
+        k_eff = C.c_size_t(0)
+        self._check(extra_fn(self._h, _ptr(queries), nq, ncols, k, _ptr(scores), None if idmap else _ptr(out),
+                             _ptr(out) if idmap else None, C.byref(k_eff)))
+        ke = int(k_eff.value)
+        return (scores.ravel()[: nq * ke].reshape(nq, ke).copy(), out.ravel()[: nq * ke].reshape(nq, ke).copy())
+
+    def search_device_prepared(self, q_ptr: int, nq: int, k: int, scores_ptr: int, slots_ptr: int) -> int:
+        k_eff = C.c_size_t(0)
+        self._check(self._lib.tv_search_device_prepared(self._h, C.c_void_p(q_ptr), nq, k, C.c_void_p(scores_ptr),
+                                                         C.c_void_p(slots_ptr), C.byref(k_eff)))
+        return int(k_eff.value)
+
+
     def _search_sliced(self, queries, k, fn, extra, out_dtype, chunk_size):
         """Per-query results do not depend on the other queries of a batch, so slices concatenate to exactly
         the result of one call."""
@@ -317,35 +381,6 @@ class TurboQuantIndex(_Base):
     def search_mask_words(self, queries: np.ndarray, k: int, words: np.ndarray):
         words = _typed_1d("words", words, np.uint64, "uint64")
         return self._search_raw(queries, k, self._lib.tv_search_mask_words, (_ptr(words), words.size), np.int64)
-
-    def search_device(self, q_ptr: int, nq: int, k: int, scores_ptr: int, slots_ptr: int, mask_words_ptr: int = 0) -> int:
-        """Device-resident search; returns k_eff.  Output rows have stride k_eff."""
-        k_eff = C.c_size_t(0)
-        self._check(self._lib.tv_search_device(self._h, C.c_void_p(q_ptr), nq, k,
-                                                C.c_void_p(mask_words_ptr) if mask_words_ptr else None,
-                                                C.c_void_p(scores_ptr), C.c_void_p(slots_ptr), C.byref(k_eff)))
-        return int(k_eff.value)
-
-    def search_device_keys(self, q_ptr: int, nq: int, k: int, keys_ptr: int, slot_offset: int = 0,
-                           mask_words_ptr: int = 0) -> int:
-        """Device-resident search of one shard of a slot-sharded index: writes rows of k 64-bit result keys
-        (ascending key = score descending, then global slot ascending; padded with EMPTY_KEY) with
-        `slot_offset` added to every slot.  All-gather the rows of every rank and pass them to
-        merge_keys_device.  Returns this shard's k_eff."""
-        k_eff = C.c_size_t(0)
-        self._check(self._lib.tv_search_device_keys(self._h, C.c_void_p(q_ptr), nq, k,
-                                                     C.c_void_p(mask_words_ptr) if mask_words_ptr else None,
-                                                     C.c_uint64(slot_offset), C.c_void_p(keys_ptr), C.byref(k_eff)))
-        return int(k_eff.value)
-
-    def search_device_noalloc(self, q_ptr: int, nq: int, k: int, scores_ptr: int, slots_ptr: int) -> int:
-        """Like search_device (unfiltered) but guaranteed not to allocate: scratch is a fixed array inside
-        the library.  For callers that must keep away from the CUDA allocator while serving.  Limits:
-        nq <= 8, k <= 128, dim <= 4096.  Returns k_eff."""
-        k_eff = C.c_size_t(0)
-        self._check(self._lib.tv_search_device_noalloc(self._h, C.c_void_p(q_ptr), nq, k, C.c_void_p(scores_ptr),
-                                                        C.c_void_p(slots_ptr), C.byref(k_eff)))
-        return int(k_eff.value)
 
     def swap_remove(self, idx: int) -> int:
         idx = _size("idx", idx)
@@ -426,11 +461,29 @@ class IdMapIndex(_Base):
             extra = (_ptr(allowlist), allowlist.size)
         return self._search_sliced(queries, k, self._lib.tv_search_allowlist, extra, np.uint64, chunk_size)
 
+    def prepare_allowlist(self, allowlist: np.ndarray) -> None:
+        """Resolves the ids once and keeps the resulting slot mask prepared on the device for search_prepared."""
+        allowlist = _typed_1d("allowlist", allowlist, np.uint64, "uint64")
+        if allowlist.size == 0:
+            raise ValueError("allowlist is empty")
+        self._check(self._lib.tv_mask_prepare_allowlist(self._h, _ptr(allowlist), allowlist.size))
+
     def __repr__(self):
         return f"IdMapIndex(dim={self.dim}, bit_width={self.bit_width}, len={len(self)})"
 
 
 EMPTY_KEY = 0xFFFFFFFFFFFFFFFF
+
+
+def measure_int8_peak(device: int = 0) -> float:
+    """int8 tensor rate of `device` in ops/s for the library's MMA form (multiply-add = 2 ops), measured by a short
+    kernel that only issues MMAs."""
+    lib = _native.load()
+    out = C.c_double(0.0)
+    rc = lib.tv_measure_int8_peak(int(device), C.byref(out))
+    if rc != 0:
+        raise RuntimeError(lib.tv_last_error(None).decode())
+    return float(out.value)
 
 
 def merge_keys_device(keys_ptr: int, n_lists: int, nq: int, k: int, scores_ptr: int, slots_ptr: int, *, device: int = 0,

@@ -51,6 +51,11 @@ SIGNATURES = {
                                       C.c_void_p, C.c_void_p, _szp]),
     "tv_search_device": (C.c_int, [_H, C.c_void_p, C.c_size_t, C.c_size_t, C.c_void_p, C.c_void_p, C.c_void_p, _szp]),
     "tv_search_device_noalloc": (C.c_int, [_H, C.c_void_p, C.c_size_t, C.c_size_t, C.c_void_p, C.c_void_p, _szp]),
+    "tv_mask_prepare_device": (C.c_int, [_H, C.c_void_p]),
+    "tv_mask_prepare_words": (C.c_int, [_H, C.c_void_p, C.c_size_t]),
+    "tv_mask_prepare_allowlist": (C.c_int, [_H, C.c_void_p, C.c_size_t]),
+    "tv_search_prepared": (C.c_int, [_H, C.c_void_p, C.c_size_t, C.c_size_t, C.c_size_t, C.c_void_p, C.c_void_p, C.c_void_p, _szp]),
+    "tv_search_device_prepared": (C.c_int, [_H, C.c_void_p, C.c_size_t, C.c_size_t, C.c_void_p, C.c_void_p, _szp]),
     "tv_prepare": (C.c_int, [_H]),
     "tv_blocked_bytes": (C.c_size_t, [_H]),
     "tv_export_blocked": (C.c_int, [_H, C.c_void_p, C.c_size_t, C.c_void_p, C.c_size_t]),
@@ -71,6 +76,7 @@ SIGNATURES = {
     "tv_calibrate": (C.c_int, [_H, C.c_void_p, C.c_size_t, C.c_size_t]),
     "tv_calibration": (C.c_int, [_H, C.c_void_p, C.c_void_p, C.c_size_t, _intp]),
     "tv_set_calibration": (C.c_int, [_H, C.c_size_t, C.c_void_p, C.c_void_p]),
+    "tv_measure_int8_peak": (C.c_int, [C.c_int, C.POINTER(C.c_double)]),
     "tv_launch_count": (C.c_uint64, [_H]),
     "tv_last_kernel_ms": (C.c_float, [_H]),
     "tv_last_main_kernel_ms": (C.c_float, [_H, _intp]),
@@ -103,3 +109,4 @@ ERR_ID_KEYERROR = {21}
 ERR_INDEXERROR = {31}
 SCORE_AUTO, SCORE_PERMUTE_DOT, SCORE_LUT_MULADD, SCORE_LUT_FLUSH = 0, 1, 2, 3
 OPT_SCORE_MODE, OPT_MMA_MIN_BATCH, OPT_FORCE_CAREFUL, OPT_TC_TILES, OPT_INGEST_PIPELINE, OPT_PD_SPLIT = 1, 2, 3, 4, 5, 6
+OPT_SMALL_SCAN, OPT_FAIL_NEXT = 7, 8

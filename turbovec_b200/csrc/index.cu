@@ -4,10 +4,13 @@
 #include <cuda_runtime.h>
 
 #include <algorithm>
+#include <atomic>
 #include <cmath>
+#include <condition_variable>
 #include <cstdio>
 #include <cstring>
 #include <mutex>
+#include <shared_mutex>
 #include <string>
 #include <thread>
 #include <unordered_map>
@@ -71,6 +74,100 @@ struct DeviceFlags {        // one pinned + one device copy of the status words 
     uint32_t k_eff;
 };
 
+// CUDA events around the launches of the dominant kernel (scan, ingest) of one call.
+struct Marks {
+    std::vector<cudaEvent_t> pool;
+    size_t used = 0;
+    float total_ms = 0.f;
+    int launches = 0;
+    ~Marks() { for (cudaEvent_t e : pool) cudaEventDestroy(e); }
+    void begin(cudaStream_t st) {
+        if (used + 2 > pool.size()) {
+            for (int i = 0; i < 64; ++i) {
+                cudaEvent_t e;
+                if (cudaEventCreate(&e) != cudaSuccess) return;
+                pool.push_back(e);
+            }
+        }
+        cudaEventRecord(pool[used], st);
+    }
+    void end(cudaStream_t st) {
+        if (used + 2 > pool.size()) return;
+        cudaEventRecord(pool[used + 1], st);
+        used += 2;
+    }
+    // after the stream has been synchronised: total time and count of the bracketed launches
+    void collect() {
+        float total = 0.f;
+        for (size_t i = 0; i + 1 < used; i += 2) {
+            float ms = 0.f;
+            if (cudaEventElapsedTime(&ms, pool[i], pool[i + 1]) == cudaSuccess) total += ms;
+        }
+        total_ms = total;
+        launches = int(used / 2);
+        used = 0;
+    }
+};
+
+// Everything one search call owns while it runs: a stream, status words, events and the scratch arrays
+// (grown on demand, reused).  A handle keeps a small pool of these so that searches from several host threads
+// overlap on the device, as the reference's `search(&self)` may run concurrently (turbovec/src/lib.rs:22-52).
+struct SearchCtx {
+    bool busy = false;
+    cudaStream_t stream = nullptr;
+    cudaEvent_t ev0 = nullptr, ev1 = nullptr;
+    Marks marks;
+    DeviceFlags *d_flags = nullptr;
+    DeviceFlags *h_flags = nullptr;
+    DeviceArray<float> d_stage;              // query upload
+    DeviceArray<float> d_qrot, d_qscale, d_qbias;
+    DeviceArray<uint8_t> d_luts;
+    DeviceArray<int8_t> d_weights;
+    DeviceArray<uint32_t> d_wfrag;
+    DeviceArray<uint64_t> d_mask;
+    DeviceArray<uint8_t> d_mask_bool;
+    DeviceArray<uint32_t> d_slots_in, d_live;
+    DeviceArray<uint64_t> d_cand, d_thr, d_topk, d_floor, d_keys_all;
+    DeviceArray<uint32_t> d_cnt;
+    DeviceArray<float> d_scores;
+    DeviceArray<int64_t> d_slots;
+    DeviceArray<uint64_t> d_keys_tmp;        // staging of tv_search_device_keys when the shard holds fewer than k vectors
+    PinnedArray<float> h_scores;
+    PinnedArray<int64_t> h_slots;
+    cudaError_t init() {
+        cudaError_t e = cudaStreamCreateWithFlags(&stream, cudaStreamNonBlocking);
+        if (e == cudaSuccess) e = cudaEventCreate(&ev0);
+        if (e == cudaSuccess) e = cudaEventCreate(&ev1);
+        if (e == cudaSuccess) e = cudaMalloc(&d_flags, sizeof(DeviceFlags));
+        if (e == cudaSuccess) e = cudaMallocHost(&h_flags, sizeof(DeviceFlags));
+        // the event pool of the common schedules up front, so that a search creates nothing
+        for (int i = 0; i < 64 && e == cudaSuccess; ++i) {
+            cudaEvent_t ev;
+            e = cudaEventCreate(&ev);
+            if (e == cudaSuccess) marks.pool.push_back(ev);
+        }
+        return e;
+    }
+    ~SearchCtx() {
+        if (stream) cudaStreamSynchronize(stream);
+        if (d_flags) cudaFree(d_flags);
+        if (h_flags) cudaFreeHost(h_flags);
+        if (ev0) cudaEventDestroy(ev0);
+        if (ev1) cudaEventDestroy(ev1);
+        if (stream) cudaStreamDestroy(stream);
+    }
+};
+constexpr int kSearchCtxs = 2;
+
+// An allow-mask kept on the device between searches (tv_mask_prepare_*): words, live-block list and the two
+// counts the kernels read.  Any change of the index invalidates it.
+struct PreparedMask {
+    bool valid = false;
+    DeviceArray<uint64_t> words;
+    DeviceArray<uint32_t> live;
+    DeviceArray<unsigned long long> counts;  // [0] = allowed slots, [1] low word = live blocks
+};
+
 }  // namespace
 
 struct tv_index {
@@ -83,7 +180,10 @@ struct tv_index {
     int sm_count = 148;
     size_t smem_limit = 0;
 
-    std::mutex mu;
+    // Readers and writers: searches hold the lock shared and take a SearchCtx from the pool; every call that changes
+    // the index, and the accessors that use the handle's own stream, hold it exclusively.
+    std::shared_mutex mu;
+    std::mutex stat_mu;          // error text / detail and the timing figures of the last call
     std::string last_error;
     size_t err_vec = 0, err_coord = 0;
     float err_value = 0.f;
@@ -96,14 +196,16 @@ struct tv_index {
     int pd_split = 1;            // 1: the small-batch permute-dot scan uses the split level lookup where the codebook allows it
     int ingest_pipeline = 1;     // 1: whole code blocks of an uncalibrated add go through the pipelined ingest kernel
     int tc_tiles = 1;            // accumulator tiles per B slab in the tcgen05 scan (1 or 2); 1 measured faster
+    int small_scan = 5;          // permute-dot scan for up to 16 queries: -1 = scan_pd_kernel, else a scan_small_kernel variant
+                                 // (5 = four-stage rings, two CTAs per SM, swizzled tensor copies: the fastest measured)
+    int fail_next = 0;           // test hook (TV_OPT_FAIL_NEXT): the next device allocation / upload of a call reports failure
 
-    cudaStream_t stream = nullptr;
+    cudaStream_t stream = nullptr;           // mutations and accessors
     cudaEvent_t ev0 = nullptr, ev1 = nullptr;
-    uint64_t launches = 0;
+    cudaEvent_t ev_mut = nullptr;            // recorded on `stream` after every mutation; searches wait for it
+    std::atomic<uint64_t> launches{0};
     float last_ms = 0.f;
-    // per-launch CUDA events around the dominant kernels (scan, ingest) of the last call
-    std::vector<cudaEvent_t> ev_pool;
-    size_t ev_used = 0;
+    Marks marks;                             // ingest launches of the last add
     float last_main_ms = 0.f;
     int last_main_launches = 0;
 
@@ -115,7 +217,6 @@ struct tv_index {
     DeviceArray<uint16_t> d_perm;            // [2][dim]
     DeviceArray<float> d_codebook;           // boundaries (16 slots) then centroids (16 slots)
     DeviceArray<uint2> d_qgrid;              // quantisation grid of the pipelined ingest kernel
-    DeviceArray<uint64_t> d_keys_tmp;        // staging of tv_search_device_keys when the shard holds fewer than k vectors
     QuantGrid qgrid;                         // cells == nullptr: the codebook has no valid grid
     DeviceArray<uint8_t> d_store_bank;       // exchange layout of the pipelined ingest kernel (empty: plain rows)
     DeviceArray<uint16_t> d_perm1_exchange;
@@ -130,28 +231,22 @@ struct tv_index {
     float *d_scales = nullptr;
     size_t scales_cap = 0;
 
-    // scratch
-    DeviceArray<float> d_stage;              // ingest staging / query upload
+    // scratch of the mutating calls
+    DeviceArray<float> d_stage;              // ingest staging (calibration sample)
+    DeviceArray<uint8_t> d_row;              // one row's byte-groups (get_row / set_row)
     // host-memory adds: two pinned + two device staging buffers, a copy stream and per-buffer events
     PinnedArray<float> h_add[2];
     DeviceArray<float> d_add[2];
     cudaStream_t copy_stream = nullptr;
     cudaEvent_t ev_copied[2] = {nullptr, nullptr}, ev_consumed[2] = {nullptr, nullptr};
-    DeviceArray<float> d_qrot, d_qscale, d_qbias;
-    DeviceArray<uint8_t> d_luts;
-    DeviceArray<int8_t> d_weights;
-    DeviceArray<uint32_t> d_wfrag;
-    DeviceArray<uint64_t> d_mask;
-    DeviceArray<uint8_t> d_mask_bool;
-    DeviceArray<uint32_t> d_slots_in, d_live;
-    DeviceArray<uint64_t> d_cand, d_thr, d_topk;
-    DeviceArray<uint32_t> d_cnt;
-    DeviceArray<float> d_scores;
-    DeviceArray<int64_t> d_slots;
     DeviceFlags *d_flags = nullptr;
     DeviceFlags *h_flags = nullptr;
-    PinnedArray<float> h_scores;
-    PinnedArray<int64_t> h_slots;
+
+    // search contexts
+    SearchCtx ctx[kSearchCtxs];
+    std::mutex ctx_mu;
+    std::condition_variable ctx_cv;
+    PreparedMask prepared;
 
     // id map (ids never reach the device; id_map.rs:221-272)
     std::vector<uint64_t> slot_to_id;
@@ -177,7 +272,7 @@ struct tv_index {
         if (h_flags) cudaFreeHost(h_flags);
         if (ev0) cudaEventDestroy(ev0);
         if (ev1) cudaEventDestroy(ev1);
-        for (cudaEvent_t e : ev_pool) cudaEventDestroy(e);
+        if (ev_mut) cudaEventDestroy(ev_mut);
         for (int b = 0; b < 2; ++b) {
             if (ev_copied[b]) cudaEventDestroy(ev_copied[b]);
             if (ev_consumed[b]) cudaEventDestroy(ev_consumed[b]);
@@ -190,37 +285,36 @@ struct tv_index {
 namespace {
 
 int fail(tv_index *h, int code, const std::string &msg) {
-    if (h) h->last_error = msg;
-    else g_create_error = msg;
+    if (h) {
+        std::lock_guard<std::mutex> g(h->stat_mu);
+        h->last_error = msg;
+    } else {
+        g_create_error = msg;
+    }
     return code;
 }
 
-// Brackets one launch of a dominant kernel with two events from the handle's pool.
-void mark_begin(tv_index *h) {
-    if (h->ev_used + 2 > h->ev_pool.size()) {
-        for (int i = 0; i < 64; ++i) {
-            cudaEvent_t e;
-            if (cudaEventCreate(&e) != cudaSuccess) return;
-            h->ev_pool.push_back(e);
-        }
-    }
-    cudaEventRecord(h->ev_pool[h->ev_used], h->stream);
-}
-void mark_end(tv_index *h) {
-    if (h->ev_used + 2 > h->ev_pool.size()) return;
-    cudaEventRecord(h->ev_pool[h->ev_used + 1], h->stream);
-    h->ev_used += 2;
-}
-// After the stream has been synchronised: total time and count of the bracketed launches.
+// Brackets one ingest launch with two events from the handle's pool.
+void mark_begin(tv_index *h) { h->marks.begin(h->stream); }
+void mark_end(tv_index *h) { h->marks.end(h->stream); }
 void collect_marks(tv_index *h) {
-    float total = 0.f;
-    for (size_t i = 0; i + 1 < h->ev_used; i += 2) {
-        float ms = 0.f;
-        if (cudaEventElapsedTime(&ms, h->ev_pool[i], h->ev_pool[i + 1]) == cudaSuccess) total += ms;
-    }
-    h->last_main_ms = total;
-    h->last_main_launches = int(h->ev_used / 2);
-    h->ev_used = 0;
+    h->marks.collect();
+    h->last_main_ms = h->marks.total_ms;
+    h->last_main_launches = h->marks.launches;
+}
+
+// Called at the end of every call that changed device state on the handle's stream: searches run on their own
+// streams and wait for this event first.  Also drops a prepared mask, which describes the index as it was.
+void mutation_done(tv_index *h) {
+    cudaEventRecord(h->ev_mut, h->stream);
+    h->prepared.valid = false;
+}
+
+// Test hook: with TV_OPT_FAIL_NEXT set, the next guarded allocation or upload of a call reports
+// cudaErrorMemoryAllocation instead of running, once.
+cudaError_t injected_failure(tv_index *h) {
+    if (h->fail_next > 0 && --h->fail_next == 0) return cudaErrorMemoryAllocation;
+    return cudaSuccess;
 }
 
 #define TV_CUDA(expr)                                                                              \
@@ -317,6 +411,7 @@ int upload_calibration(tv_index *h) {
 // Grows the code / scale arrays to hold `n_total` vectors.  New space is zero so that padding lanes read
 // as zero bytes (pack.rs:347-358).  Growth is geometric (x1.5) and copies once.
 int ensure_capacity(tv_index *h, size_t n_total) {
+    TV_CUDA(injected_failure(h));
     const size_t blocks = (n_total + kBlock - 1) / kBlock;
     const size_t block_bytes = size_t(h->ngroups) * kBlock;
     if (blocks > h->code_blocks_cap) {
@@ -452,14 +547,24 @@ int add_rows(tv_index *h, const float *x, size_t n, size_t dim, bool on_device) 
         if (cudaPointerGetAttributes(&attr, x) == cudaSuccess) src_pinned = attr.type == cudaMemoryTypeHost;
         else cudaGetLastError();
     }
+    // A failure after the first launch leaves bytes in lanes past `len`: they are cleared again before the
+    // call returns, so that a failed add leaves the index exactly as it was (lib.rs:889-930).
+    cudaError_t step_err = cudaSuccess;
+    const char *step_what = "";
+#define TV_STEP(expr)                                              \
+    {                                                              \
+        step_err = (expr);                                         \
+        if (step_err != cudaSuccess) { step_what = #expr; break; } \
+    }
     TV_CUDA(cudaEventRecord(h->ev0, h->stream));
     size_t chunk_index = 0;
     for (size_t done = 0; done < n; done += chunk_rows, ++chunk_index) {
         const size_t rows = std::min(chunk_rows, n - done);
         const float *src = x + done * dim;
+        TV_STEP(injected_failure(h));
         if (!on_device) {
             const int b = int(chunk_index & 1);
-            if (chunk_index >= 2) TV_CUDA(cudaEventSynchronize(h->ev_consumed[b]));   // the encode of chunk i-2 has read d_add[b]
+            if (chunk_index >= 2) TV_STEP(cudaEventSynchronize(h->ev_consumed[b]));   // the encode of chunk i-2 has read d_add[b]
             const size_t bytes = rows * dim * 4;
             const float *h_src = h->h_add[b].ptr;
             if (src_pinned) {
@@ -474,9 +579,9 @@ int add_rows(tv_index *h, const float *x, size_t n, size_t dim, bool on_device) 
                 }
                 for (auto &th : pool) th.join();
             }
-            TV_CUDA(cudaMemcpyAsync(h->d_add[b].ptr, h_src, bytes, cudaMemcpyHostToDevice, h->copy_stream));
-            TV_CUDA(cudaEventRecord(h->ev_copied[b], h->copy_stream));
-            TV_CUDA(cudaStreamWaitEvent(h->stream, h->ev_copied[b], 0));
+            TV_STEP(cudaMemcpyAsync(h->d_add[b].ptr, h_src, bytes, cudaMemcpyHostToDevice, h->copy_stream));
+            TV_STEP(cudaEventRecord(h->ev_copied[b], h->copy_stream));
+            TV_STEP(cudaStreamWaitEvent(h->stream, h->ev_copied[b], 0));
             src = h->d_add[b].ptr;
         }
         p.x = src; p.n = int64_t(rows); p.slot0 = int64_t(h->n + done); p.row_base = int64_t(done);
@@ -489,7 +594,7 @@ int add_rows(tv_index *h, const float *x, size_t n, size_t dim, bool on_device) 
         if (head > 0) {
             p.n = head;
             mark_begin(h);
-            TV_CUDA(launch_ingest(p, V, h->stream));
+            TV_STEP(launch_ingest(p, V, h->stream));
             mark_end(h);
             h->launches++;
         }
@@ -498,11 +603,25 @@ int add_rows(tv_index *h, const float *x, size_t n, size_t dim, bool on_device) 
             p.exact_sums = h->ingest_pipeline == 2;
             if (h->exchange_ready) { p.store_bank = h->d_store_bank.ptr; p.perm1_exchange = h->d_perm1_exchange.ptr; }
             mark_begin(h);
-            TV_CUDA(launch_ingest_fast(p, h->qgrid, h->sm_count, h->smem_limit, &h->d_flags->error, h->stream));
+            TV_STEP(launch_ingest_fast(p, h->qgrid, h->sm_count, h->smem_limit, &h->d_flags->error, h->stream));
             mark_end(h);
             h->launches++;
         }
-        if (!on_device) TV_CUDA(cudaEventRecord(h->ev_consumed[chunk_index & 1], h->stream));
+        if (!on_device) TV_STEP(cudaEventRecord(h->ev_consumed[chunk_index & 1], h->stream));
+    }
+#undef TV_STEP
+    if (step_err != cudaSuccess) {
+        cudaGetLastError();
+        cudaStreamSynchronize(h->stream);
+        if (h->copy_stream) cudaStreamSynchronize(h->copy_stream);
+        const int64_t total = int64_t(n) * h->ngroups;
+        clear_slots_kernel<<<unsigned(std::min<int64_t>((total + 255) / 256, 65535)), 256, 0, h->stream>>>(
+            h->d_codes, h->ngroups, int64_t(h->n), int64_t(h->n + n));
+        cudaStreamSynchronize(h->stream);
+        h->marks.used = 0;
+        if (was_lazy) { h->dim = 0; h->tables_ready = false; }
+        return fail(h, step_err == cudaErrorMemoryAllocation ? TV_ERR_OUT_OF_MEMORY : TV_ERR_CUDA,
+                    std::string(step_what) + ": " + cudaGetErrorString(step_err));
     }
     TV_CUDA(cudaEventRecord(h->ev1, h->stream));
     TV_CUDA(cudaMemcpyAsync(&h->h_flags->first_invalid, &h->d_flags->first_invalid, 8, cudaMemcpyDeviceToHost, h->stream));
@@ -530,6 +649,7 @@ int add_rows(tv_index *h, const float *x, size_t n, size_t dim, bool on_device) 
                         " is not finite or exceeds 1e16 in magnitude (value " + std::to_string(h->err_value) + ")");
     }
     h->n += n;
+    mutation_done(h);
     return TV_OK;
 }
 
@@ -538,100 +658,213 @@ struct MaskSpec {
     const uint64_t *words_host = nullptr; size_t n_words = 0;
     const uint64_t *words_device = nullptr;
     const uint32_t *slots_host = nullptr; size_t n_slots = 0;
-    bool any() const { return bool_host || words_host || words_device || slots_host; }
+    bool prepared = false;                 // use the handle's prepared mask
+    bool any() const { return bool_host || words_host || words_device || slots_host || prepared; }
 };
 
 int candidate_capacity(size_t k) { return k <= 512 ? 4096 : 8192; }
+constexpr size_t kPageK = 4096;            // most results one selection pass keeps per query; larger k runs in pages
 
-// The whole search on the handle's stream.  Results land in d_scores/d_slots (row stride k) unless
-// out_scores_dev is given (row stride k_eff).
-int search_core(tv_index *h, const float *queries, bool queries_on_device, size_t nq, size_t k, const MaskSpec &mask,
-                float *out_scores_dev, int64_t *out_slots_dev, size_t *k_eff_out, uint64_t *out_keys_dev = nullptr,
-                uint64_t key_offset = 0) {
-    const size_t dim = h->dim, n = h->n;
+// Takes a search context from the handle's pool for the duration of a call.
+struct CtxLease {
+    tv_index *h;
+    SearchCtx *c = nullptr;
+    explicit CtxLease(tv_index *handle) : h(handle) {
+        std::unique_lock<std::mutex> g(h->ctx_mu);
+        for (;;) {
+            for (int i = 0; i < kSearchCtxs; ++i)
+                if (!h->ctx[i].busy) { c = &h->ctx[i]; break; }
+            if (c) break;
+            h->ctx_cv.wait(g);
+        }
+        c->busy = true;
+    }
+    ~CtxLease() {
+        { std::lock_guard<std::mutex> g(h->ctx_mu); c->busy = false; }
+        h->ctx_cv.notify_one();
+    }
+};
+
+// The device buffers one search runs on: the context's arrays, or the fixed array of the allocation-free entry point.
+struct SearchScratch {
+    float *q_rot, *qscale, *qbias;
+    int8_t *weights;
+    uint32_t *wfrag;
+    uint8_t *luts;
+    uint64_t *cand, *thr, *topk, *lo;      // lo: lowest admissible key per query (paged top-k), or nullptr
+    uint32_t *cnt;
+    size_t w_rows, dim_pad;
+    int cap;
+    bool allow_tc;
+};
+
+struct MaskOnDevice {
+    const uint64_t *words = nullptr;
+    const uint32_t *live = nullptr;
+    const uint32_t *n_live = nullptr;
+    const unsigned long long *n_allowed = nullptr;
+};
+
+// Uploads / packs the allow-mask of a call and compacts its live blocks.  `words_buf` / `live_buf` receive the data,
+// the two counters are zeroed by the caller.
+int build_mask(tv_index *h, cudaStream_t st, const MaskSpec &mask, DeviceArray<uint64_t> &words_buf,
+               DeviceArray<uint8_t> &bool_buf, DeviceArray<uint32_t> &slots_buf, DeviceArray<uint32_t> &live_buf,
+               unsigned long long *d_n_allowed, uint32_t *d_n_live, MaskOnDevice &out) {
+    const size_t n = h->n, n_words = (n + 63) / 64, n_blocks = (n + kBlock - 1) / kBlock;
+    TV_CUDA(injected_failure(h));
+    TV_CUDA(words_buf.reserve(n_words));
+    if (mask.words_device) {
+        TV_CUDA(cudaMemcpyAsync(words_buf.ptr, mask.words_device, n_words * 8, cudaMemcpyDeviceToDevice, st));
+    } else if (mask.words_host) {
+        TV_CUDA(cudaMemcpyAsync(words_buf.ptr, mask.words_host, n_words * 8, cudaMemcpyHostToDevice, st));
+    } else if (mask.bool_host) {
+        TV_CUDA(bool_buf.reserve(n));
+        TV_CUDA(cudaMemcpyAsync(bool_buf.ptr, mask.bool_host, n, cudaMemcpyHostToDevice, st));
+        TV_CUDA(launch_pack_bool_mask(bool_buf.ptr, int64_t(n), words_buf.ptr, st));
+        h->launches++;
+    } else {
+        TV_CUDA(slots_buf.reserve(mask.n_slots));
+        TV_CUDA(cudaMemsetAsync(words_buf.ptr, 0, n_words * 8, st));
+        TV_CUDA(cudaMemcpyAsync(slots_buf.ptr, mask.slots_host, mask.n_slots * 4, cudaMemcpyHostToDevice, st));
+        TV_CUDA(launch_scatter_slots(slots_buf.ptr, int64_t(mask.n_slots), words_buf.ptr, st));
+        h->launches++;
+    }
+    TV_CUDA(live_buf.reserve(n_blocks));
+    TV_CUDA(launch_mask_stats(words_buf.ptr, int64_t(n), d_n_allowed, live_buf.ptr, d_n_live, st));
+    h->launches++;
+    out.words = words_buf.ptr; out.live = live_buf.ptr; out.n_live = d_n_live; out.n_allowed = d_n_allowed;
+    return TV_OK;
+}
+
+ScanParams base_scan_params(const tv_index *h, int mode) {
+    ScanParams sp{};
+    sp.codes = h->d_codes; sp.vec_scales = h->d_scales; sp.n = int64_t(h->n); sp.ngroups = h->ngroups; sp.bits = h->bits;
+    sp.mode = mode;
+    for (int w = 0; w < 4; ++w) {
+        uint32_t word = 0;
+        for (int b = 0; b < 4; ++b) word |= uint32_t(uint8_t(h->levels[4 * w + b])) << (8 * b);
+        sp.level_words[w] = word;
+    }
+    sp.pd_split = h->pd_split;
+    return sp;
+}
+
+// Which kernel family a batch runs on.
+struct ScanPlan {
+    bool use_tc = false;       // tensor-memory scan (tcgen05)
+    bool use_small = false;    // scan_small_kernel (up to 16 permute-dot queries)
+    int lut_width = 0;         // queries per launch of the CUDA-core LUT scan
+};
+
+int plan_scan(tv_index *h, int mode, size_t nq, bool allow_tc, ScanPlan &plan) {
     const int ng = h->ngroups;
-    const int mode = resolve_mode(h);
-    const size_t kk = std::min(k, n);
-    *k_eff_out = 0;
-    if (nq == 0 || kk == 0) return TV_OK;
-    if (kk > 4096) return fail(h, TV_ERR_UNSUPPORTED, "k above 4096 is not supported by the device top-k");
-    TV_CUDA(cudaSetDevice(h->device));
-    cudaStream_t st = h->stream;
-    const int cap = candidate_capacity(kk);
-    const size_t nq_pad = (nq + 15) / 16 * 16;
-    const int mt_total = int(nq_pad / 16);
-    const size_t dim_pad = (dim + 127) / 128 * 128;
-    const int ksteps = (ng + 15) / 16;
-
-    // ---- buffers ----
-    if (!queries_on_device) TV_CUDA(h->d_stage.reserve(nq * dim));
-    TV_CUDA(h->d_qrot.reserve(nq * dim));
-    TV_CUDA(h->d_qscale.reserve(nq_pad));
-    TV_CUDA(h->d_qbias.reserve(nq_pad));
-    const size_t w_rows = (nq + 255) / 256 * 256;
     // measured on 1.25 M and 10 M x 1536 4-bit: mma.sync 0.67 / 3.6 ms up to 32 queries, 0.89 / 5.1 ms from 33 on,
     // tcgen05 0.83 / 5.1 ms flat; on 1 M x 3072 2-bit the CUDA-core LUT scan costs 0.5 ms per query beyond 4,
     // tcgen05 4.2 ms flat
     const int64_t tc_from = h->mma_min_batch >= 0 ? h->mma_min_batch : (mode == TV_SCORE_PERMUTE_DOT ? 33 : 8);
-    const bool use_tc = tc_from > 0 && int64_t(nq) >= tc_from && scan_tc_supported(h->bits, mode, ng);
-    if (mode == TV_SCORE_PERMUTE_DOT) {
-        TV_CUDA(h->d_weights.reserve(w_rows * dim_pad));
-        TV_CUDA(h->d_wfrag.reserve(size_t(ksteps) * mt_total * 32 * 4));
-    } else {
-        TV_CUDA(h->d_luts.reserve(w_rows * size_t(ng) * 32));     // padded to whole query groups for the tensor path
-    }
-    TV_CUDA(h->d_cand.reserve(nq * size_t(cap)));
-    TV_CUDA(h->d_cnt.reserve(nq));
-    TV_CUDA(h->d_thr.reserve(nq));
-    TV_CUDA(h->d_topk.reserve(nq * kk));
-    if (!out_scores_dev) {
-        TV_CUDA(h->d_scores.reserve(nq * kk));
-        TV_CUDA(h->d_slots.reserve(nq * kk));
-    }
-    const size_t n_blocks = (n + kBlock - 1) / kBlock;
-    const size_t n_words = (n + 63) / 64;
-
-    // ---- inputs ----
-    const float *dq = queries;
-    if (!queries_on_device) {
-        TV_CUDA(cudaMemcpyAsync(h->d_stage.ptr, queries, nq * dim * 4, cudaMemcpyHostToDevice, st));
-        dq = h->d_stage.ptr;
-    }
-    DeviceFlags init{};
-    init.first_invalid = ~0ull;
-    *h->h_flags = init;
-    TV_CUDA(cudaMemcpyAsync(h->d_flags, h->h_flags, sizeof(DeviceFlags), cudaMemcpyHostToDevice, st));
-    TV_CUDA(cudaEventRecord(h->ev0, st));
-
-    const uint64_t *d_mask = nullptr;
-    if (mask.any()) {
-        if (mask.words_device) {
-            TV_CUDA(h->d_mask.reserve(n_words));
-            TV_CUDA(cudaMemcpyAsync(h->d_mask.ptr, mask.words_device, n_words * 8, cudaMemcpyDeviceToDevice, st));
-        } else if (mask.words_host) {
-            TV_CUDA(h->d_mask.reserve(n_words));
-            TV_CUDA(cudaMemcpyAsync(h->d_mask.ptr, mask.words_host, n_words * 8, cudaMemcpyHostToDevice, st));
-        } else if (mask.bool_host) {
-            TV_CUDA(h->d_mask.reserve(n_words));
-            TV_CUDA(h->d_mask_bool.reserve(n));
-            TV_CUDA(cudaMemcpyAsync(h->d_mask_bool.ptr, mask.bool_host, n, cudaMemcpyHostToDevice, st));
-            TV_CUDA(launch_pack_bool_mask(h->d_mask_bool.ptr, int64_t(n), h->d_mask.ptr, st));
-            h->launches++;
-        } else {
-            TV_CUDA(h->d_mask.reserve(n_words));
-            TV_CUDA(h->d_slots_in.reserve(mask.n_slots));
-            TV_CUDA(cudaMemsetAsync(h->d_mask.ptr, 0, n_words * 8, st));
-            TV_CUDA(cudaMemcpyAsync(h->d_slots_in.ptr, mask.slots_host, mask.n_slots * 4, cudaMemcpyHostToDevice, st));
-            TV_CUDA(launch_scatter_slots(h->d_slots_in.ptr, int64_t(mask.n_slots), h->d_mask.ptr, st));
-            h->launches++;
+    plan.use_tc = allow_tc && tc_from > 0 && int64_t(nq) >= tc_from && scan_tc_supported(h->bits, mode, ng);
+    if (mode != TV_SCORE_PERMUTE_DOT) {
+        plan.lut_width = scan_lut_width(ng, h->smem_limit);
+        if (!plan.use_tc && plan.lut_width == 0) {
+            // not even one query's tables fit in shared memory: the tensor-memory scan takes the tables from global memory
+            if (allow_tc && scan_tc_supported(h->bits, mode, ng)) plan.use_tc = true;
+            else return fail(h, TV_ERR_UNSUPPORTED, "the u8 tables of one query (" + std::to_string(size_t(ng) * 32) +
+                                                        " bytes) exceed shared memory and this score mode has no tensor-memory scan");
         }
-        TV_CUDA(h->d_live.reserve(n_blocks));
-        TV_CUDA(launch_mask_stats(h->d_mask.ptr, int64_t(n), &h->d_flags->n_allowed, h->d_live.ptr, &h->d_flags->n_live, st));
-        h->launches++;
-        d_mask = h->d_mask.ptr;
     }
+    return TV_OK;
+}
 
-    // ---- query preparation ----
+// Query preparation, then scan + select over a geometric chunk schedule, all enqueued on `st`.
+//   careful: chunks never exceed the candidate capacity, so no list can overflow whatever the data order.
+int enqueue_search(tv_index *h, cudaStream_t st, Marks *marks, const SearchScratch &S, const ScanPlan &plan, int mode,
+                   size_t nq, size_t kk, const MaskOnDevice &m, uint32_t *d_overflow, uint32_t *d_error, bool careful) {
+    const size_t n = h->n;
+    const int ng = h->ngroups;
+    const size_t n_blocks = (n + kBlock - 1) / kBlock;
+    const int mt_total = int((nq + 15) / 16);
+    CandidateBuffers cb{};
+    cb.cand = S.cand; cb.cnt = S.cnt; cb.thr = S.thr; cb.topk = S.topk; cb.lo = S.lo;
+    cb.overflow = d_overflow; cb.error = d_error; cb.cap = S.cap; cb.k = int(kk);
+
+    ScanParams sp = base_scan_params(h, mode);
+    sp.qscale = S.qscale; sp.qbias = S.qbias;
+    sp.mask = m.words; sp.live_blocks = m.live; sp.n_live = m.n_live;
+    sp.cb = cb; sp.wfrag = S.wfrag; sp.mtiles_total = mt_total; sp.luts = S.luts;
+    const bool use_small = plan.use_small && !plan.use_tc;
+
+    TV_CUDA(cudaMemsetAsync(S.cnt, 0, nq * 4, st));
+    TV_CUDA(cudaMemsetAsync(S.thr, 0xff, nq * 8, st));
+    TV_CUDA(cudaMemsetAsync(S.topk, 0xff, nq * kk * 8, st));
+    // Chunk 0 holds at most `cap` vectors, so every one of them may pass.  Later chunks grow so that the
+    // expected number of candidates per query, k * |chunk| / |seen|, stays near cap / 4.
+    // The tensor-memory scan pays for dense candidates (its epilogue re-reads a 32 x 32 tile of scores
+    // whenever one of them passes), so its chunks grow gently at first: x24, x10, then the list-capacity rule.
+    const size_t first = size_t(S.cap) / kBlock;
+    const double growth = std::max(0.5, double(S.cap) / (4.0 * double(kk)));
+    size_t begin = 0;
+    int stage = 0;
+    while (begin < n_blocks) {
+        size_t len = first;
+        if (!careful && begin > 0) {
+            double g = growth;
+            if (plan.use_tc) g = std::min(g, stage == 1 ? 24.0 : (stage == 2 ? 10.0 : g));
+            len = std::max<size_t>(first, size_t(double(begin) * g));
+            if (begin + len + len / 2 >= n_blocks) len = n_blocks - begin;   // no short tail chunk
+        }
+        const size_t end = std::min(n_blocks, begin + len);
+        sp.pos_begin = uint32_t(begin); sp.pos_end = uint32_t(end);
+        // first chunk on the tensor-memory path without a filter (the host then knows how many vectors
+        // the chunk holds): every key is written in place, nothing is counted
+        const bool dense = plan.use_tc && stage == 0 && !careful && m.words == nullptr && S.lo == nullptr;
+        sp.dense = dense ? 1 : 0;
+        ++stage;
+        if (plan.use_tc) {
+            sp.q_base = 0; sp.nq = int(nq); sp.mtile_base = 0;
+            if (marks) marks->begin(st);
+            if (mode == TV_SCORE_PERMUTE_DOT)
+                TV_CUDA(launch_scan_tc(sp, S.weights, int(S.w_rows), int(S.dim_pad), h->sm_count, h->tc_tiles, st));
+            else
+                TV_CUDA(launch_scan_tc(sp, reinterpret_cast<const int8_t *>(S.luts), int(S.w_rows), ng * 32, h->sm_count, 1, st));
+            if (marks) marks->end(st);
+            h->launches++;
+        } else if (use_small) {
+            sp.q_base = 0; sp.nq = int(nq); sp.mtile_base = 0;
+            if (marks) marks->begin(st);
+            TV_CUDA(launch_scan_small(sp, S.weights, int(S.dim_pad), h->code_blocks_cap * size_t(ng) * kBlock, h->small_scan,
+                                      h->sm_count, h->smem_limit, st));
+            if (marks) marks->end(st);
+            h->launches++;
+        } else if (mode == TV_SCORE_PERMUTE_DOT) {
+            for (size_t q0 = 0; q0 < nq; q0 += 64) {
+                sp.q_base = int(q0); sp.nq = int(std::min<size_t>(64, nq - q0)); sp.mtile_base = int(q0 / 16);
+                if (marks) marks->begin(st);
+                TV_CUDA(launch_scan_pd(sp, h->sm_count, st));
+                if (marks) marks->end(st);
+                h->launches++;
+            }
+        } else {
+            for (size_t q0 = 0; q0 < nq; q0 += size_t(plan.lut_width)) {
+                sp.q_base = int(q0); sp.nq = int(std::min<size_t>(size_t(plan.lut_width), nq - q0));
+                if (marks) marks->begin(st);
+                TV_CUDA(launch_scan_lut(sp, h->sm_count, st));
+                if (marks) marks->end(st);
+                h->launches++;
+            }
+        }
+        TV_CUDA(launch_select(cb, int(nq), dense ? int((end - sp.pos_begin) * kBlock) : 0, st));
+        h->launches++;
+        begin = end;
+    }
+    return TV_OK;
+}
+
+int enqueue_query_prep(tv_index *h, cudaStream_t st, const SearchScratch &S, const ScanPlan &plan, int mode, const float *dq,
+                       size_t nq, unsigned long long *d_first_invalid) {
+    const size_t dim = h->dim;
+    const int ng = h->ngroups;
+    const int ksteps = (ng + 15) / 16;
+    const int mt_total = int((nq + 15) / 16);
     QueryPrepParams qp{};
     qp.queries = dq; qp.nq = int(nq); qp.dim = int(dim); qp.bits = h->bits; qp.ngroups = ng;
     qp.mode = mode;
@@ -640,135 +873,193 @@ int search_core(tv_index *h, const float *queries, bool queries_on_device, size_
     qp.centroids = h->d_codebook.ptr + 16;
     if (!h->shift.empty()) { qp.shift = h->d_calib.ptr; qp.scale_tq = h->d_calib.ptr + dim; }
     qp.level_scale = h->level_scale;
-    qp.q_rot = h->d_qrot.ptr; qp.qscale = h->d_qscale.ptr; qp.qbias = h->d_qbias.ptr;
-    qp.luts = h->d_luts.ptr; qp.weights = h->d_weights.ptr; qp.dim_pad = int(dim_pad);
-    qp.wfrag = h->d_wfrag.ptr; qp.mtiles_total = mt_total;
-    qp.first_invalid = &h->d_flags->first_invalid;
+    qp.q_rot = S.q_rot; qp.qscale = S.qscale; qp.qbias = S.qbias;
+    qp.luts = S.luts; qp.weights = S.weights; qp.dim_pad = int(S.dim_pad);
+    qp.wfrag = S.wfrag; qp.mtiles_total = mt_total;
+    qp.first_invalid = d_first_invalid;
     if (mode == TV_SCORE_PERMUTE_DOT) {
-        TV_CUDA(cudaMemsetAsync(h->d_wfrag.ptr, 0, size_t(ksteps) * mt_total * 32 * 16, st));
-        if (use_tc) TV_CUDA(cudaMemsetAsync(h->d_weights.ptr, 0, w_rows * dim_pad, st));
-    } else if (use_tc) {
-        TV_CUDA(cudaMemsetAsync(h->d_luts.ptr, 0, w_rows * size_t(ng) * 32, st));
+        TV_CUDA(cudaMemsetAsync(S.wfrag, 0, size_t(ksteps) * mt_total * 32 * 16, st));
+        if (plan.use_tc) TV_CUDA(cudaMemsetAsync(S.weights, 0, S.w_rows * S.dim_pad, st));
+    } else if (plan.use_tc) {
+        TV_CUDA(cudaMemsetAsync(S.luts, 0, S.w_rows * size_t(ng) * 32, st));
     }
     TV_CUDA(launch_query_prep(qp, st));
     h->launches++;
+    return TV_OK;
+}
 
-    // ---- scan + select over a geometric chunk schedule ----
-    CandidateBuffers cb{};
-    cb.cand = h->d_cand.ptr; cb.cnt = h->d_cnt.ptr; cb.thr = h->d_thr.ptr; cb.topk = h->d_topk.ptr;
-    cb.overflow = &h->d_flags->overflow; cb.error = &h->d_flags->error; cb.cap = cap; cb.k = int(kk);
-
-    ScanParams sp{};
-    sp.codes = h->d_codes; sp.vec_scales = h->d_scales; sp.n = int64_t(n); sp.ngroups = ng; sp.bits = h->bits;
-    sp.mode = mode; sp.qscale = h->d_qscale.ptr; sp.qbias = h->d_qbias.ptr;
-    sp.mask = d_mask; sp.live_blocks = d_mask ? h->d_live.ptr : nullptr; sp.n_live = d_mask ? &h->d_flags->n_live : nullptr;
-    sp.cb = cb; sp.wfrag = h->d_wfrag.ptr; sp.mtiles_total = mt_total; sp.luts = h->d_luts.ptr;
-    for (int w = 0; w < 4; ++w) {
-        uint32_t word = 0;
-        for (int b = 0; b < 4; ++b) word |= uint32_t(uint8_t(h->levels[4 * w + b])) << (8 * b);
-        sp.level_words[w] = word;
-    }
-    sp.pd_split = h->pd_split;
-
-    auto run_schedule = [&](bool careful) -> int {
-        TV_CUDA(cudaMemsetAsync(h->d_cnt.ptr, 0, nq * 4, st));
-        TV_CUDA(cudaMemsetAsync(h->d_thr.ptr, 0xff, nq * 8, st));
-        TV_CUDA(cudaMemsetAsync(h->d_topk.ptr, 0xff, nq * kk * 8, st));
-        // Chunk 0 holds at most `cap` vectors, so every one of them may pass.  Later chunks grow so that the
-        // expected number of candidates per query, k * |chunk| / |seen|, stays near cap / 4.  The careful
-        // schedule never lets a chunk exceed `cap` vectors and therefore cannot overflow.
-        // The tensor-memory scan pays for dense candidates (its epilogue re-reads a 32 x 32 tile of scores
-        // whenever one of them passes), so its chunks grow gently at first: x24, x10, then the list-capacity rule.
-        const size_t first = size_t(cap) / kBlock;
-        const double growth = std::max(0.5, double(cap) / (4.0 * double(kk)));
-        size_t begin = 0;
-        int stage = 0;
-        while (begin < n_blocks) {
-            size_t len = first;
-            if (!careful && begin > 0) {
-                double g = growth;
-                if (use_tc) g = std::min(g, stage == 1 ? 24.0 : (stage == 2 ? 10.0 : g));
-                len = std::max<size_t>(first, size_t(double(begin) * g));
-                if (begin + len + len / 2 >= n_blocks) len = n_blocks - begin;   // no short tail chunk
-            }
-            const size_t end = std::min(n_blocks, begin + len);
-            sp.pos_begin = uint32_t(begin); sp.pos_end = uint32_t(end);
-            // first chunk on the tensor-memory path without a filter (the host then knows how many vectors
-            // the chunk holds): every key is written in place, nothing is counted
-            const bool dense = use_tc && stage == 0 && !careful && d_mask == nullptr;
-            sp.dense = dense ? 1 : 0;
-            ++stage;
-            if (use_tc) {
-                sp.q_base = 0; sp.nq = int(nq); sp.mtile_base = 0;
-                mark_begin(h);
-                if (mode == TV_SCORE_PERMUTE_DOT)
-                    TV_CUDA(launch_scan_tc(sp, h->d_weights.ptr, int(w_rows), int(dim_pad), h->sm_count, h->tc_tiles, st));
-                else
-                    TV_CUDA(launch_scan_tc(sp, reinterpret_cast<const int8_t *>(h->d_luts.ptr), int(w_rows), ng * 32, h->sm_count, 1, st));
-                mark_end(h);
-                h->launches++;
-            } else if (mode == TV_SCORE_PERMUTE_DOT) {
-                for (size_t q0 = 0; q0 < nq; q0 += 64) {
-                    sp.q_base = int(q0); sp.nq = int(std::min<size_t>(64, nq - q0)); sp.mtile_base = int(q0 / 16);
-                    mark_begin(h);
-                    TV_CUDA(launch_scan_pd(sp, h->sm_count, st));
-                    mark_end(h);
-                    h->launches++;
-                }
-            } else {
-                for (size_t q0 = 0; q0 < nq; q0 += kLutQueriesPerLaunch) {
-                    sp.q_base = int(q0); sp.nq = int(std::min<size_t>(kLutQueriesPerLaunch, nq - q0));
-                    mark_begin(h);
-                    TV_CUDA(launch_scan_lut(sp, h->sm_count, st));
-                    mark_end(h);
-                    h->launches++;
-                }
-            }
-            TV_CUDA(launch_select(cb, int(nq), dense ? int((end - sp.pos_begin) * kBlock) : 0, st));
-            h->launches++;
-            begin = end;
+// Reads the status words of a finished call and turns them into an error, if any.  `queries` (host or device) is
+// only used to fetch the offending value.
+int check_flags(tv_index *h, const DeviceFlags *f, const float *queries, bool queries_on_device, cudaStream_t st) {
+    if (f->error) return fail(h, TV_ERR_DEVICE_TIMEOUT, "a device-side wait ran out of polls");
+    if (f->first_invalid != ~0ull) {
+        const unsigned long long flat = f->first_invalid;
+        float value = 0.f;
+        if (queries_on_device) {
+            cudaMemcpyAsync(&value, queries + flat, 4, cudaMemcpyDeviceToHost, st);
+            cudaStreamSynchronize(st);
+        } else {
+            value = queries[flat];
         }
-        return TV_OK;
-    };
+        {
+            std::lock_guard<std::mutex> g(h->stat_mu);
+            h->err_vec = size_t(flat / h->dim); h->err_coord = size_t(flat % h->dim); h->err_value = value;
+        }
+        return fail(h, TV_ERR_INVALID_QUERY_VALUE,
+                    "query " + std::to_string(flat / h->dim) + " coordinate " + std::to_string(flat % h->dim) +
+                        " is not finite or exceeds 1e16 in magnitude");
+    }
+    return TV_OK;
+}
 
-    uint32_t *d_keff = &h->d_flags->k_eff;
-    for (int attempt = 0; attempt < 2; ++attempt) {
-        const bool careful = attempt == 1 || h->force_careful;
-        int rc = run_schedule(careful);
+// The whole search on a context's stream.  Results land in c.d_scores / c.d_slots (row stride k) unless
+// out_scores_dev is given (row stride k_eff).  The caller holds the handle's lock (shared is enough).
+int search_core(tv_index *h, SearchCtx &c, const float *queries, bool queries_on_device, size_t nq, size_t k, const MaskSpec &mask,
+                float *out_scores_dev, int64_t *out_slots_dev, size_t *k_eff_out, uint64_t *out_keys_dev = nullptr,
+                uint64_t key_offset = 0) {
+    const size_t dim = h->dim, n = h->n;
+    const int ng = h->ngroups;
+    const int mode = resolve_mode(h);
+    const size_t kk = std::min(k, n);
+    *k_eff_out = 0;
+    if (nq == 0 || kk == 0) return TV_OK;
+    TV_CUDA(cudaSetDevice(h->device));
+    cudaStream_t st = c.stream;
+    // Results beyond kPageK per query come in pages: page r keeps the kPageK best keys above the last key of page
+    // r - 1 (keys are unique: they carry the slot), one full scan each.  Exact for any k <= len, slow by design.
+    const size_t pages = (kk + kPageK - 1) / kPageK;
+    const size_t k_page = pages == 1 ? kk : kPageK;
+    const int cap = candidate_capacity(k_page);
+    const size_t nq_pad = (nq + 15) / 16 * 16;
+    const int mt_total = int(nq_pad / 16);
+    const size_t dim_pad = (dim + 127) / 128 * 128;
+    const int ksteps = (ng + 15) / 16;
+
+    ScanPlan plan;
+    int rc = plan_scan(h, mode, nq, pages == 1, plan);
+    if (rc != TV_OK) return rc;
+
+    // ---- buffers ----
+    TV_CUDA(injected_failure(h));
+    if (!queries_on_device) TV_CUDA(c.d_stage.reserve(nq * dim));
+    TV_CUDA(c.d_qrot.reserve(nq * dim));
+    TV_CUDA(c.d_qscale.reserve(nq_pad));
+    TV_CUDA(c.d_qbias.reserve(nq_pad));
+    const size_t w_rows = (nq + 255) / 256 * 256;
+    if (mode == TV_SCORE_PERMUTE_DOT) {
+        TV_CUDA(c.d_weights.reserve(w_rows * dim_pad));
+        TV_CUDA(c.d_wfrag.reserve(size_t(ksteps) * mt_total * 32 * 4));
+    } else {
+        TV_CUDA(c.d_luts.reserve(w_rows * size_t(ng) * 32));     // padded to whole query groups for the tensor path
+    }
+    TV_CUDA(c.d_cand.reserve(nq * size_t(cap)));
+    TV_CUDA(c.d_cnt.reserve(nq));
+    TV_CUDA(c.d_thr.reserve(nq));
+    TV_CUDA(c.d_topk.reserve(nq * k_page));
+    if (pages > 1) {
+        TV_CUDA(c.d_floor.reserve(nq));
+        TV_CUDA(c.d_keys_all.reserve(nq * kk));
+    }
+    if (!out_scores_dev) {
+        TV_CUDA(c.d_scores.reserve(nq * kk));
+        TV_CUDA(c.d_slots.reserve(nq * kk));
+    }
+
+    SearchScratch S{};
+    S.q_rot = c.d_qrot.ptr; S.qscale = c.d_qscale.ptr; S.qbias = c.d_qbias.ptr; S.weights = c.d_weights.ptr;
+    S.wfrag = c.d_wfrag.ptr; S.luts = c.d_luts.ptr; S.cand = c.d_cand.ptr; S.thr = c.d_thr.ptr; S.topk = c.d_topk.ptr;
+    S.cnt = c.d_cnt.ptr; S.lo = nullptr; S.w_rows = w_rows; S.dim_pad = dim_pad; S.cap = cap; S.allow_tc = pages == 1;
+    {
+        ScanParams probe = base_scan_params(h, mode);
+        plan.use_small = h->small_scan >= 0 && mode == TV_SCORE_PERMUTE_DOT && scan_small_supported(probe, int(nq), h->smem_limit);
+    }
+
+    // ---- inputs ----
+    TV_CUDA(cudaStreamWaitEvent(st, h->ev_mut, 0));          // after every mutation enqueued on the handle's stream
+    const float *dq = queries;
+    if (!queries_on_device) {
+        TV_CUDA(cudaMemcpyAsync(c.d_stage.ptr, queries, nq * dim * 4, cudaMemcpyHostToDevice, st));
+        dq = c.d_stage.ptr;
+    }
+    DeviceFlags init{};
+    init.first_invalid = ~0ull;
+    *c.h_flags = init;
+    TV_CUDA(cudaMemcpyAsync(c.d_flags, c.h_flags, sizeof(DeviceFlags), cudaMemcpyHostToDevice, st));
+    TV_CUDA(cudaEventRecord(c.ev0, st));
+
+    MaskOnDevice m;
+    if (mask.prepared) {
+        if (!h->prepared.valid) return fail(h, TV_ERR_INVALID_ARGUMENT, "no prepared mask: call tv_mask_prepare_* after the last change of the index");
+        m.words = h->prepared.words.ptr; m.live = h->prepared.live.ptr;
+        m.n_allowed = h->prepared.counts.ptr; m.n_live = reinterpret_cast<const uint32_t *>(h->prepared.counts.ptr + 1);
+    } else if (mask.any()) {
+        rc = build_mask(h, st, mask, c.d_mask, c.d_mask_bool, c.d_slots_in, c.d_live, &c.d_flags->n_allowed, &c.d_flags->n_live, m);
         if (rc != TV_OK) return rc;
-        const unsigned long long *d_allowed = d_mask ? &h->d_flags->n_allowed : nullptr;
-        if (out_keys_dev) TV_CUDA(launch_export_keys(cb.topk, int64_t(nq * kk), key_offset, out_keys_dev, st));
-        if (out_scores_dev) TV_CUDA(launch_finalize(cb, int(nq), d_allowed, int64_t(n), out_scores_dev, out_slots_dev, d_keff, 0, st));
-        else TV_CUDA(launch_finalize(cb, int(nq), d_allowed, int64_t(n), h->d_scores.ptr, h->d_slots.ptr, d_keff, 1, st));
+    }
+
+    rc = enqueue_query_prep(h, st, S, plan, mode, dq, nq, &c.d_flags->first_invalid);
+    if (rc != TV_OK) return rc;
+
+    CandidateBuffers out_cb{};                                  // what finalize reads
+    out_cb.topk = pages == 1 ? c.d_topk.ptr : c.d_keys_all.ptr;
+    out_cb.k = int(kk);
+    uint32_t *d_keff = &c.d_flags->k_eff;
+    // decode / export of the finished rows, the status words and (host searches) the results, then one synchronisation
+    auto finish = [&]() -> int {
+        if (out_keys_dev) TV_CUDA(launch_export_keys(out_cb.topk, int64_t(nq * kk), key_offset, out_keys_dev, st));
+        if (out_scores_dev) TV_CUDA(launch_finalize(out_cb, int(nq), m.n_allowed, int64_t(n), out_scores_dev, out_slots_dev, d_keff, 0, st));
+        else TV_CUDA(launch_finalize(out_cb, int(nq), m.n_allowed, int64_t(n), c.d_scores.ptr, c.d_slots.ptr, d_keff, 1, st));
         h->launches++;
-        TV_CUDA(cudaEventRecord(h->ev1, st));
-        TV_CUDA(cudaMemcpyAsync(h->h_flags, h->d_flags, sizeof(DeviceFlags), cudaMemcpyDeviceToHost, st));
+        TV_CUDA(cudaEventRecord(c.ev1, st));
+        TV_CUDA(cudaMemcpyAsync(c.h_flags, c.d_flags, sizeof(DeviceFlags), cudaMemcpyDeviceToHost, st));
         if (!out_scores_dev && !out_keys_dev) {
-            TV_CUDA(h->h_scores.reserve(nq * kk));
-            TV_CUDA(h->h_slots.reserve(nq * kk));
-            TV_CUDA(cudaMemcpyAsync(h->h_scores.ptr, h->d_scores.ptr, nq * kk * 4, cudaMemcpyDeviceToHost, st));
-            TV_CUDA(cudaMemcpyAsync(h->h_slots.ptr, h->d_slots.ptr, nq * kk * 8, cudaMemcpyDeviceToHost, st));
+            TV_CUDA(c.h_scores.reserve(nq * kk));
+            TV_CUDA(c.h_slots.reserve(nq * kk));
+            TV_CUDA(cudaMemcpyAsync(c.h_scores.ptr, c.d_scores.ptr, nq * kk * 4, cudaMemcpyDeviceToHost, st));
+            TV_CUDA(cudaMemcpyAsync(c.h_slots.ptr, c.d_slots.ptr, nq * kk * 8, cudaMemcpyDeviceToHost, st));
         }
         TV_CUDA(cudaStreamSynchronize(st));
-        cudaEventElapsedTime(&h->last_ms, h->ev0, h->ev1);
-        collect_marks(h);
-        if (h->h_flags->error) return fail(h, TV_ERR_DEVICE_TIMEOUT, "a device-side wait ran out of polls");
-        if (h->h_flags->first_invalid != ~0ull) {
-            const unsigned long long flat = h->h_flags->first_invalid;
-            h->err_vec = size_t(flat / dim); h->err_coord = size_t(flat % dim);
-            if (queries_on_device) cudaMemcpy(&h->err_value, queries + flat, 4, cudaMemcpyDeviceToHost);
-            else h->err_value = queries[flat];
-            return fail(h, TV_ERR_INVALID_QUERY_VALUE,
-                        "query " + std::to_string(h->err_vec) + " coordinate " + std::to_string(h->err_coord) +
-                            " is not finite or exceeds 1e16 in magnitude");
+        float ms = 0.f;
+        cudaEventElapsedTime(&ms, c.ev0, c.ev1);
+        c.marks.collect();
+        std::lock_guard<std::mutex> g(h->stat_mu);
+        h->last_ms = ms; h->last_main_ms = c.marks.total_ms; h->last_main_launches = c.marks.launches;
+        return TV_OK;
+    };
+    for (size_t page = 0; page < pages; ++page) {
+        const size_t k_this = pages == 1 ? kk : std::min(kPageK, kk - page * kPageK);
+        S.lo = page == 0 ? nullptr : c.d_floor.ptr;
+        for (int attempt = 0; attempt < 2; ++attempt) {
+            const bool careful = attempt == 1 || h->force_careful;
+            rc = enqueue_search(h, st, &c.marks, S, plan, mode, nq, k_this, m, &c.d_flags->overflow, &c.d_flags->error, careful);
+            if (rc != TV_OK) { c.marks.used = 0; return rc; }
+            if (pages == 1) {
+                rc = finish();                                  // the common case: one submission, one synchronisation
+            } else {
+                TV_CUDA(cudaMemcpyAsync(c.h_flags, c.d_flags, sizeof(DeviceFlags), cudaMemcpyDeviceToHost, st));
+                TV_CUDA(cudaStreamSynchronize(st));
+            }
+            if (rc == TV_OK) rc = check_flags(h, c.h_flags, queries, queries_on_device, st);
+            if (rc != TV_OK) { c.marks.used = 0; return rc; }
+            if (!c.h_flags->overflow) break;
+            if (careful) return fail(h, TV_ERR_CUDA, "candidate overflow in the bounded schedule (internal error)");
+            // a chunk produced more candidates than the buffer holds: redo this page with bounded chunks
+            c.h_flags->overflow = 0;
+            TV_CUDA(cudaMemcpyAsync(&c.d_flags->overflow, &c.h_flags->overflow, 4, cudaMemcpyHostToDevice, st));
         }
-        if (!h->h_flags->overflow) break;
-        if (careful) return fail(h, TV_ERR_CUDA, "candidate overflow in the bounded schedule (internal error)");
-        // a chunk produced more candidates than the buffer holds: redo with bounded chunks
-        h->h_flags->overflow = 0;
-        TV_CUDA(cudaMemcpyAsync(&h->d_flags->overflow, &h->h_flags->overflow, 4, cudaMemcpyHostToDevice, st));
+        if (pages > 1) {
+            // this page's keys into their columns of the full rows; its last key bounds the next page from below
+            TV_CUDA(cudaMemcpy2DAsync(c.d_keys_all.ptr + page * kPageK, kk * 8, c.d_topk.ptr, k_this * 8, k_this * 8, nq,
+                                      cudaMemcpyDeviceToDevice, st));
+            if (page + 1 < pages) {
+                TV_CUDA(launch_advance_floor(c.d_thr.ptr, c.d_floor.ptr, int(nq), st));
+            } else {
+                rc = finish();
+                if (rc != TV_OK) return rc;
+            }
+        }
     }
-    *k_eff_out = h->h_flags->k_eff;
+    *k_eff_out = c.h_flags->k_eff;
     return TV_OK;
 }
 
@@ -805,16 +1096,48 @@ int search_host(tv_index *h, const float *queries, size_t nq, size_t dim, size_t
         return TV_OK;
     }
     size_t ke = 0;
-    int rc = search_core(h, queries, false, nq, k, mask, nullptr, nullptr, &ke);
+    CtxLease lease(h);
+    SearchCtx &c = *lease.c;
+    int rc = search_core(h, c, queries, false, nq, k, mask, nullptr, nullptr, &ke);
     if (rc != TV_OK) return rc;
     const size_t kk = std::min(k, h->n);
     for (size_t q = 0; q < nq; ++q) {
-        std::memcpy(scores_out + q * ke, h->h_scores.ptr + q * kk, ke * sizeof(float));
-        if (slots_out) std::memcpy(slots_out + q * ke, h->h_slots.ptr + q * kk, ke * sizeof(int64_t));
+        std::memcpy(scores_out + q * ke, c.h_scores.ptr + q * kk, ke * sizeof(float));
+        if (slots_out) std::memcpy(slots_out + q * ke, c.h_slots.ptr + q * kk, ke * sizeof(int64_t));
         if (ids_out)
-            for (size_t j = 0; j < ke; ++j) ids_out[q * ke + j] = h->slot_to_id[size_t(h->h_slots.ptr[q * kk + j])];   // id_map.rs:695-705
+            for (size_t j = 0; j < ke; ++j) ids_out[q * ke + j] = h->slot_to_id[size_t(c.h_slots.ptr[q * kk + j])];   // id_map.rs:695-705
     }
     if (k_eff) *k_eff = ke;
+    return TV_OK;
+}
+
+// Allowlist ids -> slots (id_map.rs:670-683): one hash lookup per id; large lists are split over host threads (lookups
+// only read the table) and the first unknown id in list order is the one reported, as in a sequential walk.
+int resolve_allowlist(tv_index *h, const uint64_t *allow_ids, size_t n_allow, std::vector<uint32_t> &slots) {
+    if (n_allow == 0) return fail(h, TV_ERR_ALLOWLIST_EMPTY, "allowlist is empty");
+    slots.resize(n_allow);
+    const size_t n_threads = n_allow < (size_t(1) << 16) ? 1 : std::min<size_t>(16, std::max(1u, std::thread::hardware_concurrency()));
+    std::vector<size_t> first_unknown(n_threads, n_allow);
+    auto resolve = [&](size_t t) {
+        const size_t lo = n_allow * t / n_threads, hi = n_allow * (t + 1) / n_threads;
+        for (size_t i = lo; i < hi; ++i) {
+            auto it = h->id_to_slot.find(allow_ids[i]);
+            if (it == h->id_to_slot.end()) { first_unknown[t] = i; return; }
+            slots[i] = it->second;
+        }
+    };
+    if (n_threads == 1) {
+        resolve(0);
+    } else {
+        std::vector<std::thread> pool;
+        for (size_t t = 0; t < n_threads; ++t) pool.emplace_back(resolve, t);
+        for (auto &th : pool) th.join();
+    }
+    const size_t bad = *std::min_element(first_unknown.begin(), first_unknown.end());
+    if (bad < n_allow) {
+        { std::lock_guard<std::mutex> g(h->stat_mu); h->err_id = allow_ids[bad]; }
+        return fail(h, TV_ERR_UNKNOWN_ID, "allowlist id " + std::to_string(allow_ids[bad]) + " is not in the index");
+    }
     return TV_OK;
 }
 
@@ -907,8 +1230,12 @@ int tv_index_create(size_t dim, int bit_width, int kind, int device, tv_index **
     if ((e = cudaStreamCreateWithFlags(&h->stream, cudaStreamNonBlocking)) != cudaSuccess) return bail("cudaStreamCreate", e);
     if ((e = cudaEventCreate(&h->ev0)) != cudaSuccess) return bail("cudaEventCreate", e);
     if ((e = cudaEventCreate(&h->ev1)) != cudaSuccess) return bail("cudaEventCreate", e);
+    if ((e = cudaEventCreateWithFlags(&h->ev_mut, cudaEventDisableTiming)) != cudaSuccess) return bail("cudaEventCreate", e);
+    if ((e = cudaEventRecord(h->ev_mut, h->stream)) != cudaSuccess) return bail("cudaEventRecord", e);
     if ((e = cudaMalloc(&h->d_flags, sizeof(DeviceFlags))) != cudaSuccess) return bail("cudaMalloc", e);
     if ((e = cudaMallocHost(&h->h_flags, sizeof(DeviceFlags))) != cudaSuccess) return bail("cudaMallocHost", e);
+    for (int i = 0; i < kSearchCtxs; ++i)
+        if ((e = h->ctx[i].init()) != cudaSuccess) return bail("search context", e);
     *out = h;
     return TV_OK;
 }
@@ -929,7 +1256,7 @@ size_t tv_len(const tv_index *h) { return h ? h->n : 0; }
 size_t tv_dim(const tv_index *h) { return h ? h->dim : 0; }
 int tv_bit_width(const tv_index *h) { return h ? h->bits : 0; }
 int tv_kind(const tv_index *h) { return h ? h->kind : -1; }
-uint64_t tv_launch_count(const tv_index *h) { return h ? h->launches : 0; }
+uint64_t tv_launch_count(const tv_index *h) { return h ? h->launches.load() : uint64_t(0); }
 float tv_last_kernel_ms(const tv_index *h) { return h ? h->last_ms : 0.f; }
 float tv_last_main_kernel_ms(const tv_index *h, int *launches) {
     if (!h) return 0.f;
@@ -939,7 +1266,7 @@ float tv_last_main_kernel_ms(const tv_index *h, int *launches) {
 
 int tv_set_option(tv_index *h, int option, int64_t value) {
     if (!h) return TV_ERR_INVALID_ARGUMENT;
-    std::lock_guard<std::mutex> lock(h->mu);
+    std::unique_lock<std::shared_mutex> lock(h->mu);
     switch (option) {
         case TV_OPT_SCORE_MODE:
             if (value < TV_SCORE_AUTO || value > TV_SCORE_LUT_FLUSH) return fail(h, TV_ERR_INVALID_ARGUMENT, "unknown score mode");
@@ -951,6 +1278,8 @@ int tv_set_option(tv_index *h, int option, int64_t value) {
         case TV_OPT_TC_TILES: h->tc_tiles = value == 1 ? 1 : 2; return TV_OK;
         case TV_OPT_INGEST_PIPELINE: h->ingest_pipeline = value < 0 || value > 2 ? 1 : int(value); return TV_OK;
         case TV_OPT_PD_SPLIT: h->pd_split = value != 0; return TV_OK;
+        case TV_OPT_SMALL_SCAN: h->small_scan = value < 0 ? -1 : int(value & 7); return TV_OK;
+        case TV_OPT_FAIL_NEXT: h->fail_next = value < 0 ? 0 : int(value); return TV_OK;
         default: return fail(h, TV_ERR_INVALID_ARGUMENT, "unknown option");
     }
 }
@@ -964,20 +1293,22 @@ int64_t tv_get_option(const tv_index *h, int option) {
         case TV_OPT_TC_TILES: return h->tc_tiles;
         case TV_OPT_INGEST_PIPELINE: return h->ingest_pipeline;
         case TV_OPT_PD_SPLIT: return h->pd_split;
+        case TV_OPT_SMALL_SCAN: return h->small_scan;
+        case TV_OPT_FAIL_NEXT: return h->fail_next;
         default: return -1;
     }
 }
 
 int tv_add(tv_index *h, const float *vectors, size_t n, size_t dim) {
     if (!h || (!vectors && n)) return TV_ERR_INVALID_ARGUMENT;
-    std::lock_guard<std::mutex> lock(h->mu);
+    std::unique_lock<std::shared_mutex> lock(h->mu);
     if (h->kind != TV_KIND_POSITIONAL) return fail(h, TV_ERR_WRONG_INDEX_KIND, "tv_add on an id-mapped index; use tv_add_with_ids");
     return add_rows(h, vectors, n, dim, false);
 }
 
 int tv_add_device(tv_index *h, const float *vectors_device, size_t n, size_t dim) {
     if (!h || (!vectors_device && n)) return TV_ERR_INVALID_ARGUMENT;
-    std::lock_guard<std::mutex> lock(h->mu);
+    std::unique_lock<std::shared_mutex> lock(h->mu);
     if (h->kind != TV_KIND_POSITIONAL) return fail(h, TV_ERR_WRONG_INDEX_KIND, "tv_add_device on an id-mapped index");
     return add_rows(h, vectors_device, n, dim, true);
 }
@@ -994,7 +1325,7 @@ int tv_add_with_ids_device(tv_index *h, const float *vectors_device, size_t n, s
 namespace {
 int add_rows_with_ids(tv_index *h, const float *vectors, size_t n, size_t dim, const uint64_t *ids, bool on_device) {
     if (!h || (!vectors && n) || (!ids && n)) return TV_ERR_INVALID_ARGUMENT;
-    std::lock_guard<std::mutex> lock(h->mu);
+    std::unique_lock<std::shared_mutex> lock(h->mu);
     if (h->kind != TV_KIND_IDMAP) return fail(h, TV_ERR_WRONG_INDEX_KIND, "tv_add_with_ids needs an id-mapped index");
     if (dim == 0) return fail(h, TV_ERR_ZERO_DIM, "dim must be non-zero");          // id_map.rs:379-381
     // per id, in order: already present, then duplicate within the batch (id_map.rs:396-434)
@@ -1022,7 +1353,7 @@ int add_rows_with_ids(tv_index *h, const float *vectors, size_t n, size_t dim, c
 
 int tv_swap_remove(tv_index *h, size_t slot, size_t *moved_from) {
     if (!h) return TV_ERR_INVALID_ARGUMENT;
-    std::lock_guard<std::mutex> lock(h->mu);
+    std::unique_lock<std::shared_mutex> lock(h->mu);
     if (h->kind != TV_KIND_POSITIONAL) return fail(h, TV_ERR_WRONG_INDEX_KIND, "tv_swap_remove on an id-mapped index; use tv_remove");
     if (slot >= h->n) return fail(h, TV_ERR_SLOT_OUT_OF_RANGE, "index " + std::to_string(slot) + " out of bounds (n_vectors = " + std::to_string(h->n) + ")");
     TV_CUDA(cudaSetDevice(h->device));
@@ -1035,13 +1366,14 @@ int tv_swap_remove(tv_index *h, size_t slot, size_t *moved_from) {
     h->mark_dirty(slot);                      // lib.rs:2879-2885: the hole and the moved-from slot diverge
     if (last != slot) h->mark_dirty(last);
     h->n = last;
+    mutation_done(h);
     if (moved_from) *moved_from = last;
     return TV_OK;
 }
 
 int tv_remove(tv_index *h, uint64_t id, int *removed) {
     if (!h) return TV_ERR_INVALID_ARGUMENT;
-    std::lock_guard<std::mutex> lock(h->mu);
+    std::unique_lock<std::shared_mutex> lock(h->mu);
     if (removed) *removed = 0;
     if (h->kind != TV_KIND_IDMAP) return fail(h, TV_ERR_WRONG_INDEX_KIND, "tv_remove needs an id-mapped index");
     auto it = h->id_to_slot.find(id);
@@ -1054,6 +1386,7 @@ int tv_remove(tv_index *h, uint64_t id, int *removed) {
     h->mark_dirty(slot);
     if (last != slot) h->mark_dirty(last);
     h->n = last;                                                       // enqueued, not awaited (see tv_swap_remove)
+    mutation_done(h);
     h->id_to_slot.erase(it);
     if (slot != last) {                                                // id_map.rs:557-561
         const uint64_t moved = h->slot_to_id[last];
@@ -1068,15 +1401,15 @@ int tv_remove(tv_index *h, uint64_t id, int *removed) {
 int tv_get_row(const tv_index *hc, size_t slot, uint8_t *groups_out, size_t capacity, float *scale_out) {
     tv_index *h = const_cast<tv_index *>(hc);
     if (!h || !groups_out || !scale_out) return TV_ERR_INVALID_ARGUMENT;
-    std::lock_guard<std::mutex> lock(h->mu);
+    std::unique_lock<std::shared_mutex> lock(h->mu);
     if (slot >= h->n) return fail(h, TV_ERR_SLOT_OUT_OF_RANGE, "index " + std::to_string(slot) + " out of bounds (n_vectors = " + std::to_string(h->n) + ")");
     if (capacity < size_t(h->ngroups)) return fail(h, TV_ERR_INVALID_ARGUMENT, "output buffer too small");
     TV_CUDA(cudaSetDevice(h->device));
-    TV_CUDA(h->d_mask_bool.reserve(size_t(h->ngroups)));
-    gather_row_kernel<<<(h->ngroups + 255) / 256, 256, 0, h->stream>>>(h->d_codes, h->ngroups, int64_t(slot), h->d_mask_bool.ptr);
+    TV_CUDA(h->d_row.reserve(size_t(h->ngroups)));
+    gather_row_kernel<<<(h->ngroups + 255) / 256, 256, 0, h->stream>>>(h->d_codes, h->ngroups, int64_t(slot), h->d_row.ptr);
     h->launches++;
     TV_CUDA(cudaGetLastError());
-    TV_CUDA(cudaMemcpyAsync(groups_out, h->d_mask_bool.ptr, size_t(h->ngroups), cudaMemcpyDeviceToHost, h->stream));
+    TV_CUDA(cudaMemcpyAsync(groups_out, h->d_row.ptr, size_t(h->ngroups), cudaMemcpyDeviceToHost, h->stream));
     TV_CUDA(cudaMemcpyAsync(scale_out, h->d_scales + slot, 4, cudaMemcpyDeviceToHost, h->stream));
     TV_CUDA(cudaStreamSynchronize(h->stream));
     return TV_OK;
@@ -1084,19 +1417,20 @@ int tv_get_row(const tv_index *hc, size_t slot, uint8_t *groups_out, size_t capa
 
 int tv_set_row(tv_index *h, size_t slot, const uint8_t *groups, size_t count, float scale) {
     if (!h || !groups) return TV_ERR_INVALID_ARGUMENT;
-    std::lock_guard<std::mutex> lock(h->mu);
+    std::unique_lock<std::shared_mutex> lock(h->mu);
     if (slot >= h->n) return fail(h, TV_ERR_SLOT_OUT_OF_RANGE, "index " + std::to_string(slot) + " out of bounds (n_vectors = " + std::to_string(h->n) + ")");
     if (count != size_t(h->ngroups)) return fail(h, TV_ERR_INVALID_ARGUMENT, "a row has " + std::to_string(h->ngroups) + " byte-groups, got " + std::to_string(count));
     if (!(scale >= 0.0f) || !std::isfinite(scale)) return fail(h, TV_ERR_PARTS_INVALID, "scale is negative or not finite");
     TV_CUDA(cudaSetDevice(h->device));
-    TV_CUDA(h->d_mask_bool.reserve(count));
-    TV_CUDA(cudaMemcpyAsync(h->d_mask_bool.ptr, groups, count, cudaMemcpyHostToDevice, h->stream));
-    scatter_row_kernel<<<(h->ngroups + 255) / 256, 256, 0, h->stream>>>(h->d_codes, h->ngroups, int64_t(slot), h->d_mask_bool.ptr);
+    TV_CUDA(h->d_row.reserve(count));
+    TV_CUDA(cudaMemcpyAsync(h->d_row.ptr, groups, count, cudaMemcpyHostToDevice, h->stream));
+    scatter_row_kernel<<<(h->ngroups + 255) / 256, 256, 0, h->stream>>>(h->d_codes, h->ngroups, int64_t(slot), h->d_row.ptr);
     h->launches++;
     TV_CUDA(cudaGetLastError());
     TV_CUDA(cudaMemcpyAsync(h->d_scales + slot, &scale, 4, cudaMemcpyHostToDevice, h->stream));
     TV_CUDA(cudaStreamSynchronize(h->stream));
     h->mark_dirty(slot);
+    mutation_done(h);
     return TV_OK;
 }
 
@@ -1116,7 +1450,7 @@ int tv_ids(const tv_index *h, uint64_t *ids_out, size_t capacity) {
 int tv_search(tv_index *h, const float *queries, size_t nq, size_t dim, size_t k, const uint8_t *mask_bool,
               size_t mask_len, float *scores_out, int64_t *slots_out, size_t *k_eff) {
     if (!h || (!queries && nq)) return TV_ERR_INVALID_ARGUMENT;
-    std::lock_guard<std::mutex> lock(h->mu);
+    std::shared_lock<std::shared_mutex> lock(h->mu);
     MaskSpec m;
     m.bool_host = mask_bool; m.bool_len = mask_len;
     return search_host(h, queries, nq, dim, k, m, scores_out, slots_out, nullptr, k_eff);
@@ -1125,7 +1459,7 @@ int tv_search(tv_index *h, const float *queries, size_t nq, size_t dim, size_t k
 int tv_search_mask_words(tv_index *h, const float *queries, size_t nq, size_t dim, size_t k, const uint64_t *mask_words,
                          size_t n_words, float *scores_out, int64_t *slots_out, size_t *k_eff) {
     if (!h || (!queries && nq)) return TV_ERR_INVALID_ARGUMENT;
-    std::lock_guard<std::mutex> lock(h->mu);
+    std::shared_lock<std::shared_mutex> lock(h->mu);
     MaskSpec m;
     m.words_host = mask_words; m.n_words = n_words;
     return search_host(h, queries, nq, dim, k, m, scores_out, slots_out, nullptr, k_eff);
@@ -1134,38 +1468,14 @@ int tv_search_mask_words(tv_index *h, const float *queries, size_t nq, size_t di
 int tv_search_allowlist(tv_index *h, const float *queries, size_t nq, size_t dim, size_t k, const uint64_t *allow_ids,
                         size_t n_allow, float *scores_out, uint64_t *ids_out, size_t *k_eff) {
     if (!h || (!queries && nq)) return TV_ERR_INVALID_ARGUMENT;
-    std::lock_guard<std::mutex> lock(h->mu);
+    std::shared_lock<std::shared_mutex> lock(h->mu);
     if (h->kind != TV_KIND_IDMAP) return fail(h, TV_ERR_WRONG_INDEX_KIND, "tv_search_allowlist needs an id-mapped index");
     if (k_eff) *k_eff = 0;
     MaskSpec m;
     std::vector<uint32_t> slots;
     if (allow_ids) {                                                    // id_map.rs:670-683
-        if (n_allow == 0) return fail(h, TV_ERR_ALLOWLIST_EMPTY, "allowlist is empty");
-        // one hash lookup per id (id_map.rs:670-683); large lists are split over host threads (lookups only read
-        // the table) and the first unknown id in list order is the one reported, as in a sequential walk
-        slots.resize(n_allow);
-        const size_t n_threads = n_allow < (size_t(1) << 16) ? 1 : std::min<size_t>(16, std::max(1u, std::thread::hardware_concurrency()));
-        std::vector<size_t> first_unknown(n_threads, n_allow);
-        auto resolve = [&](size_t t) {
-            const size_t lo = n_allow * t / n_threads, hi = n_allow * (t + 1) / n_threads;
-            for (size_t i = lo; i < hi; ++i) {
-                auto it = h->id_to_slot.find(allow_ids[i]);
-                if (it == h->id_to_slot.end()) { first_unknown[t] = i; return; }
-                slots[i] = it->second;
-            }
-        };
-        if (n_threads == 1) {
-            resolve(0);
-        } else {
-            std::vector<std::thread> pool;
-            for (size_t t = 0; t < n_threads; ++t) pool.emplace_back(resolve, t);
-            for (auto &th : pool) th.join();
-        }
-        const size_t bad = *std::min_element(first_unknown.begin(), first_unknown.end());
-        if (bad < n_allow) {
-            h->err_id = allow_ids[bad];
-            return fail(h, TV_ERR_UNKNOWN_ID, "allowlist id " + std::to_string(allow_ids[bad]) + " is not in the index");
-        }
+        int rc = resolve_allowlist(h, allow_ids, n_allow, slots);
+        if (rc != TV_OK) return rc;
         m.slots_host = slots.data(); m.n_slots = slots.size();
     }
     return search_host(h, queries, nq, dim, k, m, scores_out, nullptr, ids_out, k_eff);
@@ -1174,13 +1484,14 @@ int tv_search_allowlist(tv_index *h, const float *queries, size_t nq, size_t dim
 int tv_search_device(tv_index *h, const float *queries_device, size_t nq, size_t k, const uint64_t *mask_words_device,
                      float *scores_out_device, int64_t *slots_out_device, size_t *k_eff) {
     if (!h || (!queries_device && nq) || !scores_out_device || !slots_out_device) return TV_ERR_INVALID_ARGUMENT;
-    std::lock_guard<std::mutex> lock(h->mu);
+    std::shared_lock<std::shared_mutex> lock(h->mu);
     if (k_eff) *k_eff = 0;
     if (h->dim == 0 || h->n == 0 || nq == 0) return TV_OK;
     MaskSpec m;
     m.words_device = mask_words_device;
     size_t ke = 0;
-    int rc = search_core(h, queries_device, true, nq, k, m, scores_out_device, slots_out_device, &ke);
+    CtxLease lease(h);
+    int rc = search_core(h, *lease.c, queries_device, true, nq, k, m, scores_out_device, slots_out_device, &ke);
     if (rc == TV_OK && k_eff) *k_eff = ke;
     return rc;
 }
@@ -1188,16 +1499,18 @@ int tv_search_device(tv_index *h, const float *queries_device, size_t nq, size_t
 int tv_search_device_keys(tv_index *h, const float *queries_device, size_t nq, size_t k, const uint64_t *mask_words_device,
                           uint64_t slot_offset, uint64_t *keys_out_device, size_t *k_eff) {
     if (!h || (!queries_device && nq) || !keys_out_device) return TV_ERR_INVALID_ARGUMENT;
-    std::lock_guard<std::mutex> lock(h->mu);
+    std::shared_lock<std::shared_mutex> lock(h->mu);
     if (k_eff) *k_eff = 0;
     if (nq == 0 || k == 0) return TV_OK;
     if (slot_offset + h->n > 0x100000000ull) return fail(h, TV_ERR_UNSUPPORTED, "slot_offset + len exceeds 2^32: the key holds 32 slot bits");
     TV_CUDA(cudaSetDevice(h->device));
+    CtxLease lease(h);
+    SearchCtx &c = *lease.c;
     const size_t kk = std::min(k, h->n);
     if (h->dim == 0 || h->n == 0 || kk < k) {
         // rows are k wide whatever the shard holds: fill with empty keys first
-        TV_CUDA(cudaMemsetAsync(keys_out_device, 0xff, nq * k * 8, h->stream));
-        TV_CUDA(cudaStreamSynchronize(h->stream));
+        TV_CUDA(cudaMemsetAsync(keys_out_device, 0xff, nq * k * 8, c.stream));
+        TV_CUDA(cudaStreamSynchronize(c.stream));
         if (h->dim == 0 || h->n == 0) return TV_OK;
     }
     MaskSpec m;
@@ -1205,16 +1518,94 @@ int tv_search_device_keys(tv_index *h, const float *queries_device, size_t nq, s
     size_t ke = 0;
     int rc;
     if (kk == k) {
-        rc = search_core(h, queries_device, true, nq, k, m, nullptr, nullptr, &ke, keys_out_device, slot_offset);
+        rc = search_core(h, c, queries_device, true, nq, k, m, nullptr, nullptr, &ke, keys_out_device, slot_offset);
     } else {
         // fewer vectors than k: the search yields rows of kk keys; spread them over rows of k
-        TV_CUDA(h->d_keys_tmp.reserve(nq * kk));
-        rc = search_core(h, queries_device, true, nq, k, m, nullptr, nullptr, &ke, h->d_keys_tmp.ptr, slot_offset);
+        TV_CUDA(c.d_keys_tmp.reserve(nq * kk));
+        rc = search_core(h, c, queries_device, true, nq, k, m, nullptr, nullptr, &ke, c.d_keys_tmp.ptr, slot_offset);
         if (rc == TV_OK) {
-            TV_CUDA(cudaMemcpy2DAsync(keys_out_device, k * 8, h->d_keys_tmp.ptr, kk * 8, kk * 8, nq, cudaMemcpyDeviceToDevice, h->stream));
-            TV_CUDA(cudaStreamSynchronize(h->stream));
+            TV_CUDA(cudaMemcpy2DAsync(keys_out_device, k * 8, c.d_keys_tmp.ptr, kk * 8, kk * 8, nq, cudaMemcpyDeviceToDevice, c.stream));
+            TV_CUDA(cudaStreamSynchronize(c.stream));
         }
     }
+    if (rc == TV_OK && k_eff) *k_eff = ke;
+    return rc;
+}
+
+// ---- a mask kept on the device between searches -------------------------------------------------------
+namespace {
+int prepare_mask(tv_index *h, const MaskSpec &spec) {
+    h->prepared.valid = false;
+    if (h->dim == 0 || h->n == 0) return fail(h, TV_ERR_INVALID_ARGUMENT, "the index is empty: nothing to prepare a mask for");
+    TV_CUDA(cudaSetDevice(h->device));
+    TV_CUDA(h->prepared.counts.reserve(2));
+    TV_CUDA(cudaMemsetAsync(h->prepared.counts.ptr, 0, 16, h->stream));
+    MaskOnDevice m;
+    int rc = build_mask(h, h->stream, spec, h->prepared.words, h->ctx[0].d_mask_bool, h->ctx[0].d_slots_in, h->prepared.live,
+                        h->prepared.counts.ptr, reinterpret_cast<uint32_t *>(h->prepared.counts.ptr + 1), m);
+    if (rc != TV_OK) return rc;
+    TV_CUDA(cudaEventRecord(h->ev_mut, h->stream));             // searches run on other streams: order them after this
+    TV_CUDA(cudaStreamSynchronize(h->stream));
+    h->prepared.valid = true;
+    return TV_OK;
+}
+}  // namespace
+
+int tv_mask_prepare_device(tv_index *h, const uint64_t *mask_words_device) {
+    if (!h || !mask_words_device) return TV_ERR_INVALID_ARGUMENT;
+    std::unique_lock<std::shared_mutex> lock(h->mu);
+    MaskSpec m;
+    m.words_device = mask_words_device;
+    return prepare_mask(h, m);
+}
+
+int tv_mask_prepare_words(tv_index *h, const uint64_t *mask_words, size_t n_words) {
+    if (!h || !mask_words) return TV_ERR_INVALID_ARGUMENT;
+    std::unique_lock<std::shared_mutex> lock(h->mu);
+    if (n_words != (h->n + 63) / 64)
+        return fail(h, TV_ERR_MASK_LENGTH_MISMATCH, "mask has " + std::to_string(n_words) + " words, index needs " + std::to_string((h->n + 63) / 64));
+    MaskSpec m;
+    m.words_host = mask_words; m.n_words = n_words;
+    return prepare_mask(h, m);
+}
+
+int tv_mask_prepare_allowlist(tv_index *h, const uint64_t *allow_ids, size_t n_allow) {
+    if (!h || !allow_ids) return TV_ERR_INVALID_ARGUMENT;
+    std::unique_lock<std::shared_mutex> lock(h->mu);
+    if (h->kind != TV_KIND_IDMAP) return fail(h, TV_ERR_WRONG_INDEX_KIND, "tv_mask_prepare_allowlist needs an id-mapped index");
+    std::vector<uint32_t> slots;
+    int rc = resolve_allowlist(h, allow_ids, n_allow, slots);
+    if (rc != TV_OK) return rc;
+    MaskSpec m;
+    m.slots_host = slots.data(); m.n_slots = slots.size();
+    return prepare_mask(h, m);
+}
+
+int tv_search_prepared(tv_index *h, const float *queries, size_t nq, size_t dim, size_t k, float *scores_out,
+                       int64_t *slots_out, uint64_t *ids_out, size_t *k_eff) {
+    if (!h || (!queries && nq) || !scores_out) return TV_ERR_INVALID_ARGUMENT;
+    std::shared_lock<std::shared_mutex> lock(h->mu);
+    if (ids_out && h->kind != TV_KIND_IDMAP) return fail(h, TV_ERR_WRONG_INDEX_KIND, "ids are only available on an id-mapped index");
+    if (k_eff) *k_eff = 0;
+    if (!h->prepared.valid) return fail(h, TV_ERR_INVALID_ARGUMENT, "no prepared mask: call tv_mask_prepare_* after the last change of the index");
+    if (nq == 0) return TV_OK;
+    MaskSpec m;
+    m.prepared = true;
+    return search_host(h, queries, nq, dim, k, m, scores_out, slots_out, ids_out, k_eff);
+}
+
+int tv_search_device_prepared(tv_index *h, const float *queries_device, size_t nq, size_t k, float *scores_out_device,
+                              int64_t *slots_out_device, size_t *k_eff) {
+    if (!h || (!queries_device && nq) || !scores_out_device || !slots_out_device) return TV_ERR_INVALID_ARGUMENT;
+    std::shared_lock<std::shared_mutex> lock(h->mu);
+    if (k_eff) *k_eff = 0;
+    if (!h->prepared.valid) return fail(h, TV_ERR_INVALID_ARGUMENT, "no prepared mask: call tv_mask_prepare_* after the last change of the index");
+    if (nq == 0) return TV_OK;
+    MaskSpec m;
+    m.prepared = true;
+    size_t ke = 0;
+    CtxLease lease(h);
+    int rc = search_core(h, *lease.c, queries_device, true, nq, k, m, scores_out_device, slots_out_device, &ke);
     if (rc == TV_OK && k_eff) *k_eff = ke;
     return rc;
 }
@@ -1288,7 +1679,7 @@ NoAllocLayout carve_noalloc(unsigned char *base) {
 int tv_search_device_noalloc(tv_index *h, const float *queries_device, size_t nq, size_t k, float *scores_out_device,
                              int64_t *slots_out_device, size_t *k_eff) {
     if (!h || (!queries_device && nq) || !scores_out_device || !slots_out_device) return TV_ERR_INVALID_ARGUMENT;
-    std::lock_guard<std::mutex> lock(h->mu);
+    std::shared_lock<std::shared_mutex> lock(h->mu);
     std::lock_guard<std::mutex> scratch_lock(g_noalloc_mu);
     if (k_eff) *k_eff = 0;
     if (nq > kNoAllocMaxQueries)
@@ -1309,80 +1700,90 @@ int tv_search_device_noalloc(tv_index *h, const float *queries_device, size_t nq
     }
     const NoAllocLayout L = carve_noalloc(static_cast<unsigned char *>(g_noalloc_base[h->device]));
 
-    const size_t dim = h->dim, n = h->n;
+    const size_t n = h->n;
     const int ng = h->ngroups, mode = resolve_mode(h);
     const size_t kk = std::min(k, n);
-    const int ksteps = (ng + 15) / 16;
-    cudaStream_t st = h->stream;
+    // The CUDA-core kernels only: their launches need nothing beyond the fixed array.  Geometries whose u8 tables
+    // do not fit in shared memory even for one query have no such kernel.
+    ScanPlan plan;
+    int rc = plan_scan(h, mode, nq, false, plan);
+    if (rc != TV_OK) return rc;
 
+    SearchScratch S{};
+    S.q_rot = L.q_rot; S.qscale = L.qscale; S.qbias = L.qbias; S.weights = L.weights; S.wfrag = L.wfrag; S.luts = L.luts;
+    S.cand = L.cand; S.thr = L.thr; S.topk = L.topk; S.cnt = L.cnt; S.lo = nullptr;
+    S.w_rows = 16; S.dim_pad = kNoAllocMaxDim; S.cap = int(kNoAllocCap); S.allow_tc = false;
+    {
+        ScanParams probe = base_scan_params(h, mode);
+        plan.use_small = h->small_scan >= 0 && (h->small_scan & 4) == 0 && mode == TV_SCORE_PERMUTE_DOT &&
+                         scan_small_supported(probe, int(nq), h->smem_limit);
+    }
+
+    // the context supplies a stream and the status words (allocated when the handle was created)
+    CtxLease lease(h);
+    SearchCtx &c = *lease.c;
+    cudaStream_t st = c.stream;
+    TV_CUDA(cudaStreamWaitEvent(st, h->ev_mut, 0));
     DeviceFlags init{};
     init.first_invalid = ~0ull;
-    *h->h_flags = init;
-    TV_CUDA(cudaMemcpyAsync(h->d_flags, h->h_flags, sizeof(DeviceFlags), cudaMemcpyHostToDevice, st));
+    *c.h_flags = init;
+    TV_CUDA(cudaMemcpyAsync(c.d_flags, c.h_flags, sizeof(DeviceFlags), cudaMemcpyHostToDevice, st));
+    TV_CUDA(cudaEventRecord(c.ev0, st));
 
-    // the array still holds the previous call's data: reset everything that must start from a known state
-    TV_CUDA(cudaMemsetAsync(L.wfrag, 0, size_t(ksteps) * 32 * 16, st));
-    TV_CUDA(cudaMemsetAsync(L.cnt, 0, nq * 4, st));
-    TV_CUDA(cudaMemsetAsync(L.thr, 0xff, nq * 8, st));
-    TV_CUDA(cudaMemsetAsync(L.topk, 0xff, nq * kk * 8, st));
-
-    QueryPrepParams qp{};
-    qp.queries = queries_device; qp.nq = int(nq); qp.dim = int(dim); qp.bits = h->bits; qp.ngroups = ng; qp.mode = mode;
-    qp.perm0 = h->d_perm.ptr; qp.perm1 = h->d_perm.ptr + dim; qp.inv_sqrt_block = h->rot.inv_sqrt_block;
-    qp.centroids = h->d_codebook.ptr + 16;
-    if (!h->shift.empty()) { qp.shift = h->d_calib.ptr; qp.scale_tq = h->d_calib.ptr + dim; }
-    qp.level_scale = h->level_scale;
-    qp.q_rot = L.q_rot; qp.qscale = L.qscale; qp.qbias = L.qbias; qp.luts = L.luts; qp.weights = L.weights;
-    qp.dim_pad = int(kNoAllocMaxDim); qp.wfrag = L.wfrag; qp.mtiles_total = 1;
-    qp.first_invalid = &h->d_flags->first_invalid;
-    TV_CUDA(launch_query_prep(qp, st));
-    h->launches++;
-
-    CandidateBuffers cb{};
-    cb.cand = L.cand; cb.cnt = L.cnt; cb.thr = L.thr; cb.topk = L.topk;
-    cb.overflow = &h->d_flags->overflow; cb.error = &h->d_flags->error; cb.cap = int(kNoAllocCap); cb.k = int(kk);
-    ScanParams sp{};
-    sp.codes = h->d_codes; sp.vec_scales = h->d_scales; sp.n = int64_t(n); sp.ngroups = ng; sp.bits = h->bits;
-    sp.mode = mode; sp.qscale = L.qscale; sp.qbias = L.qbias; sp.cb = cb; sp.wfrag = L.wfrag; sp.mtiles_total = 1;
-    sp.luts = L.luts;
-    for (int w = 0; w < 4; ++w) {
-        uint32_t word = 0;
-        for (int b = 0; b < 4; ++b) word |= uint32_t(uint8_t(h->levels[4 * w + b])) << (8 * b);
-        sp.level_words[w] = word;
-    }
-    sp.pd_split = h->pd_split;
-    // Chunks never exceed the candidate capacity, so the fixed buffer cannot overflow whatever the data order.
-    const size_t n_blocks = (n + kBlock - 1) / kBlock, step = kNoAllocCap / kBlock;
-    for (size_t begin = 0; begin < n_blocks; begin += step) {
-        sp.pos_begin = uint32_t(begin); sp.pos_end = uint32_t(std::min(n_blocks, begin + step));
-        if (mode == TV_SCORE_PERMUTE_DOT) {
-            sp.q_base = 0; sp.nq = int(nq); sp.mtile_base = 0;
-            TV_CUDA(launch_scan_pd(sp, h->sm_count, st));
-            h->launches++;
-        } else {
-            for (size_t q0 = 0; q0 < nq; q0 += kLutQueriesPerLaunch) {
-                sp.q_base = int(q0); sp.nq = int(std::min<size_t>(kLutQueriesPerLaunch, nq - q0));
-                TV_CUDA(launch_scan_lut(sp, h->sm_count, st));
-                h->launches++;
-            }
-        }
-        TV_CUDA(launch_select(cb, int(nq), 0, st));
+    // The array still holds the previous call's data.  Query preparation clears the query operands it does not
+    // overwrite, and the schedule resets counters, thresholds and result keys at its start.
+    rc = enqueue_query_prep(h, st, S, plan, mode, queries_device, nq, &c.d_flags->first_invalid);
+    if (rc != TV_OK) return rc;
+    MaskOnDevice no_mask;
+    CandidateBuffers out_cb{};
+    out_cb.topk = L.topk; out_cb.k = int(kk);
+    // The same geometric chunk schedule as tv_search_device (a few launches for any index size).  If a chunk
+    // overflows a candidate list (adversarial order), the search is redone with chunks of at most the list's
+    // capacity, which cannot overflow; neither schedule needs memory beyond the fixed array.
+    for (int attempt = 0; attempt < 2; ++attempt) {
+        const bool careful = attempt == 1 || h->force_careful;
+        rc = enqueue_search(h, st, &c.marks, S, plan, mode, nq, kk, no_mask, &c.d_flags->overflow, &c.d_flags->error, careful);
+        if (rc != TV_OK) { c.marks.used = 0; return rc; }
+        TV_CUDA(launch_finalize(out_cb, int(nq), nullptr, int64_t(n), scores_out_device, slots_out_device, &c.d_flags->k_eff, 0, st));
         h->launches++;
+        TV_CUDA(cudaEventRecord(c.ev1, st));
+        TV_CUDA(cudaMemcpyAsync(c.h_flags, c.d_flags, sizeof(DeviceFlags), cudaMemcpyDeviceToHost, st));
+        TV_CUDA(cudaStreamSynchronize(st));
+        {
+            float ms = 0.f;
+            cudaEventElapsedTime(&ms, c.ev0, c.ev1);
+            c.marks.collect();
+            std::lock_guard<std::mutex> g(h->stat_mu);
+            h->last_ms = ms; h->last_main_ms = c.marks.total_ms; h->last_main_launches = c.marks.launches;
+        }
+        rc = check_flags(h, c.h_flags, queries_device, true, st);
+        if (rc != TV_OK) return rc;
+        if (!c.h_flags->overflow) break;
+        if (careful) return fail(h, TV_ERR_CUDA, "candidate overflow in the bounded schedule (internal error)");
+        c.h_flags->overflow = 0;
+        TV_CUDA(cudaMemcpyAsync(&c.d_flags->overflow, &c.h_flags->overflow, 4, cudaMemcpyHostToDevice, st));
     }
-    TV_CUDA(launch_finalize(cb, int(nq), nullptr, int64_t(n), scores_out_device, slots_out_device, &h->d_flags->k_eff, 0, st));
-    h->launches++;
-    TV_CUDA(cudaMemcpyAsync(h->h_flags, h->d_flags, sizeof(DeviceFlags), cudaMemcpyDeviceToHost, st));
-    TV_CUDA(cudaStreamSynchronize(st));
-    if (h->h_flags->error) return fail(h, TV_ERR_DEVICE_TIMEOUT, "a device-side wait ran out of polls");
-    if (h->h_flags->first_invalid != ~0ull) return fail(h, TV_ERR_INVALID_QUERY_VALUE, "a query coordinate is not finite or exceeds 1e16 in magnitude");
-    if (h->h_flags->overflow) return fail(h, TV_ERR_CUDA, "candidate overflow in the bounded schedule (internal error)");
-    if (k_eff) *k_eff = h->h_flags->k_eff;
+    if (k_eff) *k_eff = c.h_flags->k_eff;
+    return TV_OK;
+}
+
+int tv_measure_int8_peak(int device, double *ops_per_second) {
+    if (!ops_per_second) return TV_ERR_INVALID_ARGUMENT;
+    *ops_per_second = 0.0;
+    cudaDeviceProp prop{};
+    if (cudaSetDevice(device) != cudaSuccess || cudaGetDeviceProperties(&prop, device) != cudaSuccess) {
+        cudaGetLastError();
+        g_create_error = "tv_measure_int8_peak: no such CUDA device";
+        return TV_ERR_CUDA;
+    }
+    *ops_per_second = measure_int8_peak(prop.multiProcessorCount, nullptr);
+    if (*ops_per_second <= 0.0) { g_create_error = "tv_measure_int8_peak: the measurement kernel failed"; return TV_ERR_CUDA; }
     return TV_OK;
 }
 
 int tv_prepare(tv_index *h) {
     if (!h) return TV_ERR_INVALID_ARGUMENT;
-    std::lock_guard<std::mutex> lock(h->mu);
+    std::unique_lock<std::shared_mutex> lock(h->mu);
     if (h->dim == 0) return TV_OK;
     TV_CUDA(cudaSetDevice(h->device));
     return ensure_tables(h);
@@ -1396,7 +1797,7 @@ size_t tv_blocked_bytes(const tv_index *h) {
 int tv_export_blocked(const tv_index *hc, uint8_t *blocked_out, size_t blocked_capacity, float *scales_out, size_t scales_capacity) {
     tv_index *h = const_cast<tv_index *>(hc);
     if (!h) return TV_ERR_INVALID_ARGUMENT;
-    std::lock_guard<std::mutex> lock(h->mu);
+    std::unique_lock<std::shared_mutex> lock(h->mu);
     const size_t bytes = tv_blocked_bytes(h);
     if ((blocked_out && blocked_capacity < bytes) || (scales_out && scales_capacity < h->n)) return fail(h, TV_ERR_INVALID_ARGUMENT, "output buffer too small");
     if (h->n == 0) return TV_OK;
@@ -1422,7 +1823,7 @@ int tv_export_packed(const tv_index *hc, uint8_t *packed_out, size_t capacity) {
 
 int tv_import_packed(tv_index *h, size_t dim, const uint8_t *packed, size_t n, const float *scales, const uint64_t *ids) {
     if (!h || (n && (!packed || !scales))) return TV_ERR_INVALID_ARGUMENT;
-    std::lock_guard<std::mutex> lock(h->mu);
+    std::unique_lock<std::shared_mutex> lock(h->mu);
     if (h->n != 0) return fail(h, TV_ERR_PARTS_INVALID, "import needs an empty index");
     int rc = validate_dim_for_add(h, dim);
     if (rc != TV_OK) return rc;
@@ -1448,6 +1849,7 @@ int tv_import_packed(tv_index *h, size_t dim, const uint8_t *packed, size_t n, c
     TV_CUDA(cudaMemcpyAsync(h->d_scales, scales, n * 4, cudaMemcpyHostToDevice, h->stream));
     TV_CUDA(cudaStreamSynchronize(h->stream));
     h->n = n;
+    mutation_done(h);
     if (ids) {
         h->slot_to_id.assign(ids, ids + n);
         h->id_to_slot.clear();
@@ -1493,7 +1895,7 @@ size_t tv_image_bytes(const tv_index *h) {
 int tv_to_bytes(const tv_index *hc, uint8_t *out, size_t capacity) {
     tv_index *h = const_cast<tv_index *>(hc);
     if (!h || !out) return TV_ERR_INVALID_ARGUMENT;
-    std::lock_guard<std::mutex> lock(h->mu);
+    std::unique_lock<std::shared_mutex> lock(h->mu);
     V7Parts p;
     int rc = gather_parts(h, p);
     if (rc != TV_OK) return rc;
@@ -1595,7 +1997,7 @@ int tv_load(const char *path, int expect_kind, int device, tv_index **out) {
 // Incremental persistence (lib.rs sync :1737, sync_v7_impl :1813-1955).
 int tv_sync(tv_index *h, const char *path) {
     if (!h || !path) return TV_ERR_INVALID_ARGUMENT;
-    std::lock_guard<std::mutex> lock(h->mu);
+    std::unique_lock<std::shared_mutex> lock(h->mu);
     if (h->dim == 0) return fail(h, TV_ERR_DIM_NOT_SET, "cannot sync a lazy index that has never seen an add or calibrate");
     int rc = ensure_tables(h);
     if (rc != TV_OK) return rc;
@@ -1711,7 +2113,7 @@ int tv_sync_state(const tv_index *h, int *bound, uint64_t *generation, size_t *n
 
 int tv_codebook(tv_index *h, float *boundaries_out, float *centroids_out) {
     if (!h) return TV_ERR_INVALID_ARGUMENT;
-    std::lock_guard<std::mutex> lock(h->mu);
+    std::unique_lock<std::shared_mutex> lock(h->mu);
     if (h->dim == 0) return fail(h, TV_ERR_DIM_NOT_SET, "dimension is not set yet");
     const Codebook &cb = codebook(h->bits, int(h->dim));
     if (boundaries_out) std::copy(cb.boundaries.begin(), cb.boundaries.end(), boundaries_out);
@@ -1721,37 +2123,38 @@ int tv_codebook(tv_index *h, float *boundaries_out, float *centroids_out) {
 
 int tv_rotate(tv_index *h, const float *rows, size_t n, size_t dim, float *rotated_out) {
     if (!h || !rows || !rotated_out) return TV_ERR_INVALID_ARGUMENT;
-    std::lock_guard<std::mutex> lock(h->mu);
+    std::unique_lock<std::shared_mutex> lock(h->mu);
     if (h->dim == 0 || dim != h->dim) return fail(h, TV_ERR_DIM_MISMATCH, "tv_rotate needs rows of the index dimension");
     if (n == 0) return TV_OK;
     TV_CUDA(cudaSetDevice(h->device));
     int rc = ensure_tables(h);
     if (rc != TV_OK) return rc;
     cudaStream_t st = h->stream;
+    SearchCtx &c = h->ctx[0];                                  // the lock is exclusive: no search holds it
     const size_t nq_pad = (n + 15) / 16 * 16;
     TV_CUDA(h->d_stage.reserve(n * dim));
-    TV_CUDA(h->d_qrot.reserve(n * dim));
-    TV_CUDA(h->d_qscale.reserve(nq_pad));
-    TV_CUDA(h->d_qbias.reserve(nq_pad));
-    TV_CUDA(h->d_luts.reserve(n * size_t(h->ngroups) * 32));
+    TV_CUDA(c.d_qrot.reserve(n * dim));
+    TV_CUDA(c.d_qscale.reserve(nq_pad));
+    TV_CUDA(c.d_qbias.reserve(nq_pad));
+    TV_CUDA(c.d_luts.reserve(n * size_t(h->ngroups) * 32));
     TV_CUDA(cudaMemcpyAsync(h->d_stage.ptr, rows, n * dim * 4, cudaMemcpyHostToDevice, st));
     QueryPrepParams qp{};
     qp.queries = h->d_stage.ptr; qp.nq = int(n); qp.dim = int(dim); qp.bits = h->bits; qp.ngroups = h->ngroups;
     qp.mode = kModeLutMulAdd;
     qp.perm0 = h->d_perm.ptr; qp.perm1 = h->d_perm.ptr + dim; qp.inv_sqrt_block = h->rot.inv_sqrt_block;
     qp.centroids = h->d_codebook.ptr + 16;
-    qp.q_rot = h->d_qrot.ptr; qp.qscale = h->d_qscale.ptr; qp.qbias = h->d_qbias.ptr; qp.luts = h->d_luts.ptr;
+    qp.q_rot = c.d_qrot.ptr; qp.qscale = c.d_qscale.ptr; qp.qbias = c.d_qbias.ptr; qp.luts = c.d_luts.ptr;
     qp.first_invalid = &h->d_flags->first_invalid;
     TV_CUDA(launch_query_prep(qp, st));
     h->launches++;
-    TV_CUDA(cudaMemcpyAsync(rotated_out, h->d_qrot.ptr, n * dim * 4, cudaMemcpyDeviceToHost, st));
+    TV_CUDA(cudaMemcpyAsync(rotated_out, c.d_qrot.ptr, n * dim * 4, cudaMemcpyDeviceToHost, st));
     TV_CUDA(cudaStreamSynchronize(st));
     return TV_OK;
 }
 
 int tv_set_calibration(tv_index *h, size_t dim, const float *shift, const float *scale) {
     if (!h || !shift || !scale) return TV_ERR_INVALID_ARGUMENT;
-    std::lock_guard<std::mutex> lock(h->mu);
+    std::unique_lock<std::shared_mutex> lock(h->mu);
     if (h->n != 0) return fail(h, TV_ERR_CALIBRATE_NOT_EMPTY, "calibration can only be set on an empty index");
     int rc = validate_dim_for_add(h, dim);
     if (rc != TV_OK) return rc;
@@ -1783,7 +2186,7 @@ int tv_calibration(const tv_index *h, float *shift_out, float *scale_out, size_t
 // (tqplus_anchor encode.rs:364-369, compute_tqplus_calibration :737-857).  Validation order of lib.rs:2599-2640.
 int tv_calibrate(tv_index *h, const float *sample, size_t n, size_t dim) {
     if (!h || (!sample && n)) return TV_ERR_INVALID_ARGUMENT;
-    std::lock_guard<std::mutex> lock(h->mu);
+    std::unique_lock<std::shared_mutex> lock(h->mu);
     int rc = validate_dim_for_add(h, dim);
     if (rc != TV_OK) return rc;
     if (n < 2) return fail(h, TV_ERR_CALIBRATE_SAMPLE_TOO_SMALL, "calibration needs at least 2 rows, got " + std::to_string(n));

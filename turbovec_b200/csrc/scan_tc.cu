@@ -16,6 +16,8 @@
 // Every wait is bounded; a wait that runs out records an error word and makes its role leave its loop.
 #include <cuda.h>
 
+#include <algorithm>
+
 #include <cstddef>
 
 #include "search.cuh"
@@ -351,7 +353,7 @@ scan_tc_kernel(ScanParams p, const __grid_constant__ CUtensorMap wmap, int n_sla
                                     if (score >= sh->qthr[pb][c]) {
                                         const int ql = qg * kTileQueries + c;
                                         const uint64_t key = make_key(score, uint32_t(slot[m]));
-                                        if (key < p.cb.thr[ql]) {
+                                        if (key < p.cb.thr[ql] && (p.cb.lo == nullptr || key >= p.cb.lo[ql])) {
                                             const uint32_t at = atomicAdd(&p.cb.cnt[ql], 1u);
                                             if (at < uint32_t(p.cb.cap)) p.cb.cand[size_t(ql) * p.cb.cap + at] = key;
                                         }
@@ -487,6 +489,53 @@ scan_tc_kernel(ScanParams p, const __grid_constant__ CUtensorMap wmap, int n_sla
     }
 }
 
+
+// ---- tensor-pipe peak for kind::i8: MMAs issued back to back on shared-memory operands, no loads, no epilogue ----
+// One CTA per SM, 1 + 1 warps: warp 0 lane 0 issues M = 128, N = 256, K = 32 MMAs alternating between the two
+// accumulator halves of TMEM and commits every 64 of them to one of two barriers, waiting (bounded) for the batch
+// before the one just issued, so the issue queue stays two batches deep.  The operands are whatever the shared memory holds: the result is discarded.
+__global__ void __launch_bounds__(64, 1) int8_peak_kernel(int batches, uint32_t *error_flag) {
+    extern __shared__ __align__(1024) unsigned char smem_raw[];
+    unsigned char *ops = reinterpret_cast<unsigned char *>((reinterpret_cast<uintptr_t>(smem_raw) + 1023) & ~uintptr_t(1023));
+    __shared__ uint64_t done_bar[2];
+    __shared__ uint32_t tmem_slot;
+    const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
+    for (int i = threadIdx.x; i < (kATileBytes + kMaxTileQueries * kSlabK) / 4; i += blockDim.x) reinterpret_cast<uint32_t *>(ops)[i] = 0x01010101u;
+    if (threadIdx.x == 0) {
+        mbar_init(&done_bar[0], 1);
+        mbar_init(&done_bar[1], 1);
+        asm volatile("fence.mbarrier_init.release.cluster;" ::: "memory");
+    }
+    if (warp == 1) {
+        asm volatile("tcgen05.alloc.cta_group::1.sync.aligned.shared::cta.b32 [%0], %1;" ::"r"(smem_u32(&tmem_slot)), "r"(512u) : "memory");
+        asm volatile("tcgen05.relinquish_alloc_permit.cta_group::1.sync.aligned;" ::: "memory");
+    }
+    asm volatile("fence.proxy.async.shared::cta;" ::: "memory");
+    asm volatile("tcgen05.fence::before_thread_sync;" ::: "memory");
+    __syncthreads();
+    asm volatile("tcgen05.fence::after_thread_sync;" ::: "memory");
+    const uint32_t tmem_base = tmem_slot;
+    if (warp == 0 && lane == 0) {
+        const uint32_t a_addr = smem_u32(ops), b_addr = a_addr + kATileBytes;
+        bool ok = true;
+        for (int b = 0; b < batches && ok; ++b) {
+#pragma unroll 4
+            for (int i = 0; i < 64; ++i)
+                umma_i8<256>(tmem_base + uint32_t(i & 1) * 256u, umma_desc(a_addr + (i & 3) * 32), umma_desc(b_addr + (i & 3) * 32), 1u);
+            umma_commit(&done_bar[b & 1]);
+            // wait for the batch before this one: one batch stays queued behind the one that runs
+            if (b > 0) ok = mbar_wait(&done_bar[(b - 1) & 1], uint32_t(((b - 1) >> 1) & 1), error_flag);
+        }
+        if (ok && batches > 0) mbar_wait(&done_bar[(batches - 1) & 1], uint32_t(((batches - 1) >> 1) & 1), error_flag);
+    }
+    asm volatile("tcgen05.fence::before_thread_sync;" ::: "memory");
+    __syncthreads();
+    if (warp == 1) {
+        asm volatile("tcgen05.fence::after_thread_sync;" ::: "memory");
+        asm volatile("tcgen05.dealloc.cta_group::1.sync.aligned.b32 %0, %1;" ::"r"(tmem_base), "r"(512u) : "memory");
+    }
+}
+
 typedef CUresult (*EncodeTiledFn)(CUtensorMap *, CUtensorMapDataType, cuuint32_t, void *, const cuuint64_t *,
                                   const cuuint64_t *, const cuuint32_t *, const cuuint32_t *, CUtensorMapInterleave,
                                   CUtensorMapSwizzle, CUtensorMapL2promotion, CUtensorMapFloatOOBfill);
@@ -504,6 +553,38 @@ EncodeTiledFn encode_fn() {
 }
 
 }  // namespace
+
+// Runs int8_peak_kernel on one CTA per SM and returns the int8 rate in ops/s (a multiply-add = 2 ops), 0 on failure.
+double measure_int8_peak(int sm_count, cudaStream_t s) {
+    const int batches = 512;                                   // 32,768 MMAs of 2 * 128 * 256 * 32 ops per CTA
+    const size_t smem = size_t(kATileBytes) + size_t(kMaxTileQueries) * kSlabK + 1024;
+    if (cudaFuncSetAttribute(int8_peak_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, int(smem)) != cudaSuccess) return 0.0;
+    uint32_t *d_err = nullptr;
+    if (cudaMalloc(&d_err, 4) != cudaSuccess) return 0.0;
+    cudaMemsetAsync(d_err, 0, 4, s);
+    cudaEvent_t e0, e1;
+    cudaEventCreate(&e0); cudaEventCreate(&e1);
+    int8_peak_kernel<<<sm_count, 64, smem, s>>>(8, d_err);     // warm-up
+    double best = 0.0;
+    for (int rep = 0; rep < 3; ++rep) {
+        cudaEventRecord(e0, s);
+        int8_peak_kernel<<<sm_count, 64, smem, s>>>(batches, d_err);
+        cudaEventRecord(e1, s);
+        if (cudaStreamSynchronize(s) != cudaSuccess) { best = 0.0; break; }
+        float ms = 0.f;
+        cudaEventElapsedTime(&ms, e0, e1);
+        const double ops = 2.0 * 128 * 256 * 32 * 64.0 * batches * sm_count;
+        if (ms > 0.f) best = std::max(best, ops / (double(ms) * 1e-3));
+    }
+    uint32_t err = 0;
+    cudaMemcpy(&err, d_err, 4, cudaMemcpyDeviceToHost);
+    cudaEventDestroy(e0); cudaEventDestroy(e1);
+    cudaFree(d_err);
+    cudaGetLastError();
+    return err ? 0.0 : best;
+}
+
+void *tensor_map_encoder() { return reinterpret_cast<void *>(encode_fn()); }
 
 static size_t scan_tc_smem_bytes(int nqt) { return size_t(4) * (kATileBytes + nqt * kSlabK) + sizeof(TcShared) + 1024; }   // MT = 2: 3 x 64 KB, the same
 
@@ -538,18 +619,6 @@ cudaError_t launch_scan_tc(const ScanParams &p, const int8_t *weights, int rows,
     const int n_slabs = pitch / kSlabK;
     const int n_qgroups = (nq_all + nqt - 1) / nqt;
     const size_t smem = scan_tc_smem_bytes(nqt);
-    static bool attr_set = false;
-    if (!attr_set) {
-        const int big = int(scan_tc_smem_bytes(kMaxTileQueries));
-        cudaError_t e = cudaFuncSetAttribute(scan_tc_kernel<1, false, 256>, cudaFuncAttributeMaxDynamicSharedMemorySize, big);
-        if (e == cudaSuccess) e = cudaFuncSetAttribute(scan_tc_kernel<2, false, 256>, cudaFuncAttributeMaxDynamicSharedMemorySize, big);
-        if (e == cudaSuccess) e = cudaFuncSetAttribute(scan_tc_kernel<1, true, 256>, cudaFuncAttributeMaxDynamicSharedMemorySize, big);
-        if (e == cudaSuccess) e = cudaFuncSetAttribute(scan_tc_kernel<1, false, 64>, cudaFuncAttributeMaxDynamicSharedMemorySize, big);
-        if (e == cudaSuccess) e = cudaFuncSetAttribute(scan_tc_kernel<1, true, 64>, cudaFuncAttributeMaxDynamicSharedMemorySize, big);
-        if (e == cudaSuccess) e = cudaFuncSetAttribute(scan_tc_kernel<1, true, 32>, cudaFuncAttributeMaxDynamicSharedMemorySize, big);
-        if (e != cudaSuccess) return e;
-        attr_set = true;
-    }
     const int mt = (tiles_per_item == 2 && !onehot && nqt == kMaxTileQueries) ? 2 : 1;
     const uint32_t vtiles = (p.pos_end - p.pos_begin + 4 * mt - 1) / (4 * mt);
     const uint64_t items = uint64_t(vtiles) * n_qgroups;
@@ -557,17 +626,25 @@ cudaError_t launch_scan_tc(const ScanParams &p, const int8_t *weights, int rows,
     unsigned grid = unsigned(sm_count - sm_count % n_qgroups);
     if (grid == 0) grid = unsigned(sm_count);
     if (items < grid) grid = unsigned(items);
-    if (onehot) {
-        if (nqt == 32) scan_tc_kernel<1, true, 32><<<grid, kThreadsTc, smem, s>>>(p, map, n_slabs, n_qgroups);
-        else if (nqt == 64) scan_tc_kernel<1, true, 64><<<grid, kThreadsTc, smem, s>>>(p, map, n_slabs, n_qgroups);
-        else scan_tc_kernel<1, true, 256><<<grid, kThreadsTc, smem, s>>>(p, map, n_slabs, n_qgroups);
-    } else if (mt == 2) {
-        scan_tc_kernel<2, false, 256><<<grid, kThreadsTc, smem, s>>>(p, map, n_slabs, n_qgroups);
-    } else if (nqt == 64) {
-        scan_tc_kernel<1, false, 64><<<grid, kThreadsTc, smem, s>>>(p, map, n_slabs, n_qgroups);
-    } else {
-        scan_tc_kernel<1, false, 256><<<grid, kThreadsTc, smem, s>>>(p, map, n_slabs, n_qgroups);
+    // the shared-memory attribute belongs to the current device: set on every launch (a host-side table write)
+#define TV_LAUNCH_TC(M, O, N)                                                                                           \
+    {                                                                                                                   \
+        cudaError_t e = cudaFuncSetAttribute(scan_tc_kernel<M, O, N>, cudaFuncAttributeMaxDynamicSharedMemorySize, int(smem)); \
+        if (e != cudaSuccess) return e;                                                                                 \
+        scan_tc_kernel<M, O, N><<<grid, kThreadsTc, smem, s>>>(p, map, n_slabs, n_qgroups);                             \
     }
+    if (onehot) {
+        if (nqt == 32) TV_LAUNCH_TC(1, true, 32)
+        else if (nqt == 64) TV_LAUNCH_TC(1, true, 64)
+        else TV_LAUNCH_TC(1, true, 256)
+    } else if (mt == 2) {
+        TV_LAUNCH_TC(2, false, 256)
+    } else if (nqt == 64) {
+        TV_LAUNCH_TC(1, false, 64)
+    } else {
+        TV_LAUNCH_TC(1, false, 256)
+    }
+#undef TV_LAUNCH_TC
     return cudaGetLastError();
 }
 

@@ -13,11 +13,10 @@
 #include <cfloat>
 
 #include "rotation.cuh"
+#include "scan_common.cuh"
 
 namespace tv {
 namespace {
-
-constexpr int kLanes = 32;   // vectors per code block
 
 // =====================================================================================================
 // Query preparation: one CTA per query.
@@ -201,78 +200,6 @@ __global__ void mask_stats_kernel(uint32_t *words32, int64_t n, unsigned long lo
 }
 
 // =====================================================================================================
-// Candidate push shared by the scan kernels
-// =====================================================================================================
-__device__ __forceinline__ void push_candidate(const CandidateBuffers &cb, int q, float score, uint32_t slot,
-                                               uint64_t thr) {
-    const uint64_t key = make_key(score, slot);
-    if (key < thr) {
-        const uint32_t pos = atomicAdd(&cb.cnt[q], 1u);
-        if (pos < uint32_t(cb.cap)) cb.cand[size_t(q) * cb.cap + pos] = key;
-    }
-}
-
-// =====================================================================================================
-// PTX helpers: mbarrier + bulk asynchronous copy (no multicast), warp-level int8 MMA
-// =====================================================================================================
-__device__ __forceinline__ uint32_t smem_addr(const void *p) { return uint32_t(__cvta_generic_to_shared(p)); }
-__device__ __forceinline__ void mbar_init(uint64_t *bar, uint32_t count) {
-    asm volatile("mbarrier.init.shared::cta.b64 [%0], %1;" ::"r"(smem_addr(bar)), "r"(count));
-}
-__device__ __forceinline__ void mbar_arrive_expect_tx(uint64_t *bar, uint32_t bytes) {
-    asm volatile("mbarrier.arrive.expect_tx.shared::cta.b64 _, [%0], %1;" ::"r"(smem_addr(bar)), "r"(bytes) : "memory");
-}
-__device__ __forceinline__ void mbar_arrive(uint64_t *bar) {
-    asm volatile("mbarrier.arrive.shared::cta.b64 _, [%0];" ::"r"(smem_addr(bar)) : "memory");
-}
-__device__ __forceinline__ bool mbar_try_wait(uint64_t *bar, uint32_t parity) {
-    uint32_t ok;
-    asm volatile(
-        "{\n\t.reg .pred p;\n\t"
-        "mbarrier.try_wait.parity.shared::cta.b64 p, [%1], %2;\n\t"
-        "selp.u32 %0, 1, 0, p;\n\t}"
-        : "=r"(ok)
-        : "r"(smem_addr(bar)), "r"(parity)
-        : "memory");
-    return ok != 0;
-}
-// Bounded wait: gives up after kWaitLimit polls (each poll itself blocks for a hardware-defined
-// interval), records the failure and lets the caller leave its loop.
-constexpr uint32_t kWaitLimit = 1u << 22;
-__device__ __forceinline__ bool mbar_wait(uint64_t *bar, uint32_t parity, uint32_t *error_flag) {
-    for (uint32_t i = 0; i < kWaitLimit; ++i)
-        if (mbar_try_wait(bar, parity)) return true;
-    atomicExch(error_flag, 1u);
-    return false;
-}
-__device__ __forceinline__ void bulk_copy_g2s(void *dst, const void *src, uint32_t bytes, uint64_t *bar) {
-    asm volatile("cp.async.bulk.shared::cluster.global.mbarrier::complete_tx::bytes [%0], [%1], %2, [%3];" ::"r"(
-                     smem_addr(dst)),
-                 "l"(src), "r"(bytes), "r"(smem_addr(bar))
-                 : "memory");
-}
-__device__ __forceinline__ uint32_t prmt(uint32_t a, uint32_t b, uint32_t sel) {
-    uint32_t d;
-    asm("prmt.b32 %0, %1, %2, %3;" : "=r"(d) : "r"(a), "r"(b), "r"(sel));
-    return d;
-}
-// Two 16 x 16 byte matrices, transposed by the load unit: lane 4*q + t receives in x[2*i + h] the bytes of column
-// q + 8*h of matrix i from its rows 4t .. 4t+3 (byte r of the word = row 4t + r).  Lanes 0..15 give the row
-// addresses of matrix 0, lanes 16..31 those of matrix 1 (16-byte aligned, 16 bytes each).
-__device__ __forceinline__ void ldmatrix_x2_trans_b8(uint32_t (&x)[4], uint32_t row_addr) {
-    asm volatile("ldmatrix.sync.aligned.m16n16.x2.trans.shared.b8 {%0, %1, %2, %3}, [%4];"
-                 : "=r"(x[0]), "=r"(x[1]), "=r"(x[2]), "=r"(x[3])
-                 : "r"(row_addr)
-                 : "memory");
-}
-__device__ __forceinline__ void mma_s8(int (&c)[4], const uint4 &a, uint32_t b0, uint32_t b1) {
-    asm(
-        "mma.sync.aligned.m16n8k32.row.col.s32.s8.s8.s32 {%0,%1,%2,%3}, {%4,%5,%6,%7}, {%8,%9}, {%0,%1,%2,%3};"
-        : "+r"(c[0]), "+r"(c[1]), "+r"(c[2]), "+r"(c[3])
-        : "r"(a.x), "r"(a.y), "r"(a.z), "r"(a.w), "r"(b0), "r"(b1));
-}
-
-// =====================================================================================================
 // Permute-dot scan (4-bit codes): S[q][v] = sum_d W[q][d] * level[code[v][d]], exact in int32
 // (search.rs:1392-1543), then fma((f32)S, scale_q, bias_q) * vec_scale[v] (search.rs:1523, 1793).
 //
@@ -287,51 +214,6 @@ constexpr int kConsumerWarps = 8;
 constexpr int kChunkRows = 64;                                // byte-group rows per block per stage
 constexpr int kStageBytes = kConsumerWarps * kChunkRows * kLanes;
 constexpr int kStages = 4;
-
-// high 32 bits of a * b + c on the FMA pipe: a right shift that does not load the (saturated) ALU pipe
-__device__ __forceinline__ uint32_t mad_hi(uint32_t a, uint32_t b, uint32_t c) {
-    uint32_t d;
-    asm("mad.hi.u32 %0, %1, %2, %3;" : "=r"(d) : "r"(a), "r"(b), "r"(c));
-    return d;
-}
-__device__ __forceinline__ void expand4(uint32_t x, const uint32_t (&T)[4], uint32_t &b0, uint32_t &b1) {
-    const uint32_t idx = x & 0x77777777u;                     // low three bits of every nibble
-    // byte i from the low or the high half-table: nibble i = i + 4 * (bit 3 of code i); (x & 8..8) >> 1 + 0x3210..
-    const uint32_t pick = mad_hi(x & 0x88888888u, 0x80000000u, 0x32103210u);
-    b0 = prmt(prmt(T[0], T[1], idx), prmt(T[2], T[3], idx), pick);
-    const uint32_t idx_h = mad_hi(idx, 0x10000u, 0u), pick_h = mad_hi(pick, 0x10000u, 0u);   // >> 16
-    b1 = prmt(prmt(T[0], T[1], idx_h), prmt(T[2], T[3], idx_h), pick_h);
-}
-
-// Split lookup for a codebook whose levels 0..7 are <= 0 and 8..15 are >= 0 (every Lloyd-Max codebook of the
-// reference is symmetric).  A packed nibble is a `prmt` selector as it stands: values 0..7 pick a byte of the
-// 8-byte table, values 8..15 ask for the sign of that byte replicated - 0x00 when the table holds
-// non-negative bytes.  So `prmt(Tn, x)` yields -level[c] where c < 8 and 0 elsewhere, `prmt(Tp, x ^ 8..8)`
-// yields level[c] where c >= 8 and 0 elsewhere, with no masking and no merge: S = W.pos - W.neg, both exact
-// int32 contractions.  Five ALU-pipe operations per eight codes against eight in expand4; the second MMA is
-// paid by the tensor pipe, which this scan leaves mostly idle.
-__device__ __forceinline__ void expand4_split(uint32_t x, const uint32_t (&Tp)[2], const uint32_t (&Tn)[2], uint32_t &p0,
-                                              uint32_t &p1, uint32_t &n0, uint32_t &n1) {
-    const uint32_t y = x ^ 0x88888888u;
-    const uint32_t xh = mad_hi(x, 0x10000u, 0u), yh = mad_hi(y, 0x10000u, 0u);   // >> 16 on the FMA pipe
-    n0 = prmt(Tn[0], Tn[1], x);
-    p0 = prmt(Tp[0], Tp[1], y);
-    n1 = prmt(Tn[0], Tn[1], xh);
-    p1 = prmt(Tp[0], Tp[1], yh);
-}
-__host__ __device__ inline uint32_t negate_bytes(uint32_t w) {                   // per-byte two's complement
-    uint32_t r = 0;
-    for (int b = 0; b < 4; ++b) r |= uint32_t(uint8_t(-int(int8_t(w >> (8 * b))))) << (8 * b);
-    return r;
-}
-// whether the level table allows the split lookup
-inline bool levels_split_ok(const uint32_t (&words)[4]) {
-    for (int c = 0; c < 16; ++c) {
-        const int v = int8_t(words[c / 4] >> (8 * (c % 4)));
-        if (c < 8 ? (v > 0 || v == -128) : v < 0) return false;
-    }
-    return true;
-}
 
 template <int MT, bool SPLIT>
 __global__ void __launch_bounds__((kConsumerWarps + 1) * 32, MT == 1 ? (SPLIT ? 2 : 3) : (MT == 2 ? 2 : 1))
@@ -475,7 +357,7 @@ scan_pd_kernel(ScanParams p) {
                     const int ql = 16 * (p.mtile_base + m) + quad + 8 * half;   // query within the prepared batch
                     if (ql >= p.q_base + p.nq) continue;
                     const float qs = p.qscale[ql], qb = p.qbias[ql];
-                    const uint64_t thr = p.cb.thr[ql];
+                    const uint64_t thr = p.cb.thr[ql], lo = p.cb.lo ? p.cb.lo[ql] : 0ull;
 #pragma unroll
                     for (int j = 0; j < 4; ++j) {
 #pragma unroll
@@ -484,7 +366,7 @@ scan_pd_kernel(ScanParams p) {
                             if (base + vl >= p.n || !((allow >> vl) & 1u)) continue;
                             const int isum = SPLIT ? acc[m][j][2 * half + c] - accn[SPLIT ? m : 0][j][2 * half + c] : acc[m][j][2 * half + c];
                             const float score = __fmul_rn(fmaf(float(isum), qs, qb), vs[2 * j + c]);
-                            push_candidate(p.cb, ql, score, uint32_t(base + vl), thr);
+                            push_candidate(p.cb, ql, score, uint32_t(base + vl), thr, lo);
                         }
                     }
                 }
@@ -518,11 +400,12 @@ __global__ void __launch_bounds__(256) scan_lut_kernel(ScanParams p) {
     if (p.live_blocks != nullptr) pos_end = min(pos_end, *p.n_live);
     const uint32_t pos_begin = min(p.pos_begin, pos_end);
     float qs[NQ], qb[NQ];
-    uint64_t thr[NQ];
+    uint64_t thr[NQ], lo[NQ];
 #pragma unroll
     for (int q = 0; q < NQ; ++q) {
         const int ql = p.q_base + min(q, nq_here - 1);
         qs[q] = p.qscale[ql]; qb[q] = p.qbias[ql]; thr[q] = p.cb.thr[ql];
+        lo[q] = p.cb.lo ? p.cb.lo[ql] : 0ull;
     }
     const int warps = blockDim.x >> 5;
     // A warp instruction reads 128 contiguous bytes = four group rows of the block: lane = (row r = lane / 8,
@@ -583,7 +466,7 @@ __global__ void __launch_bounds__(256) scan_lut_kernel(ScanParams p) {
                     if (q >= nq_here) break;
                     const float pre = p.mode == kModeLutFlush ? facc[q]
                                                               : __fadd_rn(__fmul_rn(float(int(total[q])), qs[q]), qb[q]);
-                    push_candidate(p.cb, p.q_base + q, __fmul_rn(pre, vs), uint32_t(slot), thr[q]);
+                    push_candidate(p.cb, p.q_base + q, __fmul_rn(pre, vs), uint32_t(slot), thr[q], lo[q]);
                 }
             }
         }
@@ -683,6 +566,11 @@ __global__ void finalize_kernel(CandidateBuffers cb, int nq, const unsigned long
     if (key != kEmptyKey) { s = desc_bits_to_score(uint32_t(key >> 32)); slot = int64_t(key & 0xffffffffu); }
     scores[size_t(q) * stride + j] = s;
     slots[size_t(q) * stride + j] = slot;
+}
+
+__global__ void advance_floor_kernel(const uint64_t *thr, uint64_t *lo, int nq) {
+    const int q = blockIdx.x * blockDim.x + threadIdx.x;
+    if (q < nq) lo[q] = thr[q] == kEmptyKey ? kEmptyKey : thr[q] + 1;
 }
 
 // Keys of a finished search with a slot offset added (the shard's first global slot); empty entries stay empty.
@@ -786,13 +674,16 @@ cudaError_t launch_select(const CandidateBuffers &cb, int nq, int dense_count, c
     if (nq <= 0) return cudaSuccess;
     const int sort_n = sort_capacity(cb.cap, cb.k);
     const size_t smem = size_t(sort_n) * 8;
-    static bool attr_set = false;
-    if (!attr_set) {
-        cudaError_t e = cudaFuncSetAttribute(select_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, 200 * 1024);
-        if (e != cudaSuccess) return e;
-        attr_set = true;
-    }
+    // the attribute belongs to the current device: set on every launch (a host-side table write)
+    cudaError_t e = cudaFuncSetAttribute(select_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, 200 * 1024);
+    if (e != cudaSuccess) return e;
     select_kernel<<<nq, 256, smem, s>>>(cb, sort_n, dense_count);
+    return cudaGetLastError();
+}
+
+cudaError_t launch_advance_floor(const uint64_t *thr, uint64_t *lo, int nq, cudaStream_t s) {
+    if (nq <= 0) return cudaSuccess;
+    advance_floor_kernel<<<(nq + 255) / 256, 256, 0, s>>>(thr, lo, nq);
     return cudaGetLastError();
 }
 
@@ -807,12 +698,8 @@ cudaError_t launch_merge_keys(const uint64_t *keys, int n_lists, int nq, int k, 
     int n2 = 32;
     while (n2 < n_lists * k) n2 <<= 1;
     if (n2 > kMergeMaxKeys) return cudaErrorInvalidValue;
-    static bool attr_set = false;
-    if (!attr_set) {
-        cudaError_t e = cudaFuncSetAttribute(merge_keys_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, kMergeMaxKeys * 8);
-        if (e != cudaSuccess) return e;
-        attr_set = true;
-    }
+    cudaError_t e = cudaFuncSetAttribute(merge_keys_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, kMergeMaxKeys * 8);
+    if (e != cudaSuccess) return e;
     merge_keys_kernel<<<nq, 256, size_t(n2) * 8, s>>>(keys, n_lists, nq, k, n2, scores, slots);
     return cudaGetLastError();
 }
@@ -850,16 +737,23 @@ cudaError_t launch_scan_pd(const ScanParams &p, int sm_count, cudaStream_t s) {
     return cudaGetLastError();
 }
 
+int scan_lut_width(int ngroups, size_t smem_limit) {
+    const size_t table = size_t(ngroups) * 32;
+    if (table == 0) return 0;
+    const size_t fit = (smem_limit > 1024 ? smem_limit - 1024 : 0) / table;
+    return fit >= 4 ? 4 : (fit >= 2 ? 2 : (fit >= 1 ? 1 : 0));
+}
+
 cudaError_t launch_scan_lut(const ScanParams &p, int sm_count, cudaStream_t s) {
     if (p.nq <= 0 || p.pos_end <= p.pos_begin) return cudaSuccess;
-    const int nqh = p.nq < kLutQueriesPerLaunch ? p.nq : kLutQueriesPerLaunch;
+    if (p.nq > 4) return cudaErrorInvalidValue;
     // sized by the kernel's template width: its inner loop reads all NQ tables (unused ones hold garbage
     // whose sums are discarded), so the allocation must cover them
-    const int width = nqh == 1 ? 1 : (nqh == 2 ? 2 : 4);
+    const int width = p.nq == 1 ? 1 : (p.nq == 2 ? 2 : 4);
     const size_t smem = size_t(width) * p.ngroups * 32;
     const uint32_t blocks = p.pos_end - p.pos_begin;
     // resident CTAs per SM: as many as the tables leave room for (the scan hides its lookup latency with warps)
-    const uint32_t per_sm = uint32_t(std::max<size_t>(2, std::min<size_t>(6, (size_t(200) << 10) / (smem + 1024))));
+    const uint32_t per_sm = uint32_t(std::max<size_t>(1, std::min<size_t>(6, (size_t(200) << 10) / (smem + 1024))));
     const unsigned grid = unsigned(min(uint32_t(sm_count) * per_sm, (blocks + 7) / 8));
 #define TV_LAUNCH_LUT(N)                                                                                             \
     {                                                                                                                \
@@ -867,8 +761,8 @@ cudaError_t launch_scan_lut(const ScanParams &p, int sm_count, cudaStream_t s) {
         if (e != cudaSuccess) return e;                                                                              \
         scan_lut_kernel<N><<<grid, 256, smem, s>>>(p);                                                               \
     }
-    if (nqh == 1) TV_LAUNCH_LUT(1)
-    else if (nqh == 2) TV_LAUNCH_LUT(2)
+    if (width == 1) TV_LAUNCH_LUT(1)
+    else if (width == 2) TV_LAUNCH_LUT(2)
     else TV_LAUNCH_LUT(4)
 #undef TV_LAUNCH_LUT
     return cudaGetLastError();

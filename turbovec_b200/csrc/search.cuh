@@ -51,6 +51,7 @@ struct CandidateBuffers {
     uint64_t *cand;
     uint32_t *cnt;
     uint64_t *thr;
+    const uint64_t *lo;            // per query the lowest admissible key (paged top-k), or nullptr: every key
     uint64_t *topk;
     uint32_t *overflow;
     uint32_t *error;               // device-side wait timeouts
@@ -101,8 +102,22 @@ cudaError_t launch_scan_pd(const ScanParams &p, int sm_count, cudaStream_t s);
 bool scan_tc_supported(int bits, int mode, int ngroups);
 cudaError_t launch_scan_tc(const ScanParams &p, const int8_t *weights, int rows, int pitch, int sm_count,
                            int tiles_per_item, cudaStream_t s);
-// LUT scan on CUDA cores, up to kLutQueriesPerLaunch queries per launch.
-constexpr int kLutQueriesPerLaunch = 4;
+// int8 rate (ops/s, multiply-add = 2) of back-to-back tcgen05 kind::i8 MMAs on shared-memory operands, one CTA per SM:
+// the tensor-pipe roofline of the permute-dot scan on this device.  0 on failure.
+double measure_int8_peak(int sm_count, cudaStream_t s);
+// Driver entry point cuTensorMapEncodeTiled (nullptr if the driver does not offer it).
+void *tensor_map_encoder();
+// Permute-dot scan for up to 16 queries in one launch (scan_small.cu): vectors on the M side of the warp-level MMA,
+// one private bulk-copy ring per warp.  `weights` as for launch_scan_tc (row-major int8, adjacent coordinates swapped).
+// variant: bits 0-1 ring depth (0: 3 stages x 3 CTAs per SM, 1: 4 x 2, 2: 6 x 2), bit 2 swizzled tensor copies.
+bool scan_small_supported(const ScanParams &p, int nq_total, size_t smem_limit);
+cudaError_t launch_scan_small(const ScanParams &p, const int8_t *weights, int pitch, size_t code_bytes_capacity, int variant,
+                              int sm_count, size_t smem_limit, cudaStream_t s);
+// LUT scan on CUDA cores.  The u8 tables of the queries of one launch sit in shared memory (32 * ngroups bytes
+// each): scan_lut_width gives how many fit (4, 2, 1, or 0 when not even one does); p.nq must not exceed it.
+int scan_lut_width(int ngroups, size_t smem_limit);
 cudaError_t launch_scan_lut(const ScanParams &p, int sm_count, cudaStream_t s);
+// lo[q] = thr[q] + 1, or the empty key when thr[q] is empty (fewer results than asked for: nothing more can follow).
+cudaError_t launch_advance_floor(const uint64_t *thr, uint64_t *lo, int nq, cudaStream_t s);
 
 }  // namespace tv
