@@ -207,6 +207,32 @@ int tv_search_device_keys(tv_index *h, const float *queries_device, size_t nq, s
                           size_t *k_eff);
 int tv_merge_keys_device(int device, const uint64_t *keys_device, size_t n_lists, size_t nq, size_t k,
                          float *scores_out_device, int64_t *slots_out_device, void *stream);
+/* The same merge for shards that own chunks of `chunk_slots` global slots round-robin (list r owns the chunks
+ * r, r + n_lists, ...: appends stay balanced at any length): the lists carry LOCAL slots (slot_offset 0), which
+ * become global slots = ((local / chunk_slots) * n_lists + r) * chunk_slots + local % chunk_slots before the
+ * merge, so that ties break by the global slot as in the reference.  chunk_slots a multiple of 32. */
+int tv_merge_keys_device_chunked(int device, const uint64_t *keys_device, size_t n_lists, size_t nq, size_t k,
+                                 size_t chunk_slots, float *scores_out_device, int64_t *slots_out_device, void *stream);
+
+/* ---- id tables without vectors: the slot_to_id / id_to_slot pair IdMapIndex keeps around its inner index
+ * (id_map.rs:221-272).  A slot-sharded id-mapped index numbers slots globally, so every rank keeps a replica of
+ * these tables and applies the same calls in the same order; they never touch a device.
+ * add: id checks of add_with_ids_2d in the reference's order, nothing changes on error (id_map.rs:396-434).
+ * remove: id_map.rs:520-567; *slot = the freed slot, *moved_from = the slot whose row takes its place.
+ * resolve: allowlist ids -> global slots with the allowlist errors of id_map.rs:670-683 (TV_ERR_ALLOWLIST_EMPTY,
+ * TV_ERR_UNKNOWN_ID for the first unknown id in list order).  ids_of: slots -> ids (id_map.rs:695-705). ---- */
+typedef struct tv_idtable tv_idtable;
+int tv_idtable_create(tv_idtable **out);
+void tv_idtable_destroy(tv_idtable *t);
+size_t tv_idtable_len(const tv_idtable *t);
+const char *tv_idtable_last_error(const tv_idtable *t, uint64_t *id);
+int tv_idtable_add(tv_idtable *t, const uint64_t *ids, size_t n);
+int tv_idtable_truncate(tv_idtable *t, size_t n);
+int tv_idtable_remove(tv_idtable *t, uint64_t id, int *removed, uint64_t *slot, uint64_t *moved_from);
+int tv_idtable_contains(const tv_idtable *t, uint64_t id, int *present);
+int tv_idtable_resolve(const tv_idtable *t, const uint64_t *ids, size_t n, uint64_t *slots_out);
+int tv_idtable_ids_of(const tv_idtable *t, const int64_t *slots, size_t n, uint64_t *ids_out);
+int tv_idtable_ids(const tv_idtable *t, uint64_t *ids_out, size_t capacity);
 
 /* Search that performs no allocation of any kind.  This entry point has no counterpart in the reference:
  * it exists for callers that must not reach the CUDA allocator while they serve — latency-critical loops

@@ -10,7 +10,7 @@ import torch
 import torch.distributed as dist
 import torch.multiprocessing as mp
 
-from turbovec_b200.sharded import ShardedIndex, SlotMap, merge_topk
+from turbovec_b200.sharded import IdTable, ShardedIdMapIndex, ShardedIndex, SlotMap, merge_topk, pack_mask_words
 
 
 def test_slot_map_roundtrip_and_balance():
@@ -102,6 +102,44 @@ def _worker(rank, world, port, results):
             rs, ri = ref.search(q, 7)
             ok &= bool(np.array_equal(i, ri) and np.allclose(s, rs))
         out["remove"] = bool(ok) and len(idx) == len(ref)
+
+        # id-mapped: replicated id tables, allowlists, removal by id (same-rank and cross-rank moves)
+        ids = (rng.permutation(n) + 10**9).astype(np.uint64)
+        im = ShardedIdMapIndex(dim, 4, device=torch.device("cpu"), chunk_blocks=2, local_factory=FakeLocal)
+        for a, b in ((0, 130), (130, 131), (131, 700)):
+            im.add_with_ids(x[a:b], ids[a:b])
+        ref2, ref_ids = FakeLocal(dim, 4), list(ids)
+        ref2.add(x)
+        ok = True
+        s, got = im.search(q, 10)
+        rs, ri = ref2.search(q, 10)
+        ok &= bool(np.array_equal(got, np.array(ref_ids, np.uint64)[ri]) and np.allclose(s, rs))
+        allow = np.ascontiguousarray(ids[::9])
+        s, got = im.search(q, 100, allowlist=allow)
+        amask = np.isin(np.array(ref_ids, np.uint64), allow)
+        rs, ri = ref2.search(q, 100, mask=amask)
+        ok &= bool(s.shape == (5, min(100, allow.size)) and np.array_equal(got, np.array(ref_ids, np.uint64)[ri]))
+        for victim in (int(ids[3]), int(ids[690]), int(ids[64]), int(ids[699])):
+            ok &= im.remove(victim) and not im.contains(victim) and not im.remove(victim)
+            slot = ref_ids.index(victim)
+            last = ref2.swap_remove(slot)
+            ref_ids[slot] = ref_ids[last]
+            ref_ids.pop()
+            s, got = im.search(q, 7)
+            rs, ri = ref2.search(q, 7)
+            ok &= bool(np.array_equal(got, np.array(ref_ids, np.uint64)[ri]) and np.allclose(s, rs))
+        ok &= bool(np.array_equal(im.ids(), np.array(ref_ids, np.uint64)))
+        try:
+            im.add_with_ids(x[:2], np.array([ref_ids[0], 5], np.uint64))     # already present: nothing changes
+            ok = False
+        except ValueError:
+            ok &= len(im) == len(ref_ids) and not im.contains(5)
+        try:
+            im.search(q, 3, allowlist=np.array([12345], np.uint64))
+            ok = False
+        except KeyError:
+            pass
+        out["idmap"] = bool(ok)
         results[rank] = out
     finally:
         dist.destroy_process_group()
@@ -116,4 +154,43 @@ def test_sharded_index_two_gloo_ranks():
     mp.spawn(_worker, args=(2, port, results), nprocs=2, join=True)
     assert len(results) == 2
     for rank in (0, 1):
-        assert results[rank] == {"plain": True, "masked": True, "remove": True}, results[rank]
+        assert results[rank] == {"plain": True, "masked": True, "remove": True, "idmap": True}, results[rank]
+
+
+def test_id_table_semantics():
+    t = IdTable()
+    t.add(np.array([10, 11, 12, 13], np.uint64))
+    assert len(t) == 4 and t.contains(12) and not t.contains(9)
+    with pytest.raises(ValueError, match="already present"):
+        t.add(np.array([20, 11], np.uint64))
+    with pytest.raises(ValueError, match="twice in the batch"):
+        t.add(np.array([20, 20], np.uint64))
+    assert len(t) == 4 and not t.contains(20)
+    assert t.remove(11) == (True, 1, 3)                    # the last slot's id moves into slot 1
+    assert np.array_equal(t.ids(), np.array([10, 13, 12], np.uint64))
+    assert t.remove(11) == (False, 0, 0)
+    assert np.array_equal(t.resolve(np.array([12, 10, 12], np.uint64)), np.array([2, 0, 2], np.uint64))
+    with pytest.raises(KeyError, match="11"):
+        t.resolve(np.array([10, 11, 99], np.uint64))       # the first unknown id in list order
+    with pytest.raises(ValueError, match="empty"):
+        t.resolve(np.array([], np.uint64))
+    assert np.array_equal(t.ids_of(np.array([[2, 0]], np.int64)), np.array([[12, 10]], np.uint64))
+    t.truncate(1)
+    assert np.array_equal(t.ids(), np.array([10], np.uint64)) and not t.contains(13)
+
+
+def test_local_mask_words_gather():
+    for world in (1, 2, 3):
+        m = SlotMap(world, chunk_blocks=2)                  # 64 slots per chunk: one word
+        for n in (1, 63, 64, 65, 200, 64 * world * 3, 64 * world * 3 + 5):
+            mask = np.random.default_rng(n).random(n) < 0.4
+            flags = torch.zeros(((n + 63) // 64) * 64, dtype=torch.uint8)
+            flags[:n] = torch.from_numpy(mask.view(np.uint8))
+            words = pack_mask_words(torch, flags)
+            for r in range(world):
+                n_local = m.local_len(r, n)
+                got = m.local_mask_words(torch, words, r, n)
+                want = np.zeros(((n_local + 63) // 64) * 64, bool)
+                want[:n_local] = mask[m.to_global(r, np.arange(n_local))]
+                want_words = pack_mask_words(torch, torch.from_numpy(want.view(np.uint8)))
+                assert torch.equal(got, want_words)

@@ -487,12 +487,13 @@ def measure_int8_peak(device: int = 0) -> float:
 
 
 def merge_keys_device(keys_ptr: int, n_lists: int, nq: int, k: int, scores_ptr: int, slots_ptr: int, *, device: int = 0,
-                      stream: int = 0) -> None:
+                      stream: int = 0, chunk_slots: int = 0) -> None:
     """keys[n_lists][nq][k] (device memory, e.g. all-gathered search_device_keys rows) -> per query the k best,
     decoded into scores[nq][k] (float32) and global slots[nq][k] (int64).  Enqueued on `stream` (a raw
-    cudaStream_t value, 0 = default stream) without synchronising."""
+    cudaStream_t value, 0 = default stream) without synchronising.  chunk_slots > 0: list r carries local slots of the
+    shard that owns the slot chunks r, r + n_lists, ... of that size; they are made global before the merge."""
     lib = _native.load()
-    rc = lib.tv_merge_keys_device(device, C.c_void_p(keys_ptr), n_lists, nq, k, C.c_void_p(scores_ptr), C.c_void_p(slots_ptr),
-                                  C.c_void_p(stream) if stream else None)
+    rc = lib.tv_merge_keys_device_chunked(device, C.c_void_p(keys_ptr), n_lists, nq, k, chunk_slots, C.c_void_p(scores_ptr),
+                                          C.c_void_p(slots_ptr), C.c_void_p(stream) if stream else None)
     if rc != 0:
         raise RuntimeError(lib.tv_last_error(None).decode() or f"tv_merge_keys_device failed with status {rc}")

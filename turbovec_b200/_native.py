@@ -22,6 +22,18 @@ SIGNATURES = {
     "tv_exchange_layout_conflicts": (C.c_int, [C.c_size_t] + [C.POINTER(C.c_int)] * 4),
     "tv_search_device_keys": (C.c_int, [_H, C.c_void_p, C.c_size_t, C.c_size_t, C.c_void_p, C.c_uint64, C.c_void_p, C.POINTER(C.c_size_t)]),
     "tv_merge_keys_device": (C.c_int, [C.c_int, C.c_void_p, C.c_size_t, C.c_size_t, C.c_size_t, C.c_void_p, C.c_void_p, C.c_void_p]),
+    "tv_merge_keys_device_chunked": (C.c_int, [C.c_int, C.c_void_p, C.c_size_t, C.c_size_t, C.c_size_t, C.c_size_t, C.c_void_p, C.c_void_p, C.c_void_p]),
+    "tv_idtable_create": (C.c_int, [C.POINTER(_H)]),
+    "tv_idtable_destroy": (None, [_H]),
+    "tv_idtable_len": (C.c_size_t, [_H]),
+    "tv_idtable_last_error": (C.c_char_p, [_H, _u64p]),
+    "tv_idtable_add": (C.c_int, [_H, C.c_void_p, C.c_size_t]),
+    "tv_idtable_truncate": (C.c_int, [_H, C.c_size_t]),
+    "tv_idtable_remove": (C.c_int, [_H, C.c_uint64, _intp, _u64p, _u64p]),
+    "tv_idtable_contains": (C.c_int, [_H, C.c_uint64, _intp]),
+    "tv_idtable_resolve": (C.c_int, [_H, C.c_void_p, C.c_size_t, C.c_void_p]),
+    "tv_idtable_ids_of": (C.c_int, [_H, C.c_void_p, C.c_size_t, C.c_void_p]),
+    "tv_idtable_ids": (C.c_int, [_H, C.c_void_p, C.c_size_t]),
     "tv_quantise_grid_lookup": (C.c_int, [C.POINTER(C.c_float), C.c_int, C.POINTER(C.c_float), C.c_size_t, C.POINTER(C.c_uint8)]),
     "tv_index_create": (C.c_int, [C.c_size_t, C.c_int, C.c_int, C.c_int, C.POINTER(_H)]),
     "tv_index_destroy": (None, [_H]),

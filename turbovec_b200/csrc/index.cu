@@ -1610,16 +1610,22 @@ int tv_search_device_prepared(tv_index *h, const float *queries_device, size_t n
     return rc;
 }
 
-int tv_merge_keys_device(int device, const uint64_t *keys_device, size_t n_lists, size_t nq, size_t k, float *scores_out_device,
-                         int64_t *slots_out_device, void *stream) {
+int tv_merge_keys_device_chunked(int device, const uint64_t *keys_device, size_t n_lists, size_t nq, size_t k, size_t chunk_slots,
+                                 float *scores_out_device, int64_t *slots_out_device, void *stream) {
     if (!keys_device || !scores_out_device || !slots_out_device) return TV_ERR_INVALID_ARGUMENT;
     if (n_lists == 0 || nq == 0 || k == 0) return TV_OK;
     if (n_lists * k > size_t(kMergeMaxKeys)) { g_create_error = "n_lists * k exceeds 8192 keys per query"; return TV_ERR_UNSUPPORTED; }
+    if (chunk_slots > 0xffffffffull || chunk_slots % kBlock != 0) { g_create_error = "chunk_slots must be a multiple of 32 below 2^32"; return TV_ERR_INVALID_ARGUMENT; }
     if (cudaSetDevice(device) != cudaSuccess) { g_create_error = "cudaSetDevice failed"; return TV_ERR_CUDA; }
-    cudaError_t e = launch_merge_keys(keys_device, int(n_lists), int(nq), int(k), scores_out_device, slots_out_device,
-                                      static_cast<cudaStream_t>(stream));
+    cudaError_t e = launch_merge_keys(keys_device, int(n_lists), int(nq), int(k), uint32_t(chunk_slots), scores_out_device,
+                                      slots_out_device, static_cast<cudaStream_t>(stream));
     if (e != cudaSuccess) { g_create_error = std::string("merge kernel launch: ") + cudaGetErrorString(e); return TV_ERR_CUDA; }
     return TV_OK;
+}
+
+int tv_merge_keys_device(int device, const uint64_t *keys_device, size_t n_lists, size_t nq, size_t k, float *scores_out_device,
+                         int64_t *slots_out_device, void *stream) {
+    return tv_merge_keys_device_chunked(device, keys_device, n_lists, nq, k, 0, scores_out_device, slots_out_device, stream);
 }
 
 // -----------------------------------------------------------------------------------------------------

@@ -583,15 +583,24 @@ __global__ void export_keys_kernel(const uint64_t *topk, int64_t count, uint64_t
 
 // Merge of the per-shard result lists of one query: keys[list][q][k] -> the k best keys, decoded.  One CTA per
 // query, bitonic sort of n_lists * k keys in shared memory (ascending keys = score descending, slot ascending).
+// chunk_slots > 0: the lists hold LOCAL slots of shards that own chunks of that many slots round-robin (list r owns
+// the chunks r, r + n_lists, ...); they become global slots before the sort, so ties break by the global slot.
 __global__ void __launch_bounds__(256) merge_keys_kernel(const uint64_t *keys_in, int n_lists, int nq, int k, int n2,
-                                                         float *scores, int64_t *slots) {
+                                                         uint32_t chunk_slots, float *scores, int64_t *slots) {
     extern __shared__ __align__(16) unsigned char smem_raw[];
     uint64_t *keys = reinterpret_cast<uint64_t *>(smem_raw);
     const int q = blockIdx.x, tid = threadIdx.x;
     const int total = n_lists * k;
     for (int i = tid; i < n2; i += blockDim.x) {
         uint64_t v = kEmptyKey;
-        if (i < total) v = keys_in[(size_t(i / k) * nq + q) * k + (i % k)];
+        if (i < total) {
+            v = keys_in[(size_t(i / k) * nq + q) * k + (i % k)];
+            if (chunk_slots != 0 && v != kEmptyKey) {
+                const uint32_t local = uint32_t(v), list = uint32_t(i / k);
+                const uint64_t global = (uint64_t(local / chunk_slots) * uint32_t(n_lists) + list) * chunk_slots + local % chunk_slots;
+                v = (v & 0xffffffff00000000ull) | global;
+            }
+        }
         keys[i] = v;
     }
     __syncthreads();
@@ -693,14 +702,15 @@ cudaError_t launch_export_keys(const uint64_t *topk, int64_t count, uint64_t off
     return cudaGetLastError();
 }
 
-cudaError_t launch_merge_keys(const uint64_t *keys, int n_lists, int nq, int k, float *scores, int64_t *slots, cudaStream_t s) {
+cudaError_t launch_merge_keys(const uint64_t *keys, int n_lists, int nq, int k, uint32_t chunk_slots, float *scores, int64_t *slots,
+                              cudaStream_t s) {
     if (nq <= 0 || k <= 0 || n_lists <= 0) return cudaSuccess;
     int n2 = 32;
     while (n2 < n_lists * k) n2 <<= 1;
     if (n2 > kMergeMaxKeys) return cudaErrorInvalidValue;
     cudaError_t e = cudaFuncSetAttribute(merge_keys_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, kMergeMaxKeys * 8);
     if (e != cudaSuccess) return e;
-    merge_keys_kernel<<<nq, 256, size_t(n2) * 8, s>>>(keys, n_lists, nq, k, n2, scores, slots);
+    merge_keys_kernel<<<nq, 256, size_t(n2) * 8, s>>>(keys, n_lists, nq, k, n2, chunk_slots, scores, slots);
     return cudaGetLastError();
 }
 

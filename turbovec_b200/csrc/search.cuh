@@ -64,7 +64,10 @@ cudaError_t launch_select(const CandidateBuffers &cb, int nq, int dense_count, c
 cudaError_t launch_export_keys(const uint64_t *topk, int64_t count, uint64_t offset, uint64_t *out, cudaStream_t s);
 // keys[n_lists][nq][k] -> per query the k best of all lists, decoded; n_lists * k at most kMergeMaxKeys.
 constexpr int kMergeMaxKeys = 8192;
-cudaError_t launch_merge_keys(const uint64_t *keys, int n_lists, int nq, int k, float *scores, int64_t *slots, cudaStream_t s);
+// chunk_slots > 0: list r holds local slots of the shard that owns the slot chunks r, r + n_lists, ... (round-robin);
+// they are turned into global slots before the merge.
+cudaError_t launch_merge_keys(const uint64_t *keys, int n_lists, int nq, int k, uint32_t chunk_slots, float *scores, int64_t *slots,
+                              cudaStream_t s);
 // topk keys -> scores / slots with row stride k_eff = min(k, n_allowed); *k_eff_out receives it.
 cudaError_t launch_finalize(const CandidateBuffers &cb, int nq, const unsigned long long *n_allowed_or_null,
                             int64_t n, float *scores, int64_t *slots, uint32_t *k_eff_out, int out_stride_is_k,
