@@ -282,7 +282,7 @@ def run_ours(args):
         idx = ShardedIdMapIndex(DIM, BITS, device=device)
         local = idx.local
     for opt, val in ((T.OPT_MMA_MIN_BATCH, args.tc_min_batch), (T.OPT_INGEST_PIPELINE, args.ingest_pipeline),
-                     (T.OPT_SMALL_SCAN, args.small_scan)):
+                     (T.OPT_SMALL_SCAN, args.small_scan), (T.OPT_TC_PAIR, args.tc_pair), (T.OPT_TC_WIDE, args.tc_wide)):
         if val is not None:
             local.set_option(opt, val)
     n_recall_q = 64
@@ -696,6 +696,8 @@ def main():
     ap.add_argument("--ingest-pipeline", type=int, default=None, choices=[0, 1, 2],
                     help="TV_OPT_INGEST_PIPELINE: 0 = block-at-a-time ingest kernel only (default: library default, 1)")
     ap.add_argument("--small-scan", type=int, default=None, help="TV_OPT_SMALL_SCAN variant (-1 = scan_pd_kernel)")
+    ap.add_argument("--tc-pair", type=int, default=None, choices=[0, 1], help="TV_OPT_TC_PAIR: tensor-memory scan on CTA pairs")
+    ap.add_argument("--tc-wide", type=int, default=None, choices=[0, 1], help="TV_OPT_TC_WIDE: two query groups per expanded code slab")
     ap.add_argument("--skip-cpu", dest="no_cpu", action="store_true", help="skip the cpu_baseline leg")
     ap.add_argument("--skip-filtered", dest="no_filtered", action="store_true", help="skip the filtered-search and allocation-free legs")
     ap.add_argument("--skip-mutation", dest="no_mutation", action="store_true", help="skip the online-mutation leg")

@@ -109,8 +109,13 @@ enum {
     TV_OPT_SMALL_SCAN = 7,      /* permute-dot batches of up to 16 queries: -1 = the general small-batch kernel; otherwise
                                  * a variant of the stream-shaped kernel (bits 0-1: ring depth 3 / 4 / 6 stages per warp,
                                  * bit 2: swizzled tensor copies instead of plain bulk copies; default 5).  Results are identical. */
-    TV_OPT_FAIL_NEXT = 8        /* testing: the n-th guarded device allocation / upload from now on reports an
+    TV_OPT_FAIL_NEXT = 8,       /* testing: the n-th guarded device allocation / upload from now on reports an
                                  * out-of-memory failure instead of running (1 = the next one); 0 disarms */
+    TV_OPT_TC_PAIR = 9,         /* 1: permute-dot batches of more than 64 queries run the tensor-memory scan on pairs of
+                                 * CTAs (tcgen05 cta_group::2: each SM loads half of every query slab); 0: one CTA per
+                                 * work item (default: it measured slower).  Results are identical. */
+    TV_OPT_TC_WIDE = 10         /* 1 (default): batches of more than 256 queries run the tensor-memory scan whose work items
+                                 * take two query groups per expanded code slab; 0: one group per item.  Identical results. */
 };
 
 /* ---- construction: TurboQuantIndex::new / new_lazy (lib.rs:629, 670), IdMapIndex::new (id_map.rs:278) ---- */

@@ -67,6 +67,31 @@ def test_small_scan_many_chunks_and_recovery(T):
         assert np.array_equal(i, want[1]) and np.array_equal(s, want[0])
 
 
+# ------------------------------------------------------------------ tensor-memory scan on CTA pairs
+@pytest.mark.parametrize("dim,n,nq", [(1536, 5003, 70), (1536, 4100, 300), (256, 4100, 257), (200, 9000, 1024), (1536, 40_000, 129),
+                                      (64, 300_000, 65), (256, 20_000, 513), (128, 9000, 770)])
+@pytest.mark.parametrize("form", ["pair", "wide", "narrow"])
+def test_pair_tensor_scan_matches_oracle(T, dim, n, nq, form):
+    """The three forms of the tensor-memory scan: CTA pairs (tcgen05 cta_group::2, work items of 256 vectors x 256
+    queries), two query groups per expanded slab (batches above 256 queries; 513 and 770 queries end in an item of one
+    group), one group per item.  Odd numbers of 128-vector tiles, several chunks, partial query groups, masks."""
+    x = anisotropic(n, dim, seed=57)
+    q = anisotropic(nq, dim, seed=57, offset=31)
+    pre = oracle_index(x, 4)
+    idx = T.TurboQuantIndex(dim, 4)
+    idx.add(x)
+    idx.set_option(T.OPT_TC_PAIR, 1 if form == "pair" else 0)
+    idx.set_option(T.OPT_TC_WIDE, 1 if form == "wide" else 0)
+    mask = np.random.default_rng(6).random(n) < 0.2
+    for k in (10, 100):
+        s, i = idx.search(q, k)
+        rs, ri = oracle_search(x, q, 4, k, pre=pre)
+        assert np.array_equal(i, ri) and np.array_equal(s, rs), f"k={k}"
+    s, i = idx.search(q, 10, mask=mask)
+    rs, ri = oracle_search(x, q, 4, 10, mask=mask, pre=pre)
+    assert np.array_equal(i, ri) and np.array_equal(s, rs), "masked"
+
+
 # ------------------------------------------------------------------ k above one selection pass
 @pytest.mark.parametrize("bits,dim", [(4, 64), (2, 64)])
 def test_paged_topk_beyond_4096(T, bits, dim):

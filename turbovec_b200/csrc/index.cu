@@ -198,6 +198,8 @@ struct tv_index {
     int tc_tiles = 1;            // accumulator tiles per B slab in the tcgen05 scan (1 or 2); 1 measured faster
     int small_scan = 5;          // permute-dot scan for up to 16 queries: -1 = scan_pd_kernel, else a scan_small_kernel variant
                                  // (5 = four-stage rings, two CTAs per SM, swizzled tensor copies: the fastest measured)
+    int tc_wide = 1;             // 1: batches above 256 queries share every expanded code slab between two query groups
+    int tc_pair = 0;             // 1: permute-dot batches above 64 queries run the tensor-memory scan on CTA pairs (cta_group::2)
     int fail_next = 0;           // test hook (TV_OPT_FAIL_NEXT): the next device allocation / upload of a call reports failure
 
     cudaStream_t stream = nullptr;           // mutations and accessors
@@ -822,7 +824,14 @@ int enqueue_search(tv_index *h, cudaStream_t st, Marks *marks, const SearchScrat
         if (plan.use_tc) {
             sp.q_base = 0; sp.nq = int(nq); sp.mtile_base = 0;
             if (marks) marks->begin(st);
-            if (mode == TV_SCORE_PERMUTE_DOT)
+            const bool wide = h->tc_wide && scan_tc_wide_supported(h->bits, mode, ng, int(nq));
+            if (mode == TV_SCORE_PERMUTE_DOT && h->tc_pair && scan_tc_pair_supported(h->bits, mode, int(nq)))
+                TV_CUDA(launch_scan_tc_pair(sp, S.weights, int(S.w_rows), int(S.dim_pad), h->sm_count, st));
+            else if (wide && mode == TV_SCORE_PERMUTE_DOT)
+                TV_CUDA(launch_scan_tc_wide(sp, S.weights, int(S.w_rows), int(S.dim_pad), h->sm_count, st));
+            else if (wide)
+                TV_CUDA(launch_scan_tc_wide(sp, reinterpret_cast<const int8_t *>(S.luts), int(S.w_rows), ng * 32, h->sm_count, st));
+            else if (mode == TV_SCORE_PERMUTE_DOT)
                 TV_CUDA(launch_scan_tc(sp, S.weights, int(S.w_rows), int(S.dim_pad), h->sm_count, h->tc_tiles, st));
             else
                 TV_CUDA(launch_scan_tc(sp, reinterpret_cast<const int8_t *>(S.luts), int(S.w_rows), ng * 32, h->sm_count, 1, st));
@@ -1280,6 +1289,8 @@ int tv_set_option(tv_index *h, int option, int64_t value) {
         case TV_OPT_PD_SPLIT: h->pd_split = value != 0; return TV_OK;
         case TV_OPT_SMALL_SCAN: h->small_scan = value < 0 ? -1 : int(value & 7); return TV_OK;
         case TV_OPT_FAIL_NEXT: h->fail_next = value < 0 ? 0 : int(value); return TV_OK;
+        case TV_OPT_TC_PAIR: h->tc_pair = value != 0; return TV_OK;
+        case TV_OPT_TC_WIDE: h->tc_wide = value != 0; return TV_OK;
         default: return fail(h, TV_ERR_INVALID_ARGUMENT, "unknown option");
     }
 }
@@ -1295,6 +1306,8 @@ int64_t tv_get_option(const tv_index *h, int option) {
         case TV_OPT_PD_SPLIT: return h->pd_split;
         case TV_OPT_SMALL_SCAN: return h->small_scan;
         case TV_OPT_FAIL_NEXT: return h->fail_next;
+        case TV_OPT_TC_PAIR: return h->tc_pair;
+        case TV_OPT_TC_WIDE: return h->tc_wide;
         default: return -1;
     }
 }

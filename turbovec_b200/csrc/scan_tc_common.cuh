@@ -1,0 +1,125 @@
+// Device-side pieces shared by the tensor-memory scans (scan_tc.cu: one CTA per work item; scan_tc2.cu: CTA pairs):
+// constants of the MMA tiling, bounded mbarrier waits, the nibble -> int8 level lookup, shared-memory and
+// instruction descriptors, TMA and TMEM wrappers, and the float epilogue of the score families.
+#pragma once
+#include <cuda.h>
+
+#include <cstddef>
+
+#include "search.cuh"
+#include "tv_common.cuh"
+
+namespace tv {
+namespace {
+
+constexpr int kMmaM = 128;                                    // vectors per accumulator tile (TMEM lanes)
+constexpr int kMaxTileQueries = 256;                          // largest MMA N (query columns of a work item)
+constexpr int kSlabK = 128;                                   // int8 elements (bytes) of K per stage
+constexpr int kATileBytes = kMmaM * kSlabK;                   // 16 KB per accumulator tile and stage
+constexpr int kExpandWarps = 8;
+constexpr int kEpilogueWarps = 8;                             // two per TMEM lane quarter, 128 columns each
+constexpr int kThreadsTc = (2 + kEpilogueWarps + kExpandWarps) * 32;   // 576
+constexpr uint32_t kWaitLimitTc = 1u << 22;
+
+__device__ __forceinline__ uint32_t smem_u32(const void *p) { return uint32_t(__cvta_generic_to_shared(p)); }
+__device__ __forceinline__ void mbar_init(uint64_t *bar, uint32_t count) {
+    asm volatile("mbarrier.init.shared::cta.b64 [%0], %1;" ::"r"(smem_u32(bar)), "r"(count));
+}
+__device__ __forceinline__ void mbar_arrive(uint64_t *bar) {
+    asm volatile("mbarrier.arrive.shared::cta.b64 _, [%0];" ::"r"(smem_u32(bar)) : "memory");
+}
+__device__ __forceinline__ void mbar_arrive_expect_tx(uint64_t *bar, uint32_t bytes) {
+    asm volatile("mbarrier.arrive.expect_tx.shared::cta.b64 _, [%0], %1;" ::"r"(smem_u32(bar)), "r"(bytes) : "memory");
+}
+__device__ __forceinline__ bool mbar_try_wait(uint64_t *bar, uint32_t parity) {
+    uint32_t ok;
+    asm volatile(
+        "{\n\t.reg .pred p;\n\t"
+        "mbarrier.try_wait.parity.shared::cta.b64 p, [%1], %2;\n\t"
+        "selp.u32 %0, 1, 0, p;\n\t}"
+        : "=r"(ok) : "r"(smem_u32(bar)), "r"(parity) : "memory");
+    return ok != 0;
+}
+__device__ __forceinline__ bool mbar_wait(uint64_t *bar, uint32_t parity, uint32_t *error_flag) {
+    for (uint32_t i = 0; i < kWaitLimitTc; ++i)
+        if (mbar_try_wait(bar, parity)) return true;
+    atomicExch(error_flag, 2u);
+    return false;
+}
+__device__ __forceinline__ uint32_t prmt(uint32_t a, uint32_t b, uint32_t sel) {
+    uint32_t d;
+    asm("prmt.b32 %0, %1, %2, %3;" : "=r"(d) : "r"(a), "r"(b), "r"(sel));
+    return d;
+}
+// high 32 bits of a * b + c on the FMA pipe: a right shift that does not load the ALU pipe
+__device__ __forceinline__ uint32_t mad_hi(uint32_t a, uint32_t b, uint32_t c) {
+    uint32_t d;
+    asm("mad.hi.u32 %0, %1, %2, %3;" : "=r"(d) : "r"(a), "r"(b), "r"(c));
+    return d;
+}
+// Eight nibbles of x -> eight int8 levels; output byte i of (lo, hi) belongs to nibble i / i+4 of x.
+__device__ __forceinline__ void expand8(uint32_t x, const uint32_t (&T)[4], uint32_t &lo, uint32_t &hi) {
+    const uint32_t idx = x & 0x77777777u;
+    const uint32_t pick = mad_hi(x & 0x88888888u, 0x80000000u, 0x32103210u);   // ((x >> 1) & 0x4..4) | 0x3210..
+    lo = prmt(prmt(T[0], T[1], idx), prmt(T[2], T[3], idx), pick);
+    const uint32_t idx_h = mad_hi(idx, 0x10000u, 0u), pick_h = mad_hi(pick, 0x10000u, 0u);
+    hi = prmt(prmt(T[0], T[1], idx_h), prmt(T[2], T[3], idx_h), pick_h);
+}
+
+// K-major, 128-byte swizzle, 8-row groups 1024 B apart; version 1 (sm_100), base offset 0.
+__device__ __forceinline__ uint64_t umma_desc(uint32_t smem_byte_addr) {
+    uint64_t d = 0;
+    d |= uint64_t((smem_byte_addr >> 4) & 0x3fffu);           // start address
+    d |= uint64_t(1) << 16;                                    // leading byte offset (unused for swizzled K-major)
+    d |= uint64_t(1024 >> 4) << 32;                            // stride byte offset
+    d |= uint64_t(1) << 46;                                    // descriptor version
+    d |= uint64_t(2) << 61;                                    // SWIZZLE_128B
+    return d;
+}
+// kind::i8: D = S32, A = B = signed 8-bit, both K-major, M = 128, N = NQT.
+template <int NQT>
+__device__ __forceinline__ void umma_i8(uint32_t d_tmem, uint64_t a_desc, uint64_t b_desc, uint32_t accumulate) {
+    constexpr uint32_t kIdesc = (2u << 4) | (1u << 7) | (1u << 10) | (uint32_t(NQT >> 3) << 17) | (uint32_t(kMmaM >> 4) << 24);
+    asm volatile(
+        "{\n\t.reg .pred p;\n\t"
+        "setp.ne.b32 p, %4, 0;\n\t"
+        "tcgen05.mma.cta_group::1.kind::i8 [%0], %1, %2, %3, {%5, %6, %7, %8}, p;\n\t}"
+        ::"r"(d_tmem), "l"(a_desc), "l"(b_desc), "r"(kIdesc), "r"(accumulate), "r"(0u), "r"(0u), "r"(0u), "r"(0u)
+        : "memory");
+}
+__device__ __forceinline__ void umma_commit(uint64_t *bar) {
+    asm volatile("tcgen05.commit.cta_group::1.mbarrier::arrive::one.shared::cluster.b64 [%0];" ::"r"(smem_u32(bar)) : "memory");
+}
+__device__ __forceinline__ void tma_load_2d(void *dst, const CUtensorMap *map, int x, int y, uint64_t *bar) {
+    asm volatile(
+        "cp.async.bulk.tensor.2d.shared::cluster.global.tile.mbarrier::complete_tx::bytes [%0], [%1, {%3, %4}], [%2];"
+        ::"r"(smem_u32(dst)), "l"(map), "r"(smem_u32(bar)), "r"(x), "r"(y) : "memory");
+}
+__device__ __forceinline__ void tmem_ld32(uint32_t taddr, uint32_t (&r)[32]) {
+    asm volatile(
+        "tcgen05.ld.sync.aligned.32x32b.x32.b32 "
+        "{%0, %1, %2, %3, %4, %5, %6, %7, %8, %9, %10, %11, %12, %13, %14, %15, "
+        "%16, %17, %18, %19, %20, %21, %22, %23, %24, %25, %26, %27, %28, %29, %30, %31}, [%32];"
+        : "=r"(r[0]), "=r"(r[1]), "=r"(r[2]), "=r"(r[3]), "=r"(r[4]), "=r"(r[5]), "=r"(r[6]), "=r"(r[7]), "=r"(r[8]),
+          "=r"(r[9]), "=r"(r[10]), "=r"(r[11]), "=r"(r[12]), "=r"(r[13]), "=r"(r[14]), "=r"(r[15]), "=r"(r[16]),
+          "=r"(r[17]), "=r"(r[18]), "=r"(r[19]), "=r"(r[20]), "=r"(r[21]), "=r"(r[22]), "=r"(r[23]), "=r"(r[24]),
+          "=r"(r[25]), "=r"(r[26]), "=r"(r[27]), "=r"(r[28]), "=r"(r[29]), "=r"(r[30]), "=r"(r[31])
+        : "r"(taddr));
+}
+
+__device__ __forceinline__ void tmem_ld8(uint32_t taddr, uint32_t (&r)[8]) {
+    asm volatile("tcgen05.ld.sync.aligned.32x32b.x8.b32 {%0, %1, %2, %3, %4, %5, %6, %7}, [%8];"
+                 : "=r"(r[0]), "=r"(r[1]), "=r"(r[2]), "=r"(r[3]), "=r"(r[4]), "=r"(r[5]), "=r"(r[6]), "=r"(r[7])
+                 : "r"(taddr));
+}
+
+// Float epilogue of the two score families; the integer sum is exact in both.
+template <bool ONEHOT>
+__device__ __forceinline__ float final_score(uint32_t isum, float qs, float qb, float vs) {
+    const float f = float(int(isum));
+    if constexpr (ONEHOT) return __fmul_rn(__fadd_rn(__fmul_rn(f, qs), qb), vs);   // search.rs:1176, then x vec_scale
+    else return __fmul_rn(fmaf(f, qs, qb), vs);                                    // search.rs:1523, 1793
+}
+
+}  // namespace
+}  // namespace tv
