@@ -92,6 +92,32 @@ def test_pair_tensor_scan_matches_oracle(T, dim, n, nq, form):
     assert np.array_equal(i, ri) and np.array_equal(s, rs), "masked"
 
 
+# ------------------------------------------------------------------ u8-LUT flush family on tensor memory
+@pytest.mark.parametrize("dim,n,nq", [(200, 6000, 9), (200, 6000, 300), (1000, 3000, 40), (1016, 2500, 600), (1032, 2000, 12), (40, 5000, 70)])
+def test_flush_family_scan_matches_oracle(T, dim, n, nq):
+    """2-bit geometries whose byte-group count is not a multiple of 4 (the reference's per-256-group fma family,
+    search.rs:516, 577).  Up to 256 groups the batch runs on the tensor-memory scan with K padded to whole slabs;
+    dim 1032 (258 groups) needs the partial sums and stays on the CUDA-core scan."""
+    x = anisotropic(n, dim, seed=63)
+    q = anisotropic(nq, dim, seed=63, offset=17)
+    pre = oracle_index(x, 2)
+    idx = T.TurboQuantIndex(dim, 2)
+    idx.add(x)
+    assert idx.get_option(T.OPT_SCORE_MODE) == T.SCORE_LUT_FLUSH
+    mask = np.random.default_rng(8).random(n) < 0.3
+    for k in (10, 100):
+        s, i = idx.search(q, k)
+        rs, ri = oracle_search(x, q, 2, k, pre=pre)
+        assert np.array_equal(i, ri) and np.array_equal(s, rs), f"k={k}"
+    s, i = idx.search(q, 10, mask=mask)
+    rs, ri = oracle_search(x, q, 2, 10, mask=mask, pre=pre)
+    assert np.array_equal(i, ri) and np.array_equal(s, rs), "masked"
+    idx.set_option(T.OPT_MMA_MIN_BATCH, 0)                  # the CUDA-core scan gives the same bits
+    s, i = idx.search(q, 10)
+    rs, ri = oracle_search(x, q, 2, 10, pre=pre)
+    assert np.array_equal(i, ri) and np.array_equal(s, rs), "CUDA-core scan"
+
+
 # ------------------------------------------------------------------ k above one selection pass
 @pytest.mark.parametrize("bits,dim", [(4, 64), (2, 64)])
 def test_paged_topk_beyond_4096(T, bits, dim):

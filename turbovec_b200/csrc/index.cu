@@ -695,7 +695,7 @@ struct SearchScratch {
     uint8_t *luts;
     uint64_t *cand, *thr, *topk, *lo;      // lo: lowest admissible key per query (paged top-k), or nullptr
     uint32_t *cnt;
-    size_t w_rows, dim_pad;
+    size_t w_rows, dim_pad, lut_pitch;
     int cap;
     bool allow_tc;
 };
@@ -792,7 +792,7 @@ int enqueue_search(tv_index *h, cudaStream_t st, Marks *marks, const SearchScrat
     ScanParams sp = base_scan_params(h, mode);
     sp.qscale = S.qscale; sp.qbias = S.qbias;
     sp.mask = m.words; sp.live_blocks = m.live; sp.n_live = m.n_live;
-    sp.cb = cb; sp.wfrag = S.wfrag; sp.mtiles_total = mt_total; sp.luts = S.luts;
+    sp.cb = cb; sp.wfrag = S.wfrag; sp.mtiles_total = mt_total; sp.luts = S.luts; sp.lut_pitch = int(S.lut_pitch);
     const bool use_small = plan.use_small && !plan.use_tc;
 
     TV_CUDA(cudaMemsetAsync(S.cnt, 0, nq * 4, st));
@@ -830,11 +830,11 @@ int enqueue_search(tv_index *h, cudaStream_t st, Marks *marks, const SearchScrat
             else if (wide && mode == TV_SCORE_PERMUTE_DOT)
                 TV_CUDA(launch_scan_tc_wide(sp, S.weights, int(S.w_rows), int(S.dim_pad), h->sm_count, st));
             else if (wide)
-                TV_CUDA(launch_scan_tc_wide(sp, reinterpret_cast<const int8_t *>(S.luts), int(S.w_rows), ng * 32, h->sm_count, st));
+                TV_CUDA(launch_scan_tc_wide(sp, reinterpret_cast<const int8_t *>(S.luts), int(S.w_rows), int(S.lut_pitch), h->sm_count, st));
             else if (mode == TV_SCORE_PERMUTE_DOT)
                 TV_CUDA(launch_scan_tc(sp, S.weights, int(S.w_rows), int(S.dim_pad), h->sm_count, h->tc_tiles, st));
             else
-                TV_CUDA(launch_scan_tc(sp, reinterpret_cast<const int8_t *>(S.luts), int(S.w_rows), ng * 32, h->sm_count, 1, st));
+                TV_CUDA(launch_scan_tc(sp, reinterpret_cast<const int8_t *>(S.luts), int(S.w_rows), int(S.lut_pitch), h->sm_count, 1, st));
             if (marks) marks->end(st);
             h->launches++;
         } else if (use_small) {
@@ -883,14 +883,14 @@ int enqueue_query_prep(tv_index *h, cudaStream_t st, const SearchScratch &S, con
     if (!h->shift.empty()) { qp.shift = h->d_calib.ptr; qp.scale_tq = h->d_calib.ptr + dim; }
     qp.level_scale = h->level_scale;
     qp.q_rot = S.q_rot; qp.qscale = S.qscale; qp.qbias = S.qbias;
-    qp.luts = S.luts; qp.weights = S.weights; qp.dim_pad = int(S.dim_pad);
+    qp.luts = S.luts; qp.lut_pitch = int(S.lut_pitch); qp.weights = S.weights; qp.dim_pad = int(S.dim_pad);
     qp.wfrag = S.wfrag; qp.mtiles_total = mt_total;
     qp.first_invalid = d_first_invalid;
     if (mode == TV_SCORE_PERMUTE_DOT) {
         TV_CUDA(cudaMemsetAsync(S.wfrag, 0, size_t(ksteps) * mt_total * 32 * 16, st));
         if (plan.use_tc) TV_CUDA(cudaMemsetAsync(S.weights, 0, S.w_rows * S.dim_pad, st));
     } else if (plan.use_tc) {
-        TV_CUDA(cudaMemsetAsync(S.luts, 0, S.w_rows * size_t(ng) * 32, st));
+        TV_CUDA(cudaMemsetAsync(S.luts, 0, S.w_rows * S.lut_pitch, st));
     }
     TV_CUDA(launch_query_prep(qp, st));
     h->launches++;
@@ -943,6 +943,7 @@ int search_core(tv_index *h, SearchCtx &c, const float *queries, bool queries_on
     const int mt_total = int(nq_pad / 16);
     const size_t dim_pad = (dim + 127) / 128 * 128;
     const int ksteps = (ng + 15) / 16;
+    const size_t lut_pitch = size_t((ng + 3) / 4 * 4) * 32;
 
     ScanPlan plan;
     int rc = plan_scan(h, mode, nq, pages == 1, plan);
@@ -959,7 +960,7 @@ int search_core(tv_index *h, SearchCtx &c, const float *queries, bool queries_on
         TV_CUDA(c.d_weights.reserve(w_rows * dim_pad));
         TV_CUDA(c.d_wfrag.reserve(size_t(ksteps) * mt_total * 32 * 4));
     } else {
-        TV_CUDA(c.d_luts.reserve(w_rows * size_t(ng) * 32));     // padded to whole query groups for the tensor path
+        TV_CUDA(c.d_luts.reserve(w_rows * lut_pitch));           // padded to whole query groups and whole K slabs for the tensor path
     }
     TV_CUDA(c.d_cand.reserve(nq * size_t(cap)));
     TV_CUDA(c.d_cnt.reserve(nq));
@@ -977,7 +978,7 @@ int search_core(tv_index *h, SearchCtx &c, const float *queries, bool queries_on
     SearchScratch S{};
     S.q_rot = c.d_qrot.ptr; S.qscale = c.d_qscale.ptr; S.qbias = c.d_qbias.ptr; S.weights = c.d_weights.ptr;
     S.wfrag = c.d_wfrag.ptr; S.luts = c.d_luts.ptr; S.cand = c.d_cand.ptr; S.thr = c.d_thr.ptr; S.topk = c.d_topk.ptr;
-    S.cnt = c.d_cnt.ptr; S.lo = nullptr; S.w_rows = w_rows; S.dim_pad = dim_pad; S.cap = cap; S.allow_tc = pages == 1;
+    S.cnt = c.d_cnt.ptr; S.lo = nullptr; S.w_rows = w_rows; S.dim_pad = dim_pad; S.lut_pitch = lut_pitch; S.cap = cap; S.allow_tc = pages == 1;
     {
         ScanParams probe = base_scan_params(h, mode);
         plan.use_small = h->small_scan >= 0 && mode == TV_SCORE_PERMUTE_DOT && scan_small_supported(probe, int(nq), h->smem_limit);
@@ -1731,7 +1732,7 @@ int tv_search_device_noalloc(tv_index *h, const float *queries_device, size_t nq
     SearchScratch S{};
     S.q_rot = L.q_rot; S.qscale = L.qscale; S.qbias = L.qbias; S.weights = L.weights; S.wfrag = L.wfrag; S.luts = L.luts;
     S.cand = L.cand; S.thr = L.thr; S.topk = L.topk; S.cnt = L.cnt; S.lo = nullptr;
-    S.w_rows = 16; S.dim_pad = kNoAllocMaxDim; S.cap = int(kNoAllocCap); S.allow_tc = false;
+    S.w_rows = 16; S.dim_pad = kNoAllocMaxDim; S.lut_pitch = size_t((ng + 3) / 4 * 4) * 32; S.cap = int(kNoAllocCap); S.allow_tc = false;
     {
         ScanParams probe = base_scan_params(h, mode);
         plan.use_small = h->small_scan >= 0 && (h->small_scan & 4) == 0 && mode == TV_SCORE_PERMUTE_DOT &&
@@ -2155,7 +2156,7 @@ int tv_rotate(tv_index *h, const float *rows, size_t n, size_t dim, float *rotat
     TV_CUDA(c.d_qrot.reserve(n * dim));
     TV_CUDA(c.d_qscale.reserve(nq_pad));
     TV_CUDA(c.d_qbias.reserve(nq_pad));
-    TV_CUDA(c.d_luts.reserve(n * size_t(h->ngroups) * 32));
+    TV_CUDA(c.d_luts.reserve(n * size_t((h->ngroups + 3) / 4 * 4) * 32));
     TV_CUDA(cudaMemcpyAsync(h->d_stage.ptr, rows, n * dim * 4, cudaMemcpyHostToDevice, st));
     QueryPrepParams qp{};
     qp.queries = h->d_stage.ptr; qp.nq = int(n); qp.dim = int(dim); qp.bits = h->bits; qp.ngroups = h->ngroups;
@@ -2163,6 +2164,7 @@ int tv_rotate(tv_index *h, const float *rows, size_t n, size_t dim, float *rotat
     qp.perm0 = h->d_perm.ptr; qp.perm1 = h->d_perm.ptr + dim; qp.inv_sqrt_block = h->rot.inv_sqrt_block;
     qp.centroids = h->d_codebook.ptr + 16;
     qp.q_rot = c.d_qrot.ptr; qp.qscale = c.d_qscale.ptr; qp.qbias = c.d_qbias.ptr; qp.luts = c.d_luts.ptr;
+    qp.lut_pitch = (h->ngroups + 3) / 4 * 4 * 32;
     qp.first_invalid = &h->d_flags->first_invalid;
     TV_CUDA(launch_query_prep(qp, st));
     h->launches++;

@@ -69,6 +69,7 @@ scan_tc_kernel(ScanParams p, const __grid_constant__ CUtensorMap wmap, int n_sla
 
     const int tid = threadIdx.x, warp = tid >> 5, lane = tid & 31;
     const int ng = p.ngroups;
+    const bool fused = p.mode == kModeLutFlush;          // u8-LUT flush family: one fma per (at most 256) byte-groups
     uint32_t pos_end = p.pos_end;
     if (p.live_blocks != nullptr) pos_end = min(pos_end, *p.n_live);
     const uint32_t pos_begin = min(p.pos_begin, pos_end);
@@ -209,7 +210,7 @@ scan_tc_kernel(ScanParams p, const __grid_constant__ CUtensorMap wmap, int n_sla
                                 const int c = cbase + c0 + j;
                                 const int ql = qg * kTileQueries + c;
                                 if (ql < p.q_base + p.nq) {
-                                    const float score = final_score<ONEHOT>(acc[j], sh->qscale[pb][c], sh->qbias[pb][c], vs[m]);
+                                    const float score = final_score<ONEHOT>(fused, acc[j], sh->qscale[pb][c], sh->qbias[pb][c], vs[m]);
                                     p.cb.cand[size_t(ql) * p.cb.cap + at] = live[m] ? make_key(score, uint32_t(slot[m])) : kEmptyKey;
                                 }
                             }
@@ -221,10 +222,10 @@ scan_tc_kernel(ScanParams p, const __grid_constant__ CUtensorMap wmap, int n_sla
 #pragma unroll
                     for (int j4 = 0; j4 < 8; ++j4) {
                         const float4 s4 = ps[(c0 >> 2) + j4], b4 = pbias[(c0 >> 2) + j4], t4 = pt[(c0 >> 2) + j4];
-                        any |= final_score<ONEHOT>(acc[4 * j4 + 0], s4.x, b4.x, vs[m]) >= t4.x;
-                        any |= final_score<ONEHOT>(acc[4 * j4 + 1], s4.y, b4.y, vs[m]) >= t4.y;
-                        any |= final_score<ONEHOT>(acc[4 * j4 + 2], s4.z, b4.z, vs[m]) >= t4.z;
-                        any |= final_score<ONEHOT>(acc[4 * j4 + 3], s4.w, b4.w, vs[m]) >= t4.w;
+                        any |= final_score<ONEHOT>(fused, acc[4 * j4 + 0], s4.x, b4.x, vs[m]) >= t4.x;
+                        any |= final_score<ONEHOT>(fused, acc[4 * j4 + 1], s4.y, b4.y, vs[m]) >= t4.y;
+                        any |= final_score<ONEHOT>(fused, acc[4 * j4 + 2], s4.z, b4.z, vs[m]) >= t4.z;
+                        any |= final_score<ONEHOT>(fused, acc[4 * j4 + 3], s4.w, b4.w, vs[m]) >= t4.w;
                     }
                     any = any && live[m];
                     // rare, warp-uniform: some lane has a score at or above its query's k-th score.  Re-read the
@@ -239,7 +240,7 @@ scan_tc_kernel(ScanParams p, const __grid_constant__ CUtensorMap wmap, int n_sla
 #pragma unroll
                                 for (int e = 0; e < 8; ++e) {
                                     const int c = cbase + c0 + c1 + e;
-                                    const float score = final_score<ONEHOT>(a8[e], sh->qscale[pb][c], sh->qbias[pb][c], vs[m]);
+                                    const float score = final_score<ONEHOT>(fused, a8[e], sh->qscale[pb][c], sh->qbias[pb][c], vs[m]);
                                     if (score >= sh->qthr[pb][c]) {
                                         const int ql = qg * kTileQueries + c;
                                         const uint64_t key = make_key(score, uint32_t(slot[m]));
@@ -481,7 +482,11 @@ static size_t scan_tc_smem_bytes(int nqt) { return size_t(4) * (kATileBytes + nq
 bool scan_tc_supported(int bits, int mode, int ngroups) {
     if (encode_fn() == nullptr) return false;
     if (mode == kModePermuteDot) return bits == 4;
-    return mode == kModeLutMulAdd && ngroups % 4 == 0;       // the per-256-group fma of the flush family needs partial sums
+    if (mode == kModeLutMulAdd) return ngroups % 4 == 0;
+    // flush family: acc = bias, then one fma(scale, (f32)isum, acc) per 256 byte-groups (search.rs:516, 577): with at
+    // most 256 groups that is a single fma on the whole integer sum, which the accumulator holds; longer rows need the
+    // partial sums and stay on the CUDA-core scan.  K is padded to whole slabs of 4 groups with zero tables.
+    return mode == kModeLutFlush && ngroups <= 256;
 }
 
 // Permute-dot: weights = [rows][pitch] int8, pitch a multiple of 128, rows a multiple of 256, coordinates

@@ -44,17 +44,20 @@ __device__ __forceinline__ uint32_t map_to_cta(uint32_t smem_addr, uint32_t rank
 __device__ __forceinline__ void cluster_sync_all() {
     asm volatile("barrier.cluster.arrive.release.aligned;\n\tbarrier.cluster.wait.acquire.aligned;" ::: "memory");
 }
+// Remote arrivals carry the default (CTA-scope release) semantics: what they publish was written to the arriving CTA's own
+// shared memory and made visible to the asynchronous proxy by fence.proxy.async before the arrival; a cluster-scope
+// release on every arrival cost more than the MMAs it guarded.
 __device__ __forceinline__ void mbar_arrive_cluster(uint32_t cluster_addr) {
-    asm volatile("mbarrier.arrive.release.cluster.shared::cluster.b64 _, [%0];" ::"r"(cluster_addr) : "memory");
+    asm volatile("mbarrier.arrive.shared::cluster.b64 _, [%0];" ::"r"(cluster_addr) : "memory");
 }
 __device__ __forceinline__ void mbar_arrive_expect_tx_cluster(uint32_t cluster_addr, uint32_t bytes) {
-    asm volatile("mbarrier.arrive.expect_tx.release.cluster.shared::cluster.b64 _, [%0], %1;" ::"r"(cluster_addr), "r"(bytes) : "memory");
+    asm volatile("mbarrier.arrive.expect_tx.shared::cluster.b64 _, [%0], %1;" ::"r"(cluster_addr), "r"(bytes) : "memory");
 }
 __device__ __forceinline__ bool mbar_try_wait_cluster(uint64_t *bar, uint32_t parity) {
     uint32_t ok;
     asm volatile(
         "{\n\t.reg .pred p;\n\t"
-        "mbarrier.try_wait.parity.acquire.cluster.shared::cta.b64 p, [%1], %2;\n\t"
+        "mbarrier.try_wait.parity.shared::cta.b64 p, [%1], %2;\n\t"
         "selp.u32 %0, 1, 0, p;\n\t}"
         : "=r"(ok) : "r"(smem_u32(bar)), "r"(parity) : "memory");
     return ok != 0;
@@ -240,7 +243,7 @@ scan_tc_pair_kernel(ScanParams p, const __grid_constant__ CUtensorMap wmap, int 
                             const int c = cbase + c0 + j;
                             const int ql = qg * kTileQueries + c;
                             if (ql < p.q_base + p.nq) {
-                                const float score = final_score<false>(acc[j], sh->qscale[pb][c], sh->qbias[pb][c], vs);
+                                const float score = final_score<false>(false, acc[j], sh->qscale[pb][c], sh->qbias[pb][c], vs);
                                 p.cb.cand[size_t(ql) * p.cb.cap + at] = live ? make_key(score, uint32_t(slot)) : kEmptyKey;
                             }
                         }
@@ -251,10 +254,10 @@ scan_tc_pair_kernel(ScanParams p, const __grid_constant__ CUtensorMap wmap, int 
 #pragma unroll
                 for (int j4 = 0; j4 < 8; ++j4) {
                     const float4 s4 = ps[(c0 >> 2) + j4], b4 = pbias[(c0 >> 2) + j4], t4 = pt[(c0 >> 2) + j4];
-                    any |= final_score<false>(acc[4 * j4 + 0], s4.x, b4.x, vs) >= t4.x;
-                    any |= final_score<false>(acc[4 * j4 + 1], s4.y, b4.y, vs) >= t4.y;
-                    any |= final_score<false>(acc[4 * j4 + 2], s4.z, b4.z, vs) >= t4.z;
-                    any |= final_score<false>(acc[4 * j4 + 3], s4.w, b4.w, vs) >= t4.w;
+                    any |= final_score<false>(false, acc[4 * j4 + 0], s4.x, b4.x, vs) >= t4.x;
+                    any |= final_score<false>(false, acc[4 * j4 + 1], s4.y, b4.y, vs) >= t4.y;
+                    any |= final_score<false>(false, acc[4 * j4 + 2], s4.z, b4.z, vs) >= t4.z;
+                    any |= final_score<false>(false, acc[4 * j4 + 3], s4.w, b4.w, vs) >= t4.w;
                 }
                 any = any && live;
                 if (__any_sync(kFullMask, any)) {              // rare, warp-uniform: re-read in pieces of 8 and append
@@ -267,7 +270,7 @@ scan_tc_pair_kernel(ScanParams p, const __grid_constant__ CUtensorMap wmap, int 
 #pragma unroll
                             for (int e = 0; e < 8; ++e) {
                                 const int c = cbase + c0 + c1 + e;
-                                const float score = final_score<false>(a8[e], sh->qscale[pb][c], sh->qbias[pb][c], vs);
+                                const float score = final_score<false>(false, a8[e], sh->qscale[pb][c], sh->qbias[pb][c], vs);
                                 if (score >= sh->qthr[pb][c]) {
                                     const int ql = qg * kTileQueries + c;
                                     const uint64_t key = make_key(score, uint32_t(slot));

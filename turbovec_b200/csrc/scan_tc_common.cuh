@@ -113,12 +113,15 @@ __device__ __forceinline__ void tmem_ld8(uint32_t taddr, uint32_t (&r)[8]) {
                  : "r"(taddr));
 }
 
-// Float epilogue of the two score families; the integer sum is exact in both.
+// Float epilogue of the score families; the integer sum is exact in all of them.  Permute-dot: fma((f32)S, scale, bias)
+// (search.rs:1523, 1793).  u8-LUT, mul-add family: (f32)isum * scale + bias (search.rs:1176).  u8-LUT, flush family
+// with at most 256 byte-groups (`fused`): one fma(scale, (f32)isum, bias) (search.rs:516, 577, 1596) - the same
+// single rounding as the permute-dot form.  Then x vec_scale.
 template <bool ONEHOT>
-__device__ __forceinline__ float final_score(uint32_t isum, float qs, float qb, float vs) {
+__device__ __forceinline__ float final_score(bool fused, uint32_t isum, float qs, float qb, float vs) {
     const float f = float(int(isum));
-    if constexpr (ONEHOT) return __fmul_rn(__fadd_rn(__fmul_rn(f, qs), qb), vs);   // search.rs:1176, then x vec_scale
-    else return __fmul_rn(fmaf(f, qs, qb), vs);                                    // search.rs:1523, 1793
+    if constexpr (ONEHOT) return __fmul_rn(fused ? fmaf(qs, f, qb) : __fadd_rn(__fmul_rn(f, qs), qb), vs);
+    else return __fmul_rn(fmaf(f, qs, qb), vs);
 }
 
 }  // namespace

@@ -55,6 +55,7 @@ scan_tc_wide_kernel(ScanParams p, const __grid_constant__ CUtensorMap wmap, int 
 
     const int tid = threadIdx.x, warp = tid >> 5, lane = tid & 31;
     const int ng = p.ngroups;
+    const bool fused = p.mode == kModeLutFlush;          // u8-LUT flush family: one fma per (at most 256) byte-groups
     uint32_t pos_end = p.pos_end;
     if (p.live_blocks != nullptr) pos_end = min(pos_end, *p.n_live);
     const uint32_t pos_begin = min(p.pos_begin, pos_end);
@@ -195,7 +196,7 @@ scan_tc_wide_kernel(ScanParams p, const __grid_constant__ CUtensorMap wmap, int 
                                 const int c = c0 + j;
                                 const int ql = qg * kTileQueries + c;
                                 if (ql < p.q_base + p.nq) {
-                                    const float score = final_score<ONEHOT>(acc[j], qscale[c], qbias[c], vs);
+                                    const float score = final_score<ONEHOT>(fused, acc[j], qscale[c], qbias[c], vs);
                                     p.cb.cand[size_t(ql) * p.cb.cap + at] = live ? make_key(score, uint32_t(slot)) : kEmptyKey;
                                 }
                             }
@@ -206,10 +207,10 @@ scan_tc_wide_kernel(ScanParams p, const __grid_constant__ CUtensorMap wmap, int 
 #pragma unroll
                     for (int j4 = 0; j4 < 8; ++j4) {
                         const float4 s4 = ps[(c0 >> 2) + j4], b4 = pbias[(c0 >> 2) + j4], t4 = pt[(c0 >> 2) + j4];
-                        any |= final_score<ONEHOT>(acc[4 * j4 + 0], s4.x, b4.x, vs) >= t4.x;
-                        any |= final_score<ONEHOT>(acc[4 * j4 + 1], s4.y, b4.y, vs) >= t4.y;
-                        any |= final_score<ONEHOT>(acc[4 * j4 + 2], s4.z, b4.z, vs) >= t4.z;
-                        any |= final_score<ONEHOT>(acc[4 * j4 + 3], s4.w, b4.w, vs) >= t4.w;
+                        any |= final_score<ONEHOT>(fused, acc[4 * j4 + 0], s4.x, b4.x, vs) >= t4.x;
+                        any |= final_score<ONEHOT>(fused, acc[4 * j4 + 1], s4.y, b4.y, vs) >= t4.y;
+                        any |= final_score<ONEHOT>(fused, acc[4 * j4 + 2], s4.z, b4.z, vs) >= t4.z;
+                        any |= final_score<ONEHOT>(fused, acc[4 * j4 + 3], s4.w, b4.w, vs) >= t4.w;
                     }
                     any = any && live;
                     if (__any_sync(kFullMask, any)) {          // rare, warp-uniform: re-read in pieces of 8 and append
@@ -222,7 +223,7 @@ scan_tc_wide_kernel(ScanParams p, const __grid_constant__ CUtensorMap wmap, int 
 #pragma unroll
                                 for (int e = 0; e < 8; ++e) {
                                     const int c = c0 + c1 + e;
-                                    const float score = final_score<ONEHOT>(a8[e], qscale[c], qbias[c], vs);
+                                    const float score = final_score<ONEHOT>(fused, a8[e], qscale[c], qbias[c], vs);
                                     if (score >= qthr[c]) {
                                         const int ql = qg * kTileQueries + c;
                                         const uint64_t key = make_key(score, uint32_t(slot));

@@ -148,7 +148,7 @@ __global__ void __launch_bounds__(128) query_prep_kernel(QueryPrepParams p) {
             p.qscale[q] = scale;
             p.qbias[q] = __fadd_rn(bias, bias_corr);                // search.rs:3260
         }
-        uint8_t *lut = p.luts + size_t(q) * ng * 32;
+        uint8_t *lut = p.luts + size_t(q) * p.lut_pitch;
         for (int e = tid; e < ng * 32; e += blockDim.x) {
             const int h = e >> 4;
             const unsigned nib = e & 15;
@@ -390,10 +390,10 @@ __global__ void __launch_bounds__(256) scan_lut_kernel(ScanParams p) {
     uint8_t *lut = smem_raw;                                  // [NQ][ng*32]
     const int tid = threadIdx.x, warp = tid >> 5, lane = tid & 31;
     const int nq_here = min(NQ, p.nq);
-    {
-        const uint4 *src = reinterpret_cast<const uint4 *>(p.luts + size_t(p.q_base) * ng * 32);
-        uint4 *dst = reinterpret_cast<uint4 *>(lut);
-        for (int i = tid; i < nq_here * ng * 2; i += blockDim.x) dst[i] = src[i];
+    for (int q = 0; q < nq_here; ++q) {
+        const uint4 *src = reinterpret_cast<const uint4 *>(p.luts + size_t(p.q_base + q) * p.lut_pitch);
+        uint4 *dst = reinterpret_cast<uint4 *>(lut + size_t(q) * ng * 32);
+        for (int i = tid; i < ng * 2; i += blockDim.x) dst[i] = src[i];
     }
     __syncthreads();
     uint32_t pos_end = p.pos_end;

@@ -23,7 +23,8 @@ struct QueryPrepParams {
     // outputs
     float *q_rot;                  // [nq][dim] rotated (and TQ+-inverted) queries
     float *qscale, *qbias;         // [nq]
-    uint8_t *luts;                 // [nq][ngroups*32]            (LUT modes)
+    uint8_t *luts;                 // [nq][lut_pitch], ngroups*32 bytes used per query (LUT modes)
+    int lut_pitch;                 // bytes between the tables of consecutive queries: 32 * (ngroups rounded up to 4)
     int8_t *weights;               // [rows][dim_pad] row-major, byte d^1 = weight of coordinate d (permute-dot;
                                    // tensor-core operand: the swap matches the nibble order of a code byte)
     int dim_pad;                   // row pitch of `weights`
@@ -96,12 +97,14 @@ struct ScanParams {
     int pd_split;                  // permute-dot scan on CUDA-core MMAs: 1 = split lookup where the levels allow it
     // LUT
     const uint8_t *luts;
+    int lut_pitch;                 // bytes between the tables of consecutive queries
 };
 // Permute-dot scan on mma.sync (int8 x int8 -> int32), up to 64 queries per launch.
 cudaError_t launch_scan_pd(const ScanParams &p, int sm_count, cudaStream_t s);
 // Permute-dot scan on tcgen05 tensor cores with TMEM accumulators (scan_tc.cu); all queries in one launch.
 // Permute-dot: weights [rows][pitch] int8, rows % 256 == 0, pitch % 128 == 0, adjacent coordinates swapped.
-// LUT (mul-add family, ngroups % 4 == 0): weights = the u8 tables [rows][32 * ngroups], rows % 256 == 0.
+// LUT families: weights = the u8 tables [rows][pitch = 32 * (ngroups rounded up to 4)], rows % 256 == 0, unused
+// tables and the padding groups zero.
 bool scan_tc_supported(int bits, int mode, int ngroups);
 cudaError_t launch_scan_tc(const ScanParams &p, const int8_t *weights, int rows, int pitch, int sm_count,
                            int tiles_per_item, cudaStream_t s);
