@@ -12,6 +12,7 @@
 //   * group j of an item accumulates in tensor-memory columns 256 j .. 256 j + 255; the four epilogue warps of half j
 //     drain it and hand it back on their own barrier, so the first MMAs of the next item's group 0 wait only for
 //     half 0 and overlap the drain of half 1.
+// The MMAs of an item's two groups are issued by two threads (warps 1 and 18), one per group.
 // An odd last group runs as an item of one group.  Every wait is bounded; a role whose wait runs out records the
 // error and leaves its loop.
 #include <cuda.h>
@@ -28,6 +29,8 @@ constexpr int kWideASlots = 3;
 constexpr int kWideBSlots = 5;
 constexpr int kWideBBytes = kMaxTileQueries * kSlabK;        // 32 KB: one query group, one K slab
 constexpr int kWideBlocksPerItem = 4;
+constexpr int kWideIssuerWarp = 2 + kEpilogueWarps + kExpandWarps;   // warp 18: the MMA issuer of an item's second group
+constexpr int kWideThreads = kThreadsTc + 32;
 
 struct WideShared {
     uint64_t a_full[kWideASlots];     // slab expanded: 8 expansion warps
@@ -45,7 +48,7 @@ struct WideShared {
 static_assert(offsetof(WideShared, qscale) % 16 == 0, "parameter arrays must be 16-byte aligned");
 
 template <bool ONEHOT>
-__global__ void __launch_bounds__(kThreadsTc, 1)
+__global__ void __launch_bounds__(kWideThreads, 1)
 scan_tc_wide_kernel(ScanParams p, const __grid_constant__ CUtensorMap wmap, int n_slabs, int n_qgroups) {
     constexpr int kTileQueries = kMaxTileQueries;
     extern __shared__ __align__(1024) unsigned char smem_raw[];
@@ -64,7 +67,7 @@ scan_tc_wide_kernel(ScanParams p, const __grid_constant__ CUtensorMap wmap, int 
     const uint32_t n_items = n_vtiles * uint32_t(n_gpairs);
 
     if (tid == 0) {
-        for (int s = 0; s < kWideASlots; ++s) { mbar_init(&sh->a_full[s], kExpandWarps); mbar_init(&sh->a_empty[s], 1); }
+        for (int s = 0; s < kWideASlots; ++s) { mbar_init(&sh->a_full[s], kExpandWarps); mbar_init(&sh->a_empty[s], 2); }
         for (int s = 0; s < kWideBSlots; ++s) { mbar_init(&sh->b_full[s], 1); mbar_init(&sh->b_empty[s], 1); }
         for (int b = 0; b < 2; ++b) { mbar_init(&sh->d_full[b], 1); mbar_init(&sh->d_empty[b], kEpilogueWarps / 2); }
         asm volatile("fence.mbarrier_init.release.cluster;" ::: "memory");
@@ -104,38 +107,47 @@ scan_tc_wide_kernel(ScanParams p, const __grid_constant__ CUtensorMap wmap, int 
                 if (gp >= n_gpairs) gp -= n_gpairs;
             }
         }
-    } else if (warp == 1) {
-        // ------------------------------------------------ MMA issuer -----------------------------------------
+    } else if (warp == 1 || warp == kWideIssuerWarp) {
+        // ------------------------------------------------ MMA issuers: warp 1 for group 0, warp 18 for group 1 --------
+        // One thread per group: waiting on a barrier and issuing four MMAs each take a few hundred cycles of the
+        // issuing thread, about what the four MMAs take to run, so a single issuer leaves the tensor pipe idle while it
+        // waits.  The two groups write different tensor-memory columns, so their MMAs need no order between them.
         if (lane == 0) {
-            uint32_t it_a = 0, it_b = 0, uses[2] = {0, 0};
+            const int j = warp == 1 ? 0 : 1;                  // this issuer's group within every item
+            uint32_t it_a = 0, b_base = 0, uses = 0;
             int gp = int(blockIdx.x % uint32_t(n_gpairs));
             bool ok = true;
             for (uint32_t item = blockIdx.x; item < n_items && ok; item += gridDim.x) {
                 const int gcount = groups_of(gp);
-                for (int s = 0; s < n_slabs && ok; ++s, ++it_a) {
-                    const int a_slot = it_a % kWideASlots;
-                    ok = mbar_wait(&sh->a_full[a_slot], (it_a / kWideASlots) & 1, p.cb.error);
-                    if (!ok) break;
-                    const uint32_t a_addr = smem_u32(a_ring + size_t(a_slot) * kATileBytes);
-                    for (int j = 0; j < gcount && ok; ++j, ++it_b) {
+                if (j < gcount) {
+                    for (int s = 0; s < n_slabs && ok; ++s) {
+                        const uint32_t ia = it_a + uint32_t(s);
+                        const int a_slot = ia % kWideASlots;
                         if (s == 0) {                         // the half must have been drained by the previous item's epilogue
-                            ok = mbar_wait(&sh->d_empty[j], (uses[j] & 1) ^ 1, p.cb.error);
+                            ok = mbar_wait(&sh->d_empty[j], (uses & 1) ^ 1, p.cb.error);
                             if (!ok) break;
                         }
-                        const int b_slot = it_b % kWideBSlots;
-                        ok = mbar_wait(&sh->b_full[b_slot], (it_b / kWideBSlots) & 1, p.cb.error);
+                        ok = mbar_wait(&sh->a_full[a_slot], (ia / kWideASlots) & 1, p.cb.error);
+                        if (!ok) break;
+                        const uint32_t ib = b_base + uint32_t(s * gcount + j);
+                        const int b_slot = ib % kWideBSlots;
+                        ok = mbar_wait(&sh->b_full[b_slot], (ib / kWideBSlots) & 1, p.cb.error);
                         if (!ok) break;
                         asm volatile("tcgen05.fence::after_thread_sync;" ::: "memory");
+                        const uint32_t a_addr = smem_u32(a_ring + size_t(a_slot) * kATileBytes);
                         const uint32_t b_addr = smem_u32(b_ring + size_t(b_slot) * kWideBBytes);
                         const uint32_t d_tmem = tmem_base + uint32_t(j) * kTileQueries;
 #pragma unroll
                         for (int k = 0; k < kSlabK / 32; ++k)
                             umma_i8<kTileQueries>(d_tmem, umma_desc(a_addr + k * 32), umma_desc(b_addr + k * 32), (s | k) != 0);
                         umma_commit(&sh->b_empty[b_slot]);
-                        if (s == n_slabs - 1) { umma_commit(&sh->d_full[j]); ++uses[j]; }
+                        umma_commit(&sh->a_empty[a_slot]);    // the slab is free once both groups have read it
+                        if (gcount == 1) umma_commit(&sh->a_empty[a_slot]);   // an item of one group: its issuer signs twice
+                        if (s == n_slabs - 1) { umma_commit(&sh->d_full[j]); ++uses; }
                     }
-                    if (ok) umma_commit(&sh->a_empty[a_slot]);  // every group of the item has read this A slab
                 }
+                it_a += uint32_t(n_slabs);
+                b_base += uint32_t(n_slabs * gcount);
                 gp += gp_step;
                 if (gp >= n_gpairs) gp -= n_gpairs;
             }
@@ -248,7 +260,7 @@ scan_tc_wide_kernel(ScanParams p, const __grid_constant__ CUtensorMap wmap, int 
             vt += vt_step; gp += gp_step;
             if (gp >= n_gpairs) { gp -= n_gpairs; ++vt; }
         }
-    } else {
+    } else if (warp < kWideIssuerWarp) {
         // ------------------------------------------------ expansion: codes -> int8 A slabs, once per item and slab ----
         constexpr int kAhead = 4;
         const int ew = warp - (2 + kEpilogueWarps);       // 0..7
@@ -391,11 +403,11 @@ cudaError_t launch_scan_tc_wide(const ScanParams &p, const int8_t *weights, int 
     if (onehot) {
         e = cudaFuncSetAttribute(scan_tc_wide_kernel<true>, cudaFuncAttributeMaxDynamicSharedMemorySize, int(smem));
         if (e != cudaSuccess) return e;
-        scan_tc_wide_kernel<true><<<grid, kThreadsTc, smem, s>>>(p, map, n_slabs, n_qgroups);
+        scan_tc_wide_kernel<true><<<grid, kWideThreads, smem, s>>>(p, map, n_slabs, n_qgroups);
     } else {
         e = cudaFuncSetAttribute(scan_tc_wide_kernel<false>, cudaFuncAttributeMaxDynamicSharedMemorySize, int(smem));
         if (e != cudaSuccess) return e;
-        scan_tc_wide_kernel<false><<<grid, kThreadsTc, smem, s>>>(p, map, n_slabs, n_qgroups);
+        scan_tc_wide_kernel<false><<<grid, kWideThreads, smem, s>>>(p, map, n_slabs, n_qgroups);
     }
     return cudaGetLastError();
 }
