@@ -4,6 +4,7 @@
 #pragma once
 #include <cuda.h>
 
+#include <climits>
 #include <cstddef>
 
 #include "search.cuh"
@@ -122,6 +123,29 @@ __device__ __forceinline__ float final_score(bool fused, uint32_t isum, float qs
     const float f = float(int(isum));
     if constexpr (ONEHOT) return __fmul_rn(fused ? fmaf(qs, f, qb) : __fadd_rn(__fmul_rn(f, qs), qb), vs);
     else return __fmul_rn(fmaf(f, qs, qb), vs);
+}
+
+
+// Integer bound that dismisses most accumulator columns without converting them to float.
+// For one query (scale qs > 0, bias qb, threshold score t > 0) and every vector of a work item (vector scales
+// 0 <= vs <= vs_max), a score fmul(fma((f32)isum, qs, qb), vs) can reach t only if
+//     isum >= ((t / vs_max) - qb) / qs
+// up to the roundings of the conversion, the fma and the multiply (each within 2^-23 relative).  The returned integer
+// lies below that bound by a margin a thousand times those roundings plus two units, so `isum >= bound` is necessary
+// for a candidate; the columns that satisfy it are scored exactly afterwards.  The integer compare costs one
+// instruction per column where the exact score costs four, one of them (int -> float) on a quarter-rate unit; on
+// L2-normalised data the vector scales of an item differ by a few percent, so hardly any column survives it.
+// t <= 0 (no k-th result yet, or a non-positive one): everything is kept.  vs_max = 0 with t > 0: nothing can pass.
+__device__ __forceinline__ int dismissal_bound(float qs, float qb, float t, float vs_max) {
+    if (!(t > 0.0f)) return INT_MIN;
+    if (!(qs > 0.0f)) return qb * vs_max >= t ? INT_MIN : INT_MAX;     // a column without a query has t = +inf
+    const float g = t / vs_max;                                        // +inf when vs_max is 0
+    const float bound = (g - qb) / qs;
+    const float margin = 1.0e-5f * (fabsf(g) + fabsf(qb)) / qs + 2.0f;
+    const float lo = bound - margin;
+    if (!(lo < 2.0e9f)) return INT_MAX;
+    if (lo < -2.0e9f) return INT_MIN;
+    return __float2int_rd(lo);
 }
 
 }  // namespace

@@ -44,6 +44,8 @@ struct WideShared {
     float qscale[2 * kMaxTileQueries];   // per-query parameters of the item's two groups
     float qbias[2 * kMaxTileQueries];
     float qthr[2 * kMaxTileQueries];
+    int ibound[2 * kMaxTileQueries];     // per query: integer sum below which no vector of the item can be a candidate
+    float vs_part[2][4];                 // largest vector scale per lane quarter of the item
 };
 static_assert(offsetof(WideShared, qscale) % 16 == 0, "parameter arrays must be 16-byte aligned");
 
@@ -165,6 +167,24 @@ scan_tc_wide_kernel(ScanParams p, const __grid_constant__ CUtensorMap wmap, int 
         for (uint32_t item = blockIdx.x; item < n_items && ok; item += gridDim.x) {
             if (half < groups_of(gp)) {
                 const int qg = 2 * gp + half;
+                // this lane's vector, and the largest vector scale of the item (dismissal_bound)
+                const int row = quarter * 32 + lane;                     // vector within the item
+                const uint32_t pos = pos_begin + vt * kWideBlocksPerItem + uint32_t(row >> 5);
+                const bool have_row = pos < pos_end;
+                uint32_t blk = 0;
+                if (have_row) blk = p.live_blocks ? p.live_blocks[pos] : pos;
+                const int64_t slot = int64_t(blk) * 32 + (row & 31);
+                bool live = have_row && slot < p.n;
+                if (live && p.mask) live = (p.mask[slot >> 6] >> (slot & 63)) & 1ull;
+                const float vs = live ? p.vec_scales[slot] : 0.0f;
+                {
+                    float m = vs;
+#pragma unroll
+                    for (int o = 16; o > 0; o >>= 1) m = fmaxf(m, __shfl_xor_sync(kFullMask, m, o));
+                    if (lane == 0) sh->vs_part[half][quarter] = m;
+                }
+                asm volatile("bar.sync %0, %1;" ::"r"(1 + half), "r"(128) : "memory");
+                const float vs_max = fmaxf(fmaxf(sh->vs_part[half][0], sh->vs_part[half][1]), fmaxf(sh->vs_part[half][2], sh->vs_part[half][3]));
                 // per-query parameters of this group: two queries per thread of the half
 #pragma unroll
                 for (int e = 0; e < 2; ++e) {
@@ -176,17 +196,9 @@ scan_tc_wide_kernel(ScanParams p, const __grid_constant__ CUtensorMap wmap, int 
                         th = key == kEmptyKey ? -INFINITY : desc_bits_to_score(uint32_t(key >> 32));
                     }
                     qscale[c] = qs; qbias[c] = qb; qthr[c] = th;
+                    sh->ibound[half * kTileQueries + c] = dismissal_bound(qs, qb, th, vs_max);
                 }
                 asm volatile("bar.sync %0, %1;" ::"r"(1 + half), "r"(128) : "memory");
-                const int row = quarter * 32 + lane;                     // vector within the item
-                const uint32_t pos = pos_begin + vt * kWideBlocksPerItem + uint32_t(row >> 5);
-                const bool have_row = pos < pos_end;
-                uint32_t blk = 0;
-                if (have_row) blk = p.live_blocks ? p.live_blocks[pos] : pos;
-                const int64_t slot = int64_t(blk) * 32 + (row & 31);
-                bool live = have_row && slot < p.n;
-                if (live && p.mask) live = (p.mask[slot >> 6] >> (slot & 63)) & 1ull;
-                const float vs = live ? p.vec_scales[slot] : 0.0f;
 
                 // warp-uniform outcome; a warp whose wait ran out still meets the others at the barrier below
                 ok = __all_sync(kFullMask, mbar_wait(&sh->d_full[half], used & 1, p.cb.error));
@@ -214,6 +226,20 @@ scan_tc_wide_kernel(ScanParams p, const __grid_constant__ CUtensorMap wmap, int 
                             }
                         }
                         continue;
+                    }
+                    // one integer compare per column dismisses the piece unless some column could be a candidate
+                    {
+                        const int4 *pi = reinterpret_cast<const int4 *>(sh->ibound + half * kTileQueries + c0);
+                        bool may = false;
+#pragma unroll
+                        for (int j4 = 0; j4 < 8; ++j4) {
+                            const int4 b = pi[j4];
+                            may |= int(acc[4 * j4 + 0]) >= b.x;
+                            may |= int(acc[4 * j4 + 1]) >= b.y;
+                            may |= int(acc[4 * j4 + 2]) >= b.z;
+                            may |= int(acc[4 * j4 + 3]) >= b.w;
+                        }
+                        if (!__any_sync(kFullMask, may && live)) continue;
                     }
                     bool any = false;
 #pragma unroll
