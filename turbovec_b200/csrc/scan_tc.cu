@@ -36,6 +36,8 @@ struct TcShared {
     float qscale[2][kMaxTileQueries];
     float qbias[2][kMaxTileQueries];
     float qthr[2][kMaxTileQueries];   // score of the current k-th key (-inf while fewer than k results exist)
+    int ibound[2][kMaxTileQueries];   // per query: integer sum below which no vector of the item can be a candidate
+    float vs_part[2][8];              // largest vector scale seen by each epilogue warp of the item
 };
 static_assert(offsetof(TcShared, qscale) % 16 == 0, "parameter arrays must be 16-byte aligned");
 
@@ -152,21 +154,10 @@ scan_tc_kernel(ScanParams p, const __grid_constant__ CUtensorMap wmap, int n_sla
         bool ok = true;
         for (uint32_t item = blockIdx.x; item < n_items && ok; item += gridDim.x, ++local_item) {
             const int buf = local_item % kBufs, pb = local_item & 1;
-            // per-query parameters of this item: one query per epilogue thread
-            {
-                const int ql = qg * kTileQueries + et;
-                float qs = 0.f, qb = 0.f, th = INFINITY;
-                if (et < kTileQueries && ql < p.q_base + p.nq) {
-                    qs = p.qscale[ql]; qb = p.qbias[ql];
-                    const uint64_t key = p.cb.thr[ql];
-                    th = key == kEmptyKey ? -INFINITY : desc_bits_to_score(uint32_t(key >> 32));
-                }
-                sh->qscale[pb][et] = qs; sh->qbias[pb][et] = qb; sh->qthr[pb][et] = th;
-            }
-            asm volatile("bar.sync 1, %0;" ::"r"(kEpilogueWarps * 32) : "memory");
             int64_t slot[MT];
             float vs[MT];
             bool live[MT], have_row[MT];
+            float vs_warp = 0.0f;
 #pragma unroll
             for (int m = 0; m < MT; ++m) {
                 const int row = m * kMmaM + quarter * 32 + lane;        // vector within the item
@@ -179,7 +170,29 @@ scan_tc_kernel(ScanParams p, const __grid_constant__ CUtensorMap wmap, int n_sla
                 live[m] = have && slot[m] < p.n;
                 if (live[m] && p.mask) live[m] = (p.mask[slot[m] >> 6] >> (slot[m] & 63)) & 1ull;
                 vs[m] = live[m] ? p.vec_scales[slot[m]] : 0.0f;
+                vs_warp = fmaxf(vs_warp, vs[m]);
             }
+            // the largest vector scale of the item, for the integer dismissal bound of every query
+#pragma unroll
+            for (int o = 16; o > 0; o >>= 1) vs_warp = fmaxf(vs_warp, __shfl_xor_sync(kFullMask, vs_warp, o));
+            if (lane == 0) sh->vs_part[pb][warp - 2] = vs_warp;
+            asm volatile("bar.sync 1, %0;" ::"r"(kEpilogueWarps * 32) : "memory");
+            // per-query parameters of this item: one query per epilogue thread
+            {
+                float vs_max = 0.0f;
+#pragma unroll
+                for (int i = 0; i < kEpilogueWarps; ++i) vs_max = fmaxf(vs_max, sh->vs_part[pb][i]);
+                const int ql = qg * kTileQueries + et;
+                float qs = 0.f, qb = 0.f, th = INFINITY;
+                if (et < kTileQueries && ql < p.q_base + p.nq) {
+                    qs = p.qscale[ql]; qb = p.qbias[ql];
+                    const uint64_t key = p.cb.thr[ql];
+                    th = key == kEmptyKey ? -INFINITY : desc_bits_to_score(uint32_t(key >> 32));
+                }
+                sh->qscale[pb][et] = qs; sh->qbias[pb][et] = qb; sh->qthr[pb][et] = th;
+                sh->ibound[pb][et] = dismissal_bound(qs, qb, th, vs_max);
+            }
+            asm volatile("bar.sync 1, %0;" ::"r"(kEpilogueWarps * 32) : "memory");
 
             ok = mbar_wait(&sh->d_full[buf], (local_item / kBufs) & 1, p.cb.error);
             if (!ok) break;
@@ -217,7 +230,21 @@ scan_tc_kernel(ScanParams p, const __grid_constant__ CUtensorMap wmap, int n_sla
                         }
                         continue;
                     }
-                    // hot loop: four instructions per score, the comparison folded into one predicate
+                    // one integer compare per column dismisses the piece unless some column could be a candidate
+                    {
+                        const int4 *pi = reinterpret_cast<const int4 *>(&sh->ibound[pb][cbase + c0]);
+                        bool may = false;
+#pragma unroll
+                        for (int j4 = 0; j4 < 8; ++j4) {
+                            const int4 b = pi[j4];
+                            may |= int(acc[4 * j4 + 0]) >= b.x;
+                            may |= int(acc[4 * j4 + 1]) >= b.y;
+                            may |= int(acc[4 * j4 + 2]) >= b.z;
+                            may |= int(acc[4 * j4 + 3]) >= b.w;
+                        }
+                        if (!__any_sync(kFullMask, may && live[m])) continue;
+                    }
+                    // survivors: four instructions per score, the comparison folded into one predicate
                     bool any = false;
 #pragma unroll
                     for (int j4 = 0; j4 < 8; ++j4) {
