@@ -208,6 +208,56 @@ def test_prepared_allowlist_on_idmap(T):
         idx.prepare_allowlist(np.array([5], np.uint64))
 
 
+def test_long_allowlists_resolved_by_the_device_id_table(T):
+    """Allowlists of 32768 ids and more are turned into mask bits by a hash table on the device; the result must be
+    the one the same set gives as a packed slot mask (no id table involved), through adds, removals and rebuilds."""
+    n, dim = 120_000, 64
+    rng = np.random.default_rng(101)
+    x = anisotropic(n, dim, seed=101)
+    ids = rng.permutation(n).astype(np.uint64) * np.uint64(0x9E3779B1) + np.uint64(7)
+    idx = T.IdMapIndex(dim, 4)
+    idx.add_with_ids(x[:100_000], ids[:100_000])
+    q = anisotropic(6, dim, seed=101, offset=5)
+
+    def check(k=20):
+        live = idx.ids()                                                 # slot order
+        pick = rng.random(live.size) < 0.4
+        allow = np.concatenate([live[pick], live[pick][:500]])         # duplicates are fine
+        assert allow.size >= 32768
+        rng.shuffle(allow)
+        got = idx.search(q, k, allowlist=np.ascontiguousarray(allow))
+        bits = np.zeros(((live.size + 63) // 64) * 64, np.uint8)
+        bits[: live.size] = pick
+        idx.prepare_mask_words(np.packbits(bits, bitorder="little").view(np.uint64))
+        want = idx.search_prepared(q, k)
+        assert np.array_equal(got[1], want[1]) and np.array_equal(got[0], want[0])
+        return allow
+
+    allow = check()                                                      # first use: the table is built
+    bad = np.ascontiguousarray(np.concatenate([allow[:40_000], np.array([3], np.uint64), allow[:10]]))
+    with pytest.raises(KeyError, match="allowlist id 3 "):
+        idx.search(q, 5, allowlist=bad)
+    victims = [int(v) for v in rng.choice(idx.ids(), 300, replace=False)]
+    for victim in victims:                                               # swap-removes: updates of the table
+        assert idx.remove(victim)
+    idx.add_with_ids(x[100_000:100_500], ids[100_000:100_500])
+    check()
+    gone = np.ascontiguousarray(np.concatenate([idx.ids()[:40_000], np.array([victims[0]], np.uint64)]))
+    with pytest.raises(KeyError):
+        idx.search(q, 5, allowlist=gone)
+    idx.add_with_ids(x[100_500:], ids[100_500:])                        # a larger update in one go
+    check(k=64)
+    idx = T.IdMapIndex.from_bytes(idx.to_bytes())                        # a loaded index builds its table afresh
+    check(k=64)
+    half = np.ascontiguousarray(idx.ids()[::2])
+    want = idx.search(q, 10, allowlist=half)
+    idx.prepare_allowlist(half)                                          # prepared masks use the same table
+    got = idx.search_prepared(q, 10)
+    assert np.array_equal(got[1], want[1]) and np.array_equal(got[0], want[0])
+    with pytest.raises(KeyError):
+        idx.prepare_allowlist(np.ascontiguousarray(np.concatenate([half, np.array([5], np.uint64)])))
+
+
 # ------------------------------------------------------------------ overlapping searches on one handle
 def test_searches_from_several_threads_overlap_and_agree(T):
     n, dim = 60_000, 256

@@ -68,6 +68,7 @@ struct PinnedArray {
 struct DeviceFlags {        // one pinned + one device copy of the status words of a call
     unsigned long long first_invalid;
     unsigned long long n_allowed;
+    unsigned long long first_unknown;   // smallest allowlist index whose id the device table does not hold
     uint32_t n_live;
     uint32_t overflow;
     uint32_t error;
@@ -127,6 +128,7 @@ struct SearchCtx {
     DeviceArray<uint64_t> d_mask;
     DeviceArray<uint8_t> d_mask_bool;
     DeviceArray<uint32_t> d_slots_in, d_live;
+    DeviceArray<uint64_t> d_allow_ids;       // an allowlist resolved on the device
     DeviceArray<uint64_t> d_cand, d_thr, d_topk, d_floor, d_keys_all;
     DeviceArray<uint32_t> d_cnt;
     DeviceArray<float> d_scores;
@@ -158,6 +160,34 @@ struct SearchCtx {
     }
 };
 constexpr int kSearchCtxs = 2;
+
+// Device copy of the id -> slot table, kept for large allowlists (search.cu: idtab_*_kernel).  The host tables stay the
+// authority; this copy is brought up to date lazily, by the first allowlist search after a change.
+struct DeviceIdTable {
+    DeviceArray<uint64_t> keys;
+    DeviceArray<uint32_t> vals;
+    int log2cap = 0;
+    size_t used = 0;                  // occupied places, tombstones included
+    bool valid = false;               // holds slot_to_id as of the last change, minus `pending`
+    bool unusable = false;            // an id equal to one of the two marker keys was added: the host path serves everything
+    std::vector<std::pair<uint64_t, uint32_t>> pending;   // (id, slot) in order; slot 0xffffffff = removed
+    DeviceArray<uint64_t> d_ids;      // staging of a rebuild / an update
+    DeviceArray<uint32_t> d_slots;
+    cudaEvent_t ev = nullptr;         // recorded after every update; lookups on other streams wait for it
+    std::mutex mu;
+    ~DeviceIdTable() { if (ev) cudaEventDestroy(ev); }
+    void note(uint64_t id, uint32_t slot, size_t n_ids) {
+        if (id >= 0xfffffffffffffffeull) unusable = true;
+        if (!valid) return;
+        pending.emplace_back(id, slot);
+        if (pending.size() > n_ids / 4 + 65536) { valid = false; pending.clear(); }   // a rebuild is cheaper
+    }
+    void reset(const std::vector<uint64_t> &ids) {                  // the whole id table was replaced
+        valid = false; pending.clear(); unusable = false;
+        for (uint64_t id : ids) if (id >= 0xfffffffffffffffeull) unusable = true;
+    }
+};
+constexpr size_t kDeviceAllowlistMin = 32768;   // allowlists at least this long are resolved on the device
 
 // An allow-mask kept on the device between searches (tv_mask_prepare_*): words, live-block list and the two
 // counts the kernels read.  Any change of the index invalidates it.
@@ -249,6 +279,7 @@ struct tv_index {
     std::mutex ctx_mu;
     std::condition_variable ctx_cv;
     PreparedMask prepared;
+    DeviceIdTable idtab;
 
     // id map (ids never reach the device; id_map.rs:221-272)
     std::vector<uint64_t> slot_to_id;
@@ -660,8 +691,9 @@ struct MaskSpec {
     const uint64_t *words_host = nullptr; size_t n_words = 0;
     const uint64_t *words_device = nullptr;
     const uint32_t *slots_host = nullptr; size_t n_slots = 0;
+    const uint64_t *ids_host = nullptr; size_t n_ids = 0;   // allowlist ids, resolved by the device table
     bool prepared = false;                 // use the handle's prepared mask
-    bool any() const { return bool_host || words_host || words_device || slots_host || prepared; }
+    bool any() const { return bool_host || words_host || words_device || slots_host || ids_host || prepared; }
 };
 
 int candidate_capacity(size_t k) { return k <= 512 ? 4096 : 8192; }
@@ -707,10 +739,58 @@ struct MaskOnDevice {
     const unsigned long long *n_allowed = nullptr;
 };
 
+// Brings the device id table up to date on stream `st` (a rebuild from slot_to_id, or the changes since the last time)
+// and makes `st` wait for whatever update last touched it.
+int idtab_sync(tv_index *h, cudaStream_t st) {
+    DeviceIdTable &t = h->idtab;
+    std::lock_guard<std::mutex> g(t.mu);
+    if (!t.ev) TV_CUDA(cudaEventCreateWithFlags(&t.ev, cudaEventDisableTiming));
+    const size_t n = h->slot_to_id.size();
+    const size_t cap = t.log2cap ? size_t(1) << t.log2cap : 0;
+    if (!t.valid || (t.used + t.pending.size()) * 10 > cap * 7) {
+        int lg = 16;
+        while ((size_t(1) << lg) < 2 * n) ++lg;
+        TV_CUDA(injected_failure(h));
+        TV_CUDA(t.keys.reserve(size_t(1) << lg));
+        TV_CUDA(t.vals.reserve(size_t(1) << lg));
+        TV_CUDA(t.d_ids.reserve(n));
+        t.log2cap = lg;
+        TV_CUDA(cudaMemsetAsync(t.keys.ptr, 0xff, (size_t(1) << lg) * 8, st));
+        TV_CUDA(cudaMemcpyAsync(t.d_ids.ptr, h->slot_to_id.data(), n * 8, cudaMemcpyHostToDevice, st));
+        TV_CUDA(launch_idtab_insert(t.keys.ptr, t.vals.ptr, lg, t.d_ids.ptr, int64_t(n), 0, st));
+        h->launches++;
+        t.used = n; t.valid = true; t.pending.clear();
+    } else if (!t.pending.empty()) {
+        // the last operation on an id wins; the kernel wants every id once
+        std::unordered_map<uint64_t, uint32_t> last;
+        last.reserve(t.pending.size() * 2);
+        for (const auto &op : t.pending) last[op.first] = op.second;
+        std::vector<uint64_t> ids;
+        std::vector<uint32_t> slots;
+        ids.reserve(last.size()); slots.reserve(last.size());
+        for (const auto &kv : last) { ids.push_back(kv.first); slots.push_back(kv.second); }
+        TV_CUDA(t.d_ids.reserve(ids.size()));
+        TV_CUDA(t.d_slots.reserve(ids.size()));
+        TV_CUDA(cudaMemcpyAsync(t.d_ids.ptr, ids.data(), ids.size() * 8, cudaMemcpyHostToDevice, st));
+        TV_CUDA(cudaMemcpyAsync(t.d_slots.ptr, slots.data(), slots.size() * 4, cudaMemcpyHostToDevice, st));
+        TV_CUDA(launch_idtab_upsert(t.keys.ptr, t.vals.ptr, t.log2cap, t.d_ids.ptr, t.d_slots.ptr, int64_t(ids.size()), st));
+        TV_CUDA(cudaStreamSynchronize(st));          // the host vectors above are pageable: keep them until the copies are done
+        h->launches++;
+        t.used += ids.size();
+        t.pending.clear();
+    } else {
+        TV_CUDA(cudaStreamWaitEvent(st, t.ev, 0));
+        return TV_OK;
+    }
+    TV_CUDA(cudaEventRecord(t.ev, st));
+    return TV_OK;
+}
+
 // Uploads / packs the allow-mask of a call and compacts its live blocks.  `words_buf` / `live_buf` receive the data,
 // the two counters are zeroed by the caller.
 int build_mask(tv_index *h, cudaStream_t st, const MaskSpec &mask, DeviceArray<uint64_t> &words_buf,
                DeviceArray<uint8_t> &bool_buf, DeviceArray<uint32_t> &slots_buf, DeviceArray<uint32_t> &live_buf,
+               DeviceArray<uint64_t> &ids_buf, unsigned long long *d_first_unknown,
                unsigned long long *d_n_allowed, uint32_t *d_n_live, MaskOnDevice &out) {
     const size_t n = h->n, n_words = (n + 63) / 64, n_blocks = (n + kBlock - 1) / kBlock;
     TV_CUDA(injected_failure(h));
@@ -719,6 +799,16 @@ int build_mask(tv_index *h, cudaStream_t st, const MaskSpec &mask, DeviceArray<u
         TV_CUDA(cudaMemcpyAsync(words_buf.ptr, mask.words_device, n_words * 8, cudaMemcpyDeviceToDevice, st));
     } else if (mask.words_host) {
         TV_CUDA(cudaMemcpyAsync(words_buf.ptr, mask.words_host, n_words * 8, cudaMemcpyHostToDevice, st));
+    } else if (mask.ids_host) {
+        // the allowlist itself goes to the device; the id table there turns it into mask bits (id_map.rs:670-683)
+        TV_CUDA(ids_buf.reserve(mask.n_ids));
+        TV_CUDA(cudaMemsetAsync(words_buf.ptr, 0, n_words * 8, st));
+        TV_CUDA(cudaMemcpyAsync(ids_buf.ptr, mask.ids_host, mask.n_ids * 8, cudaMemcpyHostToDevice, st));
+        int rc = idtab_sync(h, st);
+        if (rc != TV_OK) return rc;
+        TV_CUDA(launch_idtab_lookup(h->idtab.keys.ptr, h->idtab.vals.ptr, h->idtab.log2cap, ids_buf.ptr, int64_t(mask.n_ids), words_buf.ptr,
+                                    d_first_unknown, st));
+        h->launches++;
     } else if (mask.bool_host) {
         TV_CUDA(bool_buf.reserve(n));
         TV_CUDA(cudaMemcpyAsync(bool_buf.ptr, mask.bool_host, n, cudaMemcpyHostToDevice, st));
@@ -993,6 +1083,7 @@ int search_core(tv_index *h, SearchCtx &c, const float *queries, bool queries_on
     }
     DeviceFlags init{};
     init.first_invalid = ~0ull;
+    init.first_unknown = ~0ull;
     *c.h_flags = init;
     TV_CUDA(cudaMemcpyAsync(c.d_flags, c.h_flags, sizeof(DeviceFlags), cudaMemcpyHostToDevice, st));
     TV_CUDA(cudaEventRecord(c.ev0, st));
@@ -1003,7 +1094,8 @@ int search_core(tv_index *h, SearchCtx &c, const float *queries, bool queries_on
         m.words = h->prepared.words.ptr; m.live = h->prepared.live.ptr;
         m.n_allowed = h->prepared.counts.ptr; m.n_live = reinterpret_cast<const uint32_t *>(h->prepared.counts.ptr + 1);
     } else if (mask.any()) {
-        rc = build_mask(h, st, mask, c.d_mask, c.d_mask_bool, c.d_slots_in, c.d_live, &c.d_flags->n_allowed, &c.d_flags->n_live, m);
+        rc = build_mask(h, st, mask, c.d_mask, c.d_mask_bool, c.d_slots_in, c.d_live, c.d_allow_ids, &c.d_flags->first_unknown,
+                        &c.d_flags->n_allowed, &c.d_flags->n_live, m);
         if (rc != TV_OK) return rc;
     }
 
@@ -1048,6 +1140,11 @@ int search_core(tv_index *h, SearchCtx &c, const float *queries, bool queries_on
             } else {
                 TV_CUDA(cudaMemcpyAsync(c.h_flags, c.d_flags, sizeof(DeviceFlags), cudaMemcpyDeviceToHost, st));
                 TV_CUDA(cudaStreamSynchronize(st));
+            }
+            if (rc == TV_OK && mask.ids_host && c.h_flags->first_unknown != ~0ull) {     // id_map.rs:672-677
+                const uint64_t bad = mask.ids_host[c.h_flags->first_unknown];
+                { std::lock_guard<std::mutex> g(h->stat_mu); h->err_id = bad; }
+                rc = fail(h, TV_ERR_UNKNOWN_ID, "allowlist id " + std::to_string(bad) + " is not in the index");
             }
             if (rc == TV_OK) rc = check_flags(h, c.h_flags, queries, queries_on_device, st);
             if (rc != TV_OK) { c.marks.used = 0; return rc; }
@@ -1361,6 +1458,7 @@ int add_rows_with_ids(tv_index *h, const float *vectors, size_t n, size_t dim, c
     h->slot_to_id.insert(h->slot_to_id.end(), ids, ids + n);
     h->id_to_slot.reserve(h->id_to_slot.size() + n);
     for (size_t i = 0; i < n; ++i) h->id_to_slot.emplace(ids[i], uint32_t(base + i));
+    for (size_t i = 0; i < n; ++i) h->idtab.note(ids[i], uint32_t(base + i), h->slot_to_id.size());
     return TV_OK;
 }
 }  // namespace
@@ -1402,10 +1500,12 @@ int tv_remove(tv_index *h, uint64_t id, int *removed) {
     h->n = last;                                                       // enqueued, not awaited (see tv_swap_remove)
     mutation_done(h);
     h->id_to_slot.erase(it);
+    h->idtab.note(id, 0xffffffffu, h->slot_to_id.size());
     if (slot != last) {                                                // id_map.rs:557-561
         const uint64_t moved = h->slot_to_id[last];
         h->slot_to_id[slot] = moved;
         h->id_to_slot[moved] = uint32_t(slot);
+        h->idtab.note(moved, uint32_t(slot), h->slot_to_id.size());
     }
     h->slot_to_id.pop_back();
     if (removed) *removed = 1;
@@ -1488,9 +1588,14 @@ int tv_search_allowlist(tv_index *h, const float *queries, size_t nq, size_t dim
     MaskSpec m;
     std::vector<uint32_t> slots;
     if (allow_ids) {                                                    // id_map.rs:670-683
-        int rc = resolve_allowlist(h, allow_ids, n_allow, slots);
-        if (rc != TV_OK) return rc;
-        m.slots_host = slots.data(); m.n_slots = slots.size();
+        if (n_allow == 0) return fail(h, TV_ERR_ALLOWLIST_EMPTY, "allowlist is empty");
+        if (n_allow >= kDeviceAllowlistMin && !h->idtab.unusable && h->n > 0 && nq > 0) {
+            m.ids_host = allow_ids; m.n_ids = n_allow;               // long lists: resolved by the device table
+        } else {
+            int rc = resolve_allowlist(h, allow_ids, n_allow, slots);
+            if (rc != TV_OK) return rc;
+            m.slots_host = slots.data(); m.n_slots = slots.size();
+        }
     }
     return search_host(h, queries, nq, dim, k, m, scores_out, nullptr, ids_out, k_eff);
 }
@@ -1555,11 +1660,19 @@ int prepare_mask(tv_index *h, const MaskSpec &spec) {
     TV_CUDA(h->prepared.counts.reserve(2));
     TV_CUDA(cudaMemsetAsync(h->prepared.counts.ptr, 0, 16, h->stream));
     MaskOnDevice m;
+    TV_CUDA(cudaMemsetAsync(&h->d_flags->first_unknown, 0xff, 8, h->stream));
     int rc = build_mask(h, h->stream, spec, h->prepared.words, h->ctx[0].d_mask_bool, h->ctx[0].d_slots_in, h->prepared.live,
+                        h->ctx[0].d_allow_ids, &h->d_flags->first_unknown,
                         h->prepared.counts.ptr, reinterpret_cast<uint32_t *>(h->prepared.counts.ptr + 1), m);
     if (rc != TV_OK) return rc;
     TV_CUDA(cudaEventRecord(h->ev_mut, h->stream));             // searches run on other streams: order them after this
+    TV_CUDA(cudaMemcpyAsync(&h->h_flags->first_unknown, &h->d_flags->first_unknown, 8, cudaMemcpyDeviceToHost, h->stream));
     TV_CUDA(cudaStreamSynchronize(h->stream));
+    if (spec.ids_host && h->h_flags->first_unknown != ~0ull) {
+        const uint64_t bad = spec.ids_host[h->h_flags->first_unknown];
+        { std::lock_guard<std::mutex> g(h->stat_mu); h->err_id = bad; }
+        return fail(h, TV_ERR_UNKNOWN_ID, "allowlist id " + std::to_string(bad) + " is not in the index");
+    }
     h->prepared.valid = true;
     return TV_OK;
 }
@@ -1588,10 +1701,14 @@ int tv_mask_prepare_allowlist(tv_index *h, const uint64_t *allow_ids, size_t n_a
     std::unique_lock<std::shared_mutex> lock(h->mu);
     if (h->kind != TV_KIND_IDMAP) return fail(h, TV_ERR_WRONG_INDEX_KIND, "tv_mask_prepare_allowlist needs an id-mapped index");
     std::vector<uint32_t> slots;
-    int rc = resolve_allowlist(h, allow_ids, n_allow, slots);
-    if (rc != TV_OK) return rc;
     MaskSpec m;
-    m.slots_host = slots.data(); m.n_slots = slots.size();
+    if (n_allow >= kDeviceAllowlistMin && !h->idtab.unusable && h->n > 0) {
+        m.ids_host = allow_ids; m.n_ids = n_allow;
+    } else {
+        int rc = resolve_allowlist(h, allow_ids, n_allow, slots);
+        if (rc != TV_OK) return rc;
+        m.slots_host = slots.data(); m.n_slots = slots.size();
+    }
     return prepare_mask(h, m);
 }
 
@@ -1735,8 +1852,8 @@ int tv_search_device_noalloc(tv_index *h, const float *queries_device, size_t nq
     S.w_rows = 16; S.dim_pad = kNoAllocMaxDim; S.lut_pitch = size_t((ng + 3) / 4 * 4) * 32; S.cap = int(kNoAllocCap); S.allow_tc = false;
     {
         ScanParams probe = base_scan_params(h, mode);
-        plan.use_small = h->small_scan >= 0 && (h->small_scan & 4) == 0 && mode == TV_SCORE_PERMUTE_DOT &&
-                         scan_small_supported(probe, int(nq), h->smem_limit);
+        // (the tensor map of the swizzled variants is built on the host stack: no allocation)
+        plan.use_small = h->small_scan >= 0 && mode == TV_SCORE_PERMUTE_DOT && scan_small_supported(probe, int(nq), h->smem_limit);
     }
 
     // the context supplies a stream and the status words (allocated when the handle was created)
@@ -1874,6 +1991,7 @@ int tv_import_packed(tv_index *h, size_t dim, const uint8_t *packed, size_t n, c
         h->slot_to_id.assign(ids, ids + n);
         h->id_to_slot.clear();
         for (size_t i = 0; i < n; ++i) h->id_to_slot.emplace(ids[i], uint32_t(i));
+        h->idtab.reset(h->slot_to_id);
     }
     return TV_OK;
 }
@@ -1971,6 +2089,7 @@ int index_from_image(const uint8_t *data, size_t len, int expect_kind, int devic
     if (p.kind == 1) {
         h->slot_to_id = p.ids;
         for (size_t i = 0; i < p.n; ++i) h->id_to_slot.emplace(p.ids[i], uint32_t(i));
+        h->idtab.reset(h->slot_to_id);
     }
     if (bind_path && p.nonce != 0) {           // an unclaimed snapshot is loaded unbound: the first sync claims it
         h->sync_bound = true;

@@ -573,6 +573,65 @@ __global__ void advance_floor_kernel(const uint64_t *thr, uint64_t *lo, int nq) 
     if (q < nq) lo[q] = thr[q] == kEmptyKey ? kEmptyKey : thr[q] + 1;
 }
 
+// =====================================================================================================
+// Device-side id -> slot table of an id-mapped index: open addressing with linear probing over
+// (u64 key, u32 slot) pairs, hash = the multiply-shift mix the reference's IdHasher uses
+// (turbovec/src/id_map.rs:65-85).  The host tables stay the authority (ids never leave the host in results);
+// this copy only serves large allowlists, whose resolution - one hash lookup per id, id_map.rs:670-683 - would
+// otherwise run on host threads: the ids are uploaded once and one kernel turns them into mask bits.
+// =====================================================================================================
+constexpr uint64_t kIdEmpty = 0xffffffffffffffffull, kIdTomb = 0xfffffffffffffffeull;
+__device__ __forceinline__ uint32_t id_hash(uint64_t id, int log2cap) { return uint32_t((id * 0x9E3779B97F4A7C15ull) >> (64 - log2cap)); }
+
+// ids[i] -> slot first + i, for ids not yet in the table (a rebuild, or the rows of an add)
+__global__ void idtab_insert_kernel(uint64_t *keys, uint32_t *vals, int log2cap, const uint64_t *ids, int64_t n, uint32_t first) {
+    const int64_t i = int64_t(blockIdx.x) * blockDim.x + threadIdx.x;
+    if (i >= n) return;
+    const uint64_t id = ids[i];
+    const uint32_t mask = (1u << log2cap) - 1u;
+    uint32_t h = id_hash(id, log2cap);
+    for (uint32_t probe = 0; probe <= mask; ++probe, h = (h + 1) & mask) {
+        const unsigned long long prev = atomicCAS(reinterpret_cast<unsigned long long *>(&keys[h]), kIdEmpty, id);
+        if (prev == kIdEmpty || prev == id) { vals[h] = first + uint32_t(i); return; }
+    }
+}
+// (id, slot) pairs with distinct ids: slot == 0xffffffff removes the id, otherwise sets (or inserts) its slot
+__global__ void idtab_upsert_kernel(uint64_t *keys, uint32_t *vals, int log2cap, const uint64_t *ids, const uint32_t *slots, int64_t n) {
+    const int64_t i = int64_t(blockIdx.x) * blockDim.x + threadIdx.x;
+    if (i >= n) return;
+    const uint64_t id = ids[i];
+    const uint32_t slot = slots[i], mask = (1u << log2cap) - 1u;
+    uint32_t h = id_hash(id, log2cap);
+    for (uint32_t probe = 0; probe <= mask; ++probe, h = (h + 1) & mask) {
+        const uint64_t k = keys[h];
+        if (k == id) {
+            if (slot == 0xffffffffu) keys[h] = kIdTomb; else vals[h] = slot;
+            return;
+        }
+        if (k == kIdEmpty) {
+            if (slot == 0xffffffffu) return;                  // removing an id that is not there
+            const unsigned long long prev = atomicCAS(reinterpret_cast<unsigned long long *>(&keys[h]), kIdEmpty, id);
+            if (prev == kIdEmpty) { vals[h] = slot; return; }
+            // another new id took the place: keep probing
+        }
+    }
+}
+// allowlist ids -> mask bits; the smallest list index of an id that is not in the table goes to *first_unknown
+__global__ void idtab_lookup_kernel(const uint64_t *keys, const uint32_t *vals, int log2cap, const uint64_t *ids, int64_t n,
+                                    uint32_t *words32, unsigned long long *first_unknown) {
+    const int64_t i = int64_t(blockIdx.x) * blockDim.x + threadIdx.x;
+    if (i >= n) return;
+    const uint64_t id = ids[i];
+    const uint32_t mask = (1u << log2cap) - 1u;
+    uint32_t h = id_hash(id, log2cap);
+    for (uint32_t probe = 0; probe <= mask; ++probe, h = (h + 1) & mask) {
+        const uint64_t k = keys[h];
+        if (k == id) { const uint32_t s = vals[h]; atomicOr(&words32[s >> 5], 1u << (s & 31)); return; }
+        if (k == kIdEmpty) break;
+    }
+    atomicMin(first_unknown, (unsigned long long)i);
+}
+
 // Keys of a finished search with a slot offset added (the shard's first global slot); empty entries stay empty.
 __global__ void export_keys_kernel(const uint64_t *topk, int64_t count, uint64_t offset, uint64_t *out) {
     const int64_t i = int64_t(blockIdx.x) * blockDim.x + threadIdx.x;
@@ -693,6 +752,23 @@ cudaError_t launch_select(const CandidateBuffers &cb, int nq, int dense_count, c
 cudaError_t launch_advance_floor(const uint64_t *thr, uint64_t *lo, int nq, cudaStream_t s) {
     if (nq <= 0) return cudaSuccess;
     advance_floor_kernel<<<(nq + 255) / 256, 256, 0, s>>>(thr, lo, nq);
+    return cudaGetLastError();
+}
+
+cudaError_t launch_idtab_insert(uint64_t *keys, uint32_t *vals, int log2cap, const uint64_t *ids, int64_t n, uint32_t first, cudaStream_t s) {
+    if (n <= 0) return cudaSuccess;
+    idtab_insert_kernel<<<unsigned((n + 255) / 256), 256, 0, s>>>(keys, vals, log2cap, ids, n, first);
+    return cudaGetLastError();
+}
+cudaError_t launch_idtab_upsert(uint64_t *keys, uint32_t *vals, int log2cap, const uint64_t *ids, const uint32_t *slots, int64_t n, cudaStream_t s) {
+    if (n <= 0) return cudaSuccess;
+    idtab_upsert_kernel<<<unsigned((n + 255) / 256), 256, 0, s>>>(keys, vals, log2cap, ids, slots, n);
+    return cudaGetLastError();
+}
+cudaError_t launch_idtab_lookup(const uint64_t *keys, const uint32_t *vals, int log2cap, const uint64_t *ids, int64_t n, uint64_t *words,
+                                unsigned long long *first_unknown, cudaStream_t s) {
+    if (n <= 0) return cudaSuccess;
+    idtab_lookup_kernel<<<unsigned((n + 255) / 256), 256, 0, s>>>(keys, vals, log2cap, ids, n, reinterpret_cast<uint32_t *>(words), first_unknown);
     return cudaGetLastError();
 }
 

@@ -43,6 +43,14 @@ cudaError_t launch_scatter_slots(const uint32_t *slots, int64_t count, uint64_t 
 cudaError_t launch_mask_stats(uint64_t *words, int64_t n, unsigned long long *n_allowed, uint32_t *live_blocks,
                               uint32_t *n_live, cudaStream_t s);
 
+// ---- device copy of the id -> slot table (open addressing; keys 2^64-1 = empty, 2^64-2 = tombstone) ----
+// insert: ids[i] -> slot first + i (ids not yet present).  upsert: distinct ids; slot 0xffffffff removes, else sets or inserts.
+// lookup: sets the mask bit of every listed id's slot; *first_unknown = smallest list index of an id not in the table.
+cudaError_t launch_idtab_insert(uint64_t *keys, uint32_t *vals, int log2cap, const uint64_t *ids, int64_t n, uint32_t first, cudaStream_t s);
+cudaError_t launch_idtab_upsert(uint64_t *keys, uint32_t *vals, int log2cap, const uint64_t *ids, const uint32_t *slots, int64_t n, cudaStream_t s);
+cudaError_t launch_idtab_lookup(const uint64_t *keys, const uint32_t *vals, int log2cap, const uint64_t *ids, int64_t n, uint64_t *words,
+                                unsigned long long *first_unknown, cudaStream_t s);
+
 // ---- candidate machinery ----
 // Scan kernels append the key of every (query, slot) whose key is below thr[query] to
 // cand[query*cap ...]; cnt[query] counts appends (it may exceed cap: the excess is dropped and the
