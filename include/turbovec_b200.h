@@ -114,8 +114,14 @@ enum {
     TV_OPT_TC_PAIR = 9,         /* 1: permute-dot batches of more than 64 queries run the tensor-memory scan on pairs of
                                  * CTAs (tcgen05 cta_group::2: each SM loads half of every query slab); 0: one CTA per
                                  * work item (default: it measured slower).  Results are identical. */
-    TV_OPT_TC_WIDE = 10         /* 1 (default): batches of more than 256 queries run the tensor-memory scan whose work items
+    TV_OPT_TC_WIDE = 10,        /* 1 (default): batches of more than 256 queries run the tensor-memory scan whose work items
                                  * take two query groups per expanded code slab; 0: one group per item.  Identical results. */
+    TV_OPT_TC_EXPANDED = 11,    /* permute-dot batches on the tensor-memory scan read an int8 copy of the index (one level per
+                                 * coordinate: twice the bytes of the 4-bit codes) instead of expanding codes in the kernel.
+                                 * 1 (default): when the copy fits with a tenth of the device left free; 0: never (drops the
+                                 * copy); 2: always, a search fails when it does not fit.  The copy is built and kept current
+                                 * lazily by the searches that use it.  Identical results. */
+    TV_OPT_EXPANDED_BYTES = 12  /* read-only: bytes the int8 copy holds right now (0 = none) */
 };
 
 /* ---- construction: TurboQuantIndex::new / new_lazy (lib.rs:629, 670), IdMapIndex::new (id_map.rs:278) ---- */

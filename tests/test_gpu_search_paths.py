@@ -70,16 +70,18 @@ def test_small_scan_many_chunks_and_recovery(T):
 # ------------------------------------------------------------------ tensor-memory scan on CTA pairs
 @pytest.mark.parametrize("dim,n,nq", [(1536, 5003, 70), (1536, 4100, 300), (256, 4100, 257), (200, 9000, 1024), (1536, 40_000, 129),
                                       (64, 300_000, 65), (256, 20_000, 513), (128, 9000, 770)])
-@pytest.mark.parametrize("form", ["pair", "wide", "narrow"])
+@pytest.mark.parametrize("form", ["dense", "pair", "wide", "narrow"])
 def test_pair_tensor_scan_matches_oracle(T, dim, n, nq, form):
-    """The three forms of the tensor-memory scan: CTA pairs (tcgen05 cta_group::2, work items of 256 vectors x 256
-    queries), two query groups per expanded slab (batches above 256 queries; 513 and 770 queries end in an item of one
-    group), one group per item.  Odd numbers of 128-vector tiles, several chunks, partial query groups, masks."""
+    """The forms of the tensor-memory scan: over the int8 copy of the index (both operands by TMA; the default), and
+    over the codes on CTA pairs (tcgen05 cta_group::2, work items of 256 vectors x 256 queries), with two query groups
+    per expanded slab (batches above 256 queries; 513 and 770 queries end in an item of one group), with one group per
+    item.  Odd numbers of 128-vector tiles, several chunks, partial query groups, masks."""
     x = anisotropic(n, dim, seed=57)
     q = anisotropic(nq, dim, seed=57, offset=31)
     pre = oracle_index(x, 4)
     idx = T.TurboQuantIndex(dim, 4)
     idx.add(x)
+    idx.set_option(T.OPT_TC_EXPANDED, 2 if form == "dense" else 0)
     idx.set_option(T.OPT_TC_PAIR, 1 if form == "pair" else 0)
     idx.set_option(T.OPT_TC_WIDE, 1 if form == "wide" else 0)
     mask = np.random.default_rng(6).random(n) < 0.2
@@ -90,6 +92,58 @@ def test_pair_tensor_scan_matches_oracle(T, dim, n, nq, form):
     s, i = idx.search(q, 10, mask=mask)
     rs, ri = oracle_search(x, q, 4, 10, mask=mask, pre=pre)
     assert np.array_equal(i, ri) and np.array_equal(s, rs), "masked"
+    assert (idx.get_option(T.OPT_EXPANDED_BYTES) > 0) == (form == "dense")
+
+
+def test_int8_copy_follows_every_change_of_the_index(T):
+    """The int8 copy behind large permute-dot batches is brought up to date lazily: after appends (also into a
+    partly filled block and past a growth of the code array), removals, rewritten rows, a re-fit that re-encodes
+    every row and a load, a search over it must equal the search over the codes (copy switched off)."""
+    dim, nq = 256, 40
+    rng = np.random.default_rng(77)
+    x = anisotropic(30_000, dim, seed=77)
+    q = anisotropic(nq, dim, seed=77, offset=9)
+    idx = T.TurboQuantIndex(dim, 4)
+    idx.set_option(T.OPT_TC_EXPANDED, 2)
+
+    def check(tag):
+        got = idx.search(q, 10)
+        idx.set_option(T.OPT_TC_EXPANDED, 0)
+        assert idx.get_option(T.OPT_EXPANDED_BYTES) == 0
+        want = idx.search(q, 10)
+        idx.set_option(T.OPT_TC_EXPANDED, 2)
+        assert np.array_equal(got[1], want[1]) and np.array_equal(got[0], want[0]), tag
+
+    def check_kept(tag):                                          # without dropping the copy in between
+        got = idx.search(q, 10)
+        ref = T.TurboQuantIndex.from_bytes(idx.to_bytes())
+        ref.set_option(T.OPT_TC_EXPANDED, 0)
+        want = ref.search(q, 10)
+        assert np.array_equal(got[1], want[1]) and np.array_equal(got[0], want[0]), tag
+
+    idx.add(x[:1000])
+    check_kept("first build")
+    idx.add(x[1000:1013])                                         # ends inside a block
+    check_kept("append into a block")
+    idx.add(x[1013:1020])
+    check_kept("append into a partly filled block")
+    idx.add(x[1020:20_000])                                       # the code array grows: the copy is rebuilt
+    check_kept("growth")
+    for victim in rng.integers(0, 15_000, 50):
+        idx.swap_remove(int(victim))
+    check_kept("removals")
+    groups, scale = idx.get_row(5)
+    idx.set_row(77, groups, scale)
+    idx.set_row(19_000, groups, 0.5 * scale)
+    check_kept("rewritten rows")
+    for victim in rng.integers(0, 10_000, 5000):                  # more changed blocks than the list holds
+        idx.swap_remove(int(victim))
+    check_kept("many removals")
+    idx.add(x[20_000:])
+    check_kept("append after removals")
+    idx.calibrate(x[:4000])                                       # re-encodes every stored row
+    check_kept("re-fit")
+    check("copy dropped and rebuilt")
 
 
 # ------------------------------------------------------------------ u8-LUT flush family on tensor memory

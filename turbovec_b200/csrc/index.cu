@@ -189,6 +189,31 @@ struct DeviceIdTable {
 };
 constexpr size_t kDeviceAllowlistMin = 32768;   // allowlists at least this long are resolved on the device
 
+// The index as int8 levels (scan_tc_dense.cu): rows [0, rows_valid) minus the blocks in `dirty` are current.  Built and
+// brought up to date lazily by the first large-batch permute-dot search after a change; dropped when the code array moves.
+struct ExpandedCopy {
+    DeviceArray<int8_t> levels;       // rows_cap x pitch
+    size_t rows_cap = 0;              // rows allocated (the capacity of the code array, whole blocks)
+    size_t rows_valid = 0;
+    int pitch = 0;
+    std::vector<uint32_t> dirty;      // blocks below rows_valid whose codes changed in place
+    DeviceArray<uint32_t> d_dirty;
+    size_t refused_at_cap = 0;        // the allocation for this capacity did not fit: do not try again until it changes
+    cudaEvent_t ev = nullptr;         // recorded after every update; searches on other streams wait for it
+    std::mutex mu;
+    ~ExpandedCopy() { if (ev) cudaEventDestroy(ev); }
+    void touch(size_t slot) {         // the codes of `slot` changed in place
+        if (slot >= rows_valid) return;
+        const uint32_t blk = uint32_t(slot / 32);
+        if (!dirty.empty() && dirty.back() == blk) return;
+        if (dirty.size() >= 4096) { rows_valid = std::min(rows_valid, size_t(*std::min_element(dirty.begin(), dirty.end())) * 32); dirty.clear(); }
+        if (slot < rows_valid) dirty.push_back(blk);
+    }
+    void shrink(size_t n) { rows_valid = std::min(rows_valid, n); }
+    void reset() { rows_valid = 0; dirty.clear(); }
+    void drop() { levels.release(); rows_cap = 0; refused_at_cap = 0; reset(); }
+};
+
 // An allow-mask kept on the device between searches (tv_mask_prepare_*): words, live-block list and the two
 // counts the kernels read.  Any change of the index invalidates it.
 struct PreparedMask {
@@ -229,6 +254,7 @@ struct tv_index {
     int small_scan = 5;          // permute-dot scan for up to 16 queries: -1 = scan_pd_kernel, else a scan_small_kernel variant
                                  // (5 = four-stage rings, two CTAs per SM, swizzled tensor copies: the fastest measured)
     int tc_wide = 1;             // 1: batches above 256 queries share every expanded code slab between two query groups
+    int tc_expanded = 1;         // 1: large permute-dot batches scan an int8 copy of the index when device memory has room for it; 0 never; 2 always (fail if it does not fit)
     int tc_pair = 0;             // 1: permute-dot batches above 64 queries run the tensor-memory scan on CTA pairs (cta_group::2)
     int fail_next = 0;           // test hook (TV_OPT_FAIL_NEXT): the next device allocation / upload of a call reports failure
 
@@ -280,6 +306,7 @@ struct tv_index {
     std::condition_variable ctx_cv;
     PreparedMask prepared;
     DeviceIdTable idtab;
+    ExpandedCopy expanded;
 
     // id map (ids never reach the device; id_map.rs:221-272)
     std::vector<uint64_t> slot_to_id;
@@ -465,6 +492,7 @@ int ensure_capacity(tv_index *h, size_t n_total) {
         if (h->d_codes) cudaFree(h->d_codes);
         h->d_codes = fresh;
         h->code_blocks_cap = new_cap;
+        h->expanded.drop();                    // sized by the capacity: rebuilt by the next search that wants it
     }
     if (n_total > h->scales_cap) {
         size_t new_cap = std::max(n_total, h->scales_cap + h->scales_cap / 2);
@@ -867,6 +895,60 @@ int plan_scan(tv_index *h, int mode, size_t nq, bool allow_tc, ScanPlan &plan) {
     return TV_OK;
 }
 
+// Brings the int8 copy of the index (scan_tc_dense.cu) up to date on `st`: allocates it when policy and free memory
+// allow, expands the rows appended and the blocks changed in place since the last time.  *usable = false when there
+// is no copy to scan (switched off, or no room); the caller then scans the codes.
+int expanded_sync(tv_index *h, cudaStream_t st, const uint32_t level_words[4], bool *usable) {
+    *usable = false;
+    ExpandedCopy &x = h->expanded;
+    if (h->tc_expanded == 0 || h->n == 0) return TV_OK;
+    std::lock_guard<std::mutex> g(x.mu);
+    if (!x.ev) TV_CUDA(cudaEventCreateWithFlags(&x.ev, cudaEventDisableTiming));
+    const size_t rows = h->code_blocks_cap * kBlock;
+    const int pitch = expanded_pitch(int(h->dim));
+    if (x.rows_cap != rows || x.pitch != pitch || !x.levels.ptr) {
+        if (x.refused_at_cap == rows && h->tc_expanded != 2) return TV_OK;
+        const size_t bytes = rows * size_t(pitch);
+        size_t free_b = 0, total_b = 0;
+        TV_CUDA(cudaMemGetInfo(&free_b, &total_b));
+        // keep a tenth of the device (at least 1 GiB) free for scratch and for the growth of the index
+        const size_t keep = std::max<size_t>(total_b / 10, size_t(1) << 30);
+        x.drop();
+        cudaError_t e = cudaErrorMemoryAllocation;
+        if (h->tc_expanded == 2 || free_b >= bytes + keep) e = x.levels.reserve(bytes);
+        if (e != cudaSuccess) {
+            cudaGetLastError();
+            x.refused_at_cap = rows;
+            if (h->tc_expanded == 2) return fail(h, TV_ERR_CUDA, "no room for the int8 copy of the index (" + std::to_string(bytes) + " bytes)");
+            return TV_OK;
+        }
+        // padding columns and rows are never cleared: padding columns meet zero query weights, padding rows are not read out
+        x.rows_cap = rows; x.pitch = pitch;
+    }
+    bool work = false;
+    if (!x.dirty.empty()) {
+        TV_CUDA(x.d_dirty.reserve(x.dirty.size()));
+        TV_CUDA(cudaMemcpyAsync(x.d_dirty.ptr, x.dirty.data(), x.dirty.size() * 4, cudaMemcpyHostToDevice, st));   // pageable: staged before the call returns
+        TV_CUDA(launch_expand_blocks(h->d_codes, h->ngroups, x.d_dirty.ptr, 0, uint32_t(x.dirty.size()), x.levels.ptr, pitch, level_words,
+                                     h->sm_count, st));
+        h->launches++;
+        x.dirty.clear();
+        work = true;
+    }
+    if (x.rows_valid < h->n) {
+        const size_t first = x.rows_valid / kBlock, end = (h->n + kBlock - 1) / kBlock;
+        TV_CUDA(launch_expand_blocks(h->d_codes, h->ngroups, nullptr, uint32_t(first), uint32_t(end - first), x.levels.ptr, pitch, level_words,
+                                     h->sm_count, st));
+        h->launches++;
+        x.rows_valid = h->n;
+        work = true;
+    }
+    if (work) TV_CUDA(cudaEventRecord(x.ev, st));
+    else TV_CUDA(cudaStreamWaitEvent(st, x.ev, 0));
+    *usable = true;
+    return TV_OK;
+}
+
 // Query preparation, then scan + select over a geometric chunk schedule, all enqueued on `st`.
 //   careful: chunks never exceed the candidate capacity, so no list can overflow whatever the data order.
 int enqueue_search(tv_index *h, cudaStream_t st, Marks *marks, const SearchScratch &S, const ScanPlan &plan, int mode,
@@ -884,6 +966,11 @@ int enqueue_search(tv_index *h, cudaStream_t st, Marks *marks, const SearchScrat
     sp.mask = m.words; sp.live_blocks = m.live; sp.n_live = m.n_live;
     sp.cb = cb; sp.wfrag = S.wfrag; sp.mtiles_total = mt_total; sp.luts = S.luts; sp.lut_pitch = int(S.lut_pitch);
     const bool use_small = plan.use_small && !plan.use_tc;
+    bool use_dense = false;
+    if (plan.use_tc && !h->tc_pair && scan_tc_dense_supported(h->bits, mode, ng) && int(S.dim_pad) == expanded_pitch(int(h->dim))) {
+        int rc = expanded_sync(h, st, sp.level_words, &use_dense);
+        if (rc != TV_OK) return rc;
+    }
 
     TV_CUDA(cudaMemsetAsync(S.cnt, 0, nq * 4, st));
     TV_CUDA(cudaMemsetAsync(S.thr, 0xff, nq * 8, st));
@@ -915,7 +1002,10 @@ int enqueue_search(tv_index *h, cudaStream_t st, Marks *marks, const SearchScrat
             sp.q_base = 0; sp.nq = int(nq); sp.mtile_base = 0;
             if (marks) marks->begin(st);
             const bool wide = h->tc_wide && scan_tc_wide_supported(h->bits, mode, ng, int(nq));
-            if (mode == TV_SCORE_PERMUTE_DOT && h->tc_pair && scan_tc_pair_supported(h->bits, mode, int(nq)))
+            if (use_dense)
+                TV_CUDA(launch_scan_tc_dense(sp, h->expanded.levels.ptr, h->expanded.rows_cap, S.weights, int(S.w_rows), int(S.dim_pad),
+                                             h->sm_count, st));
+            else if (mode == TV_SCORE_PERMUTE_DOT && h->tc_pair && scan_tc_pair_supported(h->bits, mode, int(nq)))
                 TV_CUDA(launch_scan_tc_pair(sp, S.weights, int(S.w_rows), int(S.dim_pad), h->sm_count, st));
             else if (wide && mode == TV_SCORE_PERMUTE_DOT)
                 TV_CUDA(launch_scan_tc_wide(sp, S.weights, int(S.w_rows), int(S.dim_pad), h->sm_count, st));
@@ -1389,6 +1479,10 @@ int tv_set_option(tv_index *h, int option, int64_t value) {
         case TV_OPT_FAIL_NEXT: h->fail_next = value < 0 ? 0 : int(value); return TV_OK;
         case TV_OPT_TC_PAIR: h->tc_pair = value != 0; return TV_OK;
         case TV_OPT_TC_WIDE: h->tc_wide = value != 0; return TV_OK;
+        case TV_OPT_TC_EXPANDED:
+            h->tc_expanded = value < 0 || value > 2 ? 1 : int(value);
+            if (h->tc_expanded == 0) { std::lock_guard<std::mutex> g(h->expanded.mu); h->expanded.drop(); }
+            return TV_OK;
         default: return fail(h, TV_ERR_INVALID_ARGUMENT, "unknown option");
     }
 }
@@ -1406,6 +1500,8 @@ int64_t tv_get_option(const tv_index *h, int option) {
         case TV_OPT_FAIL_NEXT: return h->fail_next;
         case TV_OPT_TC_PAIR: return h->tc_pair;
         case TV_OPT_TC_WIDE: return h->tc_wide;
+        case TV_OPT_TC_EXPANDED: return h->tc_expanded;
+        case TV_OPT_EXPANDED_BYTES: return h->expanded.levels.ptr ? int64_t(h->expanded.rows_cap * size_t(h->expanded.pitch)) : 0;
         default: return -1;
     }
 }
@@ -1477,6 +1573,8 @@ int tv_swap_remove(tv_index *h, size_t slot, size_t *moved_from) {
     // same stream, after the move
     h->mark_dirty(slot);                      // lib.rs:2879-2885: the hole and the moved-from slot diverge
     if (last != slot) h->mark_dirty(last);
+    h->expanded.touch(slot);
+    h->expanded.shrink(last);
     h->n = last;
     mutation_done(h);
     if (moved_from) *moved_from = last;
@@ -1497,6 +1595,8 @@ int tv_remove(tv_index *h, uint64_t id, int *removed) {
     TV_CUDA(cudaGetLastError());
     h->mark_dirty(slot);
     if (last != slot) h->mark_dirty(last);
+    h->expanded.touch(slot);
+    h->expanded.shrink(last);
     h->n = last;                                                       // enqueued, not awaited (see tv_swap_remove)
     mutation_done(h);
     h->id_to_slot.erase(it);
@@ -1544,6 +1644,7 @@ int tv_set_row(tv_index *h, size_t slot, const uint8_t *groups, size_t count, fl
     TV_CUDA(cudaMemcpyAsync(h->d_scales + slot, &scale, 4, cudaMemcpyHostToDevice, h->stream));
     TV_CUDA(cudaStreamSynchronize(h->stream));
     h->mark_dirty(slot);
+    h->expanded.touch(slot);
     mutation_done(h);
     return TV_OK;
 }
@@ -1986,6 +2087,7 @@ int tv_import_packed(tv_index *h, size_t dim, const uint8_t *packed, size_t n, c
     TV_CUDA(cudaMemcpyAsync(h->d_scales, scales, n * 4, cudaMemcpyHostToDevice, h->stream));
     TV_CUDA(cudaStreamSynchronize(h->stream));
     h->n = n;
+    h->expanded.reset();
     mutation_done(h);
     if (ids) {
         h->slot_to_id.assign(ids, ids + n);
@@ -2405,6 +2507,7 @@ int tv_calibrate(tv_index *h, const float *sample, size_t n, size_t dim) {
         if (!h->shift.empty()) { rp.old_shift = h->d_calib.ptr; rp.old_inv = h->d_calib.ptr + 2 * dim; }
         rp.new_shift = d_new.ptr; rp.new_scale = d_new.ptr + dim; rp.new_inv = d_new.ptr + 2 * dim;
         TV_CUDA(launch_reencode(rp, h->stream));
+        h->expanded.reset();                       // every stored code changed
         h->launches++;
         TV_CUDA(cudaStreamSynchronize(h->stream));
     }

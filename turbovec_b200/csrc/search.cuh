@@ -119,6 +119,16 @@ cudaError_t launch_scan_tc(const ScanParams &p, const int8_t *weights, int rows,
 // The same scan for more than 256 queries with every expanded code slab shared by two query groups (scan_tc_wide.cu).
 bool scan_tc_wide_supported(int bits, int mode, int ngroups, int nq_total);
 cudaError_t launch_scan_tc_wide(const ScanParams &p, const int8_t *weights, int rows, int pitch, int sm_count, cudaStream_t s);
+// The permute-dot scan over an int8 copy of the index (scan_tc_dense.cu): both MMA operands arrive by TMA.
+// expand_blocks writes the copy: row-major int8 levels, `pitch` = expanded_pitch(dim) bytes per slot, for a range of
+// 32-slot blocks or (block_list != nullptr) for the listed blocks.
+bool scan_tc_dense_supported(int bits, int mode, int ngroups);
+int expanded_pitch(int dim);
+cudaError_t launch_expand_blocks(const uint8_t *codes, int ngroups, const uint32_t *block_list, uint32_t first_block,
+                                 uint32_t n_blocks, int8_t *expanded, int pitch, const uint32_t level_words[4], int sm_count,
+                                 cudaStream_t s);
+cudaError_t launch_scan_tc_dense(const ScanParams &p, const int8_t *expanded, size_t exp_rows, const int8_t *weights, int rows,
+                                 int pitch, int sm_count, cudaStream_t s);
 // The same scan on CTA pairs (scan_tc2.cu): tcgen05.mma.cta_group::2, each CTA of a pair expands 128 vectors and loads
 // half of the query slab.  Permute-dot batches of more than 64 queries.
 bool scan_tc_pair_supported(int bits, int mode, int nq_total);
