@@ -5,8 +5,8 @@
 // of two query groups occupy the tensor pipe, and the two never overlap well.  The index can instead keep the levels
 // themselves (`expanded`: one int8 per coordinate, row-major, row pitch = dim rounded up to 128; written by
 // expand_blocks_kernel whenever rows change), twice the bytes of the codes.  Then both MMA operands arrive by TMA:
-//   * warp 0 (one thread) loads, per 128-byte K slab, the A tile (128 vectors: four boxes of one 32-slot block each, so
-//     that the compacted block list of a filtered search works the same way) and one B tile (256 queries) per group;
+//   * warp 0 (one thread) loads, per 128-byte K slab, the A tile (128 vectors: one box, or with the compacted block list
+//     of a filtered search four boxes of one 32-slot block each); warp 3 (one thread) one B tile (256 queries) per group;
 //   * warps 1 and 2 (one thread each) issue the MMAs of the item's first and second query group: M = 128 vectors x
 //     N = 256 queries x K = 32, tcgen05.mma kind::i8, accumulators in tensor-memory columns 256 j .. 256 j + 255;
 //   * warps 4..11 are the epilogue, four per group (integer dismissal bound, then the exact float score; scan_tc_common.cuh).
@@ -48,7 +48,8 @@ struct DenseShared {
 static_assert(offsetof(DenseShared, qscale) % 16 == 0, "parameter arrays must be 16-byte aligned");
 
 __global__ void __launch_bounds__(kDenseThreads, 1)
-scan_tc_dense_kernel(ScanParams p, const __grid_constant__ CUtensorMap amap, const __grid_constant__ CUtensorMap wmap,
+scan_tc_dense_kernel(ScanParams p, const __grid_constant__ CUtensorMap amap, const __grid_constant__ CUtensorMap amap128,
+                     const __grid_constant__ CUtensorMap wmap,
                      int n_slabs, int n_qgroups) {
     constexpr bool ONEHOT = false;
     constexpr bool fused = false;
@@ -87,14 +88,15 @@ scan_tc_dense_kernel(ScanParams p, const __grid_constant__ CUtensorMap amap, con
     auto groups_of = [&](int gp) { return 2 * gp + 1 < n_qgroups ? 2 : 1; };
 
     if (warp == 0) {
-        // ------------------------------------------------ TMA producer: level tiles and query tiles ------------
+        // ------------------------------------------------ TMA producer of the level tiles ------------------------
+        // Issuing a tensor copy costs its thread about a hundred cycles, so the level tiles and the query tiles have a
+        // producer thread each.  Without a block list the four blocks of an item are neighbours: one box of 128 rows.
         if (lane == 0) {
-            uint32_t it_a = 0, it_b = 0;
+            uint32_t it_a = 0;
             uint32_t vt = blockIdx.x / uint32_t(n_gpairs);
             int gp = int(blockIdx.x % uint32_t(n_gpairs));
             bool ok = true;
             for (uint32_t item = blockIdx.x; item < n_items && ok; item += gridDim.x) {
-                const int gcount = groups_of(gp);
                 // first slot of each of the item's blocks in the expanded copy (row coordinate of its box)
                 int rows[kDenseBlocksPerItem];
                 int n_rows = 0;
@@ -108,12 +110,32 @@ scan_tc_dense_kernel(ScanParams p, const __grid_constant__ CUtensorMap amap, con
                     const int a_slot = it_a % kDenseASlots;
                     ok = mbar_wait(&sh->a_empty[a_slot], ((it_a / kDenseASlots) & 1) ^ 1, p.cb.error);
                     if (!ok) break;
-                    // blocks past the end of the chunk are not loaded: their accumulator rows are never read
-                    mbar_arrive_expect_tx(&sh->a_full[a_slot], uint32_t(n_rows) * 32u * kSlabK);
                     unsigned char *a_tile = a_ring + size_t(a_slot) * kATileBytes;
+                    if (p.live_blocks == nullptr) {
+                        // rows past the end of the chunk or of the copy are loaded or zero-filled alike: never read out
+                        mbar_arrive_expect_tx(&sh->a_full[a_slot], uint32_t(kATileBytes));
+                        tma_load_2d(a_tile, &amap128, s * kSlabK, rows[0], &sh->a_full[a_slot]);
+                    } else {
+                        // blocks past the end of the list are not loaded: their accumulator rows are never read out
+                        mbar_arrive_expect_tx(&sh->a_full[a_slot], uint32_t(n_rows) * 32u * kSlabK);
 #pragma unroll
-                    for (int b = 0; b < kDenseBlocksPerItem; ++b)
-                        if (b < n_rows) tma_load_2d(a_tile + b * 32 * kSlabK, &amap, s * kSlabK, rows[b], &sh->a_full[a_slot]);
+                        for (int b = 0; b < kDenseBlocksPerItem; ++b)
+                            if (b < n_rows) tma_load_2d(a_tile + b * 32 * kSlabK, &amap, s * kSlabK, rows[b], &sh->a_full[a_slot]);
+                    }
+                }
+                vt += vt_step; gp += gp_step;
+                if (gp >= n_gpairs) { gp -= n_gpairs; ++vt; }
+            }
+        }
+    } else if (warp == 3) {
+        // ------------------------------------------------ TMA producer of the query tiles, group by group -----------
+        if (lane == 0) {
+            uint32_t it_b = 0;
+            int gp = int(blockIdx.x % uint32_t(n_gpairs));
+            bool ok = true;
+            for (uint32_t item = blockIdx.x; item < n_items && ok; item += gridDim.x) {
+                const int gcount = groups_of(gp);
+                for (int s = 0; s < n_slabs && ok; ++s) {
                     for (int j = 0; j < gcount && ok; ++j, ++it_b) {
                         const int slot = it_b % kDenseBSlots;
                         ok = mbar_wait(&sh->b_empty[slot], ((it_b / kDenseBSlots) & 1) ^ 1, p.cb.error);
@@ -122,8 +144,8 @@ scan_tc_dense_kernel(ScanParams p, const __grid_constant__ CUtensorMap amap, con
                         tma_load_2d(b_ring + size_t(slot) * kDenseBBytes, &wmap, s * kSlabK, (2 * gp + j) * kTileQueries, &sh->b_full[slot]);
                     }
                 }
-                vt += vt_step; gp += gp_step;
-                if (gp >= n_gpairs) { gp -= n_gpairs; ++vt; }
+                gp += gp_step;
+                if (gp >= n_gpairs) gp -= n_gpairs;
             }
         }
     } else if (warp == 1 || warp == 2) {
@@ -392,7 +414,7 @@ cudaError_t launch_scan_tc_dense(const ScanParams &p, const int8_t *expanded, si
     EncodeTiledFn enc = reinterpret_cast<EncodeTiledFn>(tensor_map_encoder());
     if (!enc) return cudaErrorNotSupported;
     const int nq_all = p.q_base + p.nq;
-    CUtensorMap wmap, amap;
+    CUtensorMap wmap, amap, amap128;
     const cuuint64_t strides[1] = {cuuint64_t(pitch)};
     const cuuint32_t estr[2] = {1, 1};
     {
@@ -410,6 +432,11 @@ cudaError_t launch_scan_tc_dense(const ScanParams &p, const int8_t *expanded, si
                 CU_TENSOR_MAP_INTERLEAVE_NONE, CU_TENSOR_MAP_SWIZZLE_128B, CU_TENSOR_MAP_L2_PROMOTION_L2_256B,
                 CU_TENSOR_MAP_FLOAT_OOB_FILL_NONE) != CUDA_SUCCESS)
             return cudaErrorInvalidValue;
+        const cuuint32_t box128[2] = {cuuint32_t(kSlabK), cuuint32_t(kMmaM)};
+        if (enc(&amap128, CU_TENSOR_MAP_DATA_TYPE_UINT8, 2, const_cast<int8_t *>(expanded), dims, strides, box128, estr,
+                CU_TENSOR_MAP_INTERLEAVE_NONE, CU_TENSOR_MAP_SWIZZLE_128B, CU_TENSOR_MAP_L2_PROMOTION_L2_256B,
+                CU_TENSOR_MAP_FLOAT_OOB_FILL_NONE) != CUDA_SUCCESS)
+            return cudaErrorInvalidValue;
     }
     const int n_slabs = pitch / kSlabK;
     const int n_qgroups = (nq_all + kMaxTileQueries - 1) / kMaxTileQueries;
@@ -423,7 +450,7 @@ cudaError_t launch_scan_tc_dense(const ScanParams &p, const int8_t *expanded, si
     if (items < grid) grid = unsigned(items);
     cudaError_t e = cudaFuncSetAttribute(scan_tc_dense_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, int(smem));
     if (e != cudaSuccess) return e;
-    scan_tc_dense_kernel<<<grid, kDenseThreads, smem, s>>>(p, amap, wmap, n_slabs, n_qgroups);
+    scan_tc_dense_kernel<<<grid, kDenseThreads, smem, s>>>(p, amap, amap128, wmap, n_slabs, n_qgroups);
     return cudaGetLastError();
 }
 
