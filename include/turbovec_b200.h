@@ -121,7 +121,9 @@ enum {
                                  * 1 (default): when the copy fits with a tenth of the device left free; 0: never (drops the
                                  * copy); 2: always, a search fails when it does not fit.  The copy is built and kept current
                                  * lazily by the searches that use it.  Identical results. */
-    TV_OPT_EXPANDED_BYTES = 12  /* read-only: bytes the int8 copy holds right now (0 = none) */
+    TV_OPT_EXPANDED_BYTES = 12, /* read-only: bytes the int8 copy holds right now (0 = none) */
+    TV_OPT_DENSE_PAIR = 13      /* 1 (default): the scan over the int8 copy runs on CTA pairs (tcgen05 cta_group::2: half the
+                                 * query bytes per SM); 0: one CTA per work item.  Identical results. */
 };
 
 /* ---- construction: TurboQuantIndex::new / new_lazy (lib.rs:629, 670), IdMapIndex::new (id_map.rs:278) ---- */

@@ -255,6 +255,7 @@ struct tv_index {
                                  // (5 = four-stage rings, two CTAs per SM, swizzled tensor copies: the fastest measured)
     int tc_wide = 1;             // 1: batches above 256 queries share every expanded code slab between two query groups
     int tc_expanded = 1;         // 1: large permute-dot batches scan an int8 copy of the index when device memory has room for it; 0 never; 2 always (fail if it does not fit)
+    int dense_pair = 1;          // 1: the scan over the int8 copy runs on CTA pairs (cta_group::2)
     int tc_pair = 0;             // 1: permute-dot batches above 64 queries run the tensor-memory scan on CTA pairs (cta_group::2)
     int fail_next = 0;           // test hook (TV_OPT_FAIL_NEXT): the next device allocation / upload of a call reports failure
 
@@ -1002,7 +1003,10 @@ int enqueue_search(tv_index *h, cudaStream_t st, Marks *marks, const SearchScrat
             sp.q_base = 0; sp.nq = int(nq); sp.mtile_base = 0;
             if (marks) marks->begin(st);
             const bool wide = h->tc_wide && scan_tc_wide_supported(h->bits, mode, ng, int(nq));
-            if (use_dense)
+            if (use_dense && h->dense_pair)
+                TV_CUDA(launch_scan_tc_dense_pair(sp, h->expanded.levels.ptr, h->expanded.rows_cap, S.weights, int(S.w_rows), int(S.dim_pad),
+                                                  h->sm_count, st));
+            else if (use_dense)
                 TV_CUDA(launch_scan_tc_dense(sp, h->expanded.levels.ptr, h->expanded.rows_cap, S.weights, int(S.w_rows), int(S.dim_pad),
                                              h->sm_count, st));
             else if (mode == TV_SCORE_PERMUTE_DOT && h->tc_pair && scan_tc_pair_supported(h->bits, mode, int(nq)))
@@ -1479,6 +1483,7 @@ int tv_set_option(tv_index *h, int option, int64_t value) {
         case TV_OPT_FAIL_NEXT: h->fail_next = value < 0 ? 0 : int(value); return TV_OK;
         case TV_OPT_TC_PAIR: h->tc_pair = value != 0; return TV_OK;
         case TV_OPT_TC_WIDE: h->tc_wide = value != 0; return TV_OK;
+        case TV_OPT_DENSE_PAIR: h->dense_pair = value != 0; return TV_OK;
         case TV_OPT_TC_EXPANDED:
             h->tc_expanded = value < 0 || value > 2 ? 1 : int(value);
             if (h->tc_expanded == 0) { std::lock_guard<std::mutex> g(h->expanded.mu); h->expanded.drop(); }
@@ -1501,6 +1506,7 @@ int64_t tv_get_option(const tv_index *h, int option) {
         case TV_OPT_TC_PAIR: return h->tc_pair;
         case TV_OPT_TC_WIDE: return h->tc_wide;
         case TV_OPT_TC_EXPANDED: return h->tc_expanded;
+        case TV_OPT_DENSE_PAIR: return h->dense_pair;
         case TV_OPT_EXPANDED_BYTES: return h->expanded.levels.ptr ? int64_t(h->expanded.rows_cap * size_t(h->expanded.pitch)) : 0;
         default: return -1;
     }

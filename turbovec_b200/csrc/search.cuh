@@ -129,6 +129,10 @@ cudaError_t launch_expand_blocks(const uint8_t *codes, int ngroups, const uint32
                                  cudaStream_t s);
 cudaError_t launch_scan_tc_dense(const ScanParams &p, const int8_t *expanded, size_t exp_rows, const int8_t *weights, int rows,
                                  int pitch, int sm_count, cudaStream_t s);
+// The same on CTA pairs (scan_tc_dense2.cu): tcgen05.mma.cta_group::2, each CTA loads the levels of 128 vectors and half of
+// every query tile.
+cudaError_t launch_scan_tc_dense_pair(const ScanParams &p, const int8_t *expanded, size_t exp_rows, const int8_t *weights, int rows,
+                                      int pitch, int sm_count, cudaStream_t s);
 // The same scan on CTA pairs (scan_tc2.cu): tcgen05.mma.cta_group::2, each CTA of a pair expands 128 vectors and loads
 // half of the query slab.  Permute-dot batches of more than 64 queries.
 bool scan_tc_pair_supported(int bits, int mode, int nq_total);
