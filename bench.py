@@ -282,7 +282,8 @@ def run_ours(args):
         idx = ShardedIdMapIndex(DIM, BITS, device=device)
         local = idx.local
     for opt, val in ((T.OPT_MMA_MIN_BATCH, args.tc_min_batch), (T.OPT_INGEST_PIPELINE, args.ingest_pipeline),
-                     (T.OPT_SMALL_SCAN, args.small_scan), (T.OPT_TC_PAIR, args.tc_pair), (T.OPT_TC_WIDE, args.tc_wide)):
+                     (T.OPT_SMALL_SCAN, args.small_scan), (T.OPT_TC_PAIR, args.tc_pair), (T.OPT_TC_WIDE, args.tc_wide),
+                     (T.OPT_TC_EXPANDED, args.tc_expanded), (T.OPT_DENSE_PAIR, args.dense_pair)):
         if val is not None:
             local.set_option(opt, val)
     n_recall_q = 64
@@ -698,6 +699,9 @@ def main():
     ap.add_argument("--small-scan", type=int, default=None, help="TV_OPT_SMALL_SCAN variant (-1 = scan_pd_kernel)")
     ap.add_argument("--tc-pair", type=int, default=None, choices=[0, 1], help="TV_OPT_TC_PAIR: tensor-memory scan on CTA pairs")
     ap.add_argument("--tc-wide", type=int, default=None, choices=[0, 1], help="TV_OPT_TC_WIDE: two query groups per expanded code slab")
+    ap.add_argument("--tc-expanded", type=int, default=None, choices=[0, 1, 2],
+                    help="TV_OPT_TC_EXPANDED: large permute-dot batches scan an int8 copy of the index (0 never, 1 if it fits, 2 always)")
+    ap.add_argument("--dense-pair", type=int, default=None, choices=[0, 1], help="TV_OPT_DENSE_PAIR: that scan on CTA pairs")
     ap.add_argument("--skip-cpu", dest="no_cpu", action="store_true", help="skip the cpu_baseline leg")
     ap.add_argument("--skip-filtered", dest="no_filtered", action="store_true", help="skip the filtered-search and allocation-free legs")
     ap.add_argument("--skip-mutation", dest="no_mutation", action="store_true", help="skip the online-mutation leg")
