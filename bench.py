@@ -267,7 +267,8 @@ def run_ours(args):
     if world > 1:
         dist.init_process_group("nccl", device_id=device)
     pk = peaks()
-    int8_peak = T.measure_int8_peak(local_rank) / 1e12           # TOP/s of this library's MMA form on this device
+    int8_peak = T.measure_int8_peak(local_rank) / 1e12           # TOP/s of this library's MMA form on this device: a burst
+    int8_peak_sustained = T.measure_int8_peak(local_rank, 1.5) / 1e12   # and what it sustains at the power limit
     n_total, nq = args.n, args.batch
     ng = ngroups(DIM, BITS)
 
@@ -526,8 +527,18 @@ def run_ours(args):
     tc_min = (33 if permute_dot else 8) if tc_min < 0 else tc_min       # library defaults
     small_kernel = ("scan_small_kernel (mma.sync, vectors on M)" if local.get_option(T.OPT_SMALL_SCAN) >= 0 else "scan_pd_kernel (mma.sync)") \
         if permute_dot else "scan_lut_kernel (CUDA cores)"
-    tc_kernel = "scan_tc_kernel (tcgen05)" if permute_dot else "scan_tc_kernel (tcgen05, one-hot u8 LUT)"
-    main_kernel = tc_kernel if tc_min > 0 and nq >= tc_min and ng % 4 == 0 else small_kernel
+    expanded_bytes = local.get_option(T.OPT_EXPANDED_BYTES)
+    if not permute_dot:
+        tc_kernel = "scan_tc_wide_kernel (tcgen05, one-hot u8 LUT)" if nq > 256 else "scan_tc_kernel (tcgen05, one-hot u8 LUT)"
+    elif expanded_bytes > 0:
+        tc_kernel = ("scan_tc_dense_pair_kernel (tcgen05 cta_group::2; int8 copy of the index and query weights by TMA)"
+                     if local.get_option(T.OPT_DENSE_PAIR) else "scan_tc_dense_kernel (tcgen05; int8 copy of the index and query weights by TMA)")
+    elif local.get_option(T.OPT_TC_PAIR):
+        tc_kernel = "scan_tc_pair_kernel (tcgen05 cta_group::2, codes expanded in the kernel)"
+    else:
+        tc_kernel = ("scan_tc_wide_kernel" if nq > 256 and local.get_option(T.OPT_TC_WIDE) else "scan_tc_kernel") + " (tcgen05, codes expanded in the kernel)"
+    main_uses_tc = tc_min > 0 and nq >= tc_min and ng % 4 == 0
+    main_kernel = tc_kernel if main_uses_tc else small_kernel
     cpu = None
     if world == 1 and not args.no_cpu:
         arm = CpuArm(n_total, nq)
@@ -550,12 +561,17 @@ def run_ours(args):
                      "frac": achieved_tops / int8_peak if achieved_tops and int8_peak else None,
                      "int8_peak_measured": int8_peak,
                      "peak_source": "tv_measure_int8_peak: back-to-back tcgen05 kind::i8 MMAs (M128 N256 K32) on shared-memory operands, "
-                                    "one CTA per SM, measured on this device in this run",
+                                    "one CTA per SM, best of three 2 ms launches on this device in this run (a burst: the clocks have "
+                                    "not yet met the power limit)",
+                     "int8_peak_sustained": int8_peak_sustained,
+                     "frac_of_sustained_int8_peak": achieved_tops / int8_peak_sustained if achieved_tops and int8_peak_sustained else None,
+                     "sustained_peak_source": "the same kernel launched back to back for 1.5 s, rate over the last 0.75 s (power-limited clocks)",
                      "bf16_peak": pk["tensor_tflops"], "frac_of_bf16_peak": achieved_tops / pk["tensor_tflops"] if achieved_tops else None,
                      "bf16_peak_source": f"{pk['source']} sustained cuBLAS bf16 (MEASURED_PEAKS.json); an int8 kernel may exceed it",
-                     # DRAM bytes per step: ncu measured 1.02x the code + scale bytes on a 524,288-vector capture
-                     # (the four query groups of a vector tile share it through L2); scaled by vectors
-                     "traffic": 1.02 * n_local * (ng + 4),
+                     # DRAM bytes per step: the int8 copy (or the codes) and the scales once; the query groups of a vector
+                     # tile share it through L2 (ncu on a 524,288-vector capture: 1.02x these bytes); scaled by vectors
+                     "traffic": 1.02 * n_local * (((DIM + 127) // 128 * 128 if expanded_bytes and permute_dot and main_uses_tc else ng) + 4),
+                     "expanded_copy_bytes": int(expanded_bytes),
                      "kernel": main_kernel, "launches_per_step": scan_launches / args.steps,
                      "note": "int8 multiply-adds counted as 2 ops"},
         "batch1": {"value": b1_steps / dt1, "unit": UNIT, "ms_per_query": dt1 / b1_steps * 1e3,

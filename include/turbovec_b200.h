@@ -343,6 +343,9 @@ const char *tv_version(void);
  * multiply-add counted as 2.  About 25 ms.  The roofline the large-batch permute-dot scan is reported against;
  * no reference counterpart. */
 int tv_measure_int8_peak(int device, double *ops_per_second);
+/* The same kernel launched back to back for `seconds` (at most 10): the rate over the second half of that time, i.e. what
+ * the device sustains once its power limit acts.  seconds <= 0: the burst figure of tv_measure_int8_peak. */
+int tv_measure_int8_peak_for(int device, double seconds, double *ops_per_second);
 /* Host-side evaluation of the quantisation grid that the pipelined ingest kernel builds from a codebook's
  * boundaries (`count` ascending values, at most 15): codes_out[i] = number of boundaries strictly below
  * values[i] (encode.rs:1447-1451), looked up exactly as the kernel does.  Returns TV_ERR_UNSUPPORTED when the

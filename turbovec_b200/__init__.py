@@ -475,12 +475,12 @@ class IdMapIndex(_Base):
 EMPTY_KEY = 0xFFFFFFFFFFFFFFFF
 
 
-def measure_int8_peak(device: int = 0) -> float:
-    """int8 tensor rate of `device` in ops/s for the library's MMA form (multiply-add = 2 ops), measured by a short
-    kernel that only issues MMAs."""
+def measure_int8_peak(device: int = 0, seconds: float = 0.0) -> float:
+    """int8 tensor rate of `device` in ops/s for the library's MMA form (multiply-add = 2 ops), measured by a kernel
+    that only issues MMAs: a burst of a few milliseconds (seconds = 0), or the rate sustained over `seconds`."""
     lib = _native.load()
     out = C.c_double(0.0)
-    rc = lib.tv_measure_int8_peak(int(device), C.byref(out))
+    rc = lib.tv_measure_int8_peak_for(int(device), float(seconds), C.byref(out))
     if rc != 0:
         raise RuntimeError(lib.tv_last_error(None).decode())
     return float(out.value)

@@ -89,6 +89,7 @@ SIGNATURES = {
     "tv_calibration": (C.c_int, [_H, C.c_void_p, C.c_void_p, C.c_size_t, _intp]),
     "tv_set_calibration": (C.c_int, [_H, C.c_size_t, C.c_void_p, C.c_void_p]),
     "tv_measure_int8_peak": (C.c_int, [C.c_int, C.POINTER(C.c_double)]),
+    "tv_measure_int8_peak_for": (C.c_int, [C.c_int, C.c_double, C.POINTER(C.c_double)]),
     "tv_launch_count": (C.c_uint64, [_H]),
     "tv_last_kernel_ms": (C.c_float, [_H]),
     "tv_last_main_kernel_ms": (C.c_float, [_H, _intp]),

@@ -2011,7 +2011,7 @@ int tv_search_device_noalloc(tv_index *h, const float *queries_device, size_t nq
     return TV_OK;
 }
 
-int tv_measure_int8_peak(int device, double *ops_per_second) {
+int tv_measure_int8_peak_for(int device, double seconds, double *ops_per_second) {
     if (!ops_per_second) return TV_ERR_INVALID_ARGUMENT;
     *ops_per_second = 0.0;
     cudaDeviceProp prop{};
@@ -2020,10 +2020,12 @@ int tv_measure_int8_peak(int device, double *ops_per_second) {
         g_create_error = "tv_measure_int8_peak: no such CUDA device";
         return TV_ERR_CUDA;
     }
-    *ops_per_second = measure_int8_peak(prop.multiProcessorCount, nullptr);
+    *ops_per_second = measure_int8_peak(prop.multiProcessorCount, seconds, nullptr);
     if (*ops_per_second <= 0.0) { g_create_error = "tv_measure_int8_peak: the measurement kernel failed"; return TV_ERR_CUDA; }
     return TV_OK;
 }
+
+int tv_measure_int8_peak(int device, double *ops_per_second) { return tv_measure_int8_peak_for(device, 0.0, ops_per_second); }
 
 int tv_prepare(tv_index *h) {
     if (!h) return TV_ERR_INVALID_ARGUMENT;

@@ -473,7 +473,9 @@ EncodeTiledFn encode_fn() {
 }  // namespace
 
 // Runs int8_peak_kernel on one CTA per SM and returns the int8 rate in ops/s (a multiply-add = 2 ops), 0 on failure.
-double measure_int8_peak(int sm_count, cudaStream_t s) {
+// seconds <= 0: the best of three launches of about 2 ms (a burst, before the power limit acts); otherwise launches back
+// to back for `seconds` and the rate over the second half of that time (what the device sustains at its power limit).
+double measure_int8_peak(int sm_count, double seconds, cudaStream_t s) {
     const int batches = 512;                                   // 32,768 MMAs of 2 * 128 * 256 * 32 ops per CTA
     const size_t smem = size_t(kATileBytes) + size_t(kMaxTileQueries) * kSlabK + 1024;
     if (cudaFuncSetAttribute(int8_peak_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, int(smem)) != cudaSuccess) return 0.0;
@@ -483,16 +485,31 @@ double measure_int8_peak(int sm_count, cudaStream_t s) {
     cudaEvent_t e0, e1;
     cudaEventCreate(&e0); cudaEventCreate(&e1);
     int8_peak_kernel<<<sm_count, 64, smem, s>>>(8, d_err);     // warm-up
+    const double ops_per_launch = 2.0 * 128 * 256 * 32 * 64.0 * batches * sm_count;
     double best = 0.0;
-    for (int rep = 0; rep < 3; ++rep) {
+    if (seconds <= 0.0) {
+        for (int rep = 0; rep < 3; ++rep) {
+            cudaEventRecord(e0, s);
+            int8_peak_kernel<<<sm_count, 64, smem, s>>>(batches, d_err);
+            cudaEventRecord(e1, s);
+            if (cudaStreamSynchronize(s) != cudaSuccess) { best = 0.0; break; }
+            float ms = 0.f;
+            cudaEventElapsedTime(&ms, e0, e1);
+            if (ms > 0.f) best = std::max(best, ops_per_launch / (double(ms) * 1e-3));
+        }
+    } else {
+        seconds = std::min(seconds, 10.0);
+        // a launch takes about 2 ms at full clocks: half the launches warm the device up, the other half are timed
+        const int half = std::max(4, int(seconds * 0.5 / 2.2e-3));
+        for (int i = 0; i < half; ++i) int8_peak_kernel<<<sm_count, 64, smem, s>>>(batches, d_err);
         cudaEventRecord(e0, s);
-        int8_peak_kernel<<<sm_count, 64, smem, s>>>(batches, d_err);
+        for (int i = 0; i < half; ++i) int8_peak_kernel<<<sm_count, 64, smem, s>>>(batches, d_err);
         cudaEventRecord(e1, s);
-        if (cudaStreamSynchronize(s) != cudaSuccess) { best = 0.0; break; }
-        float ms = 0.f;
-        cudaEventElapsedTime(&ms, e0, e1);
-        const double ops = 2.0 * 128 * 256 * 32 * 64.0 * batches * sm_count;
-        if (ms > 0.f) best = std::max(best, ops / (double(ms) * 1e-3));
+        if (cudaStreamSynchronize(s) == cudaSuccess) {
+            float ms = 0.f;
+            cudaEventElapsedTime(&ms, e0, e1);
+            if (ms > 0.f) best = ops_per_launch * half / (double(ms) * 1e-3);
+        }
     }
     uint32_t err = 0;
     cudaMemcpy(&err, d_err, 4, cudaMemcpyDeviceToHost);

@@ -139,7 +139,7 @@ bool scan_tc_pair_supported(int bits, int mode, int nq_total);
 cudaError_t launch_scan_tc_pair(const ScanParams &p, const int8_t *weights, int rows, int pitch, int sm_count, cudaStream_t s);
 // int8 rate (ops/s, multiply-add = 2) of back-to-back tcgen05 kind::i8 MMAs on shared-memory operands, one CTA per SM:
 // the tensor-pipe roofline of the permute-dot scan on this device.  0 on failure.
-double measure_int8_peak(int sm_count, cudaStream_t s);
+double measure_int8_peak(int sm_count, double seconds, cudaStream_t s);
 // Driver entry point cuTensorMapEncodeTiled (nullptr if the driver does not offer it).
 void *tensor_map_encoder();
 // Permute-dot scan for up to 16 queries in one launch (scan_small.cu): vectors on the M side of the warp-level MMA,
