@@ -799,3 +799,21 @@ def test_split_and_merged_level_lookups_agree_with_the_oracle(T, nq):
             assert idx.get_option(T.OPT_PD_SPLIT) == split
             s, i = idx.search(q, k, mask=m)
             assert np.array_equal(i, want_i) and np.array_equal(s.view(np.uint32), want_s.view(np.uint32))
+
+
+@pytest.mark.parametrize("n,dim,ties", [(40_000, 256, False), (3000, 200, True), (2, 64, False), (777, 1536, True)])
+def test_device_quantile_fit_equals_the_oracle(T, n, dim, ties):
+    """The two order statistics per coordinate of the TQ+ fit are selected on the device (radix select over the rotated
+    sample); shift and scale must equal the oracle's, which sorts on the host -- also with many equal values (rows
+    repeated, coordinates quantised to a few levels) and at the smallest sample."""
+    x = anisotropic(n, dim, seed=91)
+    if ties:
+        x = np.round(x * 3.0) / 3.0 + 1e-3                       # few distinct values per coordinate, no zero rows
+        x[n // 2:] = x[: n - n // 2]                              # and every row twice
+        x = np.ascontiguousarray(x, np.float32)
+    idx = T.TurboQuantIndex(dim, 4)
+    idx.calibrate(x)
+    shift, scale = idx.calibration()
+    o_shift, o_scale = O.fit_calibration(x, 4)
+    assert np.array_equal(shift.view(np.uint32), o_shift.view(np.uint32))
+    assert np.array_equal(scale.view(np.uint32), o_scale.view(np.uint32))

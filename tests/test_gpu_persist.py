@@ -78,3 +78,16 @@ def test_roundtrip_idmap_and_errors(T):
     lazy = T.TurboQuantIndex(None, 3)
     again = T.TurboQuantIndex.from_bytes(lazy.to_bytes())
     assert again.dim is None and again.bit_width == 3 and len(again) == 0
+
+
+def test_file_errors_are_os_errors(tmp_path):
+    """A path that cannot be opened or written is an I/O error (OSError, status 95), not an argument error."""
+    import turbovec_b200 as T
+    with pytest.raises(OSError):
+        T.TurboQuantIndex.load(str(tmp_path / "missing.tv"))
+    idx = T.TurboQuantIndex(64, 4)
+    idx.add(anisotropic(40, 64, seed=3))
+    with pytest.raises(OSError):
+        idx.write(str(tmp_path / "no_such_dir" / "x.tv"))
+    idx.write(str(tmp_path / "ok.tv"))
+    assert len(T.TurboQuantIndex.load(str(tmp_path / "ok.tv"))) == 40

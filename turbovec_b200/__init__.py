@@ -196,7 +196,10 @@ class _Base:
         return buf.tobytes()
 
     def write(self, path: str, *, durable: bool = True) -> None:
-        self._check(self._lib.tv_write(self._h, str(path).encode()))
+        rc = self._lib.tv_write(self._h, str(path).encode())
+        if rc == 95:                                              # file errors raise OSError, as the reference's binding does
+            raise OSError(f"{self._lib.tv_last_error(self._h).decode()}")
+        self._check(rc)
 
     def sync(self, path: str) -> None:
         """Persist the changes since the last sync to `path` incrementally (`sync`, turbovec-python/src/lib.rs:744,
@@ -237,6 +240,8 @@ class _Base:
         lib = _native.load()
         h = C.c_void_p()
         rc = lib.tv_load(str(path).encode(), cls._KIND, int(device), C.byref(h))
+        if rc == 95:
+            raise OSError(lib.tv_last_error(None).decode())
         if rc != 0:
             raise (RuntimeError if rc >= 91 else ValueError)(lib.tv_last_error(None).decode())
         return cls._adopt(h)

@@ -979,7 +979,8 @@ int enqueue_search(tv_index *h, cudaStream_t st, Marks *marks, const SearchScrat
     // Chunk 0 holds at most `cap` vectors, so every one of them may pass.  Later chunks grow so that the
     // expected number of candidates per query, k * |chunk| / |seen|, stays near cap / 4.
     // The tensor-memory scan pays for dense candidates (its epilogue re-reads a 32 x 32 tile of scores
-    // whenever one of them passes), so its chunks grow gently at first: x24, x10, then the list-capacity rule.
+    // whenever one of them passes), so its first three chunks grow x6 each (measured against x24, x10 and others on
+    // 10 M and 1.25 M vectors), then by the list-capacity rule.
     const size_t first = size_t(S.cap) / kBlock;
     const double growth = std::max(0.5, double(S.cap) / (4.0 * double(kk)));
     size_t begin = 0;
@@ -988,7 +989,7 @@ int enqueue_search(tv_index *h, cudaStream_t st, Marks *marks, const SearchScrat
         size_t len = first;
         if (!careful && begin > 0) {
             double g = growth;
-            if (plan.use_tc) g = std::min(g, stage == 1 ? 24.0 : (stage == 2 ? 10.0 : g));
+            if (plan.use_tc && stage <= 3) g = std::min(g, 6.0);
             len = std::max<size_t>(first, size_t(double(begin) * g));
             if (begin + len + len / 2 >= n_blocks) len = n_blocks - begin;   // no short tail chunk
         }
@@ -1453,7 +1454,11 @@ void tv_error_detail(const tv_index *h, size_t *vector_index, size_t *coord_inde
     if (id) *id = h->err_id;
 }
 
-size_t tv_len(const tv_index *h) { return h ? h->n : 0; }
+size_t tv_len(const tv_index *h) {
+    if (!h) return 0;
+    std::shared_lock<std::shared_mutex> lock(const_cast<tv_index *>(h)->mu);
+    return h->n;
+}
 size_t tv_dim(const tv_index *h) { return h ? h->dim : 0; }
 int tv_bit_width(const tv_index *h) { return h ? h->bits : 0; }
 int tv_kind(const tv_index *h) { return h ? h->kind : -1; }
@@ -1657,12 +1662,14 @@ int tv_set_row(tv_index *h, size_t slot, const uint8_t *groups, size_t count, fl
 
 int tv_contains(const tv_index *h, uint64_t id, int *present) {
     if (!h || !present) return TV_ERR_INVALID_ARGUMENT;
+    std::shared_lock<std::shared_mutex> lock(const_cast<tv_index *>(h)->mu);      // the tables move under a concurrent add / remove
     *present = h->id_to_slot.count(id) ? 1 : 0;
     return TV_OK;
 }
 
 int tv_ids(const tv_index *h, uint64_t *ids_out, size_t capacity) {
     if (!h || (!ids_out && capacity)) return TV_ERR_INVALID_ARGUMENT;
+    std::shared_lock<std::shared_mutex> lock(const_cast<tv_index *>(h)->mu);
     if (capacity < h->slot_to_id.size()) return TV_ERR_INVALID_ARGUMENT;
     std::copy(h->slot_to_id.begin(), h->slot_to_id.end(), ids_out);
     return TV_OK;
@@ -2135,6 +2142,7 @@ uint32_t tv_crc32c(const uint8_t *data, size_t len) { return crc32c_split(data, 
 
 size_t tv_image_bytes(const tv_index *h) {
     if (!h) return 0;
+    std::shared_lock<std::shared_mutex> lock(const_cast<tv_index *>(h)->mu);
     V7Parts p;
     p.kind = h->kind; p.bits = h->bits; p.dim = h->dim; p.n = h->n; p.shift = h->shift;
     return v7_image_len(p);
@@ -2224,7 +2232,7 @@ int tv_write(const tv_index *hc, const char *path) {
     int rc = tv_to_bytes(h, img.data(), img.size());
     if (rc != TV_OK) return rc;
     std::string err;
-    if (!v7_write_file_atomic(path, img.data(), img.size(), err)) return fail(h, TV_ERR_INVALID_ARGUMENT, err);
+    if (!v7_write_file_atomic(path, img.data(), img.size(), err)) return fail(h, TV_ERR_IO, err);
     return TV_OK;
 }
 
@@ -2232,14 +2240,14 @@ int tv_load(const char *path, int expect_kind, int device, tv_index **out) {
     tv_index *h = nullptr;
     if (!path || !out) return fail(h, TV_ERR_INVALID_ARGUMENT, "null argument");
     FILE *f = std::fopen(path, "rb");
-    if (!f) return fail(h, TV_ERR_INVALID_ARGUMENT, std::string("cannot open ") + path);
+    if (!f) return fail(h, TV_ERR_IO, std::string("cannot open ") + path);
     std::fseek(f, 0, SEEK_END);
     const long sz = std::ftell(f);
     std::fseek(f, 0, SEEK_SET);
     std::vector<uint8_t> buf(sz > 0 ? size_t(sz) : 0);
     const bool ok = std::fread(buf.data(), 1, buf.size(), f) == buf.size();
     std::fclose(f);
-    if (!ok) return fail(h, TV_ERR_INVALID_ARGUMENT, std::string("cannot read ") + path);
+    if (!ok) return fail(h, TV_ERR_IO, std::string("cannot read ") + path);
     return index_from_image(buf.data(), buf.size(), expect_kind, device, out, path);
 }
 
@@ -2431,8 +2439,8 @@ int tv_calibration(const tv_index *h, float *shift_out, float *scale_out, size_t
     return TV_OK;
 }
 
-// TQ+ fit: encode::fit_calibration (encode.rs:470-480) = rotate the unit-normalised sample on the device, then
-// per coordinate map the empirical [p_lo, p_hi] quantiles onto the codebook's outer centroids
+// TQ+ fit: encode::fit_calibration (encode.rs:470-480) = rotate the unit-normalised sample on the device, select
+// the two order statistics per coordinate there too, then map the empirical [p_lo, p_hi] quantiles onto the codebook's outer centroids
 // (tqplus_anchor encode.rs:364-369, compute_tqplus_calibration :737-857).  Validation order of lib.rs:2599-2640.
 int tv_calibrate(tv_index *h, const float *sample, size_t n, size_t dim) {
     if (!h || (!sample && n)) return TV_ERR_INVALID_ARGUMENT;
@@ -2454,11 +2462,17 @@ int tv_calibrate(tv_index *h, const float *sample, size_t n, size_t dim) {
     const int V = ingest_vectors_per_pass(int(dim), h->ngroups, h->smem_limit);
     if (V == 0) { undo(); return fail(h, TV_ERR_UNSUPPORTED, "dim too large for the ingest kernel's shared memory"); }
 
-    std::vector<float> rotated(n * dim);
+    // The rotated sample stays on the device when it fits (a quarter of the free memory at most) and the two order
+    // statistics per coordinate are selected there (quantile.cu); a larger sample comes back to the host chunk by chunk
+    // and is selected with std::nth_element.
+    size_t free_b = 0, total_b = 0;
+    TV_CUDA(cudaMemGetInfo(&free_b, &total_b));
+    const bool on_device = n * dim * 4 <= free_b / 4 && n <= 0xffffffffull;
+    std::vector<float> rotated(on_device ? 0 : n * dim);
     DeviceArray<float> d_rot;
     const size_t chunk_rows = std::max<size_t>(1, std::min<size_t>(n, (size_t(128) << 20) / (dim * 4)));
     TV_CUDA(h->d_stage.reserve(chunk_rows * dim));
-    TV_CUDA(d_rot.reserve(chunk_rows * dim));
+    TV_CUDA(d_rot.reserve((on_device ? n : chunk_rows) * dim));
     h->h_flags->first_invalid = ~0ull;
     TV_CUDA(cudaMemcpyAsync(&h->d_flags->first_invalid, &h->h_flags->first_invalid, 8, cudaMemcpyHostToDevice, h->stream));
     IngestParams p{};
@@ -2466,15 +2480,15 @@ int tv_calibrate(tv_index *h, const float *sample, size_t n, size_t dim) {
     p.perm0 = h->d_perm.ptr; p.perm1 = h->d_perm.ptr + dim; p.inv_sqrt_block = h->rot.inv_sqrt_block;
     p.boundaries = h->d_codebook.ptr; p.centroids = h->d_codebook.ptr + 16;
     p.first_invalid = &h->d_flags->first_invalid;
-    p.rot_out = d_rot.ptr;
     for (size_t done = 0; done < n; done += chunk_rows) {
         const size_t rows = std::min(chunk_rows, n - done);
         TV_CUDA(cudaMemcpyAsync(h->d_stage.ptr, sample + done * dim, rows * dim * 4, cudaMemcpyHostToDevice, h->stream));
         p.x = h->d_stage.ptr; p.n = int64_t(rows); p.slot0 = 0; p.row_base = int64_t(done);
+        p.rot_out = on_device ? d_rot.ptr + done * dim : d_rot.ptr;
         TV_CUDA(launch_ingest(p, V, h->stream));
         h->launches++;
-        TV_CUDA(cudaMemcpyAsync(rotated.data() + done * dim, d_rot.ptr, rows * dim * 4, cudaMemcpyDeviceToHost, h->stream));
-        TV_CUDA(cudaStreamSynchronize(h->stream));
+        if (!on_device) TV_CUDA(cudaMemcpyAsync(rotated.data() + done * dim, d_rot.ptr, rows * dim * 4, cudaMemcpyDeviceToHost, h->stream));
+        TV_CUDA(cudaStreamSynchronize(h->stream));           // the staging buffer is reused by the next chunk
     }
 
     // anchor: probability mass inside the outermost centroid (encode.rs:364-369)
@@ -2485,14 +2499,26 @@ int tv_calibrate(tv_index *h, const float *sample, size_t n, size_t dim) {
     const float qc_lo = -c_outer, qc_span = c_outer - qc_lo;
     const size_t lo_idx = size_t(double(n) * p_lo);
     const size_t hi_idx = std::max(std::min(size_t(double(n) * p_hi), n - 1), lo_idx + 1);
-    std::vector<float> shift(dim, 0.f), scale(dim, 1.f), col(n);
+    std::vector<float> shift(dim, 0.f), scale(dim, 1.f), col(on_device ? 0 : n), qe(2 * dim);
+    if (on_device) {
+        DeviceArray<float> d_q;
+        TV_CUDA(d_q.reserve(2 * dim));
+        TV_CUDA(launch_quantile_pair(d_rot.ptr, int64_t(n), int(dim), int64_t(lo_idx), int64_t(hi_idx), d_q.ptr, d_q.ptr + dim, h->stream));
+        h->launches++;
+        TV_CUDA(cudaMemcpyAsync(qe.data(), d_q.ptr, 2 * dim * 4, cudaMemcpyDeviceToHost, h->stream));
+        TV_CUDA(cudaStreamSynchronize(h->stream));
+    } else {
+        for (size_t d = 0; d < dim; ++d) {
+            for (size_t i = 0; i < n; ++i) col[i] = rotated[i * dim + d];
+            std::nth_element(col.begin(), col.begin() + lo_idx, col.end());
+            qe[d] = col[lo_idx];
+            std::nth_element(col.begin() + lo_idx + 1, col.begin() + hi_idx, col.end());
+            qe[dim + d] = col[hi_idx];
+        }
+    }
     bool identity = true;
     for (size_t d = 0; d < dim; ++d) {
-        for (size_t i = 0; i < n; ++i) col[i] = rotated[i * dim + d];
-        std::nth_element(col.begin(), col.begin() + lo_idx, col.end());
-        const float qe_lo = col[lo_idx];
-        std::nth_element(col.begin() + lo_idx + 1, col.begin() + hi_idx, col.end());
-        const float qe_hi = col[hi_idx];
+        const float qe_lo = qe[d], qe_hi = qe[dim + d];
         const float qe_span = qe_hi - qe_lo;
         if (qe_span > 1e-6f) {                                       // encode.rs:846-850
             scale[d] = qc_span / qe_span;

@@ -51,6 +51,9 @@ struct ReencodeParams {
     const float *new_shift, *new_scale, *new_inv;
 };
 cudaError_t launch_reencode(const ReencodeParams &p, cudaStream_t stream);
+// Two order statistics per column of a rows x dim matrix on the device (quantile.cu): the TQ+ fit's quantiles.
+cudaError_t launch_quantile_pair(const float *rot, int64_t n, int dim, int64_t lo_rank, int64_t hi_rank, float *q_lo, float *q_hi,
+                                 cudaStream_t stream);
 
 // Pipelined form (ingest_fast.cu) for whole code blocks: p.slot0 a multiple of 32, no calibration, no
 // rotate-only mode, x 16-byte aligned, dim one of the instantiated sizes, shared memory within the limit.
