@@ -568,9 +568,10 @@ def run_ours(args):
                      "sustained_peak_source": "the same kernel launched back to back for 1.5 s, rate over the last 0.75 s (power-limited clocks)",
                      "bf16_peak": pk["tensor_tflops"], "frac_of_bf16_peak": achieved_tops / pk["tensor_tflops"] if achieved_tops else None,
                      "bf16_peak_source": f"{pk['source']} sustained cuBLAS bf16 (MEASURED_PEAKS.json); an int8 kernel may exceed it",
-                     # DRAM bytes per step: the int8 copy (or the codes) and the scales once; the query groups of a vector
-                     # tile share it through L2 (ncu on a 524,288-vector capture: 1.02x these bytes); scaled by vectors
-                     "traffic": 1.02 * n_local * (((DIM + 127) // 128 * 128 if expanded_bytes and permute_dot and main_uses_tc else ng) + 4),
+                     # DRAM bytes per step: the int8 copy (or the codes) and the scales, read once; the query groups of a
+                     # vector tile share them through L2.  ncu on 421,888 vectors of a 524,288-vector index: 1.003x these
+                     # bytes for the scan over the int8 copy (1.02x for the scans over the codes); scaled by vectors
+                     "traffic": (1.003 * ((DIM + 127) // 128 * 128 + 4) if expanded_bytes and permute_dot and main_uses_tc else 1.02 * (ng + 4)) * n_local,
                      "expanded_copy_bytes": int(expanded_bytes),
                      "kernel": main_kernel, "launches_per_step": scan_launches / args.steps,
                      "note": "int8 multiply-adds counted as 2 ops"},

@@ -201,9 +201,6 @@ scan_tc_kernel(ScanParams p, const __grid_constant__ CUtensorMap wmap, int n_sla
             constexpr int kColsPerHalf = kTileQueries >= 64 ? kTileQueries / 2 : kTileQueries;
             const int cbase = half * kColsPerHalf;
             const bool has_columns = cbase < kTileQueries;
-            const float4 *ps = reinterpret_cast<const float4 *>(&sh->qscale[pb][cbase]);
-            const float4 *pbias = reinterpret_cast<const float4 *>(&sh->qbias[pb][cbase]);
-            const float4 *pt = reinterpret_cast<const float4 *>(&sh->qthr[pb][cbase]);
 #pragma unroll
             for (int m = 0; m < MT; ++m) {
                 const uint32_t taddr = tmem_base + (uint32_t(quarter * 32) << 16) + uint32_t(buf * MT + m) * kTileQueries + uint32_t(cbase);
@@ -230,51 +227,40 @@ scan_tc_kernel(ScanParams p, const __grid_constant__ CUtensorMap wmap, int n_sla
                         }
                         continue;
                     }
-                    // one integer compare per column dismisses the piece unless some column could be a candidate
+                    // one integer compare per column dismisses the piece unless some column could be a candidate; the
+                    // columns are tracked in four runs of 8, and only the runs that some lane flags are looked at again
+                    uint32_t runs = 0;
                     {
                         const int4 *pi = reinterpret_cast<const int4 *>(&sh->ibound[pb][cbase + c0]);
-                        bool may = false;
 #pragma unroll
                         for (int j4 = 0; j4 < 8; ++j4) {
                             const int4 b = pi[j4];
-                            may |= int(acc[4 * j4 + 0]) >= b.x;
-                            may |= int(acc[4 * j4 + 1]) >= b.y;
-                            may |= int(acc[4 * j4 + 2]) >= b.z;
-                            may |= int(acc[4 * j4 + 3]) >= b.w;
+                            const bool may = (int(acc[4 * j4 + 0]) >= b.x) | (int(acc[4 * j4 + 1]) >= b.y) | (int(acc[4 * j4 + 2]) >= b.z) |
+                                             (int(acc[4 * j4 + 3]) >= b.w);
+                            runs |= uint32_t(may) << (j4 >> 1);
                         }
-                        if (!__any_sync(kFullMask, may && live[m])) continue;
+                        if (!(live[m])) runs = 0;
                     }
-                    // survivors: four instructions per score, the comparison folded into one predicate
-                    bool any = false;
-#pragma unroll
-                    for (int j4 = 0; j4 < 8; ++j4) {
-                        const float4 s4 = ps[(c0 >> 2) + j4], b4 = pbias[(c0 >> 2) + j4], t4 = pt[(c0 >> 2) + j4];
-                        any |= final_score<ONEHOT>(fused, acc[4 * j4 + 0], s4.x, b4.x, vs[m]) >= t4.x;
-                        any |= final_score<ONEHOT>(fused, acc[4 * j4 + 1], s4.y, b4.y, vs[m]) >= t4.y;
-                        any |= final_score<ONEHOT>(fused, acc[4 * j4 + 2], s4.z, b4.z, vs[m]) >= t4.z;
-                        any |= final_score<ONEHOT>(fused, acc[4 * j4 + 3], s4.w, b4.w, vs[m]) >= t4.w;
-                    }
-                    any = any && live[m];
-                    // rare, warp-uniform: some lane has a score at or above its query's k-th score.  Re-read the
-                    // 32 columns in pieces of 8 and append the keys that really beat the k-th key.
-                    if (__any_sync(kFullMask, any)) {
+                    const uint32_t warp_runs = __reduce_or_sync(kFullMask, runs);
+                    if (warp_runs == 0) continue;
+                    // rare, warp-uniform: re-read the flagged runs and score their columns exactly
 #pragma unroll 1
-                        for (int c1 = 0; c1 < 32; c1 += 8) {
-                            uint32_t a8[8];
-                            tmem_ld8(taddr + c0 + c1, a8);
-                            asm volatile("tcgen05.wait::ld.sync.aligned;" ::: "memory");
-                            if (any) {
+                    for (int c1 = 0; c1 < 32; c1 += 8) {
+                        if (!((warp_runs >> (c1 >> 3)) & 1u)) continue;
+                        uint32_t a8[8];
+                        tmem_ld8(taddr + c0 + c1, a8);
+                        asm volatile("tcgen05.wait::ld.sync.aligned;" ::: "memory");
+                        if ((runs >> (c1 >> 3)) & 1u) {
 #pragma unroll
-                                for (int e = 0; e < 8; ++e) {
-                                    const int c = cbase + c0 + c1 + e;
-                                    const float score = final_score<ONEHOT>(fused, a8[e], sh->qscale[pb][c], sh->qbias[pb][c], vs[m]);
-                                    if (score >= sh->qthr[pb][c]) {
-                                        const int ql = qg * kTileQueries + c;
-                                        const uint64_t key = make_key(score, uint32_t(slot[m]));
-                                        if (key < p.cb.thr[ql] && (p.cb.lo == nullptr || key >= p.cb.lo[ql])) {
-                                            const uint32_t at = atomicAdd(&p.cb.cnt[ql], 1u);
-                                            if (at < uint32_t(p.cb.cap)) p.cb.cand[size_t(ql) * p.cb.cap + at] = key;
-                                        }
+                            for (int e = 0; e < 8; ++e) {
+                                const int c = cbase + c0 + c1 + e;
+                                const float score = final_score<ONEHOT>(fused, a8[e], sh->qscale[pb][c], sh->qbias[pb][c], vs[m]);
+                                if (score >= sh->qthr[pb][c]) {
+                                    const int ql = qg * kTileQueries + c;
+                                    const uint64_t key = make_key(score, uint32_t(slot[m]));
+                                    if (key < p.cb.thr[ql] && (p.cb.lo == nullptr || key >= p.cb.lo[ql])) {
+                                        const uint32_t at = atomicAdd(&p.cb.cnt[ql], 1u);
+                                        if (at < uint32_t(p.cb.cap)) p.cb.cand[size_t(ql) * p.cb.cap + at] = key;
                                     }
                                 }
                             }

@@ -242,9 +242,6 @@ scan_tc_dense_kernel(ScanParams p, const __grid_constant__ CUtensorMap amap, con
                 // warp-uniform outcome; a warp whose wait ran out still meets the others at the barrier below
                 ok = __all_sync(kFullMask, mbar_wait(&sh->d_full[half], used & 1, p.cb.error));
                 asm volatile("tcgen05.fence::after_thread_sync;" ::: "memory");
-                const float4 *ps = reinterpret_cast<const float4 *>(qscale);
-                const float4 *pbias = reinterpret_cast<const float4 *>(qbias);
-                const float4 *pt = reinterpret_cast<const float4 *>(qthr);
                 const uint32_t taddr = tmem_base + (uint32_t(quarter * 32) << 16) + uint32_t(half) * kTileQueries;
                 for (int c0 = 0; c0 < (ok ? kTileQueries : 0); c0 += 32) {
                     uint32_t acc[32];
@@ -266,48 +263,40 @@ scan_tc_dense_kernel(ScanParams p, const __grid_constant__ CUtensorMap amap, con
                         }
                         continue;
                     }
-                    // one integer compare per column dismisses the piece unless some column could be a candidate
+                    // one integer compare per column dismisses the piece unless some column could be a candidate; the
+                    // columns are tracked in four runs of 8, and only the runs that some lane flags are looked at again
+                    uint32_t runs = 0;
                     {
                         const int4 *pi = reinterpret_cast<const int4 *>(sh->ibound + half * kTileQueries + c0);
-                        bool may = false;
 #pragma unroll
                         for (int j4 = 0; j4 < 8; ++j4) {
                             const int4 b = pi[j4];
-                            may |= int(acc[4 * j4 + 0]) >= b.x;
-                            may |= int(acc[4 * j4 + 1]) >= b.y;
-                            may |= int(acc[4 * j4 + 2]) >= b.z;
-                            may |= int(acc[4 * j4 + 3]) >= b.w;
+                            const bool may = (int(acc[4 * j4 + 0]) >= b.x) | (int(acc[4 * j4 + 1]) >= b.y) | (int(acc[4 * j4 + 2]) >= b.z) |
+                                             (int(acc[4 * j4 + 3]) >= b.w);
+                            runs |= uint32_t(may) << (j4 >> 1);
                         }
-                        if (!__any_sync(kFullMask, may && live)) continue;
+                        if (!(live)) runs = 0;
                     }
-                    bool any = false;
-#pragma unroll
-                    for (int j4 = 0; j4 < 8; ++j4) {
-                        const float4 s4 = ps[(c0 >> 2) + j4], b4 = pbias[(c0 >> 2) + j4], t4 = pt[(c0 >> 2) + j4];
-                        any |= final_score<ONEHOT>(fused, acc[4 * j4 + 0], s4.x, b4.x, vs) >= t4.x;
-                        any |= final_score<ONEHOT>(fused, acc[4 * j4 + 1], s4.y, b4.y, vs) >= t4.y;
-                        any |= final_score<ONEHOT>(fused, acc[4 * j4 + 2], s4.z, b4.z, vs) >= t4.z;
-                        any |= final_score<ONEHOT>(fused, acc[4 * j4 + 3], s4.w, b4.w, vs) >= t4.w;
-                    }
-                    any = any && live;
-                    if (__any_sync(kFullMask, any)) {          // rare, warp-uniform: re-read in pieces of 8 and append
+                    const uint32_t warp_runs = __reduce_or_sync(kFullMask, runs);
+                    if (warp_runs == 0) continue;
+                    // rare, warp-uniform: re-read the flagged runs and score their columns exactly
 #pragma unroll 1
-                        for (int c1 = 0; c1 < 32; c1 += 8) {
-                            uint32_t a8[8];
-                            tmem_ld8(taddr + c0 + c1, a8);
-                            asm volatile("tcgen05.wait::ld.sync.aligned;" ::: "memory");
-                            if (any) {
+                    for (int c1 = 0; c1 < 32; c1 += 8) {
+                        if (!((warp_runs >> (c1 >> 3)) & 1u)) continue;
+                        uint32_t a8[8];
+                        tmem_ld8(taddr + c0 + c1, a8);
+                        asm volatile("tcgen05.wait::ld.sync.aligned;" ::: "memory");
+                        if ((runs >> (c1 >> 3)) & 1u) {
 #pragma unroll
-                                for (int e = 0; e < 8; ++e) {
-                                    const int c = c0 + c1 + e;
-                                    const float score = final_score<ONEHOT>(fused, a8[e], qscale[c], qbias[c], vs);
-                                    if (score >= qthr[c]) {
-                                        const int ql = qg * kTileQueries + c;
-                                        const uint64_t key = make_key(score, uint32_t(slot));
-                                        if (key < p.cb.thr[ql] && (p.cb.lo == nullptr || key >= p.cb.lo[ql])) {
-                                            const uint32_t at = atomicAdd(&p.cb.cnt[ql], 1u);
-                                            if (at < uint32_t(p.cb.cap)) p.cb.cand[size_t(ql) * p.cb.cap + at] = key;
-                                        }
+                            for (int e = 0; e < 8; ++e) {
+                                const int c = c0 + c1 + e;
+                                const float score = final_score<ONEHOT>(fused, a8[e], qscale[c], qbias[c], vs);
+                                if (score >= qthr[c]) {
+                                    const int ql = qg * kTileQueries + c;
+                                    const uint64_t key = make_key(score, uint32_t(slot));
+                                    if (key < p.cb.thr[ql] && (p.cb.lo == nullptr || key >= p.cb.lo[ql])) {
+                                        const uint32_t at = atomicAdd(&p.cb.cnt[ql], 1u);
+                                        if (at < uint32_t(p.cb.cap)) p.cb.cand[size_t(ql) * p.cb.cap + at] = key;
                                     }
                                 }
                             }
