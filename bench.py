@@ -524,7 +524,7 @@ def run_ours(args):
 
     tc_min = local.get_option(T.OPT_MMA_MIN_BATCH)
     permute_dot = BITS == 4 and ng % 4 == 0
-    tc_min = (33 if permute_dot else 8) if tc_min < 0 else tc_min       # library defaults
+    tc_min = ((17 if local.get_option(T.OPT_EXPANDED_BYTES) > 0 else 33) if permute_dot else 8) if tc_min < 0 else tc_min       # library defaults
     small_kernel = ("scan_small_kernel (mma.sync, vectors on M)" if local.get_option(T.OPT_SMALL_SCAN) >= 0 else "scan_pd_kernel (mma.sync)") \
         if permute_dot else "scan_lut_kernel (CUDA cores)"
     expanded_bytes = local.get_option(T.OPT_EXPANDED_BYTES)

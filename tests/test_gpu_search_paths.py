@@ -68,7 +68,7 @@ def test_small_scan_many_chunks_and_recovery(T):
 
 
 # ------------------------------------------------------------------ tensor-memory scan on CTA pairs
-@pytest.mark.parametrize("dim,n,nq", [(1536, 5003, 70), (1536, 4100, 300), (256, 4100, 257), (200, 9000, 1024), (1536, 40_000, 129),
+@pytest.mark.parametrize("dim,n,nq", [(1536, 5003, 70), (1536, 4100, 300), (256, 4100, 257), (200, 9000, 1024), (1536, 40_000, 129), (512, 7000, 17),
                                       (64, 300_000, 65), (256, 20_000, 513), (128, 9000, 770)])
 @pytest.mark.parametrize("form", ["dense", "dense1", "pair", "wide", "narrow"])
 def test_pair_tensor_scan_matches_oracle(T, dim, n, nq, form):

@@ -882,7 +882,14 @@ int plan_scan(tv_index *h, int mode, size_t nq, bool allow_tc, ScanPlan &plan) {
     // measured on 1.25 M and 10 M x 1536 4-bit: mma.sync 0.67 / 3.6 ms up to 32 queries, 0.89 / 5.1 ms from 33 on,
     // tcgen05 0.83 / 5.1 ms flat; on 1 M x 3072 2-bit the CUDA-core LUT scan costs 0.5 ms per query beyond 4,
     // tcgen05 4.2 ms flat
-    const int64_t tc_from = h->mma_min_batch >= 0 ? h->mma_min_batch : (mode == TV_SCORE_PERMUTE_DOT ? 33 : 8);
+    // with the int8 copy of the index the tensor-memory scan is bound by reading it (2.85 ms at 33 queries on 10 M x 1536)
+    // and beats the mma.sync scan of 17 - 32 queries (3.1 ms); without the copy it expands codes and does not (4.7 ms)
+    bool copy_expected = false;
+    if (mode == TV_SCORE_PERMUTE_DOT && h->tc_expanded != 0 && !h->tc_pair) {
+        std::lock_guard<std::mutex> g(h->expanded.mu);
+        copy_expected = h->tc_expanded == 2 || h->expanded.refused_at_cap != h->code_blocks_cap * kBlock;
+    }
+    const int64_t tc_from = h->mma_min_batch >= 0 ? h->mma_min_batch : (mode == TV_SCORE_PERMUTE_DOT ? (copy_expected ? 17 : 33) : 8);
     plan.use_tc = allow_tc && tc_from > 0 && int64_t(nq) >= tc_from && scan_tc_supported(h->bits, mode, ng);
     if (mode != TV_SCORE_PERMUTE_DOT) {
         plan.lut_width = scan_lut_width(ng, h->smem_limit);
