@@ -283,7 +283,7 @@ def run_ours(args):
         idx = ShardedIdMapIndex(DIM, BITS, device=device)
         local = idx.local
     for opt, val in ((T.OPT_MMA_MIN_BATCH, args.tc_min_batch), (T.OPT_INGEST_PIPELINE, args.ingest_pipeline),
-                     (T.OPT_SMALL_SCAN, args.small_scan), (T.OPT_TC_PAIR, args.tc_pair), (T.OPT_TC_WIDE, args.tc_wide),
+                     (T.OPT_SMALL_SCAN, args.small_scan), (T.OPT_TC_WIDE, args.tc_wide),
                      (T.OPT_TC_EXPANDED, args.tc_expanded), (T.OPT_DENSE_PAIR, args.dense_pair)):
         if val is not None:
             local.set_option(opt, val)
@@ -533,8 +533,6 @@ def run_ours(args):
     elif expanded_bytes > 0:
         tc_kernel = ("scan_tc_dense_pair_kernel (tcgen05 cta_group::2; int8 copy of the index and query weights by TMA)"
                      if local.get_option(T.OPT_DENSE_PAIR) else "scan_tc_dense_kernel (tcgen05; int8 copy of the index and query weights by TMA)")
-    elif local.get_option(T.OPT_TC_PAIR):
-        tc_kernel = "scan_tc_pair_kernel (tcgen05 cta_group::2, codes expanded in the kernel)"
     else:
         tc_kernel = ("scan_tc_wide_kernel" if nq > 256 and local.get_option(T.OPT_TC_WIDE) else "scan_tc_kernel") + " (tcgen05, codes expanded in the kernel)"
     main_uses_tc = tc_min > 0 and nq >= tc_min and ng % 4 == 0
@@ -714,7 +712,6 @@ def main():
     ap.add_argument("--ingest-pipeline", type=int, default=None, choices=[0, 1, 2],
                     help="TV_OPT_INGEST_PIPELINE: 0 = block-at-a-time ingest kernel only (default: library default, 1)")
     ap.add_argument("--small-scan", type=int, default=None, help="TV_OPT_SMALL_SCAN variant (-1 = scan_pd_kernel)")
-    ap.add_argument("--tc-pair", type=int, default=None, choices=[0, 1], help="TV_OPT_TC_PAIR: tensor-memory scan on CTA pairs")
     ap.add_argument("--tc-wide", type=int, default=None, choices=[0, 1], help="TV_OPT_TC_WIDE: two query groups per expanded code slab")
     ap.add_argument("--tc-expanded", type=int, default=None, choices=[0, 1, 2],
                     help="TV_OPT_TC_EXPANDED: large permute-dot batches scan an int8 copy of the index (0 never, 1 if it fits, 2 always)")

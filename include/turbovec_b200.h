@@ -111,9 +111,6 @@ enum {
                                  * bit 2: swizzled tensor copies instead of plain bulk copies; default 5).  Results are identical. */
     TV_OPT_FAIL_NEXT = 8,       /* testing: the n-th guarded device allocation / upload from now on reports an
                                  * out-of-memory failure instead of running (1 = the next one); 0 disarms */
-    TV_OPT_TC_PAIR = 9,         /* 1: permute-dot batches of more than 64 queries run the tensor-memory scan on pairs of
-                                 * CTAs (tcgen05 cta_group::2: each SM loads half of every query slab); 0: one CTA per
-                                 * work item (default: it measured slower).  Results are identical. */
     TV_OPT_TC_WIDE = 10,        /* 1 (default): batches of more than 256 queries run the tensor-memory scan whose work items
                                  * take two query groups per expanded code slab; 0: one group per item.  Identical results. */
     TV_OPT_TC_EXPANDED = 11,    /* permute-dot batches on the tensor-memory scan read an int8 copy of the index (one level per

@@ -67,15 +67,14 @@ def test_small_scan_many_chunks_and_recovery(T):
         assert np.array_equal(i, want[1]) and np.array_equal(s, want[0])
 
 
-# ------------------------------------------------------------------ tensor-memory scan on CTA pairs
+# ------------------------------------------------------------------ the forms of the tensor-memory scan
 @pytest.mark.parametrize("dim,n,nq", [(1536, 5003, 70), (1536, 4100, 300), (256, 4100, 257), (200, 9000, 1024), (1536, 40_000, 129), (512, 7000, 17),
                                       (64, 300_000, 65), (256, 20_000, 513), (128, 9000, 770)])
-@pytest.mark.parametrize("form", ["dense", "dense1", "pair", "wide", "narrow"])
-def test_pair_tensor_scan_matches_oracle(T, dim, n, nq, form):
+@pytest.mark.parametrize("form", ["dense", "dense1", "wide", "narrow"])
+def test_tensor_scan_forms_match_oracle(T, dim, n, nq, form):
     """The forms of the tensor-memory scan: over the int8 copy of the index (both operands by TMA) on CTA pairs (the
-    default) and on single CTAs ("dense1"), and over the codes on CTA pairs (tcgen05 cta_group::2, work items of 256 vectors x 256 queries), with two query groups
-    per expanded slab (batches above 256 queries; 513 and 770 queries end in an item of one group), with one group per
-    item.  Odd numbers of 128-vector tiles, several chunks, partial query groups, masks."""
+    default) and on single CTAs ("dense1"), and over the codes with two query groups per expanded slab ("wide": batches
+    above 256 queries; 513 and 770 queries end in an item of one group) or with one group per item ("narrow").  Odd numbers of 128-vector tiles, several chunks, partial query groups, masks."""
     x = anisotropic(n, dim, seed=57)
     q = anisotropic(nq, dim, seed=57, offset=31)
     pre = oracle_index(x, 4)
@@ -83,7 +82,6 @@ def test_pair_tensor_scan_matches_oracle(T, dim, n, nq, form):
     idx.add(x)
     idx.set_option(T.OPT_TC_EXPANDED, 2 if form.startswith("dense") else 0)
     idx.set_option(T.OPT_DENSE_PAIR, 1 if form == "dense" else 0)
-    idx.set_option(T.OPT_TC_PAIR, 1 if form == "pair" else 0)
     idx.set_option(T.OPT_TC_WIDE, 1 if form == "wide" else 0)
     mask = np.random.default_rng(6).random(n) < 0.2
     for k in (10, 100):

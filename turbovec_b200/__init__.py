@@ -12,7 +12,7 @@ import numpy as np
 
 from . import _native
 from ._native import (OPT_FAIL_NEXT, OPT_FORCE_CAREFUL, OPT_INGEST_PIPELINE, OPT_MMA_MIN_BATCH, OPT_PD_SPLIT, OPT_SCORE_MODE, OPT_SMALL_SCAN,
-                      OPT_DENSE_PAIR, OPT_EXPANDED_BYTES, OPT_TC_EXPANDED, OPT_TC_PAIR, OPT_TC_TILES, OPT_TC_WIDE, SCORE_AUTO, SCORE_LUT_FLUSH, SCORE_LUT_MULADD, SCORE_PERMUTE_DOT)
+                      OPT_DENSE_PAIR, OPT_EXPANDED_BYTES, OPT_TC_EXPANDED, OPT_TC_TILES, OPT_TC_WIDE, SCORE_AUTO, SCORE_LUT_FLUSH, SCORE_LUT_MULADD, SCORE_PERMUTE_DOT)
 
 __all__ = ["TurboQuantIndex", "IdMapIndex", "BATCH_CHUNK_SIZE"]
 

@@ -122,4 +122,4 @@ ERR_ID_KEYERROR = {21}
 ERR_INDEXERROR = {31}
 SCORE_AUTO, SCORE_PERMUTE_DOT, SCORE_LUT_MULADD, SCORE_LUT_FLUSH = 0, 1, 2, 3
 OPT_SCORE_MODE, OPT_MMA_MIN_BATCH, OPT_FORCE_CAREFUL, OPT_TC_TILES, OPT_INGEST_PIPELINE, OPT_PD_SPLIT = 1, 2, 3, 4, 5, 6
-OPT_SMALL_SCAN, OPT_FAIL_NEXT, OPT_TC_PAIR, OPT_TC_WIDE, OPT_TC_EXPANDED, OPT_EXPANDED_BYTES, OPT_DENSE_PAIR = 7, 8, 9, 10, 11, 12, 13
+OPT_SMALL_SCAN, OPT_FAIL_NEXT, OPT_TC_WIDE, OPT_TC_EXPANDED, OPT_EXPANDED_BYTES, OPT_DENSE_PAIR = 7, 8, 10, 11, 12, 13

@@ -256,7 +256,6 @@ struct tv_index {
     int tc_wide = 1;             // 1: batches above 256 queries share every expanded code slab between two query groups
     int tc_expanded = 1;         // 1: large permute-dot batches scan an int8 copy of the index when device memory has room for it; 0 never; 2 always (fail if it does not fit)
     int dense_pair = 1;          // 1: the scan over the int8 copy runs on CTA pairs (cta_group::2)
-    int tc_pair = 0;             // 1: permute-dot batches above 64 queries run the tensor-memory scan on CTA pairs (cta_group::2)
     int fail_next = 0;           // test hook (TV_OPT_FAIL_NEXT): the next device allocation / upload of a call reports failure
 
     cudaStream_t stream = nullptr;           // mutations and accessors
@@ -885,7 +884,7 @@ int plan_scan(tv_index *h, int mode, size_t nq, bool allow_tc, ScanPlan &plan) {
     // with the int8 copy of the index the tensor-memory scan is bound by reading it (2.85 ms at 33 queries on 10 M x 1536)
     // and beats the mma.sync scan of 17 - 32 queries (3.1 ms); without the copy it expands codes and does not (4.7 ms)
     bool copy_expected = false;
-    if (mode == TV_SCORE_PERMUTE_DOT && h->tc_expanded != 0 && !h->tc_pair) {
+    if (mode == TV_SCORE_PERMUTE_DOT && h->tc_expanded != 0) {
         std::lock_guard<std::mutex> g(h->expanded.mu);
         copy_expected = h->tc_expanded == 2 || h->expanded.refused_at_cap != h->code_blocks_cap * kBlock;
     }
@@ -975,7 +974,7 @@ int enqueue_search(tv_index *h, cudaStream_t st, Marks *marks, const SearchScrat
     sp.cb = cb; sp.wfrag = S.wfrag; sp.mtiles_total = mt_total; sp.luts = S.luts; sp.lut_pitch = int(S.lut_pitch);
     const bool use_small = plan.use_small && !plan.use_tc;
     bool use_dense = false;
-    if (plan.use_tc && !h->tc_pair && scan_tc_dense_supported(h->bits, mode, ng) && int(S.dim_pad) == expanded_pitch(int(h->dim))) {
+    if (plan.use_tc && scan_tc_dense_supported(h->bits, mode, ng) && int(S.dim_pad) == expanded_pitch(int(h->dim))) {
         int rc = expanded_sync(h, st, sp.level_words, &use_dense);
         if (rc != TV_OK) return rc;
     }
@@ -1017,8 +1016,6 @@ int enqueue_search(tv_index *h, cudaStream_t st, Marks *marks, const SearchScrat
             else if (use_dense)
                 TV_CUDA(launch_scan_tc_dense(sp, h->expanded.levels.ptr, h->expanded.rows_cap, S.weights, int(S.w_rows), int(S.dim_pad),
                                              h->sm_count, st));
-            else if (mode == TV_SCORE_PERMUTE_DOT && h->tc_pair && scan_tc_pair_supported(h->bits, mode, int(nq)))
-                TV_CUDA(launch_scan_tc_pair(sp, S.weights, int(S.w_rows), int(S.dim_pad), h->sm_count, st));
             else if (wide && mode == TV_SCORE_PERMUTE_DOT)
                 TV_CUDA(launch_scan_tc_wide(sp, S.weights, int(S.w_rows), int(S.dim_pad), h->sm_count, st));
             else if (wide)
@@ -1493,7 +1490,6 @@ int tv_set_option(tv_index *h, int option, int64_t value) {
         case TV_OPT_PD_SPLIT: h->pd_split = value != 0; return TV_OK;
         case TV_OPT_SMALL_SCAN: h->small_scan = value < 0 ? -1 : int(value & 7); return TV_OK;
         case TV_OPT_FAIL_NEXT: h->fail_next = value < 0 ? 0 : int(value); return TV_OK;
-        case TV_OPT_TC_PAIR: h->tc_pair = value != 0; return TV_OK;
         case TV_OPT_TC_WIDE: h->tc_wide = value != 0; return TV_OK;
         case TV_OPT_DENSE_PAIR: h->dense_pair = value != 0; return TV_OK;
         case TV_OPT_TC_EXPANDED:
@@ -1515,7 +1511,6 @@ int64_t tv_get_option(const tv_index *h, int option) {
         case TV_OPT_PD_SPLIT: return h->pd_split;
         case TV_OPT_SMALL_SCAN: return h->small_scan;
         case TV_OPT_FAIL_NEXT: return h->fail_next;
-        case TV_OPT_TC_PAIR: return h->tc_pair;
         case TV_OPT_TC_WIDE: return h->tc_wide;
         case TV_OPT_TC_EXPANDED: return h->tc_expanded;
         case TV_OPT_DENSE_PAIR: return h->dense_pair;

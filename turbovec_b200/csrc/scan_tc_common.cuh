@@ -1,4 +1,4 @@
-// Device-side pieces shared by the tensor-memory scans (scan_tc.cu: one CTA per work item; scan_tc2.cu: CTA pairs):
+// Device-side pieces shared by the tensor-memory scans (scan_tc.cu, scan_tc_wide.cu, scan_tc_dense.cu, scan_tc_dense2.cu):
 // constants of the MMA tiling, bounded mbarrier waits, the nibble -> int8 level lookup, shared-memory and
 // instruction descriptors, TMA and TMEM wrappers, and the float epilogue of the score families.
 #pragma once
@@ -114,7 +114,7 @@ __device__ __forceinline__ void tmem_ld8(uint32_t taddr, uint32_t (&r)[8]) {
                  : "r"(taddr));
 }
 
-// ---- CTA pairs (clusters of two, tcgen05 cta_group::2): used by scan_tc2.cu and scan_tc_dense2.cu ----
+// ---- CTA pairs (clusters of two, tcgen05 cta_group::2): scan_tc_dense2.cu ----
 __device__ __forceinline__ uint32_t cluster_ctarank() {
     uint32_t r;
     asm volatile("mov.u32 %0, %%cluster_ctarank;" : "=r"(r));
@@ -206,6 +206,67 @@ __device__ __forceinline__ int dismissal_bound(float qs, float qb, float t, floa
     if (!(lo < 2.0e9f)) return INT_MAX;
     if (lo < -2.0e9f) return INT_MIN;
     return __float2int_rd(lo);
+}
+
+
+// First chunk of an unfiltered search: the 32 accumulator columns of a piece (queries ql0 .. ql0 + 31 of one vector) go to
+// position `at` of their queries' candidate lists, every one of them.  qscale / qbias point at the piece's first column.
+template <bool ONEHOT>
+__device__ __forceinline__ void write_piece(const uint32_t (&acc)[32], const float *qscale, const float *qbias, bool fused, float vs,
+                                            bool live, int64_t slot, int ql0, int nq_end, uint32_t at, const CandidateBuffers &cb) {
+#pragma unroll
+    for (int j = 0; j < 32; ++j) {
+        const int ql = ql0 + j;
+        if (ql < nq_end) {
+            const float score = final_score<ONEHOT>(fused, acc[j], qscale[j], qbias[j], vs);
+            cb.cand[size_t(ql) * cb.cap + at] = live ? make_key(score, uint32_t(slot)) : kEmptyKey;
+        }
+    }
+}
+
+// Later chunks: one integer compare per column dismisses the piece unless some column could be a candidate
+// (dismissal_bound).  Each lane keeps the outcome per run of 8 columns; the runs that any lane of the warp flagged are
+// re-read from tensor memory (address `taddr` = the piece's first column) and scored exactly by the lanes that flagged
+// them, and the keys that beat the query's k-th key are appended to its candidate list.  All pointers are at the
+// piece's first column; every lane of the warp must call this.
+template <bool ONEHOT>
+__device__ __forceinline__ void sift_piece(const uint32_t (&acc)[32], const int *ibound, const float *qscale, const float *qbias,
+                                           const float *qthr, bool fused, float vs, bool live, int64_t slot, int ql0, uint32_t taddr,
+                                           const CandidateBuffers &cb) {
+    uint32_t runs = 0;
+    const int4 *pi = reinterpret_cast<const int4 *>(ibound);
+#pragma unroll
+    for (int j4 = 0; j4 < 8; ++j4) {
+        const int4 b = pi[j4];
+        const bool may = (int(acc[4 * j4 + 0]) >= b.x) | (int(acc[4 * j4 + 1]) >= b.y) | (int(acc[4 * j4 + 2]) >= b.z) |
+                         (int(acc[4 * j4 + 3]) >= b.w);
+        runs |= uint32_t(may) << (j4 >> 1);
+    }
+    if (!live) runs = 0;
+    const uint32_t warp_runs = __reduce_or_sync(0xffffffffu, runs);
+    if (warp_runs == 0) return;
+#pragma unroll 1
+    for (int c1 = 0; c1 < 32; c1 += 8) {
+        if (!((warp_runs >> (c1 >> 3)) & 1u)) continue;
+        uint32_t a8[8];
+        tmem_ld8(taddr + c1, a8);
+        asm volatile("tcgen05.wait::ld.sync.aligned;" ::: "memory");
+        if ((runs >> (c1 >> 3)) & 1u) {
+#pragma unroll
+            for (int e = 0; e < 8; ++e) {
+                const int c = c1 + e;
+                const float score = final_score<ONEHOT>(fused, a8[e], qscale[c], qbias[c], vs);
+                if (score >= qthr[c]) {
+                    const int ql = ql0 + c;
+                    const uint64_t key = make_key(score, uint32_t(slot));
+                    if (key < cb.thr[ql] && (cb.lo == nullptr || key >= cb.lo[ql])) {
+                        const uint32_t at = atomicAdd(&cb.cnt[ql], 1u);
+                        if (at < uint32_t(cb.cap)) cb.cand[size_t(ql) * cb.cap + at] = key;
+                    }
+                }
+            }
+        }
+    }
 }
 
 }  // namespace

@@ -210,58 +210,12 @@ scan_tc_dense_pair_kernel(ScanParams p, const __grid_constant__ CUtensorMap amap
                 if (p.dense) {
                     // first chunk of a search: every vector's key goes to the list position of its place in the chunk
                     const uint32_t at = ((vt * 2 + rank) * kBlocksPerCta) * 32u + uint32_t(row);
-                    if (have_row) {
-#pragma unroll
-                        for (int j = 0; j < 32; ++j) {
-                            const int c = c0 + j;
-                            const int ql = qg * kTileQueries + cbase + c;
-                            if (ql < p.q_base + p.nq) {
-                                const float score = final_score<ONEHOT>(fused, acc[j], qscale[c], qbias[c], vs);
-                                p.cb.cand[size_t(ql) * p.cb.cap + at] = live ? make_key(score, uint32_t(slot)) : kEmptyKey;
-                            }
-                        }
-                    }
+                    if (have_row)
+                        write_piece<ONEHOT>(acc, qscale + c0, qbias + c0, fused, vs, live, slot, qg * kTileQueries + cbase + c0, p.q_base + p.nq, at, p.cb);
                     continue;
                 }
-                // one integer compare per column dismisses the piece unless some column could be a candidate; the
-                // columns are tracked in four runs of 8, and only the runs that some lane flags are looked at again
-                uint32_t runs = 0;
-                {
-                    const int4 *pi = reinterpret_cast<const int4 *>(sh->ibound + cbase + c0);
-#pragma unroll
-                    for (int j4 = 0; j4 < 8; ++j4) {
-                        const int4 b = pi[j4];
-                        const bool may = (int(acc[4 * j4 + 0]) >= b.x) | (int(acc[4 * j4 + 1]) >= b.y) | (int(acc[4 * j4 + 2]) >= b.z) |
-                                         (int(acc[4 * j4 + 3]) >= b.w);
-                        runs |= uint32_t(may) << (j4 >> 1);
-                    }
-                    if (!live) runs = 0;
-                }
-                const uint32_t warp_runs = __reduce_or_sync(kFullMask, runs);
-                if (warp_runs == 0) continue;
-                // rare, warp-uniform: re-read the flagged runs and score their columns exactly
-#pragma unroll 1
-                for (int c1 = 0; c1 < 32; c1 += 8) {
-                    if (!((warp_runs >> (c1 >> 3)) & 1u)) continue;
-                    uint32_t a8[8];
-                    tmem_ld8(taddr + c0 + c1, a8);
-                    asm volatile("tcgen05.wait::ld.sync.aligned;" ::: "memory");
-                    if ((runs >> (c1 >> 3)) & 1u) {
-#pragma unroll
-                        for (int e = 0; e < 8; ++e) {
-                            const int c = c0 + c1 + e;
-                            const float score = final_score<ONEHOT>(fused, a8[e], qscale[c], qbias[c], vs);
-                            if (score >= qthr[c]) {
-                                const int ql = qg * kTileQueries + cbase + c;
-                                const uint64_t key = make_key(score, uint32_t(slot));
-                                if (key < p.cb.thr[ql] && (p.cb.lo == nullptr || key >= p.cb.lo[ql])) {
-                                    const uint32_t at = atomicAdd(&p.cb.cnt[ql], 1u);
-                                    if (at < uint32_t(p.cb.cap)) p.cb.cand[size_t(ql) * p.cb.cap + at] = key;
-                                }
-                            }
-                        }
-                    }
-                }
+                sift_piece<ONEHOT>(acc, sh->ibound + cbase + c0, qscale + c0, qbias + c0, qthr + c0, fused, vs, live, slot,
+                                   qg * kTileQueries + cbase + c0, taddr + c0, p.cb);
             }
             asm volatile("tcgen05.fence::before_thread_sync;" ::: "memory");
             __syncwarp();

@@ -133,10 +133,6 @@ cudaError_t launch_scan_tc_dense(const ScanParams &p, const int8_t *expanded, si
 // every query tile.
 cudaError_t launch_scan_tc_dense_pair(const ScanParams &p, const int8_t *expanded, size_t exp_rows, const int8_t *weights, int rows,
                                       int pitch, int sm_count, cudaStream_t s);
-// The same scan on CTA pairs (scan_tc2.cu): tcgen05.mma.cta_group::2, each CTA of a pair expands 128 vectors and loads
-// half of the query slab.  Permute-dot batches of more than 64 queries.
-bool scan_tc_pair_supported(int bits, int mode, int nq_total);
-cudaError_t launch_scan_tc_pair(const ScanParams &p, const int8_t *weights, int rows, int pitch, int sm_count, cudaStream_t s);
 // int8 rate (ops/s, multiply-add = 2) of back-to-back tcgen05 kind::i8 MMAs on shared-memory operands, one CTA per SM:
 // the tensor-pipe roofline of the permute-dot scan on this device.  0 on failure.
 double measure_int8_peak(int sm_count, double seconds, cudaStream_t s);
