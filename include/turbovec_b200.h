@@ -244,6 +244,37 @@ int tv_idtable_resolve(const tv_idtable *t, const uint64_t *ids, size_t n, uint6
 int tv_idtable_ids_of(const tv_idtable *t, const int64_t *slots, size_t n, uint64_t *ids_out);
 int tv_idtable_ids(const tv_idtable *t, uint64_t *ids_out, size_t capacity);
 
+/* ---- one handle over several GPUs of one process (csrc/multi.cpp).  No reference counterpart: the reference is a
+ * single-host library.  The handle owns one positional index per listed device (the same device may be listed more
+ * than once) and deals global slots to them round-robin in chunks of 32 * chunk_blocks slots (0 = 1,024 blocks; must
+ * be even), so every call below has the meaning of its single-device namesake over GLOBAL slot numbers: add /
+ * add_with_ids (lib.rs:1114, id_map.rs:373; all or nothing), swap_remove / remove (lib.rs:2864, id_map.rs:520; the
+ * globally last row moves into the hole, across devices if need be), search with a bool mask over global slots
+ * (lib.rs:1345) or an allowlist of ids (id_map.rs:664), contains / ids (id_map.rs:593, 631).  A search runs every
+ * shard's scan at the same time (tv_search_device_keys, one host thread per shard) and merges the result keys on the
+ * first device (tv_merge_keys_device_chunked); results are identical to one index holding all the rows.
+ * kind = TV_KIND_IDMAP keeps the id tables (tv_idtable_*) beside the shards.  Limits: shards * min(k, len) <= 8192;
+ * one call at a time per handle (the handle serialises them).  tv_multi_shard gives a shard's index for options and
+ * inspection (do not add to or remove from it directly). ---- */
+typedef struct tv_multi tv_multi;
+int tv_multi_create(size_t dim, int bit_width, int kind, const int *device_ids, int n_devices, size_t chunk_blocks, tv_multi **out);
+void tv_multi_destroy(tv_multi *m);
+const char *tv_multi_last_error(const tv_multi *m);        /* m == NULL: the last failed create of this thread */
+uint64_t tv_multi_error_id(const tv_multi *m);             /* id of the last id error (already present / duplicate / unknown) */
+size_t tv_multi_len(const tv_multi *m);
+int tv_multi_shards(const tv_multi *m);
+tv_index *tv_multi_shard(tv_multi *m, int i);
+int tv_multi_add(tv_multi *m, const float *vectors, size_t n, size_t dim);
+int tv_multi_add_with_ids(tv_multi *m, const float *vectors, size_t n, size_t dim, const uint64_t *ids);
+int tv_multi_swap_remove(tv_multi *m, size_t slot, size_t *moved_from);
+int tv_multi_remove(tv_multi *m, uint64_t id, int *removed);
+int tv_multi_contains(const tv_multi *m, uint64_t id, int *present);
+int tv_multi_ids(const tv_multi *m, uint64_t *ids_out, size_t capacity);
+int tv_multi_search(tv_multi *m, const float *queries, size_t nq, size_t dim, size_t k, const uint8_t *mask_bool, size_t mask_len,
+                    float *scores_out, int64_t *slots_out, size_t *k_eff);
+int tv_multi_search_allowlist(tv_multi *m, const float *queries, size_t nq, size_t dim, size_t k, const uint64_t *allow_ids,
+                              size_t n_allow, float *scores_out, uint64_t *ids_out, size_t *k_eff);
+
 /* Search that performs no allocation of any kind.  This entry point has no counterpart in the reference:
  * it exists for callers that must not reach the CUDA allocator while they serve — latency-critical loops
  * (cudaMalloc locks the device and may synchronise it), processes whose device memory is fully handed out,

@@ -14,7 +14,7 @@ from . import _native
 from ._native import (OPT_FAIL_NEXT, OPT_FORCE_CAREFUL, OPT_INGEST_PIPELINE, OPT_MMA_MIN_BATCH, OPT_PD_SPLIT, OPT_SCORE_MODE, OPT_SMALL_SCAN,
                       OPT_DENSE_PAIR, OPT_EXPANDED_BYTES, OPT_TC_EXPANDED, OPT_TC_TILES, OPT_TC_WIDE, SCORE_AUTO, SCORE_LUT_FLUSH, SCORE_LUT_MULADD, SCORE_PERMUTE_DOT)
 
-__all__ = ["TurboQuantIndex", "IdMapIndex", "BATCH_CHUNK_SIZE"]
+__all__ = ["TurboQuantIndex", "IdMapIndex", "MultiGpuIndex", "BATCH_CHUNK_SIZE"]
 
 # turbovec-python/python/turbovec/__init__.py:17 — batches above this are fed in slices
 BATCH_CHUNK_SIZE = 4096
@@ -478,6 +478,119 @@ class IdMapIndex(_Base):
 
 
 EMPTY_KEY = 0xFFFFFFFFFFFFFFFF
+
+
+class MultiGpuIndex:
+    """One index over several GPUs of this process (tv_multi_*): the rows are dealt to the devices round-robin in
+    chunks of 32 * chunk_blocks global slots, a search scans every device at the same time and merges on the first
+    one.  `id_mapped=False` mirrors TurboQuantIndex (add / search(mask=) / swap_remove over global slots),
+    `id_mapped=True` mirrors IdMapIndex (add_with_ids / search(allowlist=) / remove / contains / ids).  Results are
+    identical to a single index holding all the rows.  A device may be listed more than once."""
+
+    def __init__(self, dim: int, bit_width: int = 4, *, devices=(0,), id_mapped: bool = False, chunk_blocks: int = 1024):
+        self._lib = _native.load()
+        self._h = C.c_void_p()
+        self._idmap = bool(id_mapped)
+        devs = (C.c_int * len(devices))(*[int(d) for d in devices])
+        rc = self._lib.tv_multi_create(_size("dim", dim), int(bit_width), 1 if id_mapped else 0, devs, len(devices), int(chunk_blocks),
+                                       C.byref(self._h))
+        if rc != 0:
+            raise (RuntimeError if rc >= 90 else ValueError)(self._lib.tv_multi_last_error(None).decode())
+
+    def __del__(self):
+        h, self._h = getattr(self, "_h", None), None
+        if h:
+            self._lib.tv_multi_destroy(h)
+
+    def _check(self, rc: int):
+        if rc == 0:
+            return
+        msg = self._lib.tv_multi_last_error(self._h).decode()
+        if rc == 21:
+            raise KeyError(msg)
+        if rc == 31:
+            raise IndexError(msg)
+        raise (RuntimeError if rc >= 90 else ValueError)(msg)
+
+    def __len__(self) -> int:
+        return int(self._lib.tv_multi_len(self._h))
+
+    @property
+    def n_shards(self) -> int:
+        return int(self._lib.tv_multi_shards(self._h))
+
+    def shard_len(self, i: int) -> int:
+        return int(self._lib.tv_len(self._lib.tv_multi_shard(self._h, int(i))))
+
+    def set_shard_option(self, option: int, value: int) -> None:
+        for i in range(self.n_shards):
+            rc = self._lib.tv_set_option(self._lib.tv_multi_shard(self._h, i), int(option), int(value))
+            if rc != 0:
+                raise ValueError(f"option {option} refused by shard {i}")
+
+    def add(self, vectors: np.ndarray) -> None:
+        vectors = _f32_2d("vectors", vectors)
+        self._check(self._lib.tv_multi_add(self._h, _ptr(vectors), vectors.shape[0], vectors.shape[1]))
+
+    def add_with_ids(self, vectors: np.ndarray, ids: np.ndarray) -> None:
+        vectors = _f32_2d("vectors", vectors)
+        ids = _typed_1d("ids", ids, np.uint64, "uint64")
+        if ids.size != vectors.shape[0]:
+            raise ValueError(f"ids length {ids.size} does not match number of vectors {vectors.shape[0]}")
+        self._check(self._lib.tv_multi_add_with_ids(self._h, _ptr(vectors), vectors.shape[0], vectors.shape[1], _ptr(ids)))
+
+    def swap_remove(self, idx: int) -> int:
+        moved = C.c_size_t(0)
+        self._check(self._lib.tv_multi_swap_remove(self._h, _size("idx", idx), C.byref(moved)))
+        return int(moved.value)
+
+    def remove(self, id: int) -> bool:
+        removed = C.c_int(0)
+        self._check(self._lib.tv_multi_remove(self._h, int(id), C.byref(removed)))
+        return bool(removed.value)
+
+    def contains(self, id: int) -> bool:
+        present = C.c_int(0)
+        self._check(self._lib.tv_multi_contains(self._h, int(id), C.byref(present)))
+        return bool(present.value)
+
+    __contains__ = contains
+
+    def ids(self) -> np.ndarray:
+        out = np.empty(len(self), np.uint64)
+        self._check(self._lib.tv_multi_ids(self._h, _ptr(out), out.size))
+        return out
+
+    def search(self, queries: np.ndarray, k: int, *, mask=None, allowlist=None):
+        """(scores, slots) or, id-mapped, (scores, ids); rows are min(k, len, n_allowed) wide."""
+        queries = _f32_2d("queries", queries)
+        k = _size("k", k)
+        nq, dim = queries.shape
+        width = max(min(k, len(self)), 1)
+        scores = np.empty((nq, width), np.float32)
+        k_eff = C.c_size_t(0)
+        if self._idmap:
+            if mask is not None:
+                raise TypeError("an id-mapped index is filtered by allowlist=")
+            out = np.empty((nq, width), np.uint64)
+            ptr, count = None, 0
+            if allowlist is not None:
+                allowlist = _typed_1d("allowlist", allowlist, np.uint64, "uint64")
+                if allowlist.size == 0:
+                    raise ValueError("allowlist is empty")
+                ptr, count = _ptr(allowlist), allowlist.size
+            self._check(self._lib.tv_multi_search_allowlist(self._h, _ptr(queries), nq, dim, k, ptr, count, _ptr(scores), _ptr(out), C.byref(k_eff)))
+        else:
+            if allowlist is not None:
+                raise TypeError("a positional index is filtered by mask=")
+            out = np.empty((nq, width), np.int64)
+            ptr, count = None, 0
+            if mask is not None:
+                mask = _typed_1d("mask", mask, np.bool_, "bool")
+                ptr, count = _ptr(mask), mask.size
+            self._check(self._lib.tv_multi_search(self._h, _ptr(queries), nq, dim, k, ptr, count, _ptr(scores), _ptr(out), C.byref(k_eff)))
+        ke = int(k_eff.value)
+        return (scores.ravel()[: nq * ke].reshape(nq, ke).copy(), out.ravel()[: nq * ke].reshape(nq, ke).copy())
 
 
 def measure_int8_peak(device: int = 0, seconds: float = 0.0) -> float:

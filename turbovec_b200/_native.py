@@ -34,6 +34,21 @@ SIGNATURES = {
     "tv_idtable_resolve": (C.c_int, [_H, C.c_void_p, C.c_size_t, C.c_void_p]),
     "tv_idtable_ids_of": (C.c_int, [_H, C.c_void_p, C.c_size_t, C.c_void_p]),
     "tv_idtable_ids": (C.c_int, [_H, C.c_void_p, C.c_size_t]),
+    "tv_multi_create": (C.c_int, [C.c_size_t, C.c_int, C.c_int, C.POINTER(C.c_int), C.c_int, C.c_size_t, C.POINTER(_H)]),
+    "tv_multi_destroy": (None, [_H]),
+    "tv_multi_last_error": (C.c_char_p, [_H]),
+    "tv_multi_error_id": (C.c_uint64, [_H]),
+    "tv_multi_len": (C.c_size_t, [_H]),
+    "tv_multi_shards": (C.c_int, [_H]),
+    "tv_multi_shard": (_H, [_H, C.c_int]),
+    "tv_multi_add": (C.c_int, [_H, C.c_void_p, C.c_size_t, C.c_size_t]),
+    "tv_multi_add_with_ids": (C.c_int, [_H, C.c_void_p, C.c_size_t, C.c_size_t, C.c_void_p]),
+    "tv_multi_swap_remove": (C.c_int, [_H, C.c_size_t, _szp]),
+    "tv_multi_remove": (C.c_int, [_H, C.c_uint64, C.POINTER(C.c_int)]),
+    "tv_multi_contains": (C.c_int, [_H, C.c_uint64, C.POINTER(C.c_int)]),
+    "tv_multi_ids": (C.c_int, [_H, C.c_void_p, C.c_size_t]),
+    "tv_multi_search": (C.c_int, [_H, C.c_void_p, C.c_size_t, C.c_size_t, C.c_size_t, C.c_void_p, C.c_size_t, C.c_void_p, C.c_void_p, _szp]),
+    "tv_multi_search_allowlist": (C.c_int, [_H, C.c_void_p, C.c_size_t, C.c_size_t, C.c_size_t, C.c_void_p, C.c_size_t, C.c_void_p, C.c_void_p, _szp]),
     "tv_quantise_grid_lookup": (C.c_int, [C.POINTER(C.c_float), C.c_int, C.POINTER(C.c_float), C.c_size_t, C.POINTER(C.c_uint8)]),
     "tv_index_create": (C.c_int, [C.c_size_t, C.c_int, C.c_int, C.c_int, C.POINTER(_H)]),
     "tv_index_destroy": (None, [_H]),

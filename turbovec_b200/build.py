@@ -12,7 +12,7 @@ import sys
 HERE = os.path.dirname(os.path.abspath(__file__))
 CSRC = os.path.join(HERE, "csrc")
 LIB = os.path.join(HERE, "libturbovec_b200.so")
-SOURCES = ["host_tables.cpp", "io_v7.cpp", "idtable.cpp", "ingest.cu", "ingest_fast.cu", "quantile.cu", "search.cu", "scan_small.cu", "scan_tc.cu", "scan_tc_wide.cu", "scan_tc_dense.cu", "scan_tc_dense2.cu", "index.cu"]
+SOURCES = ["host_tables.cpp", "io_v7.cpp", "idtable.cpp", "multi.cpp", "ingest.cu", "ingest_fast.cu", "quantile.cu", "search.cu", "scan_small.cu", "scan_tc.cu", "scan_tc_wide.cu", "scan_tc_dense.cu", "scan_tc_dense2.cu", "index.cu"]
 ARCH = ["-gencode", "arch=compute_100a,code=sm_100a"]
 # -fmad=false: the reference never contracts a multiply and an add; fused operations are written
 # explicitly (fmaf) where the reference has an explicit fma.
