@@ -389,7 +389,7 @@ def test_injected_failure_leaves_the_index_unchanged(T):
     assert np.array_equal(idx.codes_blocked_seq()[:full], codes[:full])
 
 
-# ------------------------------------------------------------------ BASELINE configuration 1 at its stated size
+# ------------------------------------------------------------------ the reference's CPU-runnable workload at its stated size
 def test_reference_workload_config1_full_size(T):
     """100,000 x 1536 4-bit, 1,000 queries, k = 10, single queries and one batch of 1,000: ids and scores against the
     multithreaded CPU restatement of the reference's permute-dot kernel on every query, and against the scalar
