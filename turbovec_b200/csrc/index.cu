@@ -2066,13 +2066,21 @@ int tv_export_blocked(const tv_index *hc, uint8_t *blocked_out, size_t blocked_c
 int tv_export_packed(const tv_index *hc, uint8_t *packed_out, size_t capacity) {
     tv_index *h = const_cast<tv_index *>(hc);
     if (!h) return TV_ERR_INVALID_ARGUMENT;
-    if (h->n == 0) return TV_OK;
-    const size_t need = h->n * size_t(h->bits) * h->dim / 8;
+    size_t n, dim, blocked_bytes;
+    {
+        // a consistent view of the sizes; the export below takes the lock itself and refuses a buffer that a
+        // concurrent add has made too small
+        std::shared_lock<std::shared_mutex> lock(h->mu);
+        n = h->n; dim = h->dim;
+        blocked_bytes = tv_blocked_bytes(h);
+    }
+    if (n == 0) return TV_OK;
+    const size_t need = n * size_t(h->bits) * dim / 8;
     if (!packed_out || capacity < need) return fail(h, TV_ERR_INVALID_ARGUMENT, "output buffer too small");
-    std::vector<uint8_t> blocked(tv_blocked_bytes(h));
+    std::vector<uint8_t> blocked(blocked_bytes);
     int rc = tv_export_blocked(h, blocked.data(), blocked.size(), nullptr, 0);
     if (rc != TV_OK) return rc;
-    blocked_to_packed(blocked.data(), h->n, h->bits, int(h->dim), packed_out);
+    blocked_to_packed(blocked.data(), n, h->bits, int(dim), packed_out);
     return TV_OK;
 }
 
@@ -2363,6 +2371,7 @@ int tv_v7_plan_sync(size_t n_synced, size_t n, const size_t *pending, size_t n_p
 // Introspection of the sync binding (tests): bound flag, generation and the sizes of the two dirty sets.
 int tv_sync_state(const tv_index *h, int *bound, uint64_t *generation, size_t *n_pending, size_t *n_fresh) {
     if (!h) return TV_ERR_INVALID_ARGUMENT;
+    std::shared_lock<std::shared_mutex> lock(const_cast<tv_index *>(h)->mu);
     if (bound) *bound = h->sync_bound ? 1 : 0;
     if (generation) *generation = h->sync_cursor.gen;
     if (n_pending) *n_pending = h->sync_pending.size();
