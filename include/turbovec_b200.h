@@ -98,7 +98,8 @@ enum {
 enum {
     TV_OPT_SCORE_MODE = 1,      /* one of TV_SCORE_* */
     TV_OPT_MMA_MIN_BATCH = 2,   /* query batches of at least this size use the tensor-memory scan; 0 = never;
-                                 * -1 (default) = measured switch points: 33 (permute-dot), 8 (u8-LUT families) */
+                                 * -1 (default) = measured switch points: permute-dot 17 with the int8 copy of the index
+                                 * (TV_OPT_TC_EXPANDED) and 33 without it, u8-LUT families 8 */
     TV_OPT_FORCE_CAREFUL = 3,   /* 1: run the candidate-overflow recovery schedule always (testing) */
     TV_OPT_TC_TILES = 4,        /* accumulator tiles of 128 vectors per query slab in the tensor-memory scan: 1 or 2 */
     TV_OPT_INGEST_PIPELINE = 5, /* 1 (default): whole code blocks are encoded by the pipelined ingest kernel; 0: never;
